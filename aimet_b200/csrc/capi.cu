@@ -1,0 +1,369 @@
+// extern "C" surface of libaimet_b200.so: argument validation, host-side encoding arithmetic and dispatch into
+// the kernels.  No torch types, no allocation, no implicit synchronisation.
+#include <float.h>
+#include <math.h>
+#include <string.h>
+
+#include <atomic>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace aq
+{
+// ---- launch accounting / error text ----------------------------------------------------------------
+static std::atomic<int64_t> g_launches {0};
+static thread_local char g_cuda_error[256] = "";
+
+void note_launch()
+{
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+int cuda_fail(cudaError_t e)
+{
+    strncpy(g_cuda_error, cudaGetErrorString(e), sizeof(g_cuda_error) - 1);
+    g_cuda_error[sizeof(g_cuda_error) - 1] = 0;
+    return AQ_ERR_CUDA;
+}
+int check_launch()
+{
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? AQ_OK : cuda_fail(e);
+}
+
+// ---- host arithmetic ---------------------------------------------------------------------------------
+// std::max / std::min with the reference's argument order (decides NaN and signed-zero behaviour)
+static inline double hmax(double a, double b)
+{
+    return (a < b) ? b : a;
+}
+static inline double hmin(double a, double b)
+{
+    return (b < a) ? b : a;
+}
+
+static void fill_encoding(int bw, double mn, double mx, aq_encoding_t* e)
+{
+    mn = hmin(mn, 0.0);
+    mx = hmax(mx, 0.0);
+    mx = hmax(mx, mn + 1e-5);
+    double steps = pow(2.0, (double) (uint8_t) bw) - 1.0;
+    if (mn == -mx)
+        steps -= 1.0;
+    e->bw     = bw;
+    e->delta  = (mx - mn) / steps;
+    e->offset = round(mn / e->delta);
+    e->min    = e->offset * e->delta;
+    e->max    = e->delta * steps + e->min;
+}
+
+static void computed_encodings(int bw, double mn, double mx, bool sym, bool strict, bool unsigned_sym,
+                               aq_encoding_t* e)
+{
+    double steps = pow(2.0, (double) (uint8_t) bw) - 1.0;
+    if (sym && strict)
+        steps -= 1.0;
+    e->bw = bw;
+    if (isinf(mn))
+        mn = -(double) FLT_MAX;
+    if (isinf(mx))
+        mx = (double) FLT_MAX;
+    if (sym && (mn < 0.0 || !unsigned_sym))
+    {
+        const double amax          = hmax(fabs(mx), fabs(mn));
+        const unsigned int pos     = (unsigned int) floor(steps / 2.0);
+        e->delta                   = amax / pos;
+        e->offset                  = -ceil(steps / 2.0);
+        e->min                     = hmax(e->offset * e->delta, -(double) FLT_MAX);
+        e->max                     = hmin(e->delta * pos, (double) FLT_MAX);
+        return;
+    }
+    e->delta = (mx - mn) / steps;
+    if (mn < 0 && mx > 0)
+    {
+        double zero_code = round(-mn / e->delta);
+        zero_code        = hmin(steps, hmax(0.0, zero_code));
+        e->offset        = -zero_code;
+        const double lo  = e->delta * e->offset;
+        e->min           = (lo >= -(double) FLT_MAX && lo <= (double) FLT_MAX) ? lo : -(double) FLT_MAX;
+        e->max           = mx - mn + e->min;
+        if (e->max > (double) FLT_MAX)
+            e->max = (double) FLT_MAX;
+    }
+    else
+    {
+        e->offset = round(mn / e->delta);
+        e->min    = mn;
+        e->max    = mx;
+    }
+}
+
+static inline bool bad_geom(int64_t n, int64_t num_ch, int64_t inner)
+{
+    return n < 0 || num_ch < 1 || inner < 1 || (num_ch > 1 && (n % inner) != 0);
+}
+}   // namespace aq
+
+using namespace aq;
+
+extern "C"
+{
+int aq_version(void)
+{
+    return 100;
+}
+
+const char* aq_status_string(int s)
+{
+    switch (s)
+    {
+    case AQ_OK: return "ok";
+    case AQ_ERR_INVALID_ARG: return "invalid argument";
+    case AQ_ERR_UNSUPPORTED: return "unsupported combination";
+    case AQ_ERR_CUDA: return "CUDA error";
+    case AQ_ERR_WORKSPACE: return "workspace missing or too small";
+    case AQ_ERR_TOO_LARGE: return "size beyond the documented maximum";
+    default: return "unknown status";
+    }
+}
+
+const char* aq_last_cuda_error(void)
+{
+    return g_cuda_error;
+}
+
+int64_t aq_launch_count(void)
+{
+    return g_launches.load(std::memory_order_relaxed);
+}
+
+int aq_fill_encoding(int bw, double enc_min, double enc_max, aq_encoding_t* h_out)
+{
+    if (!h_out || bw < 1 || bw > 32)
+        return AQ_ERR_INVALID_ARG;
+    fill_encoding(bw, enc_min, enc_max, h_out);
+    return AQ_OK;
+}
+
+int aq_computed_encodings(int bw, double mn, double mx, int symmetric, int strict, int unsigned_sym,
+                          aq_encoding_t* h_out)
+{
+    if (!h_out || bw < 1 || bw > 32)
+        return AQ_ERR_INVALID_ARG;
+    computed_encodings(bw, mn, mx, symmetric != 0, strict != 0, unsigned_sym != 0, h_out);
+    return AQ_OK;
+}
+
+int aq_minmax_encoding(int bw, double stat_min, double stat_max, int symmetric, int strict, int unsigned_sym,
+                       aq_encoding_t* h_out)
+{
+    if (!h_out || bw < 1 || bw > 32)
+        return AQ_ERR_INVALID_ARG;
+    const double mn = hmin(0.0, stat_min);
+    double mx       = hmax(0.0, stat_max);
+    mx              = hmax(mx, mn + 0.01);
+    computed_encodings(bw, mn, mx, symmetric != 0, strict != 0, unsigned_sym != 0, h_out);
+    return AQ_OK;
+}
+
+int aq_qdq_per_tensor(const float* d_in, float* d_out, int64_t n, double enc_min, double enc_max, int bw,
+                      int rounding_mode, void* stream)
+{
+    if (n < 0 || (n > 0 && (!d_in || !d_out)) || bw < 1 || bw > 32)
+        return AQ_ERR_INVALID_ARG;
+    if (rounding_mode != AQ_ROUND_NEAREST)
+        return AQ_ERR_UNSUPPORTED;
+    aq_encoding_t e;
+    fill_encoding(bw, enc_min, enc_max, &e);
+    return pymo_per_tensor(d_in, d_out, n, (float) e.min, (float) e.max, (float) e.delta, (float) e.offset, 0, 0.0f,
+                           (cudaStream_t) stream);
+}
+
+int aq_quantize_per_tensor(const float* d_in, float* d_out, int64_t n, double enc_min, double enc_max, int bw,
+                           int rounding_mode, int shift_to_signed, void* stream)
+{
+    if (n < 0 || (n > 0 && (!d_in || !d_out)) || bw < 1 || bw > 32)
+        return AQ_ERR_INVALID_ARG;
+    if (rounding_mode != AQ_ROUND_NEAREST)
+        return AQ_ERR_UNSUPPORTED;
+    aq_encoding_t e;
+    fill_encoding(bw, enc_min, enc_max, &e);
+    unsigned int shift = 0;
+    if (shift_to_signed)
+        shift = (unsigned int) pow(2.0, (double) (bw - 1));
+    return pymo_per_tensor(d_in, d_out, n, (float) e.min, (float) e.max, (float) e.delta, (float) e.offset, 1,
+                           (float) shift, (cudaStream_t) stream);
+}
+
+int aq_qdq_per_channel(const float* d_in, float* d_out, int64_t n, int64_t num_ch, int64_t inner,
+                       const float* d_enc_min, const float* d_enc_max, double num_steps, int rounding_mode,
+                       void* stream)
+{
+    if (bad_geom(n, num_ch, inner) || (n > 0 && (!d_in || !d_out)) || !d_enc_min || !d_enc_max || !(num_steps >= 1))
+        return AQ_ERR_INVALID_ARG;
+    if (rounding_mode != AQ_ROUND_NEAREST)
+        return AQ_ERR_UNSUPPORTED;
+    return pymo_per_channel(d_in, d_out, n, num_ch, inner, d_enc_min, d_enc_max, nullptr, nullptr, (float) num_steps,
+                            1, (cudaStream_t) stream);
+}
+
+int aq_qdq_broadcast(const float* d_in, float* d_out, int64_t n, int64_t ndims, const int64_t* h_in_strides,
+                     const int64_t* h_enc_strides, const float* d_enc_min, const float* d_enc_max,
+                     const float* d_enc_delta, const float* d_enc_offset, void* stream)
+{
+    if (n < 0 || ndims < 1 || ndims > 8 || !h_in_strides || !h_enc_strides || (n > 0 && (!d_in || !d_out)) ||
+        !d_enc_min || !d_enc_max || !d_enc_delta || !d_enc_offset)
+        return AQ_ERR_INVALID_ARG;
+    for (int64_t d = 0; d < ndims; ++d)
+        if (h_in_strides[d] < 1 || h_enc_strides[d] < 0)
+            return AQ_ERR_INVALID_ARG;
+    // Fast path: the non-broadcast dimensions form one contiguous group [first, last] whose encodings are laid out
+    // row-major, i.e. enc_stride[d] * inner == in_stride[d] with inner = in_stride[last].  Then the encoding
+    // index is (i / inner) % num_ch and the staged per-channel kernel applies.
+    int first = -1, last = -1;
+    for (int d = 0; d < ndims; ++d)
+        if (h_enc_strides[d] != 0)
+        {
+            if (first < 0)
+                first = d;
+            last = d;
+        }
+    if (first >= 0)
+    {
+        const int64_t inner = h_in_strides[last];
+        bool fast           = true;
+        for (int d = first; d <= last; ++d)
+            if (h_enc_strides[d] * inner != h_in_strides[d])
+                fast = false;
+        const int64_t span = (first == 0) ? n : h_in_strides[first - 1];
+        if (fast && span % inner == 0 && n % inner == 0 && (n / inner) % (span / inner) == 0)
+            return pymo_per_channel(d_in, d_out, n, span / inner, inner, d_enc_min, d_enc_max, d_enc_delta,
+                                    d_enc_offset, 0.0f, 0, (cudaStream_t) stream);
+    }
+    BroadcastArgs a;
+    a.in = d_in, a.out = d_out, a.n = n, a.ndims = (int) ndims;
+    for (int d = 0; d < 8; ++d)
+    {
+        a.in_strides[d]  = d < ndims ? h_in_strides[d] : 1;
+        a.enc_strides[d] = d < ndims ? h_enc_strides[d] : 0;
+    }
+    a.mn = d_enc_min, a.mx = d_enc_max, a.dl = d_enc_delta, a.of = d_enc_offset;
+    return pymo_broadcast(a, (cudaStream_t) stream);
+}
+
+int aq_ste_backward_v1(const float* d_x, const float* d_grad, float* d_dx, int64_t n, int64_t num_ch, int64_t inner,
+                       const float* d_enc_min, const float* d_enc_max, void* stream)
+{
+    if (bad_geom(n, num_ch, inner) || (n > 0 && (!d_x || !d_grad || !d_dx)) || !d_enc_min || !d_enc_max)
+        return AQ_ERR_INVALID_ARG;
+    SteArgs a;
+    a.x = d_x, a.g = d_grad, a.dx = d_dx, a.n = n, a.enc_min = d_enc_min, a.enc_max = d_enc_max;
+    a.geom.num_ch = num_ch, a.geom.inner = inner;
+    return ste_v1(a, (cudaStream_t) stream);
+}
+
+int aq_v2_quantize(const void* d_x, void* d_y, uint8_t* d_mask, int dtype, int64_t n, int64_t num_ch, int64_t inner,
+                   const float* d_scale, const float* d_offset, double qmin, double qmax, int out_kind,
+                   int internal_f16, void* stream)
+{
+    if (bad_geom(n, num_ch, inner) || (n > 0 && (!d_x || !d_y)) || !d_scale || !d_offset || qmin > qmax ||
+        (out_kind != AQ_V2_OUT_QDQ && out_kind != AQ_V2_OUT_CODES) || dtype < AQ_F32 || dtype > AQ_BF16)
+        return AQ_ERR_INVALID_ARG;
+    if (internal_f16 && dtype != AQ_F16)
+        return AQ_ERR_UNSUPPORTED;
+    // the grid bounds must be exact in the internal dtype (the caller checks representability like the reference)
+    if ((double) (float) qmin != qmin || (double) (float) qmax != qmax)
+        return AQ_ERR_UNSUPPORTED;
+    V2Args a;
+    a.x = d_x, a.y = d_y, a.mask = d_mask, a.n = n, a.scale = d_scale, a.offset = d_offset;
+    a.qmin = (float) qmin, a.qmax = (float) qmax, a.out_kind = out_kind, a.dequant_only = 0;
+    a.geom.num_ch = num_ch, a.geom.inner = inner;
+    return v2_launch(a, dtype, internal_f16, (cudaStream_t) stream);
+}
+
+int aq_v2_dequantize(const void* d_x, void* d_y, int dtype, int64_t n, int64_t num_ch, int64_t inner,
+                     const float* d_scale, const float* d_offset, int internal_f16, void* stream)
+{
+    if (bad_geom(n, num_ch, inner) || (n > 0 && (!d_x || !d_y)) || !d_scale || !d_offset || dtype < AQ_F32 ||
+        dtype > AQ_BF16)
+        return AQ_ERR_INVALID_ARG;
+    if (internal_f16 && dtype != AQ_F16)
+        return AQ_ERR_UNSUPPORTED;
+    V2Args a;
+    a.x = d_x, a.y = d_y, a.mask = nullptr, a.n = n, a.scale = d_scale, a.offset = d_offset;
+    a.qmin = 0, a.qmax = 0, a.out_kind = AQ_V2_OUT_QDQ, a.dequant_only = 1;
+    a.geom.num_ch = num_ch, a.geom.inner = inner;
+    return v2_launch(a, dtype, internal_f16, (cudaStream_t) stream);
+}
+
+int aq_v2_qdq_backward(const void* d_grad, const uint8_t* d_mask, void* d_dx, int dtype, int64_t n, void* stream)
+{
+    if (n < 0 || (n > 0 && (!d_grad || !d_mask || !d_dx)) || dtype < AQ_F32 || dtype > AQ_BF16)
+        return AQ_ERR_INVALID_ARG;
+    return v2_backward(d_grad, d_mask, d_dx, dtype, n, (cudaStream_t) stream);
+}
+
+int64_t aq_minmax_workspace_bytes(int64_t n, int64_t num_ch, int64_t inner)
+{
+    if (bad_geom(n, num_ch, inner))
+        return AQ_ERR_INVALID_ARG;
+    return minmax_workspace_bytes(n, num_ch, inner);
+}
+
+int aq_minmax(const void* d_x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* d_out_min,
+              float* d_out_max, int propagate_nan, void* d_workspace, int64_t workspace_bytes, void* stream)
+{
+    if (bad_geom(n, num_ch, inner) || (n > 0 && !d_x) || !d_out_min || !d_out_max || dtype < AQ_F32 ||
+        dtype > AQ_BF16)
+        return AQ_ERR_INVALID_ARG;
+    if (num_ch > 1 && n / inner % num_ch != 0)
+        return AQ_ERR_INVALID_ARG;
+    if (!d_workspace || ((uintptr_t) d_workspace % 256) != 0)
+        return AQ_ERR_WORKSPACE;
+    return minmax_dispatch(d_x, dtype, n, num_ch, inner, d_out_min, d_out_max, propagate_nan, d_workspace,
+                           workspace_bytes, (cudaStream_t) stream);
+}
+
+int aq_tfe_init_grid(const float* d_minmax, aq_tfe_state_t* d_state, void* stream)
+{
+    if (!d_minmax || !d_state)
+        return AQ_ERR_INVALID_ARG;
+    return tfe_init_grid(d_minmax, d_state, (cudaStream_t) stream);
+}
+
+int aq_tfe_histogram(const float* d_x, int64_t n, const aq_tfe_state_t* d_state, uint32_t* d_hist, int64_t* d_count,
+                     void* stream)
+{
+    if (n < 0 || (n > 0 && !d_x) || !d_state || !d_hist)
+        return AQ_ERR_INVALID_ARG;
+    if (n > 0x7fffffffLL)
+        return AQ_ERR_TOO_LARGE;   // the reference counts elements in an int; so does the PDF replay
+    return tfe_histogram(d_x, n, d_state, d_hist, d_count, (cudaStream_t) stream);
+}
+
+int aq_tfe_pdf_replay(const uint32_t* d_hists, const int64_t* d_counts, int64_t num_batches, double* d_pdf,
+                      int32_t* d_iterations, void* stream)
+{
+    if (num_batches < 0 || (num_batches > 0 && (!d_hists || !d_counts)) || !d_pdf || !d_iterations)
+        return AQ_ERR_INVALID_ARG;
+    return tfe_pdf_replay(d_hists, d_counts, num_batches, d_pdf, d_iterations, (cudaStream_t) stream);
+}
+
+int64_t aq_tfe_search_workspace_bytes(void)
+{
+    return tfe_search_workspace_bytes();
+}
+
+int aq_tfe_search(const aq_tfe_state_t* d_state, const double* d_pdf, int stats_updated, int bw, int symmetric,
+                  int strict, int unsigned_sym, double* d_out_encoding, void* d_workspace, int64_t workspace_bytes,
+                  void* stream)
+{
+    if (!d_state || !d_pdf || !d_out_encoding || bw < 1 || bw > 32)
+        return AQ_ERR_INVALID_ARG;
+    if (!d_workspace || ((uintptr_t) d_workspace % 256) != 0)
+        return AQ_ERR_WORKSPACE;
+    return tfe_search(d_state, d_pdf, stats_updated, bw, symmetric, strict, unsigned_sym, d_out_encoding,
+                      d_workspace, workspace_bytes, (cudaStream_t) stream);
+}
+
+}   // extern "C"

@@ -1,0 +1,152 @@
+// Shared device helpers for the aimet_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/aimet_b200.h"
+
+namespace aq
+{
+
+constexpr int kNumSMs = 148;   // B200: 2 dies x 74 SMs
+
+// ---- launch accounting / error capture (defined in capi.cu) -----------------------------------
+void note_launch();
+int check_launch();                 // cudaGetLastError -> AQ_OK / AQ_ERR_CUDA
+int cuda_fail(cudaError_t e);       // records the text, returns AQ_ERR_CUDA
+
+// ---- storage <-> fp32 ---------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v)
+{
+    return v;
+}
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v)
+{
+    return __half2float(v);
+}
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v)
+{
+    return __bfloat162float(v);
+}
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v)
+{
+    return v;
+}
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v)
+{
+    return __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v)
+{
+    return __float2bfloat16_rn(v);
+}
+
+// ---- VEC-wide packets: one aligned load / store instruction of up to 16 bytes -------------------
+template <typename T, int VEC>
+struct alignas(sizeof(T) * VEC) Pack
+{
+    T v[VEC];
+};
+
+template <typename T, int VEC>
+__device__ __forceinline__ Pack<T, VEC> load_pack(const T* p)
+{
+    return *reinterpret_cast<const Pack<T, VEC>*>(p);
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_pack(T* p, const Pack<T, VEC>& v)
+{
+    *reinterpret_cast<Pack<T, VEC>*>(p) = v;
+}
+
+// Largest power-of-two vector width (in elements, <= 16 bytes) that both the pointers' alignment and a
+// divisibility constraint `multiple_of` allow.
+template <typename T>
+inline int pick_vec(const void* a, const void* b, const void* c, int64_t multiple_of)
+{
+    int vec = 16 / (int) sizeof(T);
+    auto ok = [&](int v) {
+        const uintptr_t bytes = (uintptr_t) v * sizeof(T);
+        if (a && ((uintptr_t) a % bytes))
+            return false;
+        if (b && ((uintptr_t) b % bytes))
+            return false;
+        if (c && ((uintptr_t) c % bytes))
+            return false;
+        if (multiple_of > 0 && (multiple_of % v))
+            return false;
+        return true;
+    };
+    while (vec > 1 && !ok(vec))
+        vec >>= 1;
+    return vec;
+}
+
+// ---- exact rounding helpers -------------------------------------------------------------------
+// C roundf(): nearest, ties away from zero.  t - trunc(t) is exact, so the tie test is exact.
+__device__ __forceinline__ float round_half_away(float t)
+{
+    float r = truncf(t);
+    float d = t - r;
+    if (fabsf(d) >= 0.5f)
+        r += copysignf(1.0f, t);
+    return r;
+}
+
+// ---- channel geometry ---------------------------------------------------------------------------
+// Element i of a contiguous tensor belongs to encoding channel (i / inner) % num_ch.
+// A CTA covers a contiguous chunk, so it meets at most chunk/inner + 2 consecutive "runs" of `inner` elements;
+// their parameters are staged in shared memory and a run is found with one 32-bit multiply-high.
+struct ChanGeom
+{
+    int64_t inner;
+    int64_t num_ch;
+    uint32_t magic;   // ceil(2^32 / inner) when 1 < inner < 2^16, else 0
+    int mode;         // 0: inner == 1 (run = local offset), 1: magic multiply, 2: inner so large that a chunk
+                      //    meets at most two runs (compare)
+};
+
+inline ChanGeom make_geom(int64_t num_ch, int64_t inner, int64_t chunk)
+{
+    ChanGeom g;
+    g.inner  = inner;
+    g.num_ch = num_ch;
+    g.magic  = 0;
+    if (inner == 1)
+        g.mode = 0;
+    else if (inner >= chunk)
+        g.mode = 2;
+    else
+    {
+        // local offsets are < inner + chunk <= 2*chunk <= 2^15 and inner < chunk <= 2^14, so
+        // floor(loc/inner) == umulhi(loc, ceil(2^32/inner)) exactly (loc * inner < 2^32).
+        g.mode  = 1;
+        g.magic = (uint32_t) ((0x100000000ull + (uint64_t) inner - 1) / (uint64_t) inner);
+    }
+    return g;
+}
+
+__device__ __forceinline__ uint32_t local_run(const ChanGeom& g, uint32_t loc)
+{
+    if (g.mode == 1)
+        return __umulhi(loc, g.magic);
+    if (g.mode == 2)
+        return loc >= (uint32_t) g.inner ? 1u : 0u;   // only reached when inner < 2^32 (loc < inner + chunk)
+    return loc;
+}
+
+}   // namespace aq

@@ -1,0 +1,62 @@
+// Argument blocks and host-side launchers shared between the kernel files and the C ABI.
+#pragma once
+
+#include "common.cuh"
+
+namespace aq
+{
+int pymo_per_tensor(const float* in, float* out, int64_t n, float mn, float mx, float delta, float offset,
+                    int codes_only, float shift, cudaStream_t st);
+int pymo_per_channel(const float* in, float* out, int64_t n, int64_t num_ch, int64_t inner, const float* enc_min,
+                     const float* enc_max, const float* enc_delta, const float* enc_offset, float num_steps,
+                     int derive, cudaStream_t st);
+struct BroadcastArgs
+{
+    const float* in;
+    float* out;
+    int64_t n;
+    int ndims;
+    int64_t in_strides[8];
+    int64_t enc_strides[8];
+    const float *mn, *mx, *dl, *of;
+};
+int pymo_broadcast(const BroadcastArgs& a, cudaStream_t st);
+struct V2Args
+{
+    const void* x;
+    void* y;
+    uint8_t* mask;
+    int64_t n;
+    const float* scale;
+    const float* offset;
+    float qmin, qmax;
+    int out_kind;
+    int dequant_only;
+    ChanGeom geom;
+};
+int v2_launch(V2Args a, int dtype, int internal_f16, cudaStream_t st);
+int v2_backward(const void* g, const uint8_t* mask, void* dx, int dtype, int64_t n, cudaStream_t st);
+struct SteArgs
+{
+    const float* x;
+    const float* g;
+    float* dx;
+    int64_t n;
+    const float* enc_min;
+    const float* enc_max;
+    ChanGeom geom;
+};
+int ste_v1(SteArgs a, cudaStream_t st);
+int64_t minmax_workspace_bytes(int64_t n, int64_t num_ch, int64_t inner);
+int minmax_dispatch(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* out_min,
+                    float* out_max, int propagate_nan, void* ws, int64_t ws_bytes, cudaStream_t st);
+int tfe_init_grid(const float* minmax, aq_tfe_state_t* st, cudaStream_t stream);
+int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t* hist, int64_t* count,
+                  cudaStream_t stream);
+int tfe_pdf_replay(const uint32_t* hists, const int64_t* counts, int64_t num_batches, double* pdf,
+                   int32_t* iterations, cudaStream_t stream);
+int64_t tfe_search_workspace_bytes();
+int tfe_search(const aq_tfe_state_t* st, const double* pdf, int stats_updated, int bw, int symmetric, int strict,
+               int unsigned_sym, double* out, void* ws, int64_t ws_bytes, cudaStream_t stream);
+
+}   // namespace aq

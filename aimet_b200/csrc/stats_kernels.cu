@@ -1,0 +1,668 @@
+// Calibration statistics kernels for sm_100a: fused min/max reductions (per tensor / per channel / per block)
+// and the 512-bucket TF-Enhanced histogram.  All are single-pass, HBM-bound streaming reads.
+#include <float.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace aq
+{
+
+// =================================================================================================
+// min / max
+// =================================================================================================
+
+template <bool PROP>
+__device__ __forceinline__ float min_op(float a, float b)
+{
+    if (PROP)
+    {
+        float r;
+        asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+        return r;
+    }
+    return fminf(a, b);
+}
+template <bool PROP>
+__device__ __forceinline__ float max_op(float a, float b)
+{
+    if (PROP)
+    {
+        float r;
+        asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+        return r;
+    }
+    return fmaxf(a, b);
+}
+
+template <bool PROP, int WIDTH>
+__device__ __forceinline__ void group_reduce(float& mn, float& mx)
+{
+#pragma unroll
+    for (int o = WIDTH / 2; o > 0; o >>= 1)
+    {
+        mn = min_op<PROP>(mn, __shfl_xor_sync(0xffffffffu, mn, o, WIDTH));
+        mx = max_op<PROP>(mx, __shfl_xor_sync(0xffffffffu, mx, o, WIDTH));
+    }
+}
+
+constexpr int kMmThreads = 512;
+constexpr int kMmUnroll  = 4;
+
+// ---- whole-tensor reduction: persistent CTAs, warp shuffles, last CTA folds the partials -------------------
+// workspace layout: [0] uint32 ticket counter (must be 0 on entry; the kernel leaves it 0),
+//                   [64 ...) float2 partials, one per CTA.
+template <typename T, int VEC, bool PROP>
+__global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __restrict__ x, int64_t n,
+                                                                   float* __restrict__ out_min,
+                                                                   float* __restrict__ out_max,
+                                                                   unsigned int* __restrict__ ticket,
+                                                                   float2* __restrict__ partials)
+{
+    float mn = INFINITY, mx = -INFINITY;
+    const int64_t npack  = n / VEC;
+    const int64_t stride = (int64_t) gridDim.x * kMmThreads;
+    int64_t p            = (int64_t) blockIdx.x * kMmThreads + threadIdx.x;
+    // kMmUnroll independent loads in flight per thread
+    for (; p + (kMmUnroll - 1) * stride < npack; p += kMmUnroll * stride)
+    {
+        Pack<T, VEC> v[kMmUnroll];
+#pragma unroll
+        for (int u = 0; u < kMmUnroll; ++u)
+            v[u] = load_pack<T, VEC>(x + (p + u * stride) * VEC);
+#pragma unroll
+        for (int u = 0; u < kMmUnroll; ++u)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+            {
+                const float f = to_f32<T>(v[u].v[e]);
+                mn            = min_op<PROP>(mn, f);
+                mx            = max_op<PROP>(mx, f);
+            }
+    }
+    for (; p < npack; p += stride)
+    {
+        Pack<T, VEC> v = load_pack<T, VEC>(x + p * VEC);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+        {
+            const float f = to_f32<T>(v.v[e]);
+            mn            = min_op<PROP>(mn, f);
+            mx            = max_op<PROP>(mx, f);
+        }
+    }
+    // ragged tail (fewer than VEC elements)
+    if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * VEC))
+    {
+        const float f = to_f32<T>(x[npack * VEC + threadIdx.x]);
+        mn            = min_op<PROP>(mn, f);
+        mx            = max_op<PROP>(mx, f);
+    }
+
+    group_reduce<PROP, 32>(mn, mx);
+    __shared__ float s_mn[kMmThreads / 32], s_mx[kMmThreads / 32];
+    __shared__ bool s_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0)
+        s_mn[warp] = mn, s_mx[warp] = mx;
+    __syncthreads();
+    if (warp == 0)
+    {
+        mn = lane < kMmThreads / 32 ? s_mn[lane] : INFINITY;
+        mx = lane < kMmThreads / 32 ? s_mx[lane] : -INFINITY;
+        group_reduce<PROP, 32>(mn, mx);
+        if (lane == 0)
+        {
+            partials[blockIdx.x] = make_float2(mn, mx);
+            __threadfence();
+            const unsigned int t = atomicAdd(ticket, 1u);
+            s_last               = (t == gridDim.x - 1);
+        }
+    }
+    __syncthreads();
+    if (!s_last)
+        return;
+    __threadfence();
+    mn = INFINITY, mx = -INFINITY;
+    for (int i = threadIdx.x; i < (int) gridDim.x; i += kMmThreads)
+    {
+        const float2 q = __ldcg(&partials[i]);
+        mn             = min_op<PROP>(mn, q.x);
+        mx             = max_op<PROP>(mx, q.y);
+    }
+    group_reduce<PROP, 32>(mn, mx);
+    __syncthreads();
+    if (lane == 0)
+        s_mn[warp] = mn, s_mx[warp] = mx;
+    __syncthreads();
+    if (warp == 0)
+    {
+        mn = lane < kMmThreads / 32 ? s_mn[lane] : INFINITY;
+        mx = lane < kMmThreads / 32 ? s_mx[lane] : -INFINITY;
+        group_reduce<PROP, 32>(mn, mx);
+        if (lane == 0)
+        {
+            if (PROP && (mn != mn || mx != mx))
+                mn = mx = NAN;
+            out_min[0] = mn;
+            out_max[0] = mx;
+            *ticket    = 0;   // ready for the next call on this stream
+        }
+    }
+}
+
+// ---- rows: the tensor is R = n / inner contiguous rows; row r belongs to channel r % num_ch ----------------
+// A group of GS lanes reduces one (row, segment) pair.  Results go to `part_*[row * nseg + seg]`.
+template <typename T, int VEC, int GS, bool PROP>
+__global__ void __launch_bounds__(256) minmax_rows_kernel(const T* __restrict__ x, int64_t rows, int64_t inner,
+                                                          int nseg, int64_t seg_len /* elements, multiple of VEC */,
+                                                          float* __restrict__ part_min, float* __restrict__ part_max)
+{
+    const int lane_in_group  = threadIdx.x % GS;
+    const int64_t group      = ((int64_t) blockIdx.x * 256 + threadIdx.x) / GS;
+    const int64_t num_groups = (int64_t) gridDim.x * 256 / GS;
+    const int64_t items      = rows * nseg;
+    for (int64_t it = group; it < items; it += num_groups)
+    {
+        const int64_t row = it / nseg;
+        const int seg     = (int) (it - row * nseg);
+        const int64_t beg = (int64_t) seg * seg_len;
+        int64_t end       = beg + seg_len;
+        if (end > inner)
+            end = inner;
+        const T* __restrict__ rp = x + row * inner;
+        float mn = INFINITY, mx = -INFINITY;
+        int64_t e = beg + (int64_t) lane_in_group * VEC;
+        for (; e + (int64_t) (kMmUnroll - 1) * GS * VEC + VEC <= end; e += (int64_t) kMmUnroll * GS * VEC)
+        {
+            Pack<T, VEC> v[kMmUnroll];
+#pragma unroll
+            for (int u = 0; u < kMmUnroll; ++u)
+                v[u] = load_pack<T, VEC>(rp + e + (int64_t) u * GS * VEC);
+#pragma unroll
+            for (int u = 0; u < kMmUnroll; ++u)
+#pragma unroll
+                for (int k = 0; k < VEC; ++k)
+                {
+                    const float f = to_f32<T>(v[u].v[k]);
+                    mn            = min_op<PROP>(mn, f);
+                    mx            = max_op<PROP>(mx, f);
+                }
+        }
+        for (; e + VEC <= end; e += (int64_t) GS * VEC)
+        {
+            Pack<T, VEC> v = load_pack<T, VEC>(rp + e);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k)
+            {
+                const float f = to_f32<T>(v.v[k]);
+                mn            = min_op<PROP>(mn, f);
+                mx            = max_op<PROP>(mx, f);
+            }
+        }
+        // VEC divides inner and seg_len, so no ragged tail exists inside a row.
+        group_reduce<PROP, GS>(mn, mx);
+        if (lane_in_group == 0)
+        {
+            if (PROP && (mn != mn || mx != mx))
+                mn = mx = NAN;
+            part_min[it] = mn;
+            part_max[it] = mx;
+        }
+    }
+}
+
+// Folds partials [outer, num_ch, nseg] -> [num_ch].
+template <bool PROP>
+__global__ void __launch_bounds__(256) minmax_fold_kernel(const float* __restrict__ part_min,
+                                                          const float* __restrict__ part_max, int64_t outer,
+                                                          int64_t num_ch, int nseg, float* __restrict__ out_min,
+                                                          float* __restrict__ out_max)
+{
+    const int64_t c = (int64_t) blockIdx.x * 256 + threadIdx.x;
+    if (c >= num_ch)
+        return;
+    float mn = INFINITY, mx = -INFINITY;
+    for (int64_t o = 0; o < outer; ++o)
+        for (int s = 0; s < nseg; ++s)
+        {
+            const int64_t i = (o * num_ch + c) * nseg + s;
+            mn              = min_op<PROP>(mn, part_min[i]);
+            mx              = max_op<PROP>(mx, part_max[i]);
+        }
+    if (PROP && (mn != mn || mx != mx))
+        mn = mx = NAN;
+    out_min[c] = mn;
+    out_max[c] = mx;
+}
+
+struct RowsPlan
+{
+    int64_t rows, outer;
+    int nseg;
+    int64_t seg_len;
+    int gs;
+    bool direct;   // partials ARE the outputs (outer == 1, nseg == 1)
+};
+
+static RowsPlan plan_rows(int64_t n, int64_t num_ch, int64_t inner, int vec)
+{
+    RowsPlan p;
+    p.rows  = n / inner;
+    p.outer = p.rows / num_ch;
+    // lanes per row: enough to cover the row once with VEC-wide loads, capped at a warp
+    int64_t packs = inner / vec;
+    int gs        = 1;
+    while (gs < 32 && gs < packs)
+        gs <<= 1;
+    p.gs = gs;
+    // split long rows so that there are enough (row, segment) items to fill the machine
+    const int64_t target_items = (int64_t) kNumSMs * 8 * (256 / 32) * 2;
+    int nseg                   = 1;
+    if (gs == 32 && p.rows < target_items)
+    {
+        int64_t want     = (target_items + p.rows - 1) / p.rows;
+        int64_t max_segs = packs / (32 * kMmUnroll);   // keep >= one unrolled sweep per segment
+        if (max_segs < 1)
+            max_segs = 1;
+        nseg = (int) (want < max_segs ? want : max_segs);
+        if (nseg > 4096)
+            nseg = 4096;
+    }
+    int64_t seg_len = (inner + nseg - 1) / nseg;
+    seg_len         = (seg_len + vec - 1) / vec * vec;
+    nseg            = (int) ((inner + seg_len - 1) / seg_len);
+    p.nseg          = nseg;
+    p.seg_len       = seg_len;
+    p.direct        = (p.outer == 1 && nseg == 1);
+    return p;
+}
+
+static int tensor_grid(int64_t n, int vec)
+{
+    int64_t per_block = (int64_t) kMmThreads * vec * kMmUnroll;
+    int64_t blocks    = (n + per_block - 1) / per_block;
+    int64_t cap       = (int64_t) kNumSMs * 4;   // 4 CTAs of 512 threads per SM
+    if (blocks > cap)
+        blocks = cap;
+    if (blocks < 1)
+        blocks = 1;
+    return (int) blocks;
+}
+
+template <typename T>
+static int vec_for(const void* x, int64_t multiple_of)
+{
+    return pick_vec<T>(x, nullptr, nullptr, multiple_of);
+}
+
+static int dtype_vec(const void* x, int dtype, int64_t multiple_of)
+{
+    switch (dtype)
+    {
+    case AQ_F32: return vec_for<float>(x, multiple_of);
+    case AQ_F16: return vec_for<__half>(x, multiple_of);
+    case AQ_BF16: return vec_for<__nv_bfloat16>(x, multiple_of);
+    default: return 0;
+    }
+}
+
+int64_t minmax_workspace_bytes(int64_t n, int64_t num_ch, int64_t inner)
+{
+    if (num_ch <= 1)
+        return 256 + (int64_t) kNumSMs * 4 * sizeof(float2);
+    // worst case over vector widths: vec = 1 gives the most segments
+    int64_t worst = 0;
+    for (int vec = 1; vec <= 8; vec <<= 1)
+    {
+        if (inner % vec)
+            continue;
+        RowsPlan p  = plan_rows(n, num_ch, inner, vec);
+        int64_t b   = 2 * p.rows * p.nseg * (int64_t) sizeof(float);
+        worst       = b > worst ? b : worst;
+    }
+    return worst + 256;
+}
+
+template <typename T, int VEC, bool PROP>
+static void launch_rows_gs(const T* x, const RowsPlan& p, int64_t inner, float* pmin, float* pmax, cudaStream_t st)
+{
+    const int64_t items     = p.rows * p.nseg;
+    const int64_t per_block = 256 / p.gs;
+    int64_t blocks          = (items + per_block - 1) / per_block;
+    const int64_t cap       = (int64_t) kNumSMs * 8 * 4;
+    if (blocks > cap)
+        blocks = cap;
+#define AQ_GS(G)                                                                                                     \
+    case G:                                                                                                          \
+        minmax_rows_kernel<T, VEC, G, PROP>                                                                          \
+            <<<(unsigned) blocks, 256, 0, st>>>(x, p.rows, inner, p.nseg, p.seg_len, pmin, pmax);                   \
+        break;
+    switch (p.gs)
+    {
+        AQ_GS(1)
+        AQ_GS(2)
+        AQ_GS(4)
+        AQ_GS(8)
+        AQ_GS(16)
+    default:
+        minmax_rows_kernel<T, VEC, 32, PROP>
+            <<<(unsigned) blocks, 256, 0, st>>>(x, p.rows, inner, p.nseg, p.seg_len, pmin, pmax);
+    }
+#undef AQ_GS
+    note_launch();
+}
+
+template <typename T, bool PROP>
+static int minmax_t(const T* x, int64_t n, int64_t num_ch, int64_t inner, float* out_min, float* out_max, void* ws,
+                    int64_t ws_bytes, cudaStream_t st)
+{
+    if (num_ch <= 1)
+    {
+        const int vec  = vec_for<T>(x, 0);
+        const int grid = tensor_grid(n, vec);
+        if (ws_bytes < 256 + (int64_t) grid * (int64_t) sizeof(float2))
+            return AQ_ERR_WORKSPACE;
+        unsigned int* ticket = static_cast<unsigned int*>(ws);
+        float2* partials     = reinterpret_cast<float2*>(static_cast<char*>(ws) + 256);
+        switch (vec)
+        {
+        case 8:
+            minmax_tensor_kernel<T, (sizeof(T) == 2 ? 8 : 4), PROP>
+                <<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials);
+            break;
+        case 4:
+            minmax_tensor_kernel<T, 4, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials);
+            break;
+        case 2:
+            minmax_tensor_kernel<T, 2, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials);
+            break;
+        default:
+            minmax_tensor_kernel<T, 1, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials);
+        }
+        note_launch();
+        return check_launch();
+    }
+    const int vec = vec_for<T>(x, inner);
+    RowsPlan p    = plan_rows(n, num_ch, inner, vec);
+    float *pmin = out_min, *pmax = out_max;
+    if (!p.direct)
+    {
+        const int64_t need = 2 * p.rows * p.nseg * (int64_t) sizeof(float);
+        if (ws_bytes < need)
+            return AQ_ERR_WORKSPACE;
+        pmin = static_cast<float*>(ws);
+        pmax = pmin + p.rows * p.nseg;
+    }
+    switch (vec)
+    {
+    case 8: launch_rows_gs<T, (sizeof(T) == 2 ? 8 : 4), PROP>(x, p, inner, pmin, pmax, st); break;
+    case 4: launch_rows_gs<T, 4, PROP>(x, p, inner, pmin, pmax, st); break;
+    case 2: launch_rows_gs<T, 2, PROP>(x, p, inner, pmin, pmax, st); break;
+    default: launch_rows_gs<T, 1, PROP>(x, p, inner, pmin, pmax, st);
+    }
+    int rc = check_launch();
+    if (rc != AQ_OK || p.direct)
+        return rc;
+    minmax_fold_kernel<PROP><<<(unsigned) ((num_ch + 255) / 256), 256, 0, st>>>(pmin, pmax, p.outer, num_ch, p.nseg,
+                                                                                out_min, out_max);
+    note_launch();
+    return check_launch();
+}
+
+int minmax_dispatch(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* out_min,
+                    float* out_max, int propagate_nan, void* ws, int64_t ws_bytes, cudaStream_t st)
+{
+    (void) dtype_vec;
+#define AQ_T(T)                                                                                                      \
+    (propagate_nan ? minmax_t<T, true>((const T*) x, n, num_ch, inner, out_min, out_max, ws, ws_bytes, st)          \
+                   : minmax_t<T, false>((const T*) x, n, num_ch, inner, out_min, out_max, ws, ws_bytes, st))
+    switch (dtype)
+    {
+    case AQ_F32: return AQ_T(float);
+    case AQ_F16: return AQ_T(__half);
+    case AQ_BF16: return AQ_T(__nv_bfloat16);
+    default: return AQ_ERR_INVALID_ARG;
+    }
+#undef AQ_T
+}
+
+// =================================================================================================
+// TF-Enhanced: bucket grid, 512-bucket histogram, PDF replay
+// =================================================================================================
+
+// InitializePdf<float> + the geometry lines of UpdatePdf (DlQuantization/src/math_functions.cpp:207-268).
+__global__ void __launch_bounds__(AQ_PDF_SIZE) tfe_init_grid_kernel(const float* __restrict__ minmax,
+                                                                    aq_tfe_state_t* __restrict__ st)
+{
+    if (st->initialized)
+        return;
+    float mn = minmax[0], mx = minmax[1];
+    if (mn == 0.0f && mx == 0.0f)
+        return;   // an all-zero batch cannot define the range; the reference waits for the next one
+    if (mn == mx)
+    {
+        const float alt = __fadd_rn(mn, 0.01f);
+        mx              = mx < alt ? alt : mx;
+    }
+    const float center = __fdiv_rn(__fadd_rn(mx, mn), 2.0f);
+    float lo           = __fsub_rn(center, __fmul_rn(3.0f, __fsub_rn(center, mn)));
+    float hi           = __fadd_rn(center, __fmul_rn(3.0f, __fsub_rn(mx, center)));
+    lo                 = (-FLT_MAX < lo) ? lo : -FLT_MAX;
+    hi                 = (hi < FLT_MAX) ? hi : FLT_MAX;
+    const double bucket = __ddiv_rn(__dsub_rn((double) hi, (double) lo), (double) AQ_PDF_SIZE);
+    const int i         = threadIdx.x;
+    st->x_left[i]       = __dadd_rn((double) lo, __dmul_rn((double) i, bucket));
+    __syncthreads();
+    if (i == 0)
+    {
+        const double x0 = __dadd_rn((double) lo, __dmul_rn(0.0, bucket));
+        const double x1 = __dadd_rn((double) lo, __dmul_rn(1.0, bucket));
+        const float bs  = __double2float_rn(__dsub_rn(x1, x0));
+        const float m0  = __double2float_rn(x0);
+        st->bucket_size = bs;
+        st->pdf_offset  = __fdiv_rn(m0, bs);
+        __threadfence();
+        st->initialized = 1;
+    }
+}
+
+constexpr int kHistThreads = 512;
+constexpr int kHistUnroll  = 4;
+constexpr int kHistPad     = AQ_PDF_SIZE + 1;   // odd row stride: replica r, bucket b -> bank (r + b) % 32
+
+// Bucket of one sample: (int) roundf(x / bucket_size - pdf_offset), valid when inside [0, 512).
+// For t > -0.5 the half-away rounding equals floor(t + 0.5); adding with round-down keeps the sum from being
+// rounded up across an integer, so floor() of it is exact.  NaN and t <= -0.5 fail the first test.
+__device__ __forceinline__ bool bucket_of(float x, float bs, float po, int& k)
+{
+    const float t = __fsub_rn(__fdiv_rn(x, bs), po);
+    k             = __float2int_rd(__fadd_rd(t, 0.5f));
+    return (t > -0.5f) && ((unsigned) k < (unsigned) AQ_PDF_SIZE);
+}
+
+// Shared-memory privatised histogram with REPL replicas selected by lane id (so lanes of one warp that hit the
+// same bucket mostly land on different addresses), plus a register counter for the bucket that holds exact
+// zeros -- the usual spike of post-ReLU activations.
+template <int REPL>
+__global__ void __launch_bounds__(kHistThreads) tfe_hist_kernel(const float* __restrict__ x, int64_t n,
+                                                                const aq_tfe_state_t* __restrict__ st,
+                                                                uint32_t* __restrict__ hist,
+                                                                int64_t* __restrict__ count)
+{
+    const int initialized = st->initialized;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && count)
+        *count = initialized ? n : 0;
+    if (!initialized)
+        return;
+    __shared__ uint32_t s_hist[REPL * kHistPad];
+    for (int i = threadIdx.x; i < REPL * kHistPad; i += kHistThreads)
+        s_hist[i] = 0;
+    __syncthreads();
+
+    const float bs = st->bucket_size, po = st->pdf_offset;
+    uint32_t* my = s_hist + (threadIdx.x % REPL) * kHistPad;
+    int zero_bucket;
+    if (!bucket_of(0.0f, bs, po, zero_bucket))
+        zero_bucket = -1;
+    uint32_t zero_count = 0;
+
+    const int64_t npack  = n / 4;
+    const int64_t stride = (int64_t) gridDim.x * kHistThreads;
+    int64_t p            = (int64_t) blockIdx.x * kHistThreads + threadIdx.x;
+    for (; p + (kHistUnroll - 1) * stride < npack; p += kHistUnroll * stride)
+    {
+        float4 v[kHistUnroll];
+#pragma unroll
+        for (int u = 0; u < kHistUnroll; ++u)
+            v[u] = __ldcs(reinterpret_cast<const float4*>(x) + p + u * stride);
+#pragma unroll
+        for (int u = 0; u < kHistUnroll; ++u)
+        {
+            const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+            {
+                int k;
+                if (bucket_of(f[e], bs, po, k))
+                {
+                    if (k == zero_bucket)
+                        ++zero_count;
+                    else
+                        atomicAdd(&my[k], 1u);
+                }
+            }
+        }
+    }
+    for (; p < npack; p += stride)
+    {
+        const float4 v   = __ldcs(reinterpret_cast<const float4*>(x) + p);
+        const float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+        {
+            int k;
+            if (bucket_of(f[e], bs, po, k))
+            {
+                if (k == zero_bucket)
+                    ++zero_count;
+                else
+                    atomicAdd(&my[k], 1u);
+            }
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * 4))
+    {
+        int k;
+        if (bucket_of(x[npack * 4 + threadIdx.x], bs, po, k))
+            atomicAdd(&my[k], 1u);
+    }
+    if (zero_count)
+        atomicAdd(&my[zero_bucket], zero_count);
+    __syncthreads();
+    for (int b = threadIdx.x; b < AQ_PDF_SIZE; b += kHistThreads)
+    {
+        uint32_t s = 0;
+#pragma unroll
+        for (int r = 0; r < REPL; ++r)
+            s += s_hist[r * kHistPad + b];
+        if (s)
+            atomicAdd(&hist[b], s);
+    }
+}
+
+// Scalar variant for inputs whose base address is not 16-byte aligned.
+__global__ void __launch_bounds__(kHistThreads) tfe_hist_scalar_kernel(const float* __restrict__ x, int64_t n,
+                                                                       const aq_tfe_state_t* __restrict__ st,
+                                                                       uint32_t* __restrict__ hist,
+                                                                       int64_t* __restrict__ count)
+{
+    const int initialized = st->initialized;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && count)
+        *count = initialized ? n : 0;
+    if (!initialized)
+        return;
+    __shared__ uint32_t s_hist[AQ_PDF_SIZE];
+    for (int i = threadIdx.x; i < AQ_PDF_SIZE; i += kHistThreads)
+        s_hist[i] = 0;
+    __syncthreads();
+    const float bs = st->bucket_size, po = st->pdf_offset;
+    const int64_t stride = (int64_t) gridDim.x * kHistThreads;
+    for (int64_t i = (int64_t) blockIdx.x * kHistThreads + threadIdx.x; i < n; i += stride)
+    {
+        int k;
+        if (bucket_of(x[i], bs, po, k))
+            atomicAdd(&s_hist[k], 1u);
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < AQ_PDF_SIZE; b += kHistThreads)
+        if (s_hist[b])
+            atomicAdd(&hist[b], s_hist[b]);
+}
+
+int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t* hist, int64_t* count,
+                  cudaStream_t stream)
+{
+    if (((uintptr_t) x % 16) != 0)
+    {
+        int64_t blocks = (n + kHistThreads - 1) / kHistThreads;
+        int64_t cap    = (int64_t) kNumSMs * 4;
+        if (blocks > cap)
+            blocks = cap;
+        if (blocks < 1)
+            blocks = 1;
+        tfe_hist_scalar_kernel<<<(unsigned) blocks, kHistThreads, 0, stream>>>(x, n, st, hist, count);
+        note_launch();
+        return check_launch();
+    }
+    int64_t per_block = (int64_t) kHistThreads * 4 * kHistUnroll;
+    int64_t blocks    = (n + per_block - 1) / per_block;
+    int64_t cap       = (int64_t) kNumSMs * 2;
+    if (blocks > cap)
+        blocks = cap;
+    if (blocks < 1)
+        blocks = 1;
+    tfe_hist_kernel<8><<<(unsigned) blocks, kHistThreads, 0, stream>>>(x, n, st, hist, count);
+    note_launch();
+    return check_launch();
+}
+
+int tfe_init_grid(const float* minmax, aq_tfe_state_t* st, cudaStream_t stream)
+{
+    tfe_init_grid_kernel<<<1, AQ_PDF_SIZE, 0, stream>>>(minmax, st);
+    note_launch();
+    return check_launch();
+}
+
+// Running mean of per-batch PDFs, batch order preserved (DlQuantization/src/math_functions.cpp:278-287).
+__global__ void __launch_bounds__(AQ_PDF_SIZE) tfe_pdf_replay_kernel(const uint32_t* __restrict__ hists,
+                                                                     const int64_t* __restrict__ counts,
+                                                                     int64_t num_batches, double* __restrict__ pdf,
+                                                                     int32_t* __restrict__ iterations)
+{
+    const int i = threadIdx.x;
+    double acc  = 0.0;
+    int it      = 0;
+    for (int64_t b = 0; b < num_batches; ++b)
+    {
+        const int64_t cnt = counts[b];
+        if (cnt == 0)
+            continue;
+        const double prob = __ddiv_rn((double) hists[b * AQ_PDF_SIZE + i], (double) (int) cnt);
+        acc               = __ddiv_rn(__dadd_rn(__dmul_rn(acc, (double) it), prob), (double) (it + 1));
+        ++it;
+    }
+    pdf[i] = acc;
+    if (i == 0)
+        *iterations = it;
+}
+
+int tfe_pdf_replay(const uint32_t* hists, const int64_t* counts, int64_t num_batches, double* pdf,
+                   int32_t* iterations, cudaStream_t stream)
+{
+    tfe_pdf_replay_kernel<<<1, AQ_PDF_SIZE, 0, stream>>>(hists, counts, num_batches, pdf, iterations);
+    note_launch();
+    return check_launch();
+}
+
+}   // namespace aq

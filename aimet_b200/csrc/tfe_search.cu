@@ -1,0 +1,339 @@
+// TF-Enhanced SQNR grid search on the device: one warp per candidate (delta, offset).
+//
+// Follows DlQuantization/src/TfEnhancedEncodingAnalyzer.cpp (DTYPE = float): candidate lists :177-253,
+// clamping :149-175, observed range :255-291, cost :293-355, first-strict-minimum selection :115-147 and the
+// final encoding :357-397.  The mixed float/double arithmetic and the ascending-bucket summation order of the
+// reference are kept, because near-tie candidates would otherwise flip: the 512 per-bucket terms of a candidate
+// are computed by the warp's lanes in parallel, but each of the three cost sums is added up in bucket order by a
+// single lane.
+#include <float.h>
+#include <limits.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace aq
+{
+
+constexpr int kAsymDeltas  = 17;
+constexpr int kAsymOffsets = 21;
+constexpr int kAsymSlots   = kAsymDeltas * kAsymOffsets + 1;   // 358
+constexpr int kSymSlots    = 128;                              // loop runs 101 (or 100/102) times
+constexpr int kMaxSlots    = 384;
+constexpr int kSearchWarps = 4;                                // warps (= candidates) per CTA
+
+struct SearchWs
+{
+    unsigned int ticket;
+    int pad[3];
+    double cost[kMaxSlots];
+    float delta[kMaxSlots];
+    int offset[kMaxSlots];
+    int valid[kMaxSlots];
+};
+
+int64_t tfe_search_workspace_bytes()
+{
+    return (int64_t) ((sizeof(SearchWs) + 255) / 256 * 256);
+}
+
+// double -> int like x86-64 cvttsd2si: out of range or NaN gives INT_MIN
+__device__ __forceinline__ int to_int_x86(double v)
+{
+    if (!(v > -2147483649.0 && v < 2147483648.0))
+        return INT_MIN;
+    return (int) v;
+}
+__device__ __forceinline__ int to_int_x86(float v)
+{
+    if (!(v >= -2147483648.0f && v < 2147483648.0f))
+        return INT_MIN;
+    return (int) v;
+}
+// std::max(a,b) = (a<b)?b:a ; std::min(a,b) = (b<a)?b:a
+template <typename T>
+__device__ __forceinline__ T smax(T a, T b)
+{
+    return (a < b) ? b : a;
+}
+template <typename T>
+__device__ __forceinline__ T smin(T a, T b)
+{
+    return (b < a) ? b : a;
+}
+
+// _clampToObservedMinMax (:149-175)
+__device__ bool clamp_candidate(float obs_min, float obs_max, float steps, float& delta, int& offset)
+{
+    float t_min = smax(__fmul_rn(delta, (float) offset), -FLT_MAX);
+    float t_max = smin(__fmul_rn(delta, __fadd_rn((float) offset, steps)), FLT_MAX);
+    if (t_min < obs_min && t_max > obs_max)
+        return false;
+    t_min = smax(obs_min, t_min);
+    t_max = smin(obs_max, t_max);
+    if (t_min == t_max)
+        return false;
+    delta  = __double2float_rn(__ddiv_rn(__dsub_rn((double) t_max, (double) t_min), (double) steps));
+    offset = to_int_x86(round_half_away(__fdiv_rn(t_min, delta)));
+    return true;
+}
+
+struct SearchArgs
+{
+    const aq_tfe_state_t* st;
+    const double* pdf;
+    int stats_updated, bw, symmetric, strict, unsigned_sym;
+    float steps;   // (float)(2^bw - 1), computed on the host
+    double* out;   // {min, max, delta, offset, bw}
+    SearchWs* ws;
+    int slots;
+};
+
+__global__ void __launch_bounds__(kSearchWarps * 32) tfe_search_kernel(SearchArgs a)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = blockIdx.x * kSearchWarps + warp;
+    __shared__ double s_term[kSearchWarps][AQ_PDF_SIZE];
+    __shared__ bool s_last;
+
+    const int initialized = a.st->initialized;
+    float steps           = a.steps;
+
+    if (!initialized)
+    {
+        // computeEncoding (:78-107): no PDF yet
+        if (blockIdx.x == 0 && threadIdx.x == 0)
+        {
+            double e[5] = {0, 0, 0, 0, 0};
+            if (a.stats_updated)
+            {
+                const double d = __ddiv_rn(2.0, (double) (int) steps);
+                const double o = floor(__ddiv_rn(-1.0, d));
+                e[0]           = __dmul_rn(o, d);
+                e[1]           = __dadd_rn(e[0], __dmul_rn((double) (int) steps, d));
+                e[2]           = d;
+                e[3]           = o;
+                e[4]           = a.bw;
+            }
+            for (int i = 0; i < 5; ++i)
+                a.out[i] = e[i];
+        }
+        return;
+    }
+
+    // ---- observed range (_findRangeOfAggregateStats :255-291), computed redundantly by every warp -----------
+    const double* __restrict__ xl  = a.st->x_left;
+    const double* __restrict__ pdf = a.pdf;
+    int first = AQ_PDF_SIZE, last = 0;
+    for (int i = lane; i < AQ_PDF_SIZE; i += 32)
+        if (pdf[i] > 0)
+        {
+            first = min(first, i);
+            last  = max(last, i);
+        }
+    first = __reduce_min_sync(0xffffffffu, first);
+    last  = __reduce_max_sync(0xffffffffu, last);
+    float obs_mn = (first < AQ_PDF_SIZE) ? (float) xl[first] : (float) xl[0];
+    float obs_mx = (last > 0) ? (float) xl[last] : (float) xl[AQ_PDF_SIZE - 1];
+    obs_mn       = smin(obs_mn, 0.0f);
+    obs_mx       = smax(obs_mx, 0.0f);
+    obs_mx       = smax(obs_mx, __fadd_rn(obs_mn, (float) 0.01));
+
+    // ---- this warp's candidate ------------------------------------------------------------------------------
+    float c_delta = 0.f;
+    int c_offset  = 0;
+    bool valid    = false;
+    if (a.symmetric)
+    {
+        if (a.strict)
+            steps = __fsub_rn(steps, 1.0f);
+        float delta_max;
+        int t_off;
+        if (obs_mn == 0.0f && a.unsigned_sym)
+        {
+            delta_max = __fdiv_rn(obs_mx, steps);
+            t_off     = 0;
+        }
+        else
+        {
+            const float amax = smax(fabsf(obs_mx), fabsf(obs_mn));
+            delta_max        = __double2float_rn(__ddiv_rn((double) amax, __ddiv_rn((double) steps, 2.0)));
+            t_off            = (int) floorf(__fdiv_rn(-steps, 2.0f));
+        }
+        // for (float f = 1/100; f <= 1 + 1/100; f += 1/100): float accumulation through double, replayed literally
+        float f = (float) (1.0 / 100);
+        int k   = 0;
+        while ((double) f <= 1 + 1.0 / 100 && k < slot)
+        {
+            f = __double2float_rn(__dadd_rn((double) f, 1.0 / 100));
+            ++k;
+        }
+        if (k == slot && (double) f <= 1 + 1.0 / 100)
+        {
+            c_delta  = __fmul_rn(f, delta_max);
+            c_offset = t_off;
+            valid    = true;
+        }
+    }
+    else
+    {
+        // _pickTestCandidatesAsymmetric (:177-214)
+        const float obs_delta = __double2float_rn(__ddiv_rn(__dsub_rn((double) obs_mx, (double) obs_mn), (double) steps));
+        const int obs_off     = to_int_x86(round_half_away(__fdiv_rn(obs_mn, obs_delta)));
+        const float g_min     = smax(__fmul_rn(obs_delta, (float) obs_off), -FLT_MAX);
+        const float g_max     = smin(__fmul_rn(obs_delta, __fadd_rn((float) obs_off, steps)), FLT_MAX);
+        if (slot == kAsymSlots - 1)
+        {
+            c_delta  = obs_delta;
+            c_offset = obs_off;
+            valid    = true;
+        }
+        else if (slot < kAsymSlots - 1)
+        {
+            const int di  = slot / kAsymOffsets;   // f = (di + 1) / 16, exact in float
+            const int oi  = slot - di * kAsymOffsets;
+            const float f = (float) (di + 1) * 0.0625f;
+            c_delta       = __fmul_rn(f, obs_delta);
+            c_offset      = to_int_x86(__dadd_rn((double) (-steps), __dmul_rn(__ddiv_rn((double) steps, 20.0), (double) oi)));
+            valid         = clamp_candidate(g_min, g_max, steps, c_delta, c_offset);
+        }
+    }
+
+    // ---- cost (_quantAndSatCost :293-355) -------------------------------------------------------------------
+    double cost = DBL_MAX;
+    if (valid)
+    {
+        const float min_val   = __fmul_rn(c_delta, (float) c_offset);
+        const float step_size = a.steps;
+        const float max_val   = __fmul_rn(c_delta, __fadd_rn((float) c_offset, step_size));
+        const float pdf_start = (float) xl[0];
+        const double pdf_step = __dsub_rn(xl[1], xl[0]);
+        const double half     = __ddiv_rn(pdf_step, 2.0);
+        int min_ind = to_int_x86(floor(__ddiv_rn((double) __fsub_rn(min_val, pdf_start), pdf_step)));
+        min_ind     = smin(smax(0, min_ind), AQ_PDF_SIZE - 1);
+        int max_ind = to_int_x86(floor(__ddiv_rn((double) __fsub_rn(max_val, pdf_start), pdf_step)));
+        max_ind     = smin(smax(0, max_ind), AQ_PDF_SIZE - 1);
+        const float min_mid =
+            __double2float_rn(__dadd_rn(__dadd_rn((double) pdf_start, __dmul_rn((double) min_ind, pdf_step)), half));
+        const float max_mid =
+            __double2float_rn(__dadd_rn(__dadd_rn((double) pdf_start, __dmul_rn((double) max_ind, pdf_step)), half));
+        for (int i = lane; i < AQ_PDF_SIZE; i += 32)
+        {
+            const double mid = __dadd_rn(__dadd_rn((double) pdf_start, __dmul_rn((double) i, pdf_step)), half);
+            double d;
+            if (i < min_ind)
+                d = __dsub_rn(mid, (double) min_mid);
+            else if (i >= max_ind)
+                d = __dsub_rn(mid, (double) max_mid);
+            else
+            {
+                const float fv = __double2float_rn(mid);
+                const int q    = to_int_x86(round_half_away(__fsub_rn(__fdiv_rn(fv, c_delta), (float) c_offset)));
+                const float dq = __fmul_rn(c_delta, (float) (q + c_offset));
+                d              = (double) __fsub_rn(fv, dq);
+            }
+            s_term[warp][i] = __dmul_rn(pdf[i], __dmul_rn(d, d));
+        }
+        __syncwarp();
+        // three ordered sums, one lane each: [0,min_ind) bottom, [max_ind,512) top, [min_ind,max_ind) middle
+        double part = 0.0;
+        if (lane < 3)
+        {
+            const int lo = lane == 0 ? 0 : (lane == 1 ? max_ind : min_ind);
+            const int hi = lane == 0 ? min_ind : (lane == 1 ? AQ_PDF_SIZE : max_ind);
+            for (int i = lo; i < hi; ++i)
+                part = __dadd_rn(part, s_term[warp][i]);
+        }
+        const double bottom = __shfl_sync(0xffffffffu, part, 0);
+        const double top    = __shfl_sync(0xffffffffu, part, 1);
+        const double quant  = __shfl_sync(0xffffffffu, part, 2);
+        const double sqnr   = __dadd_rn(__dmul_rn((double) 3.0f, __dadd_rn(bottom, top)), quant);
+        cost                = smin(sqnr, DBL_MAX);
+    }
+    if (lane == 0 && slot < a.slots)
+    {
+        a.ws->cost[slot]   = cost;
+        a.ws->delta[slot]  = c_delta;
+        a.ws->offset[slot] = c_offset;
+        a.ws->valid[slot]  = valid ? 1 : 0;
+        __threadfence();
+    }
+
+    // ---- last CTA picks the first strict minimum and writes the encoding ----------------------------------------
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        __threadfence();
+        const unsigned int t = atomicAdd(&a.ws->ticket, 1u);
+        s_last               = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last)
+        return;
+    __threadfence();
+    if (warp == 0)
+    {
+        double best = DBL_MAX;
+        int best_i  = INT_MAX;
+        for (int i = lane; i < a.slots; i += 32)
+        {
+            const double c = __ldcg(&a.ws->cost[i]);
+            const int v    = __ldcg(&a.ws->valid[i]);
+            if (v && c < best)   // strict: keeps the earliest slot of this lane among equals
+            {
+                best   = c;
+                best_i = i;
+            }
+        }
+        // across lanes: smaller cost wins, equal costs -> smaller slot index (= the reference's first strict minimum)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+        {
+            const double oc = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi    = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (oc < best || (oc == best && oi < best_i))
+            {
+                best   = oc;
+                best_i = oi;
+            }
+        }
+        if (lane == 0)
+        {
+            float b_delta = -1.0f;
+            int b_offset  = -1;
+            if (best_i != INT_MAX && best < DBL_MAX)
+            {
+                b_delta  = __ldcg(&a.ws->delta[best_i]);
+                b_offset = __ldcg(&a.ws->offset[best_i]);
+            }
+            const float b_min = smax(__fmul_rn(b_delta, (float) b_offset), -FLT_MAX);
+            const float b_max = smin(__fmul_rn(b_delta, __fadd_rn((float) b_offset, steps)), FLT_MAX);
+            a.out[0]          = (double) b_min;
+            a.out[1]          = (double) b_max;
+            a.out[2]          = (double) b_delta;
+            a.out[3]          = (double) b_offset;
+            a.out[4]          = (double) a.bw;
+            a.ws->ticket      = 0;
+        }
+    }
+}
+
+int tfe_search(const aq_tfe_state_t* st, const double* pdf, int stats_updated, int bw, int symmetric, int strict,
+               int unsigned_sym, double* out, void* ws, int64_t ws_bytes, cudaStream_t stream)
+{
+    if (ws_bytes < tfe_search_workspace_bytes())
+        return AQ_ERR_WORKSPACE;
+    SearchArgs a;
+    a.st = st, a.pdf = pdf, a.stats_updated = stats_updated, a.bw = bw;
+    a.symmetric = symmetric, a.strict = strict, a.unsigned_sym = unsigned_sym;
+    a.out = out, a.ws = static_cast<SearchWs*>(ws);
+    a.steps         = (float) (pow(2.0, (double) bw) - 1.0);
+    a.slots         = symmetric ? kSymSlots : kAsymSlots;
+    const int grid  = (a.slots + kSearchWarps - 1) / kSearchWarps;
+    tfe_search_kernel<<<grid, kSearchWarps * 32, 0, stream>>>(a);
+    note_launch();
+    return check_launch();
+}
+
+}   // namespace aq

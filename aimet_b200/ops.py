@@ -1,0 +1,292 @@
+"""Tensor-level wrappers over the C ABI.  torch is used only for device memory and streams.
+
+Every function here launches hand-written sm_100a kernels through ``libaimet_b200.so`` on the current
+torch stream of the tensor's device.  CPU tensors are rejected: there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import lib, check
+
+_DT = {torch.float32: _lib.AQ_F32, torch.float16: _lib.AQ_F16, torch.bfloat16: _lib.AQ_BF16}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"aimet_b200: unsupported dtype {t.dtype}") from None
+
+
+def _cuda(t: torch.Tensor, name: str = "tensor") -> torch.Tensor:
+    if not t.is_cuda:
+        raise RuntimeError(f"aimet_b200: {name} must be a CUDA tensor (no CPU path exists), got {t.device}")
+    return t
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _same_device(a: torch.Tensor, *others: torch.Tensor):
+    for o in others:
+        if o.device != a.device:
+            raise RuntimeError(f"aimet_b200: tensors on different devices ({a.device} vs {o.device})")
+
+
+class _DeviceGuard:
+    """Makes the tensor's device current for the duration of a call (kernels launch on the current device)."""
+
+    def __init__(self, t: torch.Tensor):
+        self.g = torch.cuda.device(t.device)
+
+    def __enter__(self):
+        self.g.__enter__()
+
+    def __exit__(self, *a):
+        self.g.__exit__(*a)
+
+
+_WS: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def workspace(t: torch.Tensor, nbytes: int) -> torch.Tensor:
+    """Zero-initialised, 256-byte aligned scratch, cached per (device, stream).  The kernels that use a ticket
+    counter in it leave the counter at zero, so the buffer is zeroed only when it is created or grown."""
+    key = (t.device.index if t.device.index is not None else torch.cuda.current_device(), _stream(t))
+    ws = _WS.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(int(nbytes), 1 << 16), dtype=torch.uint8, device=t.device)
+        _WS[key] = ws
+    return ws
+
+
+# ---------------------------------------------------------------------------------------------------
+# libpymo semantics
+# ---------------------------------------------------------------------------------------------------
+def fill_encoding(bw: int, enc_min: float, enc_max: float) -> _lib.AqEncoding:
+    e = _lib.AqEncoding()
+    check(lib.aq_fill_encoding(int(bw), float(enc_min), float(enc_max), C.byref(e)), "aq_fill_encoding")
+    return e
+
+
+def computed_encodings(bw: int, mn: float, mx: float, symmetric=False, strict=False, unsigned_sym=False):
+    e = _lib.AqEncoding()
+    check(lib.aq_computed_encodings(int(bw), float(mn), float(mx), int(symmetric), int(strict), int(unsigned_sym),
+                                    C.byref(e)), "aq_computed_encodings")
+    return e
+
+
+def minmax_encoding(bw: int, stat_min: float, stat_max: float, symmetric=False, strict=False, unsigned_sym=False):
+    e = _lib.AqEncoding()
+    check(lib.aq_minmax_encoding(int(bw), float(stat_min), float(stat_max), int(symmetric), int(strict),
+                                 int(unsigned_sym), C.byref(e)), "aq_minmax_encoding")
+    return e
+
+
+def _f32c(t: torch.Tensor, name: str) -> torch.Tensor:
+    _cuda(t, name)
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"aimet_b200: {name} must be float32 for libpymo-semantics ops, got {t.dtype}")
+    return t
+
+
+def qdq_per_tensor(x: torch.Tensor, enc_min: float, enc_max: float, bw: int, rounding_mode: int = 0,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    x = _f32c(x, "input").contiguous()
+    out = torch.empty_like(x) if out is None else out
+    with _DeviceGuard(x):
+        check(lib.aq_qdq_per_tensor(x.data_ptr(), out.data_ptr(), x.numel(), float(enc_min), float(enc_max), int(bw),
+                                    int(rounding_mode), _stream(x)), "aq_qdq_per_tensor")
+    return out
+
+
+def quantize_per_tensor(x: torch.Tensor, enc_min: float, enc_max: float, bw: int, shift_to_signed: bool = False,
+                        rounding_mode: int = 0) -> torch.Tensor:
+    x = _f32c(x, "input").contiguous()
+    out = torch.empty_like(x)
+    with _DeviceGuard(x):
+        check(lib.aq_quantize_per_tensor(x.data_ptr(), out.data_ptr(), x.numel(), float(enc_min), float(enc_max),
+                                         int(bw), int(rounding_mode), int(shift_to_signed), _stream(x)),
+              "aq_quantize_per_tensor")
+    return out
+
+
+def qdq_per_channel(x: torch.Tensor, enc_min: torch.Tensor, enc_max: torch.Tensor, num_ch: int, inner: int,
+                    num_steps: float, rounding_mode: int = 0) -> torch.Tensor:
+    x = _f32c(x, "input").contiguous()
+    enc_min = _f32c(enc_min, "enc_min").contiguous()
+    enc_max = _f32c(enc_max, "enc_max").contiguous()
+    _same_device(x, enc_min, enc_max)
+    if enc_min.numel() != num_ch or enc_max.numel() != num_ch:
+        raise RuntimeError("aimet_b200: need one min and one max per channel")
+    out = torch.empty_like(x)
+    with _DeviceGuard(x):
+        check(lib.aq_qdq_per_channel(x.data_ptr(), out.data_ptr(), x.numel(), int(num_ch), int(inner),
+                                     enc_min.data_ptr(), enc_max.data_ptr(), float(num_steps), int(rounding_mode),
+                                     _stream(x)), "aq_qdq_per_channel")
+    return out
+
+
+def qdq_broadcast(x: torch.Tensor, in_strides, enc_strides, enc_min, enc_max, enc_delta, enc_offset) -> torch.Tensor:
+    x = _f32c(x, "input").contiguous()
+    encs = [_f32c(e, "encoding").contiguous() for e in (enc_min, enc_max, enc_delta, enc_offset)]
+    _same_device(x, *encs)
+    nd = len(in_strides)
+    ins = (C.c_int64 * nd)(*[int(s) for s in in_strides])
+    ens = (C.c_int64 * nd)(*[int(s) for s in enc_strides])
+    out = torch.empty_like(x)
+    with _DeviceGuard(x):
+        check(lib.aq_qdq_broadcast(x.data_ptr(), out.data_ptr(), x.numel(), nd, ins, ens,
+                                   *[e.data_ptr() for e in encs], _stream(x)), "aq_qdq_broadcast")
+    return out
+
+
+def ste_backward_v1(x: torch.Tensor, grad: torch.Tensor, enc_min: torch.Tensor, enc_max: torch.Tensor,
+                    num_ch: int = 1, inner: Optional[int] = None) -> torch.Tensor:
+    x = _f32c(x, "input").contiguous()
+    grad = _f32c(grad, "grad").contiguous()
+    enc_min = _f32c(enc_min, "enc_min").contiguous()
+    enc_max = _f32c(enc_max, "enc_max").contiguous()
+    _same_device(x, grad, enc_min, enc_max)
+    if inner is None:
+        inner = max(x.numel(), 1)
+    dx = torch.empty_like(grad)
+    with _DeviceGuard(x):
+        check(lib.aq_ste_backward_v1(x.data_ptr(), grad.data_ptr(), dx.data_ptr(), x.numel(), int(num_ch),
+                                     int(inner), enc_min.data_ptr(), enc_max.data_ptr(), _stream(x)),
+              "aq_ste_backward_v1")
+    return dx
+
+
+# ---------------------------------------------------------------------------------------------------
+# v2 semantics (flat, physically-contiguous tensors; geometry resolved by the caller)
+# ---------------------------------------------------------------------------------------------------
+def v2_quantize(x: torch.Tensor, y: torch.Tensor, mask: Optional[torch.Tensor], scale: torch.Tensor,
+                offset: torch.Tensor, qmin: int, qmax: int, num_ch: int, inner: int, out_kind: int,
+                internal_f16: bool = False) -> None:
+    with _DeviceGuard(x):
+        check(lib.aq_v2_quantize(x.data_ptr(), y.data_ptr(), mask.data_ptr() if mask is not None else None, _dt(x),
+                                 x.numel(), int(num_ch), int(inner), scale.data_ptr(), offset.data_ptr(),
+                                 float(qmin), float(qmax), int(out_kind), int(internal_f16), _stream(x)),
+              "aq_v2_quantize")
+
+
+def v2_dequantize(x: torch.Tensor, y: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor, num_ch: int,
+                  inner: int, internal_f16: bool = False) -> None:
+    with _DeviceGuard(x):
+        check(lib.aq_v2_dequantize(x.data_ptr(), y.data_ptr(), _dt(x), x.numel(), int(num_ch), int(inner),
+                                   scale.data_ptr(), offset.data_ptr(), int(internal_f16), _stream(x)),
+              "aq_v2_dequantize")
+
+
+def v2_qdq_backward(grad: torch.Tensor, mask: torch.Tensor, dx: torch.Tensor) -> None:
+    with _DeviceGuard(grad):
+        check(lib.aq_v2_qdq_backward(grad.data_ptr(), mask.data_ptr(), dx.data_ptr(), _dt(grad), grad.numel(),
+                                     _stream(grad)), "aq_v2_qdq_backward")
+
+
+# ---------------------------------------------------------------------------------------------------
+# statistics
+# ---------------------------------------------------------------------------------------------------
+def minmax(x: torch.Tensor, num_ch: int = 1, inner: Optional[int] = None, propagate_nan: bool = False,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fused min/max.  Returns a float32 tensor [2, num_ch] (row 0 = min, row 1 = max) on x's device."""
+    _cuda(x, "input")
+    x = x.contiguous()
+    n = x.numel()
+    if inner is None:
+        inner = max(n, 1)
+    if out is None:
+        out = torch.empty((2, num_ch), dtype=torch.float32, device=x.device)
+    need = int(lib.aq_minmax_workspace_bytes(n, int(num_ch), int(inner)))
+    if need < 0:
+        check(need, "aq_minmax_workspace_bytes")
+    ws = workspace(x, need)
+    with _DeviceGuard(x):
+        check(lib.aq_minmax(x.data_ptr(), _dt(x), n, int(num_ch), int(inner), out[0].data_ptr(), out[1].data_ptr(),
+                            int(propagate_nan), ws.data_ptr(), ws.numel(), _stream(x)), "aq_minmax")
+    return out
+
+
+class TfeDeviceState:
+    """Device-resident TF-Enhanced statistics of one quantizer: bucket grid + per-batch histogram rows.
+
+    ``hists`` is [capacity, 512] uint32 (stored as int32) and ``counts`` [capacity] int64; row b belongs to the
+    b-th batch offered.  A batch seen before the grid exists (all-zero data) keeps count 0 and is skipped by
+    the replay, exactly as the reference drops it.
+    """
+
+    def __init__(self, device: torch.device, capacity: int = 64):
+        self.device = torch.device(device)
+        self.state = torch.zeros(_lib.TFE_STATE_BYTES, dtype=torch.uint8, device=self.device)
+        self.hists = torch.zeros((capacity, _lib.AQ_PDF_SIZE), dtype=torch.int32, device=self.device)
+        self.counts = torch.zeros(capacity, dtype=torch.int64, device=self.device)
+        self.num_batches = 0
+        self.initialized_on_host = False
+        self.pdf = torch.zeros(_lib.AQ_PDF_SIZE, dtype=torch.float64, device=self.device)
+        self.iterations = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.encoding = torch.zeros(5, dtype=torch.float64, device=self.device)
+
+    def _grow(self, need: int):
+        cap = self.hists.shape[0]
+        if need <= cap:
+            return
+        new_cap = max(need, cap * 2)
+        h = torch.zeros((new_cap, _lib.AQ_PDF_SIZE), dtype=torch.int32, device=self.device)
+        c = torch.zeros(new_cap, dtype=torch.int64, device=self.device)
+        h[:cap].copy_(self.hists)
+        c[:cap].copy_(self.counts)
+        self.hists, self.counts = h, c
+
+    def reserve(self, capacity: int):
+        self._grow(capacity)
+
+    def init_grid_from(self, minmax_dev: torch.Tensor):
+        """minmax_dev: float32 tensor holding {min, max} on the device."""
+        with _DeviceGuard(self.state):
+            check(lib.aq_tfe_init_grid(minmax_dev.data_ptr(), self.state.data_ptr(), _stream(self.state)),
+                  "aq_tfe_init_grid")
+
+    def is_initialized(self) -> bool:
+        """Host view of the device flag (synchronises once; cached after it turns true)."""
+        if not self.initialized_on_host:
+            flag = self.state[_lib.AqTfeState.initialized.offset:_lib.AqTfeState.initialized.offset + 4]
+            self.initialized_on_host = bool(flag.view(torch.int32).item())
+        return self.initialized_on_host
+
+    def add_batch(self, x: torch.Tensor, row: Optional[int] = None):
+        """Histogram of one batch into row ``row`` (default: the next one)."""
+        if x.dtype != torch.float32:
+            raise RuntimeError("aimet_b200: TF-Enhanced statistics take float32 input (callers upcast)")
+        x = _cuda(x, "input").contiguous()
+        if row is None:
+            row = self.num_batches
+        self._grow(row + 1)
+        self.num_batches = max(self.num_batches, row + 1)
+        with _DeviceGuard(x):
+            check(lib.aq_tfe_histogram(x.data_ptr(), x.numel(), self.state.data_ptr(), self.hists[row].data_ptr(),
+                                       self.counts[row:].data_ptr(), _stream(x)), "aq_tfe_histogram")
+
+    def replay(self, num_batches: Optional[int] = None):
+        nb = self.num_batches if num_batches is None else num_batches
+        with _DeviceGuard(self.state):
+            check(lib.aq_tfe_pdf_replay(self.hists.data_ptr(), self.counts.data_ptr(), nb, self.pdf.data_ptr(),
+                                        self.iterations.data_ptr(), _stream(self.state)), "aq_tfe_pdf_replay")
+
+    def search(self, stats_updated: bool, bw: int, symmetric: bool, strict: bool, unsigned_sym: bool) -> torch.Tensor:
+        need = int(lib.aq_tfe_search_workspace_bytes())
+        ws = workspace(self.state, need)
+        with _DeviceGuard(self.state):
+            check(lib.aq_tfe_search(self.state.data_ptr(), self.pdf.data_ptr(), int(stats_updated), int(bw),
+                                    int(symmetric), int(strict), int(unsigned_sym), self.encoding.data_ptr(),
+                                    ws.data_ptr(), ws.numel(), _stream(self.state)), "aq_tfe_search")
+        return self.encoding
+
+    def x_left(self) -> torch.Tensor:
+        return self.state[:_lib.AQ_PDF_SIZE * 8].view(torch.float64)

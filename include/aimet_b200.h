@@ -1,0 +1,228 @@
+/*
+ * aimet_b200 -- C ABI of the B200 (sm_100a) quantization-simulation hot path.
+ *
+ * Drop-in boundary for the arithmetic layer of AIMET's quantsim:
+ *   - libpymo / "v1" semantics  (DlQuantization C++: clamp -> divide -> round-half-away -> dequantize)
+ *   - aimet_torch "v2" semantics (torch_builtins: divide -> round-half-even -> offset -> clamp -> dequantize)
+ *
+ * Conventions
+ *   - Every entry point returns 0 (AQ_OK) or a negative aq_status_t; nothing throws.
+ *   - Pointers named d_* are DEVICE pointers on the current CUDA device; h_* are host pointers.
+ *   - Nothing here allocates or frees device memory, and nothing synchronises the device unless the
+ *     comment says so.  Scratch memory is caller-owned ("workspace").
+ *   - `stream` is a cudaStream_t passed as void*; NULL means the legacy default stream.
+ *   - Element counts and strides are 64-bit.
+ *   - Channel geometry: for a contiguous tensor of n elements, element i belongs to encoding
+ *     channel (i / inner) % num_ch.  Per-tensor: num_ch = 1.  Per-output-channel conv weight
+ *     [C,I,kh,kw]: num_ch = C, inner = I*kh*kw.  Blockwise [O, I] with block B on the input dim and
+ *     scales [O, I/B]: num_ch = O*I/B, inner = B.  NCHW activations per channel: num_ch = C, inner = H*W.
+ *
+ * Reference citations are paths inside the AIMET 1.35 source tree.
+ */
+#ifndef AIMET_B200_H_
+#define AIMET_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C"
+{
+#endif
+
+typedef enum
+{
+    AQ_OK              = 0,
+    AQ_ERR_INVALID_ARG = -1, /* NULL pointer, negative size, bad enum, misaligned workspace ... */
+    AQ_ERR_UNSUPPORTED = -2, /* combination not implemented (e.g. stochastic rounding) */
+    AQ_ERR_CUDA        = -3, /* a CUDA runtime call or launch failed; see aq_last_cuda_error() */
+    AQ_ERR_WORKSPACE   = -4, /* workspace missing or too small */
+    AQ_ERR_TOO_LARGE   = -5  /* size beyond a documented maximum */
+} aq_status_t;
+
+typedef enum
+{
+    AQ_F32  = 0,
+    AQ_F16  = 1,
+    AQ_BF16 = 2
+} aq_dtype_t;
+
+/* Mirrors DlQuantization::RoundingMode (ModelOptimizations/DlQuantization/include/DlQuantization/Quantization.hpp:145-149).
+ * Stochastic rounding is not reproducible in the reference (rand()/clock()-seeded curand) and is rejected here. */
+typedef enum
+{
+    AQ_ROUND_NEAREST    = 0,
+    AQ_ROUND_STOCHASTIC = 1
+} aq_rounding_t;
+
+/* Mirrors DlQuantization::TfEncoding (Quantization.hpp:113-120). */
+typedef struct
+{
+    double min;
+    double max;
+    double delta;
+    double offset;
+    int bw;
+} aq_encoding_t;
+
+#define AQ_PDF_SIZE 512 /* DlQuantization PDF_SIZE, src/math_functions.hpp:80 */
+
+/* Device-resident TF-Enhanced histogram state (one per quantizer).
+ * Replaces DlQuantization::PDF::xLeft plus the per-call bucket geometry of UpdatePdf
+ * (src/math_functions.hpp:59-67, src/math_functions.cpp:264-268). */
+typedef struct
+{
+    double x_left[AQ_PDF_SIZE]; /* bucket left edges */
+    float bucket_size;          /* (float)(x_left[1]-x_left[0]) */
+    float pdf_offset;           /* (float)x_left[0] / bucket_size */
+    int32_t initialized;        /* 0 until a batch with (min,max) != (0,0) was seen */
+    int32_t reserved;
+} aq_tfe_state_t;
+
+/* ------------------------------------------------------------------------------------------------
+ * Library / error helpers
+ * ---------------------------------------------------------------------------------------------- */
+int aq_version(void);
+const char* aq_status_string(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* aq_last_cuda_error(void);
+/* Number of kernel launches issued by the library in this process (for launch accounting). */
+int64_t aq_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Host-side encoding arithmetic (no GPU involved)
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Replaces TensorQuantizationSim<float>::fillEncodingInfo / generateScaleOffset
+ * (ModelOptimizations/DlQuantization/src/TensorQuantizationSim.cpp:62-92) and gateMinMax
+ * (src/quantization_utils.cpp:145-156). */
+int aq_fill_encoding(int bw, double enc_min, double enc_max, aq_encoding_t* h_out);
+
+/* Replaces getComputedEncodings (src/quantization_utils.cpp:58-143). */
+int aq_computed_encodings(int bw, double min, double max, int symmetric, int strict_symmetric, int unsigned_symmetric,
+                          aq_encoding_t* h_out);
+
+/* Replaces TfEncodingAnalyzer<float>::computeEncoding (src/TfEncodingAnalyzer.cpp:80-101) given the
+ * accumulated running min / max. */
+int aq_minmax_encoding(int bw, double stat_min, double stat_max, int symmetric, int strict_symmetric,
+                       int unsigned_symmetric, aq_encoding_t* h_out);
+
+/* ------------------------------------------------------------------------------------------------
+ * libpymo-semantics fake-quant (fp32 only, like the reference)
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Replaces TensorQuantizationSim<float>::quantizeDequantizeTensor
+ * (src/TensorQuantizationSim.cpp:94-114 -> src/trim_functions.cpp:93-113,173-182; GPU kernel
+ * src/trim_functions.cu:46-60).  The grid is re-derived from (enc_min, enc_max, bw) on every call. */
+int aq_qdq_per_tensor(const float* d_in, float* d_out, int64_t n, double enc_min, double enc_max, int bw,
+                      int rounding_mode, void* stream);
+
+/* Replaces TensorQuantizationSim<float>::quantizeTensor (src/TensorQuantizationSim.cpp:116-126 ->
+ * src/trim_functions.cpp:202-218; GPU kernel src/trim_functions.cu:62-76).  Integer codes in a float container. */
+int aq_quantize_per_tensor(const float* d_in, float* d_out, int64_t n, double enc_min, double enc_max, int bw,
+                           int rounding_mode, int shift_to_signed, void* stream);
+
+/* Replaces AimetTensorQuantizer::quantizeDequantizePerChannel
+ * (TrainingExtensions/torch/src/AimetTensorQuantizer.cpp:256-307) together with
+ * TensorQuantizationSim<float>::quantizeDequantizeTensorPerChannel (src/TensorQuantizationSim.cpp:287-317,
+ * src/trim_functions.cpp:697-709, kernel src/trim_functions.cu:78-92).
+ * d_enc_min / d_enc_max: raw (un-gated) per-channel float min/max, num_ch entries, on the device.
+ * num_steps: 2^bw-1, minus one when channel 0 is value-symmetric (the caller decides, as the reference's host
+ * code does).  Gating, delta = (max-min)/num_steps and offset = round-half-even(min/delta) happen in the kernel
+ * in fp32, in the reference's operation order. */
+int aq_qdq_per_channel(const float* d_in, float* d_out, int64_t n, int64_t num_ch, int64_t inner,
+                       const float* d_enc_min, const float* d_enc_max, double num_steps, int rounding_mode,
+                       void* stream);
+
+/* Replaces quantizeDequantizeBroadcast (src/trim_functions.cpp:633-687, kernel src/trim_functions.cu:96-122;
+ * contract in include/DlQuantization/Quantization.hpp:152-222).  Encodings are used as given.
+ * h_in_strides / h_enc_strides: HOST arrays of ndims (<= 8) element strides; encoding strides are 0 on
+ * broadcast dimensions. */
+int aq_qdq_broadcast(const float* d_in, float* d_out, int64_t n, int64_t ndims, const int64_t* h_in_strides,
+                     const int64_t* h_enc_strides, const float* d_enc_min, const float* d_enc_max,
+                     const float* d_enc_delta, const float* d_enc_offset, void* stream);
+
+/* Straight-through backward of the v1 wrappers: dx = g * [enc_min <= x <= enc_max], per tensor
+ * (num_ch = 1) or per channel.  Replaces compute_dloss_by_dx
+ * (TrainingExtensions/torch/src/python/aimet_torch/v1/quantsim_straight_through_grad.py:91-118).
+ * d_enc_min / d_enc_max hold num_ch floats on the device. */
+int aq_ste_backward_v1(const float* d_x, const float* d_grad, float* d_dx, int64_t n, int64_t num_ch, int64_t inner,
+                       const float* d_enc_min, const float* d_enc_max, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * v2-semantics affine fake-quant (fp32 / fp16 / bf16 storage, fp32 internal math)
+ * ---------------------------------------------------------------------------------------------- */
+
+#define AQ_V2_OUT_QDQ   0 /* y = (clamp(round(x/s) - o, qmin, qmax) + o) * s */
+#define AQ_V2_OUT_CODES 1 /* y =  clamp(round(x/s) - o, qmin, qmax)          */
+
+/* Replaces QuantDequantFunc.forward / QuantizeFunc.forward
+ * (TrainingExtensions/torch/src/python/aimet_torch/v2/quantization/affine/backends/torch_builtins.py:290-327,208-236).
+ * d_scale / d_offset: num_ch fp32 values on the device (already cast to the internal dtype by the caller).
+ * d_mask (may be NULL): one byte per element, 1 where qmin <= round(x/s) - o <= qmax.
+ * internal_f16 != 0 rounds every intermediate to fp16 (the reference keeps fp16 as its internal dtype when the
+ * grid is narrow enough; only valid with dtype == AQ_F16). */
+int aq_v2_quantize(const void* d_x, void* d_y, uint8_t* d_mask, int dtype, int64_t n, int64_t num_ch, int64_t inner,
+                   const float* d_scale, const float* d_offset, double qmin, double qmax, int out_kind,
+                   int internal_f16, void* stream);
+
+/* Replaces DequantizeFunc.forward (torch_builtins.py:251-276): y = (x + o) * s. */
+int aq_v2_dequantize(const void* d_x, void* d_y, int dtype, int64_t n, int64_t num_ch, int64_t inner,
+                     const float* d_scale, const float* d_offset, int internal_f16, void* stream);
+
+/* Replaces the tensor-gradient of QuantDequantFunc.backward (torch_builtins.py:329-344): dx = grad * mask. */
+int aq_v2_qdq_backward(const void* d_grad, const uint8_t* d_mask, void* d_dx, int dtype, int64_t n, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Statistics
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Bytes of scratch aq_minmax needs for this geometry (0 is possible). */
+int64_t aq_minmax_workspace_bytes(int64_t n, int64_t num_ch, int64_t inner);
+
+/* One fused pass producing min and max per encoding channel.
+ * Replaces GetMin + GetMax (src/math_functions.cpp:61-100,327-347; thrust versions src/math_functions.cu:52-64)
+ * and the v2 observer reduction (aimet_torch/v2/quantization/encoding_analyzer.py:100-104 with
+ * aimet_torch/v2/utils.py:69-90).
+ * d_out_min / d_out_max: num_ch floats each (values of 16-bit inputs are exact in fp32).
+ * propagate_nan = 0: NaNs are ignored (std::min/std::max folds of the reference C++);
+ * propagate_nan = 1: any NaN in a channel makes both outputs NaN (torch.min / torch.max).
+ * An empty channel yields +inf / -inf.  d_workspace must be 256-byte aligned. */
+int aq_minmax(const void* d_x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* d_out_min,
+              float* d_out_max, int propagate_nan, void* d_workspace, int64_t workspace_bytes, void* stream);
+
+/* Builds the bucket grid from a batch's (min,max) held on the device; leaves the state un-initialised when both
+ * are zero.  Replaces the first-batch branch of UpdatePdf and InitializePdf<float>
+ * (src/math_functions.cpp:207-262).  d_minmax: {min, max} floats on the device.  No-op if already initialised. */
+int aq_tfe_init_grid(const float* d_minmax, aq_tfe_state_t* d_state, void* stream);
+
+/* One batch of the 512-bucket histogram: bucket = round-half-away(x / bucket_size - pdf_offset), samples outside
+ * [0, 512) are dropped.  Replaces GetHistogram_cpu / histogramCountKernel + histogramReduceSumKernel
+ * (src/math_functions.cpp:367-384, src/math_functions.cu:125-211).
+ * d_hist: 512 uint32 counters, ADDED to (zero them for a fresh batch).  d_count (may be NULL): one int64 that is
+ * set to n when the state is initialised and to 0 otherwise (the reference skips such batches). */
+int aq_tfe_histogram(const float* d_x, int64_t n, const aq_tfe_state_t* d_state, uint32_t* d_hist, int64_t* d_count,
+                     void* stream);
+
+/* Replays the running mean pdf <- (pdf*k + hist/cnt)/(k+1) over `num_batches` per-batch histograms in order,
+ * skipping rows whose count is 0.  Replaces the accumulation loop of UpdatePdf (src/math_functions.cpp:278-287).
+ * d_hists: [num_batches, 512] uint32; d_counts: [num_batches] int64; d_pdf: 512 doubles (overwritten);
+ * d_iterations: one int32 (overwritten with the number of batches used). */
+int aq_tfe_pdf_replay(const uint32_t* d_hists, const int64_t* d_counts, int64_t num_batches, double* d_pdf,
+                      int32_t* d_iterations, void* stream);
+
+/* Bytes of scratch for aq_tfe_search. */
+int64_t aq_tfe_search_workspace_bytes(void);
+
+/* SQNR grid search; one warp per candidate (delta, offset).  Replaces
+ * TfEnhancedEncodingAnalyzer<float>::computeEncoding (src/TfEnhancedEncodingAnalyzer.cpp:78-397).
+ * stats_updated: whether any batch was ever offered (selects the all-zero-data encoding when the state is still
+ * un-initialised).  d_out_encoding: 5 doubles {min, max, delta, offset, bw} on the device. */
+int aq_tfe_search(const aq_tfe_state_t* d_state, const double* d_pdf, int stats_updated, int bw, int symmetric,
+                  int strict_symmetric, int unsigned_symmetric, double* d_out_encoding, void* d_workspace,
+                  int64_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AIMET_B200_H_ */
