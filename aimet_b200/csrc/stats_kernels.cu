@@ -388,10 +388,11 @@ static int minmax_t(const T* x, int64_t n, int64_t num_ch, int64_t inner, float*
     float *pmin = out_min, *pmax = out_max;
     if (!p.direct)
     {
-        const int64_t need = 2 * p.rows * p.nseg * (int64_t) sizeof(float);
+        // the first 256 bytes hold the whole-tensor kernel's ticket counter and must stay untouched
+        const int64_t need = 256 + 2 * p.rows * p.nseg * (int64_t) sizeof(float);
         if (ws_bytes < need)
             return AQ_ERR_WORKSPACE;
-        pmin = static_cast<float*>(ws);
+        pmin = reinterpret_cast<float*>(static_cast<char*>(ws) + 256);
         pmax = pmin + p.rows * p.nseg;
     }
     switch (vec)

@@ -94,7 +94,8 @@ __global__ void __launch_bounds__(kSearchWarps * 32) tfe_search_kernel(SearchArg
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slot = blockIdx.x * kSearchWarps + warp;
-    __shared__ double s_term[kSearchWarps][AQ_PDF_SIZE];
+    __shared__ double s_term[kSearchWarps][AQ_PDF_SIZE];   // bottom-saturation or in-range term of a bucket
+    __shared__ double s_top[kSearchWarps][AQ_PDF_SIZE];    // top-saturation term (ranges may overlap, see below)
     __shared__ bool s_last;
 
     const int initialized = a.st->initialized;
@@ -218,33 +219,47 @@ __global__ void __launch_bounds__(kSearchWarps * 32) tfe_search_kernel(SearchArg
             __double2float_rn(__dadd_rn(__dadd_rn((double) pdf_start, __dmul_rn((double) min_ind, pdf_step)), half));
         const float max_mid =
             __double2float_rn(__dadd_rn(__dadd_rn((double) pdf_start, __dmul_rn((double) max_ind, pdf_step)), half));
+        // The reference runs three loops: i < min_ind (bottom), i >= max_ind (top), min_ind <= i < max_ind (middle).
+        // When max_ind < min_ind (a float overflow in the index arithmetic collapses max_ind to 0) a bucket is
+        // counted in BOTH saturation sums, so the two are kept in separate arrays.
         for (int i = lane; i < AQ_PDF_SIZE; i += 32)
         {
             const double mid = __dadd_rn(__dadd_rn((double) pdf_start, __dmul_rn((double) i, pdf_step)), half);
-            double d;
+            double low       = 0.0;
             if (i < min_ind)
-                d = __dsub_rn(mid, (double) min_mid);
-            else if (i >= max_ind)
-                d = __dsub_rn(mid, (double) max_mid);
-            else
+            {
+                const double d = __dsub_rn(mid, (double) min_mid);
+                low            = __dmul_rn(pdf[i], __dmul_rn(d, d));
+            }
+            else if (i < max_ind)
             {
                 const float fv = __double2float_rn(mid);
                 const int q    = to_int_x86(round_half_away(__fsub_rn(__fdiv_rn(fv, c_delta), (float) c_offset)));
-                const float dq = __fmul_rn(c_delta, (float) (q + c_offset));
-                d              = (double) __fsub_rn(fv, dq);
+                const float dq = __fmul_rn(c_delta, (float) (int) ((unsigned) q + (unsigned) c_offset));
+                const double d = (double) __fsub_rn(fv, dq);
+                low            = __dmul_rn(pdf[i], __dmul_rn(d, d));
             }
-            s_term[warp][i] = __dmul_rn(pdf[i], __dmul_rn(d, d));
+            s_term[warp][i] = low;
+            double top      = 0.0;
+            if (i >= max_ind)
+            {
+                const double d = __dsub_rn(mid, (double) max_mid);
+                top            = __dmul_rn(pdf[i], __dmul_rn(d, d));
+            }
+            s_top[warp][i] = top;
         }
         __syncwarp();
-        // three ordered sums, one lane each: [0,min_ind) bottom, [max_ind,512) top, [min_ind,max_ind) middle
+        // three ordered sums, one lane each
         double part = 0.0;
-        if (lane < 3)
-        {
-            const int lo = lane == 0 ? 0 : (lane == 1 ? max_ind : min_ind);
-            const int hi = lane == 0 ? min_ind : (lane == 1 ? AQ_PDF_SIZE : max_ind);
-            for (int i = lo; i < hi; ++i)
+        if (lane == 0)
+            for (int i = 0; i < min_ind; ++i)
                 part = __dadd_rn(part, s_term[warp][i]);
-        }
+        else if (lane == 1)
+            for (int i = max_ind; i < AQ_PDF_SIZE; ++i)
+                part = __dadd_rn(part, s_top[warp][i]);
+        else if (lane == 2)
+            for (int i = min_ind; i < max_ind; ++i)
+                part = __dadd_rn(part, s_term[warp][i]);
         const double bottom = __shfl_sync(0xffffffffu, part, 0);
         const double top    = __shfl_sync(0xffffffffu, part, 1);
         const double quant  = __shfl_sync(0xffffffffu, part, 2);

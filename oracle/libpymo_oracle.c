@@ -359,7 +359,7 @@ double orc_tfe_cost(const double* x_left, const double* pdf, int bw, float delta
     {
         float fv  = (float) ((double) pdf_start + i * pdf_step + pdf_step / 2);
         int q     = to_int_x86_f(roundf(fv / delta - (float) offset));
-        float dq  = delta * (float) (q + offset);
+        float dq  = delta * (float) (int) ((unsigned) q + (unsigned) offset); /* wraps like the x86 build */
         double d  = (double) (fv - dq);
         quant += pdf[i] * (d * d);
     }
