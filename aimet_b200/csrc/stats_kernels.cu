@@ -469,8 +469,6 @@ __global__ void __launch_bounds__(AQ_PDF_SIZE) tfe_init_grid_kernel(const float*
 }
 
 constexpr int kHistThreads = 512;
-constexpr int kHistUnroll  = 4;
-constexpr int kHistPad     = AQ_PDF_SIZE + 1;   // odd row stride: replica r, bucket b -> bank (r + b) % 32
 
 // Bucket of one sample: (int) roundf(x / bucket_size - pdf_offset), valid when inside [0, 512).
 // For t > -0.5 the half-away rounding equals floor(t + 0.5); adding with round-down keeps the sum from being
@@ -482,92 +480,134 @@ __device__ __forceinline__ bool bucket_of(float x, float bs, float po, int& k)
     return (t > -0.5f) && ((unsigned) k < (unsigned) AQ_PDF_SIZE);
 }
 
-// Shared-memory privatised histogram with REPL replicas selected by lane id (so lanes of one warp that hit the
-// same bucket mostly land on different addresses), plus a register counter for the bucket that holds exact
-// zeros -- the usual spike of post-ReLU activations.
-template <int REPL>
-__global__ void __launch_bounds__(kHistThreads) tfe_hist_kernel(const float* __restrict__ x, int64_t n,
-                                                                const aq_tfe_state_t* __restrict__ st,
-                                                                uint32_t* __restrict__ hist,
-                                                                int64_t* __restrict__ count)
+// ---- lane-private layout ------------------------------------------------------------------------------------
+// counters[bucket][lane]: a lane only ever touches shared-memory bank `lane`, so one warp-wide atomic never has
+// a bank conflict or a same-address collision, whatever the data looks like (post-ReLU spikes, a few hot
+// buckets, ...).  Row 512 is a trash row for samples that fall outside the grid, which keeps the hot loop free
+// of branches.  513 rows x 32 lanes x 4 B = 65,664 B per CTA; two persistent CTAs of 1024 threads per SM.
+constexpr int kLaneHistThreads = 1024;
+constexpr int kLaneHistRows    = AQ_PDF_SIZE + 1;
+constexpr int kLaneHistBytes   = kLaneHistRows * 32 * (int) sizeof(uint32_t);
+constexpr float kTwo23         = 8388608.0f;
+constexpr uint32_t kTwo23Bits  = 0x4B000000u;
+
+// Hot-loop bucket computation without a division and without conversion instructions.
+//   s  = x * (1/bucket_size) + (1.5 - pdf_offset)      one FMA; approximates t + 1.5 with t = x/bs - po
+//   s2 = RD(s + 2^23)                                   its low mantissa bits now hold floor(s)
+//   g  = s - (s2 - (2^23 - 0.5))                        fractional part minus one half (both steps exact)
+// The exact formula round_half_away(RN(RN(x/bs) - po)) changes value only where t + 1.5 crosses an integer, and
+// |s - (t + 1.5)| < margin (see hist_margin), so when |g| < 0.5 - margin the bucket is floor(s) - 1 for certain.
+// Everything else (near a boundary, NaN, Inf) is reported through `sure = false`; the caller takes that one
+// sample back out of the counters and redoes it with the exact division formula.
+// Returns the row to increment (512 = trash row for samples outside the grid).
+__device__ __forceinline__ uint32_t bucket_row_fast(float x, float rbs, float c, float eps, bool& sure)
+{
+    const float s  = fmaf(x, rbs, c);
+    const float s2 = __fadd_rd(s, kTwo23);
+    const float g  = s - (s2 - 8388607.5f);
+    sure           = fabsf(g) < eps;   // false for NaN
+    return min(__float_as_uint(s2) - (kTwo23Bits + 1u), (uint32_t) AQ_PDF_SIZE);
+}
+
+// counters[row][lane] += v with a 32-bit shared-window address (one LEA + one RED per sample)
+__device__ __forceinline__ void lane_hist_add(uint32_t base, uint32_t row, int v)
+{
+    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"(base + (row << 7)), "r"(v));
+}
+
+// Bound of |s - (t + 1.5)| for every sample whose approximate position s lies within [0, 515]:
+//   exact path:  RN(x/bs) = q(1+e1),  t = (RN(x/bs) - po)(1+e2)
+//   fast path:   rbs = (1/bs)(1+e3),  c = (1.5-po)(1+e4),  s = (x*rbs + c)(1+e5)          |e_i| <= 2^-24
+//   => |s - (t+1.5)| <= 2^-24 (2|q| + |c| + |s| + |t|),  |q| <= |po| + 515,  |c| <= |po| + 1.5,  |s|,|t| <= 515
+//   <= 2^-24 (3|po| + 2062); a quarter more is added for the second-order terms.
+// Samples farther out cannot come back into the grid through this error as long as the margin stays below a
+// quarter bucket, which the kernel checks.
+__host__ __device__ inline float hist_margin(float po)
+{
+    return 1.25f * 5.9604644775390625e-08f /* 2^-24 */ * (3.0f * fabsf(po) + 2062.0f);
+}
+
+constexpr int kLaneUnroll = 4;
+
+__global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(const float* __restrict__ x, int64_t n,
+                                                                            const aq_tfe_state_t* __restrict__ st,
+                                                                            uint32_t* __restrict__ hist,
+                                                                            int64_t* __restrict__ count)
 {
     const int initialized = st->initialized;
     if (blockIdx.x == 0 && threadIdx.x == 0 && count)
         *count = initialized ? n : 0;
     if (!initialized)
         return;
-    __shared__ uint32_t s_hist[REPL * kHistPad];
-    for (int i = threadIdx.x; i < REPL * kHistPad; i += kHistThreads)
-        s_hist[i] = 0;
+    extern __shared__ uint32_t s_lane_hist[];   // [513][32]
+    for (int i = threadIdx.x; i < kLaneHistRows * 32; i += kLaneHistThreads)
+        s_lane_hist[i] = 0;
     __syncthreads();
 
     const float bs = st->bucket_size, po = st->pdf_offset;
-    uint32_t* my = s_hist + (threadIdx.x % REPL) * kHistPad;
-    int zero_bucket;
-    if (!bucket_of(0.0f, bs, po, zero_bucket))
-        zero_bucket = -1;
-    uint32_t zero_count = 0;
+    const float margin = hist_margin(po);
+    // A margin of a quarter bucket or more means the grid sits so far from zero that the reciprocal form is
+    // useless; eps <= 0 then sends every sample through the exact path.
+    const float eps = margin < 0.25f ? 0.5f - margin : 0.0f;
+    const float rbs = __frcp_rn(bs);
+    const float c   = 1.5f - po;
+    // padding sample for partial groups: above the grid and mid-bucket, so it is `sure` and lands in the trash row
+    const float pad     = (514.5f - c) * bs;
+    const int lane      = threadIdx.x & 31;
+    const uint32_t base = (uint32_t) __cvta_generic_to_shared(s_lane_hist + lane);
 
     const int64_t npack  = n / 4;
-    const int64_t stride = (int64_t) gridDim.x * kHistThreads;
-    int64_t p            = (int64_t) blockIdx.x * kHistThreads + threadIdx.x;
-    for (; p + (kHistUnroll - 1) * stride < npack; p += kHistUnroll * stride)
+    const int64_t stride = (int64_t) gridDim.x * kLaneHistThreads;
+    // Every thread sweeps packets p, p + stride, ...; kLaneUnroll of them are in flight at once.
+    for (int64_t p = (int64_t) blockIdx.x * kLaneHistThreads + threadIdx.x; p < npack; p += kLaneUnroll * stride)
     {
-        float4 v[kHistUnroll];
+        float4 v[kLaneUnroll];
 #pragma unroll
-        for (int u = 0; u < kHistUnroll; ++u)
-            v[u] = __ldcs(reinterpret_cast<const float4*>(x) + p + u * stride);
+        for (int u = 0; u < kLaneUnroll; ++u)
+        {
+            const int64_t q = p + u * stride;
+            v[u]            = q < npack ? __ldcs(reinterpret_cast<const float4*>(x) + q) : make_float4(pad, pad, pad, pad);
+        }
+        uint32_t unsure = 0;   // bit 4u+e: sample e of packet u needs the exact formula
 #pragma unroll
-        for (int u = 0; u < kHistUnroll; ++u)
+        for (int u = 0; u < kLaneUnroll; ++u)
         {
             const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
             for (int e = 0; e < 4; ++e)
             {
-                int k;
-                if (bucket_of(f[e], bs, po, k))
-                {
-                    if (k == zero_bucket)
-                        ++zero_count;
-                    else
-                        atomicAdd(&my[k], 1u);
-                }
+                bool sure;
+                lane_hist_add(base, bucket_row_fast(f[e], rbs, c, eps, sure), 1);
+                if (!sure)
+                    unsure |= 1u << (4 * u + e);
             }
         }
-    }
-    for (; p < npack; p += stride)
-    {
-        const float4 v   = __ldcs(reinterpret_cast<const float4*>(x) + p);
-        const float f[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
+        while (unsure)
         {
+            // rare (about one sample in ten thousand): take the fast-path count back out, count exactly
+            const int i = __ffs(unsure) - 1;
+            unsure &= unsure - 1;
+            const float xv = x[(p + (int64_t) (i >> 2) * stride) * 4 + (i & 3)];
+            bool dummy;
+            lane_hist_add(base, bucket_row_fast(xv, rbs, c, eps, dummy), -1);
             int k;
-            if (bucket_of(f[e], bs, po, k))
-            {
-                if (k == zero_bucket)
-                    ++zero_count;
-                else
-                    atomicAdd(&my[k], 1u);
-            }
+            if (bucket_of(xv, bs, po, k))
+                lane_hist_add(base, (uint32_t) k, 1);
         }
     }
     if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * 4))
     {
         int k;
         if (bucket_of(x[npack * 4 + threadIdx.x], bs, po, k))
-            atomicAdd(&my[k], 1u);
+            lane_hist_add(base, (uint32_t) k, 1);
     }
-    if (zero_count)
-        atomicAdd(&my[zero_bucket], zero_count);
     __syncthreads();
-    for (int b = threadIdx.x; b < AQ_PDF_SIZE; b += kHistThreads)
+    // fold the 32 lane copies of each bucket: one warp per bucket row, conflict-free reads
+    const int warp = threadIdx.x >> 5;
+    for (int b = warp; b < AQ_PDF_SIZE; b += kLaneHistThreads / 32)
     {
-        uint32_t s = 0;
-#pragma unroll
-        for (int r = 0; r < REPL; ++r)
-            s += s_hist[r * kHistPad + b];
-        if (s)
+        const uint32_t s = __reduce_add_sync(0xffffffffu, s_lane_hist[(b << 5) + lane]);
+        if (lane == 0 && s)
             atomicAdd(&hist[b], s);
     }
 }
@@ -616,14 +656,26 @@ int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t*
         note_launch();
         return check_launch();
     }
-    int64_t per_block = (int64_t) kHistThreads * 4 * kHistUnroll;
+    static bool attr_set = false;
+    if (!attr_set)
+    {
+        cudaError_t e = cudaFuncSetAttribute(tfe_hist_lane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kLaneHistBytes);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(tfe_hist_lane_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess)
+            return cuda_fail(e);
+        attr_set = true;
+    }
+    int64_t per_block = (int64_t) kLaneHistThreads * 4 * kLaneUnroll;
     int64_t blocks    = (n + per_block - 1) / per_block;
-    int64_t cap       = (int64_t) kNumSMs * 2;
+    int64_t cap       = (int64_t) kNumSMs * 2;   // two resident 1024-thread CTAs per SM (32 registers, 64 KiB each)
     if (blocks > cap)
         blocks = cap;
     if (blocks < 1)
         blocks = 1;
-    tfe_hist_kernel<8><<<(unsigned) blocks, kHistThreads, 0, stream>>>(x, n, st, hist, count);
+    tfe_hist_lane_kernel<<<(unsigned) blocks, kLaneHistThreads, kLaneHistBytes, stream>>>(x, n, st, hist, count);
     note_launch();
     return check_launch();
 }
