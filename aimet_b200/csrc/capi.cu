@@ -264,13 +264,11 @@ int aq_ste_backward_v1(const float* d_x, const float* d_grad, float* d_dx, int64
 
 int aq_v2_quantize(const void* d_x, void* d_y, uint8_t* d_mask, int dtype, int64_t n, int64_t num_ch, int64_t inner,
                    const float* d_scale, const float* d_offset, double qmin, double qmax, int out_kind,
-                   int internal_f16, void* stream)
+                   int narrow_internal, void* stream)
 {
     if (bad_geom(n, num_ch, inner) || (n > 0 && (!d_x || !d_y)) || !d_scale || !d_offset || qmin > qmax ||
         (out_kind != AQ_V2_OUT_QDQ && out_kind != AQ_V2_OUT_CODES) || dtype < AQ_F32 || dtype > AQ_BF16)
         return AQ_ERR_INVALID_ARG;
-    if (internal_f16 && dtype != AQ_F16)
-        return AQ_ERR_UNSUPPORTED;
     // the grid bounds must be exact in the internal dtype (the caller checks representability like the reference)
     if ((double) (float) qmin != qmin || (double) (float) qmax != qmax)
         return AQ_ERR_UNSUPPORTED;
@@ -278,22 +276,34 @@ int aq_v2_quantize(const void* d_x, void* d_y, uint8_t* d_mask, int dtype, int64
     a.x = d_x, a.y = d_y, a.mask = d_mask, a.n = n, a.scale = d_scale, a.offset = d_offset;
     a.qmin = (float) qmin, a.qmax = (float) qmax, a.out_kind = out_kind, a.dequant_only = 0;
     a.geom.num_ch = num_ch, a.geom.inner = inner;
-    return v2_launch(a, dtype, internal_f16, (cudaStream_t) stream);
+    return v2_launch(a, dtype, narrow_internal, (cudaStream_t) stream);
 }
 
 int aq_v2_dequantize(const void* d_x, void* d_y, int dtype, int64_t n, int64_t num_ch, int64_t inner,
-                     const float* d_scale, const float* d_offset, int internal_f16, void* stream)
+                     const float* d_scale, const float* d_offset, int narrow_internal, void* stream)
 {
     if (bad_geom(n, num_ch, inner) || (n > 0 && (!d_x || !d_y)) || !d_scale || !d_offset || dtype < AQ_F32 ||
         dtype > AQ_BF16)
         return AQ_ERR_INVALID_ARG;
-    if (internal_f16 && dtype != AQ_F16)
-        return AQ_ERR_UNSUPPORTED;
     V2Args a;
     a.x = d_x, a.y = d_y, a.mask = nullptr, a.n = n, a.scale = d_scale, a.offset = d_offset;
     a.qmin = 0, a.qmax = 0, a.out_kind = AQ_V2_OUT_QDQ, a.dequant_only = 1;
     a.geom.num_ch = num_ch, a.geom.inner = inner;
-    return v2_launch(a, dtype, internal_f16, (cudaStream_t) stream);
+    return v2_launch(a, dtype, narrow_internal, (cudaStream_t) stream);
+}
+
+int aq_v2_qdq_backward_params(const void* d_x, const void* d_grad, const uint8_t* d_mask, float* d_dscale,
+                              float* d_doffset, int dtype, int64_t n, int64_t num_ch, int64_t inner,
+                              const float* d_scale, const float* d_offset, double qmin, double qmax, void* stream)
+{
+    if (bad_geom(n, num_ch, inner) || (n > 0 && (!d_x || !d_grad || !d_mask)) || (!d_dscale && !d_doffset) ||
+        !d_scale || !d_offset || qmin > qmax || dtype < AQ_F32 || dtype > AQ_BF16)
+        return AQ_ERR_INVALID_ARG;
+    V2GradArgs a;
+    a.x = d_x, a.grad = d_grad, a.mask = d_mask, a.dscale = d_dscale, a.doffset = d_doffset, a.n = n;
+    a.scale = d_scale, a.offset = d_offset, a.qmin = (float) qmin, a.qmax = (float) qmax;
+    a.geom.num_ch = num_ch, a.geom.inner = inner;
+    return v2_param_grad(a, dtype, (cudaStream_t) stream);
 }
 
 int aq_v2_qdq_backward(const void* d_grad, const uint8_t* d_mask, void* d_dx, int dtype, int64_t n, void* stream)
@@ -311,7 +321,8 @@ int64_t aq_minmax_workspace_bytes(int64_t n, int64_t num_ch, int64_t inner)
 }
 
 int aq_minmax(const void* d_x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* d_out_min,
-              float* d_out_max, int propagate_nan, void* d_workspace, int64_t workspace_bytes, void* stream)
+              float* d_out_max, int propagate_nan, int accumulate, void* d_workspace, int64_t workspace_bytes,
+              void* stream)
 {
     if (bad_geom(n, num_ch, inner) || (n > 0 && !d_x) || !d_out_min || !d_out_max || dtype < AQ_F32 ||
         dtype > AQ_BF16)
@@ -320,7 +331,7 @@ int aq_minmax(const void* d_x, int dtype, int64_t n, int64_t num_ch, int64_t inn
         return AQ_ERR_INVALID_ARG;
     if (!d_workspace || ((uintptr_t) d_workspace % 256) != 0)
         return AQ_ERR_WORKSPACE;
-    return minmax_dispatch(d_x, dtype, n, num_ch, inner, d_out_min, d_out_max, propagate_nan, d_workspace,
+    return minmax_dispatch(d_x, dtype, n, num_ch, inner, d_out_min, d_out_max, propagate_nan, accumulate, d_workspace,
                            workspace_bytes, (cudaStream_t) stream);
 }
 

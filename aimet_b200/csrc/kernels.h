@@ -34,8 +34,22 @@ struct V2Args
     int dequant_only;
     ChanGeom geom;
 };
-int v2_launch(V2Args a, int dtype, int internal_f16, cudaStream_t st);
+int v2_launch(V2Args a, int dtype, int narrow_internal, cudaStream_t st);
 int v2_backward(const void* g, const uint8_t* mask, void* dx, int dtype, int64_t n, cudaStream_t st);
+struct V2GradArgs
+{
+    const void* x;
+    const void* grad;
+    const uint8_t* mask;
+    float* dscale;    // may be null
+    float* doffset;   // may be null
+    int64_t n;
+    const float* scale;
+    const float* offset;
+    float qmin, qmax;
+    ChanGeom geom;
+};
+int v2_param_grad(V2GradArgs a, int dtype, cudaStream_t st);
 struct SteArgs
 {
     const float* x;
@@ -49,7 +63,7 @@ struct SteArgs
 int ste_v1(SteArgs a, cudaStream_t st);
 int64_t minmax_workspace_bytes(int64_t n, int64_t num_ch, int64_t inner);
 int minmax_dispatch(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* out_min,
-                    float* out_max, int propagate_nan, void* ws, int64_t ws_bytes, cudaStream_t st);
+                    float* out_max, int propagate_nan, int accumulate, void* ws, int64_t ws_bytes, cudaStream_t st);
 int tfe_init_grid(const float* minmax, aq_tfe_state_t* st, cudaStream_t stream);
 int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t* hist, int64_t* count,
                   cudaStream_t stream);

@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __re
                                                                    float* __restrict__ out_min,
                                                                    float* __restrict__ out_max,
                                                                    unsigned int* __restrict__ ticket,
-                                                                   float2* __restrict__ partials)
+                                                                   float2* __restrict__ partials, int accumulate)
 {
     float mn = INFINITY, mx = -INFINITY;
     const int64_t npack  = n / VEC;
@@ -144,6 +144,11 @@ __global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __re
         {
             if (PROP && (mn != mn || mx != mx))
                 mn = mx = NAN;
+            if (accumulate)
+            {
+                mn = min_op<PROP>(out_min[0], mn);
+                mx = max_op<PROP>(out_max[0], mx);
+            }
             out_min[0] = mn;
             out_max[0] = mx;
             *ticket    = 0;   // ready for the next call on this stream
@@ -156,7 +161,8 @@ __global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __re
 template <typename T, int VEC, int GS, bool PROP>
 __global__ void __launch_bounds__(256) minmax_rows_kernel(const T* __restrict__ x, int64_t rows, int64_t inner,
                                                           int nseg, int64_t seg_len /* elements, multiple of VEC */,
-                                                          float* __restrict__ part_min, float* __restrict__ part_max)
+                                                          float* __restrict__ part_min, float* __restrict__ part_max,
+                                                          int accumulate /* only with direct output */)
 {
     const int lane_in_group  = threadIdx.x % GS;
     const int64_t group      = ((int64_t) blockIdx.x * 256 + threadIdx.x) / GS;
@@ -206,6 +212,11 @@ __global__ void __launch_bounds__(256) minmax_rows_kernel(const T* __restrict__ 
         {
             if (PROP && (mn != mn || mx != mx))
                 mn = mx = NAN;
+            if (accumulate)
+            {
+                mn = min_op<PROP>(part_min[it], mn);
+                mx = max_op<PROP>(part_max[it], mx);
+            }
             part_min[it] = mn;
             part_max[it] = mx;
         }
@@ -217,7 +228,7 @@ template <bool PROP>
 __global__ void __launch_bounds__(256) minmax_fold_kernel(const float* __restrict__ part_min,
                                                           const float* __restrict__ part_max, int64_t outer,
                                                           int64_t num_ch, int nseg, float* __restrict__ out_min,
-                                                          float* __restrict__ out_max)
+                                                          float* __restrict__ out_max, int accumulate)
 {
     const int64_t c = (int64_t) blockIdx.x * 256 + threadIdx.x;
     if (c >= num_ch)
@@ -232,6 +243,11 @@ __global__ void __launch_bounds__(256) minmax_fold_kernel(const float* __restric
         }
     if (PROP && (mn != mn || mx != mx))
         mn = mx = NAN;
+    if (accumulate)
+    {
+        mn = min_op<PROP>(out_min[c], mn);
+        mx = max_op<PROP>(out_max[c], mx);
+    }
     out_min[c] = mn;
     out_max[c] = mx;
 }
@@ -325,7 +341,8 @@ int64_t minmax_workspace_bytes(int64_t n, int64_t num_ch, int64_t inner)
 }
 
 template <typename T, int VEC, bool PROP>
-static void launch_rows_gs(const T* x, const RowsPlan& p, int64_t inner, float* pmin, float* pmax, cudaStream_t st)
+static void launch_rows_gs(const T* x, const RowsPlan& p, int64_t inner, float* pmin, float* pmax, int acc,
+                           cudaStream_t st)
 {
     const int64_t items     = p.rows * p.nseg;
     const int64_t per_block = 256 / p.gs;
@@ -336,7 +353,7 @@ static void launch_rows_gs(const T* x, const RowsPlan& p, int64_t inner, float* 
 #define AQ_GS(G)                                                                                                     \
     case G:                                                                                                          \
         minmax_rows_kernel<T, VEC, G, PROP>                                                                          \
-            <<<(unsigned) blocks, 256, 0, st>>>(x, p.rows, inner, p.nseg, p.seg_len, pmin, pmax);                   \
+            <<<(unsigned) blocks, 256, 0, st>>>(x, p.rows, inner, p.nseg, p.seg_len, pmin, pmax, acc);                   \
         break;
     switch (p.gs)
     {
@@ -347,15 +364,15 @@ static void launch_rows_gs(const T* x, const RowsPlan& p, int64_t inner, float* 
         AQ_GS(16)
     default:
         minmax_rows_kernel<T, VEC, 32, PROP>
-            <<<(unsigned) blocks, 256, 0, st>>>(x, p.rows, inner, p.nseg, p.seg_len, pmin, pmax);
+            <<<(unsigned) blocks, 256, 0, st>>>(x, p.rows, inner, p.nseg, p.seg_len, pmin, pmax, acc);
     }
 #undef AQ_GS
     note_launch();
 }
 
 template <typename T, bool PROP>
-static int minmax_t(const T* x, int64_t n, int64_t num_ch, int64_t inner, float* out_min, float* out_max, void* ws,
-                    int64_t ws_bytes, cudaStream_t st)
+static int minmax_t(const T* x, int64_t n, int64_t num_ch, int64_t inner, float* out_min, float* out_max,
+                    int accumulate, void* ws, int64_t ws_bytes, cudaStream_t st)
 {
     if (num_ch <= 1)
     {
@@ -369,16 +386,16 @@ static int minmax_t(const T* x, int64_t n, int64_t num_ch, int64_t inner, float*
         {
         case 8:
             minmax_tensor_kernel<T, (sizeof(T) == 2 ? 8 : 4), PROP>
-                <<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials);
+                <<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials, accumulate);
             break;
         case 4:
-            minmax_tensor_kernel<T, 4, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials);
+            minmax_tensor_kernel<T, 4, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials, accumulate);
             break;
         case 2:
-            minmax_tensor_kernel<T, 2, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials);
+            minmax_tensor_kernel<T, 2, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials, accumulate);
             break;
         default:
-            minmax_tensor_kernel<T, 1, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials);
+            minmax_tensor_kernel<T, 1, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials, accumulate);
         }
         note_launch();
         return check_launch();
@@ -397,27 +414,28 @@ static int minmax_t(const T* x, int64_t n, int64_t num_ch, int64_t inner, float*
     }
     switch (vec)
     {
-    case 8: launch_rows_gs<T, (sizeof(T) == 2 ? 8 : 4), PROP>(x, p, inner, pmin, pmax, st); break;
-    case 4: launch_rows_gs<T, 4, PROP>(x, p, inner, pmin, pmax, st); break;
-    case 2: launch_rows_gs<T, 2, PROP>(x, p, inner, pmin, pmax, st); break;
-    default: launch_rows_gs<T, 1, PROP>(x, p, inner, pmin, pmax, st);
+    case 8: launch_rows_gs<T, (sizeof(T) == 2 ? 8 : 4), PROP>(x, p, inner, pmin, pmax, p.direct ? accumulate : 0, st); break;
+    case 4: launch_rows_gs<T, 4, PROP>(x, p, inner, pmin, pmax, p.direct ? accumulate : 0, st); break;
+    case 2: launch_rows_gs<T, 2, PROP>(x, p, inner, pmin, pmax, p.direct ? accumulate : 0, st); break;
+    default: launch_rows_gs<T, 1, PROP>(x, p, inner, pmin, pmax, p.direct ? accumulate : 0, st);
     }
     int rc = check_launch();
     if (rc != AQ_OK || p.direct)
         return rc;
     minmax_fold_kernel<PROP><<<(unsigned) ((num_ch + 255) / 256), 256, 0, st>>>(pmin, pmax, p.outer, num_ch, p.nseg,
-                                                                                out_min, out_max);
+                                                                                out_min, out_max, accumulate);
     note_launch();
     return check_launch();
 }
 
 int minmax_dispatch(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* out_min,
-                    float* out_max, int propagate_nan, void* ws, int64_t ws_bytes, cudaStream_t st)
+                    float* out_max, int propagate_nan, int accumulate, void* ws, int64_t ws_bytes, cudaStream_t st)
 {
     (void) dtype_vec;
 #define AQ_T(T)                                                                                                      \
-    (propagate_nan ? minmax_t<T, true>((const T*) x, n, num_ch, inner, out_min, out_max, ws, ws_bytes, st)          \
-                   : minmax_t<T, false>((const T*) x, n, num_ch, inner, out_min, out_max, ws, ws_bytes, st))
+    (propagate_nan                                                                                                   \
+         ? minmax_t<T, true>((const T*) x, n, num_ch, inner, out_min, out_max, accumulate, ws, ws_bytes, st)         \
+         : minmax_t<T, false>((const T*) x, n, num_ch, inner, out_min, out_max, accumulate, ws, ws_bytes, st))
     switch (dtype)
     {
     case AQ_F32: return AQ_T(float);

@@ -39,17 +39,22 @@ def _same_device(a: torch.Tensor, *others: torch.Tensor):
             raise RuntimeError(f"aimet_b200: tensors on different devices ({a.device} vs {o.device})")
 
 
-class _DeviceGuard:
-    """Makes the tensor's device current for the duration of a call (kernels launch on the current device)."""
-
-    def __init__(self, t: torch.Tensor):
-        self.g = torch.cuda.device(t.device)
-
+class _NoGuard:
     def __enter__(self):
-        self.g.__enter__()
+        return self
 
     def __exit__(self, *a):
-        self.g.__exit__(*a)
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _on(t: torch.Tensor):
+    """Context that makes t's device current (kernels launch on the current device); free when it already is."""
+    if t.device.index is None or t.device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(t.device)
 
 
 _WS: Dict[Tuple[int, int], torch.Tensor] = {}
@@ -98,9 +103,10 @@ def _f32c(t: torch.Tensor, name: str) -> torch.Tensor:
 
 def qdq_per_tensor(x: torch.Tensor, enc_min: float, enc_max: float, bw: int, rounding_mode: int = 0,
                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    x = _f32c(x, "input").contiguous()
+    """``x`` must be dense in memory (any memory format); the output has the same layout."""
+    x = _f32c(x, "input")
     out = torch.empty_like(x) if out is None else out
-    with _DeviceGuard(x):
+    with _on(x):
         check(lib.aq_qdq_per_tensor(x.data_ptr(), out.data_ptr(), x.numel(), float(enc_min), float(enc_max), int(bw),
                                     int(rounding_mode), _stream(x)), "aq_qdq_per_tensor")
     return out
@@ -108,9 +114,9 @@ def qdq_per_tensor(x: torch.Tensor, enc_min: float, enc_max: float, bw: int, rou
 
 def quantize_per_tensor(x: torch.Tensor, enc_min: float, enc_max: float, bw: int, shift_to_signed: bool = False,
                         rounding_mode: int = 0) -> torch.Tensor:
-    x = _f32c(x, "input").contiguous()
+    x = _f32c(x, "input")
     out = torch.empty_like(x)
-    with _DeviceGuard(x):
+    with _on(x):
         check(lib.aq_quantize_per_tensor(x.data_ptr(), out.data_ptr(), x.numel(), float(enc_min), float(enc_max),
                                          int(bw), int(rounding_mode), int(shift_to_signed), _stream(x)),
               "aq_quantize_per_tensor")
@@ -126,7 +132,7 @@ def qdq_per_channel(x: torch.Tensor, enc_min: torch.Tensor, enc_max: torch.Tenso
     if enc_min.numel() != num_ch or enc_max.numel() != num_ch:
         raise RuntimeError("aimet_b200: need one min and one max per channel")
     out = torch.empty_like(x)
-    with _DeviceGuard(x):
+    with _on(x):
         check(lib.aq_qdq_per_channel(x.data_ptr(), out.data_ptr(), x.numel(), int(num_ch), int(inner),
                                      enc_min.data_ptr(), enc_max.data_ptr(), float(num_steps), int(rounding_mode),
                                      _stream(x)), "aq_qdq_per_channel")
@@ -141,7 +147,7 @@ def qdq_broadcast(x: torch.Tensor, in_strides, enc_strides, enc_min, enc_max, en
     ins = (C.c_int64 * nd)(*[int(s) for s in in_strides])
     ens = (C.c_int64 * nd)(*[int(s) for s in enc_strides])
     out = torch.empty_like(x)
-    with _DeviceGuard(x):
+    with _on(x):
         check(lib.aq_qdq_broadcast(x.data_ptr(), out.data_ptr(), x.numel(), nd, ins, ens,
                                    *[e.data_ptr() for e in encs], _stream(x)), "aq_qdq_broadcast")
     return out
@@ -157,7 +163,7 @@ def ste_backward_v1(x: torch.Tensor, grad: torch.Tensor, enc_min: torch.Tensor, 
     if inner is None:
         inner = max(x.numel(), 1)
     dx = torch.empty_like(grad)
-    with _DeviceGuard(x):
+    with _on(x):
         check(lib.aq_ste_backward_v1(x.data_ptr(), grad.data_ptr(), dx.data_ptr(), x.numel(), int(num_ch),
                                      int(inner), enc_min.data_ptr(), enc_max.data_ptr(), _stream(x)),
               "aq_ste_backward_v1")
@@ -169,24 +175,35 @@ def ste_backward_v1(x: torch.Tensor, grad: torch.Tensor, enc_min: torch.Tensor, 
 # ---------------------------------------------------------------------------------------------------
 def v2_quantize(x: torch.Tensor, y: torch.Tensor, mask: Optional[torch.Tensor], scale: torch.Tensor,
                 offset: torch.Tensor, qmin: int, qmax: int, num_ch: int, inner: int, out_kind: int,
-                internal_f16: bool = False) -> None:
-    with _DeviceGuard(x):
+                narrow_internal: bool = False) -> None:
+    with _on(x):
         check(lib.aq_v2_quantize(x.data_ptr(), y.data_ptr(), mask.data_ptr() if mask is not None else None, _dt(x),
                                  x.numel(), int(num_ch), int(inner), scale.data_ptr(), offset.data_ptr(),
-                                 float(qmin), float(qmax), int(out_kind), int(internal_f16), _stream(x)),
+                                 float(qmin), float(qmax), int(out_kind), int(narrow_internal), _stream(x)),
               "aq_v2_quantize")
 
 
 def v2_dequantize(x: torch.Tensor, y: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor, num_ch: int,
-                  inner: int, internal_f16: bool = False) -> None:
-    with _DeviceGuard(x):
+                  inner: int, narrow_internal: bool = False) -> None:
+    with _on(x):
         check(lib.aq_v2_dequantize(x.data_ptr(), y.data_ptr(), _dt(x), x.numel(), int(num_ch), int(inner),
-                                   scale.data_ptr(), offset.data_ptr(), int(internal_f16), _stream(x)),
+                                   scale.data_ptr(), offset.data_ptr(), int(narrow_internal), _stream(x)),
               "aq_v2_dequantize")
 
 
+def v2_qdq_backward_params(x: torch.Tensor, grad: torch.Tensor, mask: torch.Tensor, dscale: Optional[torch.Tensor],
+                           doffset: Optional[torch.Tensor], scale: torch.Tensor, offset: torch.Tensor, qmin: int,
+                           qmax: int, num_ch: int, inner: int) -> None:
+    with _on(x):
+        check(lib.aq_v2_qdq_backward_params(x.data_ptr(), grad.data_ptr(), mask.data_ptr(),
+                                            dscale.data_ptr() if dscale is not None else None,
+                                            doffset.data_ptr() if doffset is not None else None, _dt(x), x.numel(),
+                                            int(num_ch), int(inner), scale.data_ptr(), offset.data_ptr(),
+                                            float(qmin), float(qmax), _stream(x)), "aq_v2_qdq_backward_params")
+
+
 def v2_qdq_backward(grad: torch.Tensor, mask: torch.Tensor, dx: torch.Tensor) -> None:
-    with _DeviceGuard(grad):
+    with _on(grad):
         check(lib.aq_v2_qdq_backward(grad.data_ptr(), mask.data_ptr(), dx.data_ptr(), _dt(grad), grad.numel(),
                                      _stream(grad)), "aq_v2_qdq_backward")
 
@@ -195,10 +212,11 @@ def v2_qdq_backward(grad: torch.Tensor, mask: torch.Tensor, dx: torch.Tensor) ->
 # statistics
 # ---------------------------------------------------------------------------------------------------
 def minmax(x: torch.Tensor, num_ch: int = 1, inner: Optional[int] = None, propagate_nan: bool = False,
-           out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Fused min/max.  Returns a float32 tensor [2, num_ch] (row 0 = min, row 1 = max) on x's device."""
+           out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """Fused min/max.  Returns a float32 tensor [2, num_ch] (row 0 = min, row 1 = max) on x's device.
+    ``x`` must be dense in memory.  With ``accumulate`` the result is folded into the values already held by
+    ``out`` (running statistics)."""
     _cuda(x, "input")
-    x = x.contiguous()
     n = x.numel()
     if inner is None:
         inner = max(n, 1)
@@ -208,10 +226,15 @@ def minmax(x: torch.Tensor, num_ch: int = 1, inner: Optional[int] = None, propag
     if need < 0:
         check(need, "aq_minmax_workspace_bytes")
     ws = workspace(x, need)
-    with _DeviceGuard(x):
-        check(lib.aq_minmax(x.data_ptr(), _dt(x), n, int(num_ch), int(inner), out[0].data_ptr(), out[1].data_ptr(),
-                            int(propagate_nan), ws.data_ptr(), ws.numel(), _stream(x)), "aq_minmax")
+    p = out.data_ptr()
+    with _on(x):
+        check(lib.aq_minmax(x.data_ptr(), _dt(x), n, int(num_ch), int(inner), p, p + 4 * num_ch,
+                            int(propagate_nan), int(accumulate), ws.data_ptr(), ws.numel(), _stream(x)), "aq_minmax")
     return out
+
+
+_INIT_OFF = _lib.AqTfeState.initialized.offset
+_HIST_ROW_BYTES = _lib.AQ_PDF_SIZE * 4
 
 
 class TfeDeviceState:
@@ -222,70 +245,69 @@ class TfeDeviceState:
     the replay, exactly as the reference drops it.
     """
 
-    def __init__(self, device: torch.device, capacity: int = 64):
+    def __init__(self, device, capacity: int = 64):
         self.device = torch.device(device)
         self.state = torch.zeros(_lib.TFE_STATE_BYTES, dtype=torch.uint8, device=self.device)
-        self.hists = torch.zeros((capacity, _lib.AQ_PDF_SIZE), dtype=torch.int32, device=self.device)
-        self.counts = torch.zeros(capacity, dtype=torch.int64, device=self.device)
-        self.num_batches = 0
-        self.initialized_on_host = False
         self.pdf = torch.zeros(_lib.AQ_PDF_SIZE, dtype=torch.float64, device=self.device)
         self.iterations = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.encoding = torch.zeros(5, dtype=torch.float64, device=self.device)
+        self.num_batches = 0
+        self.initialized_on_host = False
+        self._alloc_rows(capacity)
 
-    def _grow(self, need: int):
-        cap = self.hists.shape[0]
-        if need <= cap:
-            return
-        new_cap = max(need, cap * 2)
-        h = torch.zeros((new_cap, _lib.AQ_PDF_SIZE), dtype=torch.int32, device=self.device)
-        c = torch.zeros(new_cap, dtype=torch.int64, device=self.device)
-        h[:cap].copy_(self.hists)
-        c[:cap].copy_(self.counts)
+    def _alloc_rows(self, capacity: int, keep: bool = False):
+        h = torch.zeros((capacity, _lib.AQ_PDF_SIZE), dtype=torch.int32, device=self.device)
+        c = torch.zeros(capacity, dtype=torch.int64, device=self.device)
+        if keep:
+            old = self.hists.shape[0]
+            h[:old].copy_(self.hists)
+            c[:old].copy_(self.counts)
         self.hists, self.counts = h, c
+        self._hp, self._cp, self._sp = h.data_ptr(), c.data_ptr(), self.state.data_ptr()
 
     def reserve(self, capacity: int):
-        self._grow(capacity)
+        if capacity > self.hists.shape[0]:
+            self._alloc_rows(max(capacity, 2 * self.hists.shape[0]), keep=True)
 
     def init_grid_from(self, minmax_dev: torch.Tensor):
         """minmax_dev: float32 tensor holding {min, max} on the device."""
-        with _DeviceGuard(self.state):
-            check(lib.aq_tfe_init_grid(minmax_dev.data_ptr(), self.state.data_ptr(), _stream(self.state)),
-                  "aq_tfe_init_grid")
+        with _on(self.state):
+            check(lib.aq_tfe_init_grid(minmax_dev.data_ptr(), self._sp, _stream(self.state)), "aq_tfe_init_grid")
 
     def is_initialized(self) -> bool:
-        """Host view of the device flag (synchronises once; cached after it turns true)."""
+        """Host view of the device flag (synchronises once per call until it turns true, then cached)."""
         if not self.initialized_on_host:
-            flag = self.state[_lib.AqTfeState.initialized.offset:_lib.AqTfeState.initialized.offset + 4]
-            self.initialized_on_host = bool(flag.view(torch.int32).item())
+            self.initialized_on_host = bool(self.state[_INIT_OFF:_INIT_OFF + 4].view(torch.int32).item())
         return self.initialized_on_host
 
     def add_batch(self, x: torch.Tensor, row: Optional[int] = None):
-        """Histogram of one batch into row ``row`` (default: the next one)."""
-        if x.dtype != torch.float32:
-            raise RuntimeError("aimet_b200: TF-Enhanced statistics take float32 input (callers upcast)")
-        x = _cuda(x, "input").contiguous()
+        """Histogram of one batch into row ``row`` (default: the next one).  ``x``: dense float32 CUDA tensor."""
+        if x.dtype != torch.float32 or not x.is_cuda:
+            raise RuntimeError("aimet_b200: TF-Enhanced statistics take float32 CUDA input (callers upcast)")
         if row is None:
             row = self.num_batches
-        self._grow(row + 1)
-        self.num_batches = max(self.num_batches, row + 1)
-        with _DeviceGuard(x):
-            check(lib.aq_tfe_histogram(x.data_ptr(), x.numel(), self.state.data_ptr(), self.hists[row].data_ptr(),
-                                       self.counts[row:].data_ptr(), _stream(x)), "aq_tfe_histogram")
+        if row >= self.hists.shape[0]:
+            self.reserve(row + 1)
+        if row >= self.num_batches:
+            self.num_batches = row + 1
+        with _on(x):
+            check(lib.aq_tfe_histogram(x.data_ptr(), x.numel(), self._sp, self._hp + row * _HIST_ROW_BYTES,
+                                       self._cp + row * 8, torch.cuda.current_stream().cuda_stream),
+                  "aq_tfe_histogram")
 
     def replay(self, num_batches: Optional[int] = None):
         nb = self.num_batches if num_batches is None else num_batches
-        with _DeviceGuard(self.state):
-            check(lib.aq_tfe_pdf_replay(self.hists.data_ptr(), self.counts.data_ptr(), nb, self.pdf.data_ptr(),
-                                        self.iterations.data_ptr(), _stream(self.state)), "aq_tfe_pdf_replay")
+        with _on(self.state):
+            check(lib.aq_tfe_pdf_replay(self._hp, self._cp, nb, self.pdf.data_ptr(), self.iterations.data_ptr(),
+                                        _stream(self.state)), "aq_tfe_pdf_replay")
 
     def search(self, stats_updated: bool, bw: int, symmetric: bool, strict: bool, unsigned_sym: bool) -> torch.Tensor:
         need = int(lib.aq_tfe_search_workspace_bytes())
         ws = workspace(self.state, need)
-        with _DeviceGuard(self.state):
-            check(lib.aq_tfe_search(self.state.data_ptr(), self.pdf.data_ptr(), int(stats_updated), int(bw),
-                                    int(symmetric), int(strict), int(unsigned_sym), self.encoding.data_ptr(),
-                                    ws.data_ptr(), ws.numel(), _stream(self.state)), "aq_tfe_search")
+        with _on(self.state):
+            check(lib.aq_tfe_search(self._sp, self.pdf.data_ptr(), int(stats_updated), int(bw), int(symmetric),
+                                    int(strict), int(unsigned_sym), self.encoding.data_ptr(), ws.data_ptr(),
+                                    ws.numel(), _stream(self.state)), "aq_tfe_search")
         return self.encoding
 
     def x_left(self) -> torch.Tensor:

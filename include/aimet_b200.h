@@ -160,15 +160,24 @@ int aq_ste_backward_v1(const float* d_x, const float* d_grad, float* d_dx, int64
  * (TrainingExtensions/torch/src/python/aimet_torch/v2/quantization/affine/backends/torch_builtins.py:290-327,208-236).
  * d_scale / d_offset: num_ch fp32 values on the device (already cast to the internal dtype by the caller).
  * d_mask (may be NULL): one byte per element, 1 where qmin <= round(x/s) - o <= qmax.
- * internal_f16 != 0 rounds every intermediate to fp16 (the reference keeps fp16 as its internal dtype when the
- * grid is narrow enough; only valid with dtype == AQ_F16). */
+ * narrow_internal != 0 rounds every intermediate to the storage dtype: the reference computes in the tensor's
+ * own dtype for quantize()/dequantize() and, for quantize_dequantize(), whenever that dtype is precise enough
+ * for the grid (torch_builtins.py:60-87,162-171); otherwise intermediates stay fp32. */
 int aq_v2_quantize(const void* d_x, void* d_y, uint8_t* d_mask, int dtype, int64_t n, int64_t num_ch, int64_t inner,
                    const float* d_scale, const float* d_offset, double qmin, double qmax, int out_kind,
-                   int internal_f16, void* stream);
+                   int narrow_internal, void* stream);
 
 /* Replaces DequantizeFunc.forward (torch_builtins.py:251-276): y = (x + o) * s. */
 int aq_v2_dequantize(const void* d_x, void* d_y, int dtype, int64_t n, int64_t num_ch, int64_t inner,
-                     const float* d_scale, const float* d_offset, int internal_f16, void* stream);
+                     const float* d_scale, const float* d_offset, int narrow_internal, void* stream);
+
+/* Replaces the scale / offset gradients of QuantDequantFunc.backward (torch_builtins.py:334-343), element-wise and
+ * un-reduced like the reference (the caller's autograd sums over the broadcast dimensions):
+ *   dscale = g * (clamp(round(x/s), o+qmin, o+qmax) - (x/s)*mask),  doffset = g * ((1-mask) * s).
+ * d_dscale / d_doffset: n floats each; either may be NULL. */
+int aq_v2_qdq_backward_params(const void* d_x, const void* d_grad, const uint8_t* d_mask, float* d_dscale,
+                              float* d_doffset, int dtype, int64_t n, int64_t num_ch, int64_t inner,
+                              const float* d_scale, const float* d_offset, double qmin, double qmax, void* stream);
 
 /* Replaces the tensor-gradient of QuantDequantFunc.backward (torch_builtins.py:329-344): dx = grad * mask. */
 int aq_v2_qdq_backward(const void* d_grad, const uint8_t* d_mask, void* d_dx, int dtype, int64_t n, void* stream);
@@ -187,9 +196,14 @@ int64_t aq_minmax_workspace_bytes(int64_t n, int64_t num_ch, int64_t inner);
  * d_out_min / d_out_max: num_ch floats each (values of 16-bit inputs are exact in fp32).
  * propagate_nan = 0: NaNs are ignored (std::min/std::max folds of the reference C++);
  * propagate_nan = 1: any NaN in a channel makes both outputs NaN (torch.min / torch.max).
- * An empty channel yields +inf / -inf.  d_workspace must be 256-byte aligned. */
+ * accumulate != 0 folds the result into the values already in d_out_min / d_out_max (running statistics over
+ * batches: the accumulation of TfEncodingAnalyzer::updateStats, src/TfEncodingAnalyzer.cpp:59-71, and of
+ * _MinMaxObserver.merge_stats, encoding_analyzer.py:106-122) instead of overwriting them.
+ * An empty channel yields +inf / -inf.  d_workspace must be 256-byte aligned and zero-filled before its first
+ * use; the library leaves it reusable. */
 int aq_minmax(const void* d_x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* d_out_min,
-              float* d_out_max, int propagate_nan, void* d_workspace, int64_t workspace_bytes, void* stream);
+              float* d_out_max, int propagate_nan, int accumulate, void* d_workspace, int64_t workspace_bytes,
+              void* stream);
 
 /* Builds the bucket grid from a batch's (min,max) held on the device; leaves the state un-initialised when both
  * are zero.  Replaces the first-batch branch of UpdatePdf and InitializePdf<float>

@@ -1,0 +1,199 @@
+"""Generates the golden fixtures in this directory from the REFERENCE ITSELF (run where a reference checkout and
+oracle/_ref exist; the fixtures are committed so that the tests need neither).
+
+    python tests/golden/gen_golden.py [/path/to/aimet]
+
+* v2_backend.npz   - aimet_torch v2 ``torch_builtins`` (loaded by file path, CPU) on seeded inputs:
+                     quantize / quantize_dequantize / dequantize outputs, clamp masks (from dx with unit grads),
+                     and un-reduced-then-summed scale / offset gradients.
+* v2_minmax.npz    - aimet_torch v2 ``MinMaxEncodingAnalyzer`` encodings (CPU).
+* libpymo.npz      - the reference DlQuantization CPU code (oracle/_ref): per-tensor QDQ / codes, TF and
+                     TF-Enhanced encodings, per-batch histograms, on seeded inputs.
+"""
+import importlib.util
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def load_reference_v2(ref_root: str):
+    """Loads the three hot-path files of aimet_torch.v2 by path.  The package itself cannot be imported here
+    (it pulls in bokeh, onnx, spconv ...), so empty parent packages and an identity stub for the ONNX symbolic
+    decorator are registered first."""
+    at = os.path.join(ref_root, "TrainingExtensions", "torch", "src", "python", "aimet_torch")
+    for name in ("aimet_torch", "aimet_torch.v2", "aimet_torch.v2.quantization", "aimet_torch.v2.quantization.affine",
+                 "aimet_torch.v2.quantization.affine.backends", "aimet_torch.v2.experimental",
+                 "aimet_torch.v2.experimental.onnx"):
+        if name not in sys.modules:
+            m = types.ModuleType(name)
+            m.__path__ = []
+            sys.modules[name] = m
+    exp = types.ModuleType("aimet_torch.v2.experimental.onnx._export")
+    exp.register_symbolic = lambda sym: (lambda fn: fn)
+    for n in ("quantize_symbolic", "dequantize_symbolic", "quantize_dequantize_symbolic"):
+        setattr(exp, n, None)
+    sys.modules[exp.__name__] = exp
+    sys.modules["aimet_torch.v2.experimental.onnx"]._export = exp
+
+    def load(modname, relpath):
+        spec = importlib.util.spec_from_file_location(modname, os.path.join(at, relpath))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[modname] = mod
+        spec.loader.exec_module(mod)
+        return mod
+
+    utils = load("aimet_torch.v2.utils", "v2/utils.py")
+    tb = load("aimet_torch.v2.quantization.affine.backends.torch_builtins",
+              "v2/quantization/affine/backends/torch_builtins.py")
+    ea = load("aimet_torch.v2.quantization.encoding_analyzer", "v2/quantization/encoding_analyzer.py")
+    return utils, tb, ea
+
+
+def v2_cases():
+    """(name, tensor, scale, offset, qmin, qmax, block_size) -- small, seeded, with ties and out-of-range values."""
+    g = torch.Generator().manual_seed(1234)
+    cases = []
+
+    def rnd(*shape, s=1.0):
+        return torch.randn(*shape, generator=g) * s
+
+    ties = torch.tensor([0.25, 0.75, 1.25, -0.25, -0.75, 63.75, -64.25, 1000.0, -1000.0, 0.0])
+    for dt in (torch.float32, torch.float16, torch.bfloat16):
+        for bw, signed in ((8, False), (8, True), (4, True), (16, False)):
+            steps = 2 ** bw - 1
+            qmin, qmax = (-(steps + 1) // 2, steps // 2) if signed else (0, steps)
+            x = torch.cat([rnd(300, s=3.0), ties]).to(dt)
+            scale = torch.tensor(0.5 if bw < 16 else 0.001)
+            offset = torch.tensor(0.0 if signed else float(-(steps // 2)))
+            cases.append((f"pt_{str(dt)[6:]}_b{bw}{'s' if signed else 'u'}", x, scale, offset, qmin, qmax, None))
+    # per-channel (axis 0) conv-like weight and per-channel on axis 1 of an activation
+    w = rnd(6, 4, 3, 3, s=0.2)
+    sc = (w.abs().amax(dim=(1, 2, 3), keepdim=True) / 127)
+    cases.append(("pc_w_f32", w, sc, torch.zeros_like(sc), -128, 127, None))
+    a = rnd(3, 5, 4, 2, s=2.0)
+    sc = torch.linspace(0.01, 0.05, 5).view(1, 5, 1, 1)
+    of = torch.tensor([-128., -100., -90., -128., -5.]).view(1, 5, 1, 1)
+    cases.append(("pc_act_axis1_f32", a, sc, of, 0, 255, None))
+    cases.append(("pc_act_axis1_cl_f32", a.contiguous(memory_format=torch.channels_last), sc, of, 0, 255, None))
+    # blockwise [O, I] with block 8 on the input dim, W4 symmetric, bf16 (the LLM weight case, scaled down)
+    wb = (rnd(12, 32, s=0.02)).to(torch.bfloat16)
+    sb = (wb.float().view(12, 4, 8).abs().amax(dim=2) / 7).clamp_min(1e-6)
+    cases.append(("blk_bf16_w4", wb, sb, torch.zeros_like(sb), -8, 7, (-1, 8)))
+    cases.append(("blk_f32_w4", wb.float(), sb, torch.zeros_like(sb), -8, 7, (1, 8)))
+    # conv weight blocked on input channels: [O, I, kh, kw], block (1, 4, -1, -1)
+    wc = rnd(4, 8, 3, 3, s=0.1)
+    sc4 = (wc.view(4, 2, 4, 3, 3).abs().amax(dim=(2, 3, 4)) / 7).view(4, 2, 1, 1)
+    cases.append(("blk_conv_f32", wc, sc4, torch.zeros_like(sc4), -8, 7, (1, 4, -1, -1)))
+    # encodings interleaved with broadcast dims: scale [4,1,3]
+    t3 = rnd(4, 5, 3)
+    s3 = torch.linspace(0.02, 0.2, 12).view(4, 1, 3)
+    cases.append(("interleaved_f32", t3, s3, torch.full_like(s3, -100.0), 0, 255, None))
+    return cases
+
+
+def gen_v2(ref_root: str):
+    _, tb, ea = load_reference_v2(ref_root)
+    out = {}
+    for name, x, scale, offset, qmin, qmax, bs in v2_cases():
+        out[f"{name}/x"] = x.float().numpy()
+        out[f"{name}/dtype"] = np.array(str(x.dtype))
+        out[f"{name}/scale"] = scale.numpy()
+        out[f"{name}/offset"] = offset.numpy()
+        out[f"{name}/q"] = np.array([qmin, qmax])
+        out[f"{name}/block"] = np.array(bs if bs is not None else [], dtype=np.int64)
+        out[f"{name}/channels_last"] = np.array(x.dim() == 4 and not x.is_contiguous())
+        xr = x.clone().requires_grad_(True)
+        sr = scale.clone().requires_grad_(True)
+        orr = offset.clone().requires_grad_(True)
+        y = tb.quantize_dequantize(xr, sr, orr, qmin, qmax, bs)
+        gy = torch.randn(y.shape, generator=torch.Generator().manual_seed(7)).to(y.dtype)
+        y.backward(gy)
+        out[f"{name}/qdq"] = y.detach().float().numpy()
+        out[f"{name}/gy"] = gy.float().numpy()
+        out[f"{name}/dx"] = xr.grad.float().numpy()
+        out[f"{name}/dscale"] = sr.grad.float().numpy()
+        out[f"{name}/doffset"] = orr.grad.float().numpy()
+        ones = torch.ones_like(x)
+        xm = x.clone().requires_grad_(True)
+        tb.quantize_dequantize(xm, scale, offset, qmin, qmax, bs).backward(ones)
+        out[f"{name}/mask"] = (xm.grad.float().numpy() != 0)
+        if tb._is_grid_representable(x.dtype, qmin, qmax):
+            q = tb.quantize(x, scale, offset, qmin, qmax, bs)
+            out[f"{name}/codes"] = q.float().numpy()
+            out[f"{name}/deq"] = tb.dequantize(q, scale, offset, bs).float().numpy()
+    np.savez_compressed(os.path.join(HERE, "v2_backend.npz"), **out)
+
+    mm = {}
+    k = 0
+    for dt in (torch.float32, torch.bfloat16):
+        for shape, enc_shape in (((64, 33), (1,)), ((8, 4, 3, 3), (8, 1, 1, 1)), ((6, 16), (6, 2))):
+            for steps, sym in ((255, False), (255, True), (15, True), (65535, False)):
+                g = torch.Generator().manual_seed(100 + k)
+                x = (torch.randn(*shape, generator=g) * 2 + (0.5 if not sym else 0)).to(dt)
+                if enc_shape == (6, 2):
+                    an = ea.MinMaxEncodingAnalyzer((6, 2, 1))
+                    xin = x.view(6, 2, 8)
+                else:
+                    an = ea.MinMaxEncodingAnalyzer(enc_shape)
+                    xin = x
+                an.update_stats(xin)
+                an.update_stats(xin * 0.5 + 0.1)
+                mn, mx = an.compute_encodings(steps, sym)
+                mm[f"c{k}/x"] = x.float().numpy()
+                mm[f"c{k}/meta"] = np.array([str(dt), str(list(enc_shape)), str(steps), str(int(sym))])
+                mm[f"c{k}/min"] = mn.float().numpy()
+                mm[f"c{k}/max"] = mx.float().numpy()
+                k += 1
+    np.savez_compressed(os.path.join(HERE, "v2_minmax.npz"), **mm)
+
+
+def gen_libpymo():
+    from _data import SPECIALS, conv_weight, normal, relu_activations
+    from oracle import Reference, RefAnalyzer
+    r = Reference()
+    out = {}
+    x = np.concatenate([normal(2000, seed=0, scale=2.0), SPECIALS])
+    out["qdq/x"] = x
+    for i, (mn, mx, bw) in enumerate([(-0.46, 0.72, 8), (-3.1, 4.2, 8), (-2.0, 2.0, 8), (0.0, 5.0, 4), (-7.0, 3.0, 16)]):
+        out[f"qdq/{i}/enc"] = np.array([mn, mx, bw])
+        out[f"qdq/{i}/y"] = r.qdq_per_tensor(x, mn, mx, bw)
+        out[f"qdq/{i}/codes"] = r.quantize_per_tensor(x, mn, mx, bw, False)
+        out[f"qdq/{i}/codes_signed"] = r.quantize_per_tensor(x, mn, mx, bw, True)
+    # calibration scenarios: (kind, n) batches
+    scen = {"relu": [relu_activations(6000, 1000 + b) for b in range(4)],
+            "normal": [normal(6000, 50 + b, 2.0, 1.0) for b in range(3)],
+            "zeros_then_relu": [np.zeros(3000, np.float32), relu_activations(3000, 7), relu_activations(3000, 8)],
+            "negative": [normal(6000, 60 + b, 1.0, -2.0) for b in range(2)]}
+    for name, batches in scen.items():
+        tfe, tf = RefAnalyzer(r, "tfe"), RefAnalyzer(r, "tf")
+        for b, xb in enumerate(batches):
+            out[f"cal/{name}/batch{b}"] = xb
+            tfe.update(xb)
+            tf.update(xb)
+        xl, pdf = tfe.histogram()
+        out[f"cal/{name}/x_left"] = xl
+        out[f"cal/{name}/pdf"] = pdf
+        for b, xb in enumerate(batches):
+            if xl is not None:
+                out[f"cal/{name}/hist{b}"] = r.batch_hist(xb, xl)
+        for bw in (8, 4):
+            for sym, strict, uns in ((0, 0, 0), (1, 0, 0), (1, 1, 0), (1, 0, 1)):
+                out[f"cal/{name}/tfe_b{bw}_{sym}{strict}{uns}"] = tfe.compute(bw, sym, strict, uns)
+                out[f"cal/{name}/tf_b{bw}_{sym}{strict}{uns}"] = tf.compute(bw, sym, strict, uns)
+    np.savez_compressed(os.path.join(HERE, "libpymo.npz"), **out)
+
+
+if __name__ == "__main__":
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    gen_v2(ref)
+    gen_libpymo()
+    for f in ("v2_backend.npz", "v2_minmax.npz", "libpymo.npz"):
+        print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
