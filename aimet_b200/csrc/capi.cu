@@ -2,6 +2,7 @@
 // the kernels.  No torch types, no allocation, no implicit synchronisation.
 #include <float.h>
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -14,6 +15,12 @@ namespace aq
 // ---- launch accounting / error text ----------------------------------------------------------------
 static std::atomic<int64_t> g_launches {0};
 static thread_local char g_cuda_error[256] = "";
+
+bool pdl_enabled()
+{
+    static const bool on = getenv("AQ_NO_PDL") == nullptr;
+    return on;
+}
 
 void note_launch()
 {

@@ -18,6 +18,41 @@ void note_launch();
 int check_launch();                 // cudaGetLastError -> AQ_OK / AQ_ERR_CUDA
 int cuda_fail(cudaError_t e);       // records the text, returns AQ_ERR_CUDA
 
+// ---- programmatic dependent launch -------------------------------------------------------------------------
+// Back-to-back launches of these short kernels (8-12 us of DRAM time each) lose 2-3 us per launch to the gap between
+// the end of one grid and the start of the next.  Kernels launched through launch_pdl() may be scheduled while the
+// previous grid of the stream is still draining: every kernel first tells the scheduler that its dependents may
+// launch (pdl_launch_dependents), does whatever needs no global input (shared-memory setup), and only then waits
+// for the previous grid to complete and flush (pdl_wait) -- so data dependencies through global memory are kept.
+// Both instructions are no-ops in a grid that was launched normally.
+__device__ __forceinline__ void pdl_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;");
+}
+__device__ __forceinline__ void pdl_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+bool pdl_enabled();   // capi.cu: false when AQ_NO_PDL is set in the environment
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+                              Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim            = dim3(grid, 1, 1);
+    cfg.blockDim           = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes   = smem;
+    cfg.stream             = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs                                          = attr;
+    cfg.numAttrs                                       = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- storage <-> fp32 ---------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);

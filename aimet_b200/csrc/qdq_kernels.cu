@@ -6,12 +6,13 @@
 // it computes, and the per-channel / per-block encodings of the chunk are staged once in shared memory.
 //
 // Results must match the CPU reference bit for bit, and the reference divides (x / scale).  An IEEE division
-// costs ~10 instructions, which would make the 16-bit kernels issue-bound, so the hot loop multiplies by the
-// correctly rounded reciprocal instead and *proves* per element that this cannot change the rounded integer:
-// the product and the true quotient differ by a few ulps, so they can only round to different integers when
-// the product lies within a small margin of a rounding boundary.  Elements inside that margin (about one in
-// ten thousand for 8-bit grids), and anything non-finite, take the exact division.  The file is compiled with
-// -fmad=false; every fused multiply-add below is explicit.
+// costs ~10 instructions, which makes these kernels issue-bound (most of all the 16-bit ones, which carry twice
+// the elements per byte), so the hot loop multiplies by the correctly rounded reciprocal instead and *proves*
+// per packet that this cannot have changed a rounded integer: product and true quotient differ by at most 3 ulp,
+// so they can only round differently when the product lies within a small guard band of a rounding boundary.
+// A packet with an element inside the band (about one element in ten thousand for 8-bit grids), or with
+// anything non-finite, is recomputed out of line with the reference formula itself.
+// The file is compiled with -fmad=false; every fused multiply-add below is explicit.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -28,7 +29,7 @@ __host__ __device__ constexpr int chunk_elems()
     return kThreads * VEC * kUnroll;
 }
 
-constexpr float kMagicRne = 12582912.0f;   // 1.5 * 2^23: (t + M) - M == rint(t) for |t| < 2^22
+constexpr float kMagicRne = 12582912.0f;               // 1.5 * 2^23: (t + M) - M == rint(t) for |t| < 2^22
 constexpr float kTwo23f   = 8388608.0f;
 constexpr float kUlp24    = 5.9604644775390625e-08f;   // 2^-24
 
@@ -73,175 +74,73 @@ __device__ __forceinline__ float narrow(float v)
     return to_f32<T>(from_f32<T>(v));
 }
 
-// =================================================================================================
-// Element operators.  Each has a Slot (per-channel constants, staged in shared memory or held in registers for
-// per-tensor work), `load(ch)` to build it, and `apply(x, slot, in_range)`.
-// =================================================================================================
-
-// ---- libpymo: quantizeValueCpu + dequantizeValueCpu (DlQuantization/src/trim_functions.cpp:140-171) -------------
-//   t = fmax(fmin(x, max), min);  u = t / delta - offset;  q = roundf(u);  y = delta * (q + offset)
-struct PymoOp
+// -------------------------------------------------------------------------------------------------
+// Packet <-> fp32 conversion (pairs of 16-bit values convert with one instruction)
+// -------------------------------------------------------------------------------------------------
+template <typename T, int VEC>
+__device__ __forceinline__ void unpack(const Pack<T, VEC>& p, float (&f)[VEC])
 {
-    // per-tensor (host-derived grid, narrowed to float like the reference does at the call boundary)
-    float mn, mx, delta, offset;
-    // per-channel
-    const float* enc_min;      // raw min/max (derive = 1) or gated min/max (derive = 0)
-    const float* enc_max;
-    const float* enc_delta;    // derive = 0 only
-    const float* enc_offset;   // derive = 0 only
-    float num_steps;
-    int derive;
-    float shift;       // subtracted from codes (quantize only)
-    int codes_only;    // 1: emit integer codes, 0: quantize-dequantize
-
-    struct Slot
-    {
-        float mn, mx, dl, of;
-        float rdl;    // RN(1 / delta)
-        float c;      // 0.5 - offset
-        float eps;    // 0.5 - margin, or 0 when the reciprocal form cannot be trusted for this grid
-    };
-
-    __device__ __forceinline__ static void finish(Slot& k)
-    {
-        k.rdl = __frcp_rn(k.dl);
-        k.c   = 0.5f - k.of;
-        // u ranges over [~0, (max-min)/delta]; |s - (u + 0.5)| <= 2^-24 (2|q| + |c| + |s| + |u|) with
-        // |q| <= |of| + |u|, so 2^-24 (3|of| + 4 umax + 2), plus a quarter for second-order terms
-        const float umax   = fabsf(__fdiv_rn(__fsub_rn(k.mx, k.mn), k.dl));
-        const float margin = 1.25f * kUlp24 * (3.0f * fabsf(k.of) + 4.0f * umax + 2.0f);
-        k.eps              = (margin < 0.25f && umax < 4194304.0f) ? 0.5f - margin : 0.0f;   // NaN -> 0
-        if (!(k.eps > 0.0f))
-            k.eps = 0.0f;
-    }
-
-    __device__ __forceinline__ Slot scalar_slot() const
-    {
-        Slot k;
-        k.mn = mn, k.mx = mx, k.dl = delta, k.of = offset;
-        finish(k);
-        return k;
-    }
-
-    __device__ __forceinline__ Slot load(int64_t ch) const
-    {
-        Slot k;
-        k.mn = enc_min[ch], k.mx = enc_max[ch];
-        if (derive)
-        {
-            // AimetTensorQuantizer.cpp:236-254: gate, delta, offset in fp32 (offset: half to even)
-            k.mn     = k.mn < 0.0f ? k.mn : 0.0f;
-            k.mx     = k.mx > 0.0f ? k.mx : 0.0f;
-            float lo = __fadd_rn(k.mn, 1e-5f);
-            k.mx     = k.mx > lo ? k.mx : lo;
-            k.dl     = __fdiv_rn(__fsub_rn(k.mx, k.mn), num_steps);
-            k.of     = rintf(__fdiv_rn(k.mn, k.dl));
-        }
-        else
-        {
-            k.dl = enc_delta[ch];
-            k.of = enc_offset[ch];
-        }
-        finish(k);
-        return k;
-    }
-
-    template <bool NARROW>
-    __device__ __forceinline__ float apply(float x, const Slot& k, bool& in_range) const
-    {
-        in_range      = true;
-        const float t = fmaxf(fminf(x, k.mx), k.mn);
-        // fast: s ~ u + 0.5; q = floor(s) read from the mantissa after a round-down add of 2^23
-        const float s  = fmaf(t, k.rdl, k.c);
-        const float s2 = __fadd_rd(s, kTwo23f);
-        float q        = s2 - kTwo23f;
-        const float g  = s - (s2 - 8388607.5f);
-        if (!(fabsf(g) < k.eps) || s < 0.0f)
-        {
-            // near a rounding boundary (or a degenerate grid): the reference formula itself
-            q = round_half_away(__fsub_rn(__fdiv_rn(t, k.dl), k.of));
-        }
-        if (codes_only)
-            return __fsub_rn(q, shift);
-        return __fmul_rn(k.dl, __fadd_rn(q, k.of));
-    }
-};
-
-// ---- v2: torch_builtins.py:303-313 (QuantDequantFunc / QuantizeFunc) and :264-266 (DequantizeFunc) -------------
-//   r = round_half_even(x / s) - o;  mask = qmin <= r <= qmax;  q = clamp(r, qmin, qmax);  y = (q + o) * s
-struct V2Op
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+        f[e] = to_f32<T>(p.v[e]);
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void repack(const float (&f)[VEC], Pack<T, VEC>& p)
 {
-    const float* scale;
-    const float* offset;
-    float qmin, qmax;
-    int out_kind;
-    int dequant_only;
-
-    struct Slot
-    {
-        float s, o, rs;
-    };
-
-    __device__ __forceinline__ Slot load(int64_t ch) const
-    {
-        Slot k;
-        k.s  = scale[ch];
-        k.o  = offset[ch];
-        k.rs = __frcp_rn(k.s);
-        return k;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+        p.v[e] = from_f32<T>(f[e]);
+}
+#define AQ_PAIRWISE(T, T2, TO2, FROM2)                                                                               \
+    template <>                                                                                                      \
+    __device__ __forceinline__ void unpack<T, 8>(const Pack<T, 8>& p, float(&f)[8])                                  \
+    {                                                                                                                \
+        const T2* q = reinterpret_cast<const T2*>(&p);                                                               \
+        for (int e = 0; e < 4; ++e)                                                                                  \
+        {                                                                                                            \
+            const float2 v = TO2(q[e]);                                                                              \
+            f[2 * e] = v.x, f[2 * e + 1] = v.y;                                                                      \
+        }                                                                                                            \
+    }                                                                                                                \
+    template <>                                                                                                      \
+    __device__ __forceinline__ void repack<T, 8>(const float(&f)[8], Pack<T, 8>& p)                                  \
+    {                                                                                                                \
+        T2* q = reinterpret_cast<T2*>(&p);                                                                           \
+        for (int e = 0; e < 4; ++e)                                                                                  \
+            q[e] = FROM2(f[2 * e], f[2 * e + 1]);                                                                    \
+    }                                                                                                                \
+    template <>                                                                                                      \
+    __device__ __forceinline__ void unpack<T, 4>(const Pack<T, 4>& p, float(&f)[4])                                  \
+    {                                                                                                                \
+        const T2* q = reinterpret_cast<const T2*>(&p);                                                               \
+        for (int e = 0; e < 2; ++e)                                                                                  \
+        {                                                                                                            \
+            const float2 v = TO2(q[e]);                                                                              \
+            f[2 * e] = v.x, f[2 * e + 1] = v.y;                                                                      \
+        }                                                                                                            \
+    }                                                                                                                \
+    template <>                                                                                                      \
+    __device__ __forceinline__ void repack<T, 4>(const float(&f)[4], Pack<T, 4>& p)                                  \
+    {                                                                                                                \
+        T2* q = reinterpret_cast<T2*>(&p);                                                                           \
+        for (int e = 0; e < 2; ++e)                                                                                  \
+            q[e] = FROM2(f[2 * e], f[2 * e + 1]);                                                                    \
     }
-    __device__ __forceinline__ Slot scalar_slot() const
-    {
-        return load(0);
-    }
+AQ_PAIRWISE(__half, __half2, __half22float2, __floats2half2_rn)
+AQ_PAIRWISE(__nv_bfloat16, __nv_bfloat162, __bfloat1622float2, __floats2bfloat162_rn)
+#undef AQ_PAIRWISE
 
-    template <typename T, bool NARROW>
-    __device__ __forceinline__ float apply_t(float x, const Slot& k, bool& in_range) const
-    {
-        if (dequant_only)
-        {
-            in_range = true;
-            float r  = __fadd_rn(x, k.o);
-            if (NARROW)
-                r = narrow<T>(r);
-            return __fmul_rn(r, k.s);
-        }
-        float r;
-        if (NARROW)
-        {
-            // the storage dtype is also the arithmetic dtype: every step is rounded to it.  fp32 arithmetic
-            // followed by one rounding equals the narrow operation (24 >= 2p + 2 for p = 11 and p = 8).
-            r = narrow<T>(__fdiv_rn(x, k.s));
-            r = rintf(r);
-            r = narrow<T>(__fsub_rn(r, k.o));
-        }
-        else
-        {
-            // RN(x/s) and RN(x * RN(1/s)) differ by at most 3 ulp, so they round to different integers only if
-            // the product is within 3 ulp of a half-integer; 4 ulp = 2^-22 |t| is used as the guard band.
-            const float t = __fmul_rn(x, k.rs);
-            r             = __fsub_rn(__fadd_rn(t, kMagicRne), kMagicRne);
-            const float d = __fsub_rn(t, r);
-            if (!(fabsf(d) < fmaf(fabsf(t), -4.0f * kUlp24, 0.5f)))
-                r = rintf(__fdiv_rn(x, k.s));   // also taken for NaN / Inf / |t| >= 2^21
-            r = __fsub_rn(r, k.o);
-        }
-        // torch.clamp keeps NaN: min.NaN / max.NaN
-        float q;
-        asm("max.NaN.f32 %0, %1, %2;" : "=f"(q) : "f"(r), "f"(qmin));
-        asm("min.NaN.f32 %0, %1, %2;" : "=f"(q) : "f"(q), "f"(qmax));
-        in_range = (q == r);   // false for NaN, like (qmin <= r) & (r <= qmax)
-        if (out_kind == AQ_V2_OUT_CODES)
-            return q;
-        float y = __fadd_rn(q, k.o);
-        if (NARROW)
-            y = narrow<T>(y);
-        return __fmul_rn(y, k.s);
-    }
-};
+__device__ __forceinline__ float clamp_keep_nan(float r, float lo, float hi)
+{
+    // torch.clamp keeps NaN: min.NaN / max.NaN
+    float q;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(q) : "f"(r), "f"(lo));
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(q) : "f"(q), "f"(hi));
+    return q;
+}
 
 // =================================================================================================
-// Streaming skeleton
+// Chunk load / store
 // =================================================================================================
 template <typename T, int VEC>
 __device__ __forceinline__ void load_chunk(const T* __restrict__ x, int64_t base, int64_t n, Pack<T, VEC> (&v)[kUnroll],
@@ -277,32 +176,109 @@ __device__ __forceinline__ void store_packet(T* __restrict__ y, int64_t idx, int
     }
 }
 
+// =================================================================================================
+// libpymo semantics: quantizeValueCpu + dequantizeValueCpu (DlQuantization/src/trim_functions.cpp:140-171)
+//   t = fmax(fmin(x, max), min);  u = t / delta - offset;  q = roundf(u);  y = delta * (q + offset)
+// =================================================================================================
+struct PymoSlot
+{
+    float mn, mx, dl, of;
+    float rdl;    // RN(1 / delta)
+    float c;      // 1.5 - offset
+    float eps;    // 0.5 - guard band, or 0 when the reciprocal form cannot be trusted for this grid
+};
+
 struct PymoArgs
 {
     const float* in;
     float* out;
     int64_t n;
-    PymoOp op;
+    // per-tensor (host-derived grid, narrowed to float like the reference does at the call boundary)
+    float mn, mx, delta, offset;
+    // per-channel
+    const float* enc_min;      // raw min/max (derive = 1) or gated min/max (derive = 0)
+    const float* enc_max;
+    const float* enc_delta;    // derive = 0 only
+    const float* enc_offset;   // derive = 0 only
+    float num_steps;
+    int derive;
+    float shift;   // subtracted from codes (quantize only)
     ChanGeom geom;
 };
 
-template <int VEC, bool PER_CH>
+// Fast form: s = t * RN(1/delta) + (1.5 - offset) approximates u + 1.5 (one FMA); floor(s) is read from the
+// mantissa after a round-down add of 2^23, so q = floor(u + 0.5) = roundf(u) for u > -0.5.
+// |s - (u + 1.5)| <= 2^-24 (2|t/delta| + |c| + |s| + |u|) <= 2^-24 (3|of| + 4 umax + 6): that is the guard band.
+__device__ __forceinline__ void pymo_finish(PymoSlot& k)
+{
+    k.rdl = __frcp_rn(k.dl);
+    k.c   = 1.5f - k.of;
+    const float ulo    = __fsub_rn(__fdiv_rn(k.mn, k.dl), k.of);   // smallest / largest u the clamp lets through
+    const float uhi    = __fsub_rn(__fdiv_rn(k.mx, k.dl), k.of);
+    const float umax   = fmaxf(fabsf(ulo), fabsf(uhi));
+    const float margin = 1.25f * kUlp24 * (3.0f * fabsf(k.of) + 4.0f * umax + 6.0f);
+    const bool sane    = (ulo > -1.0f) && (umax < 4194304.0f) && (margin < 0.25f) && (fabsf(k.of) < 4194304.0f);
+    k.eps              = sane ? 0.5f - margin : 0.0f;   // any NaN makes `sane` false
+}
+
+__device__ __forceinline__ PymoSlot pymo_load(const PymoArgs& a, int64_t ch)
+{
+    PymoSlot k;
+    k.mn = a.enc_min[ch], k.mx = a.enc_max[ch];
+    if (a.derive)
+    {
+        // AimetTensorQuantizer.cpp:236-254: gate, delta, offset in fp32 (offset: half to even)
+        k.mn     = k.mn < 0.0f ? k.mn : 0.0f;
+        k.mx     = k.mx > 0.0f ? k.mx : 0.0f;
+        float lo = __fadd_rn(k.mn, 1e-5f);
+        k.mx     = k.mx > lo ? k.mx : lo;
+        k.dl     = __fdiv_rn(__fsub_rn(k.mx, k.mn), a.num_steps);
+        k.of     = rintf(__fdiv_rn(k.mn, k.dl));
+    }
+    else
+    {
+        k.dl = a.enc_delta[ch];
+        k.of = a.enc_offset[ch];
+    }
+    pymo_finish(k);
+    return k;
+}
+
+template <int VEC, bool CODES>
+__device__ __forceinline__ void pymo_exact_packet(const Pack<float, VEC>& in, Pack<float, VEC>& out, PymoSlot k, float shift)
+{
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+    {
+        const float t = fmaxf(fminf(in.v[e], k.mx), k.mn);
+        const float q = round_half_away(__fsub_rn(__fdiv_rn(t, k.dl), k.of));
+        out.v[e]      = CODES ? __fsub_rn(q, shift) : __fmul_rn(k.dl, __fadd_rn(q, k.of));
+    }
+}
+
+template <int VEC, bool PER_CH, bool CODES>
 __global__ void __launch_bounds__(kThreads) pymo_qdq_kernel(PymoArgs a)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int CHUNK = chunk_elems<VEC>();
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
-    __shared__ PymoOp::Slot s_slot[PER_CH ? kMaxRuns : 1];
+    __shared__ PymoSlot s_slot[PER_CH ? kMaxRuns : 1];
     RunCtx rc {0, 0, 1};
-    PymoOp::Slot k0;
+    PymoSlot k0;
     if (PER_CH)
     {
         rc = make_run_ctx<VEC>(a.geom, base, a.n);
         for (int lr = threadIdx.x; lr < rc.nruns; lr += kThreads)
-            s_slot[lr] = a.op.load((rc.r0 + lr) % a.geom.num_ch);
+            s_slot[lr] = pymo_load(a, (rc.r0 + lr) % a.geom.num_ch);
         __syncthreads();
     }
     else
-        k0 = a.op.scalar_slot();
+    {
+        k0.mn = a.mn, k0.mx = a.mx, k0.dl = a.delta, k0.of = a.offset;
+        pymo_finish(k0);
+    }
+    const float shift = a.shift;
 
     Pack<float, VEC> v[kUnroll];
     bool full[kUnroll];
@@ -311,21 +287,30 @@ __global__ void __launch_bounds__(kThreads) pymo_qdq_kernel(PymoArgs a)
     for (int u = 0; u < kUnroll; ++u)
     {
         const uint32_t off = (uint32_t) (u * kThreads + threadIdx.x) * VEC;
-        PymoOp::Slot k     = k0;
+        PymoSlot k         = k0;
         if (PER_CH)
             k = s_slot[run_of(a.geom, rc, off)];   // VEC | inner: one run per packet
+        Pack<float, VEC> r;
+        bool ok = true;
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
         {
-            bool dummy;
-            v[u].v[e] = a.op.apply<false>(v[u].v[e], k, dummy);
+            const float t  = fmaxf(fminf(v[u].v[e], k.mx), k.mn);
+            const float s  = fmaf(t, k.rdl, k.c);
+            const float s2 = __fadd_rd(s, kTwo23f);
+            const float g  = s - (s2 - 8388607.5f);
+            ok             = ok && (fabsf(g) < k.eps);
+            const float q  = s2 - 8388609.0f;   // floor(s) - 1
+            r.v[e]         = CODES ? __fsub_rn(q, shift) : __fmul_rn(k.dl, __fadd_rn(q, k.of));
         }
-        store_packet<float, VEC>(a.out, base + off, a.n, v[u], full[u]);
+        if (!ok)
+            pymo_exact_packet<VEC, CODES>(v[u], r, k, shift);
+        store_packet<float, VEC>(a.out, base + off, a.n, r, full[u]);
     }
 }
 
 template <bool PER_CH>
-static int launch_pymo(PymoArgs a, int vec, cudaStream_t st)
+static int launch_pymo(PymoArgs a, int vec, bool codes, cudaStream_t st)
 {
     if (a.n == 0)
         return AQ_OK;
@@ -333,7 +318,10 @@ static int launch_pymo(PymoArgs a, int vec, cudaStream_t st)
     {                                                                                                                \
         a.geom       = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>());                                     \
         int64_t grid = (a.n + chunk_elems<V>() - 1) / chunk_elems<V>();                                              \
-        pymo_qdq_kernel<V, PER_CH><<<(unsigned) grid, kThreads, 0, st>>>(a);                                         \
+        if (codes)                                                                                                   \
+            launch_pdl(pymo_qdq_kernel<V, PER_CH, true>, (unsigned) grid, kThreads, 0, st, a);                                 \
+        else                                                                                                         \
+            launch_pdl(pymo_qdq_kernel<V, PER_CH, false>, (unsigned) grid, kThreads, 0, st, a);                                \
     }
     switch (vec)
     {
@@ -351,10 +339,10 @@ int pymo_per_tensor(const float* in, float* out, int64_t n, float mn, float mx, 
 {
     PymoArgs a {};
     a.in = in, a.out = out, a.n = n;
-    a.op.mn = mn, a.op.mx = mx, a.op.delta = delta, a.op.offset = offset;
-    a.op.codes_only = codes_only, a.op.shift = shift;
+    a.mn = mn, a.mx = mx, a.delta = delta, a.offset = offset;
+    a.shift       = shift;
     a.geom.num_ch = 1, a.geom.inner = n > 0 ? n : 1;
-    return launch_pymo<false>(a, pick_vec<float>(in, out, nullptr, 0), st);
+    return launch_pymo<false>(a, pick_vec<float>(in, out, nullptr, 0), codes_only != 0, st);
 }
 
 int pymo_per_channel(const float* in, float* out, int64_t n, int64_t num_ch, int64_t inner, const float* enc_min,
@@ -363,10 +351,10 @@ int pymo_per_channel(const float* in, float* out, int64_t n, int64_t num_ch, int
 {
     PymoArgs a {};
     a.in = in, a.out = out, a.n = n;
-    a.op.enc_min = enc_min, a.op.enc_max = enc_max, a.op.enc_delta = enc_delta, a.op.enc_offset = enc_offset;
-    a.op.num_steps = num_steps, a.op.derive = derive;
+    a.enc_min = enc_min, a.enc_max = enc_max, a.enc_delta = enc_delta, a.enc_offset = enc_offset;
+    a.num_steps = num_steps, a.derive = derive;
     a.geom.num_ch = num_ch, a.geom.inner = inner;
-    return launch_pymo<true>(a, pick_vec<float>(in, out, nullptr, inner), st);
+    return launch_pymo<true>(a, pick_vec<float>(in, out, nullptr, inner), false, st);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -403,29 +391,81 @@ int pymo_broadcast(const BroadcastArgs& a, cudaStream_t st)
     return check_launch();
 }
 
-// -------------------------------------------------------------------------------------------------
-// v2-semantics quantize / quantize-dequantize (+ optional clamp mask) and dequantize
-// -------------------------------------------------------------------------------------------------
-template <typename T, int VEC, bool PER_CH, bool NARROW>
+// =================================================================================================
+// v2 semantics: torch_builtins.py:303-313 (QuantDequantFunc / QuantizeFunc) and :264-266 (DequantizeFunc)
+//   r = round_half_even(x / s) - o;  mask = qmin <= r <= qmax;  q = clamp(r, qmin, qmax);  y = (q + o) * s
+// =================================================================================================
+struct V2Slot
+{
+    float s, o, rs;
+    float eps;   // 0.5 - guard band of the reciprocal form for this encoding
+};
+
+// RN(x/s) and RN(x * RN(1/s)) differ by at most 3 ulp of the quotient t.  Wherever the rounded value can matter
+// (within one step of the clamp range) |t| <= T = max(|qmin + o|, |qmax + o|) + 1, so a guard band of
+// 4 ulp(T) = 2^-22 T around every half-integer is enough; outside that range both forms clamp to the same bound.
+__device__ __forceinline__ V2Slot v2_load(const float* scale, const float* offset, int64_t ch, float qmin, float qmax)
+{
+    V2Slot k;
+    k.s  = scale[ch];
+    k.o  = offset[ch];
+    k.rs = __frcp_rn(k.s);
+    const float T      = fmaxf(fabsf(__fadd_rn(qmin, k.o)), fabsf(__fadd_rn(qmax, k.o))) + 1.0f;
+    const float margin = 4.0f * kUlp24 * T;
+    k.eps              = (margin < 0.25f) ? 0.5f - margin : 0.0f;   // NaN -> 0: always the exact path
+    return k;
+}
+
+// Reference formula for one packet (also the only path when intermediates are kept in the storage dtype).
+template <typename T, int VEC, bool NARROW, bool CODES>
+__device__ __forceinline__ void v2_exact_packet(const float (&x)[VEC], float (&y)[VEC], uint8_t (&m)[VEC], V2Slot k, float qmin,
+                                             float qmax)
+{
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+    {
+        float r = __fdiv_rn(x[e], k.s);
+        if (NARROW)
+            r = narrow<T>(r);   // fp32 arithmetic + one rounding == the narrow operation (24 >= 2p + 2)
+        r = rintf(r);
+        r = __fsub_rn(r, k.o);
+        if (NARROW)
+            r = narrow<T>(r);
+        const float q = clamp_keep_nan(r, qmin, qmax);
+        m[e]          = (q == r) ? 1 : 0;
+        if (CODES)
+            y[e] = q;
+        else
+        {
+            float v = __fadd_rn(q, k.o);
+            if (NARROW)
+                v = narrow<T>(v);
+            y[e] = __fmul_rn(v, k.s);
+        }
+    }
+}
+
+// MODE: 0 = fast fp32-internal quantize(-dequantize); 1 = exact / narrow-internal quantize(-dequantize); 2 = dequantize
+template <typename T, int VEC, bool PER_CH, int MODE, bool NARROW, bool CODES, bool MASK>
 __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int CHUNK = chunk_elems<VEC>();
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
-    V2Op op;
-    op.scale = a.scale, op.offset = a.offset, op.qmin = a.qmin, op.qmax = a.qmax;
-    op.out_kind = a.out_kind, op.dequant_only = a.dequant_only;
-    __shared__ V2Op::Slot s_slot[PER_CH ? kMaxRuns : 1];
+    const float qmin = a.qmin, qmax = a.qmax;
+    __shared__ V2Slot s_slot[PER_CH ? kMaxRuns : 1];
     RunCtx rc {0, 0, 1};
-    V2Op::Slot k0;
+    V2Slot k0;
     if (PER_CH)
     {
         rc = make_run_ctx<VEC>(a.geom, base, a.n);
         for (int lr = threadIdx.x; lr < rc.nruns; lr += kThreads)
-            s_slot[lr] = op.load((rc.r0 + lr) % a.geom.num_ch);
+            s_slot[lr] = v2_load(a.scale, a.offset, (rc.r0 + lr) % a.geom.num_ch, qmin, qmax);
         __syncthreads();
     }
     else
-        k0 = op.scalar_slot();
+        k0 = v2_load(a.scale, a.offset, 0, qmin, qmax);
 
     Pack<T, VEC> v[kUnroll];
     bool full[kUnroll];
@@ -435,39 +475,101 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
     {
         const uint32_t off = (uint32_t) (u * kThreads + threadIdx.x) * VEC;
         const int64_t idx  = base + off;
-        V2Op::Slot k       = k0;
+        V2Slot k           = k0;
         if (PER_CH)
             k = s_slot[run_of(a.geom, rc, off)];
-        Pack<uint8_t, VEC> m;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e)
+        float x[VEC], y[VEC];
+        uint8_t m[VEC];
+        unpack<T, VEC>(v[u], x);
+        if (MODE == 2)
         {
-            bool in_range;
-            const float r = op.apply_t<T, NARROW>(to_f32<T>(v[u].v[e]), k, in_range);
-            v[u].v[e]     = from_f32<T>(r);
-            m.v[e]        = in_range ? 1 : 0;
+            // DequantizeFunc: (x + o) * s, in the storage dtype
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+            {
+                float r = __fadd_rn(x[e], k.o);
+                if (NARROW)
+                    r = narrow<T>(r);
+                y[e] = __fmul_rn(r, k.s);
+            }
         }
-        store_packet<T, VEC>(static_cast<T*>(a.y), idx, a.n, v[u], full[u]);
-        if (a.mask)
-            store_packet<uint8_t, VEC>(a.mask, idx, a.n, m, full[u]);
+        else if (MODE == 1)
+            v2_exact_packet<T, VEC, NARROW, CODES>(x, y, m, k, qmin, qmax);
+        else
+        {
+            bool ok = true;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+            {
+                const float t = __fmul_rn(x[e], k.rs);
+                float r       = __fsub_rn(__fadd_rn(t, kMagicRne), kMagicRne);
+                ok            = ok && (fabsf(__fsub_rn(t, r)) < k.eps);   // false for NaN / Inf
+                r             = __fsub_rn(r, k.o);
+                const float q = clamp_keep_nan(r, qmin, qmax);
+                if (MASK)
+                    m[e] = (q == r) ? 1 : 0;
+                y[e] = CODES ? q : __fmul_rn(__fadd_rn(q, k.o), k.s);
+            }
+            if (!ok)
+                v2_exact_packet<T, VEC, false, CODES>(x, y, m, k, qmin, qmax);
+        }
+        Pack<T, VEC> r;
+        repack<T, VEC>(y, r);
+        store_packet<T, VEC>(static_cast<T*>(a.y), idx, a.n, r, full[u]);
+        if (MASK)
+        {
+            Pack<uint8_t, VEC> mp;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+                mp.v[e] = m[e];
+            store_packet<uint8_t, VEC>(a.mask, idx, a.n, mp, full[u]);
+        }
     }
 }
 
-template <typename T, bool PER_CH, bool NARROW>
-static int launch_v2_vec(V2Args a, int vec, cudaStream_t st)
+template <typename T, int VEC, bool PER_CH>
+static void launch_v2_variant(const V2Args& a, bool narrow, cudaStream_t st)
+{
+    const int64_t grid = (a.n + chunk_elems<VEC>() - 1) / chunk_elems<VEC>();
+    const unsigned g   = (unsigned) grid;
+    const bool codes = a.out_kind == AQ_V2_OUT_CODES, mask = a.mask != nullptr;
+#define AQ_K(MODE, NARROW, CODES, MASK) launch_pdl(v2_kernel<T, VEC, PER_CH, MODE, NARROW, CODES, MASK>, g, kThreads, 0, st, a)
+    if (a.dequant_only)
+    {
+        if (narrow)
+            AQ_K(2, true, false, false);
+        else
+            AQ_K(2, false, false, false);
+    }
+    else if (narrow)
+    {
+        if (codes)
+            mask ? AQ_K(1, true, true, true) : AQ_K(1, true, true, false);
+        else
+            mask ? AQ_K(1, true, false, true) : AQ_K(1, true, false, false);
+    }
+    else
+    {
+        if (codes)
+            mask ? AQ_K(0, false, true, true) : AQ_K(0, false, true, false);
+        else
+            mask ? AQ_K(0, false, false, true) : AQ_K(0, false, false, false);
+    }
+#undef AQ_K
+}
+
+template <typename T, bool PER_CH>
+static int launch_v2_vec(V2Args a, int vec, bool narrow, cudaStream_t st)
 {
 #define AQ_LAUNCH(V)                                                                                                 \
     {                                                                                                                \
-        a.geom       = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>());                                     \
-        int64_t grid = (a.n + chunk_elems<V>() - 1) / chunk_elems<V>();                                              \
-        v2_kernel<T, V, PER_CH, NARROW><<<(unsigned) grid, kThreads, 0, st>>>(a);                                    \
+        a.geom = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>());                                           \
+        launch_v2_variant<T, V, PER_CH>(a, narrow, st);                                                              \
     }
     if (sizeof(T) == 2 && vec == 8)
         AQ_LAUNCH((sizeof(T) == 2 ? 8 : 4))
-    else if (vec == 4)
+    else if (vec >= 4)
         AQ_LAUNCH(4)
-    else if (vec == 2)
-        AQ_LAUNCH(2)
     else
         AQ_LAUNCH(1)
 #undef AQ_LAUNCH
@@ -475,8 +577,8 @@ static int launch_v2_vec(V2Args a, int vec, cudaStream_t st)
     return check_launch();
 }
 
-template <typename T, bool NARROW>
-static int launch_v2_t(V2Args a, cudaStream_t st)
+template <typename T>
+static int launch_v2_t(V2Args a, bool narrow, cudaStream_t st)
 {
     const bool per_ch = a.geom.num_ch > 1;
     // the mask is written with VEC-byte packets, so it constrains the width like the tensors do
@@ -484,8 +586,8 @@ static int launch_v2_t(V2Args a, cudaStream_t st)
     while (vec > 1 && a.mask && ((uintptr_t) a.mask % vec))
         vec >>= 1;
     if (per_ch)
-        return launch_v2_vec<T, true, NARROW>(a, vec, st);
-    return launch_v2_vec<T, false, NARROW>(a, vec, st);
+        return launch_v2_vec<T, true>(a, vec, narrow, st);
+    return launch_v2_vec<T, false>(a, vec, narrow, st);
 }
 
 int v2_launch(V2Args a, int dtype, int narrow_internal, cudaStream_t st)
@@ -494,10 +596,9 @@ int v2_launch(V2Args a, int dtype, int narrow_internal, cudaStream_t st)
         return AQ_OK;
     switch (dtype)
     {
-    case AQ_F32: return launch_v2_t<float, false>(a, st);
-    case AQ_BF16:
-        return narrow_internal ? launch_v2_t<__nv_bfloat16, true>(a, st) : launch_v2_t<__nv_bfloat16, false>(a, st);
-    case AQ_F16: return narrow_internal ? launch_v2_t<__half, true>(a, st) : launch_v2_t<__half, false>(a, st);
+    case AQ_F32: return launch_v2_t<float>(a, false, st);
+    case AQ_BF16: return launch_v2_t<__nv_bfloat16>(a, narrow_internal != 0, st);
+    case AQ_F16: return launch_v2_t<__half>(a, narrow_internal != 0, st);
     default: return AQ_ERR_INVALID_ARG;
     }
 }
@@ -511,6 +612,8 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(kThreads) v2_bwd_kernel(const T* __restrict__ g, const uint8_t* __restrict__ mask,
                                                           T* __restrict__ dx, int64_t n)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int CHUNK = chunk_elems<VEC>();
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
     Pack<T, VEC> v[kUnroll];
@@ -522,14 +625,17 @@ __global__ void __launch_bounds__(kThreads) v2_bwd_kernel(const T* __restrict__ 
     for (int u = 0; u < kUnroll; ++u)
     {
         const int64_t idx = base + (int64_t) (u * kThreads + threadIdx.x) * VEC;
+        float f[VEC];
+        unpack<T, VEC>(v[u], f);
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
         {
             // grad * bool: x*1 and x*0 are exact in any dtype (-0 and NaN behave as in the reference product)
-            const float p = __fmul_rn(to_f32<T>(v[u].v[e]), m[u].v[e] ? 1.0f : 0.0f);
-            v[u].v[e]     = from_f32<T>(p);
+            f[e] = __fmul_rn(f[e], m[u].v[e] ? 1.0f : 0.0f);
         }
-        store_packet<T, VEC>(dx, idx, n, v[u], full[u]);
+        Pack<T, VEC> r;
+        repack<T, VEC>(f, r);
+        store_packet<T, VEC>(dx, idx, n, r, full[u]);
     }
 }
 
@@ -542,14 +648,12 @@ static int launch_v2_bwd(const void* g, const uint8_t* mask, void* dx, int64_t n
 #define AQ_LAUNCH(V)                                                                                                 \
     {                                                                                                                \
         int64_t grid = (n + chunk_elems<V>() - 1) / chunk_elems<V>();                                                \
-        v2_bwd_kernel<T, V><<<(unsigned) grid, kThreads, 0, st>>>((const T*) g, mask, (T*) dx, n);                    \
+        launch_pdl(v2_bwd_kernel<T, V>, (unsigned) grid, kThreads, 0, st, (const T*) g, mask, (T*) dx, n);                    \
     }
     if (sizeof(T) == 2 && vec == 8)
         AQ_LAUNCH((sizeof(T) == 2 ? 8 : 4))
-    else if (vec == 4)
+    else if (vec >= 4)
         AQ_LAUNCH(4)
-    else if (vec == 2)
-        AQ_LAUNCH(2)
     else
         AQ_LAUNCH(1)
 #undef AQ_LAUNCH
@@ -622,11 +726,9 @@ __global__ void __launch_bounds__(kThreads) v2_param_grad_kernel(V2GradArgs a)
             const float g = to_f32<T>(gv[u].v[e]);
             const float m = mv[u].v[e] ? 1.0f : 0.0f;
             const float t = __fdiv_rn(to_f32<T>(xv[u].v[e]), sc);
-            float c       = rintf(t);
-            asm("max.NaN.f32 %0, %1, %2;" : "=f"(c) : "f"(c), "f"(lo));
-            asm("min.NaN.f32 %0, %1, %2;" : "=f"(c) : "f"(c), "f"(hi));
-            ds.v[e]  = __fmul_rn(g, __fsub_rn(c, __fmul_rn(t, m)));
-            dof.v[e] = __fmul_rn(g, __fmul_rn(1.0f - m, sc));
+            const float c = clamp_keep_nan(rintf(t), lo, hi);
+            ds.v[e]       = __fmul_rn(g, __fsub_rn(c, __fmul_rn(t, m)));
+            dof.v[e]      = __fmul_rn(g, __fmul_rn(1.0f - m, sc));
         }
         if (a.dscale)
             store_packet<float, VEC>(a.dscale, idx, a.n, ds, full[u]);
@@ -655,8 +757,6 @@ static int launch_param_grad(V2GradArgs a, cudaStream_t st)
     {
         if (vec == 4)
             AQ_LAUNCH(4, true)
-        else if (vec == 2)
-            AQ_LAUNCH(2, true)
         else
             AQ_LAUNCH(1, true)
     }
@@ -664,8 +764,6 @@ static int launch_param_grad(V2GradArgs a, cudaStream_t st)
     {
         if (vec == 4)
             AQ_LAUNCH(4, false)
-        else if (vec == 2)
-            AQ_LAUNCH(2, false)
         else
             AQ_LAUNCH(1, false)
     }
@@ -692,6 +790,8 @@ int v2_param_grad(V2GradArgs a, int dtype, cudaStream_t st)
 template <int VEC, bool PER_CH>
 __global__ void __launch_bounds__(kThreads) ste_v1_kernel(SteArgs a)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int CHUNK = chunk_elems<VEC>();
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
     __shared__ float s_mn[PER_CH ? kMaxRuns : 1], s_mx[PER_CH ? kMaxRuns : 1];
@@ -747,14 +847,12 @@ int ste_v1(SteArgs a, cudaStream_t st)
     {                                                                                                                \
         a.geom       = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>());                                     \
         int64_t grid = (a.n + chunk_elems<V>() - 1) / chunk_elems<V>();                                              \
-        ste_v1_kernel<V, PC><<<(unsigned) grid, kThreads, 0, st>>>(a);                                               \
+        launch_pdl(ste_v1_kernel<V, PC>, (unsigned) grid, kThreads, 0, st, a);                                               \
     }
     if (per_ch)
     {
         if (vec == 4)
             AQ_LAUNCH(4, true)
-        else if (vec == 2)
-            AQ_LAUNCH(2, true)
         else
             AQ_LAUNCH(1, true)
     }
@@ -762,8 +860,6 @@ int ste_v1(SteArgs a, cudaStream_t st)
     {
         if (vec == 4)
             AQ_LAUNCH(4, false)
-        else if (vec == 2)
-            AQ_LAUNCH(2, false)
         else
             AQ_LAUNCH(1, false)
     }

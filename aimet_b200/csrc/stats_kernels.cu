@@ -59,6 +59,8 @@ __global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __re
                                                                    unsigned int* __restrict__ ticket,
                                                                    float2* __restrict__ partials, int accumulate)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     float mn = INFINITY, mx = -INFINITY;
     const int64_t npack  = n / VEC;
     const int64_t stride = (int64_t) gridDim.x * kMmThreads;
@@ -385,17 +387,20 @@ static int minmax_t(const T* x, int64_t n, int64_t num_ch, int64_t inner, float*
         switch (vec)
         {
         case 8:
-            minmax_tensor_kernel<T, (sizeof(T) == 2 ? 8 : 4), PROP>
-                <<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials, accumulate);
+            launch_pdl(minmax_tensor_kernel<T, (sizeof(T) == 2 ? 8 : 4), PROP>, (unsigned) grid, kMmThreads, 0, st, x, n, out_min, out_max, ticket,
+                       partials, accumulate);
             break;
         case 4:
-            minmax_tensor_kernel<T, 4, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials, accumulate);
+            launch_pdl(minmax_tensor_kernel<T, 4, PROP>, (unsigned) grid, kMmThreads, 0, st, x, n, out_min, out_max, ticket,
+                       partials, accumulate);
             break;
         case 2:
-            minmax_tensor_kernel<T, 2, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials, accumulate);
+            launch_pdl(minmax_tensor_kernel<T, 2, PROP>, (unsigned) grid, kMmThreads, 0, st, x, n, out_min, out_max, ticket,
+                       partials, accumulate);
             break;
         default:
-            minmax_tensor_kernel<T, 1, PROP><<<grid, kMmThreads, 0, st>>>(x, n, out_min, out_max, ticket, partials, accumulate);
+            launch_pdl(minmax_tensor_kernel<T, 1, PROP>, (unsigned) grid, kMmThreads, 0, st, x, n, out_min, out_max, ticket,
+                       partials, accumulate);
         }
         note_launch();
         return check_launch();
@@ -547,72 +552,105 @@ __host__ __device__ inline float hist_margin(float po)
 
 constexpr int kLaneUnroll = 4;
 
+// Packets that held an unsure sample are not repaired inside the hot loop (any call or long branch body there
+// costs registers that the two-CTAs-per-SM budget does not have); their indices go to a small shared-memory queue
+// and the CTA repairs them together after its sweep.  About one packet in 700 is queued on ordinary data.
+constexpr int kFixQueue        = 4096;
+constexpr int kLaneHistSmem    = kLaneHistBytes + kFixQueue * (int) sizeof(uint32_t);
+
+// Repair of one queued packet: re-read it, take every unsure sample's fast-path count back out and count it with
+// the exact formula instead.
+__device__ __forceinline__ void hist_fix_packet(const float* __restrict__ x, int64_t q, uint32_t base, float rbs, float c,
+                                                float eps, float bs, float po)
+{
+    const float4 w   = __ldg(reinterpret_cast<const float4*>(x) + q);
+    const float f[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+    {
+        bool sure;
+        const uint32_t row = bucket_row_fast(f[e], rbs, c, eps, sure);
+        if (!sure)
+        {
+            lane_hist_add(base, row, -1);
+            int k;
+            if (bucket_of(f[e], bs, po, k))
+                lane_hist_add(base, (uint32_t) k, 1);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(const float* __restrict__ x, int64_t n,
                                                                             const aq_tfe_state_t* __restrict__ st,
                                                                             uint32_t* __restrict__ hist,
                                                                             int64_t* __restrict__ count)
 {
+    pdl_launch_dependents();
+    extern __shared__ uint32_t s_lane_hist[];   // [513][32] counters, then the repair queue
+    uint32_t* s_queue = s_lane_hist + kLaneHistRows * 32;
+    __shared__ uint32_t s_queued;
+    {
+        // shared-memory setup needs no global input: it overlaps the tail of the previous grid
+        uint4* z = reinterpret_cast<uint4*>(s_lane_hist);
+        for (int i = threadIdx.x; i < kLaneHistRows * 32 / 4; i += kLaneHistThreads)
+            z[i] = make_uint4(0, 0, 0, 0);
+        if (threadIdx.x == 0)
+            s_queued = 0;
+    }
+    pdl_wait();
     const int initialized = st->initialized;
     if (blockIdx.x == 0 && threadIdx.x == 0 && count)
         *count = initialized ? n : 0;
     if (!initialized)
         return;
-    extern __shared__ uint32_t s_lane_hist[];   // [513][32]
-    for (int i = threadIdx.x; i < kLaneHistRows * 32; i += kLaneHistThreads)
-        s_lane_hist[i] = 0;
     __syncthreads();
 
     const float bs = st->bucket_size, po = st->pdf_offset;
     const float margin = hist_margin(po);
     // A margin of a quarter bucket or more means the grid sits so far from zero that the reciprocal form is
-    // useless; eps <= 0 then sends every sample through the exact path.
+    // useless: eps = 0 marks every packet unsure, the queue overflows and the CTA takes the exact sweep below.
     const float eps = margin < 0.25f ? 0.5f - margin : 0.0f;
     const float rbs = __frcp_rn(bs);
     const float c   = 1.5f - po;
-    // padding sample for partial groups: above the grid and mid-bucket, so it is `sure` and lands in the trash row
+    // padding sample for the partial group: above the grid and mid-bucket, so it is `sure` and lands in the trash row
     const float pad     = (514.5f - c) * bs;
     const int lane      = threadIdx.x & 31;
     const uint32_t base = (uint32_t) __cvta_generic_to_shared(s_lane_hist + lane);
+    const float4* __restrict__ x4 = reinterpret_cast<const float4*>(x);
 
     const int64_t npack  = n / 4;
     const int64_t stride = (int64_t) gridDim.x * kLaneHistThreads;
-    // Every thread sweeps packets p, p + stride, ...; kLaneUnroll of them are in flight at once.
-    for (int64_t p = (int64_t) blockIdx.x * kLaneHistThreads + threadIdx.x; p < npack; p += kLaneUnroll * stride)
-    {
-        float4 v[kLaneUnroll];
-#pragma unroll
-        for (int u = 0; u < kLaneUnroll; ++u)
-        {
-            const int64_t q = p + u * stride;
-            v[u]            = q < npack ? __ldcs(reinterpret_cast<const float4*>(x) + q) : make_float4(pad, pad, pad, pad);
-        }
-        uint32_t unsure = 0;   // bit 4u+e: sample e of packet u needs the exact formula
-#pragma unroll
-        for (int u = 0; u < kLaneUnroll; ++u)
-        {
-            const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-            {
-                bool sure;
-                lane_hist_add(base, bucket_row_fast(f[e], rbs, c, eps, sure), 1);
-                if (!sure)
-                    unsure |= 1u << (4 * u + e);
-            }
-        }
-        while (unsure)
-        {
-            // rare (about one sample in ten thousand): take the fast-path count back out, count exactly
-            const int i = __ffs(unsure) - 1;
-            unsure &= unsure - 1;
-            const float xv = x[(p + (int64_t) (i >> 2) * stride) * 4 + (i & 3)];
-            bool dummy;
-            lane_hist_add(base, bucket_row_fast(xv, rbs, c, eps, dummy), -1);
-            int k;
-            if (bucket_of(xv, bs, po, k))
-                lane_hist_add(base, (uint32_t) k, 1);
-        }
+    // Every thread sweeps packets p, p + stride, ...; kLaneUnroll of them are in flight at once.  Full groups
+    // run without any bounds test; the last, partial group is padded.
+    int64_t p = (int64_t) blockIdx.x * kLaneHistThreads + threadIdx.x;
+#define AQ_HIST_GROUP(FULL)                                                                                          \
+    {                                                                                                                \
+        float4 v[kLaneUnroll];                                                                                       \
+        _Pragma("unroll") for (int u = 0; u < kLaneUnroll; ++u)                                                     \
+        {                                                                                                            \
+            const int64_t q = p + u * stride;                                                                        \
+            v[u]            = (FULL || q < npack) ? __ldcs(x4 + q) : make_float4(pad, pad, pad, pad);                \
+        }                                                                                                            \
+        _Pragma("unroll") for (int u = 0; u < kLaneUnroll; ++u)                                                     \
+        {                                                                                                            \
+            bool s0, s1, s2, s3;                                                                                     \
+            lane_hist_add(base, bucket_row_fast(v[u].x, rbs, c, eps, s0), 1);                                        \
+            lane_hist_add(base, bucket_row_fast(v[u].y, rbs, c, eps, s1), 1);                                        \
+            lane_hist_add(base, bucket_row_fast(v[u].z, rbs, c, eps, s2), 1);                                        \
+            lane_hist_add(base, bucket_row_fast(v[u].w, rbs, c, eps, s3), 1);                                        \
+            if (!(s0 && s1 && s2 && s3))                                                                             \
+            {                                                                                                        \
+                const uint32_t slot = atomicAdd(&s_queued, 1u);                                                      \
+                if (slot < (uint32_t) kFixQueue)                                                                     \
+                    s_queue[slot] = (uint32_t) (p + u * stride); /* pads are always sure; n <= 2^31 */               \
+            }                                                                                                        \
+        }                                                                                                            \
     }
+    for (; p + (kLaneUnroll - 1) * stride < npack; p += kLaneUnroll * stride)
+        AQ_HIST_GROUP(true)
+    if (p < npack)
+        AQ_HIST_GROUP(false)
+#undef AQ_HIST_GROUP
     if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * 4))
     {
         int k;
@@ -620,10 +658,47 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
             lane_hist_add(base, (uint32_t) k, 1);
     }
     __syncthreads();
+    const uint32_t queued = s_queued;
+    if (queued <= (uint32_t) kFixQueue)
+    {
+        for (uint32_t i = threadIdx.x; i < queued; i += kLaneHistThreads)
+            hist_fix_packet(x, (int64_t) s_queue[i], base, rbs, c, eps, bs, po);
+    }
+    else
+    {
+        // Queue overflow (adversarial data sitting on bucket boundaries): throw this CTA's counts away and redo
+        // its whole share with the exact formula.
+        __syncthreads();
+        for (int i = threadIdx.x; i < kLaneHistRows * 32; i += kLaneHistThreads)
+            s_lane_hist[i] = 0;
+        __syncthreads();
+        for (int64_t q = (int64_t) blockIdx.x * kLaneHistThreads + threadIdx.x; q < npack; q += stride)
+        {
+            const float4 w   = __ldg(x4 + q);
+            const float f[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+            {
+                int k;
+                if (bucket_of(f[e], bs, po, k))
+                    lane_hist_add(base, (uint32_t) k, 1);
+            }
+        }
+        if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * 4))
+        {
+            int k;
+            if (bucket_of(x[npack * 4 + threadIdx.x], bs, po, k))
+                lane_hist_add(base, (uint32_t) k, 1);
+        }
+    }
+    __syncthreads();
     // fold the 32 lane copies of each bucket: one warp per bucket row, conflict-free reads
     const int warp = threadIdx.x >> 5;
-    for (int b = warp; b < AQ_PDF_SIZE; b += kLaneHistThreads / 32)
+    // (CTAs walk the rows in rotated order so that they do not all hit the same global counter at the same time)
+    const int rot = (blockIdx.x * 37) & (AQ_PDF_SIZE - 1);
+    for (int j = warp; j < AQ_PDF_SIZE; j += kLaneHistThreads / 32)
     {
+        const int b      = (j + rot) & (AQ_PDF_SIZE - 1);
         const uint32_t s = __reduce_add_sync(0xffffffffu, s_lane_hist[(b << 5) + lane]);
         if (lane == 0 && s)
             atomicAdd(&hist[b], s);
@@ -678,7 +753,7 @@ int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t*
     if (!attr_set)
     {
         cudaError_t e = cudaFuncSetAttribute(tfe_hist_lane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kLaneHistBytes);
+                                             kLaneHistSmem);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(tfe_hist_lane_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                      cudaSharedmemCarveoutMaxShared);
@@ -693,7 +768,7 @@ int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t*
         blocks = cap;
     if (blocks < 1)
         blocks = 1;
-    tfe_hist_lane_kernel<<<(unsigned) blocks, kLaneHistThreads, kLaneHistBytes, stream>>>(x, n, st, hist, count);
+    launch_pdl(tfe_hist_lane_kernel, (unsigned) blocks, kLaneHistThreads, kLaneHistSmem, stream, x, n, st, hist, count);
     note_launch();
     return check_launch();
 }
