@@ -532,10 +532,14 @@ __device__ __forceinline__ uint32_t bucket_row_fast(float x, float rbs, float c,
     return min(__float_as_uint(s2) - (kTwo23Bits + 1u), (uint32_t) AQ_PDF_SIZE);
 }
 
-// counters[row][lane] += v with a 32-bit shared-window address (one LEA + one RED per sample)
-__device__ __forceinline__ void lane_hist_add(uint32_t base, uint32_t row, int v)
+// counters[row][lane] += 1 / -= 1 with a 32-bit shared-window address (one LEA + one RED per sample)
+__device__ __forceinline__ void lane_hist_inc(uint32_t base, uint32_t row)
 {
-    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"(base + (row << 7)), "r"(v));
+    asm volatile("red.shared.add.u32 [%0], 1;" ::"r"(base + (row << 7)));
+}
+__device__ __forceinline__ void lane_hist_dec(uint32_t base, uint32_t row)
+{
+    asm volatile("red.shared.add.s32 [%0], -1;" ::"r"(base + (row << 7)));
 }
 
 // Bound of |s - (t + 1.5)| for every sample whose approximate position s lies within [0, 515]:
@@ -554,7 +558,7 @@ constexpr int kLaneUnroll = 4;
 
 // Packets that held an unsure sample are not repaired inside the hot loop (any call or long branch body there
 // costs registers that the two-CTAs-per-SM budget does not have); their indices go to a small shared-memory queue
-// and the CTA repairs them together after its sweep.  About one packet in 700 is queued on ordinary data.
+// and the CTA repairs them together after its sweep.  About one group of 16 samples in 170 is queued on ordinary data.
 constexpr int kFixQueue        = 4096;
 constexpr int kLaneHistSmem    = kLaneHistBytes + kFixQueue * (int) sizeof(uint32_t);
 
@@ -572,10 +576,10 @@ __device__ __forceinline__ void hist_fix_packet(const float* __restrict__ x, int
         const uint32_t row = bucket_row_fast(f[e], rbs, c, eps, sure);
         if (!sure)
         {
-            lane_hist_add(base, row, -1);
+            lane_hist_dec(base, row);
             int k;
             if (bucket_of(f[e], bs, po, k))
-                lane_hist_add(base, (uint32_t) k, 1);
+                lane_hist_inc(base, (uint32_t) k);
         }
     }
 }
@@ -598,6 +602,15 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
             s_queued = 0;
     }
     pdl_wait();
+    {
+        // start this thread's first packets on their way from DRAM to L2 while the state is being read
+        const uint32_t np = (uint32_t) (n / 4), sd = gridDim.x * kLaneHistThreads;
+        const uint32_t p0 = blockIdx.x * kLaneHistThreads + threadIdx.x;
+#pragma unroll
+        for (int u = 0; u < kLaneUnroll; ++u)
+            if (p0 + u * sd < np)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const float4*>(x) + (p0 + u * sd)));
+    }
     const int initialized = st->initialized;
     if (blockIdx.x == 0 && threadIdx.x == 0 && count)
         *count = initialized ? n : 0;
@@ -612,57 +625,86 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
     const float eps = margin < 0.25f ? 0.5f - margin : 0.0f;
     const float rbs = __frcp_rn(bs);
     const float c   = 1.5f - po;
-    // padding sample for the partial group: above the grid and mid-bucket, so it is `sure` and lands in the trash row
-    const float pad     = (514.5f - c) * bs;
     const int lane      = threadIdx.x & 31;
     const uint32_t base = (uint32_t) __cvta_generic_to_shared(s_lane_hist + lane);
     const float4* __restrict__ x4 = reinterpret_cast<const float4*>(x);
 
-    const int64_t npack  = n / 4;
-    const int64_t stride = (int64_t) gridDim.x * kLaneHistThreads;
-    // Every thread sweeps packets p, p + stride, ...; kLaneUnroll of them are in flight at once.  Full groups
-    // run without any bounds test; the last, partial group is padded.
-    int64_t p = (int64_t) blockIdx.x * kLaneHistThreads + threadIdx.x;
-#define AQ_HIST_GROUP(FULL)                                                                                          \
+    // Packet indices fit 32 bits (n <= 2^31 elements).  Every thread sweeps packets p, p + stride, ...;
+    // kLaneUnroll of them are in flight at once; the last, partial group handles its packets one by one.
+    const uint32_t npack  = (uint32_t) (n / 4);
+    const uint32_t stride = gridDim.x * kLaneHistThreads;
+    uint32_t p            = blockIdx.x * kLaneHistThreads + threadIdx.x;
+    // Per sample: FFMA, 3 FADD, FMNMX, VIADDMNMX, LEA, RED.  `worst` collects max |g| of the group; a NaN (from a
+    // NaN / Inf sample) is dropped by fmaxf, which is fine: such a sample went to the trash row, and the exact
+    // formula drops it too.
+#define AQ_HIST_SAMPLE(X)                                                                                            \
     {                                                                                                                \
-        float4 v[kLaneUnroll];                                                                                       \
-        _Pragma("unroll") for (int u = 0; u < kLaneUnroll; ++u)                                                     \
-        {                                                                                                            \
-            const int64_t q = p + u * stride;                                                                        \
-            v[u]            = (FULL || q < npack) ? __ldcs(x4 + q) : make_float4(pad, pad, pad, pad);                \
-        }                                                                                                            \
-        _Pragma("unroll") for (int u = 0; u < kLaneUnroll; ++u)                                                     \
-        {                                                                                                            \
-            bool s0, s1, s2, s3;                                                                                     \
-            lane_hist_add(base, bucket_row_fast(v[u].x, rbs, c, eps, s0), 1);                                        \
-            lane_hist_add(base, bucket_row_fast(v[u].y, rbs, c, eps, s1), 1);                                        \
-            lane_hist_add(base, bucket_row_fast(v[u].z, rbs, c, eps, s2), 1);                                        \
-            lane_hist_add(base, bucket_row_fast(v[u].w, rbs, c, eps, s3), 1);                                        \
-            if (!(s0 && s1 && s2 && s3))                                                                             \
-            {                                                                                                        \
-                const uint32_t slot = atomicAdd(&s_queued, 1u);                                                      \
-                if (slot < (uint32_t) kFixQueue)                                                                     \
-                    s_queue[slot] = (uint32_t) (p + u * stride); /* pads are always sure; n <= 2^31 */               \
-            }                                                                                                        \
-        }                                                                                                            \
+        const float s_  = fmaf((X), rbs, c);                                                                         \
+        const float s2_ = __fadd_rd(s_, kTwo23);                                                                     \
+        worst           = fmaxf(worst, fabsf(s_ - (s2_ - 8388607.5f)));                                              \
+        lane_hist_inc(base, min(__float_as_uint(s2_) - (kTwo23Bits + 1u), (uint32_t) AQ_PDF_SIZE));                  \
     }
-    for (; p + (kLaneUnroll - 1) * stride < npack; p += kLaneUnroll * stride)
-        AQ_HIST_GROUP(true)
-    if (p < npack)
-        AQ_HIST_GROUP(false)
-#undef AQ_HIST_GROUP
-    if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * 4))
+#define AQ_HIST_PACKET(V)                                                                                            \
+    {                                                                                                                \
+        AQ_HIST_SAMPLE((V).x) AQ_HIST_SAMPLE((V).y) AQ_HIST_SAMPLE((V).z) AQ_HIST_SAMPLE((V).w)                      \
+    }
+#define AQ_HIST_QUEUE()                                                                                              \
+    if (!(worst < eps))                                                                                              \
+    {                                                                                                                \
+        const uint32_t slot = atomicAdd(&s_queued, 1u);                                                              \
+        if (slot < (uint32_t) kFixQueue)                                                                             \
+            s_queue[slot] = p;                                                                                       \
+    }
+    if (npack >= (kLaneUnroll - 1) * stride)
+    {
+        const uint32_t last_full = npack - (kLaneUnroll - 1) * stride;   // p < last_full: a full group fits
+        for (; p < last_full; p += kLaneUnroll * stride)
+        {
+            float4 v[kLaneUnroll];
+#pragma unroll
+            for (int u = 0; u < kLaneUnroll; ++u)
+                v[u] = __ldcs(x4 + (p + u * stride));
+            float worst = 0.0f;
+#pragma unroll
+            for (int u = 0; u < kLaneUnroll; ++u)
+                AQ_HIST_PACKET(v[u])
+            AQ_HIST_QUEUE()
+        }
+    }
+    {
+        // partial group: up to kLaneUnroll - 1 packets
+        float4 v[kLaneUnroll - 1];
+#pragma unroll
+        for (int u = 0; u < kLaneUnroll - 1; ++u)
+            if (p + u * stride < npack)
+                v[u] = __ldcs(x4 + (p + u * stride));
+        float worst = 0.0f;
+#pragma unroll
+        for (int u = 0; u < kLaneUnroll - 1; ++u)
+            if (p + u * stride < npack)
+                AQ_HIST_PACKET(v[u])
+        AQ_HIST_QUEUE()
+    }
+#undef AQ_HIST_SAMPLE
+#undef AQ_HIST_PACKET
+#undef AQ_HIST_QUEUE
+    if (blockIdx.x == 0 && threadIdx.x < (int) (n - (int64_t) npack * 4))
     {
         int k;
-        if (bucket_of(x[npack * 4 + threadIdx.x], bs, po, k))
-            lane_hist_add(base, (uint32_t) k, 1);
+        if (bucket_of(x[(int64_t) npack * 4 + threadIdx.x], bs, po, k))
+            lane_hist_inc(base, (uint32_t) k);
     }
     __syncthreads();
     const uint32_t queued = s_queued;
     if (queued <= (uint32_t) kFixQueue)
     {
-        for (uint32_t i = threadIdx.x; i < queued; i += kLaneHistThreads)
-            hist_fix_packet(x, (int64_t) s_queue[i], base, rbs, c, eps, bs, po);
+        // one queued group = up to kLaneUnroll packets; (entry, packet) pairs are spread over the threads
+        for (uint32_t i = threadIdx.x; i < queued * kLaneUnroll; i += kLaneHistThreads)
+        {
+            const uint32_t q = s_queue[i / kLaneUnroll] + (i % kLaneUnroll) * stride;
+            if (q < npack)
+                hist_fix_packet(x, (int64_t) q, base, rbs, c, eps, bs, po);
+        }
     }
     else
     {
@@ -672,7 +714,7 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
         for (int i = threadIdx.x; i < kLaneHistRows * 32; i += kLaneHistThreads)
             s_lane_hist[i] = 0;
         __syncthreads();
-        for (int64_t q = (int64_t) blockIdx.x * kLaneHistThreads + threadIdx.x; q < npack; q += stride)
+        for (uint32_t q = blockIdx.x * kLaneHistThreads + threadIdx.x; q < npack; q += stride)
         {
             const float4 w   = __ldg(x4 + q);
             const float f[4] = {w.x, w.y, w.z, w.w};
@@ -681,27 +723,33 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
             {
                 int k;
                 if (bucket_of(f[e], bs, po, k))
-                    lane_hist_add(base, (uint32_t) k, 1);
+                    lane_hist_inc(base, (uint32_t) k);
             }
         }
-        if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * 4))
+        if (blockIdx.x == 0 && threadIdx.x < (int) (n - (int64_t) npack * 4))
         {
             int k;
-            if (bucket_of(x[npack * 4 + threadIdx.x], bs, po, k))
-                lane_hist_add(base, (uint32_t) k, 1);
+            if (bucket_of(x[(int64_t) npack * 4 + threadIdx.x], bs, po, k))
+                lane_hist_inc(base, (uint32_t) k);
         }
     }
     __syncthreads();
-    // fold the 32 lane copies of each bucket: one warp per bucket row, conflict-free reads
-    const int warp = threadIdx.x >> 5;
-    // (CTAs walk the rows in rotated order so that they do not all hit the same global counter at the same time)
-    const int rot = (blockIdx.x * 37) & (AQ_PDF_SIZE - 1);
-    for (int j = warp; j < AQ_PDF_SIZE; j += kLaneHistThreads / 32)
+    // Fold the 32 lane copies of each bucket and add the sums to the global row.  Two threads per bucket, each
+    // sums 16 copies; the column order is rotated by the bucket index so that the 32 lanes of a warp (16 buckets
+    // x 2 halves) read 32 different banks at every step.  CTAs start at rotated buckets so that they do not all
+    // hit the same global counter at the same moment.
     {
-        const int b      = (j + rot) & (AQ_PDF_SIZE - 1);
-        const uint32_t s = __reduce_add_sync(0xffffffffu, s_lane_hist[(b << 5) + lane]);
-        if (lane == 0 && s)
-            atomicAdd(&hist[b], s);
+        const int rot  = (blockIdx.x * 37) & (AQ_PDF_SIZE - 1);
+        const int b    = ((threadIdx.x >> 1) + rot) & (AQ_PDF_SIZE - 1);
+        const int half = threadIdx.x & 1;
+        const uint32_t* row = s_lane_hist + (b << 5) + (half << 4);
+        uint32_t sum = 0;
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+            sum += row[(k + b) & 15];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        if (half == 0 && sum)
+            atomicAdd(&hist[b], sum);
     }
 }
 
