@@ -53,6 +53,7 @@ SIGNATURES = {
     "aq_v2_qdq_backward_params": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _f64, _f64, _vp]),
     "aq_minmax_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "aq_minmax": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _i32, _i32, _vp, _i64, _vp]),
+    "aq_minmax_static": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _i32, _vp]),
     "aq_tfe_init_grid": (_i32, [_vp, _vp, _vp]),
     "aq_tfe_histogram": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp]),
     "aq_tfe_pdf_replay": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp]),

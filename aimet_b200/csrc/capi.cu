@@ -342,6 +342,17 @@ int aq_minmax(const void* d_x, int dtype, int64_t n, int64_t num_ch, int64_t inn
                            workspace_bytes, (cudaStream_t) stream);
 }
 
+int aq_minmax_static(const void* d_x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* d_out_min,
+                     float* d_out_max, int propagate_nan, void* stream)
+{
+    if (bad_geom(n, num_ch, inner) || (n > 0 && !d_x) || !d_out_min || !d_out_max || dtype < AQ_F32 ||
+        dtype > AQ_BF16)
+        return AQ_ERR_INVALID_ARG;
+    if (num_ch > 1 && n / inner % num_ch != 0)
+        return AQ_ERR_INVALID_ARG;
+    return minmax_static(d_x, dtype, n, num_ch, inner, d_out_min, d_out_max, propagate_nan, (cudaStream_t) stream);
+}
+
 int aq_tfe_init_grid(const float* d_minmax, aq_tfe_state_t* d_state, void* stream)
 {
     if (!d_minmax || !d_state)

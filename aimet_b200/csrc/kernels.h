@@ -64,6 +64,8 @@ int ste_v1(SteArgs a, cudaStream_t st);
 int64_t minmax_workspace_bytes(int64_t n, int64_t num_ch, int64_t inner);
 int minmax_dispatch(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* out_min,
                     float* out_max, int propagate_nan, int accumulate, void* ws, int64_t ws_bytes, cudaStream_t st);
+int minmax_static(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* out_min, float* out_max,
+                  int propagate_nan, cudaStream_t st);
 int tfe_init_grid(const float* minmax, aq_tfe_state_t* st, cudaStream_t stream);
 int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t* hist, int64_t* count,
                   cudaStream_t stream);

@@ -451,6 +451,50 @@ int minmax_dispatch(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t
 #undef AQ_T
 }
 
+// -------------------------------------------------------------------------------------------------
+// Min/max without caller scratch.
+//
+// Some hosts of this library may not allocate device memory at the point where they need statistics: an
+// inference runtime whose memory arena was sized and frozen at start-up, an operator callback that another
+// framework runs with allocation disabled, or a process that has handed all device memory to a pool it does not
+// own.  For them the reduction scratch lives in this fixed array inside the library image.  Every GPU that loads
+// the library holds these bytes until the process exits; all calls on a device share them, so two calls that
+// overlap on the GPU (different streams) race, and the array keeps whatever the previous call left behind.
+// -------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_minmax_static_scratch[AQ_MINMAX_STATIC_SCRATCH_BYTES];
+
+int minmax_static(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* out_min, float* out_max,
+                  int propagate_nan, cudaStream_t st)
+{
+    const int64_t need = minmax_workspace_bytes(n, num_ch, inner);
+    if (need > (int64_t) AQ_MINMAX_STATIC_SCRATCH_BYTES)
+        return AQ_ERR_TOO_LARGE;
+    // In host code the array's name is only a handle; the address the kernels need comes from the runtime, once per
+    // device, with that device current.
+    constexpr int kMaxDevices = 64;
+    static void* scratch_of_device[kMaxDevices] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return cuda_fail(e);
+    if (dev < 0 || dev >= kMaxDevices)
+        return AQ_ERR_UNSUPPORTED;
+    void* scratch = scratch_of_device[dev];
+    if (!scratch)
+    {
+        e = cudaGetSymbolAddress(&scratch, g_minmax_static_scratch);
+        if (e != cudaSuccess)
+            return cuda_fail(e);
+        scratch_of_device[dev] = scratch;
+    }
+    // The whole-tensor kernel expects its ticket counter (first 256 bytes) to be zero; nothing else has to be.
+    e = cudaMemsetAsync(scratch, 0, 256, st);
+    if (e != cudaSuccess)
+        return cuda_fail(e);
+    return minmax_dispatch(x, dtype, n, num_ch, inner, out_min, out_max, propagate_nan, 0, scratch,
+                           (int64_t) AQ_MINMAX_STATIC_SCRATCH_BYTES, st);
+}
+
 // =================================================================================================
 // TF-Enhanced: bucket grid, 512-bucket histogram, PDF replay
 // =================================================================================================

@@ -205,6 +205,27 @@ int aq_minmax(const void* d_x, int dtype, int64_t n, int64_t num_ch, int64_t inn
               float* d_out_max, int propagate_nan, int accumulate, void* d_workspace, int64_t workspace_bytes,
               void* stream);
 
+/* Size of the scratch that aq_minmax_static keeps inside the library image (per GPU that loads the library). */
+#define AQ_MINMAX_STATIC_SCRATCH_BYTES (1 << 20)
+
+/* aq_minmax for callers that must not allocate device memory.  (It has no counterpart in the reference, which
+ * always allocates its scratch through an allocator callback.)  Think of an inference runtime whose device arena
+ * was sized and frozen at start-up, or an operator callback that a host framework runs with allocation switched
+ * off: such a caller has nowhere to get the workspace that aq_minmax asks for.  Here the scratch is a fixed array
+ * of AQ_MINMAX_STATIC_SCRATCH_BYTES inside the library; the caller passes only the input and the two outputs.
+ *   - Same results as aq_minmax(..., accumulate = 0, ...): one min and one max per encoding channel.
+ *   - Returns AQ_ERR_TOO_LARGE when the geometry would need more scratch than the array holds, i.e. when
+ *     aq_minmax_workspace_bytes(n, num_ch, inner) > AQ_MINMAX_STATIC_SCRATCH_BYTES (whole-tensor statistics
+ *     always fit; per-channel statistics fit up to about 130,000 (row, segment) partials).
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.  The first call on each device looks the
+ *     array's device address up (cudaGetSymbolAddress, with that device current); make that first call before
+ *     any stream capture begins.
+ *   - All calls on a device share the one array and it keeps the previous call's contents; the entry point clears
+ *     the part that has to start at zero on `stream` itself.  Calls that overlap on the GPU (different streams,
+ *     no ordering between them) race on the scratch: serialise them. */
+int aq_minmax_static(const void* d_x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* d_out_min,
+                     float* d_out_max, int propagate_nan, void* stream);
+
 /* Builds the bucket grid from a batch's (min,max) held on the device; leaves the state un-initialised when both
  * are zero.  Replaces the first-batch branch of UpdatePdf and InitializePdf<float>
  * (src/math_functions.cpp:207-262).  d_minmax: {min, max} floats on the device.  No-op if already initialised. */
