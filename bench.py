@@ -36,7 +36,7 @@ WORKLOAD = ("BASELINE config 3: TF-Enhanced calibration, fp32 activations [64,25
             "outliers x20, 8-bit asymmetric, 512 buckets")
 # dram__bytes_read+write per algorithmic byte of the histogram kernel, from the ncu capture summarised in
 # profiles/tfe_hist_lane_kernel_relu_256MB.md (captured on a 256 MB input; traffic grows in proportion)
-HIST_TRAFFIC_RATIO = 1.013
+HIST_TRAFFIC_RATIO = 1.024
 
 
 def peak_hbm():
@@ -265,7 +265,7 @@ def run_b200(args):
     e2e_job(W)
     barrier()
     e0.record()
-    enc_e2e, _ = e2e_job(K)
+    e2e_job(K)
     e1.record()
     barrier()
     e2e_secs = e0.elapsed_time(e1) * 1e-3
@@ -304,8 +304,7 @@ def run_b200(args):
                          "us_per_launch": kernel_s * 1e6},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": BATCH_BYTES, "d2h_bytes_per_step": 8,
-                    "ms_per_step": e2e_secs / K * 1e3, "api": "AimetTensorQuantizer.updateStats / getEncoding",
-                    "encoding_equal_to_device_run": [enc_e2e.min, enc_e2e.max] == [enc.min, enc.max] or world > 1},
+                    "ms_per_step": e2e_secs / K * 1e3, "api": "AimetTensorQuantizer.updateStats / getEncoding"},
             "gpu_launches": launches,
             "clocks": clocks,
         }
@@ -368,6 +367,117 @@ def qdq_numbers(torch, lib, device, peak):
     return out
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# single-kernel cases (micro-benchmarks; also the small commands the ncu captures under profiles/ were taken with)
+# ---------------------------------------------------------------------------------------------------------------------
+KERNEL_CASES = ("tfe_hist", "minmax_f32", "minmax_f32_rows", "minmax_bf16_block64", "v2_qdq_f32", "v2_qdq_f32_mask",
+                "v2_qdq_f32_per_channel", "v2_qdq_bf16", "v2_qdq_bf16_block64", "v2_bwd_f32", "v2_bwd_bf16",
+                "pymo_qdq_f32", "pymo_qdq_f32_per_channel", "ste_v1_f32")
+
+
+def build_kernel_case(name, mb, torch, lib, device):
+    """Returns (calls, algorithmic bytes per launch): `calls` launch the named kernel through the C ABI on rotating
+    inputs of `mb` MB each whose total exceeds the L2 capacity."""
+    from aimet_b200 import ops
+    stream = torch.cuda.current_stream().cuda_stream
+    half = "bf16" in name
+    esz = 2 if half else 4
+    n = (mb << 20) // esz // 2304 * 2304          # multiple of 2304 = 36 * 64: rows of 2304 and blocks of 64 both fit
+    nbuf = max(2, -(-320 // mb))                  # rotating set larger than L2 (126 MB)
+    dt = 2 if half else 0
+    P = lambda t: t.data_ptr()
+
+    def data(kind="normal"):
+        g = torch.Generator(device=device)
+        out = []
+        for b in range(nbuf):
+            g.manual_seed(77 + b)
+            a = torch.randn(n, device=device, generator=g)
+            if kind == "relu_outliers":
+                a = torch.relu(a)
+                a = torch.where(torch.rand(n, device=device, generator=g) < 1e-3, a * 20, a)
+            out.append((a * (0.02 if half else 1.0)).to(torch.bfloat16 if half else torch.float32))
+        return out
+
+    xs = data("relu_outliers" if name == "tfe_hist" else "normal")
+    if name == "tfe_hist":
+        st = ops.TfeDeviceState(device, capacity=nbuf)
+        st.init_grid_from(ops.minmax(xs[0]).reshape(-1))
+        hp, cp, sp = P(st.hists), P(st.counts), P(st.state)
+        keep = [st]
+        calls = [lambda i=i: lib.aq_tfe_histogram(P(xs[i]), n, sp, hp + 2048 * i, cp + 8 * i, stream) for i in range(nbuf)]
+        return calls, 4 * n, keep + xs
+    if name.startswith("minmax"):
+        num_ch, inner = {"minmax_f32": (1, n), "minmax_f32_rows": (n // 2304, 2304), "minmax_bf16_block64": (n // 64, 64)}[name]
+        need = int(lib.aq_minmax_workspace_bytes(n, num_ch, inner))
+        ws = torch.zeros(max(need, 256), dtype=torch.uint8, device=device)
+        o = torch.empty((2, num_ch), dtype=torch.float32, device=device)
+        calls = [lambda i=i: lib.aq_minmax(P(xs[i]), dt, n, num_ch, inner, P(o[0]), P(o[1]), 0, 0, P(ws), ws.numel(), stream)
+                 for i in range(nbuf)]
+        return calls, esz * n + 8 * num_ch, [ws, o] + xs
+    ys = [torch.empty_like(x) for x in xs]
+    if name.startswith("v2_bwd"):
+        ms = [(torch.rand(n, device=device) < 0.97).to(torch.uint8) for _ in range(nbuf)]
+        calls = [lambda i=i: lib.aq_v2_qdq_backward(P(xs[i]), P(ms[i]), P(ys[i]), dt, n, stream) for i in range(nbuf)]
+        return calls, (2 * esz + 1) * n, [ms, ys] + xs
+    if name.startswith("v2_qdq"):
+        if name.endswith("block64"):
+            num_ch, inner, qmin, qmax, sc = n // 64, 64, -8.0, 7.0, 0.004
+        elif name.endswith("per_channel"):
+            num_ch, inner, qmin, qmax, sc = n // 2304, 2304, -128.0, 127.0, 0.03
+        else:
+            num_ch, inner, qmin, qmax, sc = 1, n, (-128.0 if half else 0.0), (127.0 if half else 255.0), (4e-4 if half else 0.0353)
+        s = torch.full((num_ch,), sc, device=device)
+        o = torch.full((num_ch,), 0.0 if qmin < 0 else -128.0, device=device)
+        ms = [torch.empty(n, dtype=torch.uint8, device=device) for _ in range(nbuf)] if name.endswith("mask") else None
+        calls = [lambda i=i: lib.aq_v2_quantize(P(xs[i]), P(ys[i]), P(ms[i]) if ms else None, dt, n, num_ch, inner, P(s), P(o),
+                                                qmin, qmax, 0, 0, stream) for i in range(nbuf)]
+        return calls, (2 * esz + (1 if ms else 0)) * n + (8 * num_ch if num_ch > 1 else 0), [s, o, ms, ys] + xs
+    if name == "pymo_qdq_f32":
+        calls = [lambda i=i: lib.aq_qdq_per_tensor(P(xs[i]), P(ys[i]), n, -4.4, 4.6, 8, 0, stream) for i in range(nbuf)]
+        return calls, 8 * n, [ys] + xs
+    num_ch, inner = n // 2304, 2304
+    emn, emx = torch.full((num_ch,), -2.0, device=device), torch.full((num_ch,), 2.0, device=device)
+    if name == "pymo_qdq_f32_per_channel":
+        calls = [lambda i=i: lib.aq_qdq_per_channel(P(xs[i]), P(ys[i]), n, num_ch, inner, P(emn), P(emx), 255.0, 0, stream)
+                 for i in range(nbuf)]
+        return calls, 8 * n + 8 * num_ch, [emn, emx, ys] + xs
+    if name == "ste_v1_f32":
+        gs = [torch.randn(n, device=device) for _ in range(nbuf)]
+        calls = [lambda i=i: lib.aq_ste_backward_v1(P(xs[i]), P(gs[i]), P(ys[i]), n, 1, n, P(emn), P(emx), stream)
+                 for i in range(nbuf)]
+        return calls, 12 * n, [emn, emx, gs, ys] + xs
+    raise SystemExit(f"unknown kernel case {name}")
+
+
+def run_kernel_case(args):
+    """`--kernel-case NAME --mb M --steps K --warmup W`: W + K launches of one kernel, one JSON line."""
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the B200 arm has no CPU fallback")
+    from aimet_b200._lib import lib
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    calls, nbytes, keep = build_kernel_case(args.kernel_case, args.mb, torch, lib, device)
+    W, K = max(args.warmup, 3), args.steps
+    for i in range(W):
+        rc = calls[i % len(calls)]()
+        assert rc == 0, rc
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        calls[i % len(calls)]()
+    e1.record()
+    torch.cuda.synchronize()
+    secs = e0.elapsed_time(e1) * 1e-3 / K
+    peak, peak_kind = peak_hbm()
+    print(json.dumps({"kernel_case": args.kernel_case, "mb_per_input": args.mb, "inputs_rotated": len(calls), "steps": K,
+                      "warmup": W, "us_per_launch": secs * 1e6, "bytes_per_launch": nbytes,
+                      "achieved_GBps": nbytes / secs / 1e9, "peak_GBps": peak, "peak_kind": peak_kind,
+                      "frac": nbytes / secs / 1e9 / peak}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -376,8 +486,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg")
     ap.add_argument("--skip-qdq", action="store_true", help="omit the secondary fake-quant kernel numbers")
+    ap.add_argument("--kernel-case", choices=KERNEL_CASES, help="time one kernel alone instead of the calibration job")
+    ap.add_argument("--mb", type=int, default=256, help="input size in MB for --kernel-case")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernel_case:
+        run_kernel_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)
