@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libaimet_b200.so")
+#: the in-tree build, unless AIMET_B200_LIB names another build of the same library
+LIB_PATH = os.environ.get("AIMET_B200_LIB") or os.path.join(_HERE, "lib", "libaimet_b200.so")
 
 AQ_OK = 0
 AQ_F32, AQ_F16, AQ_BF16 = 0, 1, 2

@@ -143,21 +143,26 @@ class TfEnhancedCalibrator:
             # the tables were exchanged by an earlier call; every rank already holds all rows
             enc = eng.encoding(self._merged, bw, symmetric, strict, unsigned_sym)
         elif self.distributed:
+            # One exchange: a zero-padded int32 buffer holding [n_total, 512] histogram rows, then the n_total int64
+            # counts (as int32 pairs), then the number of ranks that saw data.  Every row is non-zero on exactly one
+            # rank, so the element-wise integer sum reproduces each row and each 64-bit count exactly.  n_total needs
+            # no agreement step: all ranks have called update() the same number of times.
             dev = self.device
             n_local = eng.num_rows()
-            total = torch.tensor([self.round * self.world, int(self.updated)], dtype=torch.int64, device=dev)
-            dist.all_reduce(total, op=dist.ReduceOp.MAX, group=self.group)
-            n_total, any_updated = int(total[0]), bool(total[1])
-            hists = torch.zeros((n_total, 512), dtype=torch.int32, device=dev)
-            counts = torch.zeros(n_total, dtype=torch.int64, device=dev)
+            n_total = self.round * self.world
+            buf = torch.zeros(n_total * 514 + 2, dtype=torch.int32, device=dev)
+            hists = buf[:n_total * 512].view(n_total, 512)
+            counts = buf[n_total * 512:n_total * 514].view(torch.int64)
             if n_local:
                 idx = torch.tensor(self.local_global_index, dtype=torch.int64, device=dev)
                 h, c = eng.rows()
                 hists.index_copy_(0, idx, h)
                 counts.index_copy_(0, idx, c)
-            dist.all_reduce(hists, op=dist.ReduceOp.SUM, group=self.group)
-            dist.all_reduce(counts, op=dist.ReduceOp.SUM, group=self.group)
+            if self.updated:
+                buf[-2:].fill_(1)
+            dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
             eng.load_rows(hists, counts)
+            any_updated = bool(buf[-1].item())
             self._merged = any_updated   # statistics are final from here on (further update() calls are not merged)
             enc = eng.encoding(any_updated, bw, symmetric, strict, unsigned_sym).clone()
             dist.broadcast(enc, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,

@@ -153,9 +153,21 @@ struct ChanGeom
     uint32_t magic;   // ceil(2^32 / inner) when 1 < inner < 2^16, else 0
     int mode;         // 0: inner == 1 (run = local offset), 1: magic multiply, 2: inner so large that a chunk
                       //    meets at most two runs (compare)
+    // exact division of a 32-bit value by inner / num_ch with one 64-bit multiply-high: ceil(2^64 / d) for d > 1
+    // (0 stands for d == 1).  Only used when the tensor has fewer than 2^32 elements (`small`).
+    uint64_t inner_m64, ch_m64;
+    int small;
 };
 
-inline ChanGeom make_geom(int64_t num_ch, int64_t inner, int64_t chunk)
+inline uint64_t magic64(int64_t d)
+{
+    if (d <= 1)
+        return 0;
+    const unsigned __int128 one = (unsigned __int128) 1 << 64;
+    return (uint64_t) ((one + (unsigned __int128) d - 1) / (unsigned __int128) d);
+}
+
+inline ChanGeom make_geom(int64_t num_ch, int64_t inner, int64_t chunk, int64_t n = -1)
 {
     ChanGeom g;
     g.inner  = inner;
@@ -172,16 +184,23 @@ inline ChanGeom make_geom(int64_t num_ch, int64_t inner, int64_t chunk)
         g.mode  = 1;
         g.magic = (uint32_t) ((0x100000000ull + (uint64_t) inner - 1) / (uint64_t) inner);
     }
+    g.small     = (n >= 0 && (uint64_t) n <= 0xffffffffull) ? 1 : 0;
+    g.inner_m64 = magic64(inner);
+    g.ch_m64    = magic64(num_ch);
     return g;
 }
 
+// floor(v / d) for v < 2^32 and 1 <= d < 2^32, m = magic64(d): v * (m * d - 2^64) < 2^64 keeps the product's error
+// below one step of 1 / d.
+__device__ __forceinline__ uint32_t div_m64(uint32_t v, uint64_t m)
+{
+    return m ? (uint32_t) __umul64hi((uint64_t) v, m) : v;
+}
+
+// Run index of local offset `loc` (< inner + chunk) for modes 0 and 1.
 __device__ __forceinline__ uint32_t local_run(const ChanGeom& g, uint32_t loc)
 {
-    if (g.mode == 1)
-        return __umulhi(loc, g.magic);
-    if (g.mode == 2)
-        return loc >= (uint32_t) g.inner ? 1u : 0u;   // only reached when inner < 2^32 (loc < inner + chunk)
-    return loc;
+    return g.mode == 1 ? __umulhi(loc, g.magic) : loc;
 }
 
 }   // namespace aq

@@ -20,13 +20,21 @@ namespace aq
 {
 
 constexpr int kThreads = 256;
-constexpr int kUnroll  = 4;
+#ifndef AQ_UNROLL8
+#define AQ_UNROLL8 2
+#endif
+// 16-byte packets in flight per thread, by packet width in elements (8 = 16-bit types)
+template <int VEC>
+__host__ __device__ constexpr int unroll_of()
+{
+    return VEC == 8 ? AQ_UNROLL8 : 4;
+}
 constexpr int kMaxRuns = 1026;   // chunk / inner + 2 with VEC | inner  (see make_geom)
 
 template <int VEC>
 __host__ __device__ constexpr int chunk_elems()
 {
-    return kThreads * VEC * kUnroll;
+    return kThreads * VEC * unroll_of<VEC>();
 }
 
 constexpr float kMagicRne = 12582912.0f;               // 1.5 * 2^23: (t + M) - M == rint(t) for |t| < 2^22
@@ -41,25 +49,52 @@ struct RunCtx
     int64_t r0;     // index of the first run met by this CTA
     int64_t loc0;   // offset of the CTA's first element inside run r0
     int nruns;      // runs met by this CTA
+    int64_t ch0;    // channel of run r0
 };
 
+// Integer divisions below run once per CTA but in every thread; tensors below 2^32 elements replace them by one
+// multiply-high each (a 64-bit division costs about as many instructions as a thread's whole element work).
 template <int VEC>
 __device__ __forceinline__ RunCtx make_run_ctx(const ChanGeom& g, int64_t base, int64_t n)
 {
     RunCtx c;
-    c.r0              = base / g.inner;
+    if (g.small)
+        c.r0 = (int64_t) div_m64((uint32_t) base, g.inner_m64);
+    else
+        c.r0 = base / g.inner;
     c.loc0            = base - c.r0 * g.inner;
     int64_t remaining = n - base;
     int64_t span      = remaining < (int64_t) chunk_elems<VEC>() ? remaining : (int64_t) chunk_elems<VEC>();
-    c.nruns           = (int) ((c.loc0 + span - 1) / g.inner) + 1;
+    if (g.mode == 2)
+        c.nruns = (c.loc0 + span - 1 >= g.inner) ? 2 : 1;
+    else
+        c.nruns = (int) local_run(g, (uint32_t) (c.loc0 + span - 1)) + 1;
+    if (g.small)
+        c.ch0 = (int64_t) ((uint32_t) c.r0 - div_m64((uint32_t) c.r0, g.ch_m64) * (uint32_t) g.num_ch);
+    else
+        c.ch0 = c.r0 % g.num_ch;
     return c;
+}
+
+// Channel of the lr-th run met by the CTA (lr < kMaxRuns).
+__device__ __forceinline__ int64_t run_channel(const ChanGeom& g, const RunCtx& c, int lr)
+{
+    int64_t ch = c.ch0 + lr;
+    if (ch >= g.num_ch)
+    {
+        ch -= g.num_ch;
+        if (ch >= g.num_ch)
+            ch = ((uint64_t) ch <= 0xffffffffull) ? (int64_t) ((uint32_t) ch % (uint32_t) g.num_ch) : ch % g.num_ch;
+    }
+    return ch;
 }
 
 __device__ __forceinline__ uint32_t run_of(const ChanGeom& g, const RunCtx& c, uint32_t off)
 {
-    if (g.mode == 2)
-        return (c.loc0 + (int64_t) off) >= g.inner ? 1u : 0u;
-    return local_run(g, (uint32_t) c.loc0 + off);
+    // branch-free; mode 2 compares in 64 bits because inner may exceed 2^32 there
+    const uint32_t loc        = (uint32_t) c.loc0 + off;
+    const uint32_t by_compare = (c.loc0 + (int64_t) off >= g.inner) ? 1u : 0u;
+    return g.mode == 1 ? __umulhi(loc, g.magic) : (g.mode == 2 ? by_compare : loc);
 }
 
 template <>
@@ -139,15 +174,56 @@ __device__ __forceinline__ float clamp_keep_nan(float r, float lo, float hi)
     return q;
 }
 
+// -------------------------------------------------------------------------------------------------
+// Two fp32 lanes per instruction (sm_100 add/sub/mul.f32x2, round-to-nearest, no flush): the 16-bit kernels carry
+// twice the elements per byte and are issue-bound with one lane per instruction.
+// -------------------------------------------------------------------------------------------------
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t pair(float lo, float hi)
+{
+    f32x2_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpair(f32x2_t v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2_t mul2(f32x2_t a, f32x2_t b)
+{
+    f32x2_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2_t add2(f32x2_t a, f32x2_t b)
+{
+    f32x2_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2_t sub2(f32x2_t a, f32x2_t b)
+{
+    f32x2_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// max(a, |b|, |c|), NaN if any operand is NaN
+__device__ __forceinline__ float max3_abs_nan(float a, float b, float c)
+{
+    float r;
+    asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(fabsf(b)), "f"(fabsf(c)));
+    return r;
+}
+
 // =================================================================================================
 // Chunk load / store
 // =================================================================================================
-template <typename T, int VEC>
-__device__ __forceinline__ void load_chunk(const T* __restrict__ x, int64_t base, int64_t n, Pack<T, VEC> (&v)[kUnroll],
-                                           bool (&full)[kUnroll])
+template <typename T, int VEC, int U>
+__device__ __forceinline__ void load_chunk(const T* __restrict__ x, int64_t base, int64_t n, Pack<T, VEC> (&v)[U],
+                                           bool (&full)[U])
 {
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
+    for (int u = 0; u < U; ++u)
     {
         const int64_t idx = base + (int64_t) (u * kThreads + threadIdx.x) * VEC;
         full[u]           = idx + VEC <= n;
@@ -264,13 +340,17 @@ __global__ void __launch_bounds__(kThreads) pymo_qdq_kernel(PymoArgs a)
     constexpr int CHUNK = chunk_elems<VEC>();
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
     __shared__ PymoSlot s_slot[PER_CH ? kMaxRuns : 1];
-    RunCtx rc {0, 0, 1};
+    RunCtx rc {0, 0, 1, 0};
     PymoSlot k0;
+    // the element loads go out first; the encodings are staged while they are in flight
+    Pack<float, VEC> v[unroll_of<VEC>()];
+    bool full[unroll_of<VEC>()];
+    load_chunk<float, VEC, unroll_of<VEC>()>(a.in, base, a.n, v, full);
     if (PER_CH)
     {
         rc = make_run_ctx<VEC>(a.geom, base, a.n);
         for (int lr = threadIdx.x; lr < rc.nruns; lr += kThreads)
-            s_slot[lr] = pymo_load(a, (rc.r0 + lr) % a.geom.num_ch);
+            s_slot[lr] = pymo_load(a, run_channel(a.geom, rc, lr));
         __syncthreads();
     }
     else
@@ -279,12 +359,8 @@ __global__ void __launch_bounds__(kThreads) pymo_qdq_kernel(PymoArgs a)
         pymo_finish(k0);
     }
     const float shift = a.shift;
-
-    Pack<float, VEC> v[kUnroll];
-    bool full[kUnroll];
-    load_chunk<float, VEC>(a.in, base, a.n, v, full);
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
+    for (int u = 0; u < unroll_of<VEC>(); ++u)
     {
         const uint32_t off = (uint32_t) (u * kThreads + threadIdx.x) * VEC;
         PymoSlot k         = k0;
@@ -316,7 +392,7 @@ static int launch_pymo(PymoArgs a, int vec, bool codes, cudaStream_t st)
         return AQ_OK;
 #define AQ_LAUNCH(V)                                                                                                 \
     {                                                                                                                \
-        a.geom       = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>());                                     \
+        a.geom       = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>(), a.n);                                     \
         int64_t grid = (a.n + chunk_elems<V>() - 1) / chunk_elems<V>();                                              \
         if (codes)                                                                                                   \
             launch_pdl(pymo_qdq_kernel<V, PER_CH, true>, (unsigned) grid, kThreads, 0, st, a);                                 \
@@ -404,16 +480,20 @@ struct V2Slot
 // RN(x/s) and RN(x * RN(1/s)) differ by at most 3 ulp of the quotient t.  Wherever the rounded value can matter
 // (within one step of the clamp range) |t| <= T = max(|qmin + o|, |qmax + o|) + 1, so a guard band of
 // 4 ulp(T) = 2^-22 T around every half-integer is enough; outside that range both forms clamp to the same bound.
-__device__ __forceinline__ V2Slot v2_load(const float* scale, const float* offset, int64_t ch, float qmin, float qmax)
+__device__ __forceinline__ V2Slot v2_slot(float s, float o, float qmin, float qmax)
 {
     V2Slot k;
-    k.s  = scale[ch];
-    k.o  = offset[ch];
+    k.s  = s;
+    k.o  = o;
     k.rs = __frcp_rn(k.s);
     const float T      = fmaxf(fabsf(__fadd_rn(qmin, k.o)), fabsf(__fadd_rn(qmax, k.o))) + 1.0f;
     const float margin = 4.0f * kUlp24 * T;
     k.eps              = (margin < 0.25f) ? 0.5f - margin : 0.0f;   // NaN -> 0: always the exact path
     return k;
+}
+__device__ __forceinline__ V2Slot v2_load(const float* scale, const float* offset, int64_t ch, float qmin, float qmax)
+{
+    return v2_slot(scale[ch], offset[ch], qmin, qmax);
 }
 
 // Reference formula for one packet (also the only path when intermediates are kept in the storage dtype).
@@ -446,38 +526,60 @@ __device__ __forceinline__ void v2_exact_packet(const float (&x)[VEC], float (&y
 }
 
 // MODE: 0 = fast fp32-internal quantize(-dequantize); 1 = exact / narrow-internal quantize(-dequantize); 2 = dequantize
-template <typename T, int VEC, bool PER_CH, int MODE, bool NARROW, bool CODES, bool MASK>
+// PER_CH: 0 = one encoding; 1 = the encodings of the runs met by the CTA are staged in shared memory (few, long
+// runs); 2 = every packet fetches its own encoding (many short runs per tile, e.g. blocks of 64: staging would cost
+// a barrier and a slot per run, the direct loads go out together with the element loads and hit the same lines
+// from neighbouring lanes).
+template <typename T, int VEC, int PER_CH, int MODE, bool NARROW, bool CODES, bool MASK>
 __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
 {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int CHUNK = chunk_elems<VEC>();
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
+    const int64_t hi    = a.n;
     const float qmin = a.qmin, qmax = a.qmax;
-    __shared__ V2Slot s_slot[PER_CH ? kMaxRuns : 1];
-    RunCtx rc {0, 0, 1};
+    __shared__ V2Slot s_slot[PER_CH == 1 ? kMaxRuns : 1];
+    RunCtx rc {0, 0, 1, 0};
     V2Slot k0;
-    if (PER_CH)
+    float sc_u[unroll_of<VEC>()], of_u[unroll_of<VEC>()];
+    if (!PER_CH)
+        k0 = v2_load(a.scale, a.offset, 0, qmin, qmax);
+    // per channel: the element loads go out first and the encodings are fetched while they are in flight
+    Pack<T, VEC> v[unroll_of<VEC>()];
+    bool full[unroll_of<VEC>()];
+    load_chunk<T, VEC, unroll_of<VEC>()>(static_cast<const T*>(a.x), base, hi, v, full);
+    if (PER_CH == 1)
     {
-        rc = make_run_ctx<VEC>(a.geom, base, a.n);
+        rc = make_run_ctx<VEC>(a.geom, base, hi);
         for (int lr = threadIdx.x; lr < rc.nruns; lr += kThreads)
-            s_slot[lr] = v2_load(a.scale, a.offset, (rc.r0 + lr) % a.geom.num_ch, qmin, qmax);
+            s_slot[lr] = v2_load(a.scale, a.offset, run_channel(a.geom, rc, lr), qmin, qmax);
         __syncthreads();
     }
-    else
-        k0 = v2_load(a.scale, a.offset, 0, qmin, qmax);
-
-    Pack<T, VEC> v[kUnroll];
-    bool full[kUnroll];
-    load_chunk<T, VEC>(static_cast<const T*>(a.x), base, a.n, v, full);
+    if (PER_CH == 2)
+    {
+        rc = make_run_ctx<VEC>(a.geom, base, hi);
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
+        for (int u = 0; u < unroll_of<VEC>(); ++u)
+        {
+            const uint32_t off = (uint32_t) (u * kThreads + threadIdx.x) * VEC;
+            int64_t ch         = 0;
+            if (base + off < hi)
+                ch = run_channel(a.geom, rc, (int) run_of(a.geom, rc, off));
+            sc_u[u] = __ldg(a.scale + ch);
+            of_u[u] = __ldg(a.offset + ch);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < unroll_of<VEC>(); ++u)
     {
         const uint32_t off = (uint32_t) (u * kThreads + threadIdx.x) * VEC;
         const int64_t idx  = base + off;
         V2Slot k           = k0;
-        if (PER_CH)
+        if (PER_CH == 1)
             k = s_slot[run_of(a.geom, rc, off)];
+        if (PER_CH == 2)
+            k = v2_slot(sc_u[u], of_u[u], qmin, qmax);
         float x[VEC], y[VEC];
         uint8_t m[VEC];
         unpack<T, VEC>(v[u], x);
@@ -498,36 +600,59 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
         else
         {
             bool ok = true;
-#pragma unroll
-            for (int e = 0; e < VEC; ++e)
+            if (VEC == 1)
             {
-                const float t = __fmul_rn(x[e], k.rs);
+                const float t = __fmul_rn(x[0], k.rs);
                 float r       = __fsub_rn(__fadd_rn(t, kMagicRne), kMagicRne);
-                ok            = ok && (fabsf(__fsub_rn(t, r)) < k.eps);   // false for NaN / Inf
+                ok            = fabsf(__fsub_rn(t, r)) < k.eps;   // false for NaN / Inf
                 r             = __fsub_rn(r, k.o);
                 const float q = clamp_keep_nan(r, qmin, qmax);
                 if (MASK)
-                    m[e] = (q == r) ? 1 : 0;
-                y[e] = CODES ? q : __fmul_rn(__fadd_rn(q, k.o), k.s);
+                    m[0] = (q == r) ? 1 : 0;
+                y[0] = CODES ? q : __fmul_rn(__fadd_rn(q, k.o), k.s);
+            }
+            else
+            {
+                const f32x2_t rs2 = pair(k.rs, k.rs), o2 = pair(k.o, k.o), s2 = pair(k.s, k.s);
+                const f32x2_t magic = pair(kMagicRne, kMagicRne);
+                float worst = 0.0f;   // largest distance of a product from its rounded value; NaN for NaN / Inf
+#pragma unroll
+                for (int e = 0; e + 1 < VEC; e += 2)
+                {
+                    const f32x2_t t = mul2(pair(x[e], x[e + 1]), rs2);
+                    f32x2_t r       = sub2(add2(t, magic), magic);
+                    float d0, d1, r0, r1;
+                    unpair(sub2(t, r), d0, d1);
+                    worst = max3_abs_nan(worst, d0, d1);
+                    unpair(sub2(r, o2), r0, r1);
+                    const float q0 = clamp_keep_nan(r0, qmin, qmax), q1 = clamp_keep_nan(r1, qmin, qmax);
+                    if (MASK)
+                        m[e] = (q0 == r0) ? 1 : 0, m[e + 1] = (q1 == r1) ? 1 : 0;
+                    if (CODES)
+                        y[e] = q0, y[e + 1] = q1;
+                    else
+                        unpair(mul2(add2(pair(q0, q1), o2), s2), y[e], y[e + 1]);
+                }
+                ok = worst < k.eps;
             }
             if (!ok)
                 v2_exact_packet<T, VEC, false, CODES>(x, y, m, k, qmin, qmax);
         }
         Pack<T, VEC> r;
         repack<T, VEC>(y, r);
-        store_packet<T, VEC>(static_cast<T*>(a.y), idx, a.n, r, full[u]);
+        store_packet<T, VEC>(static_cast<T*>(a.y), idx, hi, r, full[u]);
         if (MASK)
         {
             Pack<uint8_t, VEC> mp;
 #pragma unroll
             for (int e = 0; e < VEC; ++e)
                 mp.v[e] = m[e];
-            store_packet<uint8_t, VEC>(a.mask, idx, a.n, mp, full[u]);
+            store_packet<uint8_t, VEC>(a.mask, idx, hi, mp, full[u]);
         }
     }
 }
 
-template <typename T, int VEC, bool PER_CH>
+template <typename T, int VEC, int PER_CH>
 static void launch_v2_variant(const V2Args& a, bool narrow, cudaStream_t st)
 {
     const int64_t grid = (a.n + chunk_elems<VEC>() - 1) / chunk_elems<VEC>();
@@ -561,10 +686,14 @@ static void launch_v2_variant(const V2Args& a, bool narrow, cudaStream_t st)
 template <typename T, bool PER_CH>
 static int launch_v2_vec(V2Args a, int vec, bool narrow, cudaStream_t st)
 {
+    // more than 16 runs per tile: per-packet encoding loads instead of shared-memory staging
 #define AQ_LAUNCH(V)                                                                                                 \
     {                                                                                                                \
-        a.geom = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>());                                           \
-        launch_v2_variant<T, V, PER_CH>(a, narrow, st);                                                              \
+        a.geom = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>(), a.n);                                      \
+        if (PER_CH && a.geom.inner * 16 < chunk_elems<V>())                                                          \
+            launch_v2_variant<T, V, PER_CH ? 2 : 0>(a, narrow, st);                                                  \
+        else                                                                                                         \
+            launch_v2_variant<T, V, PER_CH ? 1 : 0>(a, narrow, st);                                                  \
     }
     if (sizeof(T) == 2 && vec == 8)
         AQ_LAUNCH((sizeof(T) == 2 ? 8 : 4))
@@ -607,7 +736,26 @@ int v2_launch(V2Args a, int dtype, int narrow_internal, cudaStream_t st)
 // Backward kernels
 // -------------------------------------------------------------------------------------------------
 
-// v2: dx = grad * mask  (torch_builtins.py:342)
+template <typename T>
+struct PairOf
+{
+    using type                       = float2;
+    static constexpr uint32_t one_bits = 0;
+};
+template <>
+struct PairOf<__half>
+{
+    using type                       = __half2;
+    static constexpr uint32_t one_bits = 0x3c00u;
+};
+template <>
+struct PairOf<__nv_bfloat16>
+{
+    using type                       = __nv_bfloat162;
+    static constexpr uint32_t one_bits = 0x3f80u;
+};
+
+// v2: dx = grad * mask  (torch_builtins.py:342).  Mask bytes are 0 or 1 (as aq_v2_quantize writes them).
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kThreads) v2_bwd_kernel(const T* __restrict__ g, const uint8_t* __restrict__ mask,
                                                           T* __restrict__ dx, int64_t n)
@@ -616,25 +764,46 @@ __global__ void __launch_bounds__(kThreads) v2_bwd_kernel(const T* __restrict__ 
     pdl_wait();
     constexpr int CHUNK = chunk_elems<VEC>();
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
-    Pack<T, VEC> v[kUnroll];
-    Pack<uint8_t, VEC> m[kUnroll];
-    bool full[kUnroll];
-    load_chunk<T, VEC>(g, base, n, v, full);
-    load_chunk<uint8_t, VEC>(mask, base, n, m, full);
+    Pack<T, VEC> v[unroll_of<VEC>()];
+    Pack<uint8_t, VEC> m[unroll_of<VEC>()];
+    bool full[unroll_of<VEC>()];
+    load_chunk<T, VEC, unroll_of<VEC>()>(g, base, n, v, full);
+    load_chunk<uint8_t, VEC, unroll_of<VEC>()>(mask, base, n, m, full);
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
+    for (int u = 0; u < unroll_of<VEC>(); ++u)
     {
         const int64_t idx = base + (int64_t) (u * kThreads + threadIdx.x) * VEC;
-        float f[VEC];
-        unpack<T, VEC>(v[u], f);
-#pragma unroll
-        for (int e = 0; e < VEC; ++e)
-        {
-            // grad * bool: x*1 and x*0 are exact in any dtype (-0 and NaN behave as in the reference product)
-            f[e] = __fmul_rn(f[e], m[u].v[e] ? 1.0f : 0.0f);
-        }
         Pack<T, VEC> r;
-        repack<T, VEC>(f, r);
+        if constexpr (sizeof(T) == 2 && VEC == 8)
+        {
+            // grad * bool with two lanes per instruction: the 0 / 1 mask bytes of a pair are spread to 16-bit lanes
+            // and scaled to the bit pattern of 1.0, then one packed multiply in the storage type (x * 1 and x * 0
+            // are exact there, and -0 / Inf / NaN behave as in the reference product).
+            using T2            = typename PairOf<T>::type;
+            const uint32_t one  = PairOf<T>::one_bits;
+            const uint32_t* mw  = reinterpret_cast<const uint32_t*>(&m[u]);
+            const uint32_t* gw  = reinterpret_cast<const uint32_t*>(&v[u]);
+            uint32_t* rw        = reinterpret_cast<uint32_t*>(&r);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+            {
+                const uint32_t sel = __byte_perm(mw[j >> 1], 0u, (j & 1) ? 0x4342u : 0x4140u) * one;
+                const T2 prod      = __hmul2(*reinterpret_cast<const T2*>(&gw[j]), *reinterpret_cast<const T2*>(&sel));
+                rw[j]              = *reinterpret_cast<const uint32_t*>(&prod);
+            }
+        }
+        else
+        {
+            float f[VEC];
+            unpack<T, VEC>(v[u], f);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+            {
+                // grad * bool: x*1 and x*0 are exact in any dtype (-0 and NaN behave as in the reference product)
+                f[e] = __fmul_rn(f[e], m[u].v[e] ? 1.0f : 0.0f);
+            }
+            repack<T, VEC>(f, r);
+        }
         store_packet<T, VEC>(dx, idx, n, r, full[u]);
     }
 }
@@ -683,14 +852,20 @@ __global__ void __launch_bounds__(kThreads) v2_param_grad_kernel(V2GradArgs a)
     constexpr int CHUNK = chunk_elems<VEC>();
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
     __shared__ float s_sc[PER_CH ? kMaxRuns : 1], s_of[PER_CH ? kMaxRuns : 1];
-    RunCtx rc {0, 0, 1};
+    RunCtx rc {0, 0, 1, 0};
     float sc0 = 0.f, of0 = 0.f;
+    Pack<T, VEC> xv[unroll_of<VEC>()], gv[unroll_of<VEC>()];
+    Pack<uint8_t, VEC> mv[unroll_of<VEC>()];
+    bool full[unroll_of<VEC>()];
+    load_chunk<T, VEC, unroll_of<VEC>()>(static_cast<const T*>(a.x), base, a.n, xv, full);
+    load_chunk<T, VEC, unroll_of<VEC>()>(static_cast<const T*>(a.grad), base, a.n, gv, full);
+    load_chunk<uint8_t, VEC, unroll_of<VEC>()>(a.mask, base, a.n, mv, full);
     if (PER_CH)
     {
         rc = make_run_ctx<VEC>(a.geom, base, a.n);
         for (int lr = threadIdx.x; lr < rc.nruns; lr += kThreads)
         {
-            const int64_t ch = (rc.r0 + lr) % a.geom.num_ch;
+            const int64_t ch = run_channel(a.geom, rc, lr);
             s_sc[lr]         = a.scale[ch];
             s_of[lr]         = a.offset[ch];
         }
@@ -701,14 +876,8 @@ __global__ void __launch_bounds__(kThreads) v2_param_grad_kernel(V2GradArgs a)
         sc0 = __ldg(a.scale);
         of0 = __ldg(a.offset);
     }
-    Pack<T, VEC> xv[kUnroll], gv[kUnroll];
-    Pack<uint8_t, VEC> mv[kUnroll];
-    bool full[kUnroll];
-    load_chunk<T, VEC>(static_cast<const T*>(a.x), base, a.n, xv, full);
-    load_chunk<T, VEC>(static_cast<const T*>(a.grad), base, a.n, gv, full);
-    load_chunk<uint8_t, VEC>(a.mask, base, a.n, mv, full);
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
+    for (int u = 0; u < unroll_of<VEC>(); ++u)
     {
         const uint32_t off = (uint32_t) (u * kThreads + threadIdx.x) * VEC;
         const int64_t idx  = base + off;
@@ -749,7 +918,7 @@ static int launch_param_grad(V2GradArgs a, cudaStream_t st)
         vec >>= 1;
 #define AQ_LAUNCH(V, PC)                                                                                             \
     {                                                                                                                \
-        a.geom       = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>());                                     \
+        a.geom       = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>(), a.n);                                     \
         int64_t grid = (a.n + chunk_elems<V>() - 1) / chunk_elems<V>();                                              \
         v2_param_grad_kernel<T, V, PC><<<(unsigned) grid, kThreads, 0, st>>>(a);                                     \
     }
@@ -795,14 +964,18 @@ __global__ void __launch_bounds__(kThreads) ste_v1_kernel(SteArgs a)
     constexpr int CHUNK = chunk_elems<VEC>();
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
     __shared__ float s_mn[PER_CH ? kMaxRuns : 1], s_mx[PER_CH ? kMaxRuns : 1];
-    RunCtx rc {0, 0, 1};
+    RunCtx rc {0, 0, 1, 0};
     float mn0 = 0.f, mx0 = 0.f;
+    Pack<float, VEC> xv[unroll_of<VEC>()], gv[unroll_of<VEC>()];
+    bool full[unroll_of<VEC>()];
+    load_chunk<float, VEC, unroll_of<VEC>()>(a.x, base, a.n, xv, full);
+    load_chunk<float, VEC, unroll_of<VEC>()>(a.g, base, a.n, gv, full);
     if (PER_CH)
     {
         rc = make_run_ctx<VEC>(a.geom, base, a.n);
         for (int lr = threadIdx.x; lr < rc.nruns; lr += kThreads)
         {
-            const int64_t ch = (rc.r0 + lr) % a.geom.num_ch;
+            const int64_t ch = run_channel(a.geom, rc, lr);
             s_mn[lr]         = a.enc_min[ch];
             s_mx[lr]         = a.enc_max[ch];
         }
@@ -813,12 +986,8 @@ __global__ void __launch_bounds__(kThreads) ste_v1_kernel(SteArgs a)
         mn0 = __ldg(a.enc_min);
         mx0 = __ldg(a.enc_max);
     }
-    Pack<float, VEC> xv[kUnroll], gv[kUnroll];
-    bool full[kUnroll];
-    load_chunk<float, VEC>(a.x, base, a.n, xv, full);
-    load_chunk<float, VEC>(a.g, base, a.n, gv, full);
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u)
+    for (int u = 0; u < unroll_of<VEC>(); ++u)
     {
         const uint32_t off = (uint32_t) (u * kThreads + threadIdx.x) * VEC;
         float mn = mn0, mx = mx0;
@@ -845,7 +1014,7 @@ int ste_v1(SteArgs a, cudaStream_t st)
     const int vec     = pick_vec<float>(a.x, a.g, a.dx, per_ch ? a.geom.inner : 0);
 #define AQ_LAUNCH(V, PC)                                                                                             \
     {                                                                                                                \
-        a.geom       = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>());                                     \
+        a.geom       = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>(), a.n);                                     \
         int64_t grid = (a.n + chunk_elems<V>() - 1) / chunk_elems<V>();                                              \
         launch_pdl(ste_v1_kernel<V, PC>, (unsigned) grid, kThreads, 0, st, a);                                               \
     }

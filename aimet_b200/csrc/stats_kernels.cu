@@ -2,6 +2,8 @@
 // and the 512-bucket TF-Enhanced histogram.  All are single-pass, HBM-bound streaming reads.
 #include <float.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -46,6 +48,38 @@ __device__ __forceinline__ void group_reduce(float& mn, float& mx)
     }
 }
 
+// Folds one packet into (mn, mx).  16-bit packets are reduced two lanes per instruction in their own type first
+// (min / max select one of their operands, so the type they run in cannot change the result).
+template <typename T, int VEC, bool PROP>
+__device__ __forceinline__ void fold_pack(const Pack<T, VEC>& v, float& mn, float& mx)
+{
+    if constexpr (sizeof(T) == 2 && VEC >= 4)
+    {
+        using T2     = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+        const T2* q  = reinterpret_cast<const T2*>(&v);
+        T2 lo = q[0], hi = q[0];
+#pragma unroll
+        for (int e = 1; e < VEC / 2; ++e)
+        {
+            lo = PROP ? __hmin2_nan(lo, q[e]) : __hmin2(lo, q[e]);
+            hi = PROP ? __hmax2_nan(hi, q[e]) : __hmax2(hi, q[e]);
+        }
+        mn = min_op<PROP>(mn, min_op<PROP>(to_f32<T>(lo.x), to_f32<T>(lo.y)));
+        mx = max_op<PROP>(mx, max_op<PROP>(to_f32<T>(hi.x), to_f32<T>(hi.y)));
+    }
+    else
+    {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+        {
+            const float f = to_f32<T>(v.v[e]);
+            mn            = min_op<PROP>(mn, f);
+            mx            = max_op<PROP>(mx, f);
+        }
+    }
+}
+
+constexpr int kMaxDevices = 64;   // per-device bookkeeping tables
 constexpr int kMmThreads = 512;
 constexpr int kMmUnroll  = 4;
 
@@ -74,25 +108,10 @@ __global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __re
             v[u] = load_pack<T, VEC>(x + (p + u * stride) * VEC);
 #pragma unroll
         for (int u = 0; u < kMmUnroll; ++u)
-#pragma unroll
-            for (int e = 0; e < VEC; ++e)
-            {
-                const float f = to_f32<T>(v[u].v[e]);
-                mn            = min_op<PROP>(mn, f);
-                mx            = max_op<PROP>(mx, f);
-            }
+            fold_pack<T, VEC, PROP>(v[u], mn, mx);
     }
     for (; p < npack; p += stride)
-    {
-        Pack<T, VEC> v = load_pack<T, VEC>(x + p * VEC);
-#pragma unroll
-        for (int e = 0; e < VEC; ++e)
-        {
-            const float f = to_f32<T>(v.v[e]);
-            mn            = min_op<PROP>(mn, f);
-            mx            = max_op<PROP>(mx, f);
-        }
-    }
+        fold_pack<T, VEC, PROP>(load_pack<T, VEC>(x + p * VEC), mn, mx);
     // ragged tail (fewer than VEC elements)
     if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * VEC))
     {
@@ -170,6 +189,45 @@ __global__ void __launch_bounds__(256) minmax_rows_kernel(const T* __restrict__ 
     const int64_t group      = ((int64_t) blockIdx.x * 256 + threadIdx.x) / GS;
     const int64_t num_groups = (int64_t) gridDim.x * 256 / GS;
     const int64_t items      = rows * nseg;
+    if (nseg == 1 && inner <= (int64_t) GS * VEC)
+    {
+        // Short rows (block scales, small kernels): one packet per lane covers a row, so the loads in flight come
+        // from kMmUnroll different rows instead of from one row's sweep.
+        const bool lane_has = (int64_t) (lane_in_group + 1) * VEC <= inner;
+        for (int64_t it = group; it < rows; it += (int64_t) kMmUnroll * num_groups)
+        {
+            Pack<T, VEC> v[kMmUnroll];
+#pragma unroll
+            for (int u = 0; u < kMmUnroll; ++u)
+            {
+                const int64_t r = it + u * num_groups;
+                if (r < rows && lane_has)
+                    v[u] = load_pack<T, VEC>(x + r * inner + lane_in_group * VEC);
+            }
+#pragma unroll
+            for (int u = 0; u < kMmUnroll; ++u)
+            {
+                const int64_t r = it + u * num_groups;
+                float mn = INFINITY, mx = -INFINITY;
+                if (r < rows && lane_has)
+                    fold_pack<T, VEC, PROP>(v[u], mn, mx);
+                group_reduce<PROP, GS>(mn, mx);
+                if (r < rows && lane_in_group == 0)
+                {
+                    if (PROP && (mn != mn || mx != mx))
+                        mn = mx = NAN;
+                    if (accumulate)
+                    {
+                        mn = min_op<PROP>(part_min[r], mn);
+                        mx = max_op<PROP>(part_max[r], mx);
+                    }
+                    part_min[r] = mn;
+                    part_max[r] = mx;
+                }
+            }
+        }
+        return;
+    }
     for (int64_t it = group; it < items; it += num_groups)
     {
         const int64_t row = it / nseg;
@@ -189,25 +247,10 @@ __global__ void __launch_bounds__(256) minmax_rows_kernel(const T* __restrict__ 
                 v[u] = load_pack<T, VEC>(rp + e + (int64_t) u * GS * VEC);
 #pragma unroll
             for (int u = 0; u < kMmUnroll; ++u)
-#pragma unroll
-                for (int k = 0; k < VEC; ++k)
-                {
-                    const float f = to_f32<T>(v[u].v[k]);
-                    mn            = min_op<PROP>(mn, f);
-                    mx            = max_op<PROP>(mx, f);
-                }
+                fold_pack<T, VEC, PROP>(v[u], mn, mx);
         }
         for (; e + VEC <= end; e += (int64_t) GS * VEC)
-        {
-            Pack<T, VEC> v = load_pack<T, VEC>(rp + e);
-#pragma unroll
-            for (int k = 0; k < VEC; ++k)
-            {
-                const float f = to_f32<T>(v.v[k]);
-                mn            = min_op<PROP>(mn, f);
-                mx            = max_op<PROP>(mx, f);
-            }
-        }
+            fold_pack<T, VEC, PROP>(load_pack<T, VEC>(rp + e), mn, mx);
         // VEC divides inner and seg_len, so no ragged tail exists inside a row.
         group_reduce<PROP, GS>(mn, mx);
         if (lane_in_group == 0)
@@ -841,17 +884,21 @@ int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t*
         note_launch();
         return check_launch();
     }
-    static bool attr_set = false;
-    if (!attr_set)
+    static bool attr_set[kMaxDevices] = {};   // function attributes are per device
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return cuda_fail(e);
+    if (dev < 0 || dev >= kMaxDevices || !attr_set[dev])
     {
-        cudaError_t e = cudaFuncSetAttribute(tfe_hist_lane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kLaneHistSmem);
+        e = cudaFuncSetAttribute(tfe_hist_lane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLaneHistSmem);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(tfe_hist_lane_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                      cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess)
             return cuda_fail(e);
-        attr_set = true;
+        if (dev >= 0 && dev < kMaxDevices)
+            attr_set[dev] = true;
     }
     int64_t per_block = (int64_t) kLaneHistThreads * 4 * kLaneUnroll;
     int64_t blocks    = (n + per_block - 1) / per_block;
@@ -872,33 +919,187 @@ int tfe_init_grid(const float* minmax, aq_tfe_state_t* st, cudaStream_t stream)
     return check_launch();
 }
 
-// Running mean of per-batch PDFs, batch order preserved (DlQuantization/src/math_functions.cpp:278-287).
-__global__ void __launch_bounds__(AQ_PDF_SIZE) tfe_pdf_replay_kernel(const uint32_t* __restrict__ hists,
-                                                                     const int64_t* __restrict__ counts,
-                                                                     int64_t num_batches, double* __restrict__ pdf,
-                                                                     int32_t* __restrict__ iterations)
+// Correctly rounded a / b from y = RN(1 / b): two residual corrections.  After the first one q is within one ulp
+// of a / b, and for such a q Markstein's theorem gives RN(q + (a - b q) y) = RN(a / b).  Five dependent fused
+// operations instead of the ~20 of a full division; b must be a positive normal number, a zero or normal.
+__device__ __forceinline__ double div_by_rcp(double a, double b, double y)
 {
-    const int i = threadIdx.x;
+    double q = __dmul_rn(a, y);
+    q        = __fma_rn(__fma_rn(-b, q, a), y, q);
+    return __fma_rn(__fma_rn(-b, q, a), y, q);
+}
+
+constexpr int kReplayThreads = 128;   // buckets per CTA (4 CTAs cover the 512 buckets)
+constexpr int kReplayChunk   = 64;    // rows per shared-memory stage
+constexpr int kReplayGroup   = 16;    // rows folded between two checks of the speculation
+constexpr int kReplaySmem    = 2 * kReplayChunk * kReplayThreads * (int) sizeof(uint32_t);
+
+// Running mean of per-batch PDFs, batch order preserved (DlQuantization/src/math_functions.cpp:278-287):
+// pdf <- (pdf * k + hist / count) / (k + 1) for every batch with a non-zero count.  The chain over k is serial per
+// bucket and a CTA has one warp per scheduler, so the kernel is built to keep that warp's instruction stream short
+// and free of branches:
+//  * rows arrive through a two-stage cp.async ring (64 rows x this CTA's 128 buckets per stage);
+//  * per stage the CTA prepares, per row, count, RN(1/count), k, k + 1 and RN(1/(k + 1)); both divisions then use
+//    div_by_rcp (bit-identical to IEEE division).  A dropped row (count 0, or past the end of the table) is encoded
+//    as (1, 0, 1, 1, 1): its probability evaluates to 0 and the mean step to (acc * 1 + 0) / 1 = acc, so the fold
+//    needs no test per row;
+//  * inside a group of rows the chain runs on the quotient after ONE correction while the second correction is
+//    evaluated beside it; the second one is the correctly rounded quotient, so when the two agree for every row of
+//    the group the result stands, otherwise the group is folded again with the full sequence.
+// A count whose low 32 bits are zero (the reference divides by (int) count) takes the plain-division path.
+__global__ void __launch_bounds__(kReplayThreads) tfe_pdf_replay_kernel(const uint32_t* __restrict__ hists,
+                                                                        const int64_t* __restrict__ counts,
+                                                                        int64_t num_batches, double* __restrict__ pdf,
+                                                                        int32_t* __restrict__ iterations)
+{
+    constexpr int CH = kReplayChunk, G = kReplayGroup;
+    extern __shared__ __align__(16) unsigned char replay_dyn[];
+    uint32_t(*buf)[CH][kReplayThreads] = reinterpret_cast<uint32_t(*)[CH][kReplayThreads]>(replay_dyn);
+    __shared__ __align__(8) int64_t s_c[2][CH];
+    __shared__ double s_d[CH], s_rd[CH], s_k[CH], s_b[CH], s_rb[CH];
+    __shared__ int s_warp[kReplayThreads / 32];
+    __shared__ int s_odd;
+    const int t = threadIdx.x;
+    const int i = blockIdx.x * kReplayThreads + t;
+    auto issue  = [&](int stage, int64_t c0) {
+        const int rows = (int) ((num_batches - c0 < CH) ? (num_batches - c0) : CH);
+#pragma unroll 4
+        for (int pass = 0; pass < CH / 4; ++pass)   // a warp copies one row's 512-byte slice, 16 bytes per lane
+        {
+            const int r = pass * 4 + (t >> 5);
+            if (r < rows)
+            {
+                const unsigned dst  = (unsigned) __cvta_generic_to_shared(&buf[stage][r][(t & 31) * 4]);
+                const uint32_t* src = hists + (c0 + r) * AQ_PDF_SIZE + blockIdx.x * kReplayThreads + (t & 31) * 4;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+            }
+        }
+        if (t < rows)
+        {
+            const unsigned dst = (unsigned) __cvta_generic_to_shared(&s_c[stage][t]);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(counts + c0 + t) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (t == 0)
+        s_odd = 0;
+    issue(0, 0);
     double acc  = 0.0;
-    int it      = 0;
-    for (int64_t b = 0; b < num_batches; ++b)
+    int it_base = 0;
+    int chunk   = 0;
+    for (int64_t c0 = 0; c0 < num_batches; c0 += CH, ++chunk)
     {
-        const int64_t cnt = counts[b];
-        if (cnt == 0)
-            continue;
-        const double prob = __ddiv_rn((double) hists[b * AQ_PDF_SIZE + i], (double) (int) cnt);
-        acc               = __ddiv_rn(__dadd_rn(__dmul_rn(acc, (double) it), prob), (double) (it + 1));
-        ++it;
+        const int stage = chunk & 1;
+        const int rows  = (int) ((num_batches - c0 < CH) ? (num_batches - c0) : CH);
+        if (c0 + CH < num_batches)
+        {
+            issue(stage ^ 1, c0 + CH);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        }
+        else
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        // ---- per-row preparation: thread t owns row c0 + t ----
+        const int64_t cnt   = (t < rows) ? s_c[stage][t] : 0;
+        const bool live     = cnt != 0;
+        const unsigned mask = __ballot_sync(0xffffffffu, live);
+        if ((t & 31) == 0)
+            s_warp[t >> 5] = __popc(mask);
+        __syncthreads();
+        int before = __popc(mask & ((1u << (t & 31)) - 1u));
+        int total  = 0;
+#pragma unroll
+        for (int w = 0; w < kReplayThreads / 32; ++w)
+        {
+            if (w < (t >> 5))
+                before += s_warp[w];
+            total += s_warp[w];
+        }
+        if (t < CH)
+        {
+            if (live)
+            {
+                const int it   = it_base + before;
+                const double d = (double) (int) cnt;
+                if (d == 0.0)
+                    s_odd = 1;
+                s_d[t]  = d;
+                s_rd[t] = __drcp_rn(d);
+                s_k[t]  = (double) it;
+                s_b[t]  = (double) (it + 1);
+                s_rb[t] = __drcp_rn((double) (it + 1));
+            }
+            else
+            {
+                s_d[t] = s_k[t] = s_b[t] = s_rb[t] = 1.0;
+                s_rd[t]                            = 0.0;
+            }
+        }
+        __syncthreads();
+        if (s_odd)
+        {
+            for (int r = 0; r < rows; ++r)
+                if (s_c[stage][r] != 0)
+                    acc = __ddiv_rn(__dadd_rn(__dmul_rn(acc, s_k[r]), __ddiv_rn((double) buf[stage][r][t], s_d[r])), s_b[r]);
+        }
+        else
+        {
+            for (int j0 = 0; j0 < CH; j0 += G)
+            {
+                double prob[G];
+#pragma unroll
+                for (int u = 0; u < G; ++u)
+                    prob[u] = div_by_rcp((double) buf[stage][j0 + u][t], s_d[j0 + u], s_rd[j0 + u]);
+                const double acc0 = acc;
+                bool redo         = false;
+#pragma unroll
+                for (int u = 0; u < G; ++u)
+                {
+                    const double b = s_b[j0 + u], y = s_rb[j0 + u];
+                    const double a = __dadd_rn(__dmul_rn(acc, s_k[j0 + u]), prob[u]);
+                    double q       = __dmul_rn(a, y);
+                    q              = __fma_rn(__fma_rn(-b, q, a), y, q);
+                    redo |= __fma_rn(__fma_rn(-b, q, a), y, q) != q;
+                    acc = q;
+                }
+                if (redo)
+                {
+                    acc = acc0;
+#pragma unroll
+                    for (int u = 0; u < G; ++u)
+                        acc = div_by_rcp(__dadd_rn(__dmul_rn(acc, s_k[j0 + u]), prob[u]), s_b[j0 + u], s_rb[j0 + u]);
+                }
+            }
+        }
+        it_base += total;
+        __syncthreads();
+        if (t == 0)
+            s_odd = 0;
     }
     pdf[i] = acc;
     if (i == 0)
-        *iterations = it;
+        *iterations = it_base;
 }
 
 int tfe_pdf_replay(const uint32_t* hists, const int64_t* counts, int64_t num_batches, double* pdf,
                    int32_t* iterations, cudaStream_t stream)
 {
-    tfe_pdf_replay_kernel<<<1, AQ_PDF_SIZE, 0, stream>>>(hists, counts, num_batches, pdf, iterations);
+    static bool attr_set[kMaxDevices] = {};   // function attributes are per device
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return cuda_fail(e);
+    if (dev < 0 || dev >= kMaxDevices || !attr_set[dev])
+    {
+        e = cudaFuncSetAttribute(tfe_pdf_replay_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kReplaySmem);
+        if (e != cudaSuccess)
+            return cuda_fail(e);
+        if (dev >= 0 && dev < kMaxDevices)
+            attr_set[dev] = true;
+    }
+    tfe_pdf_replay_kernel<<<AQ_PDF_SIZE / kReplayThreads, kReplayThreads, kReplaySmem, stream>>>(hists, counts,
+                                                                                                 num_batches, pdf,
+                                                                                                 iterations);
     note_launch();
     return check_launch();
 }
