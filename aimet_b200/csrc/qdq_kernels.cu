@@ -207,6 +207,12 @@ __device__ __forceinline__ f32x2_t sub2(f32x2_t a, f32x2_t b)
     asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
+__device__ __forceinline__ f32x2_t fma2(f32x2_t a, f32x2_t b, f32x2_t c)
+{
+    f32x2_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
 // max(a, |b|, |c|), NaN if any operand is NaN
 __device__ __forceinline__ float max3_abs_nan(float a, float b, float c)
 {
@@ -476,10 +482,11 @@ struct V2Slot
     float s, o, rs;
     float eps;   // 0.5 - guard band of the reciprocal form for this encoding
 };
+constexpr float kBandPerUnit = 2.384185791015625e-07f;   // 2^-22 = 4 ulp of 1.0
 
-// RN(x/s) and RN(x * RN(1/s)) differ by at most 3 ulp of the quotient t.  Wherever the rounded value can matter
-// (within one step of the clamp range) |t| <= T = max(|qmin + o|, |qmax + o|) + 1, so a guard band of
-// 4 ulp(T) = 2^-22 T around every half-integer is enough; outside that range both forms clamp to the same bound.
+// RN(x/s) and RN(x * RN(1/s)) differ by at most 3 ulp of the quotient t, i.e. by less than 2^-22 |t|.  Wherever the
+// rounded value can matter (within one step of the clamp range) |t| <= T = max(|qmin + o|, |qmax + o|) + 1, so a
+// guard band of 2^-22 T around every half-integer is enough; outside that range both forms clamp to the same bound.
 __device__ __forceinline__ V2Slot v2_slot(float s, float o, float qmin, float qmax)
 {
     V2Slot k;
@@ -487,8 +494,12 @@ __device__ __forceinline__ V2Slot v2_slot(float s, float o, float qmin, float qm
     k.o  = o;
     k.rs = __frcp_rn(k.s);
     const float T      = fmaxf(fabsf(__fadd_rn(qmin, k.o)), fabsf(__fadd_rn(qmax, k.o))) + 1.0f;
-    const float margin = 4.0f * kUlp24 * T;
-    k.eps              = (margin < 0.25f) ? 0.5f - margin : 0.0f;   // NaN -> 0: always the exact path
+    const float margin = kBandPerUnit * T;
+    // One band for the whole encoding.  (For grids of 2^11 steps or more, e.g. 16-bit activations, a band sized
+    // for the largest quotient would send a percent of all elements to the exact path; the kernel is then built
+    // with WIDE and takes the band from each element's own quotient instead, 2^-22 (|t| + 1), at the price of two
+    // more packed operations per pair, and ignores eps.)
+    k.eps = (margin < 0.25f) ? 0.5f - margin : 0.0f;   // NaN -> 0: always the exact path
     return k;
 }
 __device__ __forceinline__ V2Slot v2_load(const float* scale, const float* offset, int64_t ch, float qmin, float qmax)
@@ -530,7 +541,8 @@ __device__ __forceinline__ void v2_exact_packet(const float (&x)[VEC], float (&y
 // runs); 2 = every packet fetches its own encoding (many short runs per tile, e.g. blocks of 64: staging would cost
 // a barrier and a slot per run, the direct loads go out together with the element loads and hit the same lines
 // from neighbouring lanes).
-template <typename T, int VEC, int PER_CH, int MODE, bool NARROW, bool CODES, bool MASK>
+// WIDE (fast mode only): the grid has 2^11 steps or more and the guard band follows each element's quotient.
+template <typename T, int VEC, int PER_CH, int MODE, bool NARROW, bool CODES, bool MASK, bool WIDE>
 __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
 {
     pdl_launch_dependents();
@@ -604,7 +616,9 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
             {
                 const float t = __fmul_rn(x[0], k.rs);
                 float r       = __fsub_rn(__fadd_rn(t, kMagicRne), kMagicRne);
-                ok            = fabsf(__fsub_rn(t, r)) < k.eps;   // false for NaN / Inf
+                const float d = fabsf(__fsub_rn(t, r));
+                ok = !WIDE ? (d < k.eps)   // false for NaN / Inf
+                           : (__fadd_rn(d, __fmul_rn(kBandPerUnit, fabsf(t))) < 0.5f - 2.0f * kBandPerUnit);
                 r             = __fsub_rn(r, k.o);
                 const float q = clamp_keep_nan(r, qmin, qmax);
                 if (MASK)
@@ -615,6 +629,8 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
             {
                 const f32x2_t rs2 = pair(k.rs, k.rs), o2 = pair(k.o, k.o), s2 = pair(k.s, k.s);
                 const f32x2_t magic = pair(kMagicRne, kMagicRne);
+                constexpr bool per_element = WIDE;
+                const f32x2_t band_p = pair(kBandPerUnit, kBandPerUnit), band_n = pair(-kBandPerUnit, -kBandPerUnit);
                 float worst = 0.0f;   // largest distance of a product from its rounded value; NaN for NaN / Inf
 #pragma unroll
                 for (int e = 0; e + 1 < VEC; e += 2)
@@ -622,8 +638,20 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
                     const f32x2_t t = mul2(pair(x[e], x[e + 1]), rs2);
                     f32x2_t r       = sub2(add2(t, magic), magic);
                     float d0, d1, r0, r1;
-                    unpair(sub2(t, r), d0, d1);
-                    worst = max3_abs_nan(worst, d0, d1);
+                    const f32x2_t d = sub2(t, r);
+                    if (per_element)
+                    {
+                        // |d| + 2^-22 |t| = max(|d + 2^-22 t|, |d - 2^-22 t|)
+                        float u0, u1, w0, w1;
+                        unpair(fma2(t, band_p, d), u0, u1);
+                        unpair(fma2(t, band_n, d), w0, w1);
+                        worst = max3_abs_nan(max3_abs_nan(worst, u0, u1), w0, w1);
+                    }
+                    else
+                    {
+                        unpair(d, d0, d1);
+                        worst = max3_abs_nan(worst, d0, d1);
+                    }
                     unpair(sub2(r, o2), r0, r1);
                     const float q0 = clamp_keep_nan(r0, qmin, qmax), q1 = clamp_keep_nan(r1, qmin, qmax);
                     if (MASK)
@@ -633,7 +661,7 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
                     else
                         unpair(mul2(add2(pair(q0, q1), o2), s2), y[e], y[e + 1]);
                 }
-                ok = worst < k.eps;
+                ok = worst < (per_element ? 0.5f - 2.0f * kBandPerUnit : k.eps);
             }
             if (!ok)
                 v2_exact_packet<T, VEC, false, CODES>(x, y, m, k, qmin, qmax);
@@ -658,28 +686,32 @@ static void launch_v2_variant(const V2Args& a, bool narrow, cudaStream_t st)
     const int64_t grid = (a.n + chunk_elems<VEC>() - 1) / chunk_elems<VEC>();
     const unsigned g   = (unsigned) grid;
     const bool codes = a.out_kind == AQ_V2_OUT_CODES, mask = a.mask != nullptr;
-#define AQ_K(MODE, NARROW, CODES, MASK) launch_pdl(v2_kernel<T, VEC, PER_CH, MODE, NARROW, CODES, MASK>, g, kThreads, 0, st, a)
+    const bool wide = (a.qmax - a.qmin) >= 2048.0f;
+#define AQ_K(MODE, NARROW, CODES, MASK, WIDE)                                                                        \
+    launch_pdl(v2_kernel<T, VEC, PER_CH, MODE, NARROW, CODES, MASK, WIDE>, g, kThreads, 0, st, a)
+#define AQ_K0(CODES, MASK) (wide ? AQ_K(0, false, CODES, MASK, true) : AQ_K(0, false, CODES, MASK, false))
     if (a.dequant_only)
     {
         if (narrow)
-            AQ_K(2, true, false, false);
+            AQ_K(2, true, false, false, false);
         else
-            AQ_K(2, false, false, false);
+            AQ_K(2, false, false, false, false);
     }
     else if (narrow)
     {
         if (codes)
-            mask ? AQ_K(1, true, true, true) : AQ_K(1, true, true, false);
+            mask ? AQ_K(1, true, true, true, false) : AQ_K(1, true, true, false, false);
         else
-            mask ? AQ_K(1, true, false, true) : AQ_K(1, true, false, false);
+            mask ? AQ_K(1, true, false, true, false) : AQ_K(1, true, false, false, false);
     }
     else
     {
         if (codes)
-            mask ? AQ_K(0, false, true, true) : AQ_K(0, false, true, false);
+            mask ? AQ_K0(true, true) : AQ_K0(true, false);
         else
-            mask ? AQ_K(0, false, false, true) : AQ_K(0, false, false, false);
+            mask ? AQ_K0(false, true) : AQ_K0(false, false);
     }
+#undef AQ_K0
 #undef AQ_K
 }
 

@@ -349,14 +349,29 @@ def qdq_numbers(torch, lib, device, peak):
     rec("c1_v2_qdq_fwd_mask_9B", 9 * n1, timed([lambda i=i: lib.aq_v2_quantize(P(xs[i]), P(ys[i]), P(ms[i]), 0, n1, 1, n1, P(sc), P(of), 0.0, 255.0, 0, 0, stream) for i in range(nb)], 4))
     rec("c1_v2_qdq_bwd_9B", 9 * n1, timed([lambda i=i: lib.aq_v2_qdq_backward(P(xs[i]), P(ms[i]), P(ys[i]), 0, n1, stream) for i in range(nb)], 4))
     rec("c1_libpymo_qdq_fwd_8B", 8 * n1, timed([lambda i=i: lib.aq_qdq_per_tensor(P(xs[i]), P(ys[i]), n1, -4.4, 4.6, 8, 0, stream) for i in range(nb)], 4))
+    emn, emx = torch.tensor([-4.4], device=device), torch.tensor([4.6], device=device)
+    rec("c1_v1_ste_bwd_12B", 12 * n1, timed([lambda i=i: lib.aq_ste_backward_v1(P(xs[i]), P(xs[(i + 1) % nb]), P(ys[i]), n1, 1, n1, P(emn), P(emx), stream) for i in range(nb)], 4))
+    mm = torch.empty(2, device=device)
+    ws = torch.zeros(int(lib.aq_minmax_workspace_bytes(n1, 1, n1)), dtype=torch.uint8, device=device)
+    rec("c1_minmax_4B", 4 * n1, timed([lambda i=i: lib.aq_minmax(P(xs[i]), 0, n1, 1, n1, P(mm[0:1]), P(mm[1:2]), 0, 0, P(ws), ws.numel(), stream) for i in range(nb)], 4))
     del xs, ys, ms
-    # config 2: [512,256,3,3] fp32 per-output-channel 8-bit symmetric (launch-latency bound: 9.4 MB per launch)
+    # config 2: [512,256,3,3] fp32 per-output-channel 8-bit symmetric (launch-latency bound: 9.4 MB per launch);
+    # timed launch by launch and, without the per-launch CPU cost, as one CUDA graph of all the launches
     n2, kb = 512 * 2304, 64
     w = [torch.randn(n2, device=device) * 0.03 for _ in range(kb)]
     wo = [torch.empty(n2, device=device) for _ in range(kb)]
     s2, o2 = torch.full((512,), 1e-3, device=device), torch.zeros(512, device=device)
-    rec("c2_v2_qdq_fwd_per_channel_8B", 8 * n2, timed([lambda i=i: lib.aq_v2_quantize(P(w[i]), P(wo[i]), None, 0, n2, 512, 2304, P(s2), P(o2), -128.0, 127.0, 0, 0, stream) for i in range(kb)], 3))
-    del w, wo
+    c2 = lambda st: [lambda i=i: lib.aq_v2_quantize(P(w[i]), P(wo[i]), None, 0, n2, 512, 2304, P(s2), P(o2), -128.0, 127.0, 0, 0, st) for i in range(kb)]
+    rec("c2_v2_qdq_fwd_per_channel_8B", 8 * n2, timed(c2(stream), 3))
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for c in c2(side.cuda_stream):
+            c()
+    torch.cuda.current_stream().wait_stream(side)
+    rec("c2_v2_qdq_fwd_per_channel_8B_graph", 8 * n2, timed([graph.replay], 6) / kb)
+    del w, wo, graph
     # config 5: bf16 weight [4096,11008], W4 symmetric, block 64 on the input dim
     n5 = 4096 * 11008
     wh = [(torch.randn(n5, device=device) * 0.02).to(torch.bfloat16) for _ in range(4)]
@@ -364,6 +379,10 @@ def qdq_numbers(torch, lib, device, peak):
     nch = n5 // 64
     s5, o5 = torch.full((nch,), 0.004, device=device), torch.zeros(nch, device=device)
     rec("c5_v2_qdq_fwd_bf16_block64_4B", 4 * n5 + 8 * nch, timed([lambda i=i: lib.aq_v2_quantize(P(wh[i]), P(wq[i]), None, 2, n5, nch, 64, P(s5), P(o5), -8.0, 7.0, 0, 0, stream) for i in range(4)], 4))
+    s1, o1 = torch.full((1,), 4e-4, device=device), torch.zeros(1, device=device)
+    rec("c5_v2_qdq_fwd_bf16_per_tensor_4B", 4 * n5, timed([lambda i=i: lib.aq_v2_quantize(P(wh[i]), P(wq[i]), None, 2, n5, 1, n5, P(s1), P(o1), -32768.0, 32767.0, 0, 0, stream) for i in range(4)], 4))
+    bm = torch.empty((2, nch), device=device)
+    rec("c5_minmax_bf16_block64_2B", 2 * n5 + 8 * nch, timed([lambda i=i: lib.aq_minmax(P(wh[i]), 2, n5, nch, 64, P(bm[0]), P(bm[1]), 0, 0, P(ws), ws.numel(), stream) for i in range(4)], 4))
     return out
 
 
@@ -372,7 +391,7 @@ def qdq_numbers(torch, lib, device, peak):
 # ---------------------------------------------------------------------------------------------------------------------
 KERNEL_CASES = ("tfe_hist", "minmax_f32", "minmax_f32_rows", "minmax_bf16_block64", "v2_qdq_f32", "v2_qdq_f32_mask",
                 "v2_qdq_f32_per_channel", "v2_qdq_bf16", "v2_qdq_bf16_block64", "v2_bwd_f32", "v2_bwd_bf16",
-                "pymo_qdq_f32", "pymo_qdq_f32_per_channel", "ste_v1_f32")
+                "pymo_qdq_f32", "pymo_qdq_f32_per_channel", "ste_v1_f32", "tfe_replay", "tfe_search")
 
 
 def build_kernel_case(name, mb, torch, lib, device):
@@ -399,6 +418,23 @@ def build_kernel_case(name, mb, torch, lib, device):
             out.append((a * (0.02 if half else 1.0)).to(torch.bfloat16 if half else torch.float32))
         return out
 
+    if name in ("tfe_replay", "tfe_search"):
+        # the tail of a calibration: running-mean replay over `mb` x 8 per-batch rows (2048 at the default), SQNR search
+        rows = mb * 8
+        g = torch.Generator(device=device)
+        g.manual_seed(5)
+        x = torch.relu(torch.randn(1 << 22, device=device, generator=g))
+        st = ops.TfeDeviceState(device, capacity=rows)
+        st.init_grid_from(ops.minmax(x).reshape(-1))
+        for r in range(rows):
+            st.add_batch(x[(r % 8) * 4096:(r % 8) * 4096 + (1 << 19)], r)
+        st.replay()
+        ws = ops.workspace(st.state, int(lib.aq_tfe_search_workspace_bytes()))
+        if name == "tfe_replay":
+            calls = [lambda: lib.aq_tfe_pdf_replay(P(st.hists), P(st.counts), rows, P(st.pdf), P(st.iterations), stream)]
+            return calls, rows * (2048 + 8) + 4096, [st, x]
+        calls = [lambda: lib.aq_tfe_search(P(st.state), P(st.pdf), 1, 8, 0, 0, 0, P(st.encoding), P(ws), ws.numel(), stream)]
+        return calls, 2 * 512 * 8, [st, x, ws]
     xs = data("relu_outliers" if name == "tfe_hist" else "normal")
     if name == "tfe_hist":
         st = ops.TfeDeviceState(device, capacity=nbuf)
@@ -437,7 +473,10 @@ def build_kernel_case(name, mb, torch, lib, device):
         calls = [lambda i=i: lib.aq_qdq_per_tensor(P(xs[i]), P(ys[i]), n, -4.4, 4.6, 8, 0, stream) for i in range(nbuf)]
         return calls, 8 * n, [ys] + xs
     num_ch, inner = n // 2304, 2304
-    emn, emx = torch.full((num_ch,), -2.0, device=device), torch.full((num_ch,), 2.0, device=device)
+    # encodings as a calibration produces them: min and max are multiples of the step, so clamped values land on a
+    # grid point (with arbitrary bounds every clamped value sits on a rounding boundary and takes the exact path)
+    step = 4.0 / 255.0
+    emn, emx = torch.full((num_ch,), -128 * step, device=device), torch.full((num_ch,), 127 * step, device=device)
     if name == "pymo_qdq_f32_per_channel":
         calls = [lambda i=i: lib.aq_qdq_per_channel(P(xs[i]), P(ys[i]), n, num_ch, inner, P(emn), P(emx), 255.0, 0, stream)
                  for i in range(nbuf)]

@@ -179,7 +179,8 @@ int aq_v2_qdq_backward_params(const void* d_x, const void* d_grad, const uint8_t
                               float* d_doffset, int dtype, int64_t n, int64_t num_ch, int64_t inner,
                               const float* d_scale, const float* d_offset, double qmin, double qmax, void* stream);
 
-/* Replaces the tensor-gradient of QuantDequantFunc.backward (torch_builtins.py:329-344): dx = grad * mask. */
+/* Replaces the tensor-gradient of QuantDequantFunc.backward (torch_builtins.py:329-344): dx = grad * mask.
+ * d_mask holds one byte per element, 0 or 1 (what aq_v2_quantize writes, and how a bool tensor is stored). */
 int aq_v2_qdq_backward(const void* d_grad, const uint8_t* d_mask, void* d_dx, int dtype, int64_t n, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
