@@ -157,6 +157,7 @@ struct ChanGeom
     // (0 stands for d == 1).  Only used when the tensor has fewer than 2^32 elements (`small`).
     uint64_t inner_m64, ch_m64;
     int small;
+    int wraps;   // 0 when every run is its own channel (n / inner <= num_ch), so that channel == run
 };
 
 inline uint64_t magic64(int64_t d)
@@ -187,6 +188,7 @@ inline ChanGeom make_geom(int64_t num_ch, int64_t inner, int64_t chunk, int64_t 
     g.small     = (n >= 0 && (uint64_t) n <= 0xffffffffull) ? 1 : 0;
     g.inner_m64 = magic64(inner);
     g.ch_m64    = magic64(num_ch);
+    g.wraps     = (n < 0 || inner <= 0 || (n + inner - 1) / inner > num_ch) ? 1 : 0;
     return g;
 }
 

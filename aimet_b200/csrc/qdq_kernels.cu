@@ -224,14 +224,23 @@ __device__ __forceinline__ float max3_abs_nan(float a, float b, float c)
 // =================================================================================================
 // Chunk load / store
 // =================================================================================================
-template <typename T, int VEC, int U>
+// Offset of a thread's u-th packet inside the CTA's chunk.  Interleaved: packet u of all threads is one contiguous
+// stretch.  Adjacent (ADJ): a thread's packets follow one another, so that they share an encoding when the run
+// length is a multiple of U * VEC.
+template <int VEC, int U, bool ADJ>
+__device__ __forceinline__ uint32_t packet_offset(int u)
+{
+    return ADJ ? (uint32_t) (threadIdx.x * U + u) * VEC : (uint32_t) (u * kThreads + threadIdx.x) * VEC;
+}
+
+template <typename T, int VEC, int U, bool ADJ = false>
 __device__ __forceinline__ void load_chunk(const T* __restrict__ x, int64_t base, int64_t n, Pack<T, VEC> (&v)[U],
                                            bool (&full)[U])
 {
 #pragma unroll
     for (int u = 0; u < U; ++u)
     {
-        const int64_t idx = base + (int64_t) (u * kThreads + threadIdx.x) * VEC;
+        const int64_t idx = base + (int64_t) packet_offset<VEC, U, ADJ>(u);
         full[u]           = idx + VEC <= n;
         if (full[u])
             v[u] = load_pack<T, VEC>(x + idx);
@@ -538,9 +547,8 @@ __device__ __forceinline__ void v2_exact_packet(const float (&x)[VEC], float (&y
 
 // MODE: 0 = fast fp32-internal quantize(-dequantize); 1 = exact / narrow-internal quantize(-dequantize); 2 = dequantize
 // PER_CH: 0 = one encoding; 1 = the encodings of the runs met by the CTA are staged in shared memory (few, long
-// runs); 2 = every packet fetches its own encoding (many short runs per tile, e.g. blocks of 64: staging would cost
-// a barrier and a slot per run, the direct loads go out together with the element loads and hit the same lines
-// from neighbouring lanes).
+// runs); 2 = every thread fetches the one encoding its adjacent packets share (many short runs per tile, e.g.
+// blocks of 64: staging would cost a barrier and a slot per run).
 // WIDE (fast mode only): the grid has 2^11 steps or more and the guard band follows each element's quotient.
 template <typename T, int VEC, int PER_CH, int MODE, bool NARROW, bool CODES, bool MASK, bool WIDE>
 __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
@@ -554,13 +562,14 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
     __shared__ V2Slot s_slot[PER_CH == 1 ? kMaxRuns : 1];
     RunCtx rc {0, 0, 1, 0};
     V2Slot k0;
-    float sc_u[unroll_of<VEC>()], of_u[unroll_of<VEC>()];
+    constexpr int U    = unroll_of<VEC>();
+    constexpr bool ADJ = PER_CH == 2;
     if (!PER_CH)
         k0 = v2_load(a.scale, a.offset, 0, qmin, qmax);
     // per channel: the element loads go out first and the encodings are fetched while they are in flight
-    Pack<T, VEC> v[unroll_of<VEC>()];
-    bool full[unroll_of<VEC>()];
-    load_chunk<T, VEC, unroll_of<VEC>()>(static_cast<const T*>(a.x), base, hi, v, full);
+    Pack<T, VEC> v[U];
+    bool full[U];
+    load_chunk<T, VEC, U, ADJ>(static_cast<const T*>(a.x), base, hi, v, full);
     if (PER_CH == 1)
     {
         rc = make_run_ctx<VEC>(a.geom, base, hi);
@@ -570,28 +579,30 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
     }
     if (PER_CH == 2)
     {
-        rc = make_run_ctx<VEC>(a.geom, base, hi);
-#pragma unroll
-        for (int u = 0; u < unroll_of<VEC>(); ++u)
+        // the thread's packets are adjacent and the run length is a multiple of U * VEC: one encoding per thread,
+        // fetched straight from global memory (neighbouring lanes read the same words)
+        const int64_t first = base + packet_offset<VEC, U, true>(0);
+        int64_t ch          = 0;
+        if (first < hi)
         {
-            const uint32_t off = (uint32_t) (u * kThreads + threadIdx.x) * VEC;
-            int64_t ch         = 0;
-            if (base + off < hi)
-                ch = run_channel(a.geom, rc, (int) run_of(a.geom, rc, off));
-            sc_u[u] = __ldg(a.scale + ch);
-            of_u[u] = __ldg(a.offset + ch);
+            if (a.geom.small)
+            {
+                const uint32_t run = div_m64((uint32_t) first, a.geom.inner_m64);
+                ch = a.geom.wraps ? (int64_t) (run - div_m64(run, a.geom.ch_m64) * (uint32_t) a.geom.num_ch) : (int64_t) run;
+            }
+            else
+                ch = (first / a.geom.inner) % a.geom.num_ch;
         }
+        k0 = v2_slot(__ldg(a.scale + ch), __ldg(a.offset + ch), qmin, qmax);
     }
 #pragma unroll
-    for (int u = 0; u < unroll_of<VEC>(); ++u)
+    for (int u = 0; u < U; ++u)
     {
-        const uint32_t off = (uint32_t) (u * kThreads + threadIdx.x) * VEC;
+        const uint32_t off = packet_offset<VEC, U, ADJ>(u);
         const int64_t idx  = base + off;
         V2Slot k           = k0;
         if (PER_CH == 1)
             k = s_slot[run_of(a.geom, rc, off)];
-        if (PER_CH == 2)
-            k = v2_slot(sc_u[u], of_u[u], qmin, qmax);
         float x[VEC], y[VEC];
         uint8_t m[VEC];
         unpack<T, VEC>(v[u], x);
@@ -718,11 +729,12 @@ static void launch_v2_variant(const V2Args& a, bool narrow, cudaStream_t st)
 template <typename T, bool PER_CH>
 static int launch_v2_vec(V2Args a, int vec, bool narrow, cudaStream_t st)
 {
-    // more than 16 runs per tile: per-packet encoding loads instead of shared-memory staging
+    // more than 16 runs per tile, each a whole number of thread shares: per-thread encoding loads instead of
+    // shared-memory staging
 #define AQ_LAUNCH(V)                                                                                                 \
     {                                                                                                                \
         a.geom = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>(), a.n);                                      \
-        if (PER_CH && a.geom.inner * 16 < chunk_elems<V>())                                                          \
+        if (PER_CH && a.geom.inner * 16 < chunk_elems<V>() && a.geom.inner % (unroll_of<V>() * V) == 0)              \
             launch_v2_variant<T, V, PER_CH ? 2 : 0>(a, narrow, st);                                                  \
         else                                                                                                         \
             launch_v2_variant<T, V, PER_CH ? 1 : 0>(a, narrow, st);                                                  \
