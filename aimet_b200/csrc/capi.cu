@@ -365,6 +365,8 @@ int aq_tfe_histogram(const float* d_x, int64_t n, const aq_tfe_state_t* d_state,
 {
     if (n < 0 || (n > 0 && !d_x) || !d_state || !d_hist)
         return AQ_ERR_INVALID_ARG;
+    if (((uintptr_t) d_state % 16) || ((uintptr_t) d_x % 4) || ((uintptr_t) d_hist % 4) || ((uintptr_t) d_count % 8))
+        return AQ_ERR_INVALID_ARG;   // the kernels use 16-byte loads of the state
     if (n > 0x7fffffffLL)
         return AQ_ERR_TOO_LARGE;   // the reference counts elements in an int; so does the PDF replay
     return tfe_histogram(d_x, n, d_state, d_hist, d_count, (cudaStream_t) stream);
@@ -375,6 +377,8 @@ int aq_tfe_pdf_replay(const uint32_t* d_hists, const int64_t* d_counts, int64_t 
 {
     if (num_batches < 0 || (num_batches > 0 && (!d_hists || !d_counts)) || !d_pdf || !d_iterations)
         return AQ_ERR_INVALID_ARG;
+    if (((uintptr_t) d_hists % 16) || ((uintptr_t) d_counts % 8) || ((uintptr_t) d_pdf % 8))
+        return AQ_ERR_INVALID_ARG;   // rows are fetched with 16-byte asynchronous copies
     return tfe_pdf_replay(d_hists, d_counts, num_batches, d_pdf, d_iterations, (cudaStream_t) stream);
 }
 

@@ -1,6 +1,7 @@
 // Calibration statistics kernels for sm_100a: fused min/max reductions (per tensor / per channel / per block)
 // and the 512-bucket TF-Enhanced histogram.  All are single-pass, HBM-bound streaming reads.
 #include <float.h>
+#include <stddef.h>
 
 #include <type_traits>
 
@@ -79,6 +80,9 @@ __device__ __forceinline__ void fold_pack(const Pack<T, VEC>& v, float& mn, floa
     }
 }
 
+static_assert(offsetof(aq_tfe_state_t, bucket_size) % 16 == 0 && offsetof(aq_tfe_state_t, pdf_offset) == offsetof(aq_tfe_state_t, bucket_size) + 4 &&
+                  offsetof(aq_tfe_state_t, initialized) == offsetof(aq_tfe_state_t, bucket_size) + 8,
+              "the histogram kernel reads bucket_size, pdf_offset and initialized with one 16-byte load");
 constexpr int kMaxDevices = 64;   // per-device bookkeeping tables
 constexpr int kMmThreads = 512;
 constexpr int kMmUnroll  = 4;
@@ -698,14 +702,16 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
             if (p0 + u * sd < np)
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const float4*>(x) + (p0 + u * sd)));
     }
-    const int initialized = st->initialized;
+    // bucket_size, pdf_offset and the initialized flag sit in one aligned 16-byte group: one load, one round trip
+    const int4 tail       = *reinterpret_cast<const int4*>(&st->bucket_size);
+    const int initialized = tail.z;
     if (blockIdx.x == 0 && threadIdx.x == 0 && count)
         *count = initialized ? n : 0;
     if (!initialized)
         return;
     __syncthreads();
 
-    const float bs = st->bucket_size, po = st->pdf_offset;
+    const float bs = __int_as_float(tail.x), po = __int_as_float(tail.y);
     const float margin = hist_margin(po);
     // A margin of a quarter bucket or more means the grid sits so far from zero that the reciprocal form is
     // useless: eps = 0 marks every packet unsure, the queue overflows and the CTA takes the exact sweep below.

@@ -1,0 +1,331 @@
+"""Affine quantizer modules on the B200 kernels: ``Quantize`` and ``QuantizeDequantize``.
+
+Same constructor signatures, parameters (``min`` / ``max``), calibration context and accessor methods as
+aimet_torch/v2/quantization/affine/quantizer.py:66-697 (AffineQuantizerBase, MinMaxQuantizer, Quantize,
+QuantizeDequantize) and aimet_torch/v2/quantization/base/quantizer.py:59-219 (initialisation tracking, overwrite
+flag); ``AffineEncoding`` carries what aimet_torch/v2/quantization/affine/encoding.py:54-280 exposes as properties.
+The forward passes go through :mod:`aimet_b200.v2.backend` (one fused kernel each way); statistics go through the
+analyzers of :mod:`aimet_b200.v2.encoding_analyzer`.
+
+Host-side differences, on purpose:
+
+* scale and offset are cached between forward passes while ``min`` / ``max`` are unchanged and no gradient is
+  being recorded (the reference recomputes them with five small tensor operations per call);
+* the outputs are plain tensors (the reference wraps them in tensor subclasses that carry the encoding; use
+  ``get_encoding()`` for it);
+* ``scale = (max - min) / num_steps`` divides by a tensor, so that the CUDA result equals the reference's CPU
+  result bit for bit (a CUDA tensor divided by a Python number is multiplied by its reciprocal instead).
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+from torch import nn
+
+from . import backend
+from .encoding_analyzer import EncodingAnalyzer, MinMaxEncodingAnalyzer, StatisticsNotFoundError
+
+__all__ = ["AffineEncoding", "MinMaxQuantizer", "Quantize", "QuantizeDequantize"]
+
+
+def derive_qmin_qmax(bitwidth: int, signed: bool) -> Tuple[int, int]:
+    """Integer grid of a bit-width (backends/__init__.py:359-370): signed grids are [-ceil(n/2), floor(n/2)]."""
+    steps = 2 ** bitwidth - 1
+    if signed:
+        return -math.ceil(steps / 2), math.floor(steps / 2)
+    return 0, steps
+
+
+class _RoundSte(torch.autograd.Function):
+    """torch.round with an identity gradient (aimet_torch/v2/utils.py:195-199)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        return torch.round(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g
+
+
+class AffineEncoding:
+    """Scale / offset / integer grid of one quantizer (affine/encoding.py:54-280)."""
+
+    def __init__(self, scale: torch.Tensor, offset: torch.Tensor, qmin: int, qmax: int, symmetry: bool = False,
+                 block_size: Optional[Sequence[int]] = None):
+        self.scale, self.offset, self.qmin, self.qmax = scale, offset, int(qmin), int(qmax)
+        self.symmetry, self.block_size = bool(symmetry), block_size
+
+    mapping = "affine"
+
+    @property
+    def granularity(self) -> str:
+        if self.scale.dim() == 0:
+            return "pertensor"
+        if self.block_size is not None:
+            return "blockwise"
+        return "perchannel" if sum(d > 1 for d in self.scale.shape) == 1 else "unknown"
+
+    @property
+    def num_steps(self) -> int:
+        return self.qmax - self.qmin
+
+    @property
+    def bitwidth(self) -> int:
+        return int(math.log2(self.num_steps + 1))
+
+    @property
+    def signed(self) -> bool:
+        return self.qmin < 0
+
+    @property
+    def min(self) -> torch.Tensor:
+        return (self.offset + self.qmin) * self.scale
+
+    @property
+    def max(self) -> torch.Tensor:
+        return (self.offset + self.qmax) * self.scale
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.scale.dtype
+
+    def to(self, *args, **kwargs) -> "AffineEncoding":
+        return AffineEncoding(self.scale.to(*args, **kwargs), self.offset.to(*args, **kwargs), self.qmin, self.qmax,
+                              self.symmetry, self.block_size)
+
+    def quantize(self, x: torch.Tensor) -> torch.Tensor:
+        return backend.quantize(x, self.scale, self.offset, self.qmin, self.qmax, self.block_size)
+
+    def dequantize(self, x: torch.Tensor) -> torch.Tensor:
+        return backend.dequantize(x, self.scale, self.offset, self.block_size)
+
+
+def _encoding_shape_with_blocks(shape: Sequence[int], block_size: Optional[Sequence[int]]) -> Tuple[int, ...]:
+    """Shape of the statistics when blocks are split out: [d0, 1, d1, 1, ...] (torch_builtins.py:387-403)."""
+    if block_size is None:
+        return tuple(shape)
+    out: List[int] = []
+    for d in shape:
+        out += [d, 1]
+    return tuple(out)
+
+
+def _reshape_for_blocks(x: torch.Tensor, enc_shape: Sequence[int], block_size: Optional[Sequence[int]]) -> torch.Tensor:
+    """View [.., d_k, ..] as [.., d_k / B_k, B_k, ..] for the trailing len(block_size) dimensions
+    (torch_builtins.py:366-403); -1 stands for "one block spans the whole dimension share"."""
+    if block_size is None:
+        return x
+    view: List[int] = []
+    for i in range(1, len(block_size) + 1):
+        blocks = enc_shape[-i]
+        width = x.shape[-i] // blocks if block_size[-i] == -1 else block_size[-i]
+        view = [blocks, width] + view
+    return x.view(list(x.shape[:-len(block_size)]) + view)
+
+
+class MinMaxQuantizer(nn.Module):
+    """Affine quantizer whose trainable parameters are ``min`` and ``max`` (affine/quantizer.py:66-437).
+
+    ``MinMaxQuantizer(shape, bitwidth, symmetric, encoding_analyzer=None, block_size=None)`` or
+    ``MinMaxQuantizer(shape, qmin, qmax, symmetric, encoding_analyzer=None, block_size=None)``.
+    """
+
+    def __init__(self, shape, *args, **kwargs):
+        super().__init__()
+        self.shape = (shape,) if isinstance(shape, int) else tuple(shape)
+        pos = list(args) + [None] * (5 - len(args))
+        first = kwargs.pop("qmin", kwargs.pop("bitwidth", pos[0]))
+        second = kwargs.pop("qmax", pos[1])
+        if second is not None and not isinstance(second, bool):
+            qmin, qmax = first, second
+            symmetric = kwargs.pop("symmetric", pos[2])
+            analyzer, block_size = kwargs.pop("encoding_analyzer", pos[3]), kwargs.pop("block_size", pos[4])
+            if qmin is None or qmax is None or symmetric is None:
+                raise TypeError(f"{type(self).__qualname__}: expected (shape, qmin, qmax, symmetric, ...)")
+        else:
+            symmetric = kwargs.pop("symmetric", pos[1])
+            if first is None or symmetric is None:
+                raise TypeError(f"{type(self).__qualname__}: expected (shape, bitwidth, symmetric, ...)")
+            qmin, qmax = derive_qmin_qmax(first, signed=symmetric)
+            analyzer, block_size = kwargs.pop("encoding_analyzer", pos[2]), kwargs.pop("block_size", pos[3])
+        if kwargs:
+            raise TypeError(f"{type(self).__qualname__}.__init__ got unexpected keyword argument: "
+                            f"{', '.join(kwargs.keys())}")
+        if qmin >= qmax:
+            raise ValueError(f"qmax should be strictly larger than qmin. Got qmax={qmax}, qmin={qmin}")
+        self.qmin, self.qmax, self._symmetric = int(qmin), int(qmax), bool(symmetric)
+        self.block_size = tuple(block_size) if block_size is not None else None
+        self.encoding_analyzer: EncodingAnalyzer = analyzer or MinMaxEncodingAnalyzer(
+            _encoding_shape_with_blocks(self.shape, self.block_size))
+        if self.block_size is None and not backend._is_expandable(self.encoding_analyzer.observer.shape, self.shape):
+            raise RuntimeError(f"Encoding analyzer of shape {self.encoding_analyzer.observer.shape} "
+                               f"is incompatible with quantizer of shape {self.shape}.")
+        self._allow_overwrite = True
+        self._calibrating = False
+        self._cache = None
+        self.min = nn.Parameter(-torch.ones(self.shape))
+        self.max = nn.Parameter(torch.ones(self.shape))
+        # a parameter counts as initialised once it has been written after construction (base/quantizer.py:109-135)
+        self._initial_versions = {"min": (self.min, self.min._version), "max": (self.max, self.max._version)}
+
+    # ---- bookkeeping -------------------------------------------------------------------------------------------
+    @property
+    def symmetric(self) -> bool:
+        return self._symmetric
+
+    @symmetric.setter
+    def symmetric(self, value: bool):
+        self._symmetric = bool(value)
+        self._cache = None
+
+    @property
+    def bitwidth(self) -> int:
+        return int(math.log2(self.qmax - self.qmin + 1))
+
+    @bitwidth.setter
+    def bitwidth(self, bitwidth: int):
+        self.qmin, self.qmax = derive_qmin_qmax(bitwidth, signed=self.signed)
+        self._cache = None
+
+    @property
+    def signed(self) -> bool:
+        return self.qmin < 0
+
+    def allow_overwrite(self, mode: bool):
+        self._allow_overwrite = bool(mode)
+
+    def is_initialized(self) -> bool:
+        for name, (tensor, version) in self._initial_versions.items():
+            current = getattr(self, name)
+            if current is tensor and current._version == version:
+                return False
+        return True
+
+    def get_extra_state(self):
+        return {name: torch.tensor(self.is_initialized()) for name in ("min", "max")}
+
+    @torch.no_grad()
+    def set_extra_state(self, state):
+        for name in ("min", "max"):
+            p = getattr(self, name)
+            self._initial_versions[name] = (p, p._version)
+            if name in state and bool(state[name]):
+                p.mul_(1.0)   # bumps the version: marks the loaded value as initialised
+        self._cache = None
+
+    # ---- encodings ---------------------------------------------------------------------------------------------
+    def _scale_offset(self, dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor]:
+        recording = torch.is_grad_enabled() and (self.min.requires_grad or self.max.requires_grad)
+        key = (self.min, self.min._version, self.max, self.max._version, dtype, self._symmetric, self.qmin, self.qmax)
+        if not recording and self._cache is not None and all(a is b if isinstance(a, torch.Tensor) else a == b
+                                                             for a, b in zip(self._cache[0], key)):
+            return self._cache[1], self._cache[2]
+        steps = torch.tensor(float(self.qmax - self.qmin), dtype=dtype, device=self.min.device)
+        scale = ((self.max.to(dtype) - self.min.to(dtype)) / steps).to(dtype)
+        if self._symmetric:
+            offset = torch.zeros_like(self.min, requires_grad=False, dtype=dtype)
+        else:
+            offset = (_RoundSte.apply(self.min.to(dtype) / scale) - self.qmin).to(dtype)
+        if not recording:
+            self._cache = (key, scale.detach(), offset.detach())
+        return scale, offset
+
+    def get_scale(self, dtype=None) -> Optional[torch.Tensor]:
+        if not self.is_initialized():
+            return None
+        return self._scale_offset(dtype or torch.float32)[0]
+
+    def get_offset(self, dtype=None) -> Optional[torch.Tensor]:
+        if not self.is_initialized():
+            return None
+        return self._scale_offset(dtype or torch.float32)[1]
+
+    def get_min(self, dtype=None) -> Optional[torch.Tensor]:
+        if not self.is_initialized():
+            return None
+        scale, offset = self._scale_offset(dtype or torch.float32)
+        return scale * (offset + self.qmin)
+
+    def get_max(self, dtype=None) -> Optional[torch.Tensor]:
+        if not self.is_initialized():
+            return None
+        scale, offset = self._scale_offset(dtype or torch.float32)
+        return scale * (offset + self.qmax)
+
+    def get_encoding(self) -> Optional[AffineEncoding]:
+        if not self.is_initialized():
+            return None
+        scale, offset = self._scale_offset(torch.float32)
+        return AffineEncoding(scale, offset, self.qmin, self.qmax, self._symmetric, self.block_size)
+
+    @torch.no_grad()
+    def set_range(self, min: torch.Tensor, max: torch.Tensor):   # pylint: disable=redefined-builtin
+        self.min.copy_(min)
+        self.max.copy_(max)
+        self._cache = None
+
+    # ---- calibration -------------------------------------------------------------------------------------------
+    @contextlib.contextmanager
+    def compute_encodings(self):
+        """Observes the inputs seen inside the context and sets ``min`` / ``max`` from their statistics on exit;
+        inside the context every forward pass quantizes with the statistics of its own batch
+        (affine/quantizer.py:317-374)."""
+        if not self._allow_overwrite:
+            yield
+            return
+        self.encoding_analyzer.reset_stats()
+        self._calibrating = True
+        try:
+            yield
+        finally:
+            self._calibrating = False
+        steps = self.qmax - self.qmin
+        try:
+            enc_min, enc_max = self.encoding_analyzer.compute_encodings(steps, self._symmetric)
+        except StatisticsNotFoundError:
+            return
+        if enc_min is None or enc_max is None:
+            return
+        self.set_range(enc_min.view(self.min.shape) if self.block_size is not None else enc_min,
+                       enc_max.view(self.max.shape) if self.block_size is not None else enc_max)
+
+    def _dynamic_scale_offset(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        stats = self.encoding_analyzer.update_stats(_reshape_for_blocks(x, self.shape, self.block_size))
+        steps = self.qmax - self.qmin
+        dmin, dmax = self.encoding_analyzer.compute_encodings_from_stats(stats, steps, self._symmetric)
+        if self.block_size is not None:
+            dmin, dmax = dmin.view(self.min.shape), dmax.view(self.max.shape)
+        dmin = dmin.to(dtype=self.min.dtype, device=self.min.device).expand_as(self.min)
+        dmax = dmax.to(dtype=self.max.dtype, device=self.max.device).expand_as(self.max)
+        div = torch.tensor(float(steps), dtype=torch.float32, device=dmin.device)
+        scale = (dmax.to(torch.float32) - dmin.to(torch.float32)) / div
+        offset = torch.zeros_like(scale) if self._symmetric else torch.round(dmin.to(torch.float32) / scale) - self.qmin
+        return scale, offset
+
+    def _encoding_for(self, x: torch.Tensor, what: str) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self._calibrating:
+            return self._dynamic_scale_offset(x)
+        if not self.is_initialized():
+            raise RuntimeError(f"Failed to run {what} since quantization parameters are not initialized."
+                               " Please initialize the quantization parameters using `compute_encodings()`.")
+        return self._scale_offset(torch.float32)
+
+
+class Quantize(MinMaxQuantizer):
+    """out = clamp(round(input / scale) - offset, qmin, qmax)  (affine/quantizer.py:440-563)."""
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:   # pylint: disable=redefined-builtin
+        scale, offset = self._encoding_for(input, "Quantize")
+        return backend.quantize(input, scale, offset, self.qmin, self.qmax, block_size=self.block_size)
+
+
+class QuantizeDequantize(MinMaxQuantizer):
+    """out = (clamp(round(input / scale) - offset, qmin, qmax) + offset) * scale  (affine/quantizer.py:566-697)."""
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:   # pylint: disable=redefined-builtin
+        scale, offset = self._encoding_for(input, "QuantizeDequantize")
+        return backend.quantize_dequantize(input, scale, offset, self.qmin, self.qmax, block_size=self.block_size)

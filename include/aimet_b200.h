@@ -236,7 +236,8 @@ int aq_tfe_init_grid(const float* d_minmax, aq_tfe_state_t* d_state, void* strea
  * [0, 512) are dropped.  Replaces GetHistogram_cpu / histogramCountKernel + histogramReduceSumKernel
  * (src/math_functions.cpp:367-384, src/math_functions.cu:125-211).
  * d_hist: 512 uint32 counters, ADDED to (zero them for a fresh batch).  d_count (may be NULL): one int64 that is
- * set to n when the state is initialised and to 0 otherwise (the reference skips such batches). */
+ * set to n when the state is initialised and to 0 otherwise (the reference skips such batches).
+ * d_state must be 16-byte aligned (any block from cudaMalloc is); d_hists rows likewise in aq_tfe_pdf_replay. */
 int aq_tfe_histogram(const float* d_x, int64_t n, const aq_tfe_state_t* d_state, uint32_t* d_hist, int64_t* d_count,
                      void* stream);
 

@@ -7,6 +7,9 @@ oracle/_ref exist; the fixtures are committed so that the tests need neither).
                      quantize / quantize_dequantize / dequantize outputs, clamp masks (from dx with unit grads),
                      and un-reduced-then-summed scale / offset gradients.
 * v2_minmax.npz    - aimet_torch v2 ``MinMaxEncodingAnalyzer`` encodings (CPU).
+* v2_quantizer.npz - aimet_torch v2 ``Quantize`` / ``QuantizeDequantize`` modules (affine/quantizer.py loaded by path,
+                     CPU): outputs inside the calibration context (dynamic encodings), calibrated min / max /
+                     scale / offset, outputs after calibration.
 * libpymo.npz      - the reference DlQuantization CPU code (oracle/_ref): per-tensor QDQ / codes, TF and
                      TF-Enhanced encodings, per-batch histograms, on seeded inputs.
 """
@@ -155,6 +158,77 @@ def gen_v2(ref_root: str):
     np.savez_compressed(os.path.join(HERE, "v2_minmax.npz"), **mm)
 
 
+def load_reference_quantizer(ref_root: str):
+    """Loads aimet_torch/v2/quantization/affine/quantizer.py and what it imports, by path (after load_reference_v2)."""
+    at = os.path.join(ref_root, "TrainingExtensions", "torch", "src", "python", "aimet_torch")
+
+    def load(modname, relpath, pkg=False):
+        path = os.path.join(at, relpath)
+        spec = importlib.util.spec_from_file_location(modname, path,
+                                                      submodule_search_locations=[os.path.dirname(path)] if pkg else None)
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[modname] = mod
+        spec.loader.exec_module(mod)
+        return mod
+
+    q = "aimet_torch.v2.quantization"
+    load(q + ".affine.backends.utils", "v2/quantization/affine/backends/utils.py")
+    load(q + ".affine.backends", "v2/quantization/affine/backends/__init__.py", pkg=True)
+    benc = load(q + ".base.encoding", "v2/quantization/base/encoding.py")
+    base = types.ModuleType(q + ".base")
+    base.__path__ = []
+    sys.modules[q + ".base"] = base
+    base.EncodingBase = benc.EncodingBase
+    base.QuantizerBase = load(q + ".base.quantizer", "v2/quantization/base/quantizer.py").QuantizerBase
+    load(q + ".affine._utils", "v2/quantization/affine/_utils.py")
+    aenc = load(q + ".affine.encoding", "v2/quantization/affine/encoding.py")
+    load(q + ".tensor", "v2/quantization/tensor.py")
+    sys.modules[q + ".affine"].AffineEncoding = aenc.AffineEncoding
+    sys.modules[q + ".affine"].VectorEncoding = getattr(aenc, "VectorEncoding", None)
+    return load(q + ".affine.quantizer", "v2/quantization/affine/quantizer.py")
+
+
+def quantizer_cases():
+    """(name, kind, ctor args, ctor kwargs, calibration batches, probe input)."""
+    g = torch.Generator().manual_seed(77)
+
+    def rnd(*shape, s=1.0):
+        return torch.randn(*shape, generator=g) * s
+
+    return [
+        ("pt_a8", "qdq", ((), 8, False), {}, [rnd(4, 8, 5, 5, s=k) for k in (1.0, 2.5, 0.5)], rnd(4, 8, 5, 5, s=3.0)),
+        ("pt_s4_codes", "q", ((), 4, True), {}, [rnd(64, 33, s=k) for k in (0.3, 0.2)], rnd(64, 33, s=0.4)),
+        ("pc_w8", "qdq", ((6, 1, 1, 1), 8, True), {}, [rnd(6, 4, 3, 3, s=0.2)], rnd(6, 4, 3, 3, s=0.25)),
+        ("pc_axis1_qminqmax", "qdq", ((1, 5, 1, 1), -100, 27, False), {}, [rnd(3, 5, 4, 2, s=k) for k in (1.0, 2.0)],
+         rnd(3, 5, 4, 2, s=2.0)),
+        ("blk_w4", "qdq", ((12, 4), 4, True), {"block_size": (-1, 8)}, [rnd(12, 32, s=0.02)], rnd(12, 32, s=0.03)),
+        ("blk_w4_bf16", "qdq", ((12, 4), 4, True), {"block_size": (1, 8)}, [rnd(12, 32, s=0.02).to(torch.bfloat16)],
+         rnd(12, 32, s=0.03).to(torch.bfloat16)),
+        ("pt_a16", "qdq", ((), 16, False), {}, [rnd(2048, s=k) for k in (1.0, 4.0)], rnd(2048, s=5.0)),
+    ]
+
+
+def gen_quantizer(ref_root: str):
+    load_reference_v2(ref_root)
+    rq = load_reference_quantizer(ref_root)
+    out = {}
+    for name, kind, args, kwargs, batches, probe in quantizer_cases():
+        q = (rq.QuantizeDequantize if kind == "qdq" else rq.Quantize)(*args, **kwargs)
+        with torch.no_grad():
+            with q.compute_encodings():
+                for b, x in enumerate(batches):
+                    out[f"{name}/batch{b}"] = x.float().numpy()
+                    out[f"{name}/dyn{b}"] = q(x).as_subclass(torch.Tensor).float().numpy()
+            out[f"{name}/min"] = q.min.detach().numpy()
+            out[f"{name}/max"] = q.max.detach().numpy()
+            out[f"{name}/scale"] = q.get_scale().detach().numpy()
+            out[f"{name}/offset"] = q.get_offset().detach().numpy()
+            out[f"{name}/probe"] = probe.float().numpy()
+            out[f"{name}/out"] = q(probe).as_subclass(torch.Tensor).float().numpy()
+        out[f"{name}/dtype"] = np.array(str(probe.dtype))
+    np.savez_compressed(os.path.join(HERE, "v2_quantizer.npz"), **out)
+
+
 def gen_libpymo():
     from _data import SPECIALS, conv_weight, normal, relu_activations
     from oracle import Reference, RefAnalyzer
@@ -194,6 +268,7 @@ def gen_libpymo():
 if __name__ == "__main__":
     ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     gen_v2(ref)
+    gen_quantizer(ref)
     gen_libpymo()
-    for f in ("v2_backend.npz", "v2_minmax.npz", "libpymo.npz"):
+    for f in ("v2_backend.npz", "v2_minmax.npz", "v2_quantizer.npz", "libpymo.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
