@@ -164,6 +164,11 @@ class TfEnhancedEncodingAnalyzer(EncodingAnalyzer):
         def __init__(self, shape):
             self.shape = tuple(shape)
 
+    #: Inside a quantizer's calibration context the input passes through unquantized while statistics are taken
+    #: (the analysis mode of the libpymo flow, aimet_torch/v1/qc_quantize_op.py): no per-batch encoding exists for
+    #: these statistics, whose bucket grid is fixed by the first batch.
+    calibration_passthrough = True
+
     def __init__(self, shape: tuple = (1,)):
         shape = (shape,) if isinstance(shape, int) else tuple(shape)
         if math.prod(shape) != 1:

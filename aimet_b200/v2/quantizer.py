@@ -306,6 +306,13 @@ class MinMaxQuantizer(nn.Module):
         offset = torch.zeros_like(scale) if self._symmetric else torch.round(dmin.to(torch.float32) / scale) - self.qmin
         return scale, offset
 
+    def _observe_only(self, x: torch.Tensor) -> bool:
+        """True when the calibration context is open and the analyzer only wants to see the input."""
+        if self._calibrating and getattr(self.encoding_analyzer, "calibration_passthrough", False):
+            self.encoding_analyzer.update_stats(_reshape_for_blocks(x, self.shape, self.block_size))
+            return True
+        return False
+
     def _encoding_for(self, x: torch.Tensor, what: str) -> Tuple[torch.Tensor, torch.Tensor]:
         if self._calibrating:
             return self._dynamic_scale_offset(x)
@@ -319,6 +326,8 @@ class Quantize(MinMaxQuantizer):
     """out = clamp(round(input / scale) - offset, qmin, qmax)  (affine/quantizer.py:440-563)."""
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:   # pylint: disable=redefined-builtin
+        if self._observe_only(input):
+            return input
         scale, offset = self._encoding_for(input, "Quantize")
         return backend.quantize(input, scale, offset, self.qmin, self.qmax, block_size=self.block_size)
 
@@ -327,5 +336,7 @@ class QuantizeDequantize(MinMaxQuantizer):
     """out = (clamp(round(input / scale) - offset, qmin, qmax) + offset) * scale  (affine/quantizer.py:566-697)."""
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:   # pylint: disable=redefined-builtin
+        if self._observe_only(input):
+            return input
         scale, offset = self._encoding_for(input, "QuantizeDequantize")
         return backend.quantize_dequantize(input, scale, offset, self.qmin, self.qmax, block_size=self.block_size)

@@ -527,8 +527,21 @@ def main():
     ap.add_argument("--skip-qdq", action="store_true", help="omit the secondary fake-quant kernel numbers")
     ap.add_argument("--kernel-case", choices=KERNEL_CASES, help="time one kernel alone instead of the calibration job")
     ap.add_argument("--mb", type=int, default=256, help="input size in MB for --kernel-case")
+    ap.add_argument("--model-case", choices=("resnet50", "llama_layer"),
+                    help="whole-model calibration / fake-quant measurement instead of the calibration job")
+    ap.add_argument("--batches", type=int, default=32, help="calibration batches for --model-case resnet50")
+    ap.add_argument("--batch-size", type=int, default=128, help="batch size for --model-case resnet50")
     args = ap.parse_args()
-    if args.kernel_case:
+    if args.model_case:
+        import torch
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py: no CUDA device; the B200 arm has no CPU fallback")
+        from aimet_b200.v2 import model_cases
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        kw = {"batches": args.batches, "batch_size": args.batch_size} if args.model_case == "resnet50" else {}
+        print(json.dumps(model_cases.CASES[args.model_case](dev, **kw)), flush=True)
+    elif args.kernel_case:
         run_kernel_case(args)
     elif args.impl == "reference":
         run_reference(args)
