@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantization-simulation hot path on B200.
 
-Headline workload (BASELINE.json config 3): TF-Enhanced encoding calibration of one quantizer -- per batch a
+Headline workload (benchmark configuration 3): TF-Enhanced encoding calibration of one quantizer -- per batch a
 512-bucket histogram of fp32 activations [64, 256, 28, 28] (ReLU(N(0,1)) with 0.1 % outliers x20), then the
 running-PDF replay and the SQNR grid search for an 8-bit asymmetric encoding.  A step is one batch.  With N GPUs
 every rank calibrates its own K batches (batch b of the job belongs to rank b % N) and the ranks exchange the
@@ -32,7 +32,7 @@ N_EL = 64 * 256 * 28 * 28
 BATCH_BYTES = 4 * N_EL
 MAX_DISTINCT = 256            # distinct device batches kept per GPU (13.2 GB); more steps cycle through them
 METRIC = "TF-Enhanced calibration throughput (512-bin histogram + SQNR search)"
-WORKLOAD = ("BASELINE config 3: TF-Enhanced calibration, fp32 activations [64,256,28,28] = ReLU(N(0,1)) with 0.1% "
+WORKLOAD = ("configuration 3: TF-Enhanced calibration, fp32 activations [64,256,28,28] = ReLU(N(0,1)) with 0.1% "
             "outliers x20, 8-bit asymmetric, 512 buckets")
 # dram__bytes_read+write per algorithmic byte of the histogram kernel, from the ncu capture summarised in
 # profiles/tfe_hist_lane_kernel_relu_256MB.md (captured on a 256 MB input; traffic grows in proportion)
@@ -316,7 +316,7 @@ def run_b200(args):
 
 
 def qdq_numbers(torch, lib, device, peak):
-    """Fake-quant kernels at the BASELINE shapes (configs 1, 2 and 5), raw C-ABI launches over rotating buffers
+    """Fake-quant kernels at the shapes of benchmark configurations 1, 2 and 5, raw C-ABI launches over rotating buffers
     larger than L2, CUDA-event timed."""
     stream = torch.cuda.current_stream().cuda_stream
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -10,6 +10,8 @@ oracle/_ref exist; the fixtures are committed so that the tests need neither).
 * v2_quantizer.npz - aimet_torch v2 ``Quantize`` / ``QuantizeDequantize`` modules (affine/quantizer.py loaded by path,
                      CPU): outputs inside the calibration context (dynamic encodings), calibrated min / max /
                      scale / offset, outputs after calibration.
+* v1_range_learning.npz - aimet_torch v1 learned-grid functions ``calculate_forward_pass`` / ``calculate_gradients``
+                     (v1/quantsim_straight_through_grad.py loaded by path, CPU): outputs, dx, min / max gradients.
 * libpymo.npz      - the reference DlQuantization CPU code (oracle/_ref): per-tensor QDQ / codes, TF and
                      TF-Enhanced encodings, per-batch histograms, on seeded inputs.
 """
@@ -229,6 +231,78 @@ def gen_quantizer(ref_root: str):
     np.savez_compressed(os.path.join(HERE, "v2_quantizer.npz"), **out)
 
 
+def range_learning_cases():
+    """(name, tensor, encoding_min, encoding_max, bitwidth, symmetric, strict, unsigned, channel_axis)."""
+    g = torch.Generator().manual_seed(4242)
+
+    def rnd(*shape, s=1.0):
+        return torch.randn(*shape, generator=g) * s
+
+    x = rnd(5, 6, 7, 3, s=2.0)
+    w = rnd(8, 4, 3, 3, s=0.3)
+    pc_min = -torch.linspace(0.3, 0.9, 8)
+    pc_max = torch.linspace(0.4, 1.0, 8)
+    return [
+        ("pt_a8", x, torch.tensor([-3.3]), torch.tensor([4.1]), 8, False, False, False, 0),
+        ("pt_a4", x, torch.tensor([-1.0]), torch.tensor([2.0]), 4, False, False, False, 0),
+        ("pt_s8", x, torch.tensor([-3.5]), torch.tensor([3.5]), 8, True, False, False, 0),
+        ("pt_s8_strict", x, torch.tensor([-3.5]), torch.tensor([3.5]), 8, True, True, False, 0),
+        ("pt_u8_unsigned_sym", x.abs(), torch.tensor([0.0]), torch.tensor([5.0]), 8, True, False, True, 0),
+        ("pc_w8_sym", w, -pc_max, pc_max, 8, True, False, False, 0),
+        ("pc_w8_asym", w, pc_min, pc_max, 8, False, False, False, 0),
+        ("pc_axis1_a8", x, -torch.linspace(1, 3, 6), torch.linspace(2, 4, 6), 8, False, False, False, 1),
+        ("bias_1d", rnd(8, s=0.5), pc_min, pc_max, 8, False, False, False, 0),
+        ("pt_a16", x, torch.tensor([-6.0]), torch.tensor([7.0]), 16, False, False, False, 0),
+        ("pt_a8_bf16", x.to(torch.bfloat16), torch.tensor([-3.3]).to(torch.bfloat16),
+         torch.tensor([4.1]).to(torch.bfloat16), 8, False, False, False, 0),
+        ("pt_a16_bf16", x.to(torch.bfloat16), torch.tensor([-6.0]).to(torch.bfloat16),
+         torch.tensor([7.0]).to(torch.bfloat16), 16, False, False, False, 0),
+    ]
+
+
+def gen_range_learning(ref_root: str):
+    at = os.path.join(ref_root, "TrainingExtensions", "torch", "src", "python", "aimet_torch")
+    for name in ("aimet_torch", "aimet_torch.v1"):
+        if name not in sys.modules:
+            m = types.ModuleType(name)
+            m.__path__ = []
+            sys.modules[name] = m
+
+    def load(modname, relpath):
+        spec = importlib.util.spec_from_file_location(modname, os.path.join(at, relpath))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[modname] = mod
+        spec.loader.exec_module(mod)
+        return mod
+
+    load("aimet_torch.v1.tensor_factory_utils", "v1/tensor_factory_utils.py")
+    gf = load("aimet_torch.v1.quantsim_straight_through_grad", "v1/quantsim_straight_through_grad.py")
+    out = {}
+    gen = torch.Generator().manual_seed(99)
+    for name, x, emin, emax, bw, sym, strict, unsigned, axis in range_learning_cases():
+        q = types.SimpleNamespace(bitwidth=bw, use_symmetric_encodings=sym, use_strict_symmetric=strict,
+                                  is_unsigned_symmetric=unsigned, channel_axis=axis)
+        gy = torch.randn(x.shape, generator=gen).to(x.dtype)
+        with torch.no_grad():
+            y, inter = gf.calculate_forward_pass(x, q, emin, emax)
+            dx = inter.mask_tensor * gy
+            # the function receives the tensor as the forward pass used it (float32 after the 16-bit upcast)
+            xin = x.float() if (x.dtype != torch.float32 and bw >= 16) else x
+            gin = gy.float() if (x.dtype != torch.float32 and bw >= 16) else gy
+            dmin, dmax = gf.calculate_gradients(xin, gin, inter, axis)
+        out[f"{name}/x"] = x.float().numpy()
+        out[f"{name}/gy"] = gy.float().numpy()
+        out[f"{name}/min"] = emin.float().numpy()
+        out[f"{name}/max"] = emax.float().numpy()
+        out[f"{name}/cfg"] = np.array([bw, int(sym), int(strict), int(unsigned), axis])
+        out[f"{name}/dtype"] = np.array(str(x.dtype))
+        out[f"{name}/y"] = y.float().numpy()
+        out[f"{name}/dx"] = dx.float().numpy()
+        out[f"{name}/dmin"] = dmin.float().numpy()
+        out[f"{name}/dmax"] = dmax.float().numpy()
+    np.savez_compressed(os.path.join(HERE, "v1_range_learning.npz"), **out)
+
+
 def gen_libpymo():
     from _data import SPECIALS, conv_weight, normal, relu_activations
     from oracle import Reference, RefAnalyzer
@@ -269,6 +343,7 @@ if __name__ == "__main__":
     ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     gen_v2(ref)
     gen_quantizer(ref)
+    gen_range_learning(ref)
     gen_libpymo()
-    for f in ("v2_backend.npz", "v2_minmax.npz", "v2_quantizer.npz", "libpymo.npz"):
+    for f in ("v2_backend.npz", "v2_minmax.npz", "v2_quantizer.npz", "v1_range_learning.npz", "libpymo.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
