@@ -48,6 +48,15 @@ class CudaTfeEngine:
     def is_initialized(self) -> bool:
         return self.state.is_initialized()
 
+    def offer_grid(self, x: torch.Tensor) -> bool:
+        """Single-process shortcut: the batch's (min, max) goes straight to the device-side grid setup, which
+        ignores it when the grid exists or the batch is all zeros; nothing waits for the device.  Returns True once
+        the host has learned that the grid exists."""
+        if self.state.poll_initialized():
+            return True
+        self.state.init_grid_from(self.minmax(x))
+        return False
+
     def add_batch(self, x: torch.Tensor, row: int) -> None:
         self.state.add_batch(x, row)
 
@@ -101,7 +110,12 @@ class TfEnhancedCalibrator:
             self.updated = True
         defining_rank = None
         if not self.grid_known:
-            defining_rank = self._agree_on_grid(x)
+            if not self.distributed and x is not None and hasattr(self.engine, "offer_grid"):
+                # no exchange needed: the device decides whether this batch defines the grid (a batch seen while no
+                # grid exists keeps count 0 and is skipped by the replay, exactly like the reference drops it)
+                self.grid_known = self.engine.offer_grid(x)
+            else:
+                defining_rank = self._agree_on_grid(x)
         if x is None:
             return
         row = len(self.local_global_index)

@@ -119,8 +119,10 @@ class _TfEnhancedStats:
             self.dev = ops.TfeDeviceState(x.device)
         self.updated = True
         st = self.dev
-        if not st.is_initialized():
-            # first batch(es): the grid comes from this batch's min/max, unless it is all zeros
+        if not st.poll_initialized():
+            # first batch(es): the grid comes from this batch's min/max, unless it is all zeros.  The device decides
+            # (the grid setup ignores the offer once a grid exists); the host only stops offering when an
+            # asynchronous read of the flag has come back, so no call waits for the GPU.
             self._mm = ops.minmax(x, 1, None, propagate_nan=False, out=self._mm)
             st.init_grid_from(self._mm)
         st.add_batch(x)

@@ -6,7 +6,7 @@ torch stream of the tensor's device.  CPU tensors are rejected: there is no fall
 from __future__ import annotations
 
 import ctypes as C
-from typing import Dict, Optional, Tuple
+from typing import List, Dict, Optional, Tuple
 
 import torch
 
@@ -237,6 +237,28 @@ _INIT_OFF = _lib.AqTfeState.initialized.offset
 _HIST_ROW_BYTES = _lib.AQ_PDF_SIZE * 4
 
 
+_FLAG_POOL: List[torch.Tensor] = []
+_FLAG_NEXT = [0]
+
+
+def _pinned_flag() -> torch.Tensor:
+    """One int32 of pinned host memory for an asynchronous flag read.  Slots come from pooled 4 KiB pinned blocks
+    (pinning memory per object would cost more than the synchronisation the probe avoids) and are handed out
+    round-robin: a probe lives for a few batches, the pool for the process."""
+    if not _FLAG_POOL or _FLAG_NEXT[0] >= _FLAG_POOL[-1].numel():
+        if len(_FLAG_POOL) >= 16:
+            _FLAG_NEXT[0] = 0
+            _FLAG_POOL.append(_FLAG_POOL.pop(0))   # recycle the oldest block
+        else:
+            _FLAG_POOL.append(torch.zeros(1024, dtype=torch.int32).pin_memory())
+            _FLAG_NEXT[0] = 0
+    i = _FLAG_NEXT[0]
+    _FLAG_NEXT[0] = i + 1
+    slot = _FLAG_POOL[-1][i:i + 1]
+    slot.zero_()
+    return slot
+
+
 class TfeDeviceState:
     """Device-resident TF-Enhanced statistics of one quantizer: bucket grid + per-batch histogram rows.
 
@@ -245,19 +267,24 @@ class TfeDeviceState:
     the replay, exactly as the reference drops it.
     """
 
-    def __init__(self, device, capacity: int = 64):
+    def __init__(self, device, capacity: int = 256):
         self.device = torch.device(device)
-        self.state = torch.zeros(_lib.TFE_STATE_BYTES, dtype=torch.uint8, device=self.device)
-        self.pdf = torch.zeros(_lib.AQ_PDF_SIZE, dtype=torch.float64, device=self.device)
-        self.iterations = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.encoding = torch.zeros(5, dtype=torch.float64, device=self.device)
+        # one zero-filled allocation, carved into the state record, the PDF, the result and the iteration count
+        sb = (_lib.TFE_STATE_BYTES + 15) // 16 * 16
+        pb = _lib.AQ_PDF_SIZE * 8
+        blob = torch.zeros(sb + pb + 48 + 16, dtype=torch.uint8, device=self.device)
+        self.state = blob[:_lib.TFE_STATE_BYTES]
+        self.pdf = blob[sb:sb + pb].view(torch.float64)
+        self.encoding = blob[sb + pb:sb + pb + 40].view(torch.float64)
+        self.iterations = blob[sb + pb + 48:sb + pb + 52].view(torch.int32)
         self.num_batches = 0
         self.initialized_on_host = False
         self._alloc_rows(capacity)
 
     def _alloc_rows(self, capacity: int, keep: bool = False):
-        h = torch.zeros((capacity, _lib.AQ_PDF_SIZE), dtype=torch.int32, device=self.device)
-        c = torch.zeros(capacity, dtype=torch.int64, device=self.device)
+        rows = torch.zeros(capacity * (_lib.AQ_PDF_SIZE + 2), dtype=torch.int32, device=self.device)
+        h = rows[:capacity * _lib.AQ_PDF_SIZE].view(capacity, _lib.AQ_PDF_SIZE)
+        c = rows[capacity * _lib.AQ_PDF_SIZE:].view(torch.int64)
         if keep:
             old = self.hists.shape[0]
             h[:old].copy_(self.hists)
@@ -279,6 +306,28 @@ class TfeDeviceState:
         if not self.initialized_on_host:
             self.initialized_on_host = bool(self.state[_INIT_OFF:_INIT_OFF + 4].view(torch.int32).item())
         return self.initialized_on_host
+
+    def poll_initialized(self) -> bool:
+        """Like is_initialized(), but never waits for the device: the flag travels to pinned host memory with an
+        asynchronous copy and the answer is False until a copy that read 1 has completed.  Callers keep offering
+        min/max to init_grid_from() (a no-op on the device once the grid exists) while the answer is False."""
+        if self.initialized_on_host:
+            return True
+        probe = getattr(self, "_probe", None)
+        if probe is not None:
+            flag, event = probe
+            if not event.query():
+                return False
+            if int(flag.item()) == 1:
+                self.initialized_on_host = True
+                self._probe = None
+                return True
+        flag = _pinned_flag() if probe is None else probe[0]
+        flag.copy_(self.state[_INIT_OFF:_INIT_OFF + 4].view(torch.int32), non_blocking=True)
+        event = torch.cuda.Event() if probe is None else probe[1]
+        event.record(torch.cuda.current_stream(self.device))
+        self._probe = (flag, event)
+        return False
 
     def add_batch(self, x: torch.Tensor, row: Optional[int] = None):
         """Histogram of one batch into row ``row`` (default: the next one).  ``x``: dense float32 CUDA tensor."""

@@ -217,6 +217,16 @@ class MinMaxQuantizer(nn.Module):
                 p.mul_(1.0)   # bumps the version: marks the loaded value as initialised
         self._cache = None
 
+    @torch.no_grad()
+    def __deepcopy__(self, memo):
+        # a copied parameter starts a new version count: carry the "has been written" facts over explicitly
+        import copy
+        new = self.__new__(type(self))
+        memo[id(self)] = new
+        new.__dict__ = copy.deepcopy(self.__dict__, memo)
+        new.set_extra_state(self.get_extra_state())
+        return new
+
     # ---- encodings ---------------------------------------------------------------------------------------------
     def _scale_offset(self, dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor]:
         recording = torch.is_grad_enabled() and (self.min.requires_grad or self.max.requires_grad)

@@ -181,7 +181,7 @@ def run_b200(args):
     sampler.start()
 
     # ---- data: this rank's batches (global batch index k * world + rank), resident in HBM -----------------------
-    distinct = min(K, MAX_DISTINCT)
+    distinct = min(max(K, 4), MAX_DISTINCT)   # at least 4 x 51 MB, so that the rotating inputs exceed the 126 MB L2
     batches = [device_batch(k * world + rank, device) for k in range(distinct)]
     torch.cuda.synchronize()
 

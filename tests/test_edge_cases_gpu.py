@@ -1,0 +1,71 @@
+"""Edge cases through the public entry points: empty tensors, pointers that are not 16-byte aligned, one element
+per channel, and sizes around the packet / chunk boundaries -- each against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from _data import assert_bits_equal, normal
+
+pytestmark = pytest.mark.gpu
+
+
+def test_empty_inputs(cuda):
+    import aimet_b200.v2.backend as b200
+    from aimet_b200 import ops
+    from aimet_b200._lib import lib
+    s, o = torch.tensor(0.1, device=cuda), torch.tensor(0.0, device=cuda)
+    for shape in [(0,), (3, 0, 4)]:
+        for dt in (torch.float32, torch.bfloat16):
+            x = torch.empty(shape, device=cuda, dtype=dt)
+            y = b200.quantize_dequantize(x, s, o, -128, 127)
+            assert y.shape == x.shape and y.dtype == dt
+            assert b200.quantize(x, s, o, -128, 127).shape == x.shape
+    mm = ops.minmax(torch.empty(0, device=cuda))
+    assert mm[0].item() == float("inf") and mm[1].item() == float("-inf")
+    # an empty batch leaves the histogram row untouched and records its size
+    st = ops.TfeDeviceState(cuda, capacity=2)
+    st.init_grid_from(torch.tensor([-1.0, 1.0], device=cuda))
+    st.add_batch(torch.empty(0, device=cuda), 0)
+    torch.cuda.synchronize()
+    assert int(st.hists[0].sum()) == 0 and int(st.counts[0]) == 0
+    assert lib.aq_qdq_per_tensor(None, None, 0, -1.0, 1.0, 8, 0, None) == 0
+
+
+@pytest.mark.parametrize("shift", [1, 2, 3])
+@pytest.mark.parametrize("n", [1, 7, 4095, 4096, 4097, 8191, 8193, 100003])
+def test_unaligned_pointers_and_ragged_sizes(cuda, oracle, shift, n):
+    """Slices that start 4, 8 or 12 bytes past a 16-byte boundary take the narrower packet paths."""
+    import aimet_b200.v2.backend as b200
+    from oracle import v2_oracle as v2
+    from aimet_b200 import ops
+    base = normal(n + 8, seed=n + shift, scale=2.0)
+    xd = torch.from_numpy(base).to(cuda)[shift:shift + n]
+    xn = base[shift:shift + n]
+    assert xd.data_ptr() % 16 == 4 * shift
+    sc, of = np.float32(0.0371), np.float32(-120.0)
+    want, _ = v2.quantize_dequantize(xn, np.array(sc), np.array(of), 0, 255, None, "float32")
+    got = b200.quantize_dequantize(xd, torch.tensor(sc, device=cuda), torch.tensor(of, device=cuda), 0, 255)
+    assert_bits_equal(got.cpu().numpy(), want, "v2 qdq")
+    assert_bits_equal(ops.qdq_per_tensor(xd, -3.0, 4.5, 8).cpu().numpy(), oracle.qdq_per_tensor(xn, -3.0, 4.5, 8), "libpymo qdq")
+    mm = ops.minmax(xd).cpu().numpy().reshape(-1)
+    assert mm[0] == xn.min() and mm[1] == xn.max()
+    # histogram of an unaligned batch
+    st = ops.TfeDeviceState(cuda, capacity=1)
+    st.init_grid_from(torch.tensor([float(xn.min()), float(xn.max())], device=cuda))
+    st.add_batch(xd, 0)
+    x_left = oracle.pdf_init(np.float32(xn.min()), np.float32(xn.max()))
+    bs, po = oracle.pdf_geometry(x_left)
+    np.testing.assert_array_equal(st.hists[0].cpu().numpy().astype(np.int64), oracle.hist512(xn, bs, po).astype(np.int64))
+
+
+def test_one_element_per_channel_and_tiny_channels(cuda):
+    import aimet_b200.v2.backend as b200
+    from oracle import v2_oracle as v2
+    for shape, enc in [((64, 1), (64, 1)), ((5, 3), (1, 3)), ((2, 3, 2), (2, 3, 2)), ((1000, 2), (1000, 1))]:
+        x = normal(shape, 3, 0.5)
+        scale = (np.abs(normal(enc, 4, 0.01)) + np.float32(0.002)).astype(np.float32)
+        offset = np.zeros(enc, np.float32)
+        want, _ = v2.quantize_dequantize(x, scale, offset, -8, 7, None, "float32")
+        got = b200.quantize_dequantize(torch.from_numpy(x).to(cuda), torch.from_numpy(scale).to(cuda),
+                                       torch.from_numpy(offset).to(cuda), -8, 7)
+        assert_bits_equal(got.cpu().numpy(), want, f"{shape} / {enc}")

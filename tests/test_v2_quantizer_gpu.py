@@ -106,6 +106,10 @@ def test_initialisation_tracking_and_state_dict():
     r = QuantizeDequantize((2,), 8, False)
     r.load_state_dict(sd)
     assert r.is_initialized() and torch.equal(r.min, q.min) and torch.equal(r.max, q.max)
+    import copy
+    c = copy.deepcopy(q)
+    assert c.is_initialized() and torch.equal(c.min, q.min) and c.min is not q.min
+    assert not copy.deepcopy(QuantizeDequantize((2,), 8, False)).is_initialized()
     fresh = QuantizeDequantize((2,), 8, False)
     r2 = QuantizeDequantize((2,), 8, False)
     r2.load_state_dict(fresh.state_dict())
