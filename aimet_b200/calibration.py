@@ -55,6 +55,7 @@ class CudaTfeEngine:
         if self.state.poll_initialized():
             return True
         self.state.init_grid_from(self.minmax(x))
+        self.state.start_probe()
         return False
 
     def add_batch(self, x: torch.Tensor, row: int) -> None:

@@ -125,6 +125,7 @@ class _TfEnhancedStats:
             # asynchronous read of the flag has come back, so no call waits for the GPU.
             self._mm = ops.minmax(x, 1, None, propagate_nan=False, out=self._mm)
             st.init_grid_from(self._mm)
+            st.start_probe()
         st.add_batch(x)
 
     def compute(self, bw, symmetric, strict, unsigned_sym) -> TfEncoding:

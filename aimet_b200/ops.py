@@ -308,26 +308,27 @@ class TfeDeviceState:
         return self.initialized_on_host
 
     def poll_initialized(self) -> bool:
-        """Like is_initialized(), but never waits for the device: the flag travels to pinned host memory with an
-        asynchronous copy and the answer is False until a copy that read 1 has completed.  Callers keep offering
-        min/max to init_grid_from() (a no-op on the device once the grid exists) while the answer is False."""
+        """Like is_initialized(), but never waits for the device: True once an asynchronous read of the flag
+        (start_probe) that saw 1 has completed.  Callers keep offering min/max to init_grid_from() (a no-op on the
+        device once the grid exists), each offer followed by start_probe(), while the answer is False."""
         if self.initialized_on_host:
             return True
         probe = getattr(self, "_probe", None)
-        if probe is not None:
-            flag, event = probe
-            if not event.query():
-                return False
-            if int(flag.item()) == 1:
-                self.initialized_on_host = True
-                self._probe = None
-                return True
+        if probe is not None and probe[1].query() and int(probe[0].item()) == 1:
+            self.initialized_on_host = True
+            self._probe = None
+        return self.initialized_on_host
+
+    def start_probe(self) -> None:
+        """Queues a copy of the flag, as it is after everything enqueued so far, to pinned host memory."""
+        probe = getattr(self, "_probe", None)
+        if probe is not None and not probe[1].query():
+            return   # the previous read is still in flight
         flag = _pinned_flag() if probe is None else probe[0]
         flag.copy_(self.state[_INIT_OFF:_INIT_OFF + 4].view(torch.int32), non_blocking=True)
         event = torch.cuda.Event() if probe is None else probe[1]
         event.record(torch.cuda.current_stream(self.device))
         self._probe = (flag, event)
-        return False
 
     def add_batch(self, x: torch.Tensor, row: Optional[int] = None):
         """Histogram of one batch into row ``row`` (default: the next one).  ``x``: dense float32 CUDA tensor."""
