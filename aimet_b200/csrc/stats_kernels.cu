@@ -189,6 +189,8 @@ __global__ void __launch_bounds__(256) minmax_rows_kernel(const T* __restrict__ 
                                                           float* __restrict__ part_min, float* __restrict__ part_max,
                                                           int accumulate /* only with direct output */)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane_in_group  = threadIdx.x % GS;
     const int64_t group      = ((int64_t) blockIdx.x * 256 + threadIdx.x) / GS;
     const int64_t num_groups = (int64_t) gridDim.x * 256 / GS;
@@ -279,6 +281,8 @@ __global__ void __launch_bounds__(256) minmax_fold_kernel(const float* __restric
                                                           int64_t num_ch, int nseg, float* __restrict__ out_min,
                                                           float* __restrict__ out_max, int accumulate)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t c = (int64_t) blockIdx.x * 256 + threadIdx.x;
     if (c >= num_ch)
         return;
@@ -321,8 +325,9 @@ static RowsPlan plan_rows(int64_t n, int64_t num_ch, int64_t inner, int vec)
     while (gs < 32 && gs < packs)
         gs <<= 1;
     p.gs = gs;
-    // split long rows so that there are enough (row, segment) items to fill the machine
-    const int64_t target_items = (int64_t) kNumSMs * 8 * (256 / 32) * 2;
+    // Split long rows only when there are too few of them to give every SM half its warps: a split costs a second
+    // launch for the fold, which outweighs the better balance from about 90 MB down.
+    const int64_t target_items = (int64_t) kNumSMs * 32;
     int nseg                   = 1;
     if (gs == 32 && p.rows < target_items)
     {
@@ -396,13 +401,13 @@ static void launch_rows_gs(const T* x, const RowsPlan& p, int64_t inner, float* 
     const int64_t items     = p.rows * p.nseg;
     const int64_t per_block = 256 / p.gs;
     int64_t blocks          = (items + per_block - 1) / per_block;
-    const int64_t cap       = (int64_t) kNumSMs * 8 * 4;
+    const int64_t cap       = (int64_t) kNumSMs * 6;   // one resident wave (6 CTAs of 256 threads per SM at 40 registers)
     if (blocks > cap)
         blocks = cap;
 #define AQ_GS(G)                                                                                                     \
     case G:                                                                                                          \
-        minmax_rows_kernel<T, VEC, G, PROP>                                                                          \
-            <<<(unsigned) blocks, 256, 0, st>>>(x, p.rows, inner, p.nseg, p.seg_len, pmin, pmax, acc);                   \
+        launch_pdl(minmax_rows_kernel<T, VEC, G, PROP>, (unsigned) blocks, 256, 0, st, x, p.rows, inner, p.nseg,     \
+                   p.seg_len, pmin, pmax, acc);                                                                      \
         break;
     switch (p.gs)
     {
@@ -412,8 +417,8 @@ static void launch_rows_gs(const T* x, const RowsPlan& p, int64_t inner, float* 
         AQ_GS(8)
         AQ_GS(16)
     default:
-        minmax_rows_kernel<T, VEC, 32, PROP>
-            <<<(unsigned) blocks, 256, 0, st>>>(x, p.rows, inner, p.nseg, p.seg_len, pmin, pmax, acc);
+        launch_pdl(minmax_rows_kernel<T, VEC, 32, PROP>, (unsigned) blocks, 256, 0, st, x, p.rows, inner, p.nseg,
+                   p.seg_len, pmin, pmax, acc);
     }
 #undef AQ_GS
     note_launch();
@@ -474,8 +479,8 @@ static int minmax_t(const T* x, int64_t n, int64_t num_ch, int64_t inner, float*
     int rc = check_launch();
     if (rc != AQ_OK || p.direct)
         return rc;
-    minmax_fold_kernel<PROP><<<(unsigned) ((num_ch + 255) / 256), 256, 0, st>>>(pmin, pmax, p.outer, num_ch, p.nseg,
-                                                                                out_min, out_max, accumulate);
+    launch_pdl(minmax_fold_kernel<PROP>, (unsigned) ((num_ch + 255) / 256), 256, 0, st, (const float*) pmin,
+               (const float*) pmax, p.outer, num_ch, p.nseg, out_min, out_max, accumulate);
     note_launch();
     return check_launch();
 }
