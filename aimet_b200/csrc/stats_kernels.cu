@@ -555,6 +555,8 @@ int minmax_static(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t i
 __global__ void __launch_bounds__(AQ_PDF_SIZE) tfe_init_grid_kernel(const float* __restrict__ minmax,
                                                                     aq_tfe_state_t* __restrict__ st)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     if (st->initialized)
         return;
     float mn = minmax[0], mx = minmax[1];
@@ -925,7 +927,7 @@ int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t*
 
 int tfe_init_grid(const float* minmax, aq_tfe_state_t* st, cudaStream_t stream)
 {
-    tfe_init_grid_kernel<<<1, AQ_PDF_SIZE, 0, stream>>>(minmax, st);
+    launch_pdl(tfe_init_grid_kernel, 1, AQ_PDF_SIZE, 0, stream, minmax, st);
     note_launch();
     return check_launch();
 }
@@ -963,6 +965,8 @@ __global__ void __launch_bounds__(kReplayThreads) tfe_pdf_replay_kernel(const ui
                                                                         int64_t num_batches, double* __restrict__ pdf,
                                                                         int32_t* __restrict__ iterations)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int CH = kReplayChunk, G = kReplayGroup;
     extern __shared__ __align__(16) unsigned char replay_dyn[];
     uint32_t(*buf)[CH][kReplayThreads] = reinterpret_cast<uint32_t(*)[CH][kReplayThreads]>(replay_dyn);
@@ -1108,9 +1112,8 @@ int tfe_pdf_replay(const uint32_t* hists, const int64_t* counts, int64_t num_bat
         if (dev >= 0 && dev < kMaxDevices)
             attr_set[dev] = true;
     }
-    tfe_pdf_replay_kernel<<<AQ_PDF_SIZE / kReplayThreads, kReplayThreads, kReplaySmem, stream>>>(hists, counts,
-                                                                                                 num_batches, pdf,
-                                                                                                 iterations);
+    launch_pdl(tfe_pdf_replay_kernel, AQ_PDF_SIZE / kReplayThreads, kReplayThreads, kReplaySmem, stream, hists, counts,
+               num_batches, pdf, iterations);
     note_launch();
     return check_launch();
 }

@@ -92,6 +92,8 @@ struct SearchArgs
 
 __global__ void __launch_bounds__(kSearchWarps * 32) tfe_search_kernel(SearchArgs a)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slot = blockIdx.x * kSearchWarps + warp;
     __shared__ double s_term[kSearchWarps][AQ_PDF_SIZE];   // bottom-saturation or in-range term of a bucket
@@ -346,7 +348,7 @@ int tfe_search(const aq_tfe_state_t* st, const double* pdf, int stats_updated, i
     a.steps         = (float) (pow(2.0, (double) bw) - 1.0);
     a.slots         = symmetric ? kSymSlots : kAsymSlots;
     const int grid  = (a.slots + kSearchWarps - 1) / kSearchWarps;
-    tfe_search_kernel<<<grid, kSearchWarps * 32, 0, stream>>>(a);
+    launch_pdl(tfe_search_kernel, (unsigned) grid, kSearchWarps * 32, 0, stream, a);
     note_launch();
     return check_launch();
 }
