@@ -31,6 +31,10 @@ from .libpymo import TfEncoding
 class CudaTfeEngine:
     """TF-Enhanced statistics of one quantizer on one GPU (kernels through the C ABI)."""
 
+    #: rows are addressed by GLOBAL batch index: a rank's rows sit where the merged table wants them (the rows of
+    #: other ranks stay zero), so the exchange is an all-reduce of the table itself, with nothing to pack or unpack
+    global_rows = True
+
     def __init__(self, device):
         from . import ops   # needs the CUDA library; imported here so that CPU-only protocol tests can run
         self._ops = ops
@@ -71,6 +75,12 @@ class CudaTfeEngine:
     def rows(self) -> Tuple[torch.Tensor, torch.Tensor]:
         n = self.state.num_batches
         return self.state.hists[:n], self.state.counts[:n]
+
+    def exchange_views(self, n_total: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The first n_total rows of the histogram table and of the counts, as the tensors to all-reduce in place."""
+        self.state.reserve(n_total)
+        self.state.num_batches = n_total
+        return self.state.hists[:n_total], self.state.counts[:n_total]
 
     def load_rows(self, hists: torch.Tensor, counts: torch.Tensor) -> None:
         n = hists.shape[0]
@@ -119,7 +129,7 @@ class TfEnhancedCalibrator:
                 defining_rank = self._agree_on_grid(x)
         if x is None:
             return
-        row = len(self.local_global_index)
+        row = g if getattr(self.engine, "global_rows", False) else len(self.local_global_index)
         self.local_global_index.append(g)
         if defining_rank is not None and self.rank < defining_rank:
             # an all-zero batch that precedes, in global order, the batch that defines the grid: the sequential
@@ -131,18 +141,26 @@ class TfEnhancedCalibrator:
 
     def _agree_on_grid(self, x: Optional[torch.Tensor]) -> Optional[int]:
         """Returns the rank whose batch of this round defines the grid, or None if no batch of the round can."""
+        bufs = getattr(self, "_grid_bufs", None)
+        if bufs is None:
+            # (min, max, present) of this rank, and the gathered table; allocated once
+            bufs = (torch.zeros(3, dtype=torch.float32, device=self.device),
+                    torch.empty(self.world * 3, dtype=torch.float32, device=self.device))
+            self._grid_bufs = bufs
+        mine, flat = bufs
         if x is not None:
-            mm = self.engine.minmax(x).to(torch.float32)
-            mine = torch.cat([mm.reshape(2), torch.ones(1, dtype=torch.float32, device=mm.device)])
+            mine[:2].copy_(self.engine.minmax(x).reshape(2))
+            mine[2:].fill_(1.0)
         else:
-            mine = torch.zeros(3, dtype=torch.float32, device=self.device)
+            mine.zero_()
         if self.distributed:
-            flat = torch.empty(self.world * 3, dtype=torch.float32, device=mine.device)
-            dist.all_gather_into_tensor(flat, mine.contiguous(), group=self.group)
+            dist.all_gather_into_tensor(flat, mine, group=self.group)
             table = flat.view(self.world, 3)
         else:
             table = mine.reshape(1, 3)
         t = table.cpu()
+        if not hasattr(self, "_any_present"):
+            self._any_present = bool(t[:, 2].any())   # first round: a rank without data now never gets any
         for r in range(self.world):   # global order inside the round == rank order
             mn, mx, present = t[r].tolist()
             if present and not (mn == 0.0 and mx == 0.0):
@@ -157,6 +175,20 @@ class TfEnhancedCalibrator:
         if self.distributed and getattr(self, "_merged", None) is not None:
             # the tables were exchanged by an earlier call; every rank already holds all rows
             enc = eng.encoding(self._merged, bw, symmetric, strict, unsigned_sym)
+        elif self.distributed and getattr(eng, "global_rows", False):
+            # The engine keeps its rows at their global indices, zero elsewhere: the merged table is the element-wise
+            # sum over ranks of the tables themselves.  All ranks have called update() the same number of times, so
+            # the row count needs no agreement; whether any rank saw data is known from the first round's exchange.
+            n_total = self.round * self.world
+            if n_total:
+                h, c = eng.exchange_views(n_total)
+                dist.all_reduce(h, op=dist.ReduceOp.SUM, group=self.group)
+                dist.all_reduce(c, op=dist.ReduceOp.SUM, group=self.group)
+            any_updated = bool(getattr(self, "_any_present", False) or self.updated)
+            self._merged = any_updated
+            enc = eng.encoding(any_updated, bw, symmetric, strict, unsigned_sym).clone()
+            dist.broadcast(enc, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
+                           group=self.group)
         elif self.distributed:
             # One exchange: a zero-padded int32 buffer holding [n_total, 512] histogram rows, then the n_total int64
             # counts (as int32 pairs), then the number of ranks that saw data.  Every row is non-zero on exactly one

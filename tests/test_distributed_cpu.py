@@ -74,6 +74,49 @@ class OracleEngine:
         return torch.from_numpy(a.compute(bw, symmetric, strict, unsigned_sym))
 
 
+class GlobalRowsOracleEngine(OracleEngine):
+    """Same stand-in, but keeping its rows at their global indices in one dense table, like the CUDA engine does:
+    exercises the exchange that all-reduces the table in place."""
+    global_rows = True
+
+    def __init__(self):
+        super().__init__()
+        self.table = torch.zeros((0, 512), dtype=torch.int32)
+        self.counts = torch.zeros(0, dtype=torch.int64)
+
+    def _reserve(self, n):
+        if n > self.table.shape[0]:
+            t, c = torch.zeros((n, 512), dtype=torch.int32), torch.zeros(n, dtype=torch.int64)
+            t[:self.table.shape[0]], c[:self.counts.shape[0]] = self.table, self.counts
+            self.table, self.counts = t, c
+
+    def add_batch(self, x, row):
+        self._reserve(row + 1)
+        if self.x_left is None:
+            return
+        bs, po = self.o.pdf_geometry(self.x_left)
+        self.table[row] = torch.from_numpy(self.o.hist512(x.numpy(), bs, po).astype(np.int32))
+        self.counts[row] = x.numel()
+
+    def add_empty_row(self, row):
+        self._reserve(row + 1)
+
+    def num_rows(self):
+        return self.table.shape[0]
+
+    def exchange_views(self, n_total):
+        self._reserve(n_total)
+        return self.table[:n_total], self.counts[:n_total]
+
+    def encoding(self, stats_updated, bw, symmetric, strict, unsigned_sym):
+        self.h = [r.numpy().astype(np.int64) for r in self.table]
+        self.c = self.counts.tolist()
+        return super().encoding(stats_updated, bw, symmetric, strict, unsigned_sym)
+
+
+ENGINES = {"packed": OracleEngine, "in_place": GlobalRowsOracleEngine}
+
+
 def make_batches(scenario):
     if scenario == "relu":
         return [relu_activations(3000 + 17 * b, 1000 + b) for b in range(7)]
@@ -92,13 +135,13 @@ def sequential(batches, bw, flags):
     return a.compute(bw, *flags)
 
 
-def _worker(rank, world, port, scenario, out):
+def _worker(rank, world, port, scenario, out, engine="packed"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from aimet_b200.calibration import TfEnhancedCalibrator
         batches = make_batches(scenario)
-        cal = TfEnhancedCalibrator("cpu", engine=OracleEngine())
+        cal = TfEnhancedCalibrator("cpu", engine=ENGINES[engine]())
         rounds = (len(batches) + world - 1) // world
         for k in range(rounds):
             g = k * world + rank
@@ -118,12 +161,13 @@ def _free_port():
         return s.getsockname()[1]
 
 
+@pytest.mark.parametrize("engine", ["packed", "in_place"])
 @pytest.mark.parametrize("world", [2, 3])
 @pytest.mark.parametrize("scenario", ["relu", "zeros_first", "all_zero"])
-def test_sharded_tf_enhanced_equals_sequential(world, scenario):
+def test_sharded_tf_enhanced_equals_sequential(world, scenario, engine):
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), scenario, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), scenario, out, engine), nprocs=world, join=True)
     batches = make_batches(scenario)
     want = [sequential(batches, bw, flags) for bw, flags in
             ((8, (False, False, False)), (8, (True, False, False)), (4, (True, True, False)))]
