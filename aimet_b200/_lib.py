@@ -16,6 +16,7 @@ AQ_OK = 0
 AQ_F32, AQ_F16, AQ_BF16 = 0, 1, 2
 AQ_V2_OUT_QDQ, AQ_V2_OUT_CODES = 0, 1
 AQ_PDF_SIZE = 512
+AQ_TFE_HIST_MANY = 16
 
 
 class AqEncoding(C.Structure):
@@ -57,9 +58,15 @@ SIGNATURES = {
     "aq_minmax_static": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _i32, _vp]),
     "aq_tfe_init_grid": (_i32, [_vp, _vp, _vp]),
     "aq_tfe_histogram": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp]),
+    "aq_tfe_histogram_many": (_i32, [C.POINTER(_vp), C.POINTER(_i64), _i32, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "aq_tfe_offer_grid_workspace_bytes": (_i64, []),
+    "aq_tfe_offer_grid": (_i32, [_vp, _i64, _vp, _vp, _i32, _vp, _i64, _vp]),
+    "aq_tfe_select_grid": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp]),
     "aq_tfe_pdf_replay": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp]),
     "aq_tfe_search_workspace_bytes": (_i64, []),
     "aq_tfe_search": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _vp]),
+    "aq_tfe_compute_encoding": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i64,
+                                       _vp]),
 }
 
 

@@ -8,19 +8,22 @@ result is bit-identical to the sequential reference run:
 * MinMax: every rank keeps a running min/max, one all-reduce(MIN) and one all-reduce(MAX) combine them (exact,
   order independent).
 * TF-Enhanced: the bucket grid is defined by the first batch, in global order, whose (min, max) is not (0, 0)
-  (DlQuantization/src/math_functions.cpp:248-262).  The ranks all-gather the (min, max) of their first batches
-  until such a batch is found.  Each rank then histograms its own batches into per-batch rows; at the end one
-  all-reduce(SUM) over the zero-padded [num_batches, 512] integer table gives every rank every batch's exact
+  (DlQuantization/src/math_functions.cpp:248-262).  Per round the ranks all-gather the (min, max, present) triple of
+  their batch and every rank's device picks the defining batch from the gathered table (no host read); the rounds
+  with an exchange end as soon as the host has learned, from an asynchronous read, that the grid exists.  Each rank
+  histograms its own batches into rows at their GLOBAL batch indices; at the end ONE all-reduce(SUM) over the
+  ``[num_batches, 512]`` integer table, the 64-bit counts and a flag word gives every rank every batch's exact
   histogram, and the reference's floating-point running mean (math_functions.cpp:278-287) is replayed in global
   batch order before the SQNR search.  (Summing histograms first would not reproduce the running mean bit for
-  bit.)  The encoding is finally broadcast from rank 0.
+  bit.)  All ranks hold identical rows and run identical arithmetic, so every rank ends with the same encoding and
+  nothing is broadcast.
 
 The arithmetic lives behind a small engine interface so that the exchange protocol can be tested on CPU ranks
 (gloo) with a stand-in engine; the product engine is ``CudaTfeEngine`` and runs everything on the device.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -29,69 +32,60 @@ from .libpymo import TfEncoding
 
 
 class CudaTfeEngine:
-    """TF-Enhanced statistics of one quantizer on one GPU (kernels through the C ABI)."""
+    """TF-Enhanced statistics of one quantizer on one GPU (kernels through the C ABI).
 
-    #: rows are addressed by GLOBAL batch index: a rank's rows sit where the merged table wants them (the rows of
-    #: other ranks stay zero), so the exchange is an all-reduce of the table itself, with nothing to pack or unpack
-    global_rows = True
+    Engine interface (what ``TfEnhancedCalibrator`` needs; the CPU stand-in of the protocol tests has the same):
+    ``reserve``, ``mark_updated``, ``offer_grid``, ``grid_known``, ``batch_range``, ``select_grid``, ``add_batch``,
+    ``add_batches``, ``exchange_buffer``, ``encoding``.
+    """
 
-    def __init__(self, device):
+    def __init__(self, device, capacity: int = 256):
         from . import ops   # needs the CUDA library; imported here so that CPU-only protocol tests can run
         self._ops = ops
         self.device = torch.device(device)
-        self.state = ops.TfeDeviceState(self.device)
-        self._mm: Optional[torch.Tensor] = None
+        self.state = ops.TfeDeviceState(self.device, capacity)
+        self._marked = False
 
-    def minmax(self, x: torch.Tensor) -> torch.Tensor:
-        self._mm = self._ops.minmax(x, 1, None, propagate_nan=False, out=self._mm)
-        return self._mm.reshape(-1)
+    def reserve(self, rows: int) -> None:
+        self.state.reserve(rows)
 
-    def init_grid(self, minmax: torch.Tensor) -> None:
-        self.state.init_grid_from(minmax.to(self.device, torch.float32).contiguous())
+    def mark_updated(self) -> None:
+        """Sets the device-side "this rank offered a batch" flag (summed over ranks by the exchange)."""
+        if not self._marked:
+            self.state.flags[0:1].fill_(1)
+            self._marked = True
 
-    def is_initialized(self) -> bool:
-        return self.state.is_initialized()
-
-    def offer_grid(self, x: torch.Tensor) -> bool:
-        """Single-process shortcut: the batch's (min, max) goes straight to the device-side grid setup, which
-        ignores it when the grid exists or the batch is all zeros; nothing waits for the device.  Returns True once
-        the host has learned that the grid exists."""
-        if self.state.poll_initialized():
-            return True
-        self.state.init_grid_from(self.minmax(x))
+    def offer_grid(self, x: torch.Tensor) -> None:
+        """The batch's (min, max) goes straight to the device-side grid setup, which ignores it when the grid exists
+        or the batch is all zeros; nothing waits for the device."""
+        self.state.offer_grid(x)
         self.state.start_probe()
-        return False
 
-    def add_batch(self, x: torch.Tensor, row: int) -> None:
-        self.state.add_batch(x, row)
+    def grid_known(self, wait: bool = False) -> bool:
+        """Whether the HOST has learned that the grid exists (never waits for the device unless ``wait``)."""
+        return self.state.poll_initialized(wait)
 
-    def add_empty_row(self, row: int) -> None:
-        self.state.reserve(row + 1)   # rows are zero-filled; count 0 marks the batch as dropped
-        self.state.num_batches = max(self.state.num_batches, row + 1)
+    def batch_range(self, x: Optional[torch.Tensor]) -> torch.Tensor:
+        return self.state.batch_range(x)
 
-    def num_rows(self) -> int:
-        return self.state.num_batches
+    def select_grid(self, ranges: torch.Tensor, num_ranks: int, rank: int) -> None:
+        self.state.select_grid(ranges, num_ranks, rank)
+        self.state.start_probe()
 
-    def rows(self) -> Tuple[torch.Tensor, torch.Tensor]:
-        n = self.state.num_batches
-        return self.state.hists[:n], self.state.counts[:n]
+    def add_batch(self, x: torch.Tensor, row: int, gated: bool = False) -> None:
+        self.state.add_batch(x, row, gated)
 
-    def exchange_views(self, n_total: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        """The first n_total rows of the histogram table and of the counts, as the tensors to all-reduce in place."""
-        self.state.reserve(n_total)
-        self.state.num_batches = n_total
-        return self.state.hists[:n_total], self.state.counts[:n_total]
+    def add_batches(self, xs: Sequence[torch.Tensor], row0: int, row_stride: int) -> None:
+        self.state.add_batches(xs, row0, row_stride)
 
-    def load_rows(self, hists: torch.Tensor, counts: torch.Tensor) -> None:
-        n = hists.shape[0]
-        self.state.reserve(n)
-        self.state.hists[:n].copy_(hists)
-        self.state.counts[:n].copy_(counts)
-        self.state.num_batches = n
+    def exchange_buffer(self, n_total: int) -> torch.Tensor:
+        """The dense int32 buffer to all-reduce in place: n_total rows, their counts, the flag words."""
+        self.state.resize_exact(n_total)
+        return self.state.buffer
 
-    def encoding(self, stats_updated: bool, bw: int, symmetric: bool, strict: bool, unsigned_sym: bool) -> torch.Tensor:
-        self.state.replay()
-        return self.state.search(stats_updated, bw, symmetric, strict, unsigned_sym)
+    def encoding(self, stats_updated, bw: int, symmetric: bool, strict: bool, unsigned_sym: bool,
+                 num_rows: Optional[int] = None) -> torch.Tensor:
+        return self.state.compute_encoding(stats_updated, bw, symmetric, strict, unsigned_sym, num_rows)
 
 
 class TfEnhancedCalibrator:
@@ -99,123 +93,127 @@ class TfEnhancedCalibrator:
 
     Every rank calls ``update(x)`` once per calibration round, in the same order (round k holds global batches
     k * world_size ... k * world_size + world_size - 1; rank r feeds batch k * world_size + r).  A rank that has no
-    batch left in the last round passes ``None``.
+    batch left in the last round passes ``None``.  ``update_many(xs)`` feeds several rounds at once when the batches
+    are resident already; every rank must pass the same number of rounds.  ``num_batches`` (the job's total over all
+    ranks, when known) sizes the row table once instead of growing it during the job.
     """
 
-    def __init__(self, device, group=None, engine=None):
+    def __init__(self, device, group=None, engine=None, num_batches: Optional[int] = None):
         self.device = torch.device(device)
         self.group = group
         self.distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
         self.rank = dist.get_rank(group) if self.distributed else 0
         self.world = dist.get_world_size(group) if self.distributed else 1
-        self.engine = engine if engine is not None else CudaTfeEngine(self.device)
+        cap = int(num_batches) if num_batches else 256
+        self.engine = engine if engine is not None else CudaTfeEngine(self.device, cap)
+        if engine is not None and num_batches:
+            self.engine.reserve(int(num_batches))
         self.round = 0
         self.updated = False
-        self.grid_known = False
-        self.local_global_index: List[int] = []   # global batch index of each local row
+        self._merged = False
+        self._known = False       # host knowledge that the grid exists (same on every rank in every round)
+        self._gathered = None     # [world, 3] table of the grid agreement, allocated once
+        self._host_table = None
+        self._table_read = None   # (pinned copy of the table, event) of the previous round, not yet looked at
+
+    # ---- statistics ---------------------------------------------------------------------------------------------
+    def _grid_known(self, wait: bool = False) -> bool:
+        """Whether this rank's HOST knows that the grid exists.  With several ranks the answer must be the same on
+        every rank in every round (it decides whether the round has a collective), so it is derived from the gathered
+        table of the previous round -- identical everywhere -- whose copy to pinned memory was queued before that
+        round's histogram: by the time it is waited for, the device is busy with that histogram."""
+        if self._known:
+            return True
+        if not self.distributed:
+            self._known = self.engine.grid_known(wait)
+            return self._known
+        pending = self._table_read
+        if pending is None:
+            return False
+        host, event = pending
+        if event is not None:
+            event.synchronize()
+        self._table_read = None
+        for r in range(self.world):   # global order inside the round == rank order
+            mn, mx, present = host[3 * r:3 * r + 3].tolist()
+            if present and not (mn == 0.0 and mx == 0.0):
+                self._known = True
+                break
+        return self._known
+
+    def _exchange_round(self, x: Optional[torch.Tensor], row: int) -> None:
+        """One round with grid agreement: the device decides (no host read in between) which batch of the round
+        defines the grid and whether this rank's batch counts."""
+        eng = self.engine
+        mine = eng.batch_range(x)
+        if self._gathered is None:
+            cuda = self.device.type == "cuda"
+            self._gathered = torch.empty(self.world * 3, dtype=torch.float32, device=self.device)
+            self._host_table = torch.empty(self.world * 3, dtype=torch.float32, pin_memory=cuda)
+        dist.all_gather_into_tensor(self._gathered, mine, group=self.group)
+        eng.select_grid(self._gathered, self.world, self.rank)
+        self._host_table.copy_(self._gathered, non_blocking=True)
+        event = None
+        if self.device.type == "cuda":
+            event = torch.cuda.Event()
+            event.record(torch.cuda.current_stream(self.device))
+        self._table_read = (self._host_table, event)
+        if x is not None:
+            eng.add_batch(x, row, gated=True)
 
     def update(self, x: Optional[torch.Tensor]) -> None:
-        g = self.round * self.world + self.rank
+        eng = self.engine
+        row = self.round * self.world + self.rank
         self.round += 1
-        if x is not None:
+        if x is not None and not self.updated:
             self.updated = True
-        defining_rank = None
-        if not self.grid_known:
-            if not self.distributed and x is not None and hasattr(self.engine, "offer_grid"):
-                # no exchange needed: the device decides whether this batch defines the grid (a batch seen while no
-                # grid exists keeps count 0 and is skipped by the replay, exactly like the reference drops it)
-                self.grid_known = self.engine.offer_grid(x)
-            else:
-                defining_rank = self._agree_on_grid(x)
-        if x is None:
+            eng.mark_updated()
+        if self._grid_known():
+            if x is not None:
+                eng.add_batch(x, row)
+        elif self.distributed:
+            self._exchange_round(x, row)
+        elif x is not None:
+            # no exchange needed: the device decides whether this batch defines the grid (a batch seen while no
+            # grid exists keeps count 0 and is skipped by the replay, exactly like the reference drops it)
+            eng.offer_grid(x)
+            eng.add_batch(x, row)
+
+    def update_many(self, xs: Sequence[torch.Tensor]) -> None:
+        """``len(xs)`` consecutive rounds.  Until the host knows that the grid exists the batches go one by one
+        (each launch must see the state its predecessors left); after that, many per launch."""
+        i = 0
+        while i < len(xs) and not self._grid_known():
+            self.update(xs[i])
+            i += 1
+            # wait for the read queued behind the grid setup -- the device meanwhile works on the histogram that was
+            # queued behind it, so this costs the host a few microseconds and the device nothing
+            self._grid_known(wait=True)
+        rest = xs[i:]
+        if not len(rest):
             return
-        row = g if getattr(self.engine, "global_rows", False) else len(self.local_global_index)
-        self.local_global_index.append(g)
-        if defining_rank is not None and self.rank < defining_rank:
-            # an all-zero batch that precedes, in global order, the batch that defines the grid: the sequential
-            # reference dropped it before the grid existed, so it must not be counted now either
-            self.engine.add_empty_row(row)
-        else:
-            # (a batch seen while no grid exists at all keeps count 0 and is skipped by the replay)
-            self.engine.add_batch(x, row)
+        if not self.updated:
+            self.updated = True
+            self.engine.mark_updated()
+        row0 = self.round * self.world + self.rank
+        self.round += len(rest)
+        self.engine.add_batches(rest, row0, self.world)
 
-    def _agree_on_grid(self, x: Optional[torch.Tensor]) -> Optional[int]:
-        """Returns the rank whose batch of this round defines the grid, or None if no batch of the round can."""
-        bufs = getattr(self, "_grid_bufs", None)
-        if bufs is None:
-            # (min, max, present) of this rank, and the gathered table; allocated once
-            bufs = (torch.zeros(3, dtype=torch.float32, device=self.device),
-                    torch.empty(self.world * 3, dtype=torch.float32, device=self.device))
-            self._grid_bufs = bufs
-        mine, flat = bufs
-        if x is not None:
-            mine[:2].copy_(self.engine.minmax(x).reshape(2))
-            mine[2:].fill_(1.0)
-        else:
-            mine.zero_()
-        if self.distributed:
-            dist.all_gather_into_tensor(flat, mine, group=self.group)
-            table = flat.view(self.world, 3)
-        else:
-            table = mine.reshape(1, 3)
-        t = table.cpu()
-        if not hasattr(self, "_any_present"):
-            self._any_present = bool(t[:, 2].any())   # first round: a rank without data now never gets any
-        for r in range(self.world):   # global order inside the round == rank order
-            mn, mx, present = t[r].tolist()
-            if present and not (mn == 0.0 and mx == 0.0):
-                self.engine.init_grid(table[r, :2].contiguous())
-                self.grid_known = True
-                return r
-        return None
-
+    # ---- encoding -----------------------------------------------------------------------------------------------
     def compute_encoding(self, bw: int, symmetric: bool = False, strict: bool = False,
                          unsigned_sym: bool = False) -> TfEncoding:
         eng = self.engine
-        if self.distributed and getattr(self, "_merged", None) is not None:
-            # the tables were exchanged by an earlier call; every rank already holds all rows
-            enc = eng.encoding(self._merged, bw, symmetric, strict, unsigned_sym)
-        elif self.distributed and getattr(eng, "global_rows", False):
-            # The engine keeps its rows at their global indices, zero elsewhere: the merged table is the element-wise
-            # sum over ranks of the tables themselves.  All ranks have called update() the same number of times, so
-            # the row count needs no agreement; whether any rank saw data is known from the first round's exchange.
+        if self.distributed:
+            # All ranks have called update() the same number of times, so the row count needs no agreement.  Every
+            # row is non-zero on exactly one rank, so the element-wise integer sum reproduces each batch's exact
+            # histogram and 64-bit count on every rank; the flag word sums to the number of ranks that saw data.
             n_total = self.round * self.world
-            if n_total:
-                h, c = eng.exchange_views(n_total)
-                dist.all_reduce(h, op=dist.ReduceOp.SUM, group=self.group)
-                dist.all_reduce(c, op=dist.ReduceOp.SUM, group=self.group)
-            any_updated = bool(getattr(self, "_any_present", False) or self.updated)
-            self._merged = any_updated
-            enc = eng.encoding(any_updated, bw, symmetric, strict, unsigned_sym).clone()
-            dist.broadcast(enc, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
-                           group=self.group)
-        elif self.distributed:
-            # One exchange: a zero-padded int32 buffer holding [n_total, 512] histogram rows, then the n_total int64
-            # counts (as int32 pairs), then the number of ranks that saw data.  Every row is non-zero on exactly one
-            # rank, so the element-wise integer sum reproduces each row and each 64-bit count exactly.  n_total needs
-            # no agreement step: all ranks have called update() the same number of times.
-            dev = self.device
-            n_local = eng.num_rows()
-            n_total = self.round * self.world
-            buf = torch.zeros(n_total * 514 + 2, dtype=torch.int32, device=dev)
-            hists = buf[:n_total * 512].view(n_total, 512)
-            counts = buf[n_total * 512:n_total * 514].view(torch.int64)
-            if n_local:
-                idx = torch.tensor(self.local_global_index, dtype=torch.int64, device=dev)
-                h, c = eng.rows()
-                hists.index_copy_(0, idx, h)
-                counts.index_copy_(0, idx, c)
-            if self.updated:
-                buf[-2:].fill_(1)
-            dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
-            eng.load_rows(hists, counts)
-            any_updated = bool(buf[-1].item())
-            self._merged = any_updated   # statistics are final from here on (further update() calls are not merged)
-            enc = eng.encoding(any_updated, bw, symmetric, strict, unsigned_sym).clone()
-            dist.broadcast(enc, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
-                           group=self.group)
+            if not self._merged:
+                dist.all_reduce(eng.exchange_buffer(n_total), op=dist.ReduceOp.SUM, group=self.group)
+                self._merged = True   # statistics are final from here on (further update() calls are not merged)
+            enc = eng.encoding(None, bw, symmetric, strict, unsigned_sym, n_total)
         else:
-            enc = eng.encoding(self.updated, bw, symmetric, strict, unsigned_sym)
+            enc = eng.encoding(self.updated, bw, symmetric, strict, unsigned_sym, self.round)
         e = enc.tolist()
         return TfEncoding(e[0], e[1], e[2], e[3], int(e[4]))
 

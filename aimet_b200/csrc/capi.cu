@@ -369,7 +369,52 @@ int aq_tfe_histogram(const float* d_x, int64_t n, const aq_tfe_state_t* d_state,
         return AQ_ERR_INVALID_ARG;   // the kernels use 16-byte loads of the state
     if (n > 0x7fffffffLL)
         return AQ_ERR_TOO_LARGE;   // the reference counts elements in an int; so does the PDF replay
-    return tfe_histogram(d_x, n, d_state, d_hist, d_count, (cudaStream_t) stream);
+    return tfe_histogram(d_x, n, d_state, d_hist, d_count, nullptr, (cudaStream_t) stream);
+}
+
+int aq_tfe_histogram_many(const float* const* h_d_x, const int64_t* h_n, int m, int64_t row_stride,
+                          const aq_tfe_state_t* d_state, uint32_t* d_hists, int64_t* d_counts, const int32_t* d_gate,
+                          void* stream)
+{
+    if (m < 1 || m > AQ_TFE_HIST_MANY || row_stride < 1 || !h_d_x || !h_n || !d_state || !d_hists)
+        return AQ_ERR_INVALID_ARG;
+    if (((uintptr_t) d_state % 16) || ((uintptr_t) d_hists % 4) || ((uintptr_t) d_counts % 8) || ((uintptr_t) d_gate % 4))
+        return AQ_ERR_INVALID_ARG;
+    for (int b = 0; b < m; ++b)
+    {
+        if (h_n[b] < 0 || (h_n[b] > 0 && !h_d_x[b]) || ((uintptr_t) h_d_x[b] % 4))
+            return AQ_ERR_INVALID_ARG;
+        if (h_n[b] > 0x7fffffffLL)
+            return AQ_ERR_TOO_LARGE;
+    }
+    return tfe_histogram_many(h_d_x, h_n, m, row_stride, d_state, d_hists, d_counts, d_gate, (cudaStream_t) stream);
+}
+
+int64_t aq_tfe_offer_grid_workspace_bytes(void)
+{
+    return 256 + (int64_t) kNumSMs * 4 * (int64_t) sizeof(float2);
+}
+
+int aq_tfe_offer_grid(const float* d_x, int64_t n, aq_tfe_state_t* d_state, float* d_range, int init,
+                      void* d_workspace, int64_t workspace_bytes, void* stream)
+{
+    if (n < 0 || (n > 0 && !d_x) || !d_state || ((uintptr_t) d_x % 4) || ((uintptr_t) d_state % 16) ||
+        ((uintptr_t) d_range % 4))
+        return AQ_ERR_INVALID_ARG;
+    if (n > 0x7fffffffLL)
+        return AQ_ERR_TOO_LARGE;
+    if (!d_workspace || ((uintptr_t) d_workspace % 256) != 0)
+        return AQ_ERR_WORKSPACE;
+    return tfe_offer_grid(d_x, n, d_state, d_range, init, d_workspace, workspace_bytes, (cudaStream_t) stream);
+}
+
+int aq_tfe_select_grid(const float* d_ranges, int num_ranks, int rank, aq_tfe_state_t* d_state, int32_t* d_gate,
+                       void* stream)
+{
+    if (!d_ranges || num_ranks < 1 || rank < 0 || rank >= num_ranks || !d_state || !d_gate ||
+        ((uintptr_t) d_ranges % 4) || ((uintptr_t) d_state % 16) || ((uintptr_t) d_gate % 4))
+        return AQ_ERR_INVALID_ARG;
+    return tfe_select_grid(d_ranges, num_ranks, rank, d_state, d_gate, (cudaStream_t) stream);
 }
 
 int aq_tfe_pdf_replay(const uint32_t* d_hists, const int64_t* d_counts, int64_t num_batches, double* d_pdf,
@@ -395,8 +440,24 @@ int aq_tfe_search(const aq_tfe_state_t* d_state, const double* d_pdf, int stats_
         return AQ_ERR_INVALID_ARG;
     if (!d_workspace || ((uintptr_t) d_workspace % 256) != 0)
         return AQ_ERR_WORKSPACE;
-    return tfe_search(d_state, d_pdf, stats_updated, bw, symmetric, strict, unsigned_sym, d_out_encoding,
+    return tfe_search(d_state, d_pdf, stats_updated, nullptr, bw, symmetric, strict, unsigned_sym, d_out_encoding,
                       d_workspace, workspace_bytes, (cudaStream_t) stream);
+}
+
+int aq_tfe_compute_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_hists, const int64_t* d_counts,
+                            int64_t num_batches, double* d_pdf, int32_t* d_iterations, int stats_updated,
+                            const int32_t* d_stats_updated, int bw, int symmetric, int strict, int unsigned_sym,
+                            double* d_out_encoding, void* d_workspace, int64_t workspace_bytes, void* stream)
+{
+    if (!d_state || !d_out_encoding || bw < 1 || bw > 32 || ((uintptr_t) d_stats_updated % 4))
+        return AQ_ERR_INVALID_ARG;
+    if (!d_workspace || ((uintptr_t) d_workspace % 256) != 0)
+        return AQ_ERR_WORKSPACE;
+    const int rc = aq_tfe_pdf_replay(d_hists, d_counts, num_batches, d_pdf, d_iterations, stream);
+    if (rc != AQ_OK)
+        return rc;
+    return tfe_search(d_state, d_pdf, stats_updated, d_stats_updated, bw, symmetric, strict, unsigned_sym,
+                      d_out_encoding, d_workspace, workspace_bytes, (cudaStream_t) stream);
 }
 
 }   // extern "C"

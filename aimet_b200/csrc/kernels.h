@@ -68,11 +68,17 @@ int minmax_static(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t i
                   int propagate_nan, cudaStream_t st);
 int tfe_init_grid(const float* minmax, aq_tfe_state_t* st, cudaStream_t stream);
 int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t* hist, int64_t* count,
-                  cudaStream_t stream);
+                  const int32_t* gate, cudaStream_t stream);
+int tfe_histogram_many(const float* const* xs, const int64_t* ns, int m, int64_t row_stride, const aq_tfe_state_t* st,
+                       uint32_t* hist, int64_t* count, const int32_t* gate, cudaStream_t stream);
+int tfe_offer_grid(const float* x, int64_t n, aq_tfe_state_t* st, float* range, int init, void* ws, int64_t ws_bytes,
+                   cudaStream_t stream);
+int tfe_select_grid(const float* ranges, int num_ranks, int rank, aq_tfe_state_t* st, int32_t* gate,
+                    cudaStream_t stream);
 int tfe_pdf_replay(const uint32_t* hists, const int64_t* counts, int64_t num_batches, double* pdf,
                    int32_t* iterations, cudaStream_t stream);
 int64_t tfe_search_workspace_bytes();
-int tfe_search(const aq_tfe_state_t* st, const double* pdf, int stats_updated, int bw, int symmetric, int strict,
-               int unsigned_sym, double* out, void* ws, int64_t ws_bytes, cudaStream_t stream);
+int tfe_search(const aq_tfe_state_t* st, const double* pdf, int stats_updated, const int32_t* stats_updated_dev, int bw,
+               int symmetric, int strict, int unsigned_sym, double* out, void* ws, int64_t ws_bytes, cudaStream_t stream);
 
 }   // namespace aq

@@ -3,6 +3,7 @@
 #include <float.h>
 #include <stddef.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -84,26 +85,30 @@ static_assert(offsetof(aq_tfe_state_t, bucket_size) % 16 == 0 && offsetof(aq_tfe
                   offsetof(aq_tfe_state_t, initialized) == offsetof(aq_tfe_state_t, bucket_size) + 8,
               "the histogram kernel reads bucket_size, pdf_offset and initialized with one 16-byte load");
 constexpr int kMaxDevices = 64;   // per-device bookkeeping tables
-constexpr int kMmThreads = 512;
+constexpr int kMmThreads = 512;   // persistent form (large tensors)
+constexpr int kMmTileThreads = 256;   // one-tile-per-CTA form (small and medium tensors)
 constexpr int kMmUnroll  = 4;
+constexpr int kTensorGridCap = 4096;   // most CTAs (= partials) a whole-tensor reduction ever uses
 
-// ---- whole-tensor reduction: persistent CTAs, warp shuffles, last CTA folds the partials -------------------
+// ---- whole-tensor reduction: warp shuffles, last CTA folds the partials ------------------------------------
 // workspace layout: [0] uint32 ticket counter (must be 0 on entry; the kernel leaves it 0),
 //                   [64 ...) float2 partials, one per CTA.
-template <typename T, int VEC, bool PROP>
-__global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __restrict__ x, int64_t n,
-                                                                   float* __restrict__ out_min,
-                                                                   float* __restrict__ out_max,
-                                                                   unsigned int* __restrict__ ticket,
-                                                                   float2* __restrict__ partials, int accumulate)
+// Every thread sweeps packets p, p + stride, ...; kMmUnroll of them are in flight at once and the last, partial
+// group is issued together as well (never one load at a time).  Small and medium tensors get one group per thread
+// (grid = number of tiles, so the whole tensor is requested at once); large ones a resident grid that loops.
+template <typename T, int VEC, bool PROP, int THREADS>
+__global__ void __launch_bounds__(THREADS) minmax_tensor_kernel(const T* __restrict__ x, int64_t n,
+                                                                float* __restrict__ out_min,
+                                                                float* __restrict__ out_max,
+                                                                unsigned int* __restrict__ ticket,
+                                                                float2* __restrict__ partials, int accumulate)
 {
     pdl_launch_dependents();
     pdl_wait();
     float mn = INFINITY, mx = -INFINITY;
     const int64_t npack  = n / VEC;
-    const int64_t stride = (int64_t) gridDim.x * kMmThreads;
-    int64_t p            = (int64_t) blockIdx.x * kMmThreads + threadIdx.x;
-    // kMmUnroll independent loads in flight per thread
+    const int64_t stride = (int64_t) gridDim.x * THREADS;
+    int64_t p            = (int64_t) blockIdx.x * THREADS + threadIdx.x;
     for (; p + (kMmUnroll - 1) * stride < npack; p += kMmUnroll * stride)
     {
         Pack<T, VEC> v[kMmUnroll];
@@ -114,8 +119,18 @@ __global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __re
         for (int u = 0; u < kMmUnroll; ++u)
             fold_pack<T, VEC, PROP>(v[u], mn, mx);
     }
-    for (; p < npack; p += stride)
-        fold_pack<T, VEC, PROP>(load_pack<T, VEC>(x + p * VEC), mn, mx);
+    {
+        // partial group: up to kMmUnroll - 1 packets, all in flight together
+        Pack<T, VEC> v[kMmUnroll - 1];
+#pragma unroll
+        for (int u = 0; u < kMmUnroll - 1; ++u)
+            if (p + u * stride < npack)
+                v[u] = load_pack<T, VEC>(x + (p + u * stride) * VEC);
+#pragma unroll
+        for (int u = 0; u < kMmUnroll - 1; ++u)
+            if (p + u * stride < npack)
+                fold_pack<T, VEC, PROP>(v[u], mn, mx);
+    }
     // ragged tail (fewer than VEC elements)
     if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * VEC))
     {
@@ -125,7 +140,7 @@ __global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __re
     }
 
     group_reduce<PROP, 32>(mn, mx);
-    __shared__ float s_mn[kMmThreads / 32], s_mx[kMmThreads / 32];
+    __shared__ float s_mn[THREADS / 32], s_mx[THREADS / 32];
     __shared__ bool s_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0)
@@ -133,8 +148,8 @@ __global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __re
     __syncthreads();
     if (warp == 0)
     {
-        mn = lane < kMmThreads / 32 ? s_mn[lane] : INFINITY;
-        mx = lane < kMmThreads / 32 ? s_mx[lane] : -INFINITY;
+        mn = lane < THREADS / 32 ? s_mn[lane] : INFINITY;
+        mx = lane < THREADS / 32 ? s_mx[lane] : -INFINITY;
         group_reduce<PROP, 32>(mn, mx);
         if (lane == 0)
         {
@@ -149,7 +164,7 @@ __global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __re
         return;
     __threadfence();
     mn = INFINITY, mx = -INFINITY;
-    for (int i = threadIdx.x; i < (int) gridDim.x; i += kMmThreads)
+    for (int i = threadIdx.x; i < (int) gridDim.x; i += THREADS)
     {
         const float2 q = __ldcg(&partials[i]);
         mn             = min_op<PROP>(mn, q.x);
@@ -162,8 +177,8 @@ __global__ void __launch_bounds__(kMmThreads) minmax_tensor_kernel(const T* __re
     __syncthreads();
     if (warp == 0)
     {
-        mn = lane < kMmThreads / 32 ? s_mn[lane] : INFINITY;
-        mx = lane < kMmThreads / 32 ? s_mx[lane] : -INFINITY;
+        mn = lane < THREADS / 32 ? s_mn[lane] : INFINITY;
+        mx = lane < THREADS / 32 ? s_mx[lane] : -INFINITY;
         group_reduce<PROP, 32>(mn, mx);
         if (lane == 0)
         {
@@ -305,6 +320,19 @@ __global__ void __launch_bounds__(256) minmax_fold_kernel(const float* __restric
     out_max[c] = mx;
 }
 
+// Empty tensor with several channels: every channel reports the identity of min / max.
+__global__ void __launch_bounds__(256) minmax_fill_empty_kernel(float* __restrict__ out_min, float* __restrict__ out_max,
+                                                                int64_t num_ch)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t c = (int64_t) blockIdx.x * 256 + threadIdx.x; c < num_ch; c += (int64_t) gridDim.x * 256)
+    {
+        out_min[c] = INFINITY;
+        out_max[c] = -INFINITY;
+    }
+}
+
 struct RowsPlan
 {
     int64_t rows, outer;
@@ -348,16 +376,18 @@ static RowsPlan plan_rows(int64_t n, int64_t num_ch, int64_t inner, int vec)
     return p;
 }
 
-static int tensor_grid(int64_t n, int vec)
+// Whole-tensor grid: one tile (kMmTileThreads x kMmUnroll packets) per CTA while that stays within kTensorGridCap CTAs
+// (fp32: up to 67 MB), otherwise a resident grid of 4 CTAs of kMmThreads threads per SM that loops.
+static int tensor_grid(int64_t n, int vec, bool& tiled)
 {
-    int64_t per_block = (int64_t) kMmThreads * vec * kMmUnroll;
-    int64_t blocks    = (n + per_block - 1) / per_block;
-    int64_t cap       = (int64_t) kNumSMs * 4;   // 4 CTAs of 512 threads per SM
-    if (blocks > cap)
-        blocks = cap;
-    if (blocks < 1)
-        blocks = 1;
-    return (int) blocks;
+    const int64_t per_tile = (int64_t) kMmTileThreads * vec * kMmUnroll;
+    int64_t tiles          = (n + per_tile - 1) / per_tile;
+    if (tiles < 1)
+        tiles = 1;
+    tiled = tiles <= kTensorGridCap;
+    if (tiled)
+        return (int) tiles;
+    return kNumSMs * 4;
 }
 
 template <typename T>
@@ -380,7 +410,9 @@ static int dtype_vec(const void* x, int dtype, int64_t multiple_of)
 int64_t minmax_workspace_bytes(int64_t n, int64_t num_ch, int64_t inner)
 {
     if (num_ch <= 1)
-        return 256 + (int64_t) kNumSMs * 4 * sizeof(float2);
+        return 256 + (int64_t) kTensorGridCap * sizeof(float2);
+    if (n / inner == 0)
+        return 256;   // no rows: nothing to plan (the outputs are filled directly)
     // worst case over vector widths: vec = 1 gives the most segments
     int64_t worst = 0;
     for (int vec = 1; vec <= 8; vec <<= 1)
@@ -430,30 +462,40 @@ static int minmax_t(const T* x, int64_t n, int64_t num_ch, int64_t inner, float*
 {
     if (num_ch <= 1)
     {
-        const int vec  = vec_for<T>(x, 0);
-        const int grid = tensor_grid(n, vec);
+        const int vec = vec_for<T>(x, 0);
+        bool tiled;
+        const int grid = tensor_grid(n, vec, tiled);
         if (ws_bytes < 256 + (int64_t) grid * (int64_t) sizeof(float2))
             return AQ_ERR_WORKSPACE;
         unsigned int* ticket = static_cast<unsigned int*>(ws);
         float2* partials     = reinterpret_cast<float2*>(static_cast<char*>(ws) + 256);
+#define AQ_MM(V)                                                                                                     \
+    if (tiled)                                                                                                       \
+        launch_pdl(minmax_tensor_kernel<T, V, PROP, kMmTileThreads>, (unsigned) grid, kMmTileThreads, 0, st, x, n,   \
+                   out_min, out_max, ticket, partials, accumulate);                                                  \
+    else                                                                                                             \
+        launch_pdl(minmax_tensor_kernel<T, V, PROP, kMmThreads>, (unsigned) grid, kMmThreads, 0, st, x, n, out_min,  \
+                   out_max, ticket, partials, accumulate);
         switch (vec)
         {
-        case 8:
-            launch_pdl(minmax_tensor_kernel<T, (sizeof(T) == 2 ? 8 : 4), PROP>, (unsigned) grid, kMmThreads, 0, st, x, n, out_min, out_max, ticket,
-                       partials, accumulate);
-            break;
-        case 4:
-            launch_pdl(minmax_tensor_kernel<T, 4, PROP>, (unsigned) grid, kMmThreads, 0, st, x, n, out_min, out_max, ticket,
-                       partials, accumulate);
-            break;
-        case 2:
-            launch_pdl(minmax_tensor_kernel<T, 2, PROP>, (unsigned) grid, kMmThreads, 0, st, x, n, out_min, out_max, ticket,
-                       partials, accumulate);
-            break;
-        default:
-            launch_pdl(minmax_tensor_kernel<T, 1, PROP>, (unsigned) grid, kMmThreads, 0, st, x, n, out_min, out_max, ticket,
-                       partials, accumulate);
+        case 8: AQ_MM((sizeof(T) == 2 ? 8 : 4)) break;
+        case 4: AQ_MM(4) break;
+        case 2: AQ_MM(2) break;
+        default: AQ_MM(1)
         }
+#undef AQ_MM
+        note_launch();
+        return check_launch();
+    }
+    if (n / inner == 0)
+    {
+        // no rows at all: min over nothing is +inf, max is -inf; running statistics stay as they are
+        if (accumulate)
+            return AQ_OK;
+        int64_t blocks = (num_ch + 255) / 256;
+        if (blocks > kNumSMs)
+            blocks = kNumSMs;
+        launch_pdl(minmax_fill_empty_kernel, (unsigned) blocks, 256, 0, st, out_min, out_max, num_ch);
         note_launch();
         return check_launch();
     }
@@ -488,7 +530,6 @@ static int minmax_t(const T* x, int64_t n, int64_t num_ch, int64_t inner, float*
 int minmax_dispatch(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* out_min,
                     float* out_max, int propagate_nan, int accumulate, void* ws, int64_t ws_bytes, cudaStream_t st)
 {
-    (void) dtype_vec;
 #define AQ_T(T)                                                                                                      \
     (propagate_nan                                                                                                   \
          ? minmax_t<T, true>((const T*) x, n, num_ch, inner, out_min, out_max, accumulate, ws, ws_bytes, st)         \
@@ -515,29 +556,43 @@ int minmax_dispatch(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t
 // -------------------------------------------------------------------------------------------------
 static __device__ __align__(256) unsigned char g_minmax_static_scratch[AQ_MINMAX_STATIC_SCRATCH_BYTES];
 
+// Scratch bytes the call would really touch (the public size query is a worst case over vector widths and always
+// charges row partials; a plan whose rows are written straight to the outputs needs only the ticket area).
+static int64_t minmax_scratch_need(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t inner)
+{
+    if (num_ch <= 1)
+    {
+        bool tiled;
+        return 256 + (int64_t) tensor_grid(n, dtype_vec(x, dtype, 0), tiled) * (int64_t) sizeof(float2);
+    }
+    if (n / inner == 0)
+        return 256;
+    const RowsPlan p = plan_rows(n, num_ch, inner, dtype_vec(x, dtype, inner));
+    return p.direct ? 256 : 256 + 2 * p.rows * p.nseg * (int64_t) sizeof(float);
+}
+
 int minmax_static(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t inner, float* out_min, float* out_max,
                   int propagate_nan, cudaStream_t st)
 {
-    const int64_t need = minmax_workspace_bytes(n, num_ch, inner);
-    if (need > (int64_t) AQ_MINMAX_STATIC_SCRATCH_BYTES)
+    if (minmax_scratch_need(x, dtype, n, num_ch, inner) > (int64_t) AQ_MINMAX_STATIC_SCRATCH_BYTES)
         return AQ_ERR_TOO_LARGE;
     // In host code the array's name is only a handle; the address the kernels need comes from the runtime, once per
-    // device, with that device current.
-    constexpr int kMaxDevices = 64;
-    static void* scratch_of_device[kMaxDevices] = {};
+    // device, with that device current.  Entries are written once with the same value by whichever thread gets there
+    // first, so relaxed atomics are enough.
+    static std::atomic<void*> scratch_of_device[kMaxDevices];
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess)
         return cuda_fail(e);
     if (dev < 0 || dev >= kMaxDevices)
         return AQ_ERR_UNSUPPORTED;
-    void* scratch = scratch_of_device[dev];
+    void* scratch = scratch_of_device[dev].load(std::memory_order_relaxed);
     if (!scratch)
     {
         e = cudaGetSymbolAddress(&scratch, g_minmax_static_scratch);
         if (e != cudaSuccess)
             return cuda_fail(e);
-        scratch_of_device[dev] = scratch;
+        scratch_of_device[dev].store(scratch, std::memory_order_relaxed);
     }
     // The whole-tensor kernel expects its ticket counter (first 256 bytes) to be zero; nothing else has to be.
     e = cudaMemsetAsync(scratch, 0, 256, st);
@@ -551,17 +606,13 @@ int minmax_static(const void* x, int dtype, int64_t n, int64_t num_ch, int64_t i
 // TF-Enhanced: bucket grid, 512-bucket histogram, PDF replay
 // =================================================================================================
 
-// InitializePdf<float> + the geometry lines of UpdatePdf (DlQuantization/src/math_functions.cpp:207-268).
-__global__ void __launch_bounds__(AQ_PDF_SIZE) tfe_init_grid_kernel(const float* __restrict__ minmax,
-                                                                    aq_tfe_state_t* __restrict__ st)
+// InitializePdf<float> + the geometry lines of UpdatePdf (DlQuantization/src/math_functions.cpp:207-268), run by the
+// first AQ_PDF_SIZE threads of one CTA (all threads of the CTA must call it: it contains a barrier).  Leaves the
+// state alone when it is initialised already or when the batch is all zeros (the reference waits for the next one).
+__device__ __forceinline__ void tfe_grid_from_range(float mn, float mx, aq_tfe_state_t* __restrict__ st)
 {
-    pdl_launch_dependents();
-    pdl_wait();
-    if (st->initialized)
-        return;
-    float mn = minmax[0], mx = minmax[1];
-    if (mn == 0.0f && mx == 0.0f)
-        return;   // an all-zero batch cannot define the range; the reference waits for the next one
+    if (st->initialized || (mn == 0.0f && mx == 0.0f))
+        return;   // uniform over the CTA: both operands are the same for every thread
     if (mn == mx)
     {
         const float alt = __fadd_rn(mn, 0.01f);
@@ -574,7 +625,8 @@ __global__ void __launch_bounds__(AQ_PDF_SIZE) tfe_init_grid_kernel(const float*
     hi                 = (hi < FLT_MAX) ? hi : FLT_MAX;
     const double bucket = __ddiv_rn(__dsub_rn((double) hi, (double) lo), (double) AQ_PDF_SIZE);
     const int i         = threadIdx.x;
-    st->x_left[i]       = __dadd_rn((double) lo, __dmul_rn((double) i, bucket));
+    if (i < AQ_PDF_SIZE)
+        st->x_left[i] = __dadd_rn((double) lo, __dmul_rn((double) i, bucket));
     __syncthreads();
     if (i == 0)
     {
@@ -589,7 +641,154 @@ __global__ void __launch_bounds__(AQ_PDF_SIZE) tfe_init_grid_kernel(const float*
     }
 }
 
-constexpr int kHistThreads = 512;
+__global__ void __launch_bounds__(AQ_PDF_SIZE) tfe_init_grid_kernel(const float* __restrict__ minmax,
+                                                                    aq_tfe_state_t* __restrict__ st)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    tfe_grid_from_range(minmax[0], minmax[1], st);
+}
+
+// ---- range of a batch, fused with the grid set-up -------------------------------------------------------------
+// One launch does what the reference's first-batch branch of UpdatePdf does with GetMin + GetMax + InitializePdf:
+// a single min/max pass over the batch, and the last CTA to finish builds the bucket grid from the result.  Once
+// the state is initialised the launch returns at once (a few microseconds instead of a pass over the tensor), so a
+// caller that does not yet KNOW on the host whether the grid exists can keep offering batches without waiting
+// for the device.  With `range` the (min, max, 1.0f) triple of the batch is also written out -- (0, 0, 1) when the
+// pass was skipped -- for callers that agree on the grid across ranks; `init` = 0 leaves the state alone.
+// workspace layout as for minmax_tensor_kernel.
+constexpr int kOfferThreads = 512;
+__global__ void __launch_bounds__(kOfferThreads, 4) tfe_offer_grid_kernel(const float* __restrict__ x, int64_t n,
+                                                                       aq_tfe_state_t* __restrict__ st,
+                                                                       float* __restrict__ range, int init,
+                                                                       unsigned int* __restrict__ ticket,
+                                                                       float2* __restrict__ partials)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    if (st->initialized)
+    {
+        if (range && blockIdx.x == 0 && threadIdx.x == 0)
+            range[0] = 0.0f, range[1] = 0.0f, range[2] = 1.0f;
+        return;
+    }
+    float mn = INFINITY, mx = -INFINITY;
+    const bool vec4      = ((uintptr_t) x % 16) == 0;
+    const int64_t npack  = vec4 ? n / 4 : 0;
+    const int64_t stride = (int64_t) gridDim.x * kOfferThreads;
+    int64_t p            = (int64_t) blockIdx.x * kOfferThreads + threadIdx.x;
+    for (; p + (kMmUnroll - 1) * stride < npack; p += kMmUnroll * stride)
+    {
+        Pack<float, 4> v[kMmUnroll];
+#pragma unroll
+        for (int u = 0; u < kMmUnroll; ++u)
+            v[u] = load_pack<float, 4>(x + (p + u * stride) * 4);
+#pragma unroll
+        for (int u = 0; u < kMmUnroll; ++u)
+            fold_pack<float, 4, false>(v[u], mn, mx);
+    }
+    {
+        Pack<float, 4> v[kMmUnroll - 1];
+#pragma unroll
+        for (int u = 0; u < kMmUnroll - 1; ++u)
+            if (p + u * stride < npack)
+                v[u] = load_pack<float, 4>(x + (p + u * stride) * 4);
+#pragma unroll
+        for (int u = 0; u < kMmUnroll - 1; ++u)
+            if (p + u * stride < npack)
+                fold_pack<float, 4, false>(v[u], mn, mx);
+    }
+    // what the packets did not cover: the ragged tail, or everything when the base address is not 16-byte aligned
+    for (int64_t i = npack * 4 + (int64_t) blockIdx.x * kOfferThreads + threadIdx.x; i < n; i += stride)
+    {
+        mn = fminf(mn, x[i]);
+        mx = fmaxf(mx, x[i]);
+    }
+    group_reduce<false, 32>(mn, mx);
+    __shared__ float s_mn[kOfferThreads / 32], s_mx[kOfferThreads / 32];
+    __shared__ bool s_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0)
+        s_mn[warp] = mn, s_mx[warp] = mx;
+    __syncthreads();
+    if (warp == 0)
+    {
+        mn = lane < kOfferThreads / 32 ? s_mn[lane] : INFINITY;
+        mx = lane < kOfferThreads / 32 ? s_mx[lane] : -INFINITY;
+        group_reduce<false, 32>(mn, mx);
+        if (lane == 0)
+        {
+            partials[blockIdx.x] = make_float2(mn, mx);
+            __threadfence();
+            const unsigned int t = atomicAdd(ticket, 1u);
+            s_last               = (t == gridDim.x - 1);
+        }
+    }
+    __syncthreads();
+    if (!s_last)
+        return;
+    __threadfence();
+    mn = INFINITY, mx = -INFINITY;
+    for (int i = threadIdx.x; i < (int) gridDim.x; i += kOfferThreads)
+    {
+        const float2 q = __ldcg(&partials[i]);
+        mn             = fminf(mn, q.x);
+        mx             = fmaxf(mx, q.y);
+    }
+    group_reduce<false, 32>(mn, mx);
+    __syncthreads();
+    if (lane == 0)
+        s_mn[warp] = mn, s_mx[warp] = mx;
+    __syncthreads();
+    mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kOfferThreads / 32; ++w)   // every thread needs the result: the grid set-up is CTA-wide
+    {
+        mn = fminf(mn, s_mn[w]);
+        mx = fmaxf(mx, s_mx[w]);
+    }
+    if (threadIdx.x == 0)
+    {
+        *ticket = 0;   // ready for the next call on this stream
+        if (range)
+            range[0] = mn, range[1] = mx, range[2] = 1.0f;
+    }
+    if (init)
+        tfe_grid_from_range(mn, mx, st);
+}
+
+// Grid agreement across ranks, decided on the device: `ranges` holds one (min, max, present) triple per rank for the
+// batches of one round (global order inside a round = rank order).  The first present batch whose (min, max) is
+// not (0, 0) defines the grid (DlQuantization/src/math_functions.cpp:248-262).  `gate` tells this rank whether its own
+// batch of the round counts: an all-zero batch that precedes the defining one was dropped by the sequential
+// reference before the grid existed, so it must be dropped here too.
+__global__ void __launch_bounds__(AQ_PDF_SIZE) tfe_select_grid_kernel(const float* __restrict__ ranges, int num_ranks,
+                                                                      int rank, aq_tfe_state_t* __restrict__ st,
+                                                                      int32_t* __restrict__ gate)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    if (st->initialized)
+    {
+        if (threadIdx.x == 0)
+            *gate = 1;
+        return;
+    }
+    int chosen = -1;
+    for (int r = 0; r < num_ranks; ++r)
+    {
+        const float mn = ranges[3 * r], mx = ranges[3 * r + 1], present = ranges[3 * r + 2];
+        if (present != 0.0f && !(mn == 0.0f && mx == 0.0f))
+        {
+            chosen = r;
+            break;
+        }
+    }
+    if (threadIdx.x == 0)
+        *gate = (chosen >= 0 && rank >= chosen) ? 1 : 0;
+    if (chosen >= 0)
+        tfe_grid_from_range(ranges[3 * chosen], ranges[3 * chosen + 1], st);
+}
 
 // Bucket of one sample: (int) roundf(x / bucket_size - pdf_offset), valid when inside [0, 512).
 // For t > -0.5 the half-away rounding equals floor(t + 0.5); adding with round-down keeps the sum from being
@@ -655,17 +854,18 @@ __host__ __device__ inline float hist_margin(float po)
 constexpr int kLaneUnroll = 4;
 
 // Packets that held an unsure sample are not repaired inside the hot loop (any call or long branch body there
-// costs registers that the two-CTAs-per-SM budget does not have); their indices go to a small shared-memory queue
-// and the CTA repairs them together after its sweep.  About one group of 16 samples in 170 is queued on ordinary data.
+// costs registers that the two-CTAs-per-SM budget does not have); the index of their group goes to a small
+// shared-memory queue and the CTA repairs them together after its sweep.  About one group of 16 samples in 170 is
+// queued on ordinary data.
 constexpr int kFixQueue        = 4096;
 constexpr int kLaneHistSmem    = kLaneHistBytes + kFixQueue * (int) sizeof(uint32_t);
 
-// Repair of one queued packet: re-read it, take every unsure sample's fast-path count back out and count it with
-// the exact formula instead.
-__device__ __forceinline__ void hist_fix_packet(const float* __restrict__ x, int64_t q, uint32_t base, float rbs, float c,
-                                                float eps, float bs, float po)
+// Repair of one queued packet: re-read it (it has just passed through L2), take every unsure sample's fast-path count
+// back out and count it with the exact formula instead.
+__device__ __forceinline__ void hist_fix_packet(const float4* __restrict__ x4, uint32_t q, uint32_t base, float rbs,
+                                                float c, float eps, float bs, float po)
 {
-    const float4 w   = __ldg(reinterpret_cast<const float4*>(x) + q);
+    const float4 w   = __ldg(x4 + q);
     const float f[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int e = 0; e < 4; ++e)
@@ -682,15 +882,42 @@ __device__ __forceinline__ void hist_fix_packet(const float* __restrict__ x, int
     }
 }
 
-__global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(const float* __restrict__ x, int64_t n,
-                                                                            const aq_tfe_state_t* __restrict__ st,
-                                                                            uint32_t* __restrict__ hist,
-                                                                            int64_t* __restrict__ count)
+// Up to AQ_TFE_HIST_MANY batches per launch, each into its own row: the launch overhead (about 1.3 us of the 13 us a
+// 51 MB batch takes as a launch of its own) is paid once per launch instead of once per batch.  What stays per batch is
+// the stop at its end -- measured with cycle stamps at 51 MB per batch: 1.35 us until the CTA's slowest warp arrives,
+// 1.7 us to repair the ~30 queued packets (a dependent re-read), 1.0 us to fold (0.6 us with 128-bit shared loads) --
+// which the other CTA of the SM only partly covers.  Forms that avoid the stop were built and measured slower:
+// one CTA per SM with a dedicated fold warp and two counter sets (32 warps cannot keep the SM busy: 3.9 TB/s even
+// without any atomics), repair in place from the registers or through a queue of sample values (both make the compiler
+// spill inside the hot loop at 32 registers), and counters shared by the CTA with per-set tickets instead of a barrier
+// (same-address reductions cost nothing on this GPU, but the per-thread recount calls are slower than the joint
+// repair).
+struct HistJob
+{
+    const float* x[AQ_TFE_HIST_MANY];
+    int64_t n[AQ_TFE_HIST_MANY];
+    int m;
+    int64_t row_stride;   // rows between consecutive batches of the launch (1 = adjacent rows)
+    uint32_t* hist;    // row of batch 0; batch b adds into hist + b * row_stride * 512
+    int64_t* count;    // may be null; batch b sets count[b * row_stride]
+    const int32_t* gate;   // may be null; *gate == 0 drops the batches (count 0, rows untouched)
+};
+
+// A batch that does not start on a 16-byte boundary (a view into a larger buffer) has up to three leading elements
+// before its first aligned packet; they are counted one by one like the ragged tail.
+__device__ __forceinline__ int hist_lead(const float* x, int64_t n)
+{
+    return (int) min((int64_t) ((0u - (uint32_t) ((uintptr_t) x >> 2)) & 3u), n);
+}
+
+__global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(const __grid_constant__ HistJob job,
+                                                                            const aq_tfe_state_t* __restrict__ st)
 {
     pdl_launch_dependents();
     extern __shared__ uint32_t s_lane_hist[];   // [513][32] counters, then the repair queue
     uint32_t* s_queue = s_lane_hist + kLaneHistRows * 32;
     __shared__ uint32_t s_queued;
+    __shared__ float s_bs, s_po;   // only the exact formula (rare paths) needs them: kept out of the registers
     {
         // shared-memory setup needs no global input: it overlaps the tail of the previous grid
         uint4* z = reinterpret_cast<uint4*>(s_lane_hist);
@@ -699,41 +926,42 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
         if (threadIdx.x == 0)
             s_queued = 0;
     }
-    pdl_wait();
-    {
-        // start this thread's first packets on their way from DRAM to L2 while the state is being read
-        const uint32_t np = (uint32_t) (n / 4), sd = gridDim.x * kLaneHistThreads;
-        const uint32_t p0 = blockIdx.x * kLaneHistThreads + threadIdx.x;
+    const uint32_t stride = gridDim.x * kLaneHistThreads;
+    const uint32_t p0     = blockIdx.x * kLaneHistThreads + threadIdx.x;
+    // Bringing a batch's first packets into L2 may start before the previous grid has finished even if that grid is
+    // still writing them: L2 is the point of coherence, a line fetched early is simply updated by the later stores.
+    auto prefetch_head = [&](const float* x, int64_t n) {
+        const int lead    = hist_lead(x, n);
+        const float4* h4  = reinterpret_cast<const float4*>(x + lead);
+        const uint32_t np = (uint32_t) ((n - lead) / 4);
 #pragma unroll
         for (int u = 0; u < kLaneUnroll; ++u)
-            if (p0 + u * sd < np)
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const float4*>(x) + (p0 + u * sd)));
-    }
+            if (p0 + u * stride < np)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(h4 + (p0 + u * stride)));
+    };
+    prefetch_head(job.x[0], job.n[0]);
+    pdl_wait();
     // bucket_size, pdf_offset and the initialized flag sit in one aligned 16-byte group: one load, one round trip
-    const int4 tail       = *reinterpret_cast<const int4*>(&st->bucket_size);
-    const int initialized = tail.z;
-    if (blockIdx.x == 0 && threadIdx.x == 0 && count)
-        *count = initialized ? n : 0;
+    const int4 tail = *reinterpret_cast<const int4*>(&st->bucket_size);
+    int initialized = tail.z;
+    if (job.gate && *job.gate == 0)
+        initialized = 0;
+    if (blockIdx.x == 0 && threadIdx.x < job.m && job.count)
+        job.count[threadIdx.x * job.row_stride] = initialized ? job.n[threadIdx.x] : 0;
     if (!initialized)
         return;
+    if (threadIdx.x == 0)
+        s_bs = __int_as_float(tail.x), s_po = __int_as_float(tail.y);
     __syncthreads();
 
-    const float bs = __int_as_float(tail.x), po = __int_as_float(tail.y);
-    const float margin = hist_margin(po);
+    const float margin = hist_margin(__int_as_float(tail.y));
     // A margin of a quarter bucket or more means the grid sits so far from zero that the reciprocal form is
     // useless: eps = 0 marks every packet unsure, the queue overflows and the CTA takes the exact sweep below.
     const float eps = margin < 0.25f ? 0.5f - margin : 0.0f;
-    const float rbs = __frcp_rn(bs);
-    const float c   = 1.5f - po;
-    const int lane      = threadIdx.x & 31;
-    const uint32_t base = (uint32_t) __cvta_generic_to_shared(s_lane_hist + lane);
-    const float4* __restrict__ x4 = reinterpret_cast<const float4*>(x);
+    const float rbs = __frcp_rn(__int_as_float(tail.x));
+    const float c   = 1.5f - __int_as_float(tail.y);
+    const uint32_t base = (uint32_t) __cvta_generic_to_shared(s_lane_hist + (threadIdx.x & 31));
 
-    // Packet indices fit 32 bits (n <= 2^31 elements).  Every thread sweeps packets p, p + stride, ...;
-    // kLaneUnroll of them are in flight at once; the last, partial group handles its packets one by one.
-    const uint32_t npack  = (uint32_t) (n / 4);
-    const uint32_t stride = gridDim.x * kLaneHistThreads;
-    uint32_t p            = blockIdx.x * kLaneHistThreads + threadIdx.x;
     // Per sample: FFMA, 3 FADD, FMNMX, VIADDMNMX, LEA, RED.  `worst` collects max |g| of the group; a NaN (from a
     // NaN / Inf sample) is dropped by fmaxf, which is fine: such a sample went to the trash row, and the exact
     // formula drops it too.
@@ -755,149 +983,143 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
         if (slot < (uint32_t) kFixQueue)                                                                             \
             s_queue[slot] = p;                                                                                       \
     }
-    if (npack >= (kLaneUnroll - 1) * stride)
+    for (int b = 0; b < job.m; ++b)
     {
-        const uint32_t last_full = npack - (kLaneUnroll - 1) * stride;   // p < last_full: a full group fits
-        for (; p < last_full; p += kLaneUnroll * stride)
+        const float* __restrict__ x0  = job.x[b];
+        const int lead                = hist_lead(x0, job.n[b]);
+        const float4* __restrict__ x4 = reinterpret_cast<const float4*>(x0 + lead);
+        // Packet indices fit 32 bits (n <= 2^31 elements).  Every thread sweeps packets p, p + stride, ...;
+        // kLaneUnroll of them are in flight at once; the last, partial group is issued together as well.
+        const uint32_t npack = (uint32_t) ((job.n[b] - lead) / 4);
+        uint32_t p           = p0;
+        if (npack >= (kLaneUnroll - 1) * stride)
         {
-            float4 v[kLaneUnroll];
+            const uint32_t last_full = npack - (kLaneUnroll - 1) * stride;   // p < last_full: a full group fits
+            for (; p < last_full; p += kLaneUnroll * stride)
+            {
+                float4 v[kLaneUnroll];
 #pragma unroll
-            for (int u = 0; u < kLaneUnroll; ++u)
-                v[u] = __ldcs(x4 + (p + u * stride));
+                for (int u = 0; u < kLaneUnroll; ++u)
+                    v[u] = __ldcs(x4 + (p + u * stride));
+                float worst = 0.0f;
+#pragma unroll
+                for (int u = 0; u < kLaneUnroll; ++u)
+                    AQ_HIST_PACKET(v[u])
+                AQ_HIST_QUEUE()
+            }
+        }
+        {
+            // partial group: up to kLaneUnroll - 1 packets
+            float4 v[kLaneUnroll - 1];
+#pragma unroll
+            for (int u = 0; u < kLaneUnroll - 1; ++u)
+                if (p + u * stride < npack)
+                    v[u] = __ldcs(x4 + (p + u * stride));
             float worst = 0.0f;
 #pragma unroll
-            for (int u = 0; u < kLaneUnroll; ++u)
-                AQ_HIST_PACKET(v[u])
+            for (int u = 0; u < kLaneUnroll - 1; ++u)
+                if (p + u * stride < npack)
+                    AQ_HIST_PACKET(v[u])
             AQ_HIST_QUEUE()
         }
-    }
-    {
-        // partial group: up to kLaneUnroll - 1 packets
-        float4 v[kLaneUnroll - 1];
-#pragma unroll
-        for (int u = 0; u < kLaneUnroll - 1; ++u)
-            if (p + u * stride < npack)
-                v[u] = __ldcs(x4 + (p + u * stride));
-        float worst = 0.0f;
-#pragma unroll
-        for (int u = 0; u < kLaneUnroll - 1; ++u)
-            if (p + u * stride < npack)
-                AQ_HIST_PACKET(v[u])
-        AQ_HIST_QUEUE()
-    }
-#undef AQ_HIST_SAMPLE
-#undef AQ_HIST_PACKET
-#undef AQ_HIST_QUEUE
-    if (blockIdx.x == 0 && threadIdx.x < (int) (n - (int64_t) npack * 4))
-    {
-        int k;
-        if (bucket_of(x[(int64_t) npack * 4 + threadIdx.x], bs, po, k))
-            lane_hist_inc(base, (uint32_t) k);
-    }
-    __syncthreads();
-    const uint32_t queued = s_queued;
-    if (queued <= (uint32_t) kFixQueue)
-    {
-        // one queued group = up to kLaneUnroll packets; (entry, packet) pairs are spread over the threads
-        for (uint32_t i = threadIdx.x; i < queued * kLaneUnroll; i += kLaneHistThreads)
+        // the next batch's first packets travel to L2 while this one is being repaired and folded
+        if (b + 1 < job.m)
+            prefetch_head(job.x[b + 1], job.n[b + 1]);
+        const int ragged = (int) (job.n[b] - lead - (int64_t) npack * 4);   // elements after the last whole packet
+        if (blockIdx.x == 0 && threadIdx.x < lead + ragged)
         {
-            const uint32_t q = s_queue[i / kLaneUnroll] + (i % kLaneUnroll) * stride;
-            if (q < npack)
-                hist_fix_packet(x, (int64_t) q, base, rbs, c, eps, bs, po);
+            const int t = threadIdx.x;
+            int k;
+            if (bucket_of(t < lead ? x0[t] : x0[lead + (int64_t) npack * 4 + (t - lead)], s_bs, s_po, k))
+                lane_hist_inc(base, (uint32_t) k);
         }
-    }
-    else
-    {
-        // Queue overflow (adversarial data sitting on bucket boundaries): throw this CTA's counts away and redo
-        // its whole share with the exact formula.
         __syncthreads();
-        for (int i = threadIdx.x; i < kLaneHistRows * 32; i += kLaneHistThreads)
-            s_lane_hist[i] = 0;
-        __syncthreads();
-        for (uint32_t q = blockIdx.x * kLaneHistThreads + threadIdx.x; q < npack; q += stride)
+        const uint32_t queued = s_queued;
+        if (queued <= (uint32_t) kFixQueue)
         {
-            const float4 w   = __ldg(x4 + q);
-            const float f[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
+            // one queued group = up to kLaneUnroll packets; (entry, packet) pairs are spread over the threads
+            for (uint32_t i = threadIdx.x; i < queued * kLaneUnroll; i += kLaneHistThreads)
             {
+                const uint32_t q = s_queue[i / kLaneUnroll] + (i % kLaneUnroll) * stride;
+                if (q < npack)
+                    hist_fix_packet(x4, q, base, rbs, c, eps, s_bs, s_po);
+            }
+        }
+        else
+        {
+            // Queue overflow (adversarial data sitting on bucket boundaries): throw this CTA's counts away and redo
+            // its whole share with the exact formula.
+            __syncthreads();
+            for (int i = threadIdx.x; i < kLaneHistRows * 32; i += kLaneHistThreads)
+                s_lane_hist[i] = 0;
+            __syncthreads();
+            for (uint32_t q = p0; q < npack; q += stride)
+            {
+                const float4 w   = __ldg(x4 + q);
+                const float f[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                {
+                    int k;
+                    if (bucket_of(f[e], s_bs, s_po, k))
+                        lane_hist_inc(base, (uint32_t) k);
+                }
+            }
+            if (blockIdx.x == 0 && threadIdx.x < lead + ragged)
+            {
+                const int t = threadIdx.x;
                 int k;
-                if (bucket_of(f[e], bs, po, k))
+                if (bucket_of(t < lead ? x0[t] : x0[lead + (int64_t) npack * 4 + (t - lead)], s_bs, s_po, k))
                     lane_hist_inc(base, (uint32_t) k);
             }
         }
-        if (blockIdx.x == 0 && threadIdx.x < (int) (n - (int64_t) npack * 4))
+        __syncthreads();
+        // Fold the 32 lane copies of each bucket and add the sums to the global row.  Two threads per bucket, each
+        // sums 16 copies (and leaves them zero for the next batch); the column order is rotated by the bucket index so
+        // that the 32 lanes of a warp (16 buckets x 2 halves) touch 32 different banks at every step.  CTAs start at
+        // rotated buckets so that they do not all hit the same global counter at the same moment.
         {
-            int k;
-            if (bucket_of(x[(int64_t) npack * 4 + threadIdx.x], bs, po, k))
-                lane_hist_inc(base, (uint32_t) k);
-        }
-    }
-    __syncthreads();
-    // Fold the 32 lane copies of each bucket and add the sums to the global row.  Two threads per bucket, each
-    // sums 16 copies; the column order is rotated by the bucket index so that the 32 lanes of a warp (16 buckets
-    // x 2 halves) read 32 different banks at every step.  CTAs start at rotated buckets so that they do not all
-    // hit the same global counter at the same moment.
-    {
-        const int rot  = (blockIdx.x * 37) & (AQ_PDF_SIZE - 1);
-        const int b    = ((threadIdx.x >> 1) + rot) & (AQ_PDF_SIZE - 1);
-        const int half = threadIdx.x & 1;
-        const uint32_t* row = s_lane_hist + (b << 5) + (half << 4);
-        uint32_t sum = 0;
+            const bool more = b + 1 < job.m;
+            const int rot   = (blockIdx.x * 37) & (AQ_PDF_SIZE - 1);
+            const int bk    = ((threadIdx.x >> 1) + rot) & (AQ_PDF_SIZE - 1);
+            const int half  = threadIdx.x & 1;
+            uint32_t* row   = s_lane_hist + (bk << 5) + (half << 4);
+            uint32_t sum    = 0;
+            // four 16-byte loads per thread; the order is rotated by the bucket index so that the eight threads of a
+            // quarter warp (4 buckets x 2 halves) touch eight different groups of four banks
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
-            sum += row[(k + b) & 15];
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        if (half == 0 && sum)
-            atomicAdd(&hist[b], sum);
-    }
+            for (int k = 0; k < 4; ++k)
+            {
+                uint4* q      = reinterpret_cast<uint4*>(row) + ((k + bk) & 3);
+                const uint4 w = *q;
+                sum += w.x + w.y + w.z + w.w;
+                if (more)
+                    *q = make_uint4(0, 0, 0, 0);
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            if (half == 0 && sum)
+                atomicAdd(&job.hist[b * job.row_stride * AQ_PDF_SIZE + bk], sum);
+            if (more)
+            {
+                // the trash row and the queue counter start the next batch at zero as well
+                if (threadIdx.x < 32)
+                    s_lane_hist[(AQ_PDF_SIZE << 5) + threadIdx.x] = 0;
+                if (threadIdx.x == 32)
+                    s_queued = 0;
+                __syncthreads();
+            }
+        }
+    }   // batches
+#undef AQ_HIST_SAMPLE
+#undef AQ_HIST_PACKET
+#undef AQ_HIST_QUEUE
+#undef AQ_HIST_QUEUE_FULL
 }
 
-// Scalar variant for inputs whose base address is not 16-byte aligned.
-__global__ void __launch_bounds__(kHistThreads) tfe_hist_scalar_kernel(const float* __restrict__ x, int64_t n,
-                                                                       const aq_tfe_state_t* __restrict__ st,
-                                                                       uint32_t* __restrict__ hist,
-                                                                       int64_t* __restrict__ count)
-{
-    const int initialized = st->initialized;
-    if (blockIdx.x == 0 && threadIdx.x == 0 && count)
-        *count = initialized ? n : 0;
-    if (!initialized)
-        return;
-    __shared__ uint32_t s_hist[AQ_PDF_SIZE];
-    for (int i = threadIdx.x; i < AQ_PDF_SIZE; i += kHistThreads)
-        s_hist[i] = 0;
-    __syncthreads();
-    const float bs = st->bucket_size, po = st->pdf_offset;
-    const int64_t stride = (int64_t) gridDim.x * kHistThreads;
-    for (int64_t i = (int64_t) blockIdx.x * kHistThreads + threadIdx.x; i < n; i += stride)
-    {
-        int k;
-        if (bucket_of(x[i], bs, po, k))
-            atomicAdd(&s_hist[k], 1u);
-    }
-    __syncthreads();
-    for (int b = threadIdx.x; b < AQ_PDF_SIZE; b += kHistThreads)
-        if (s_hist[b])
-            atomicAdd(&hist[b], s_hist[b]);
-}
 
-int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t* hist, int64_t* count,
-                  cudaStream_t stream)
+static int hist_lane_attributes()
 {
-    if (((uintptr_t) x % 16) != 0)
-    {
-        int64_t blocks = (n + kHistThreads - 1) / kHistThreads;
-        int64_t cap    = (int64_t) kNumSMs * 4;
-        if (blocks > cap)
-            blocks = cap;
-        if (blocks < 1)
-            blocks = 1;
-        tfe_hist_scalar_kernel<<<(unsigned) blocks, kHistThreads, 0, stream>>>(x, n, st, hist, count);
-        note_launch();
-        return check_launch();
-    }
-    static bool attr_set[kMaxDevices] = {};   // function attributes are per device
+    static std::atomic<bool> attr_set[kMaxDevices];   // function attributes are per device
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess)
@@ -913,14 +1135,64 @@ int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t*
         if (dev >= 0 && dev < kMaxDevices)
             attr_set[dev] = true;
     }
+    return AQ_OK;
+}
+
+int tfe_histogram_many(const float* const* xs, const int64_t* ns, int m, int64_t row_stride, const aq_tfe_state_t* st,
+                       uint32_t* hist, int64_t* count, const int32_t* gate, cudaStream_t stream)
+{
+    int64_t n_max = 0;
+    for (int b = 0; b < m; ++b)
+        n_max = ns[b] > n_max ? ns[b] : n_max;
+    const int rc = hist_lane_attributes();
+    if (rc != AQ_OK)
+        return rc;
+    HistJob job;
+    for (int b = 0; b < AQ_TFE_HIST_MANY; ++b)
+    {
+        job.x[b] = b < m ? xs[b] : nullptr;
+        job.n[b] = b < m ? ns[b] : 0;
+    }
+    job.m = m, job.row_stride = row_stride, job.hist = hist, job.count = count, job.gate = gate;
     int64_t per_block = (int64_t) kLaneHistThreads * 4 * kLaneUnroll;
-    int64_t blocks    = (n + per_block - 1) / per_block;
+    int64_t blocks    = (n_max + per_block - 1) / per_block;
     int64_t cap       = (int64_t) kNumSMs * 2;   // two resident 1024-thread CTAs per SM (32 registers, 64 KiB each)
     if (blocks > cap)
         blocks = cap;
     if (blocks < 1)
         blocks = 1;
-    launch_pdl(tfe_hist_lane_kernel, (unsigned) blocks, kLaneHistThreads, kLaneHistSmem, stream, x, n, st, hist, count);
+    launch_pdl(tfe_hist_lane_kernel, (unsigned) blocks, kLaneHistThreads, kLaneHistSmem, stream, job, st);
+    note_launch();
+    return check_launch();
+}
+
+int tfe_histogram(const float* x, int64_t n, const aq_tfe_state_t* st, uint32_t* hist, int64_t* count,
+                  const int32_t* gate, cudaStream_t stream)
+{
+    return tfe_histogram_many(&x, &n, 1, 1, st, hist, count, gate, stream);
+}
+
+int tfe_offer_grid(const float* x, int64_t n, aq_tfe_state_t* st, float* range, int init, void* ws, int64_t ws_bytes,
+                   cudaStream_t stream)
+{
+    // resident grid (every CTA first looks at the state: an offer that is not needed costs one small wave)
+    int64_t blocks = (n + (int64_t) kOfferThreads * 4 * kMmUnroll - 1) / ((int64_t) kOfferThreads * 4 * kMmUnroll);
+    if (blocks > (int64_t) kNumSMs * 4)
+        blocks = (int64_t) kNumSMs * 4;
+    if (blocks < 1)
+        blocks = 1;
+    if (ws_bytes < 256 + blocks * (int64_t) sizeof(float2))
+        return AQ_ERR_WORKSPACE;
+    launch_pdl(tfe_offer_grid_kernel, (unsigned) blocks, kOfferThreads, 0, stream, x, n, st, range, init,
+               static_cast<unsigned int*>(ws), reinterpret_cast<float2*>(static_cast<char*>(ws) + 256));
+    note_launch();
+    return check_launch();
+}
+
+int tfe_select_grid(const float* ranges, int num_ranks, int rank, aq_tfe_state_t* st, int32_t* gate,
+                    cudaStream_t stream)
+{
+    launch_pdl(tfe_select_grid_kernel, 1, AQ_PDF_SIZE, 0, stream, ranges, num_ranks, rank, st, gate);
     note_launch();
     return check_launch();
 }
@@ -1099,7 +1371,7 @@ __global__ void __launch_bounds__(kReplayThreads) tfe_pdf_replay_kernel(const ui
 int tfe_pdf_replay(const uint32_t* hists, const int64_t* counts, int64_t num_batches, double* pdf,
                    int32_t* iterations, cudaStream_t stream)
 {
-    static bool attr_set[kMaxDevices] = {};   // function attributes are per device
+    static std::atomic<bool> attr_set[kMaxDevices];   // function attributes are per device
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess)

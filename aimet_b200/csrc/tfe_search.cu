@@ -84,6 +84,7 @@ struct SearchArgs
     const aq_tfe_state_t* st;
     const double* pdf;
     int stats_updated, bw, symmetric, strict, unsigned_sym;
+    const int32_t* stats_updated_dev;   // when not null: the flag lives on the device (non-zero = updated)
     float steps;   // (float)(2^bw - 1), computed on the host
     double* out;   // {min, max, delta, offset, bw}
     SearchWs* ws;
@@ -109,7 +110,7 @@ __global__ void __launch_bounds__(kSearchWarps * 32) tfe_search_kernel(SearchArg
         if (blockIdx.x == 0 && threadIdx.x == 0)
         {
             double e[5] = {0, 0, 0, 0, 0};
-            if (a.stats_updated)
+            if (a.stats_updated_dev ? (*a.stats_updated_dev != 0) : (a.stats_updated != 0))
             {
                 const double d = __ddiv_rn(2.0, (double) (int) steps);
                 const double o = floor(__ddiv_rn(-1.0, d));
@@ -336,13 +337,13 @@ __global__ void __launch_bounds__(kSearchWarps * 32) tfe_search_kernel(SearchArg
     }
 }
 
-int tfe_search(const aq_tfe_state_t* st, const double* pdf, int stats_updated, int bw, int symmetric, int strict,
-               int unsigned_sym, double* out, void* ws, int64_t ws_bytes, cudaStream_t stream)
+int tfe_search(const aq_tfe_state_t* st, const double* pdf, int stats_updated, const int32_t* stats_updated_dev, int bw,
+               int symmetric, int strict, int unsigned_sym, double* out, void* ws, int64_t ws_bytes, cudaStream_t stream)
 {
     if (ws_bytes < tfe_search_workspace_bytes())
         return AQ_ERR_WORKSPACE;
     SearchArgs a;
-    a.st = st, a.pdf = pdf, a.stats_updated = stats_updated, a.bw = bw;
+    a.st = st, a.pdf = pdf, a.stats_updated = stats_updated, a.stats_updated_dev = stats_updated_dev, a.bw = bw;
     a.symmetric = symmetric, a.strict = strict, a.unsigned_sym = unsigned_sym;
     a.out = out, a.ws = static_cast<SearchWs*>(ws);
     a.steps         = (float) (pow(2.0, (double) bw) - 1.0);

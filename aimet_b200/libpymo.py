@@ -112,7 +112,6 @@ class _TfEnhancedStats:
     def __init__(self):
         self.dev: Optional[ops.TfeDeviceState] = None
         self.updated = False
-        self._mm: Optional[torch.Tensor] = None
 
     def update(self, x: torch.Tensor):
         if self.dev is None:
@@ -121,17 +120,14 @@ class _TfEnhancedStats:
         st = self.dev
         if not st.poll_initialized():
             # first batch(es): the grid comes from this batch's min/max, unless it is all zeros.  The device decides
-            # (the grid setup ignores the offer once a grid exists); the host only stops offering when an
-            # asynchronous read of the flag has come back, so no call waits for the GPU.
-            self._mm = ops.minmax(x, 1, None, propagate_nan=False, out=self._mm)
-            st.init_grid_from(self._mm)
+            # (one launch: min/max pass + grid setup, which returns at once when a grid exists); the host only stops
+            # offering when an asynchronous read of the flag has come back, so no call waits for the GPU.
+            st.offer_grid(x)
             st.start_probe()
         st.add_batch(x)
 
     def compute(self, bw, symmetric, strict, unsigned_sym) -> TfEncoding:
-        st = self.dev
-        st.replay()
-        e = st.search(self.updated, bw, symmetric, strict, unsigned_sym).tolist()
+        e = self.dev.compute_encoding(self.updated, bw, symmetric, strict, unsigned_sym).tolist()
         return TfEncoding(e[0], e[1], e[2], e[3], int(e[4]))
 
     def histogram(self) -> List[Tuple[float, float]]:

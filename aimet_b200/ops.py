@@ -6,7 +6,7 @@ torch stream of the tensor's device.  CPU tensors are rejected: there is no fall
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Dict, Optional, Tuple
+from typing import List, Dict, Optional, Sequence, Tuple
 
 import torch
 
@@ -237,69 +237,114 @@ _INIT_OFF = _lib.AqTfeState.initialized.offset
 _HIST_ROW_BYTES = _lib.AQ_PDF_SIZE * 4
 
 
-_FLAG_POOL: List[torch.Tensor] = []
-_FLAG_NEXT = [0]
+_FLAG_BLOCKS: List[torch.Tensor] = []     # pinned blocks, kept for the life of the process
+_FLAG_FREE: List[torch.Tensor] = []       # slots nobody holds
 
 
 def _pinned_flag() -> torch.Tensor:
-    """One int32 of pinned host memory for an asynchronous flag read.  Slots come from pooled 4 KiB pinned blocks
-    (pinning memory per object would cost more than the synchronisation the probe avoids) and are handed out
-    round-robin: a probe lives for a few batches, the pool for the process."""
-    if not _FLAG_POOL or _FLAG_NEXT[0] >= _FLAG_POOL[-1].numel():
-        if len(_FLAG_POOL) >= 16:
-            _FLAG_NEXT[0] = 0
-            _FLAG_POOL.append(_FLAG_POOL.pop(0))   # recycle the oldest block
-        else:
-            _FLAG_POOL.append(torch.zeros(1024, dtype=torch.int32).pin_memory())
-            _FLAG_NEXT[0] = 0
-    i = _FLAG_NEXT[0]
-    _FLAG_NEXT[0] = i + 1
-    slot = _FLAG_POOL[-1][i:i + 1]
+    """One int32 of pinned host memory for an asynchronous flag read.  Slots are carved from pooled 4 KiB pinned
+    blocks (pinning memory per object would cost more than the synchronisation the probe avoids).  A slot belongs
+    to one statistics object until that object hands it back (_release_flag); a slot that is still held is never
+    given to anybody else, and a new block is pinned when none is free."""
+    if not _FLAG_FREE:
+        block = torch.zeros(1024, dtype=torch.int32).pin_memory()
+        _FLAG_BLOCKS.append(block)
+        _FLAG_FREE.extend(block[i:i + 1] for i in range(block.numel() - 1, -1, -1))
+    slot = _FLAG_FREE.pop()
     slot.zero_()
     return slot
+
+
+def _release_flag(slot: torch.Tensor) -> None:
+    _FLAG_FREE.append(slot)
 
 
 class TfeDeviceState:
     """Device-resident TF-Enhanced statistics of one quantizer: bucket grid + per-batch histogram rows.
 
-    ``hists`` is [capacity, 512] uint32 (stored as int32) and ``counts`` [capacity] int64; row b belongs to the
-    b-th batch offered.  A batch seen before the grid exists (all-zero data) keeps count 0 and is skipped by
-    the replay, exactly as the reference drops it.
+    One int32 buffer holds the whole exchangeable part: ``[capacity, 512]`` histogram rows (uint32 stored as int32),
+    then ``capacity`` int64 counts (as int32 pairs), then two int32 flags (flag 0: "this rank offered a batch").
+    Row b belongs to the b-th batch offered (or to global batch b in a data-parallel calibration).  A batch seen
+    before the grid exists (all-zero data) keeps count 0 and is skipped by the replay, exactly as the reference
+    drops it.  Pass ``capacity`` = the number of batches of the job when it is known: growing the table later costs a
+    reallocation and a copy in the middle of the job.
     """
 
     def __init__(self, device, capacity: int = 256):
         self.device = torch.device(device)
-        # one zero-filled allocation, carved into the state record, the PDF, the result and the iteration count
+        # one zero-filled allocation, carved into the state record, the PDF, the result, the iteration count, the
+        # gate of the cross-rank grid agreement and this rank's (min, max, present) triple
         sb = (_lib.TFE_STATE_BYTES + 15) // 16 * 16
         pb = _lib.AQ_PDF_SIZE * 8
-        blob = torch.zeros(sb + pb + 48 + 16, dtype=torch.uint8, device=self.device)
+        blob = torch.zeros(sb + pb + 48 + 16 + 16, dtype=torch.uint8, device=self.device)
         self.state = blob[:_lib.TFE_STATE_BYTES]
         self.pdf = blob[sb:sb + pb].view(torch.float64)
         self.encoding = blob[sb + pb:sb + pb + 40].view(torch.float64)
         self.iterations = blob[sb + pb + 48:sb + pb + 52].view(torch.int32)
+        self.gate = blob[sb + pb + 52:sb + pb + 56].view(torch.int32)
+        self.range = blob[sb + pb + 64:sb + pb + 76].view(torch.float32)
         self.num_batches = 0
         self.initialized_on_host = False
-        self._alloc_rows(capacity)
+        self._probe = None
+        self._alloc_rows(max(int(capacity), 1))
 
     def _alloc_rows(self, capacity: int, keep: bool = False):
-        rows = torch.zeros(capacity * (_lib.AQ_PDF_SIZE + 2), dtype=torch.int32, device=self.device)
-        h = rows[:capacity * _lib.AQ_PDF_SIZE].view(capacity, _lib.AQ_PDF_SIZE)
-        c = rows[capacity * _lib.AQ_PDF_SIZE:].view(torch.int64)
+        P = _lib.AQ_PDF_SIZE
+        buf = torch.zeros(capacity * (P + 2) + 2, dtype=torch.int32, device=self.device)
+        h = buf[:capacity * P].view(capacity, P)
+        c = buf[capacity * P:capacity * (P + 2)].view(torch.int64)
         if keep:
-            old = self.hists.shape[0]
-            h[:old].copy_(self.hists)
-            c[:old].copy_(self.counts)
-        self.hists, self.counts = h, c
+            old = min(self.hists.shape[0], capacity)
+            h[:old].copy_(self.hists[:old])
+            c[:old].copy_(self.counts[:old])
+            buf[-2:].copy_(self.flags)
+        self.buffer, self.hists, self.counts, self.flags = buf, h, c, buf[-2:]
         self._hp, self._cp, self._sp = h.data_ptr(), c.data_ptr(), self.state.data_ptr()
+
+    @property
+    def capacity(self) -> int:
+        return self.hists.shape[0]
 
     def reserve(self, capacity: int):
         if capacity > self.hists.shape[0]:
             self._alloc_rows(max(capacity, 2 * self.hists.shape[0]), keep=True)
 
+    def resize_exact(self, capacity: int):
+        """Makes the table hold exactly ``capacity`` rows, so that ``buffer`` is the dense thing to exchange."""
+        if capacity != self.hists.shape[0]:
+            self._alloc_rows(capacity, keep=True)
+        self.num_batches = capacity
+
+    # ---- grid ----------------------------------------------------------------------------------------------
     def init_grid_from(self, minmax_dev: torch.Tensor):
         """minmax_dev: float32 tensor holding {min, max} on the device."""
         with _on(self.state):
             check(lib.aq_tfe_init_grid(minmax_dev.data_ptr(), self._sp, _stream(self.state)), "aq_tfe_init_grid")
+
+    def _offer(self, x: torch.Tensor, init: bool, want_range: bool):
+        _tfe_input(x)
+        need = int(lib.aq_tfe_offer_grid_workspace_bytes())
+        ws = workspace(x, need)
+        with _on(x):
+            check(lib.aq_tfe_offer_grid(x.data_ptr(), x.numel(), self._sp, self.range.data_ptr() if want_range else None,
+                                        int(init), ws.data_ptr(), ws.numel(), _stream(x)), "aq_tfe_offer_grid")
+
+    def offer_grid(self, x: torch.Tensor):
+        """One launch: min/max of the batch and, unless a grid exists or the batch is all zeros, the grid from it."""
+        self._offer(x, True, False)
+
+    def batch_range(self, x: Optional[torch.Tensor]) -> torch.Tensor:
+        """(min, max, present) of a batch on the device, for the cross-rank grid agreement; leaves the state alone."""
+        if x is None:
+            self.range.zero_()
+        else:
+            self._offer(x, False, True)
+        return self.range
+
+    def select_grid(self, ranges: torch.Tensor, num_ranks: int, rank: int):
+        with _on(self.state):
+            check(lib.aq_tfe_select_grid(ranges.data_ptr(), int(num_ranks), int(rank), self._sp, self.gate.data_ptr(),
+                                         _stream(self.state)), "aq_tfe_select_grid")
 
     def is_initialized(self) -> bool:
         """Host view of the device flag (synchronises once per call until it turns true, then cached)."""
@@ -307,21 +352,38 @@ class TfeDeviceState:
             self.initialized_on_host = bool(self.state[_INIT_OFF:_INIT_OFF + 4].view(torch.int32).item())
         return self.initialized_on_host
 
-    def poll_initialized(self) -> bool:
-        """Like is_initialized(), but never waits for the device: True once an asynchronous read of the flag
-        (start_probe) that saw 1 has completed.  Callers keep offering min/max to init_grid_from() (a no-op on the
-        device once the grid exists), each offer followed by start_probe(), while the answer is False."""
+    def poll_initialized(self, wait: bool = False) -> bool:
+        """Like is_initialized(), but by default never waits for the device: True once an asynchronous read of the
+        flag (start_probe) that saw 1 has completed.  Callers keep offering batches (a no-op on the device once the
+        grid exists), each offer followed by start_probe(), while the answer is False.  ``wait`` blocks until the
+        read in flight has landed (the device goes on with whatever was queued behind it)."""
         if self.initialized_on_host:
             return True
-        probe = getattr(self, "_probe", None)
+        probe = self._probe
+        if probe is not None and wait:
+            probe[1].synchronize()
         if probe is not None and probe[1].query() and int(probe[0].item()) == 1:
             self.initialized_on_host = True
-            self._probe = None
+            self._drop_probe()
         return self.initialized_on_host
+
+    def _drop_probe(self) -> None:
+        """Hands the pinned slot back.  Only when no copy into it can still be in flight: otherwise the slot stays
+        out of circulation (a later owner must never see this object's flag arrive)."""
+        probe = self._probe
+        self._probe = None
+        if probe is not None and probe[1].query():
+            _release_flag(probe[0])
+
+    def __del__(self):
+        try:
+            self._drop_probe()
+        except Exception:
+            pass
 
     def start_probe(self) -> None:
         """Queues a copy of the flag, as it is after everything enqueued so far, to pinned host memory."""
-        probe = getattr(self, "_probe", None)
+        probe = self._probe
         if probe is not None and not probe[1].query():
             return   # the previous read is still in flight
         flag = _pinned_flag() if probe is None else probe[0]
@@ -330,10 +392,11 @@ class TfeDeviceState:
         event.record(torch.cuda.current_stream(self.device))
         self._probe = (flag, event)
 
-    def add_batch(self, x: torch.Tensor, row: Optional[int] = None):
-        """Histogram of one batch into row ``row`` (default: the next one).  ``x``: dense float32 CUDA tensor."""
-        if x.dtype != torch.float32 or not x.is_cuda:
-            raise RuntimeError("aimet_b200: TF-Enhanced statistics take float32 CUDA input (callers upcast)")
+    # ---- rows ------------------------------------------------------------------------------------------------
+    def add_batch(self, x: torch.Tensor, row: Optional[int] = None, gated: bool = False):
+        """Histogram of one batch into row ``row`` (default: the next one).  ``x``: dense float32 CUDA tensor.
+        ``gated``: the batch only counts if the last select_grid() said so."""
+        _tfe_input(x)
         if row is None:
             row = self.num_batches
         if row >= self.hists.shape[0]:
@@ -341,10 +404,42 @@ class TfeDeviceState:
         if row >= self.num_batches:
             self.num_batches = row + 1
         with _on(x):
-            check(lib.aq_tfe_histogram(x.data_ptr(), x.numel(), self._sp, self._hp + row * _HIST_ROW_BYTES,
-                                       self._cp + row * 8, torch.cuda.current_stream().cuda_stream),
-                  "aq_tfe_histogram")
+            if gated:
+                xs, ns = (C.c_void_p * 1)(x.data_ptr()), (C.c_int64 * 1)(x.numel())
+                check(lib.aq_tfe_histogram_many(xs, ns, 1, 1, self._sp, self._hp + row * _HIST_ROW_BYTES,
+                                                self._cp + row * 8, self.gate.data_ptr(), _stream(x)),
+                      "aq_tfe_histogram_many")
+            else:
+                check(lib.aq_tfe_histogram(x.data_ptr(), x.numel(), self._sp, self._hp + row * _HIST_ROW_BYTES,
+                                           self._cp + row * 8, _stream(x)), "aq_tfe_histogram")
 
+    def add_batches(self, xs: Sequence[torch.Tensor], row0: Optional[int] = None, row_stride: int = 1):
+        """Histograms of several resident batches, ``AQ_TFE_HIST_MANY`` per launch, into rows row0, row0 + row_stride,
+        ...  Only valid once the grid exists (every batch of a launch sees the same state)."""
+        if row0 is None:
+            row0 = self.num_batches
+        if not xs:
+            return
+        last = row0 + (len(xs) - 1) * row_stride
+        if last >= self.hists.shape[0]:
+            self.reserve(last + 1)
+        self.num_batches = max(self.num_batches, last + 1)
+        M = _lib.AQ_TFE_HIST_MANY
+        with _on(xs[0]):
+            st = _stream(xs[0])
+            for i in range(0, len(xs), M):
+                part = xs[i:i + M]
+                for x in part:
+                    _tfe_input(x)
+                m = len(part)
+                ptrs = (C.c_void_p * m)(*[x.data_ptr() for x in part])
+                ns = (C.c_int64 * m)(*[x.numel() for x in part])
+                row = row0 + i * row_stride
+                check(lib.aq_tfe_histogram_many(ptrs, ns, m, int(row_stride), self._sp,
+                                                self._hp + row * _HIST_ROW_BYTES, self._cp + row * 8, None, st),
+                      "aq_tfe_histogram_many")
+
+    # ---- encoding ----------------------------------------------------------------------------------------------
     def replay(self, num_batches: Optional[int] = None):
         nb = self.num_batches if num_batches is None else num_batches
         with _on(self.state):
@@ -360,5 +455,26 @@ class TfeDeviceState:
                                     ws.numel(), _stream(self.state)), "aq_tfe_search")
         return self.encoding
 
+    def compute_encoding(self, stats_updated, bw: int, symmetric: bool, strict: bool, unsigned_sym: bool,
+                         num_batches: Optional[int] = None) -> torch.Tensor:
+        """Replay of the running mean over the rows, then the SQNR search: one call, two dependent launches.
+        ``stats_updated``: a bool, or None to take the flag from ``flags[0]`` on the device."""
+        nb = self.num_batches if num_batches is None else num_batches
+        need = int(lib.aq_tfe_search_workspace_bytes())
+        ws = workspace(self.state, need)
+        with _on(self.state):
+            check(lib.aq_tfe_compute_encoding(self._sp, self._hp, self._cp, nb, self.pdf.data_ptr(),
+                                              self.iterations.data_ptr(), int(bool(stats_updated)),
+                                              self.flags.data_ptr() if stats_updated is None else None, int(bw),
+                                              int(symmetric), int(strict), int(unsigned_sym),
+                                              self.encoding.data_ptr(), ws.data_ptr(), ws.numel(),
+                                              _stream(self.state)), "aq_tfe_compute_encoding")
+        return self.encoding
+
     def x_left(self) -> torch.Tensor:
         return self.state[:_lib.AQ_PDF_SIZE * 8].view(torch.float64)
+
+
+def _tfe_input(x: torch.Tensor) -> None:
+    if x.dtype != torch.float32 or not x.is_cuda:
+        raise RuntimeError("aimet_b200: TF-Enhanced statistics take float32 CUDA input (callers upcast)")

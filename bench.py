@@ -1,11 +1,17 @@
 #!/usr/bin/env python
 """Benchmark of the quantization-simulation hot path on B200.
 
-Headline workload (benchmark configuration 3): TF-Enhanced encoding calibration of one quantizer -- per batch a
-512-bucket histogram of fp32 activations [64, 256, 28, 28] (ReLU(N(0,1)) with 0.1 % outliers x20), then the
-running-PDF replay and the SQNR grid search for an 8-bit asymmetric encoding.  A step is one batch.  With N GPUs
-every rank calibrates its own K batches (batch b of the job belongs to rank b % N) and the ranks exchange the
-per-batch histogram table once (NCCL all-reduce) before the search: weak scaling.
+Headline workload (benchmark configuration 3): TF-Enhanced encoding calibration of one quantizer over 256 batches of
+fp32 activations [64, 256, 28, 28] (ReLU(N(0,1)) with 0.1 % outliers x20): per batch a 512-bucket histogram, then the
+running-PDF replay and the SQNR grid search for an 8-bit asymmetric encoding.
+
+A STEP is one whole calibration job.  `--steps K` times K jobs back to back; the K-job block is repeated until at
+least half a second has been timed and the median block is reported.  With N GPUs every rank calibrates 256 batches
+of its own per job (batch b of the N x 256 belongs to rank b % N) and the ranks exchange the per-batch histogram
+table once per job (one NCCL all-reduce) before the search: weak scaling, `value`.  The same run also times
+configuration 3 itself split over the N ranks (256 batches in total, 256 / N per rank: strong scaling, key `strong`)
+and checks, outside the timed regions, that the N-rank result equals a single-process run over the same batches bit
+for bit (`parity_multi_gpu`).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
@@ -30,13 +36,14 @@ BATCH_SHAPE = (64, 256, 28, 28)
 SAMPLES_PER_BATCH = BATCH_SHAPE[0]
 N_EL = 64 * 256 * 28 * 28
 BATCH_BYTES = 4 * N_EL
-MAX_DISTINCT = 256            # distinct device batches kept per GPU (13.2 GB); more steps cycle through them
+JOB_BATCHES = 256             # batches of one calibration job per GPU (configuration 3; 13.2 GB resident)
 METRIC = "TF-Enhanced calibration throughput (512-bin histogram + SQNR search)"
-WORKLOAD = ("configuration 3: TF-Enhanced calibration, fp32 activations [64,256,28,28] = ReLU(N(0,1)) with 0.1% "
-            "outliers x20, 8-bit asymmetric, 512 buckets")
-# dram__bytes_read+write per algorithmic byte of the histogram kernel, from the ncu capture summarised in
-# profiles/tfe_hist_lane_kernel_relu_256MB.md (captured on a 256 MB input; traffic grows in proportion)
+WORKLOAD = ("configuration 3: TF-Enhanced calibration, 256 batches of fp32 activations [64,256,28,28] = ReLU(N(0,1)) "
+            "with 0.1% outliers x20, 8-bit asymmetric, 512 buckets")
+# dram__bytes_read+write per algorithmic byte of the histogram kernel, from an ncu capture on a 256 MB input
+# (traffic grows in proportion to the input)
 HIST_TRAFFIC_RATIO = 1.024
+MIN_TIMED_S = 0.5
 
 
 def peak_hbm():
@@ -47,6 +54,16 @@ def peak_hbm():
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def job_config(n_gpus: int):
+    """`config` of the JSON line; both arms print exactly this."""
+    return {"workload": WORKLOAD, "batch_shape": list(BATCH_SHAPE), "step": "one calibration job",
+            "batches_per_job_per_gpu": JOB_BATCHES, "batches_per_job": JOB_BATCHES * n_gpus,
+            "samples_per_step": JOB_BATCHES * n_gpus * SAMPLES_PER_BATCH,
+            "parallelism": f"batch-sharded x{n_gpus}, one histogram-table all-reduce per job" if n_gpus > 1
+            else "single GPU",
+            "l2": f"inputs larger than L2: {JOB_BATCHES} distinct batches x 51.4 MB per GPU"}
 
 
 def host_batch(b: int):
@@ -68,19 +85,19 @@ def device_batch(b: int, device):
     return torch.where(m, a * 20, a).view(BATCH_SHAPE)
 
 
+def median_spread(xs):
+    s = sorted(xs)
+    return s[len(s) // 2], s[0], s[-1]
+
+
 # ---------------------------------------------------------------------------------------------------------------------
 # CPU arms (reference code on the host cores)
 # ---------------------------------------------------------------------------------------------------------------------
-def cpu_calibration(num_batches: int, distinct: int = 4):
-    """Times the reference's TF-Enhanced updateStats/computeEncoding on `num_batches` batches (single thread: the
-    reference's loops are scalar and serial).  Returns (seconds, kind)."""
+def cpu_calibration(num_batches: int, data):
+    """Times the reference's TF-Enhanced updateStats/computeEncoding on `num_batches` batches cycled from `data`
+    (single thread: the reference's loops are scalar and serial).  Returns (seconds, kind)."""
     from oracle import Oracle, OracleTfeAnalyzer, RefAnalyzer, Reference
-    data = [host_batch(b) for b in range(min(distinct, num_batches))]
-    if Reference.available():
-        an, kind = RefAnalyzer(Reference(), "tfe"), "reference"
-    else:
-        an, kind = OracleTfeAnalyzer(Oracle()), "port"
-    an.update(data[0][:4096])            # warm-up (page in the library), then a fresh analyzer
+    kind = "reference" if Reference.available() else "port"
     an = RefAnalyzer(Reference(), "tfe") if kind == "reference" else OracleTfeAnalyzer(Oracle())
     t0 = time.perf_counter()
     for b in range(num_batches):
@@ -89,24 +106,39 @@ def cpu_calibration(num_batches: int, distinct: int = 4):
     return time.perf_counter() - t0, kind
 
 
+CPU_SAMPLE_BATCHES = 8   # batches of the job that one CPU step really runs (about a quarter of a second)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    # warm-up steps, then K timed steps; one step = one full batch through the reference's CPU code
-    cpu_calibration(min(args.warmup, 1), 1)
-    secs, kind = cpu_calibration(args.steps)
-    value = args.steps * SAMPLES_PER_BATCH / secs
+    # A step is a bounded sample of the job: the first CPU_SAMPLE_BATCHES batches through updateStats, then
+    # computeEncoding.  The reference's per-batch cost does not depend on how many batches came before, so
+    # samples/s of the sample is samples/s of the whole job.
+    data = [host_batch(b) for b in range(4)]
+    for _ in range(max(args.warmup, 1)):
+        cpu_calibration(1, data)
+    times = []
+    kind = "port"
+    for _ in range(args.steps):
+        secs, kind = cpu_calibration(CPU_SAMPLE_BATCHES, data)
+        times.append(secs)
+    total = sum(times)
+    value = args.steps * CPU_SAMPLE_BATCHES * SAMPLES_PER_BATCH / total
+    sample = (f"each step = the first {CPU_SAMPLE_BATCHES} of the job's {JOB_BATCHES} batches [64,256,28,28] (4 distinct, "
+              f"cycled) + computeEncoding; {args.steps} steps, {total:.1f} s")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "batch_shape": list(BATCH_SHAPE), "batches": args.steps,
-                   "note": "reference DlQuantization TfEnhancedEncodingAnalyzer on the host, rank 0 only"},
-        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": 1, "kind": kind,
-                         "sample": f"{args.steps} batches of [64,256,28,28] (4 distinct, cycled) + computeEncoding"},
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total / args.steps * 1e3 * (JOB_BATCHES * args.gpus / CPU_SAMPLE_BATCHES),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": job_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": 1, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "notes": "reference DlQuantization TfEnhancedEncodingAnalyzer on one host core (its loops are scalar and "
+                 "serial), rank 0 only; ms_per_step is the sampled rate scaled to a whole job",
     }
     print(json.dumps(line), flush=True)
 
@@ -121,6 +153,8 @@ class ClockSampler(threading.Thread):
     def __init__(self, index: int):
         super().__init__(daemon=True)
         self.index, self.samples, self.reasons, self.max_mhz, self.ok = index, [], set(), None, False
+        self.loaded = []          # samples taken while `busy` was set (inside a timed region)
+        self.busy = False
         self._stop_evt = threading.Event()
         try:
             import pynvml
@@ -135,29 +169,57 @@ class ClockSampler(threading.Thread):
     def run(self):
         while self.ok and not self._stop_evt.is_set():
             try:
-                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
-                r = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
-                for bit, name in self.REASONS.items():
-                    if r & bit:
-                        self.reasons.add(name)
+                mhz = self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)
+                self.samples.append(mhz)
+                if self.busy:
+                    self.loaded.append(mhz)
+                    r = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                    for bit, name in self.REASONS.items():
+                        if r & bit:
+                            self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.01)
+            time.sleep(0.005)
 
     def stop(self):
         self._stop_evt.set()
         if self.is_alive():
             self.join(timeout=1.0)
-        s = sorted(self.samples)
-        # samples under load: the upper half (idle samples between phases sit at the idle clock)
-        busy = s[len(s) // 2:] if s else []
-        return {"sm_mhz": busy[len(busy) // 2] if busy else None, "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(s)}
+        s = sorted(self.loaded)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples), "samples_under_load": len(s)}
 
 
 # ---------------------------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------------------------
+def gpu_numa_setup(local: int):
+    """Best effort: run this rank on the CPUs of its GPU's NUMA node, so that the pinned staging buffers it
+    allocates afterwards are local to the GPU's PCIe root.  Returns a short description for the JSON line."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local)
+        bus = pynvml.nvmlDeviceGetPciInfo(h).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        path = f"/sys/bus/pci/devices/{bus[-12:].lower()}/numa_node"
+        node = int(open(path).read()) if os.path.exists(path) else -1
+        if node < 0:
+            return {"gpu_numa_node": node, "affinity": "unchanged"}
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        want = cpus & allowed
+        if want:
+            os.sched_setaffinity(0, want)
+            return {"gpu_numa_node": node, "affinity": f"{len(want)} CPUs of node {node}"}
+        return {"gpu_numa_node": node, "affinity": f"unchanged (node {node} CPUs not in this process's cpuset)"}
+    except Exception as e:   # sysfs / NVML not available: nothing to do
+        return {"gpu_numa_node": None, "affinity": f"unchanged ({type(e).__name__})"}
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -167,87 +229,273 @@ def run_b200(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the B200 arm has no CPU fallback")
+    numa = gpu_numa_setup(local)
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    from aimet_b200 import _lib, libpymo
+    from aimet_b200 import _lib, libpymo, ops
     from aimet_b200._lib import lib
     from aimet_b200.calibration import TfEnhancedCalibrator
 
-    K, W = args.steps, max(args.warmup, 3)
+    K, W = max(args.steps, 1), max(args.warmup, 3)
     sampler = ClockSampler(local)
     sampler.start()
 
     # ---- data: this rank's batches (global batch index k * world + rank), resident in HBM -----------------------
-    distinct = min(max(K, 4), MAX_DISTINCT)   # at least 4 x 51 MB, so that the rotating inputs exceed the 126 MB L2
-    batches = [device_batch(k * world + rank, device) for k in range(distinct)]
+    batches = [device_batch(k * world + rank, device) for k in range(JOB_BATCHES)]
     torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def calibrate(steps):
-        cal = TfEnhancedCalibrator(device)
-        for k in range(steps):
-            cal.update(batches[k % distinct])
-        return cal.compute_encoding(8, False, False, False)
+    def max_over_ranks(secs):
+        if world > 1:
+            t = torch.tensor([secs], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t)
+        return secs
 
-    # ---- warm-up, then the timed job ------------------------------------------------------------------------------
-    calibrate(W)
-    barrier()
-    launches0 = _lib.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    enc = calibrate(K)
-    e1.record()
-    barrier()
-    launches = _lib.launch_count() - launches0
-    secs = e0.elapsed_time(e1) * 1e-3
+    def calibrate(rounds):
+        """One job: `rounds` batches of this rank (all resident), exchange, replay, search, encoding on the host."""
+        cal = TfEnhancedCalibrator(device, num_batches=rounds * world)
+        cal.update_many(batches[:rounds])
+        return cal, cal.compute_encoding(8, False, False, False)
+
+    def timed_jobs(rounds, steps):
+        """`steps` jobs back to back, device-timed, max over ranks."""
+        barrier()
+        sampler.busy = True
+        e0.record()
+        for _ in range(steps):
+            out = calibrate(rounds)
+        e1.record()
+        barrier()
+        sampler.busy = False
+        return max_over_ranks(e0.elapsed_time(e1) * 1e-3), out
+
+    def measure(rounds):
+        """W warm-up jobs, then blocks of exactly K jobs until MIN_TIMED_S has been timed (at least 3 blocks)."""
+        for _ in range(W):
+            calibrate(rounds)
+        launches0 = _lib.launch_count()
+        first, out = timed_jobs(rounds, K)
+        launches = _lib.launch_count() - launches0
+        reps = max(3, min(200, int(MIN_TIMED_S / max(first, 1e-6)) + 1))
+        if world > 1:   # every rank must run the same number of blocks
+            t = torch.tensor([reps], dtype=torch.int64, device=device)
+            dist.broadcast(t, 0)
+            reps = int(t)
+        times = [first] + [timed_jobs(rounds, K)[0] for _ in range(reps - 1)]
+        med, lo, hi = median_spread(times)
+        return {"secs": med, "min": lo, "max": hi, "blocks": len(times), "total_s": sum(times),
+                "launches": launches, "out": out}
+
+    # ---- the timed job: 256 batches per GPU (weak scaling) -----------------------------------------------------------
+    weak = measure(JOB_BATCHES)
+    value = world * K * JOB_BATCHES * SAMPLES_PER_BATCH / weak["secs"]
+    cal, enc = weak["out"]
+
+    # ---- configuration 3 itself split over the ranks (strong scaling): 256 batches in total --------------------------
+    strong = None
+    if world > 1 and JOB_BATCHES % world == 0:
+        strong = measure(JOB_BATCHES // world)
+
+    # ---- parity of the N-rank result with a single-process run over the same batches (outside the timed regions) ----
+    parity = None
     if world > 1:
-        t = torch.tensor([secs], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        secs = float(t)
-    value = world * K * SAMPLES_PER_BATCH / secs
+        parity = multi_gpu_parity(torch, dist, device, rank, world, batches,
+                                  [("weak", weak["out"]), ("strong", strong["out"])] if strong else [("weak", weak["out"])])
 
-    # ---- roofline of the dominant kernel: K back-to-back histogram launches through the raw C ABI ------------------
-    from aimet_b200 import ops
-    st = ops.TfeDeviceState(device, capacity=distinct)
-    st.init_grid_from(ops.minmax(batches[0]).reshape(-1))
+    # ---- roofline of the dominant kernel: back-to-back launches through the raw C ABI, CUDA events ---------------------
+    roof = hist_roofline(torch, lib, ops, device, batches, e0, e1, sampler)
+
+    # ---- end to end: batches start in pinned host memory; H2D copy + updateStats per batch, getEncoding per job ------
+    e2e = e2e_leg(torch, libpymo, device, batches, K, W, barrier, max_over_ranks, e0, e1, sampler)
+    e2e_value = world * K * JOB_BATCHES * SAMPLES_PER_BATCH / e2e["secs"]
+    h2d_rates = [e2e["h2d_gbps"]]
+    if world > 1:
+        t = torch.zeros(world, dtype=torch.float64, device=device)
+        t[rank] = e2e["h2d_gbps"]
+        dist.all_reduce(t)
+        h2d_rates = [round(v, 2) for v in t.tolist()]
+
+    # ---- secondary numbers (rank 0): fake-quant kernels, model-level configurations 4 and 5 ----------------------------
+    del batches
+    torch.cuda.empty_cache()
+    qdq = qdq_numbers(torch, lib, device, roof["peak"]) if (rank == 0 and not args.skip_qdq) else None
+    models = None
+    if rank == 0 and world == 1 and not args.skip_models:
+        from aimet_b200.v2 import model_cases
+        models = {}
+        for name, kw in (("resnet50", {"batches": 32, "batch_size": 128}), ("llama_layer", {})):
+            try:
+                models[name] = model_cases.CASES[name](device, **kw)
+            except Exception as e:   # a model case must not take the headline down with it
+                models[name] = {"error": f"{type(e).__name__}: {e}"}
+            torch.cuda.empty_cache()
+    clocks = sampler.stop()
+
+    # ---- CPU baseline: the reference's own code on one host core, bounded sample (rank 0, N = 1 only) -------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        nb = 400
+        data = [host_batch(b) for b in range(4)]
+        cpu_calibration(1, data)
+        cs, kind = cpu_calibration(nb, data)
+        cpu = {"value": nb * SAMPLES_PER_BATCH / cs, "unit": "samples/s", "cores": 1, "kind": kind,
+               "sample": f"{nb} batches of [64,256,28,28] (4 distinct, cycled) + computeEncoding, {cs:.1f} s"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": weak["secs"] / K * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": job_config(world),
+            "timing": {"blocks_of_K_steps": weak["blocks"], "timed_region_s": weak["total_s"],
+                       "block_s_median": weak["secs"], "block_s_min": weak["min"], "block_s_max": weak["max"],
+                       "us_per_batch": weak["secs"] / (K * JOB_BATCHES) * 1e6,
+                       "timed_region": "per job: update_many over the rank's resident batches (first batch: fused "
+                                       "min/max + grid setup, then histogram launches of up to 16 batches), "
+                                       "table all-reduce (N > 1), PDF replay + SQNR search, encoding read-back"},
+            "encoding": [enc.min, enc.max, enc.delta, enc.offset, enc.bw],
+            "roofline": roof,
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": JOB_BATCHES * BATCH_BYTES,
+                    "d2h_bytes_per_step": 40, "ms_per_step": e2e["secs"] / K * 1e3,
+                    "ms_per_batch": e2e["secs"] / (K * JOB_BATCHES) * 1e3, "h2d_GBps_per_rank": h2d_rates,
+                    "api": "AimetTensorQuantizer.updateStats per batch (pinned host buffer -> device copy inside the "
+                           "timed region) / getEncoding per job (the 5-double encoding comes back to the host)",
+                    "numa": numa},
+            "gpu_launches": weak["launches"],
+            "clocks": clocks,
+        }
+        if strong is not None:
+            sv = K * JOB_BATCHES * SAMPLES_PER_BATCH / strong["secs"]
+            line["strong"] = {"value": sv, "unit": "samples/s", "scaling": "strong", "batches_per_job": JOB_BATCHES,
+                              "batches_per_job_per_gpu": JOB_BATCHES // world,
+                              "ms_per_step": strong["secs"] / K * 1e3, "blocks_of_K_steps": strong["blocks"],
+                              "block_s_min": strong["min"], "block_s_max": strong["max"]}
+        if parity is not None:
+            line["parity_multi_gpu"] = parity["ok"]
+            line["parity_multi_gpu_detail"] = parity
+        if qdq is not None:
+            line["qdq"] = qdq
+        if models is not None:
+            line["model_cases"] = models
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def multi_gpu_parity(torch, dist, device, rank, world, batches, jobs):
+    """Bit-for-bit check of the N-rank result against a single-process run over the same global batches.
+
+    Every rank contributes its encoding (all ranks must hold the same bits: nothing is broadcast); rank 0 regenerates
+    the batches of the other ranks one at a time (batches are seeded by global index), runs the single-process
+    calibrator over all of them in global order and compares the encoding, the merged [n, 512] row table and the
+    counts as raw bits.  Returns {"ok": bool, "<job>": {...mismatch counts...}}."""
+    from aimet_b200.calibration import TfEnhancedCalibrator
+    result = {"ok": True}
+    for name, (cal, enc) in jobs:
+        n_total = cal.round * world
+        mine = torch.tensor([enc.min, enc.max, enc.delta, enc.offset, float(enc.bw)], dtype=torch.float64, device=device)
+        everyone = torch.empty(world * 5, dtype=torch.float64, device=device)
+        dist.all_gather_into_tensor(everyone, mine)
+        detail = {"batches": n_total}
+        if rank == 0:
+            ranks_differ = int((everyone.view(world, 5).view(torch.int64) != mine.view(torch.int64)).any(dim=1).sum())
+            single = TfEnhancedCalibrator(device, num_batches=n_total)
+            single.distributed, single.world, single.rank = False, 1, 0
+            for g in range(n_total):
+                x = batches[g // world] if g % world == 0 else device_batch(g, device)
+                single.update(x)
+            ref = single.compute_encoding(8, False, False, False)
+            st_n, st_1 = cal.engine.state, single.engine.state
+            rows_bad = int((st_n.hists[:n_total] != st_1.hists[:n_total]).any(dim=1).sum())
+            counts_bad = int((st_n.counts[:n_total] != st_1.counts[:n_total]).sum())
+            enc_same = [ref.min, ref.max, ref.delta, ref.offset, ref.bw] == [enc.min, enc.max, enc.delta, enc.offset, enc.bw]
+            pdf_bad = int((st_n.pdf.view(torch.int64) != st_1.pdf.view(torch.int64)).sum())
+            detail.update({"ranks_with_other_encoding": ranks_differ, "rows_mismatched": rows_bad,
+                           "counts_mismatched": counts_bad, "pdf_buckets_mismatched": pdf_bad,
+                           "encoding_equal": bool(enc_same)})
+            ok = ranks_differ == 0 and rows_bad == 0 and counts_bad == 0 and pdf_bad == 0 and enc_same
+            result["ok"] = bool(result["ok"] and ok)
+        result[name] = detail
+    flag = torch.tensor([1 if result["ok"] else 0], dtype=torch.int32, device=device)
+    dist.broadcast(flag, 0)
+    result["ok"] = bool(int(flag))
+    return result
+
+
+def hist_roofline(torch, lib, ops, device, batches, e0, e1, sampler):
+    """The dominant kernel alone, as the job launches it (16 resident batches per launch) and one batch per launch."""
+    import ctypes as C
+    M = 16
+    n = len(batches)
+    st = ops.TfeDeviceState(device, capacity=n)
+    st.offer_grid(batches[0])
     stream = torch.cuda.current_stream().cuda_stream
-    ptrs = [b.data_ptr() for b in batches]
     hp, cp, sp = st.hists.data_ptr(), st.counts.data_ptr(), st.state.data_ptr()
-    reps = max(K, 64)
-    for i in range(3):
-        lib.aq_tfe_histogram(ptrs[i % distinct], N_EL, sp, hp + 2048 * (i % distinct), cp + 8 * (i % distinct), stream)
-    torch.cuda.synchronize()
-    e0.record()
-    for i in range(reps):
-        j = i % distinct
-        lib.aq_tfe_histogram(ptrs[j], N_EL, sp, hp + 2048 * j, cp + 8 * j, stream)
-    e1.record()
-    torch.cuda.synchronize()
-    kernel_s = e0.elapsed_time(e1) * 1e-3 / reps
-    peak, peak_kind = peak_hbm()
-    achieved = BATCH_BYTES / kernel_s / 1e9
+    groups = []
+    for i in range(0, n, M):
+        part = batches[i:i + M]
+        groups.append(((C.c_void_p * len(part))(*[b.data_ptr() for b in part]),
+                       (C.c_int64 * len(part))(*[b.numel() for b in part]), len(part), i))
 
-    # ---- end to end: batches start in pinned host memory; H2D copy, updateStats, and a D2H read every step ---------
+    def many_pass():
+        for ptrs, ns, m, row in groups:
+            lib.aq_tfe_histogram_many(ptrs, ns, m, 1, sp, hp + 2048 * row, cp + 8 * row, None, stream)
+
+    def single_pass():
+        for i, b in enumerate(batches):
+            lib.aq_tfe_histogram(b.data_ptr(), N_EL, sp, hp + 2048 * i, cp + 8 * i, stream)
+
+    out = {}
+    for name, fn, launches in (("many", many_pass, len(groups)), ("single", single_pass, n)):
+        fn()
+        torch.cuda.synchronize()
+        sampler.busy = True
+        times = []
+        for _ in range(5):
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e-3)
+        sampler.busy = False
+        out[name] = median_spread(times)[0] / launches
+    peak, peak_kind = peak_hbm()
+    per_launch = M * BATCH_BYTES
+    achieved = per_launch / out["many"] / 1e9
+    single = BATCH_BYTES / out["single"] / 1e9
+    return {"bound": "hbm", "kernel": "tfe_hist_lane_kernel", "achieved": achieved, "peak": peak,
+            "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": HIST_TRAFFIC_RATIO * per_launch, "bytes_per_launch": per_launch,
+            "batches_per_launch": M, "us_per_launch": out["many"] * 1e6,
+            "one_batch_per_launch": {"bytes_per_launch": BATCH_BYTES, "us_per_launch": out["single"] * 1e6,
+                                     "achieved": single, "frac": single / peak}}
+
+
+def e2e_leg(torch, libpymo, device, batches, K, W, barrier, max_over_ranks, e0, e1, sampler):
+    """K jobs through the reference-facing API with HOST buffers: every batch is copied from pinned host memory to the
+    device inside the timed region (double-buffered on a copy stream), and every job ends with getEncoding."""
     ring = [torch.empty(BATCH_SHAPE, dtype=torch.float32).pin_memory() for _ in range(4)]
     for i, r in enumerate(ring):
-        r.copy_(batches[i % distinct])
+        r.copy_(batches[i])
     dev_buf = [torch.empty(BATCH_SHAPE, dtype=torch.float32, device=device) for _ in range(2)]
     copy_stream = torch.cuda.Stream(device)
     copied = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
-    host_counts = torch.zeros(2, dtype=torch.int64).pin_memory()
 
-    def e2e_job(steps):
+    def job(num):
         q = libpymo.AimetTensorQuantizer(libpymo.QUANTIZATION_TF_ENHANCED)
         main = torch.cuda.current_stream()
-        for k in range(steps):
+        for k in range(num):
             s = k % 2
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(consumed[s])
@@ -256,63 +504,24 @@ def run_b200(args):
             main.wait_event(copied[s])
             q.updateStats(dev_buf[s], True)
             consumed[s].record(main)
-            # per-step device->host read of the step's result (the batch's sample count)
-            host_counts[s:s + 1].copy_(q._stats.dev.counts[k:k + 1], non_blocking=True)
         return q.getEncoding(8, False, False, False)
 
     for ev in consumed:
         ev.record(torch.cuda.current_stream())
-    e2e_job(W)
+    job(8)   # warm-up: a short job is enough to page everything in
+    # e2e steps are long (a quarter of a second each): a few of them already give a stable number
+    steps = K if K * JOB_BATCHES * 1e-3 < 6.0 else max(1, int(6.0 / (JOB_BATCHES * 1e-3)))
     barrier()
+    sampler.busy = True
     e0.record()
-    e2e_job(K)
+    for _ in range(steps):
+        job(JOB_BATCHES)
     e1.record()
     barrier()
-    e2e_secs = e0.elapsed_time(e1) * 1e-3
-    if world > 1:
-        t = torch.tensor([e2e_secs], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_secs = float(t)
-    e2e_value = world * K * SAMPLES_PER_BATCH / e2e_secs
-
-    # ---- secondary numbers: fake-quant forward / backward kernels (reported, not the headline) ---------------------
-    qdq = qdq_numbers(torch, lib, device, peak) if (rank == 0 and not args.skip_qdq) else None
-    clocks = sampler.stop()
-
-    # ---- CPU baseline: the reference's own code on one host core, bounded sample (rank 0, N = 1 only) -------------
-    cpu = None
-    if rank == 0 and world == 1 and not args.skip_cpu:
-        nb = 200
-        cs, kind = cpu_calibration(nb)
-        cpu = {"value": nb * SAMPLES_PER_BATCH / cs, "unit": "samples/s", "cores": 1, "kind": kind,
-               "sample": f"{nb} batches of [64,256,28,28] (4 distinct, cycled) + computeEncoding, {cs:.1f} s"}
-
-    if rank == 0:
-        line = {
-            "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": secs / K * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_shape": list(BATCH_SHAPE), "batches_per_gpu": K,
-                       "batches_total": K * world, "parallelism": f"batch-sharded x{world}, histogram-table all-reduce",
-                       "l2": f"inputs larger than L2: {distinct} distinct batches x 51.4 MB per GPU",
-                       "timed_region": "K x update (histogram kernel; first batch also min/max + grid) + exchange + "
-                                       "PDF replay + SQNR search + encoding read-back",
-                       "encoding": [enc.min, enc.max, enc.delta, enc.offset, enc.bw]},
-            "roofline": {"bound": "hbm", "kernel": "tfe_hist_lane_kernel", "achieved": achieved, "peak": peak,
-                         "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": HIST_TRAFFIC_RATIO * BATCH_BYTES, "bytes_per_launch": BATCH_BYTES,
-                         "us_per_launch": kernel_s * 1e6},
-            "cpu_baseline": cpu,
-            "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": BATCH_BYTES, "d2h_bytes_per_step": 8,
-                    "ms_per_step": e2e_secs / K * 1e3, "api": "AimetTensorQuantizer.updateStats / getEncoding"},
-            "gpu_launches": launches,
-            "clocks": clocks,
-        }
-        if qdq is not None:
-            line["qdq"] = qdq
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    sampler.busy = False
+    local = e0.elapsed_time(e1) * 1e-3
+    secs = max_over_ranks(local) * K / steps    # scaled to K steps when fewer were run
+    return {"secs": secs, "steps_run": steps, "h2d_gbps": steps * JOB_BATCHES * BATCH_BYTES / local / 1e9}
 
 
 def qdq_numbers(torch, lib, device, peak):
@@ -389,7 +598,7 @@ def qdq_numbers(torch, lib, device, peak):
 # ---------------------------------------------------------------------------------------------------------------------
 # single-kernel cases (micro-benchmarks; also the small commands the ncu captures under profiles/ were taken with)
 # ---------------------------------------------------------------------------------------------------------------------
-KERNEL_CASES = ("tfe_hist", "minmax_f32", "minmax_f32_rows", "minmax_bf16_block64", "v2_qdq_f32", "v2_qdq_f32_mask",
+KERNEL_CASES = ("tfe_hist", "tfe_hist_many", "tfe_offer_grid", "minmax_f32", "minmax_f32_rows", "minmax_bf16_block64", "v2_qdq_f32", "v2_qdq_f32_mask",
                 "v2_qdq_f32_per_channel", "v2_qdq_bf16", "v2_qdq_bf16_block64", "v2_bwd_f32", "v2_bwd_bf16",
                 "pymo_qdq_f32", "pymo_qdq_f32_per_channel", "ste_v1_f32", "tfe_replay", "tfe_search")
 
@@ -397,7 +606,7 @@ KERNEL_CASES = ("tfe_hist", "minmax_f32", "minmax_f32_rows", "minmax_bf16_block6
 def build_kernel_case(name, mb, torch, lib, device):
     """Returns (calls, algorithmic bytes per launch): `calls` launch the named kernel through the C ABI on rotating
     inputs of `mb` MB each whose total exceeds the L2 capacity."""
-    from aimet_b200 import ops
+    from aimet_b200 import ops, _lib
     stream = torch.cuda.current_stream().cuda_stream
     half = "bf16" in name
     esz = 2 if half else 4
@@ -435,7 +644,29 @@ def build_kernel_case(name, mb, torch, lib, device):
             return calls, rows * (2048 + 8) + 4096, [st, x]
         calls = [lambda: lib.aq_tfe_search(P(st.state), P(st.pdf), 1, 8, 0, 0, 0, P(st.encoding), P(ws), ws.numel(), stream)]
         return calls, 2 * 512 * 8, [st, x, ws]
-    xs = data("relu_outliers" if name == "tfe_hist" else "normal")
+    if name == "tfe_hist_many":
+        # 16 resident batches of `mb` MB per launch, each into its own row; two such groups are rotated
+        import ctypes as C
+        nbuf = 32
+        xs = data("relu_outliers")
+        st = ops.TfeDeviceState(device, capacity=nbuf)
+        st.offer_grid(xs[0])
+        hp, cp, sp = P(st.hists), P(st.counts), P(st.state)
+        groups = [((C.c_void_p * 16)(*[P(x) for x in xs[i:i + 16]]), (C.c_int64 * 16)(*([n] * 16)), i) for i in (0, 16)]
+        calls = [lambda g=g: lib.aq_tfe_histogram_many(g[0], g[1], 16, 1, sp, hp + 2048 * g[2], cp + 8 * g[2], None, stream)
+                 for g in groups]
+        return calls, 16 * 4 * n, [st, groups] + xs
+    xs = data("relu_outliers" if name.startswith("tfe_") else "normal")
+    if name == "tfe_offer_grid":
+        # fused min/max pass + grid setup on a state that is reset before every launch (otherwise the launch is a no-op)
+        st = ops.TfeDeviceState(device, capacity=1)
+        ws = ops.workspace(st.state, int(lib.aq_tfe_offer_grid_workspace_bytes()))
+        sp = P(st.state)
+        flag = st.state[_lib.AqTfeState.initialized.offset:_lib.AqTfeState.initialized.offset + 4]
+        def call(i):
+            flag.zero_()
+            return lib.aq_tfe_offer_grid(P(xs[i]), n, sp, None, 1, P(ws), ws.numel(), stream)
+        return [lambda i=i: call(i) for i in range(nbuf)], 4 * n, [st, ws] + xs
     if name == "tfe_hist":
         st = ops.TfeDeviceState(device, capacity=nbuf)
         st.init_grid_from(ops.minmax(xs[0]).reshape(-1))
@@ -520,11 +751,12 @@ def run_kernel_case(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=20, help="calibration jobs per timed block")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg")
     ap.add_argument("--skip-qdq", action="store_true", help="omit the secondary fake-quant kernel numbers")
+    ap.add_argument("--skip-models", action="store_true", help="omit the model-level cases (configurations 4 and 5)")
     ap.add_argument("--kernel-case", choices=KERNEL_CASES, help="time one kernel alone instead of the calibration job")
     ap.add_argument("--mb", type=int, default=256, help="input size in MB for --kernel-case")
     ap.add_argument("--model-case", choices=("resnet50", "llama_layer"),

@@ -215,12 +215,15 @@ int aq_minmax(const void* d_x, int dtype, int64_t n, int64_t num_ch, int64_t inn
  * off: such a caller has nowhere to get the workspace that aq_minmax asks for.  Here the scratch is a fixed array
  * of AQ_MINMAX_STATIC_SCRATCH_BYTES inside the library; the caller passes only the input and the two outputs.
  *   - Same results as aq_minmax(..., accumulate = 0, ...): one min and one max per encoding channel.
- *   - Returns AQ_ERR_TOO_LARGE when the geometry would need more scratch than the array holds, i.e. when
- *     aq_minmax_workspace_bytes(n, num_ch, inner) > AQ_MINMAX_STATIC_SCRATCH_BYTES (whole-tensor statistics
- *     always fit; per-channel statistics fit up to about 130,000 (row, segment) partials).
+ *   - Returns AQ_ERR_TOO_LARGE when the call would touch more scratch than the array holds.  Whole-tensor
+ *     statistics always fit.  Per-channel / per-block statistics whose rows each map to one output (n / inner ==
+ *     num_ch and rows short enough not to be split) write straight to the outputs and fit at any size; the others
+ *     keep one (min, max) pair per (row, segment) in the scratch and fit up to about 130,000 such pairs.  The limit
+ *     is never looser than aq_minmax_workspace_bytes(n, num_ch, inner) <= AQ_MINMAX_STATIC_SCRATCH_BYTES.
  *   - Calls no cudaMalloc / cudaFree and no allocating library routine.  The first call on each device looks the
  *     array's device address up (cudaGetSymbolAddress, with that device current); make that first call before
- *     any stream capture begins.
+ *     any stream capture begins.  That look-up may run on several host threads at once (they store the same
+ *     address).
  *   - All calls on a device share the one array and it keeps the previous call's contents; the entry point clears
  *     the part that has to start at zero on `stream` itself.  Calls that overlap on the GPU (different streams,
  *     no ordering between them) race on the scratch: serialise them. */
@@ -241,6 +244,45 @@ int aq_tfe_init_grid(const float* d_minmax, aq_tfe_state_t* d_state, void* strea
 int aq_tfe_histogram(const float* d_x, int64_t n, const aq_tfe_state_t* d_state, uint32_t* d_hist, int64_t* d_count,
                      void* stream);
 
+/* Most batches one aq_tfe_histogram_many call takes. */
+#define AQ_TFE_HIST_MANY 16
+
+/* aq_tfe_histogram for m batches that are all resident already (1 <= m <= AQ_TFE_HIST_MANY), in ONE launch: batch b
+ * (h_d_x[b], h_n[b] elements) is added into row d_hists + b * row_stride * 512 and sets d_counts[b * row_stride]
+ * (row_stride = 1: adjacent rows; a rank of a data-parallel calibration that owns every R-th batch passes R).  The reference has no such
+ * call -- TfEnhancedEncodingAnalyzer::updateStats (src/TfEnhancedEncodingAnalyzer.cpp:60-76) takes one tensor at a
+ * time -- but a calibration that holds a list of batches gives the same rows this way without the gap between
+ * launches, which at 51 MB per batch is a third of the time.  h_d_x and h_n are HOST arrays (of device pointers and
+ * of element counts); they are read before the call returns.
+ * d_gate (may be NULL): one int32 on the device; when it holds 0 the batches are dropped (counts 0, rows untouched),
+ * exactly as when the state is not initialised.  See aq_tfe_select_grid. */
+int aq_tfe_histogram_many(const float* const* h_d_x, const int64_t* h_n, int m, int64_t row_stride,
+                          const aq_tfe_state_t* d_state, uint32_t* d_hists, int64_t* d_counts, const int32_t* d_gate,
+                          void* stream);
+
+/* Bytes of scratch for aq_tfe_offer_grid (zero-filled before first use, 256-byte aligned, left reusable). */
+int64_t aq_tfe_offer_grid_workspace_bytes(void);
+
+/* Offers a batch as the one that defines the bucket grid: min and max of d_x in one pass and, in the same launch, the
+ * grid set-up from them.  Replaces GetMin + GetMax + InitializePdf in the first-batch branch of UpdatePdf
+ * (src/math_functions.cpp:207-262), which the reference runs as two tensor passes, two host read-backs and host
+ * arithmetic.  When the state is initialised already the launch returns without touching d_x, so a caller that has
+ * not yet learned on the host whether the grid exists can keep offering batches without waiting for the device.
+ * d_range (may be NULL): 3 floats {min, max, 1.0f} of the batch, {0, 0, 1} when the pass was skipped.
+ * init = 0: only report the range, leave the state alone (grid agreement across ranks, aq_tfe_select_grid). */
+int aq_tfe_offer_grid(const float* d_x, int64_t n, aq_tfe_state_t* d_state, float* d_range, int init,
+                      void* d_workspace, int64_t workspace_bytes, void* stream);
+
+/* Grid agreement of a data-parallel calibration, decided on the device.  d_ranges: num_ranks triples {min, max,
+ * present} of the batches of one round in global order (an all-gather of every rank's d_range; present = 0 for a rank
+ * without a batch).  The first present batch whose (min, max) is not (0, 0) defines the grid -- the rule of the
+ * sequential reference (src/math_functions.cpp:248-262) applied to the round.  *d_gate becomes 1 when this rank's
+ * batch of the round counts and 0 when it must be dropped (no grid yet, or an all-zero batch that precedes the
+ * defining one).  No-op with *d_gate = 1 when the state is initialised already.  The reference calibrates in one
+ * process and has no counterpart. */
+int aq_tfe_select_grid(const float* d_ranges, int num_ranks, int rank, aq_tfe_state_t* d_state, int32_t* d_gate,
+                       void* stream);
+
 /* Replays the running mean pdf <- (pdf*k + hist/cnt)/(k+1) over `num_batches` per-batch histograms in order,
  * skipping rows whose count is 0.  Replaces the accumulation loop of UpdatePdf (src/math_functions.cpp:278-287).
  * d_hists: [num_batches, 512] uint32; d_counts: [num_batches] int64; d_pdf: 512 doubles (overwritten);
@@ -258,6 +300,17 @@ int64_t aq_tfe_search_workspace_bytes(void);
 int aq_tfe_search(const aq_tfe_state_t* d_state, const double* d_pdf, int stats_updated, int bw, int symmetric,
                   int strict_symmetric, int unsigned_symmetric, double* d_out_encoding, void* d_workspace,
                   int64_t workspace_bytes, void* stream);
+
+/* aq_tfe_pdf_replay followed by aq_tfe_search in one call: everything TfEnhancedEncodingAnalyzer<float>::computeEncoding
+ * (src/TfEnhancedEncodingAnalyzer.cpp:78-113) does after the last updateStats, from the per-batch rows to the
+ * encoding.  d_stats_updated (may be NULL): the "any batch was ever offered" flag as an int32 on the device
+ * (non-zero = yes), used instead of `stats_updated` when given -- for ranks of a data-parallel calibration, which
+ * learn it from the exchanged buffer without a host read.  Workspace as for aq_tfe_search. */
+int aq_tfe_compute_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_hists, const int64_t* d_counts,
+                            int64_t num_batches, double* d_pdf, int32_t* d_iterations, int stats_updated,
+                            const int32_t* d_stats_updated, int bw, int symmetric, int strict_symmetric,
+                            int unsigned_symmetric, double* d_out_encoding, void* d_workspace, int64_t workspace_bytes,
+                            void* stream);
 
 #ifdef __cplusplus
 }

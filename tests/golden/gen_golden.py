@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this directory from the REFERENCE ITSELF (run where a reference checkout and
 oracle/_ref exist; the fixtures are committed so that the tests need neither).
 
-    python tests/golden/gen_golden.py [/path/to/aimet]
+    python tests/golden/gen_golden.py /path/to/aimet        (or AIMET_REFERENCE_ROOT=/path/to/aimet)
 
 * v2_backend.npz   - aimet_torch v2 ``torch_builtins`` (loaded by file path, CPU) on seeded inputs:
                      quantize / quantize_dequantize / dequantize outputs, clamp masks (from dx with unit grads),
@@ -12,6 +12,8 @@ oracle/_ref exist; the fixtures are committed so that the tests need neither).
                      scale / offset, outputs after calibration.
 * v1_range_learning.npz - aimet_torch v1 learned-grid functions ``calculate_forward_pass`` / ``calculate_gradients``
                      (v1/quantsim_straight_through_grad.py loaded by path, CPU): outputs, dx, min / max gradients.
+* v1_ste.npz       - aimet_torch v1 straight-through gradient ``compute_dloss_by_dx`` (same file, CPU): per tensor
+                     and per channel on axis 0 / 1, with inputs exactly on the encoding bounds.
 * libpymo.npz      - the reference DlQuantization CPU code (oracle/_ref): per-tensor QDQ / codes, TF and
                      TF-Enhanced encodings, per-batch histograms, on seeded inputs.
 """
@@ -303,6 +305,54 @@ def gen_range_learning(ref_root: str):
     np.savez_compressed(os.path.join(HERE, "v1_range_learning.npz"), **out)
 
 
+def _load_v1_grad(ref_root: str):
+    at = os.path.join(ref_root, "TrainingExtensions", "torch", "src", "python", "aimet_torch")
+    for name in ("aimet_torch", "aimet_torch.v1"):
+        if name not in sys.modules:
+            m = types.ModuleType(name)
+            m.__path__ = []
+            sys.modules[name] = m
+
+    def load(modname, relpath):
+        spec = importlib.util.spec_from_file_location(modname, os.path.join(at, relpath))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[modname] = mod
+        spec.loader.exec_module(mod)
+        return mod
+
+    load("aimet_torch.v1.tensor_factory_utils", "v1/tensor_factory_utils.py")
+    return load("aimet_torch.v1.quantsim_straight_through_grad", "v1/quantsim_straight_through_grad.py")
+
+
+def gen_ste_v1(ref_root: str):
+    """compute_dloss_by_dx (aimet_torch/v1/quantsim_straight_through_grad.py:91-118) on seeded inputs."""
+    gf = _load_v1_grad(ref_root)
+    g = torch.Generator().manual_seed(321)
+    out = {}
+
+    def case(name, x, emin, emax, axis):
+        grad = torch.randn(x.shape, generator=g)
+        dx = gf.compute_dloss_by_dx(x, grad, emin, emax, axis)
+        out[f"{name}/x"], out[f"{name}/grad"] = x.numpy(), grad.numpy()
+        out[f"{name}/min"], out[f"{name}/max"] = emin.numpy(), emax.numpy()
+        out[f"{name}/axis"], out[f"{name}/dx"] = np.array(axis), dx.numpy()
+
+    x = torch.randn(4, 6, 5, 3, generator=g) * 2
+    flat = x.view(-1)
+    flat[:6] = torch.tensor([-1.5, 2.25, float("nan"), float("inf"), -float("inf"), 0.0])   # bounds, specials
+    case("per_tensor", x, torch.tensor([-1.5]), torch.tensor([2.25]), 0)
+    case("per_tensor_scalar", x, torch.tensor(-0.75), torch.tensor(0.5), 0)
+    mins, maxs = -torch.linspace(0.2, 2.0, 4), torch.linspace(0.3, 2.5, 4)
+    x0 = x.clone()
+    x0[1, 0, 0, 0], x0[2, 0, 0, 0] = mins[1], maxs[2]
+    case("per_channel_axis0", x0, mins, maxs, 0)
+    mins, maxs = -torch.linspace(0.1, 3.0, 6), torch.linspace(0.5, 1.0, 6)
+    case("per_channel_axis1", x, mins, maxs, 1)
+    w = torch.randn(16, 9, generator=g) * 0.3
+    case("linear_weight_axis0", w, -w.abs().amax(dim=1) * 0.5, w.abs().amax(dim=1) * 0.5, 0)
+    np.savez_compressed(os.path.join(HERE, "v1_ste.npz"), **out)
+
+
 def gen_libpymo():
     from _data import SPECIALS, conv_weight, normal, relu_activations
     from oracle import Reference, RefAnalyzer
@@ -340,10 +390,14 @@ def gen_libpymo():
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    gen_v2(ref)
-    gen_quantizer(ref)
-    gen_range_learning(ref)
-    gen_libpymo()
-    for f in ("v2_backend.npz", "v2_minmax.npz", "v2_quantizer.npz", "v1_range_learning.npz", "libpymo.npz"):
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AIMET_REFERENCE_ROOT")
+    if not ref:
+        raise SystemExit("usage: gen_golden.py /path/to/aimet   (a checkout of the reference; or set AIMET_REFERENCE_ROOT)")
+    only = sys.argv[2:]   # optionally: names of the generators to run
+    gens = {"v2": lambda: gen_v2(ref), "quantizer": lambda: gen_quantizer(ref),
+            "range_learning": lambda: gen_range_learning(ref), "ste_v1": lambda: gen_ste_v1(ref), "libpymo": gen_libpymo}
+    for name, fn in gens.items():
+        if not only or name in only:
+            fn()
+    for f in ("v2_backend.npz", "v2_minmax.npz", "v2_quantizer.npz", "v1_range_learning.npz", "v1_ste.npz", "libpymo.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")

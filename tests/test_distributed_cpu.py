@@ -1,8 +1,9 @@
 """Multi-rank calibration protocol on CPU ranks (gloo, world_size 2 and 3).
 
-The exchange logic of aimet_b200.calibration (grid agreement, per-batch rows, all-reduce, ordered replay,
-broadcast) runs unchanged; only the per-GPU arithmetic is replaced by a stand-in engine built on the CPU oracle,
-because this machine has no GPU.  The result must equal the sequential single-process oracle run bit for bit.
+The exchange logic of aimet_b200.calibration (grid agreement decided per round from the gathered ranges, rows kept
+at global batch indices, one all-reduce of the dense row buffer, ordered replay on every rank) runs unchanged; only
+the per-GPU arithmetic is replaced by a stand-in engine built on the CPU oracle, so that the protocol is covered
+without a GPU.  The result must equal the sequential single-process oracle run bit for bit on every rank.
 """
 import ctypes as C
 import os
@@ -18,103 +19,92 @@ from _data import normal, relu_activations
 
 
 class OracleEngine:
-    """Stand-in for CudaTfeEngine (same interface) on CPU tensors, for protocol tests only."""
+    """Stand-in for CudaTfeEngine (same interface, same buffer layout) on CPU tensors, for protocol tests only."""
 
     def __init__(self):
         from oracle import Oracle
         self.o = Oracle()
         self.x_left = None
-        self.h, self.c = [], []
+        self.gate = 1
+        self._alloc(4)
 
-    def minmax(self, x):
-        return torch.from_numpy(self.o.min_max(x.numpy()))
+    def _alloc(self, cap, keep=False):
+        buf = torch.zeros(cap * 514 + 2, dtype=torch.int32)
+        h = buf[:cap * 512].view(cap, 512)
+        c = buf[cap * 512:cap * 514].view(torch.int64)
+        if keep:
+            old = min(self.h.shape[0], cap)
+            h[:old], c[:old] = self.h[:old], self.c[:old]
+            buf[-2:] = self.flags
+        self.buffer, self.h, self.c, self.flags = buf, h, c, buf[-2:]
 
-    def init_grid(self, minmax):
-        mn, mx = (np.float32(v) for v in minmax.tolist())
-        self.x_left = self.o.pdf_init(mn, mx)
+    def reserve(self, rows):
+        if rows > self.h.shape[0]:
+            self._alloc(max(rows, 2 * self.h.shape[0]), keep=True)
 
-    def is_initialized(self):
+    def mark_updated(self):
+        self.flags[0] = 1
+
+    def _init(self, mn, mx):
+        if self.x_left is None and not (mn == 0.0 and mx == 0.0):
+            self.x_left = self.o.pdf_init(np.float32(mn), np.float32(mx))
+
+    def offer_grid(self, x):
+        if self.x_left is None:
+            self._init(*self.o.min_max(x.numpy()).tolist())
+
+    def grid_known(self, wait=False):
         return self.x_left is not None
 
-    def add_batch(self, x, row):
-        assert row == len(self.h)
-        if self.x_left is None:
-            return self.add_empty_row(row)
+    def batch_range(self, x):
+        if x is None:
+            return torch.zeros(3)
+        if self.x_left is not None:
+            return torch.tensor([0.0, 0.0, 1.0])
+        mn, mx = self.o.min_max(x.numpy()).tolist()
+        return torch.tensor([mn, mx, 1.0], dtype=torch.float32)
+
+    def select_grid(self, ranges, num_ranks, rank):
+        if self.x_left is not None:
+            self.gate = 1
+            return
+        t = ranges.view(num_ranks, 3).tolist()
+        chosen = next((r for r, (mn, mx, present) in enumerate(t) if present and not (mn == 0.0 and mx == 0.0)), -1)
+        self.gate = 1 if (chosen >= 0 and rank >= chosen) else 0
+        if chosen >= 0:
+            self._init(t[chosen][0], t[chosen][1])
+
+    def add_batch(self, x, row, gated=False):
+        self.reserve(row + 1)
+        if self.x_left is None or (gated and not self.gate):
+            return
         bs, po = self.o.pdf_geometry(self.x_left)
-        self.h.append(self.o.hist512(x.numpy(), bs, po).astype(np.int64))
-        self.c.append(x.numel())
+        self.h[row] += torch.from_numpy(self.o.hist512(x.numpy(), bs, po).astype(np.int32))
+        self.c[row] = x.numel()
 
-    def add_empty_row(self, row):
-        assert row == len(self.h)
-        self.h.append(np.zeros(512, np.int64))
-        self.c.append(0)
+    def add_batches(self, xs, row0, row_stride):
+        for i, x in enumerate(xs):
+            self.add_batch(x, row0 + i * row_stride)
 
-    def num_rows(self):
-        return len(self.h)
+    def exchange_buffer(self, n_total):
+        if n_total != self.h.shape[0]:
+            self._alloc(n_total, keep=True)
+        return self.buffer
 
-    def rows(self):
-        return torch.from_numpy(np.stack(self.h)).to(torch.int32), torch.tensor(self.c, dtype=torch.int64)
-
-    def load_rows(self, hists, counts):
-        self.h = [r.numpy().astype(np.int64) for r in hists]
-        self.c = counts.tolist()
-
-    def encoding(self, stats_updated, bw, symmetric, strict, unsigned_sym):
+    def encoding(self, stats_updated, bw, symmetric, strict, unsigned_sym, num_rows=None):
         from oracle import OracleTfeAnalyzer
         a = OracleTfeAnalyzer(self.o)
-        a.stats_updated = bool(stats_updated)
+        a.stats_updated = bool(self.flags[0].item()) if stats_updated is None else bool(stats_updated)
+        n = self.h.shape[0] if num_rows is None else num_rows
         if self.x_left is not None:
             a.x_left[:] = self.x_left
             a.initialized = C.c_int(1)
-            for h, c in zip(self.h, self.c):
+            for h, c in zip(self.h[:n].numpy(), self.c[:n].tolist()):
                 if c:
                     hh = np.ascontiguousarray(h, np.uint32)
                     self.o.lib.orc_pdf_accumulate(hh.ctypes.data_as(C.POINTER(C.c_uint32)), int(c),
                                                   a.pdf.ctypes.data_as(C.POINTER(C.c_double)), C.byref(a.iterations))
         return torch.from_numpy(a.compute(bw, symmetric, strict, unsigned_sym))
-
-
-class GlobalRowsOracleEngine(OracleEngine):
-    """Same stand-in, but keeping its rows at their global indices in one dense table, like the CUDA engine does:
-    exercises the exchange that all-reduces the table in place."""
-    global_rows = True
-
-    def __init__(self):
-        super().__init__()
-        self.table = torch.zeros((0, 512), dtype=torch.int32)
-        self.counts = torch.zeros(0, dtype=torch.int64)
-
-    def _reserve(self, n):
-        if n > self.table.shape[0]:
-            t, c = torch.zeros((n, 512), dtype=torch.int32), torch.zeros(n, dtype=torch.int64)
-            t[:self.table.shape[0]], c[:self.counts.shape[0]] = self.table, self.counts
-            self.table, self.counts = t, c
-
-    def add_batch(self, x, row):
-        self._reserve(row + 1)
-        if self.x_left is None:
-            return
-        bs, po = self.o.pdf_geometry(self.x_left)
-        self.table[row] = torch.from_numpy(self.o.hist512(x.numpy(), bs, po).astype(np.int32))
-        self.counts[row] = x.numel()
-
-    def add_empty_row(self, row):
-        self._reserve(row + 1)
-
-    def num_rows(self):
-        return self.table.shape[0]
-
-    def exchange_views(self, n_total):
-        self._reserve(n_total)
-        return self.table[:n_total], self.counts[:n_total]
-
-    def encoding(self, stats_updated, bw, symmetric, strict, unsigned_sym):
-        self.h = [r.numpy().astype(np.int64) for r in self.table]
-        self.c = self.counts.tolist()
-        return super().encoding(stats_updated, bw, symmetric, strict, unsigned_sym)
-
-
-ENGINES = {"packed": OracleEngine, "in_place": GlobalRowsOracleEngine}
 
 
 def make_batches(scenario):
@@ -135,17 +125,25 @@ def sequential(batches, bw, flags):
     return a.compute(bw, *flags)
 
 
-def _worker(rank, world, port, scenario, out, engine="packed"):
+def _worker(rank, world, port, scenario, out, feed="single"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from aimet_b200.calibration import TfEnhancedCalibrator
         batches = make_batches(scenario)
-        cal = TfEnhancedCalibrator("cpu", engine=ENGINES[engine]())
+        cal = TfEnhancedCalibrator("cpu", engine=OracleEngine(), num_batches=len(batches) if feed == "many" else None)
         rounds = (len(batches) + world - 1) // world
-        for k in range(rounds):
-            g = k * world + rank
-            cal.update(torch.from_numpy(batches[g]) if g < len(batches) else None)
+        mine = [torch.from_numpy(batches[k * world + rank]) if k * world + rank < len(batches) else None
+                for k in range(rounds)]
+        if feed == "many" and mine[-1] is not None:
+            cal.update_many(mine)
+        elif feed == "many":
+            # update_many takes whole rounds only; a rank without a batch in the last round feeds that one singly
+            cal.update_many(mine[:-1])
+            cal.update(None)
+        else:
+            for x in mine:
+                cal.update(x)
         res = []
         for bw, flags in ((8, (False, False, False)), (8, (True, False, False)), (4, (True, True, False))):
             e = cal.compute_encoding(bw, *flags)
@@ -161,13 +159,13 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("engine", ["packed", "in_place"])
+@pytest.mark.parametrize("feed", ["single", "many"])
 @pytest.mark.parametrize("world", [2, 3])
 @pytest.mark.parametrize("scenario", ["relu", "zeros_first", "all_zero"])
-def test_sharded_tf_enhanced_equals_sequential(world, scenario, engine):
+def test_sharded_tf_enhanced_equals_sequential(world, scenario, feed):
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), scenario, out, engine), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), scenario, out, feed), nprocs=world, join=True)
     batches = make_batches(scenario)
     want = [sequential(batches, bw, flags) for bw, flags in
             ((8, (False, False, False)), (8, (True, False, False)), (4, (True, True, False)))]
@@ -180,9 +178,13 @@ def test_sharded_tf_enhanced_equals_sequential(world, scenario, engine):
 def test_single_process_protocol_matches_sequential():
     from aimet_b200.calibration import TfEnhancedCalibrator
     batches = make_batches("zeros_first")
-    cal = TfEnhancedCalibrator("cpu", engine=OracleEngine())
-    for b in batches:
-        cal.update(torch.from_numpy(b))
-    e = cal.compute_encoding(8)
     w = sequential(batches, 8, (False, False, False))
-    assert [e.min, e.max, e.delta, e.offset, e.bw] == list(w)
+    for feed in ("single", "many"):
+        cal = TfEnhancedCalibrator("cpu", engine=OracleEngine())
+        if feed == "many":
+            cal.update_many([torch.from_numpy(b) for b in batches])
+        else:
+            for b in batches:
+                cal.update(torch.from_numpy(b))
+        e = cal.compute_encoding(8)
+        assert [e.min, e.max, e.delta, e.offset, e.bw] == list(w), feed

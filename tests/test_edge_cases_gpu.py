@@ -31,6 +31,27 @@ def test_empty_inputs(cuda):
     assert lib.aq_qdq_per_tensor(None, None, 0, -1.0, 1.0, 8, 0, None) == 0
 
 
+@pytest.mark.parametrize("shape,num_ch,inner", [((0, 3, 64), 3, 64), ((0, 2, 4), 2, 4), ((0, 512, 2304), 512, 2304)])
+def test_empty_per_channel_statistics(cuda, shape, num_ch, inner):
+    """No rows at all: every channel reports +inf / -inf, running statistics stay as they were; aq_minmax,
+    aq_minmax_static and the size query all accept the geometry."""
+    from aimet_b200 import ops
+    from aimet_b200._lib import lib
+    x = torch.empty(shape, device=cuda)
+    assert lib.aq_minmax_workspace_bytes(0, num_ch, inner) >= 0
+    mm = ops.minmax(x, num_ch, inner)
+    assert mm.shape == (2, num_ch)
+    assert (mm[0] == float("inf")).all() and (mm[1] == float("-inf")).all()
+    acc = torch.tensor([[-1.0] * num_ch, [2.0] * num_ch], device=cuda)
+    ops.minmax(x, num_ch, inner, out=acc, accumulate=True)
+    assert (acc[0] == -1.0).all() and (acc[1] == 2.0).all()
+    out = torch.zeros((2, num_ch), device=cuda)
+    rc = lib.aq_minmax_static(x.data_ptr(), 0, 0, num_ch, inner, out[0].data_ptr(), out[1].data_ptr(), 0,
+                              torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert (out[0] == float("inf")).all() and (out[1] == float("-inf")).all()
+
+
 @pytest.mark.parametrize("shift", [1, 2, 3])
 @pytest.mark.parametrize("n", [1, 7, 4095, 4096, 4097, 8191, 8193, 100003])
 def test_unaligned_pointers_and_ragged_sizes(cuda, oracle, shift, n):

@@ -131,6 +131,22 @@ def test_ste_backward_v1_per_channel(oracle, cuda):
     assert_bits_equal(got.cpu().numpy(), want)
 
 
+def test_ste_backward_v1_matches_reference_fixture(cuda):
+    """The kernel against compute_dloss_by_dx of the reference itself (tests/golden/v1_ste.npz): bounds inclusive,
+    NaN / Inf inputs, per tensor and per channel on axis 0 and 1."""
+    import os
+    from aimet_b200 import ops
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "v1_ste.npz"))
+    names = sorted({k.split("/")[0] for k in g.files})
+    for name in names:
+        x, grad, want = g[f"{name}/x"], g[f"{name}/grad"], g[f"{name}/dx"]
+        mins, maxs = g[f"{name}/min"].reshape(-1), g[f"{name}/max"].reshape(-1)
+        axis = int(g[f"{name}/axis"])
+        num_ch, inner = (1, x.size) if mins.size == 1 else (x.shape[axis], int(np.prod(x.shape[axis + 1:])))
+        got = ops.ste_backward_v1(dev(x, cuda), dev(grad, cuda), dev(mins, cuda), dev(maxs, cuda), num_ch, inner)
+        assert_bits_equal(got.cpu().numpy(), want, name)
+
+
 @pytest.mark.parametrize("n", [1, 3, 128, 4097, 1 << 20, (1 << 22) + 5])
 def test_minmax_per_tensor(oracle, cuda, n):
     from aimet_b200 import ops

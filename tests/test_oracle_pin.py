@@ -141,6 +141,36 @@ def test_golden_v2_backend(name):
         np.testing.assert_allclose(do_sum, g[f"{name}/doffset"], rtol=2e-4, atol=1e-4)
 
 
+def _ste_cases():
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "v1_ste.npz"))
+    names = sorted({k.split("/")[0] for k in g.files})
+    return g, names
+
+
+def ste_geometry(shape, axis, num_enc):
+    """(num_ch, inner) of the flat buffer for encodings broadcast on `axis` (one encoding: per tensor)."""
+    if num_enc == 1:
+        return 1, int(np.prod(shape))
+    return shape[axis], int(np.prod(shape[axis + 1:]))
+
+
+def test_golden_v1_ste_backward(oracle):
+    """orc_ste_bwd against compute_dloss_by_dx of the reference (fixture generated by the reference's own file):
+    per tensor, and per channel on axis 0 / 1 through the (num_ch, inner) geometry the kernels use."""
+    g, names = _ste_cases()
+    assert len(names) >= 5
+    for name in names:
+        x, grad, want = g[f"{name}/x"], g[f"{name}/grad"], g[f"{name}/dx"]
+        mins, maxs = g[f"{name}/min"].reshape(-1), g[f"{name}/max"].reshape(-1)
+        num_ch, inner = ste_geometry(x.shape, int(g[f"{name}/axis"]), mins.size)
+        rows = x.reshape(-1, inner)
+        grows = grad.reshape(-1, inner)
+        got = np.stack([oracle.ste_bwd(rows[r], grows[r], mins[r % num_ch], maxs[r % num_ch])
+                        for r in range(rows.shape[0])]).reshape(x.shape)
+        from _data import assert_bits_equal
+        assert_bits_equal(got, want, name)
+
+
 def test_golden_v2_minmax():
     from oracle import v2_oracle as v2
     g = np.load(os.path.join(GOLDEN, "v2_minmax.npz"))

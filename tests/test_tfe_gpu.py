@@ -106,3 +106,143 @@ def test_tfe_misaligned_input(oracle, cuda):
     st.init_grid_from(ops.minmax(xd).reshape(-1))
     st.add_batch(xd)
     np.testing.assert_array_equal(st.hists[0].cpu().numpy().view(np.uint32), want)
+
+
+# ---- fused range + grid setup, gated / many-batch histogram, cross-rank grid selection ------------------------------
+def _rows(st):
+    n = st.num_batches
+    return st.hists[:n].cpu().numpy().view(np.uint32), st.counts[:n].cpu().numpy()
+
+
+@pytest.mark.parametrize("kinds,n", SCENARIOS)
+def test_offer_grid_equals_minmax_plus_init(oracle, cuda, kinds, n):
+    """One launch (min/max pass + grid setup, a no-op once a grid exists) against the two-step form."""
+    from aimet_b200 import ops
+    batches = [gen(k, 100 + i, n) for i, k in enumerate(kinds)]
+    ref = run_gpu(batches, cuda)
+    st = ops.TfeDeviceState(cuda, capacity=len(batches))
+    for b in batches:
+        xd = dev(b, cuda)
+        st.offer_grid(xd)      # always offered: the device ignores it once the grid exists
+        st.add_batch(xd)
+    st.replay()
+    h0, c0 = _rows(ref)
+    h1, c1 = _rows(st)
+    np.testing.assert_array_equal(c1, c0)
+    np.testing.assert_array_equal(h1, h0)
+    np.testing.assert_array_equal(st.state.cpu().numpy(), ref.state.cpu().numpy(), err_msg="state record")
+    assert_bits_equal(st.pdf.cpu().numpy(), ref.pdf.cpu().numpy(), "pdf")
+
+
+def test_offer_grid_reports_range(oracle, cuda):
+    from aimet_b200 import ops
+    for n, off in ((100003, 0), (4097, 1), (3, 0), (70001, 3)):
+        x = normal(n + off, 7 + n, 3.0, 0.5)
+        xd = dev(x, cuda)[off:]
+        st = ops.TfeDeviceState(cuda)
+        r = st.batch_range(xd).cpu().numpy()
+        want = oracle.min_max(x[off:])
+        assert_bits_equal(r[:2], want, f"range n={n} off={off}")
+        assert r[2] == 1.0 and not st.is_initialized()
+        st.offer_grid(xd)
+        assert st.is_initialized()
+        assert_bits_equal(st.x_left().cpu().numpy(), oracle.pdf_init(*want), "grid")
+        # a second offer is skipped and reports (0, 0, 1)
+        r = st.batch_range(dev(normal(1000, 1, 50.0), cuda)).cpu().numpy()
+        np.testing.assert_array_equal(r, [0.0, 0.0, 1.0])
+    assert st.batch_range(None).cpu().tolist() == [0.0, 0.0, 0.0]
+
+
+@pytest.mark.parametrize("m,stride", [(1, 1), (3, 1), (16, 1), (19, 1), (5, 4)])
+def test_histogram_many_equals_single(oracle, cuda, m, stride):
+    """m resident batches in one launch (ragged sizes, one of them not 16-byte aligned) against one launch each."""
+    from aimet_b200 import ops
+    sizes = [50000 + 4099 * (i % 5) + i for i in range(m)]
+    xs = [dev(relu_activations(s + 1, 300 + i), cuda) for i, s in enumerate(sizes)]
+    xs = [x[1:] if i % 4 == 2 else x[:-1] for i, x in enumerate(xs)]
+    rows = (m - 1) * stride + 1
+    one, many = ops.TfeDeviceState(cuda, rows), ops.TfeDeviceState(cuda, rows)
+    for st in (one, many):
+        st.offer_grid(xs[0])
+    for i, x in enumerate(xs):
+        one.add_batch(x, i * stride)
+    many.add_batches(xs, 0, stride)
+    h0, c0 = _rows(one)
+    h1, c1 = _rows(many)
+    np.testing.assert_array_equal(c1, c0)
+    np.testing.assert_array_equal(h1, h0)
+    assert (c0[::stride] == [x.numel() for x in xs]).all() and c0.sum() == sum(x.numel() for x in xs)
+    bs, po = oracle.pdf_geometry(one.x_left().cpu().numpy())
+    for i, x in enumerate(xs):
+        np.testing.assert_array_equal(h0[i * stride], oracle.hist512(x.cpu().numpy(), bs, po))
+
+
+def test_histogram_many_before_grid_counts_nothing(cuda):
+    from aimet_b200 import ops
+    st = ops.TfeDeviceState(cuda, 4)
+    st.add_batches([dev(normal(5000, i), cuda) for i in range(3)], 0, 1)
+    h, c = _rows(st)
+    assert not h.any() and not c.any()
+
+
+@pytest.mark.parametrize("table,rank,want_gate,want_range", [
+    ([[0, 0, 1], [-1, 2, 1], [5, 6, 1]], 0, 0, (-1, 2)),     # all-zero batch ahead of the defining one: dropped
+    ([[0, 0, 1], [-1, 2, 1], [5, 6, 1]], 1, 1, (-1, 2)),
+    ([[0, 0, 1], [-1, 2, 1], [5, 6, 1]], 2, 1, (-1, 2)),
+    ([[3, 4, 0], [0, 0, 1], [0.5, 0.5, 1]], 1, 0, (0.5, 0.5)),   # absent ranks are skipped
+    ([[0, 0, 1], [0, 0, 1]], 1, 0, None),                        # nobody can define the grid this round
+])
+def test_select_grid(oracle, cuda, table, rank, want_gate, want_range):
+    from aimet_b200 import ops
+    st = ops.TfeDeviceState(cuda)
+    t = torch.tensor(table, dtype=torch.float32, device=cuda).reshape(-1)
+    st.select_grid(t, len(table), rank)
+    assert int(st.gate.item()) == want_gate
+    x = dev(np.zeros(1000, np.float32), cuda)
+    st.add_batch(x, 0, gated=True)
+    assert int(st.counts[0].item()) == (1000 if want_gate else 0)
+    if want_range is None:
+        assert not st.is_initialized()
+        return
+    assert_bits_equal(st.x_left().cpu().numpy(), oracle.pdf_init(np.float32(want_range[0]), np.float32(want_range[1])), "grid")
+    # once a grid exists the selection is a no-op that opens the gate
+    st.select_grid(torch.tensor([[9.0, 10.0, 1.0]], device=cuda).reshape(-1), 1, 0)
+    assert int(st.gate.item()) == 1
+    assert_bits_equal(st.x_left().cpu().numpy(), oracle.pdf_init(np.float32(want_range[0]), np.float32(want_range[1])), "grid kept")
+
+
+def test_compute_encoding_equals_replay_plus_search(oracle, cuda):
+    from aimet_b200 import ops
+    st = run_gpu([gen("relu", 100 + i, 60000) for i in range(5)], cuda)
+    for bw, sym in ((8, 0), (4, 1)):
+        want = st.search(True, bw, sym, 0, 0).cpu().numpy().copy()
+        got = st.compute_encoding(True, bw, sym, 0, 0).cpu().numpy()
+        assert_bits_equal(got, want, "encoding")
+    # the "any batch offered" flag taken from the device instead of the host
+    empty = ops.TfeDeviceState(cuda)
+    np.testing.assert_array_equal(empty.compute_encoding(None, 8, 0, 0, 0).cpu().numpy(), np.zeros(5))
+    empty.flags[0:1].fill_(2)
+    assert_bits_equal(empty.compute_encoding(None, 8, 0, 0, 0).cpu().numpy(),
+                      empty.compute_encoding(True, 8, 0, 0, 0).cpu().numpy().copy(), "all-zero-data encoding")
+
+
+def test_calibrator_update_many_equals_updates(oracle, cuda):
+    from aimet_b200.calibration import TfEnhancedCalibrator
+    batches = [np.zeros(3000, np.float32)] * 2 + [relu_activations(30000 + 7 * i, 40 + i) for i in range(21)]
+    xs = [dev(b, cuda) for b in batches]
+    a, b = TfEnhancedCalibrator(cuda), TfEnhancedCalibrator(cuda, num_batches=len(xs))
+    for x in xs:
+        a.update(x)
+    b.update_many(xs[:5])
+    b.update_many(xs[5:])
+    ea, eb = a.compute_encoding(8), b.compute_encoding(8)
+    assert [ea.min, ea.max, ea.delta, ea.offset] == [eb.min, eb.max, eb.delta, eb.offset]
+    ha, ca = _rows(a.engine.state)
+    hb, cb = _rows(b.engine.state)
+    np.testing.assert_array_equal(ca, cb)
+    np.testing.assert_array_equal(ha, hb)
+    from oracle import OracleTfeAnalyzer
+    oa = OracleTfeAnalyzer(oracle)
+    for x in batches:
+        oa.update(x)
+    assert_bits_equal(np.array([ea.min, ea.max, ea.delta, ea.offset, ea.bw]), oa.compute(8, 0, 0, 0), "encoding")

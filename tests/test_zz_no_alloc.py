@@ -65,6 +65,60 @@ def test_static_scratch_minmax_matches_workspace_version_twice(cuda):
     assert _same_bits(want, got)
 
 
+def test_static_scratch_direct_rows_fit_at_any_size(cuda):
+    """Block statistics whose rows map one to one to the outputs never touch the array, however many rows there are:
+    300,000 blocks of 64 (more than the 131,071 partial pairs the array could hold) are accepted."""
+    from aimet_b200._lib import lib
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device=cuda)
+    g.manual_seed(3)
+    x = (torch.randn(300_000, 64, device=cuda, generator=g) * 0.02).to(torch.bfloat16)
+    assert lib.aq_minmax_workspace_bytes(x.numel(), 300_000, 64) > (1 << 20)
+    want, got = _both(x, 300_000, 64, False, lib, stream)
+    torch.cuda.synchronize()
+    assert _same_bits(want, got)
+    xf = x.float()
+    assert torch.equal(got[0], xf.amin(dim=1)) and torch.equal(got[1], xf.amax(dim=1))
+
+
+def test_static_scratch_allocates_nothing_and_follows_stream_and_device(cuda):
+    """The point of the entry: device memory in use does not move across calls.  Also run on a side stream, and on a
+    second GPU where there is one (the scratch address is looked up per device)."""
+    from aimet_b200._lib import lib
+    g = torch.Generator(device=cuda)
+    g.manual_seed(5)
+    x = torch.randn(6, 40, 4800, device=cuda, generator=g)
+    out = torch.empty((2, 40), device=cuda)
+    ref_mn = x.permute(1, 0, 2).reshape(40, -1).amin(dim=1)
+    ref_mx = x.permute(1, 0, 2).reshape(40, -1).amax(dim=1)
+    side = torch.cuda.Stream(cuda)
+    side.wait_stream(torch.cuda.current_stream())
+    call = lambda st: lib.aq_minmax_static(x.data_ptr(), 0, x.numel(), 40, 4800, out[0].data_ptr(), out[1].data_ptr(),
+                                           0, st)
+    assert call(side.cuda_stream) == 0   # the first call may look the array up; it still allocates nothing
+    side.synchronize()
+    allocs = lambda: torch.cuda.memory_stats(cuda).get("allocation.all.allocated", 0)
+    for _ in range(3):
+        out.fill_(0)
+        side.wait_stream(torch.cuda.current_stream())
+        torch.cuda.synchronize(cuda)
+        free0, allocs0 = torch.cuda.mem_get_info(cuda)[0], allocs()
+        assert call(side.cuda_stream) == 0
+        side.synchronize()
+        assert torch.cuda.mem_get_info(cuda)[0] == free0 and allocs() == allocs0
+        assert torch.equal(out[0], ref_mn) and torch.equal(out[1], ref_mx)   # against plain tensor reductions
+    if torch.cuda.device_count() > 1:
+        d1 = torch.device("cuda:1")
+        with torch.cuda.device(d1):
+            x1 = x.to(d1)
+            o1 = torch.empty((2, 40), device=d1)
+            rc = lib.aq_minmax_static(x1.data_ptr(), 0, x1.numel(), 40, 4800, o1[0].data_ptr(), o1[1].data_ptr(), 0,
+                                      torch.cuda.current_stream(d1).cuda_stream)
+            assert rc == 0
+            torch.cuda.synchronize(d1)
+            assert torch.equal(o1[0].cpu(), ref_mn.cpu()) and torch.equal(o1[1].cpu(), ref_mx.cpu())
+
+
 def test_static_scratch_rejects_oversized_geometry(cuda):
     from aimet_b200._lib import lib
     # 400,000 rows of 4 elements need 2 x 400,000 partial floats: more than the 1 MiB array holds... unless the
