@@ -277,11 +277,12 @@ int aq_v2_quantize(const void* d_x, void* d_y, uint8_t* d_mask, int dtype, int64
         (out_kind != AQ_V2_OUT_QDQ && out_kind != AQ_V2_OUT_CODES) || dtype < AQ_F32 || dtype > AQ_BF16)
         return AQ_ERR_INVALID_ARG;
     // the grid bounds must be exact in the internal dtype (the caller checks representability like the reference)
-    if ((double) (float) qmin != qmin || (double) (float) qmax != qmax)
+    if (narrow_internal != AQ_V2_INTERNAL_F64 && ((double) (float) qmin != qmin || (double) (float) qmax != qmax))
         return AQ_ERR_UNSUPPORTED;
     V2Args a;
     a.x = d_x, a.y = d_y, a.mask = d_mask, a.n = n, a.scale = d_scale, a.offset = d_offset;
     a.qmin = (float) qmin, a.qmax = (float) qmax, a.out_kind = out_kind, a.dequant_only = 0;
+    a.qmin_wide = qmin, a.qmax_wide = qmax;
     a.geom.num_ch = num_ch, a.geom.inner = inner;
     return v2_launch(a, dtype, narrow_internal, (cudaStream_t) stream);
 }
@@ -294,7 +295,7 @@ int aq_v2_dequantize(const void* d_x, void* d_y, int dtype, int64_t n, int64_t n
         return AQ_ERR_INVALID_ARG;
     V2Args a;
     a.x = d_x, a.y = d_y, a.mask = nullptr, a.n = n, a.scale = d_scale, a.offset = d_offset;
-    a.qmin = 0, a.qmax = 0, a.out_kind = AQ_V2_OUT_QDQ, a.dequant_only = 1;
+    a.qmin = 0, a.qmax = 0, a.qmin_wide = 0, a.qmax_wide = 0, a.out_kind = AQ_V2_OUT_QDQ, a.dequant_only = 1;
     a.geom.num_ch = num_ch, a.geom.inner = inner;
     return v2_launch(a, dtype, narrow_internal, (cudaStream_t) stream);
 }

@@ -30,6 +30,7 @@ struct V2Args
     const float* scale;
     const float* offset;
     float qmin, qmax;
+    double qmin_wide, qmax_wide;   // the same bounds for the float64 form (grids of 2^24 steps or more)
     int out_kind;
     int dequant_only;
     ChanGeom geom;

@@ -763,10 +763,59 @@ static int launch_v2_t(V2Args a, bool narrow, cudaStream_t st)
     return launch_v2_vec<T, false>(a, vec, narrow, st);
 }
 
+// Grids of 2^24 steps or more (a 32-bit quantizer): the reference evaluates the same expressions in float64
+// (torch_builtins.py:162-171).  A plain element-per-thread kernel with IEEE double arithmetic; such grids are rare and
+// the kernel is division-bound, not memory-bound.
+template <typename T>
+__global__ void __launch_bounds__(256) v2_f64_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                     uint8_t* __restrict__ mask, int64_t n, const float* __restrict__ scale,
+                                                     const float* __restrict__ offset, double qmin, double qmax,
+                                                     int codes, int64_t num_ch, int64_t inner)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t) blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t) gridDim.x * 256)
+    {
+        const int64_t ch = num_ch > 1 ? (i / inner) % num_ch : 0;
+        const double s = (double) scale[ch], o = (double) offset[ch];
+        const double r = __dsub_rn(rint(__ddiv_rn((double) to_f32<T>(x[i]), s)), o);
+        if (mask)
+            mask[i] = (r >= qmin && r <= qmax) ? 1 : 0;
+        const double q = fmin(fmax(r, qmin), qmax);   // NaN stays NaN in torch.clamp; fmin / fmax would drop it
+        const double c = (r != r) ? r : q;
+        const double out = codes ? c : __dmul_rn(__dadd_rn(c, o), s);
+        y[i] = from_f32<T>(__double2float_rn(out));
+    }
+}
+
+template <typename T>
+static int launch_v2_f64(const V2Args& a, cudaStream_t st)
+{
+    int64_t blocks = (a.n + 255) / 256;
+    if (blocks > (int64_t) kNumSMs * 8)
+        blocks = (int64_t) kNumSMs * 8;
+    launch_pdl(v2_f64_kernel<T>, (unsigned) blocks, 256, 0, st, (const T*) a.x, (T*) a.y, a.mask, a.n, a.scale, a.offset,
+               a.qmin_wide, a.qmax_wide, a.out_kind == AQ_V2_OUT_CODES ? 1 : 0, a.geom.num_ch, a.geom.inner);
+    note_launch();
+    return check_launch();
+}
+
 int v2_launch(V2Args a, int dtype, int narrow_internal, cudaStream_t st)
 {
     if (a.n == 0)
         return AQ_OK;
+    if (narrow_internal == AQ_V2_INTERNAL_F64)
+    {
+        if (a.dequant_only)
+            return AQ_ERR_UNSUPPORTED;
+        switch (dtype)
+        {
+        case AQ_F32: return launch_v2_f64<float>(a, st);
+        case AQ_BF16: return launch_v2_f64<__nv_bfloat16>(a, st);
+        case AQ_F16: return launch_v2_f64<__half>(a, st);
+        default: return AQ_ERR_INVALID_ARG;
+        }
+    }
     switch (dtype)
     {
     case AQ_F32: return launch_v2_t<float>(a, false, st);

@@ -229,7 +229,7 @@ class _QuantDequantFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, tensor, scale, offset, qmin, qmax, block_size, out_kind, narrow):
         g = resolve_geometry(tensor, scale.shape, block_size)
-        narrow_dt = tensor.dtype if narrow else None
+        narrow_dt = tensor.dtype if narrow == 1 else None
         sc = _flat_encoding(scale.detach(), g, narrow_dt)
         of = _flat_encoding(_offset_like_scale(offset.detach(), scale), g, narrow_dt)
         need_mask = tensor.requires_grad or scale.requires_grad or offset.requires_grad
@@ -290,6 +290,62 @@ def _reduce_to_encoding(full: torch.Tensor, enc_shape: Tuple[int, ...], block_si
     return v.reshape(enc_shape)
 
 
+class _QuantFn(torch.autograd.Function):
+    """Integer codes with the gradients of QuantizeFunc (torch_builtins.py:208-247): with masked = grad * mask,
+    dx = masked / scale, dscale = -(masked / scale) * (x / scale), doffset = -masked, the last two summed over the dims
+    the encoding is broadcast along (autograd's reduction of the reference's un-reduced returns).  Forward and the
+    mask product are kernels; the two divisions are tensor expressions on the device (codes are not on the
+    fake-quant training path)."""
+
+    @staticmethod
+    def forward(ctx, tensor, scale, offset, qmin, qmax, block_size, narrow):
+        g = resolve_geometry(tensor, scale.shape, block_size)
+        narrow_dt = tensor.dtype if narrow else None
+        sc = _flat_encoding(scale.detach(), g, narrow_dt)
+        of = _flat_encoding(_offset_like_scale(offset.detach(), scale), g, narrow_dt)
+        need_mask = tensor.requires_grad or scale.requires_grad or offset.requires_grad
+        x = g.x_work
+        y = torch.empty_like(x)
+        mask = torch.empty_like(x, dtype=torch.uint8) if need_mask else None
+        ops.v2_quantize(x, y, mask, sc, of, qmin, qmax, g.num_ch, g.inner, _lib.AQ_V2_OUT_CODES, narrow)
+        out = g.from_work(y)
+        g.x_work = None
+        ctx.g, ctx.block_size = g, block_size
+        ctx.enc_shape, ctx.off_shape = tuple(scale.shape), tuple(offset.shape)
+        ctx.save_for_backward(mask, tensor.detach() if scale.requires_grad else None,
+                              scale.detach() if (tensor.requires_grad or scale.requires_grad) else None)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        mask, tensor, scale = ctx.saved_tensors
+        g = ctx.g
+        if g.order is not None:
+            gw = grad.reshape(g.t_log).permute(g.order).contiguous()
+        elif grad.shape == mask.shape and grad.stride() == mask.stride():
+            gw = grad
+        else:
+            gw = torch.empty_like(mask, dtype=grad.dtype)
+            gw.copy_(grad)
+        mw = torch.empty_like(gw)
+        ops.v2_qdq_backward(gw, mask, mw)
+        masked = g.from_work(mw)
+        dx = ds = do = None
+        if scale is not None:
+            t_log, s_log = _expanded_shapes(tuple(masked.shape), tuple(scale.shape), ctx.block_size)
+            by_scale = (masked.reshape(t_log) / scale.reshape(s_log).to(masked.dtype)).reshape(masked.shape)
+            if ctx.needs_input_grad[0]:
+                dx = by_scale
+            if ctx.needs_input_grad[1]:
+                ratio = (tensor.reshape(t_log) / scale.reshape(s_log).to(tensor.dtype)).reshape(masked.shape)
+                ds = _reduce_to_encoding(-by_scale * ratio, tuple(scale.shape), ctx.block_size).to(scale.dtype)
+        if ctx.needs_input_grad[2]:
+            do = _reduce_to_encoding(-masked, ctx.enc_shape, ctx.block_size)
+            if ctx.off_shape != ctx.enc_shape:
+                do = do.sum_to_size(ctx.off_shape)
+        return dx, ds, do, None, None, None, None
+
+
 class _DequantFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, tensor, scale, offset, block_size, narrow):
@@ -336,12 +392,8 @@ def quantize(tensor: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor, qm
     _check_inputs(tensor, scale, offset)
     if not _is_grid_representable(tensor.dtype, qmin, qmax):
         raise RuntimeError(f"{tensor.dtype} is unable to represent quantized output of range [{qmin}, {qmax}].")
-    if tensor.requires_grad or scale.requires_grad or offset.requires_grad:
-        raise RuntimeError("aimet_b200 backend: gradients through quantize() (integer codes) are outside the "
-                           "accelerated path; use quantize_dequantize() for fake-quant training")
     narrow = tensor.dtype != torch.float32
-    return _QuantDequantFn.apply(tensor, scale, offset, int(qmin), int(qmax), _bs(block_size),
-                                 _lib.AQ_V2_OUT_CODES, narrow)
+    return _QuantFn.apply(tensor, scale, offset, int(qmin), int(qmax), _bs(block_size), narrow)
 
 
 def quantize_dequantize(tensor: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor, qmin: int, qmax: int,
@@ -356,10 +408,8 @@ def quantize_dequantize(tensor: torch.Tensor, scale: torch.Tensor, offset: torch
             internal = torch.float64
     if not _is_grid_representable(internal, qmin, qmax):
         raise RuntimeError(f"{internal} is unable to represent quantized output of range [{qmin}, {qmax}].")
-    if internal == torch.float64:
-        raise RuntimeError(f"aimet_b200 backend: a grid of [{qmin}, {qmax}] needs float64 arithmetic, which the "
-                           "B200 kernels do not provide")
-    narrow = internal != torch.float32
+    # 0: float32 intermediates, 1: the tensor's own dtype, 2: float64 (grids of 2^24 steps or more)
+    narrow = 2 if internal == torch.float64 else int(internal != torch.float32)
     return _QuantDequantFn.apply(tensor, scale, offset, int(qmin), int(qmax), _bs(block_size),
                                  _lib.AQ_V2_OUT_QDQ, narrow)
 

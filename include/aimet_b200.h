@@ -156,13 +156,17 @@ int aq_ste_backward_v1(const float* d_x, const float* d_grad, float* d_dx, int64
 #define AQ_V2_OUT_QDQ   0 /* y = (clamp(round(x/s) - o, qmin, qmax) + o) * s */
 #define AQ_V2_OUT_CODES 1 /* y =  clamp(round(x/s) - o, qmin, qmax)          */
 
+#define AQ_V2_INTERNAL_F64 2 /* value of narrow_internal: float64 arithmetic */
+
 /* Replaces QuantDequantFunc.forward / QuantizeFunc.forward
  * (TrainingExtensions/torch/src/python/aimet_torch/v2/quantization/affine/backends/torch_builtins.py:290-327,208-236).
  * d_scale / d_offset: num_ch fp32 values on the device (already cast to the internal dtype by the caller).
  * d_mask (may be NULL): one byte per element, 1 where qmin <= round(x/s) - o <= qmax.
- * narrow_internal != 0 rounds every intermediate to the storage dtype: the reference computes in the tensor's
- * own dtype for quantize()/dequantize() and, for quantize_dequantize(), whenever that dtype is precise enough
- * for the grid (torch_builtins.py:60-87,162-171); otherwise intermediates stay fp32. */
+ * narrow_internal selects the arithmetic dtype, following the reference's rule (torch_builtins.py:60-87,162-171):
+ * 0 = fp32 intermediates; 1 = every intermediate rounded to the storage dtype (what the reference does for
+ * quantize()/dequantize() and, for quantize_dequantize(), whenever that dtype is precise enough for the grid);
+ * AQ_V2_INTERNAL_F64 = float64 intermediates, for grids of 2^24 steps or more (32-bit quantizers), where qmin / qmax
+ * need not be exact in fp32. */
 int aq_v2_quantize(const void* d_x, void* d_y, uint8_t* d_mask, int dtype, int64_t n, int64_t num_ch, int64_t inner,
                    const float* d_scale, const float* d_offset, double qmin, double qmax, int out_kind,
                    int narrow_internal, void* stream);

@@ -12,6 +12,11 @@ oracle/_ref exist; the fixtures are committed so that the tests need neither).
                      scale / offset, outputs after calibration.
 * v1_range_learning.npz - aimet_torch v1 learned-grid functions ``calculate_forward_pass`` / ``calculate_gradients``
                      (v1/quantsim_straight_through_grad.py loaded by path, CPU): outputs, dx, min / max gradients.
+* v2_backend_reference_tests.npz - the data of the reference's OWN backend test file
+                     (test/python/v2/quantization/affine/backends/test_backend.py, loaded by path): its six
+                     known-answer vector sets, its block-quantization cases, and the inputs / expected values of its
+                     gradient-comparison tests as that file builds them (same seed, same helpers), with the expected
+                     values computed on CPU by the reference's plain-autograd modules and by ``torch_builtins``.
 * v1_ste.npz       - aimet_torch v1 straight-through gradient ``compute_dloss_by_dx`` (same file, CPU): per tensor
                      and per channel on axis 0 / 1, with inputs exactly on the encoding bounds.
 * libpymo.npz      - the reference DlQuantization CPU code (oracle/_ref): per-tensor QDQ / codes, TF and
@@ -305,6 +310,91 @@ def gen_range_learning(ref_root: str):
     np.savez_compressed(os.path.join(HERE, "v1_range_learning.npz"), **out)
 
 
+def gen_reference_backend_tests(ref_root: str):
+    """Data of the reference's backend test file, so that its cases can be replayed where the file itself is absent."""
+    import random
+    _, tb, _ = load_reference_v2(ref_root)
+    if "aimet_torch.v2.quantization.affine" in sys.modules:
+        sys.modules["aimet_torch.v2.quantization"].affine = sys.modules["aimet_torch.v2.quantization.affine"]
+    path = os.path.join(ref_root, "TrainingExtensions", "torch", "test", "python", "v2", "quantization", "affine",
+                        "backends", "test_backend.py")
+    spec = importlib.util.spec_from_file_location("reference_test_backend", path)
+    T = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(T)
+    out = {}
+    # 1. known-answer vector sets (module-level literals of the test file)
+    for name in ("bfloat16_compat_per_tensor_4b_test_set", "bfloat16_compat_per_tensor_8b_test_set",
+                 "per_tensor_4b_test_set", "per_tensor_8b_test_set", "per_channel_4b_test_set",
+                 "per_channel_8b_test_set"):
+        ts = getattr(T, name)
+        for f in ("tensor", "tensor_q", "tensor_qdq", "mask", "delta", "offset"):
+            out[f"set/{name}/{f}"] = getattr(ts, f).numpy()
+        out[f"set/{name}/q"] = np.array([ts.qmin, ts.qmax])
+
+    # 2. gradient comparisons, built exactly as the test file builds them (seed, helper functions, plain-autograd modules)
+    def seeded():
+        random.seed(19521)
+        torch.random.manual_seed(19521)
+
+    seeded()
+    session_offset = torch.randint(-5, 5, []).to(torch.float32)   # the file's session fixture
+    for kind in ("quantize", "dequantize", "qdq"):
+        for qmin, qmax in ((0, 255), (-128, 127)):
+            seeded()
+            scale = torch.rand([])
+            scale[scale == 0.0] = 0.1
+            offset = session_offset.detach().clone()
+            if kind == "dequantize":
+                x = T.get_random_quantized_tensor((2, 3, 4, 5), qmin, qmax)
+                module = T.AutogradDequantizationModule(scale, offset)
+            else:
+                x = T.get_round_safe_quantizable_tensor((2, 3, 4, 5), scale, qmin, qmax)
+                module = (T.AutogradQuantizationModule if kind == "quantize" else T.AutogradQuantDequantModule)(
+                    scale, offset, qmin, qmax)
+            xa = x.detach().clone().requires_grad_(True)
+            expected = module(xa)
+            grad_in = torch.randn_like(x)
+            expected.backward(grad_in)
+            key = f"grad/{kind}/{qmin}_{qmax}"
+            out[f"{key}/x"], out[f"{key}/scale"], out[f"{key}/offset"] = x.numpy(), scale.numpy(), offset.numpy()
+            out[f"{key}/grad_in"], out[f"{key}/y"] = grad_in.numpy(), expected.detach().numpy()
+            out[f"{key}/dx"] = xa.grad.numpy()
+            out[f"{key}/dscale"], out[f"{key}/doffset"] = module.scale.grad.numpy(), module.offset.grad.numpy()
+
+    # 3. block quantization: the parametrised cases of test_block_quant (inputs and expected codes are its literals)
+    marks = [m for m in T.TestQuantizationBackends.test_block_quant.pytestmark if m.name == "parametrize"
+             and m.args[0].startswith("scale")]
+    inp = torch.tensor([[-1.2, 2.4], [-.6, -.18]])
+    out["block/inp"] = inp.numpy()
+    for i, (scale, offset, block_size, output) in enumerate(marks[0].args[1]):
+        out[f"block/{i}/scale"], out[f"block/{i}/offset"] = scale.numpy(), offset.numpy()
+        out[f"block/{i}/block_size"] = np.array(block_size if block_size is not None else [], dtype=np.int64)
+        out[f"block/{i}/codes"] = output.numpy()
+    out["block/count"] = np.array(len(marks[0].args[1]))
+    # test_block_size and test_block_quant_2: shapes as in the file; expected values from torch_builtins on CPU
+    for name, ishape, sshape, block_size in (("block_size", (8, 6, 8, 3), (4, 3, 8, 1), [-1, 2, 1, 3]),
+                                             ("block_quant_2", (3, 5, 4, 6, 12, 9), (2, 1, 4, 9), [2, 6, 3, 1])):
+        seeded()
+        if name == "block_size":
+            scale = torch.randn(*sshape)
+            offset = torch.randint(low=-128, high=127, size=sshape).to(dtype=scale.dtype)
+            x = torch.randn(*ishape)
+        else:
+            x = torch.randn(*ishape)
+            scale = torch.randn(*sshape)
+            offset = torch.randint(low=-128, high=127, size=sshape).to(dtype=scale.dtype)
+        with torch.no_grad():
+            q = tb.quantize(x, scale, offset, -128, 127, block_size)
+            dq = tb.dequantize(q, scale, offset, block_size)
+            qdq = tb.quantize_dequantize(x, scale, offset, -128, 127, block_size)
+        out[f"blockcase/{name}/x"], out[f"blockcase/{name}/scale"] = x.numpy(), scale.numpy()
+        out[f"blockcase/{name}/offset"] = offset.numpy()
+        out[f"blockcase/{name}/block_size"] = np.array(block_size, dtype=np.int64)
+        out[f"blockcase/{name}/q"], out[f"blockcase/{name}/dq"], out[f"blockcase/{name}/qdq"] = \
+            q.numpy(), dq.numpy(), qdq.numpy()
+    np.savez_compressed(os.path.join(HERE, "v2_backend_reference_tests.npz"), **out)
+
+
 def _load_v1_grad(ref_root: str):
     at = os.path.join(ref_root, "TrainingExtensions", "torch", "src", "python", "aimet_torch")
     for name in ("aimet_torch", "aimet_torch.v1"):
@@ -395,9 +485,11 @@ if __name__ == "__main__":
         raise SystemExit("usage: gen_golden.py /path/to/aimet   (a checkout of the reference; or set AIMET_REFERENCE_ROOT)")
     only = sys.argv[2:]   # optionally: names of the generators to run
     gens = {"v2": lambda: gen_v2(ref), "quantizer": lambda: gen_quantizer(ref),
-            "range_learning": lambda: gen_range_learning(ref), "ste_v1": lambda: gen_ste_v1(ref), "libpymo": gen_libpymo}
+            "range_learning": lambda: gen_range_learning(ref), "reference_backend_tests": lambda: gen_reference_backend_tests(ref),
+            "ste_v1": lambda: gen_ste_v1(ref), "libpymo": gen_libpymo}
     for name, fn in gens.items():
         if not only or name in only:
             fn()
-    for f in ("v2_backend.npz", "v2_minmax.npz", "v2_quantizer.npz", "v1_range_learning.npz", "v1_ste.npz", "libpymo.npz"):
+    for f in ("v2_backend.npz", "v2_minmax.npz", "v2_quantizer.npz", "v1_range_learning.npz", "v1_ste.npz", "v2_backend_reference_tests.npz",
+              "libpymo.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")

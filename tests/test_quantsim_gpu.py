@@ -74,7 +74,7 @@ def test_resnet18_every_quantizer_matches_cpu_reference(cuda, oracle):
             ref.update(t)
         want = ref.compute(8, False, False, False)
         assert q.is_initialized(), name
-        assert float(q.min) == float(np.float32(want[0])) and float(q.max) == float(np.float32(want[1])), name
+        assert float(q.min.detach()) == float(np.float32(want[0])) and float(q.max.detach()) == float(np.float32(want[1])), name
     # weights: per-output-channel symmetric min/max of the folded weights
     for name, layer in sim.layers.items():
         w = layer.layer.weight.detach().cpu().numpy()
@@ -92,3 +92,52 @@ def test_resnet18_every_quantizer_matches_cpu_reference(cuda, oracle):
     assert x.grad is not None and torch.isfinite(x.grad).all()
     first = sim.layers["conv1"]
     assert first.layer.weight.grad is not None and first.param_quantizers["weight"].min.grad is not None
+
+
+@pytest.mark.gpu
+def test_resnet50_full_size_every_quantizer_matches_cpu_reference(cuda, oracle):
+    """Benchmark configuration 4 at its real size: ResNet-50, batches of 128 x 3 x 224 x 224 (two of them), W8 per
+    channel symmetric / A8 TF-Enhanced.  Every activation quantizer must end with the encoding the CPU reference
+    analyzer derives from the very tensors it saw (fed to the analyzer as they pass, batch by batch), every weight
+    quantizer with the per-channel min/max encoding of the folded weights."""
+    from oracle import OracleTfeAnalyzer, v2_oracle as v2
+    from aimet_b200.v2.quantsim import QuantizationSimModel
+    m = _resnet("resnet50").to(cuda)
+    g = torch.Generator(device=cuda)
+    batches = []
+    for b in range(2):
+        g.manual_seed(2000 + b)
+        batches.append(torch.randn(128, 3, 224, 224, device=cuda, generator=g))
+    sim = QuantizationSimModel(m, batches[0])
+    assert len(sim.layers) == 54 and len(sim.activation_quantizers) == 73
+    refs = {name: OracleTfeAnalyzer(oracle) for name in sim.activation_quantizers}
+    fed = {name: 0 for name in sim.activation_quantizers}
+
+    def feed(name, t):
+        refs[name].update(t.detach().float().cpu().numpy().reshape(-1))
+        fed[name] += 1
+
+    hooks = [q.register_forward_pre_hook(lambda mod, args, n=name: feed(n, args[0]))
+             for name, q in sim.activation_quantizers.items()]
+    sim.compute_encodings(lambda model, data: [model(x) for x in data], batches)
+    for h in hooks:
+        h.remove()
+    for name, q in sim.activation_quantizers.items():
+        assert fed[name] == len(batches), name
+        want = refs[name].compute(8, False, False, False)
+        assert q.is_initialized(), name
+        assert float(q.min.detach()) == float(np.float32(want[0])) and float(q.max.detach()) == float(np.float32(want[1])), name
+    for name, layer in sim.layers.items():
+        w = layer.layer.weight.detach().cpu().numpy()
+        flat = w.reshape(w.shape[0], -1)
+        shape = (w.shape[0],) + (1,) * (w.ndim - 1)
+        emn, emx = v2.minmax_encodings(flat.min(axis=1).reshape(shape), flat.max(axis=1).reshape(shape), 255, True)
+        wq = layer.param_quantizers["weight"]
+        assert_bits_equal(wq.min.detach().cpu().numpy(), emn, name + " min")
+        assert_bits_equal(wq.max.detach().cpu().numpy(), emx, name + " max")
+    # one fake-quantized forward + backward step at full size
+    x = batches[0].requires_grad_(True)
+    y = sim.model(x)
+    assert y.shape == (128, 1000) and torch.isfinite(y).all()
+    y.square().mean().backward()
+    assert x.grad is not None and torch.isfinite(x.grad).all()
