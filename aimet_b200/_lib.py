@@ -65,6 +65,7 @@ SIGNATURES = {
     "aq_tfe_pdf_replay": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp]),
     "aq_tfe_search_workspace_bytes": (_i64, []),
     "aq_tfe_search": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _vp]),
+    "aq_tfe_percentile_encoding": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _f64, _i32, _i32, _i32, _i32, _vp, _vp]),
     "aq_tfe_compute_encoding": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i64,
                                        _vp]),
 }

@@ -14,7 +14,7 @@ CSRC = os.path.join(_HERE, "csrc")
 LIB_DIR = os.path.join(_HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libaimet_b200.so")
 SOURCES = ["capi.cu", "qdq_kernels.cu", "stats_kernels.cu", "tfe_search.cu"]
-HEADERS = ["common.cuh", "kernels.h", os.path.join("..", "..", "include", "aimet_b200.h")]
+HEADERS = ["common.cuh", "encoding_math.cuh", "kernels.h", os.path.join("..", "..", "include", "aimet_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

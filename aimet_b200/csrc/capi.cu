@@ -8,6 +8,7 @@
 #include <atomic>
 
 #include "common.cuh"
+#include "encoding_math.cuh"
 #include "kernels.h"
 
 namespace aq
@@ -39,16 +40,6 @@ int check_launch()
 }
 
 // ---- host arithmetic ---------------------------------------------------------------------------------
-// std::max / std::min with the reference's argument order (decides NaN and signed-zero behaviour)
-static inline double hmax(double a, double b)
-{
-    return (a < b) ? b : a;
-}
-static inline double hmin(double a, double b)
-{
-    return (b < a) ? b : a;
-}
-
 static void fill_encoding(int bw, double mn, double mx, aq_encoding_t* e)
 {
     mn = hmin(mn, 0.0);
@@ -62,47 +53,6 @@ static void fill_encoding(int bw, double mn, double mx, aq_encoding_t* e)
     e->offset = round(mn / e->delta);
     e->min    = e->offset * e->delta;
     e->max    = e->delta * steps + e->min;
-}
-
-static void computed_encodings(int bw, double mn, double mx, bool sym, bool strict, bool unsigned_sym,
-                               aq_encoding_t* e)
-{
-    double steps = pow(2.0, (double) (uint8_t) bw) - 1.0;
-    if (sym && strict)
-        steps -= 1.0;
-    e->bw = bw;
-    if (isinf(mn))
-        mn = -(double) FLT_MAX;
-    if (isinf(mx))
-        mx = (double) FLT_MAX;
-    if (sym && (mn < 0.0 || !unsigned_sym))
-    {
-        const double amax          = hmax(fabs(mx), fabs(mn));
-        const unsigned int pos     = (unsigned int) floor(steps / 2.0);
-        e->delta                   = amax / pos;
-        e->offset                  = -ceil(steps / 2.0);
-        e->min                     = hmax(e->offset * e->delta, -(double) FLT_MAX);
-        e->max                     = hmin(e->delta * pos, (double) FLT_MAX);
-        return;
-    }
-    e->delta = (mx - mn) / steps;
-    if (mn < 0 && mx > 0)
-    {
-        double zero_code = round(-mn / e->delta);
-        zero_code        = hmin(steps, hmax(0.0, zero_code));
-        e->offset        = -zero_code;
-        const double lo  = e->delta * e->offset;
-        e->min           = (lo >= -(double) FLT_MAX && lo <= (double) FLT_MAX) ? lo : -(double) FLT_MAX;
-        e->max           = mx - mn + e->min;
-        if (e->max > (double) FLT_MAX)
-            e->max = (double) FLT_MAX;
-    }
-    else
-    {
-        e->offset = round(mn / e->delta);
-        e->min    = mn;
-        e->max    = mx;
-    }
 }
 
 static inline bool bad_geom(int64_t n, int64_t num_ch, int64_t inner)
@@ -459,6 +409,21 @@ int aq_tfe_compute_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_his
         return rc;
     return tfe_search(d_state, d_pdf, stats_updated, d_stats_updated, bw, symmetric, strict, unsigned_sym,
                       d_out_encoding, d_workspace, workspace_bytes, (cudaStream_t) stream);
+}
+
+int aq_tfe_percentile_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_hists, const int64_t* d_counts,
+                               int64_t num_batches, double* d_pdf, int32_t* d_iterations, int stats_updated,
+                               const int32_t* d_stats_updated, double percentile, int bw, int symmetric, int strict,
+                               int unsigned_sym, double* d_out_encoding, void* stream)
+{
+    if (!d_state || !d_out_encoding || bw < 1 || bw > 32 || ((uintptr_t) d_stats_updated % 4) ||
+        !(percentile >= 0.0 && percentile <= 100.0))
+        return AQ_ERR_INVALID_ARG;
+    const int rc = aq_tfe_pdf_replay(d_hists, d_counts, num_batches, d_pdf, d_iterations, stream);
+    if (rc != AQ_OK)
+        return rc;
+    return tfe_percentile(d_state, d_pdf, stats_updated, d_stats_updated, (float) percentile, bw, symmetric, strict,
+                          unsigned_sym, d_out_encoding, (cudaStream_t) stream);
 }
 
 }   // extern "C"

@@ -82,4 +82,7 @@ int64_t tfe_search_workspace_bytes();
 int tfe_search(const aq_tfe_state_t* st, const double* pdf, int stats_updated, const int32_t* stats_updated_dev, int bw,
                int symmetric, int strict, int unsigned_sym, double* out, void* ws, int64_t ws_bytes, cudaStream_t stream);
 
+int tfe_percentile(const aq_tfe_state_t* st, const double* pdf, int stats_updated, const int32_t* stats_updated_dev,
+                   float percentile, int bw, int symmetric, int strict, int unsigned_sym, double* out, cudaStream_t stream);
+
 }   // namespace aq

@@ -11,6 +11,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "encoding_math.cuh"
 #include "kernels.h"
 
 namespace aq
@@ -350,6 +351,99 @@ int tfe_search(const aq_tfe_state_t* st, const double* pdf, int stats_updated, c
     a.slots         = symmetric ? kSymSlots : kAsymSlots;
     const int grid  = (a.slots + kSearchWarps - 1) / kSearchWarps;
     launch_pdl(tfe_search_kernel, (unsigned) grid, kSearchWarps * 32, 0, stream, a);
+    note_launch();
+    return check_launch();
+}
+
+// ---- percentile analyzer on the same statistics ----------------------------------------------------------------
+// PercentileEncodingAnalyzer<float>::computeEncoding (DlQuantization/src/PercentileEncodingAnalyzer.cpp:79-194) with
+// findOriginalRange<float> (src/math_functions.cpp:404-438).  512 buckets and a serial cumulative sum whose order the
+// result depends on: one thread does it, in the reference's mixed float / double arithmetic.
+__global__ void tfe_percentile_kernel(const aq_tfe_state_t* __restrict__ st, const double* __restrict__ pdf,
+                                      int stats_updated, const int32_t* __restrict__ stats_updated_dev, float percentile,
+                                      int bw, int symmetric, int strict, int unsigned_sym, double* __restrict__ out)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x != 0 || blockIdx.x != 0)
+        return;
+    float num_steps = (float) (ldexp(1.0, bw) - 1.0);
+    if (symmetric && strict)
+        num_steps = __fsub_rn(num_steps, 1.0f);
+    if (!st->initialized)
+    {
+        double e[5] = {0, 0, 0, 0, 0};
+        if (stats_updated_dev ? (*stats_updated_dev != 0) : (stats_updated != 0))
+        {
+            const double d = __ddiv_rn(2.0, (double) (int) num_steps);
+            const double o = floor(__ddiv_rn(-1.0, d));
+            e[0]           = __dmul_rn(o, d);
+            e[1]           = __dadd_rn(e[0], __dmul_rn((double) (int) num_steps, d));
+            e[2] = d, e[3] = o, e[4] = bw;
+        }
+        for (int i = 0; i < 5; ++i)
+            out[i] = e[i];
+        return;
+    }
+    const double* __restrict__ xl = st->x_left;
+    float min_val = (float) xl[0], max_val = (float) xl[AQ_PDF_SIZE - 1];
+    for (int i = 0; i < AQ_PDF_SIZE; ++i)
+        if (pdf[i] > 0)
+        {
+            min_val = (float) xl[i];
+            break;
+        }
+    for (int i = AQ_PDF_SIZE - 1; i > 0; --i)
+        if (pdf[i] > 0)
+        {
+            max_val = (float) xl[i];
+            break;
+        }
+    min_val = smin(min_val, 0.0f);
+    max_val = smax(max_val, 0.0f);
+    max_val = smax(max_val, __fadd_rn(min_val, (float) 0.01));
+    float a_min = min_val, a_max = max_val;
+    if (percentile != 100.0f)
+    {
+        const float bin_width = (float) __dsub_rn(xl[1], xl[0]);
+        float p_min           = (float) xl[0];
+        float p_max           = (float) __dadd_rn(xl[AQ_PDF_SIZE - 1], (double) bin_width);
+        const float left      = __fsub_rn(1.0f, __fdiv_rn(percentile, 100.0f));
+        const float right     = __fdiv_rn(percentile, 100.0f);
+        // cumulative distribution, summed in bucket order; the first bucket reaching `left` gives the lower bound,
+        // the last bucket still below `right` (and below the observed maximum) the upper one
+        double cdf = 0.0;
+        bool have_min = false;
+        int top = -1;
+        for (int i = 0; i < AQ_PDF_SIZE; ++i)
+        {
+            cdf = (i == 0) ? pdf[0] : __dadd_rn(pdf[i], cdf);
+            if (!have_min && cdf >= (double) left)
+            {
+                p_min    = (float) xl[i];
+                have_min = true;
+            }
+            if (cdf < (double) right && xl[i] < (double) max_val)
+                top = i;
+        }
+        if (top >= 0)
+            p_max = (float) __dadd_rn(xl[top], (double) bin_width);
+        if (p_min == p_max)
+            p_max = __fadd_rn(p_max, bin_width);
+        a_min = p_min, a_max = p_max;
+    }
+    a_min = smin(a_min, 0.0f);
+    a_max = smax(a_max, 0.0f);
+    aq_encoding_t e;
+    computed_encodings(bw, (double) a_min, (double) a_max, symmetric != 0, strict != 0, unsigned_sym != 0, &e);
+    out[0] = e.min, out[1] = e.max, out[2] = e.delta, out[3] = e.offset, out[4] = (double) bw;
+}
+
+int tfe_percentile(const aq_tfe_state_t* st, const double* pdf, int stats_updated, const int32_t* stats_updated_dev,
+                   float percentile, int bw, int symmetric, int strict, int unsigned_sym, double* out, cudaStream_t stream)
+{
+    launch_pdl(tfe_percentile_kernel, 1, 32, 0, stream, st, pdf, stats_updated, stats_updated_dev, percentile, bw,
+               symmetric, strict, unsigned_sym, out);
     note_launch();
     return check_launch();
 }

@@ -65,7 +65,7 @@ class TfEncoding:
 
 
 _SUPPORTED_SCHEMES = (QuantizationMode.QUANTIZATION_TF, QuantizationMode.QUANTIZATION_TF_ENHANCED,
-                      QuantizationMode.QUANTIZATION_RANGE_LEARNING)
+                      QuantizationMode.QUANTIZATION_RANGE_LEARNING, QuantizationMode.QUANTIZATION_PERCENTILE)
 
 
 def _require_gpu(t: torch.Tensor, use_cuda: bool, what: str):
@@ -109,9 +109,12 @@ class _TfEnhancedStats:
     """512-bucket PDF statistics on the device (TfEnhancedEncodingAnalyzer,
     DlQuantization/src/TfEnhancedEncodingAnalyzer.cpp:60-113)."""
 
-    def __init__(self):
+    def __init__(self, percentile_of=None):
         self.dev: Optional[ops.TfeDeviceState] = None
         self.updated = False
+        #: None for TF-Enhanced; for the percentile analyzer (PercentileEncodingAnalyzer.cpp, same statistics) a
+        #: callable returning the percentile currently set on the owning quantizer
+        self.percentile_of = percentile_of
 
     def update(self, x: torch.Tensor):
         if self.dev is None:
@@ -127,7 +130,11 @@ class _TfEnhancedStats:
         st.add_batch(x)
 
     def compute(self, bw, symmetric, strict, unsigned_sym) -> TfEncoding:
-        e = self.dev.compute_encoding(self.updated, bw, symmetric, strict, unsigned_sym).tolist()
+        if self.percentile_of is not None:
+            e = self.dev.percentile_encoding(self.updated, self.percentile_of(), bw, symmetric, strict,
+                                             unsigned_sym).tolist()
+        else:
+            e = self.dev.compute_encoding(self.updated, bw, symmetric, strict, unsigned_sym).tolist()
         return TfEncoding(e[0], e[1], e[2], e[3], int(e[4]))
 
     def histogram(self) -> List[Tuple[float, float]]:
@@ -146,13 +153,15 @@ class AimetTensorQuantizer:
         self._scheme = QuantizationMode(quantizationScheme)
         if self._scheme not in _SUPPORTED_SCHEMES:
             raise RuntimeError(f"aimet_b200: quantization scheme {self._scheme.name} is outside the accelerated path "
-                               "(TF and TF-Enhanced are implemented)")
+                               "(TF, TF-Enhanced and percentile are implemented)")
         self._isEncodingValid = False
         self._stats = self._new_stats()
 
     def _new_stats(self):
         if self._scheme == QuantizationMode.QUANTIZATION_TF_ENHANCED:
             return _TfEnhancedStats()
+        if self._scheme == QuantizationMode.QUANTIZATION_PERCENTILE:
+            return _TfEnhancedStats(percentile_of=self.getPercentileValue)
         return _MinMaxStats()
 
     # -- statistics ----------------------------------------------------------------------------------
@@ -177,9 +186,11 @@ class AimetTensorQuantizer:
         return self._stats.histogram()
 
     def setPercentileValue(self, percentile: float):
-        # only meaningful for the percentile scheme, which the constructor rejects; a no-op otherwise,
-        # as in the reference
-        return None
+        """Kept for the percentile scheme; the other analyzers ignore it, as in the reference."""
+        self._percentile = float(percentile)
+
+    def getPercentileValue(self) -> float:
+        return getattr(self, "_percentile", 100.0)
 
     # -- fake-quant ------------------------------------------------------------------------------------
     def quantizeDequantize(self, input: torch.Tensor, encoding: TfEncoding, roundingMode: RoundingMode,
@@ -201,18 +212,27 @@ class AimetTensorQuantizer:
     def quantizeDequantizePerChannel(self, input: torch.Tensor, encodings: Sequence[TfEncoding], numChannel: int,
                                      numElement: int, numElementPerChannel: int, roundingMode: RoundingMode,
                                      useCuda: bool) -> torch.Tensor:
-        _require_gpu(input, useCuda, "quantizeDequantizePerChannel")
-        if len(encodings) != numChannel:
-            raise RuntimeError("aimet_b200: one encoding per channel is required")
-        x = input.contiguous()
-        if x.numel() != numElement:
-            raise RuntimeError("aimet_b200: numElement does not match the tensor")
-        mm = torch.tensor([[e.min for e in encodings], [e.max for e in encodings]], dtype=torch.float32)
-        mm = mm.to(x.device, non_blocking=True)
-        steps = 2.0 ** encodings[0].bw - 1
-        if encodings[0].min == -encodings[0].max:
-            steps -= 1
-        return ops.qdq_per_channel(x, mm[0], mm[1], numChannel, numElementPerChannel, steps, int(roundingMode))
+        return quantize_dequantize_per_channel(input, encodings, numChannel, numElement, numElementPerChannel,
+                                               roundingMode, useCuda)
+
+
+def quantize_dequantize_per_channel(input: torch.Tensor, encodings: Sequence[TfEncoding], numChannel: int,
+                                    numElement: int, numElementPerChannel: int, roundingMode: RoundingMode,
+                                    useCuda: bool) -> torch.Tensor:
+    """AimetTensorQuantizer::quantizeDequantizePerChannel (TrainingExtensions/torch/src/AimetTensorQuantizer.cpp:256-307):
+    the per-channel grid is derived from the encodings' (min, max) inside the kernel."""
+    _require_gpu(input, useCuda, "quantizeDequantizePerChannel")
+    if len(encodings) != numChannel:
+        raise RuntimeError("aimet_b200: one encoding per channel is required")
+    x = input.contiguous()
+    if x.numel() != numElement:
+        raise RuntimeError("aimet_b200: numElement does not match the tensor")
+    mm = torch.tensor([[e.min for e in encodings], [e.max for e in encodings]], dtype=torch.float32)
+    mm = mm.to(x.device, non_blocking=True)
+    steps = 2.0 ** encodings[0].bw - 1
+    if encodings[0].min == -encodings[0].max:
+        steps -= 1
+    return ops.qdq_per_channel(x, mm[0], mm[1], numChannel, numElementPerChannel, steps, int(roundingMode))
 
 
 class TensorQuantizer:
@@ -271,3 +291,81 @@ class TensorQuantizer:
 
     def getStatsHistogram(self):
         return self._q.getStatsHistogram()
+
+    def setPercentileValue(self, percentile: float):
+        self._q.setPercentileValue(percentile)
+
+    def getPercentileValue(self) -> float:
+        return self._q.getPercentileValue()
+
+    def computePartialEncoding(self, bw: int, encoding: TfEncoding, useSymmetricEncodings: bool,
+                               useUnsignedSymmetric: bool, useStrictSymmetric: bool) -> None:
+        """Fills in the missing half of ``encoding`` in place (DlQuantization/src/TensorQuantizer.cpp:327-343):
+        (min, max) from (delta, offset) when min == max == 0, (delta, offset) from (min, max) when delta == 0."""
+        compute_partial_encoding(bw, encoding, useSymmetricEncodings, useUnsignedSymmetric, useStrictSymmetric)
+
+
+def compute_partial_encoding(bw: int, encoding: TfEncoding, use_symmetric: bool, use_unsigned_symmetric: bool,
+                             use_strict_symmetric: bool) -> None:
+    """``computeMinMaxRangeFromDeltaOffset`` / ``computeDeltaAndOffsetFromMinMax``
+    (DlQuantization/src/quantization_utils.cpp:158-228); host arithmetic in double, as in the reference."""
+    import math
+    if encoding.min == 0 and encoding.max == 0:
+        if encoding.bw == 0:
+            raise ValueError("Encodings must have a valid non-zero bitwidth")
+        if encoding.delta == 0 and encoding.offset > 0:
+            raise ValueError("Encoding must have a valid non-zero delta/offset if min and max are zero")
+        steps = 2.0 ** bw - 1
+        if use_symmetric and use_strict_symmetric:
+            steps -= 1
+        encoding.min = encoding.offset * encoding.delta
+        if use_symmetric and (encoding.min < 0.0 or not use_unsigned_symmetric):
+            encoding.max = encoding.delta * math.floor(steps / 2)
+        else:
+            encoding.max = encoding.delta * steps + encoding.min
+    elif encoding.delta == 0:
+        if encoding.bw == 0:
+            raise ValueError("Encodings must have a valid non-zero bitwidth")
+        if encoding.delta != 0 and encoding.offset != 0:
+            raise ValueError("Encoding delta and offset must be zero to use this function")
+        e = ops.computed_encodings(int(bw), encoding.min, encoding.max, use_symmetric, use_strict_symmetric,
+                                   use_unsigned_symmetric)
+        encoding.delta, encoding.offset, encoding.bw = e.delta, e.offset, int(e.bw)
+    else:
+        raise RuntimeError("Cannot determine how to compute partial encoding")
+
+
+class EncodingAnalyzerForPython:
+    """Mirror of ``libpymo.EncodingAnalyzerForPython`` (DlQuantization/src/EncodingAnalyzerForPython.cpp:54-92): numpy
+    in, ``(TfEncoding, is_valid)`` out.  The array is staged to the GPU and the statistics stay there."""
+
+    def __init__(self, quantizationScheme: QuantizationMode, device: str = "cuda"):
+        self._q = AimetTensorQuantizer(quantizationScheme)
+        self._device = torch.device(device)
+
+    def updateStats(self, input: np.ndarray, use_cuda: bool = True):
+        t = torch.from_numpy(np.ascontiguousarray(input, dtype=np.float32)).to(self._device, non_blocking=True)
+        self._q.updateStats(t, True)
+
+    def computeEncoding(self, bitwidth: int, isSymmetric: bool, useStrictSymmetric: bool,
+                        useUnsignedSymmetric: bool) -> Tuple[TfEncoding, bool]:
+        return self._q.getEncoding(bitwidth, isSymmetric, useStrictSymmetric, useUnsignedSymmetric)
+
+
+class TensorQuantizationSimForPython:
+    """Mirror of ``libpymo.TensorQuantizationSimForPython`` (DlQuantization/src/TensorQuantizationSimForPython.cpp:54-79):
+    ``quantizeDequantize(array, encoding, roundingMode[, bitwidth], use_cuda) -> array``."""
+
+    def __init__(self, device: str = "cuda"):
+        self._device = torch.device(device)
+
+    def quantizeDequantize(self, input: np.ndarray, encoding: TfEncoding, roundingMode: RoundingMode, *rest):
+        if len(rest) == 2:
+            bitwidth = int(rest[0])
+        elif len(rest) == 1:
+            bitwidth = int(encoding.bw)
+        else:
+            raise TypeError("quantizeDequantize(input, encoding, roundingMode, [bitwidth,] use_cuda)")
+        t = torch.from_numpy(np.ascontiguousarray(input, dtype=np.float32)).to(self._device, non_blocking=True)
+        y = ops.qdq_per_tensor(t, encoding.min, encoding.max, bitwidth, int(roundingMode))
+        return y.cpu().numpy().reshape(np.shape(input))

@@ -316,6 +316,17 @@ int aq_tfe_compute_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_his
                             int unsigned_symmetric, double* d_out_encoding, void* d_workspace, int64_t workspace_bytes,
                             void* stream);
 
+/* The percentile analyzer on the same per-batch rows: aq_tfe_pdf_replay, then
+ * PercentileEncodingAnalyzer<float>::computeEncoding (src/PercentileEncodingAnalyzer.cpp:79-194): the range that holds
+ * `percentile` percent of the probability mass from either side, widened to include zero, then the grid of
+ * getComputedEncodings (src/quantization_utils.cpp:58-143).  percentile = 100 keeps the observed range.  Statistics
+ * (state, rows, counts) are those of aq_tfe_offer_grid / aq_tfe_histogram: the reference's percentile, MSE and
+ * TF-Enhanced analyzers all collect the same 512-bucket PDF.  d_stats_updated as for aq_tfe_compute_encoding. */
+int aq_tfe_percentile_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_hists, const int64_t* d_counts,
+                               int64_t num_batches, double* d_pdf, int32_t* d_iterations, int stats_updated,
+                               const int32_t* d_stats_updated, double percentile, int bw, int symmetric,
+                               int strict_symmetric, int unsigned_symmetric, double* d_out_encoding, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -24,11 +24,21 @@ REF_SO = os.path.join(_HERE, "_ref", "libaimet_ref.so")
 PDF_SIZE = 512
 
 
+def reference_root(ref_root: Optional[str] = None) -> Optional[str]:
+    """Where a checkout of the reference lies: the argument, else ``AIMET_REFERENCE_ROOT``, else a directory named
+    ``reference`` next to this repository.  None when there is none (the fixtures under tests/golden then stand in)."""
+    for root in (ref_root, os.environ.get("AIMET_REFERENCE_ROOT"),
+                 os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if root and os.path.isdir(os.path.join(root, "ModelOptimizations", "DlQuantization", "src")):
+            return root
+    return None
+
+
 def build(ref_root: Optional[str] = None) -> None:
-    """Compile the C restatement; also the reference shim when ``ref_root`` (or the default checkout) exists."""
+    """Compile the C restatement; also the reference shim when a reference checkout is found (reference_root)."""
     subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
-    root = ref_root or "/root/reference"
-    if os.path.isdir(os.path.join(root, "ModelOptimizations", "DlQuantization", "src")):
+    root = reference_root(ref_root)
+    if root is not None:
         subprocess.run(["make", "-s", "-C", _HERE, "ref", f"REF_ROOT={root}"], check=True)
 
 
@@ -72,6 +82,7 @@ class Oracle:
         L.orc_tfe_candidates.argtypes = [_PD, _PD, C.c_int, C.c_int, C.c_int, C.c_int, _PF, _PI]
         L.orc_tfe_candidates.restype = C.c_int
         L.orc_tfe_compute.argtypes = [_PD, _PD, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
+        L.orc_percentile_compute.argtypes = [_PD, _PD, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
 
     # --- QDQ -------------------------------------------------------------------------------------
     def fill_encoding(self, bw, mn, mx):
@@ -161,6 +172,16 @@ class Oracle:
         self.lib.orc_hist512(_p(x, C.c_float), x.size, bucket_size, pdf_offset, _p(h, C.c_uint32))
         return h
 
+    def percentile_compute(self, x_left, pdf, initialized, stats_updated, percentile, bw, symmetric=False,
+                           strict=False, unsigned_sym=False):
+        out = np.zeros(5, np.float64)
+        x_left = np.ascontiguousarray(x_left, np.float64)
+        pdf = np.ascontiguousarray(pdf, np.float64)
+        self.lib.orc_percentile_compute(_p(x_left, C.c_double), _p(pdf, C.c_double), int(initialized),
+                                        int(stats_updated), float(percentile), int(bw), int(symmetric), int(strict),
+                                        int(unsigned_sym), _p(out, C.c_double))
+        return out
+
     def tfe_cost(self, x_left, pdf, bw, delta, offset):
         return self.lib.orc_tfe_cost(_p(x_left, C.c_double), _p(pdf, C.c_double), bw, delta, offset)
 
@@ -204,6 +225,12 @@ class OracleTfeAnalyzer:
         return out
 
 
+    def compute_percentile(self, percentile, bw, symmetric=False, strict=False, unsigned_sym=False):
+        """The percentile analyzer's encoding from the same statistics (PercentileEncodingAnalyzer.cpp:79-194)."""
+        return self.o.percentile_compute(self.x_left, self.pdf, self.initialized.value, self.stats_updated, percentile,
+                                         bw, symmetric, strict, unsigned_sym)
+
+
 class Reference:
     """ctypes view of libaimet_ref.so (the reference's own CPU code). ``available()`` says whether it exists."""
 
@@ -231,6 +258,14 @@ class Reference:
         L.ref_tfe_histogram.argtypes = [C.c_void_p, _PD, _PD]
         L.ref_tfe_histogram.restype = C.c_int
         L.ref_update_pdf.argtypes = [_PF, C.c_int64, _PD, _PD, _PI, _PI]
+        if hasattr(L, "ref_pct_new"):
+            L.ref_pct_new.restype = C.c_void_p
+            L.ref_pct_free.argtypes = [C.c_void_p]
+            L.ref_pct_update.argtypes = [C.c_void_p, _PF, C.c_int64]
+            L.ref_pct_set_percentile.argtypes = [C.c_void_p, C.c_float]
+            L.ref_pct_compute.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
+            L.ref_partial_encoding.argtypes = [C.c_int, _PD, C.c_int, C.c_int, C.c_int]
+            L.ref_partial_encoding.restype = C.c_int
 
     def fill_encoding(self, bw, mn, mx):
         out = np.zeros(5, np.float64)
@@ -293,7 +328,7 @@ class Reference:
 
 
 class RefAnalyzer:
-    """Owns one reference analyzer object: kind 'tf' (MinMax) or 'tfe' (TF-Enhanced)."""
+    """Owns one reference analyzer object: kind 'tf' (MinMax), 'tfe' (TF-Enhanced) or 'pct' (percentile)."""
 
     def __init__(self, ref: Reference, kind: str):
         self.ref, self.kind = ref, kind
@@ -313,6 +348,9 @@ class RefAnalyzer:
         getattr(self.ref.lib, f"ref_{self.kind}_compute")(self.h, bw, int(symmetric), int(strict), int(unsigned_sym),
                                                           _p(out, C.c_double))
         return out
+
+    def set_percentile(self, percentile: float):
+        self.ref.lib.ref_pct_set_percentile(self.h, float(percentile))
 
     def histogram(self):
         xl = np.zeros(PDF_SIZE, np.float64)

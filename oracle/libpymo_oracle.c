@@ -515,3 +515,90 @@ void orc_tfe_compute(const double* x_left, const double* pdf, int initialized, i
     out5[3]     = best_offset;
     out5[4]     = bw;
 }
+
+/* ---------------------------------------------------------------------------------------------
+ * A6. Percentile analyzer on the same 512-bucket PDF (DTYPE = float).
+ * ------------------------------------------------------------------------------------------- */
+/* math_functions.cpp:404-438 (findOriginalRange<float>) */
+static void orc_original_range(const double* x_left, const double* pdf, float* mn_out, float* mx_out)
+{
+    float mn = (float) x_left[0];
+    float mx = (float) x_left[ORC_PDF_SIZE - 1];
+    for (int i = 0; i < ORC_PDF_SIZE; ++i)
+        if (pdf[i] > 0)
+        {
+            mn = (float) x_left[i];
+            break;
+        }
+    for (int i = ORC_PDF_SIZE - 1; i > 0; --i)
+        if (pdf[i] > 0)
+        {
+            mx = (float) x_left[i];
+            break;
+        }
+    mn = STD_MIN(mn, 0.0f);
+    mx = STD_MAX(mx, 0.0f);
+    mx = STD_MAX(mx, mn + (float) 0.01);
+    *mn_out = mn, *mx_out = mx;
+}
+
+/* PercentileEncodingAnalyzer.cpp:79-194 (computeEncoding + _computePercentileRange).
+ * out5 = {min, max, delta, offset, bw}; initialized = whether the PDF exists. */
+void orc_percentile_compute(const double* x_left, const double* pdf, int initialized, int stats_updated, float percentile,
+                            int bw, int symmetric, int strict, int unsigned_sym, double* out5)
+{
+    for (int i = 0; i < 5; ++i)
+        out5[i] = 0;
+    float num_steps = (float) (pow(2, bw) - 1);
+    if (symmetric && strict)
+        num_steps -= 1;
+    if (!initialized)
+    {
+        if (stats_updated)
+        {
+            double e_min = -1, e_max = 1;
+            double delta  = (e_max - e_min) / (int) num_steps;
+            double offset = floor(e_min / delta);
+            e_min         = offset * delta;
+            e_max         = e_min + (int) num_steps * delta;
+            out5[0] = e_min, out5[1] = e_max, out5[2] = delta, out5[3] = offset, out5[4] = bw;
+        }
+        return;
+    }
+    float min_val, max_val;
+    orc_original_range(x_left, pdf, &min_val, &max_val);
+    float a_min = min_val, a_max = max_val;
+    if (percentile != 100.0f)
+    {
+        const float bin_width = (float) (x_left[1] - x_left[0]);
+        float hist_min        = (float) x_left[0];
+        float hist_max        = (float) (x_left[ORC_PDF_SIZE - 1] + bin_width);
+        float p_min = hist_min, p_max = hist_max;
+        double cdf[ORC_PDF_SIZE];
+        cdf[0] = pdf[0];
+        for (int i = 1; i < ORC_PDF_SIZE; ++i)
+            cdf[i] = pdf[i] + cdf[i - 1];
+        float left = 1 - percentile / 100;
+        for (int i = 0; i < ORC_PDF_SIZE; ++i)
+            if (cdf[i] >= left)
+            {
+                p_min = (float) x_left[i];
+                break;
+            }
+        float right = percentile / 100;
+        for (int i = ORC_PDF_SIZE - 1; i >= 0; --i)
+            if (cdf[i] < right && x_left[i] < max_val)
+            {
+                p_max = (float) (x_left[i] + bin_width);
+                break;
+            }
+        if (p_min == p_max)
+            p_max += bin_width;
+        a_min = p_min, a_max = p_max;
+    }
+    a_min = STD_MIN(a_min, 0.0f);
+    a_max = STD_MAX(a_max, 0.0f);
+    orc_computed_encodings(bw, a_min, a_max, symmetric, strict, unsigned_sym, out5);
+    out5[4] = bw;
+}
+

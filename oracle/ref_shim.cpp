@@ -18,6 +18,7 @@
 #include "DlQuantization/Quantization.hpp"
 #include "TensorQuantizationSim.h"
 #include "TfEncodingAnalyzer.h"
+#include "PercentileEncodingAnalyzer.h"
 #include "TfEnhancedEncodingAnalyzer.h"
 #include "math_functions.hpp"
 #include "quantization_utils.hpp"
@@ -173,6 +174,54 @@ void ref_update_pdf(const float* in, int64_t n, double* xLeft, double* pdf, int*
         *initialized = 1;
         *iterations  = p.iterations;
     }
+}
+
+// ---- PercentileEncodingAnalyzer<float> ---------------------------------------------------------
+void* ref_pct_new()
+{
+    return new PercentileEncodingAnalyzer<float>();
+}
+void ref_pct_free(void* h)
+{
+    delete static_cast<PercentileEncodingAnalyzer<float>*>(h);
+}
+void ref_pct_update(void* h, const float* in, int64_t n)
+{
+    static_cast<PercentileEncodingAnalyzer<float>*>(h)->updateStats(in, (size_t) n, COMP_MODE_CPU);
+}
+void ref_pct_set_percentile(void* h, float percentile)
+{
+    static_cast<PercentileEncodingAnalyzer<float>*>(h)->setPercentileValue(percentile);
+}
+void ref_pct_compute(void* h, int bw, int symmetric, int strict, int unsignedSym, double* out5)
+{
+    TfEncoding e = static_cast<PercentileEncodingAnalyzer<float>*>(h)->computeEncoding(
+        (uint8_t) bw, symmetric != 0, strict != 0, unsignedSym != 0);
+    storeEncoding(e, out5);
+}
+
+// computeMinMaxRangeFromDeltaOffset / computeDeltaAndOffsetFromMinMax (quantization_utils.cpp:158-228) the way
+// TensorQuantizer::computePartialEncoding picks between them (TensorQuantizer.cpp:327-343).  enc5 is in/out;
+// returns 1 when the reference throws.
+int ref_partial_encoding(int bw, double* enc5, int symmetric, int unsignedSym, int strict)
+{
+    TfEncoding e;
+    e.min = enc5[0], e.max = enc5[1], e.delta = enc5[2], e.offset = enc5[3], e.bw = (int) enc5[4];
+    try
+    {
+        if (e.min == 0 && e.max == 0)
+            computeMinMaxRangeFromDeltaOffset((uint8_t) bw, e, symmetric != 0, unsignedSym != 0, strict != 0);
+        else if (e.delta == 0)
+            computeDeltaAndOffsetFromMinMax((uint8_t) bw, e, symmetric != 0, unsignedSym != 0, strict != 0);
+        else
+            return 1;
+    }
+    catch (...)
+    {
+        return 1;
+    }
+    storeEncoding(e, enc5);
+    return 0;
 }
 
 }   // extern "C"

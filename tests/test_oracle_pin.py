@@ -262,3 +262,42 @@ def test_ref_tf_enhanced(oracle, reference, kinds):
     for bw in (4, 8, 16):
         for sym, strict, uns in [(0, 0, 0), (1, 0, 0), (1, 1, 0), (1, 0, 1)]:
             assert_bits_equal(oa.compute(bw, sym, strict, uns), ra.compute(bw, sym, strict, uns), f"{bw} {sym}{strict}{uns}")
+
+
+@pytest.mark.parametrize("kinds", [("relu",) * 4, ("normal",) * 3, ("zeros", "zeros", "relu"), ("neg", "neg"), ("zeros",)])
+def test_ref_percentile(oracle, reference, kinds):
+    """The percentile restatement against the reference's PercentileEncodingAnalyzer on the same batches."""
+    from oracle import OracleTfeAnalyzer, RefAnalyzer
+    gens = {"relu": lambda s: relu_activations(7001, s), "normal": lambda s: normal(7001, s, 2.0, 1.0),
+            "neg": lambda s: normal(7001, s, 1.0, -2.0), "zeros": lambda s: np.zeros(500, np.float32)}
+    batches = [gens[k](31 + i) for i, k in enumerate(kinds)]
+    oa = OracleTfeAnalyzer(oracle)
+    for b in batches:
+        oa.update(b)
+    for pct in (100.0, 99.99, 99.9, 99.0, 90.0, 50.0):
+        ra = RefAnalyzer(reference, "pct")
+        ra.set_percentile(pct)
+        for b in batches:
+            ra.update(b)
+        for bw, sym, strict, uns in ((8, 0, 0, 0), (8, 1, 0, 0), (4, 1, 1, 0), (16, 1, 0, 1)):
+            want = ra.compute(bw, sym, strict, uns)
+            got = oa.compute_percentile(pct, bw, sym, strict, uns)
+            assert_bits_equal(got[:4], want[:4], f"percentile {pct} bw={bw} sym={sym}{strict}{uns}")
+
+
+def test_ref_partial_encoding(reference):
+    """compute_partial_encoding (host arithmetic of the libpymo mirror) against the reference's two helper functions."""
+    import ctypes as C
+    from aimet_b200.libpymo import TfEncoding, compute_partial_encoding
+    cases = [(8, dict(delta=0.5, offset=-10.0, bw=8)), (8, dict(delta=0.0123, offset=-128.0, bw=8)),
+             (4, dict(delta=0.25, offset=0.0, bw=4)), (8, dict(min=-1.0, max=2.0, bw=8)), (8, dict(min=0.0, max=3.3, bw=8)),
+             (16, dict(min=-7.5, max=7.5, bw=16)), (8, dict(min=-2.0, max=-0.5, bw=8))]
+    for bw, fields in cases:
+        for sym, uns, strict in ((0, 0, 0), (1, 0, 0), (1, 1, 0), (1, 0, 1), (1, 1, 1)):
+            e = TfEncoding(**fields)
+            enc5 = np.array([e.min, e.max, e.delta, e.offset, e.bw], np.float64)
+            rc = reference.lib.ref_partial_encoding(bw, enc5.ctypes.data_as(C.POINTER(C.c_double)), sym, uns, strict)
+            assert rc == 0
+            compute_partial_encoding(bw, e, bool(sym), bool(uns), bool(strict))
+            assert_bits_equal(np.array([e.min, e.max, e.delta, e.offset]), enc5[:4], f"{fields} {sym}{uns}{strict}")
+
