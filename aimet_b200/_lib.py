@@ -17,6 +17,8 @@ AQ_F32, AQ_F16, AQ_BF16 = 0, 1, 2
 AQ_V2_OUT_QDQ, AQ_V2_OUT_CODES = 0, 1
 AQ_PDF_SIZE = 512
 AQ_TFE_HIST_MANY = 16
+AQ_V2HIST_MAX_BINS = 4096
+V2HIST_HEAD_BYTES = 16
 
 
 class AqEncoding(C.Structure):
@@ -66,6 +68,11 @@ SIGNATURES = {
     "aq_tfe_search_workspace_bytes": (_i64, []),
     "aq_tfe_search": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _vp]),
     "aq_tfe_percentile_encoding": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _f64, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "aq_v2hist_scratch_bytes": (_i64, []),
+    "aq_v2hist_collect": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp]),
+    "aq_v2hist_merge": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "aq_v2hist_sqnr_workspace_bytes": (_i64, []),
+    "aq_v2hist_sqnr": (_i32, [_vp, _i32, _f64, _i32, _i32, _vp, _i32, _f64, _vp, _vp, _i64, _vp]),
     "aq_tfe_compute_encoding": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i64,
                                        _vp]),
 }

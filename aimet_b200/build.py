@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_DIR = os.path.join(_HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libaimet_b200.so")
-SOURCES = ["capi.cu", "qdq_kernels.cu", "stats_kernels.cu", "tfe_search.cu"]
+SOURCES = ["capi.cu", "qdq_kernels.cu", "stats_kernels.cu", "tfe_search.cu", "v2_hist.cu"]
 HEADERS = ["common.cuh", "encoding_math.cuh", "kernels.h", os.path.join("..", "..", "include", "aimet_b200.h")]
 
 NVCC_FLAGS = [

@@ -426,4 +426,51 @@ int aq_tfe_percentile_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_
                           unsigned_sym, d_out_encoding, (cudaStream_t) stream);
 }
 
+int64_t aq_v2hist_scratch_bytes(void)
+{
+    return v2hist_scratch_bytes();
+}
+
+static inline bool bad_v2hist(const void* d_x, int dtype, int64_t n, int bins, const void* a, const void* b)
+{
+    return n < 0 || (n > 0 && !d_x) || dtype < AQ_F32 || dtype > AQ_BF16 || bins < 1 || bins > AQ_V2HIST_MAX_BINS ||
+           !a || !b || ((uintptr_t) a % 16) || ((uintptr_t) b % 256);
+}
+
+int aq_v2hist_collect(const void* d_x, int dtype, int64_t n, int bins, aq_v2hist_head_t* d_batch, void* d_scratch,
+                      void* stream)
+{
+    if (bad_v2hist(d_x, dtype, n, bins, d_batch, d_scratch))
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_collect(d_x, dtype, n, bins, d_batch, d_scratch, (cudaStream_t) stream);
+}
+
+int aq_v2hist_merge(const void* d_x, int dtype, int64_t n, int bins, aq_v2hist_head_t* d_state,
+                    const aq_v2hist_head_t* d_batch, int state_has_stats, void* d_scratch, float* d_updates,
+                    void* stream)
+{
+    if (bad_v2hist(d_x, dtype, n, bins, d_state, d_scratch) || !d_batch || !d_updates)
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_merge(d_x, dtype, n, bins, d_state, d_batch, state_has_stats, d_scratch, d_updates,
+                        (cudaStream_t) stream);
+}
+
+int64_t aq_v2hist_sqnr_workspace_bytes(void)
+{
+    return v2hist_sqnr_workspace_bytes();
+}
+
+int aq_v2hist_sqnr(const aq_v2hist_head_t* d_stats, int bins, double num_steps, int symmetric, int num_deltas,
+                   const float* d_offsets, int num_offsets, double gamma, float* d_out, void* d_workspace,
+                   int64_t workspace_bytes, void* stream)
+{
+    if (!d_stats || bins < 1 || bins > AQ_V2HIST_MAX_BINS || !(num_steps > 0) || num_deltas < 2 || !d_offsets ||
+        num_offsets < 1 || !d_out)
+        return AQ_ERR_INVALID_ARG;
+    if (!d_workspace || ((uintptr_t) d_workspace % 256) != 0)
+        return AQ_ERR_WORKSPACE;
+    return v2hist_sqnr(d_stats, bins, num_steps, symmetric, num_deltas, d_offsets, num_offsets, gamma, d_out,
+                       d_workspace, workspace_bytes, (cudaStream_t) stream);
+}
+
 }   // extern "C"

@@ -1,0 +1,593 @@
+// aimet_torch v2 histogram statistics and SQNR range search on the device.
+//
+// Follows aimet_torch/v2/quantization/encoding_analyzer.py: _HistogramObserver.collect_stats (:145-182), merge_stats
+// (:212-262), _create_bin_edges (:194-203), _get_bin_num (:205-208) and SqnrEncodingAnalyzer (:577-725).  That code is
+// a sequence of float32 tensor operations; every operation here is the same IEEE float32 operation in the same order
+// (explicit round-to-nearest intrinsics, no contraction), so histograms, bin edges, candidates and the chosen
+// (delta, offset) come out with the reference's bits.  Two things are decided outside that file:
+//   * torch.histc.  The bin rule of the installed CPU operator was derived by experiment (values on, just below and
+//     just above every boundary): elements outside [lo, hi] and NaN are ignored, an element goes to bin
+//     min(bins - 1, floor(fl(fl((x - lo) * bins) / (hi - lo)))), and equal bounds are replaced by (lo - 1, hi + 1).
+//     tests/golden/histc_rule.npz holds the boundary-value fixtures this rule is locked to.
+//   * the reduction order of torch.sum over the bins of a candidate's noise, which torch does not specify.  The
+//     float32 terms are the reference's; they are accumulated in double and rounded to float32 once, so only
+//     candidates whose noise agrees to the last float32 bit can be ordered differently.
+#include <float.h>
+#include <limits.h>
+#include <math.h>
+#include <stddef.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace aq
+{
+
+constexpr int kV2HistThreads  = 256;
+constexpr int kV2HistMaxParts = 1024;
+constexpr float kEps32        = 1.1920928955078125e-07f;   // torch.finfo(torch.float32).eps
+
+// Scratch of one collect / merge sequence (device memory, caller-owned):
+//   uint32 counts[AQ_V2HIST_MAX_BINS + 2]   bins, then "below lo", then "above hi"
+//   float2 partials[kV2HistMaxParts]        per-CTA finite (min, max)
+//   float  plan[8]                          lo, hi, batch_min, batch_max, any_finite, pad...
+struct V2HistScratch
+{
+    uint32_t counts[AQ_V2HIST_MAX_BINS + 2];
+    uint32_t pad[2];
+    float2 partials[kV2HistMaxParts];
+    float plan[8];
+};
+
+int64_t v2hist_scratch_bytes()
+{
+    return (int64_t) ((sizeof(V2HistScratch) + 255) / 256 * 256);
+}
+
+__device__ __forceinline__ float* v2h_hist(aq_v2hist_head_t* s)
+{
+    return reinterpret_cast<float*>(s + 1);
+}
+__device__ __forceinline__ float* v2h_edges(aq_v2hist_head_t* s, int nb)
+{
+    return reinterpret_cast<float*>(s + 1) + nb;
+}
+
+// ---- pass 1: min / max over the finite elements -----------------------------------------------------------------
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kV2HistThreads) v2h_finite_minmax_kernel(const T* __restrict__ x, int64_t n,
+                                                                           float2* __restrict__ partials)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    float mn = INFINITY, mx = -INFINITY;
+    auto take = [&](float f) {
+        if (fabsf(f) <= FLT_MAX)   // false for NaN and +-Inf
+        {
+            mn = fminf(mn, f);
+            mx = fmaxf(mx, f);
+        }
+    };
+    const int64_t npack  = n / VEC;
+    const int64_t stride = (int64_t) gridDim.x * kV2HistThreads;
+    for (int64_t p = (int64_t) blockIdx.x * kV2HistThreads + threadIdx.x; p < npack; p += stride)
+    {
+        const Pack<T, VEC> v = load_pack<T, VEC>(x + p * VEC);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+            take(to_f32<T>(v.v[e]));
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * VEC))
+        take(to_f32<T>(x[npack * VEC + threadIdx.x]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+    {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    __shared__ float s_mn[kV2HistThreads / 32], s_mx[kV2HistThreads / 32];
+    if ((threadIdx.x & 31) == 0)
+        s_mn[threadIdx.x >> 5] = mn, s_mx[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        for (int w = 1; w < kV2HistThreads / 32; ++w)
+            mn = fminf(mn, s_mn[w]), mx = fmaxf(mx, s_mx[w]);
+        partials[blockIdx.x] = make_float2(mn, mx);
+    }
+}
+
+// ---- plan: fold the partials, decide the range the histogram pass uses, clear the counters -------------------------
+// merge = 0: the batch alone (collect_stats): range = first and last bin edge of _create_bin_edges(min, max).
+// merge = 1: the widened range of merge_stats: [min(batch, state), max(batch, state)].
+__global__ void __launch_bounds__(kV2HistThreads) v2h_plan_kernel(V2HistScratch* __restrict__ sc, int nparts, int nb,
+                                                                  int merge, const aq_v2hist_head_t* __restrict__ state)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    float mn = INFINITY, mx = -INFINITY;
+    for (int i = threadIdx.x; i < nparts; i += kV2HistThreads)
+    {
+        mn = fminf(mn, sc->partials[i].x);
+        mx = fmaxf(mx, sc->partials[i].y);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+    {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    __shared__ float s_mn[kV2HistThreads / 32], s_mx[kV2HistThreads / 32];
+    if ((threadIdx.x & 31) == 0)
+        s_mn[threadIdx.x >> 5] = mn, s_mx[threadIdx.x >> 5] = mx;
+    for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
+        sc->counts[i] = 0;
+    __syncthreads();
+    if (threadIdx.x != 0)
+        return;
+    for (int w = 1; w < kV2HistThreads / 32; ++w)
+        mn = fminf(mn, s_mn[w]), mx = fmaxf(mx, s_mx[w]);
+    const bool any = mn <= mx;
+    float lo, hi;
+    if (!any)
+    {
+        lo = 0.0f, hi = 1.0f;   // nothing finite: the caller is told through any_finite; counters stay meaningless
+        mn = mx = 0.0f;
+    }
+    else if (!merge)
+    {
+        float a = mn, b = mx;
+        if (a == b)
+            a = __fsub_rn(a, 0.5f), b = __fadd_rn(b, 0.5f);
+        const float step = __fdiv_rn(__fsub_rn(b, a), (float) nb);
+        lo               = __fadd_rn(__fmul_rn(0.0f, step), a);
+        hi               = __fadd_rn(__fmul_rn((float) nb, step), a);
+    }
+    else
+    {
+        // Python min(new, cur) / max(new, cur): the second argument wins only when it is strictly smaller / larger
+        lo = (state->min < mn) ? state->min : mn;
+        hi = (state->max > mx) ? state->max : mx;
+    }
+    sc->plan[0] = lo, sc->plan[1] = hi, sc->plan[2] = mn, sc->plan[3] = mx, sc->plan[4] = any ? 1.0f : 0.0f;
+}
+
+// ---- pass 2: counts with the torch.histc bin rule, plus the elements below lo and above hi ------------------------
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __restrict__ x, int64_t n,
+                                                                   V2HistScratch* __restrict__ sc, int nb)
+{
+    pdl_launch_dependents();
+    extern __shared__ uint32_t s_cnt[];   // nb + 2
+    for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
+        s_cnt[i] = 0;
+    pdl_wait();
+    float lo = sc->plan[0], hi = sc->plan[1];
+    const float cmp_lo = lo, cmp_hi = hi;
+    if (lo == hi)
+        lo = __fsub_rn(lo, 1.0f), hi = __fadd_rn(hi, 1.0f);   // torch.histc's own rule for equal bounds
+    const float width = __fsub_rn(hi, lo);
+    const float nbf   = (float) nb;
+    __syncthreads();
+    auto take = [&](float f) {
+        if (f >= lo && f <= hi)
+        {
+            int b = (int) floorf(__fdiv_rn(__fmul_rn(__fsub_rn(f, lo), nbf), width));
+            b     = b < nb - 1 ? b : nb - 1;
+            atomicAdd(&s_cnt[b], 1u);
+        }
+        if (f < cmp_lo)
+            atomicAdd(&s_cnt[nb], 1u);
+        else if (f > cmp_hi)
+            atomicAdd(&s_cnt[nb + 1], 1u);
+    };
+    const int64_t npack  = n / VEC;
+    const int64_t stride = (int64_t) gridDim.x * kV2HistThreads;
+    for (int64_t p = (int64_t) blockIdx.x * kV2HistThreads + threadIdx.x; p < npack; p += stride)
+    {
+        const Pack<T, VEC> v = load_pack<T, VEC>(x + p * VEC);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+            take(to_f32<T>(v.v[e]));
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * VEC))
+        take(to_f32<T>(x[npack * VEC + threadIdx.x]));
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
+        if (s_cnt[i])
+            atomicAdd(&sc->counts[i], s_cnt[i]);
+}
+
+// _create_bin_edges(min, max): arange(0, bins + 1) * step + min with step = (max - min) / bins, after widening equal
+// bounds by 0.5 on either side.
+__device__ __forceinline__ void v2h_write_edges(float mn, float mx, int nb, float* __restrict__ edges)
+{
+    if (mx == mn)
+        mn = __fsub_rn(mn, 0.5f), mx = __fadd_rn(mx, 0.5f);
+    const float step = __fdiv_rn(__fsub_rn(mx, mn), (float) nb);
+    for (int i = threadIdx.x; i <= nb; i += blockDim.x)
+        edges[i] = __fadd_rn(__fmul_rn((float) i, step), mn);
+}
+
+// ---- collect_stats: the batch's own _Histogram ---------------------------------------------------------------------
+__global__ void __launch_bounds__(kV2HistThreads) v2h_finish_collect_kernel(const V2HistScratch* __restrict__ sc, int nb,
+                                                                            aq_v2hist_head_t* __restrict__ out)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    float* hist = v2h_hist(out);
+    for (int i = threadIdx.x; i < nb; i += kV2HistThreads)
+    {
+        float h = (float) sc->counts[i];
+        if (i == 0)
+            h = __fadd_rn(h, (float) sc->counts[nb]);          // histogram[0]  += sum(x < bin_edges[0])
+        if (i == nb - 1)
+            h = __fadd_rn(h, (float) sc->counts[nb + 1]);      // histogram[-1] += sum(x > bin_edges[-1])
+        hist[i] = h;
+    }
+    v2h_write_edges(sc->plan[2], sc->plan[3], nb, v2h_edges(out, nb));
+    if (threadIdx.x == 0)
+    {
+        out->min = sc->plan[2], out->max = sc->plan[3];
+        out->initialized = 1;
+        out->error       = sc->plan[4] != 0.0f ? 0 : 1;
+    }
+}
+
+// torch.minimum: NaN wins
+__device__ __forceinline__ float torch_minimum(float a, float b)
+{
+    return (a != a || b != b) ? NAN : (a < b ? a : b);
+}
+__device__ __forceinline__ int v2h_bin_num(float width, float cur_min, float data, int nb)
+{
+    // _get_bin_num: ((data - curr_min) / bin_width).to(int32) clipped to bins - 1
+    const float idx = __fdiv_rn(__fsub_rn(data, cur_min), width);
+    int b;
+    if (!(idx > -2147483648.0f && idx < 2147483648.0f))
+        b = INT_MIN;   // what the x86 float->int32 conversion gives for NaN and out-of-range values
+    else
+        b = (int) idx;
+    return b < nb - 1 ? b : nb - 1;
+}
+
+// ---- merge_stats: state <- state re-binned to the widened range + the batch counted at that range -----------------
+// The re-binning is two sequential scatter loops over the bins in the reference (float additions whose order matters
+// once counts pass 2^24): one thread walks them in the same order; the rest is element-wise.
+__global__ void __launch_bounds__(kV2HistThreads) v2h_merge_kernel(const V2HistScratch* __restrict__ sc, int nb,
+                                                                   aq_v2hist_head_t* __restrict__ state,
+                                                                   float* __restrict__ updates /* nb floats */)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    float* hist      = v2h_hist(state);
+    const float umin = sc->plan[0], umax = sc->plan[1];
+    const float cmin = state->min, cmax = state->max;
+    const bool same  = (umin == cmin) && (umax == cmax);
+    if (same)
+    {
+        for (int i = threadIdx.x; i < nb; i += kV2HistThreads)
+            updates[i] = hist[i];
+    }
+    else
+    {
+        for (int i = threadIdx.x; i < nb; i += kV2HistThreads)
+            updates[i] = 0.0f;
+    }
+    __syncthreads();
+    if (!same && threadIdx.x == 0)
+    {
+        const float dest_w = __fdiv_rn(__fsub_rn(umax, umin), (float) nb);
+        const float src_w  = __fdiv_rn(__fsub_rn(cmax, cmin), (float) nb);
+        for (int i = 0; i < nb; ++i)
+        {
+            const float src_start = __fadd_rn(cmin, __fmul_rn(src_w, (float) i));
+            const int dest        = v2h_bin_num(dest_w, umin, src_start, nb);
+            const float dest_end  = __fadd_rn(umin, __fmul_rn(dest_w, (float) (dest + 1)));
+            const float split     = rintf(__fmul_rn(__fdiv_rn(__fsub_rn(dest_end, src_start), src_w), hist[i]));
+            const float upd       = torch_minimum(split, hist[i]);
+            if (dest >= 0)
+                updates[dest] = __fadd_rn(updates[dest], upd);
+        }
+        for (int i = 0; i < nb; ++i)
+        {
+            // recomputed rather than stored: the same operations give the same values
+            const float src_start = __fadd_rn(cmin, __fmul_rn(src_w, (float) i));
+            const int dest        = v2h_bin_num(dest_w, umin, src_start, nb);
+            const float dest_end  = __fadd_rn(umin, __fmul_rn(dest_w, (float) (dest + 1)));
+            const float split     = rintf(__fmul_rn(__fdiv_rn(__fsub_rn(dest_end, src_start), src_w), hist[i]));
+            const float upd       = torch_minimum(split, hist[i]);
+            if (upd < hist[i])
+            {
+                const int other = v2h_bin_num(dest_w, umin, __fadd_rn(src_start, dest_w), nb);
+                if (other >= 0)
+                    updates[other] = __fadd_rn(updates[other], __fsub_rn(hist[i], upd));
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb; i += kV2HistThreads)
+    {
+        float h = __fadd_rn((float) sc->counts[i], updates[i]);
+        if (i == 0)
+            h = __fadd_rn(h, (float) sc->counts[nb]);        // expanded[0]  += sum(x == -inf)
+        if (i == nb - 1)
+            h = __fadd_rn(h, (float) sc->counts[nb + 1]);    // expanded[-1] += sum(x == +inf)
+        hist[i] = h;
+    }
+    v2h_write_edges(umin, umax, nb, v2h_edges(state, nb));
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        state->min = umin, state->max = umax;
+        if (sc->plan[4] == 0.0f)
+            state->error = 1;
+    }
+}
+
+__global__ void __launch_bounds__(kV2HistThreads) v2h_copy_kernel(const aq_v2hist_head_t* __restrict__ src, int nb,
+                                                                  aq_v2hist_head_t* __restrict__ dst)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* s = reinterpret_cast<const float*>(src + 1);
+    float* d       = reinterpret_cast<float*>(dst + 1);
+    for (int i = threadIdx.x; i < 2 * nb + 1; i += kV2HistThreads)
+        d[i] = s[i];
+    if (threadIdx.x == 0)
+        *dst = *src;
+}
+
+// ---- launchers ------------------------------------------------------------------------------------------------------
+template <typename T>
+static int v2h_passes(const T* x, int64_t n, int nb, int merge, const aq_v2hist_head_t* state, V2HistScratch* sc,
+                      cudaStream_t st)
+{
+    const int vec      = pick_vec<T>(x, nullptr, nullptr, 0);
+    int64_t blocks     = (n + (int64_t) kV2HistThreads * vec * 4 - 1) / ((int64_t) kV2HistThreads * vec * 4);
+    const int64_t cap  = (int64_t) kNumSMs * 6;
+    blocks             = blocks > cap ? cap : (blocks < 1 ? 1 : blocks);
+    const int nparts   = (int) (blocks < kV2HistMaxParts ? blocks : kV2HistMaxParts);
+    const size_t smem  = (size_t) (nb + 2) * sizeof(uint32_t);
+#define AQ_V2H(V)                                                                                                    \
+    launch_pdl(v2h_finite_minmax_kernel<T, V>, (unsigned) nparts, kV2HistThreads, 0, st, x, n, sc->partials);        \
+    note_launch();                                                                                                   \
+    launch_pdl(v2h_plan_kernel, 1, kV2HistThreads, 0, st, sc, nparts, nb, merge, state);                             \
+    note_launch();                                                                                                   \
+    launch_pdl(v2h_count_kernel<T, V>, (unsigned) blocks, kV2HistThreads, smem, st, x, n, sc, nb);                   \
+    note_launch();
+    if (vec >= 4 && sizeof(T) == 4)
+    {
+        AQ_V2H(4)
+    }
+    else if (vec >= 8)
+    {
+        AQ_V2H((sizeof(T) == 2 ? 8 : 4))
+    }
+    else
+    {
+        AQ_V2H(1)
+    }
+#undef AQ_V2H
+    return check_launch();
+}
+
+static int v2h_passes_any(const void* x, int dtype, int64_t n, int nb, int merge, const aq_v2hist_head_t* state,
+                          V2HistScratch* sc, cudaStream_t st)
+{
+    switch (dtype)
+    {
+    case AQ_F32: return v2h_passes<float>((const float*) x, n, nb, merge, state, sc, st);
+    case AQ_F16: return v2h_passes<__half>((const __half*) x, n, nb, merge, state, sc, st);
+    case AQ_BF16: return v2h_passes<__nv_bfloat16>((const __nv_bfloat16*) x, n, nb, merge, state, sc, st);
+    default: return AQ_ERR_INVALID_ARG;
+    }
+}
+
+int v2hist_collect(const void* x, int dtype, int64_t n, int nb, aq_v2hist_head_t* batch, void* scratch, cudaStream_t st)
+{
+    V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
+    int rc            = v2h_passes_any(x, dtype, n, nb, 0, nullptr, sc, st);
+    if (rc != AQ_OK)
+        return rc;
+    launch_pdl(v2h_finish_collect_kernel, 1, kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb, batch);
+    note_launch();
+    return check_launch();
+}
+
+int v2hist_merge(const void* x, int dtype, int64_t n, int nb, aq_v2hist_head_t* state, const aq_v2hist_head_t* batch,
+                 int state_has_stats, void* scratch, float* updates, cudaStream_t st)
+{
+    if (!state_has_stats)
+    {
+        // merge_stats on an empty observer adopts the batch's statistics as they are
+        launch_pdl(v2h_copy_kernel, 1, kV2HistThreads, 0, st, batch, nb, state);
+        note_launch();
+        return check_launch();
+    }
+    V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
+    int rc            = v2h_passes_any(x, dtype, n, nb, 1, state, sc, st);
+    if (rc != AQ_OK)
+        return rc;
+    launch_pdl(v2h_merge_kernel, 1, kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb, state, updates);
+    note_launch();
+    return check_launch();
+}
+
+// =================================================================================================
+// SQNR search (SqnrEncodingAnalyzer.compute_encodings_from_stats for one histogram)
+// =================================================================================================
+constexpr int kSqnrWarps = 4;
+
+struct SqnrArgs
+{
+    const aq_v2hist_head_t* stats;
+    int nb;
+    float num_steps;        // float32(num_steps)
+    float min_gap;          // float32(eps * num_steps)
+    int symmetric;
+    int num_deltas;
+    int num_offsets;        // entries of `offsets` (asymmetric: the fixed grid; the observed offset is appended)
+    const float* offsets;   // device; symmetric: one entry, (-num_steps) // 2
+    float gamma;
+    float* noise;           // [candidates] workspace
+    unsigned int* ticket;   // workspace, zero on entry, left zero
+    float* out;             // {min, max}
+};
+
+__device__ __forceinline__ void sqnr_candidate(const SqnrArgs& a, float min_v, float max_v, int cand, float& delta,
+                                               float& offset)
+{
+    const float ns = a.num_steps;
+    if (a.symmetric)
+    {
+        // _pick_test_candidates_symmetric (:639-652)
+        const float m         = fmaxf(max_v, -min_v);
+        const float max_delta = __fdiv_rn(__fmul_rn(2.0f, m), ns);
+        const float k         = (float) (cand + 1);
+        delta                 = fmaxf(__fdiv_rn(__fmul_rn(max_delta, k), (float) (a.num_deltas - 1)), kEps32);
+        offset                = a.offsets[0];
+        return;
+    }
+    // _pick_test_candidates_asymmetric (:613-637) + _clamp_delta_offset_values (:654-672)
+    const int per_delta   = a.num_offsets + 1;
+    const int di          = cand / per_delta;
+    const int oi          = cand - di * per_delta;
+    const float max_delta = __fdiv_rn(__fsub_rn(max_v, min_v), ns);
+    const float obs_off   = rintf(__fdiv_rn(min_v, max_delta));
+    const float obs_min   = __fmul_rn(max_delta, obs_off);
+    const float obs_max   = __fadd_rn(obs_min, __fmul_rn(max_delta, ns));
+    const float td        = __fdiv_rn(__fmul_rn(max_delta, (float) (di + 1)), (float) (a.num_deltas - 1));
+    const float to        = oi < a.num_offsets ? a.offsets[oi] : obs_off;
+    float t_min           = __fmul_rn(td, to);
+    float t_max           = __fadd_rn(t_min, __fmul_rn(td, ns));
+    t_min                 = fmaxf(obs_min, t_min);   // torch.max / torch.min: finite operands here
+    t_max                 = fminf(obs_max, t_max);
+    delta                 = fmaxf(__fdiv_rn(__fsub_rn(t_max, t_min), ns), kEps32);
+    offset                = rintf(__fdiv_rn(t_min, delta));
+}
+
+__global__ void __launch_bounds__(kSqnrWarps * 32) v2h_sqnr_kernel(SqnrArgs a)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_delta  = a.symmetric ? 1 : a.num_offsets + 1;
+    const int candidates = a.num_deltas * per_delta;
+    const int cand       = blockIdx.x * kSqnrWarps + warp;
+    __shared__ bool s_last;
+    const aq_v2hist_head_t* st = a.stats;
+    const float* hist  = reinterpret_cast<const float*>(st + 1);
+    const float* edges = hist + a.nb;
+    // _pick_test_candidates (:602-611)
+    float min_v = fminf(st->min, 0.0f);
+    float max_v = fmaxf(st->max, 0.0f);
+    max_v       = fmaxf(max_v, __fadd_rn(min_v, a.min_gap));
+    if (cand < candidates)
+    {
+        float delta, offset;
+        sqnr_candidate(a, min_v, max_v, cand, delta, offset);
+        // _estimate_clip_and_quant_noise (:688-725)
+        const float hd   = __fsub_rn(edges[1], edges[0]);
+        const float mid0 = __fadd_rn(edges[0], __fdiv_rn(hd, 2.0f));
+        double sum       = 0.0;
+        for (int i = lane; i < a.nb; i += 32)
+        {
+            const float mid = __fadd_rn(mid0, __fmul_rn(hd, (float) i));
+            float q         = rintf(__fsub_rn(__fdiv_rn(mid, delta), offset));
+            const bool clip = (q < 0.0f) || (q > a.num_steps);
+            if (q == q)   // torch.clamp keeps NaN
+                q = fminf(fmaxf(q, 0.0f), a.num_steps);
+            const float qdq = __fmul_rn(__fadd_rn(q, offset), delta);
+            const float d   = __fsub_rn(qdq, mid);
+            float err       = __fmul_rn(__fmul_rn(d, d), hist[i]);
+            if (a.gamma != 1.0f && clip)
+                err = __fmul_rn(err, a.gamma);
+            sum += (double) err;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0)
+            a.noise[cand] = (float) sum;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        __threadfence();
+        const unsigned int t = atomicAdd(a.ticket, 1u);
+        s_last               = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last || warp != 0)
+        return;
+    __threadfence();
+    // torch.min over the flattened (delta, offset) grid: the first smallest value
+    float best = INFINITY;
+    int best_i = INT_MAX;
+    bool nan   = false;
+    for (int i = lane; i < candidates; i += 32)
+    {
+        const float v = __ldcg(&a.noise[i]);
+        if (v != v)
+        {
+            if (!nan || i < best_i)
+                best_i = nan ? min(best_i, i) : i;
+            nan = true;
+        }
+        else if (!nan && (v < best || (v == best && i < best_i)))
+        {
+            best   = v;
+            best_i = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+    {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi   = __shfl_xor_sync(0xffffffffu, best_i, o);
+        const int on   = __shfl_xor_sync(0xffffffffu, (int) nan, o);
+        if (on && (!nan || oi < best_i))
+            nan = true, best_i = oi;
+        else if (!on && !nan && (ov < best || (ov == best && oi < best_i)))
+            best = ov, best_i = oi;
+    }
+    if (lane == 0)
+    {
+        float delta = 0.0f, offset = 0.0f;
+        if (best_i != INT_MAX)
+            sqnr_candidate(a, min_v, max_v, best_i, delta, offset);
+        const float mn = __fmul_rn(offset, delta);
+        a.out[0]       = mn;
+        a.out[1]       = __fadd_rn(mn, __fmul_rn(a.num_steps, delta));
+        *a.ticket      = 0;
+    }
+}
+
+int64_t v2hist_sqnr_workspace_bytes()
+{
+    return 256 + 4096 * (int64_t) sizeof(float);
+}
+
+int v2hist_sqnr(const aq_v2hist_head_t* stats, int nb, double num_steps, int symmetric, int num_deltas,
+                const float* offsets, int num_offsets, double gamma, float* out, void* ws, int64_t ws_bytes,
+                cudaStream_t st)
+{
+    SqnrArgs a;
+    a.stats = stats, a.nb = nb, a.num_steps = (float) num_steps;
+    a.min_gap   = (float) ((double) kEps32 * num_steps);
+    a.symmetric = symmetric, a.num_deltas = num_deltas, a.num_offsets = num_offsets, a.offsets = offsets;
+    a.gamma     = (float) gamma;
+    a.ticket    = static_cast<unsigned int*>(ws);
+    a.noise     = reinterpret_cast<float*>(static_cast<char*>(ws) + 256);
+    a.out       = out;
+    const int candidates = num_deltas * (symmetric ? 1 : num_offsets + 1);
+    if (candidates < 1 || candidates > 4096 || ws_bytes < v2hist_sqnr_workspace_bytes())
+        return candidates > 4096 ? AQ_ERR_TOO_LARGE : AQ_ERR_WORKSPACE;
+    const int grid = (candidates + kSqnrWarps - 1) / kSqnrWarps;
+    launch_pdl(v2h_sqnr_kernel, (unsigned) grid, kSqnrWarps * 32, 0, st, a);
+    note_launch();
+    return check_launch();
+}
+
+}   // namespace aq

@@ -213,3 +213,197 @@ class TfEnhancedEncodingAnalyzer(EncodingAnalyzer):
 
     def compute_encodings_from_stats(self, stats, num_steps, is_symmetric):
         raise RuntimeError("aimet_b200: TF-Enhanced statistics are device-resident; use compute_encodings()")
+
+
+# ---------------------------------------------------------------------------------------------------
+# v2 histogram statistics + SQNR search
+# ---------------------------------------------------------------------------------------------------
+from .. import _lib   # noqa: E402
+from .._lib import check, lib   # noqa: E402
+
+_DT = {torch.float32: _lib.AQ_F32, torch.float16: _lib.AQ_F16, torch.bfloat16: _lib.AQ_BF16}
+
+
+@dataclass
+class _Histogram:
+    """Host view of one histogram (reference: _Histogram, encoding_analyzer.py:57-62).  The tensors are views of the
+    device-resident statistics block; reading them synchronises like any device tensor."""
+    histogram: Optional[torch.Tensor] = None
+    bin_edges: Optional[torch.Tensor] = None
+    min: Optional[torch.Tensor] = None
+    max: Optional[torch.Tensor] = None
+    _block: Optional[torch.Tensor] = None   # the raw statistics block (header + histogram + edges)
+
+    @staticmethod
+    def of_block(block: torch.Tensor, num_bins: int, dtype: torch.dtype) -> "_Histogram":
+        f = block.view(torch.float32)
+        hist = f[4:4 + num_bins]
+        edges = f[4 + num_bins:4 + 2 * num_bins + 1]
+        return _Histogram(hist, edges, f[0].to(dtype), f[1].to(dtype), block)
+
+
+def _new_block(num_bins: int, device) -> torch.Tensor:
+    words = (_lib.V2HIST_HEAD_BYTES + (2 * num_bins + 1) * 4 + 3) // 4
+    return torch.zeros(words, dtype=torch.int32, device=device)
+
+
+class _HistogramObserver:
+    """Per-encoding histograms of everything seen so far (reference: _HistogramObserver, encoding_analyzer.py:131-270).
+
+    ``collect_stats`` gives the batch's own histograms (finite min / max, ``torch.histc`` counts over that range,
+    infinities folded into the end bins); ``merge_stats`` widens the running histograms' range when needed, re-bins
+    the old counts with the reference's split-and-round rule and counts the batch again at the widened range.  All of
+    it runs on the device, three launches per pass over the data, no host synchronisation.  With several histograms
+    (per-channel observers) the channels are processed one after the other, like the reference's Python loop.
+    """
+
+    def __init__(self, shape: tuple, num_bins: int):
+        if isinstance(shape, int):
+            shape = (shape,)
+        self.shape = tuple(shape)
+        self.num_bins = int(num_bins)
+        if self.num_bins > _lib.AQ_V2HIST_MAX_BINS:
+            raise ValueError(f"aimet_b200: at most {_lib.AQ_V2HIST_MAX_BINS} histogram bins are supported")
+        self.num_histograms = int(math.prod(self.shape))
+        self._state = None          # list of device blocks, one per histogram, once statistics exist
+        self._dtype = torch.float32
+        self._scratch = None
+        self._updates = None
+
+    # ---- helpers ---------------------------------------------------------------------------------------------
+    def _buffers(self, device):
+        if self._scratch is None or self._scratch.device != device:
+            self._scratch = torch.empty(int(lib.aq_v2hist_scratch_bytes()), dtype=torch.uint8, device=device)
+            self._updates = torch.empty(self.num_bins, dtype=torch.float32, device=device)
+        return self._scratch, self._updates
+
+    def _slices(self, input_tensor: torch.Tensor):
+        """The part of the input that belongs to each histogram, dense, in histogram order."""
+        x = input_tensor.detach()
+        if not x.is_cuda:
+            raise RuntimeError("aimet_b200: statistics are collected on the GPU only (no CPU path exists)")
+        if x.dtype not in _DT:
+            raise RuntimeError(f"aimet_b200: unsupported dtype {x.dtype}")
+        enc_shape = self.shape
+        if len(enc_shape) > x.dim() or any(s not in (1, t) for s, t in zip(enc_shape[::-1], tuple(x.shape)[::-1])):
+            raise RuntimeError(f"Shape {self.shape} is incompatible with input of shape {tuple(x.shape)}")
+        if self.num_histograms == 1:
+            return [x if x.is_contiguous() else x.contiguous()]
+        padded = (1,) * (x.dim() - len(enc_shape)) + tuple(enc_shape)
+        axes = [a for a, d in enumerate(padded) if d != 1]
+        rest = [a for a in range(x.dim()) if a not in axes]
+        moved = x.permute(axes + rest).reshape(self.num_histograms, -1)
+        return [moved[i].contiguous() for i in range(self.num_histograms)]
+
+    # ---- observer interface ----------------------------------------------------------------------------------
+    @torch.no_grad()
+    def collect_stats(self, input_tensor: torch.Tensor):
+        parts = self._slices(input_tensor)
+        scratch, _ = self._buffers(input_tensor.device)
+        stream = torch.cuda.current_stream(input_tensor.device).cuda_stream
+        out = []
+        with ops._on(input_tensor):
+            for part in parts:
+                block = _new_block(self.num_bins, part.device)
+                check(lib.aq_v2hist_collect(part.data_ptr(), _DT[part.dtype], part.numel(), self.num_bins,
+                                            block.data_ptr(), scratch.data_ptr(), stream), "aq_v2hist_collect")
+                h = _Histogram.of_block(block, self.num_bins, input_tensor.dtype)
+                h._part = part
+                out.append(h)
+        return out
+
+    @torch.no_grad()
+    def merge_stats(self, new_stats_list, input_tensor: torch.Tensor):
+        scratch, updates = self._buffers(input_tensor.device)
+        stream = torch.cuda.current_stream(input_tensor.device).cuda_stream
+        first = self._state is None
+        if first:
+            self._state = [_new_block(self.num_bins, input_tensor.device) for _ in range(self.num_histograms)]
+            self._dtype = input_tensor.dtype
+        parts = [getattr(h, "_part", None) for h in new_stats_list]
+        if any(p is None for p in parts):
+            parts = self._slices(input_tensor)
+        with ops._on(input_tensor):
+            for block, new, part in zip(self._state, new_stats_list, parts):
+                check(lib.aq_v2hist_merge(part.data_ptr(), _DT[part.dtype], part.numel(), self.num_bins,
+                                          block.data_ptr(), new._block.data_ptr(), 0 if first else 1,
+                                          scratch.data_ptr(), updates.data_ptr(), stream), "aq_v2hist_merge")
+        for h in new_stats_list:
+            h._part = None   # the batch need not outlive the update
+
+    def reset_stats(self):
+        self._state = None
+
+    def get_stats(self):
+        if self._state is None:
+            return [_Histogram() for _ in range(self.num_histograms)]
+        return [_Histogram.of_block(b, self.num_bins, self._dtype) for b in self._state]
+
+    @property
+    def stats(self):
+        return self.get_stats()
+
+
+class SqnrEncodingAnalyzer(EncodingAnalyzer):
+    """SQNR calibration on the v2 histograms (reference: SqnrEncodingAnalyzer, encoding_analyzer.py:522-725): same
+    constructor arguments, same candidate grids (17 deltas x 21 offsets + the observed offset, or 101 deltas when
+    symmetric), same clipping-weighted noise estimate, first candidate of least noise.  One warp per candidate."""
+
+    def __init__(self, shape: tuple, num_bins: int = 2048, *, asymmetric_delta_candidates=17,
+                 symmetric_delta_candidates=101, offset_candidates=21, max_parallelism=64, gamma=3.0):
+        if num_bins <= 0:
+            raise ValueError('Number of bins cannot be less than or equal to 0.')
+        super().__init__(_HistogramObserver(shape=shape, num_bins=num_bins))
+        self.asym_delta_candidates = asymmetric_delta_candidates
+        self.sym_delta_candidates = symmetric_delta_candidates
+        self.num_offset_candidates = offset_candidates
+        self.gamma = gamma
+        self.max_parallelism = max_parallelism
+        self._offsets = {}
+        self._ws = None
+
+    @torch.no_grad()
+    def update_stats(self, input_tensor: torch.Tensor):
+        new_stats = self.observer.collect_stats(input_tensor)
+        self.observer.merge_stats(new_stats, input_tensor)
+        return new_stats
+
+    def compute_dynamic_encodings(self, input_tensor, num_steps, is_symmetric):
+        return self.compute_encodings_from_stats(self.observer.collect_stats(input_tensor), num_steps, is_symmetric)
+
+    def _offset_grid(self, num_steps, is_symmetric: bool, device) -> torch.Tensor:
+        """The offsets the search walks: host arithmetic of a handful of values, exactly the reference's expressions
+        (encoding_analyzer.py:629-632, :644), cached per (num_steps, symmetric, device)."""
+        key = (num_steps, is_symmetric, str(device))
+        if key not in self._offsets:
+            if is_symmetric:
+                t = torch.full((1,), (-num_steps) // 2, dtype=torch.float32)
+            else:
+                num_offsets = min(num_steps + 2, self.num_offset_candidates)
+                step = num_steps / (num_offsets - 2)   # 2 fewer: the observed offset is added on the device
+                t = torch.round(torch.arange(start=-num_steps, end=step, step=step, dtype=torch.float32))
+            self._offsets[key] = t.to(device)
+        return self._offsets[key]
+
+    @torch.no_grad()
+    def compute_encodings_from_stats(self, stats, num_steps: int, is_symmetric: bool) \
+            -> Tuple[torch.Tensor, torch.Tensor]:
+        if stats[0].histogram is None:
+            raise StatisticsNotFoundError('No statistics present to compute encodings.')
+        if num_steps <= 0:
+            raise ValueError('The number of quantization bins cannot be less than or equal to 0.')
+        device = stats[0]._block.device
+        offsets = self._offset_grid(num_steps, bool(is_symmetric), device)
+        if self._ws is None or self._ws.device != device:
+            self._ws = torch.zeros(int(lib.aq_v2hist_sqnr_workspace_bytes()), dtype=torch.uint8, device=device)
+        out = torch.empty((len(stats), 2), dtype=torch.float32, device=device)
+        num_deltas = self.sym_delta_candidates if is_symmetric else self.asym_delta_candidates
+        stream = torch.cuda.current_stream(device).cuda_stream
+        with ops._on(out):
+            for i, st in enumerate(stats):
+                check(lib.aq_v2hist_sqnr(st._block.data_ptr(), self.observer.num_bins, float(num_steps),
+                                         int(bool(is_symmetric)), int(num_deltas), offsets.data_ptr(), offsets.numel(),
+                                         float(self.gamma), out[i].data_ptr(), self._ws.data_ptr(), self._ws.numel(),
+                                         stream), "aq_v2hist_sqnr")
+        dtype = stats[0].min.dtype
+        return out[:, 0].to(dtype).view(self.observer.shape), out[:, 1].to(dtype).view(self.observer.shape)

@@ -32,7 +32,8 @@ def _timed(fn, device) -> float:
     return e0.elapsed_time(e1) * 1e-3
 
 
-def resnet50_case(device, batches: int = 32, batch_size: int = 128) -> Dict:
+def resnet50_case(device, batches: int = 32, batch_size: int = 128,
+                  scheme: str = "post_training_tf_enhanced_libpymo") -> Dict:
     import torchvision
     model = torchvision.models.resnet50(weights=None)
     for m in model.modules():
@@ -45,7 +46,7 @@ def resnet50_case(device, batches: int = 32, batch_size: int = 128) -> Dict:
         g.manual_seed(2000 + b)
         return torch.randn(batch_size, 3, 224, 224, device=device, generator=g)
 
-    sim = QuantizationSimModel(model, batch(0))
+    sim = QuantizationSimModel(model, batch(0), quant_scheme=scheme)
 
     def float_pass():
         with torch.no_grad():
@@ -68,7 +69,7 @@ def resnet50_case(device, batches: int = 32, batch_size: int = 128) -> Dict:
     step()
     t_step = _timed(step, device)
     n = batches * batch_size
-    return {"model_case": "resnet50", "batches": batches, "batch_size": batch_size,
+    return {"model_case": "resnet50", "quant_scheme": scheme, "batches": batches, "batch_size": batch_size,
             "weight_quantizers": len(sim.layers), "activation_quantizers": len(sim.activation_quantizers),
             "compute_encodings_s": t_cal, "calibration_samples_per_s": n / t_cal,
             "float_forward_only_s": t_float, "float_forward_samples_per_s": n / t_float,

@@ -24,7 +24,7 @@ import torch
 import torch.nn.functional as F
 from torch import fx, nn
 
-from .encoding_analyzer import MinMaxEncodingAnalyzer, TfEnhancedEncodingAnalyzer
+from .encoding_analyzer import MinMaxEncodingAnalyzer, SqnrEncodingAnalyzer, TfEnhancedEncodingAnalyzer
 from .quantizer import QuantizeDequantize
 
 __all__ = ["QuantizationSimModel", "QuantizedLayer", "fold_batch_norms"]
@@ -101,14 +101,19 @@ def _is_relu(node: fx.Node, mods: Dict[str, nn.Module]) -> bool:
 class QuantizationSimModel:
     """``sim = QuantizationSimModel(model, dummy_input); sim.compute_encodings(callback, args); sim.model(x)``.
 
-    quant_scheme: ``"post_training_tf_enhanced"`` (activations: 512-bucket TF-Enhanced, libpymo semantics) or
-    ``"post_training_tf"`` (min/max).  Weights always calibrate by min/max per output channel.
+    quant_scheme, mapped to analyzers as the reference does (aimet_torch/quantsim_config/builder.py:294-309):
+
+    * ``"post_training_tf"``: min/max for parameters and activations;
+    * ``"post_training_tf_enhanced"``: the v2 ``SqnrEncodingAnalyzer`` (histogram + SQNR search) for parameters (one
+      histogram per output channel) and activations;
+    * ``"post_training_tf_enhanced_libpymo"``: not a reference scheme name -- activations get the v1 / libpymo
+      TF-Enhanced analyzer (512-bucket PDF frozen by the first batch) behind the v2 interface, parameters min/max.
     """
 
     def __init__(self, model: nn.Module, dummy_input=None, quant_scheme: str = "post_training_tf_enhanced",
                  default_output_bw: int = 8, default_param_bw: int = 8, per_channel_quantization: bool = True,
                  fold_bn: bool = True):
-        if quant_scheme not in ("post_training_tf_enhanced", "post_training_tf"):
+        if quant_scheme not in ("post_training_tf_enhanced", "post_training_tf", "post_training_tf_enhanced_libpymo"):
             raise ValueError(f"unsupported quant_scheme {quant_scheme!r}")
         self._scheme = quant_scheme
         self._act_bw, self._param_bw = int(default_output_bw), int(default_param_bw)
@@ -123,7 +128,8 @@ class QuantizationSimModel:
             if node.op == "call_module" and isinstance(mods.get(node.target), _LAYERS):
                 layer = mods[node.target]
                 shape = (layer.weight.shape[0],) + (1,) * (layer.weight.dim() - 1) if per_channel_quantization else ()
-                wrapped = QuantizedLayer(layer, QuantizeDequantize(shape, self._param_bw, True))
+                wrapped = QuantizedLayer(layer, QuantizeDequantize(shape, self._param_bw, True,
+                                                                   self._new_analyzer(shape, for_param=True)))
                 self._set_submodule(gm, node.target, wrapped)
                 self.layers[node.target] = wrapped
         mods = dict(gm.named_modules())
@@ -132,7 +138,7 @@ class QuantizationSimModel:
             if not self._wants_output_quantizer(node, mods):
                 continue
             name = "act_q_" + node.name
-            q = QuantizeDequantize((), self._act_bw, False, self._new_analyzer())
+            q = QuantizeDequantize((), self._act_bw, False, self._new_analyzer(()))
             gm.add_submodule(name, q)
             with gm.graph.inserting_after(node):
                 new = gm.graph.call_module(name, (node,))
@@ -147,8 +153,12 @@ class QuantizationSimModel:
             self.model.to(ref.device)
 
     # ---- construction helpers ----------------------------------------------------------------------------------
-    def _new_analyzer(self):
-        return TfEnhancedEncodingAnalyzer(()) if self._scheme == "post_training_tf_enhanced" else MinMaxEncodingAnalyzer(())
+    def _new_analyzer(self, shape, for_param: bool = False):
+        if self._scheme == "post_training_tf_enhanced":
+            return SqnrEncodingAnalyzer(shape)
+        if self._scheme == "post_training_tf_enhanced_libpymo" and not for_param:
+            return TfEnhancedEncodingAnalyzer(shape)
+        return MinMaxEncodingAnalyzer(shape)
 
     @staticmethod
     def _set_submodule(root: nn.Module, target: str, new: nn.Module):

@@ -332,9 +332,12 @@ def run_b200(args):
     if rank == 0 and world == 1 and not args.skip_models:
         from aimet_b200.v2 import model_cases
         models = {}
-        for name, kw in (("resnet50", {"batches": 32, "batch_size": 128}), ("llama_layer", {})):
+        for name, case, kw in (("resnet50", "resnet50", {"batches": 32, "batch_size": 128}),
+                               ("resnet50_v2_sqnr", "resnet50", {"batches": 32, "batch_size": 128,
+                                                                 "scheme": "post_training_tf_enhanced"}),
+                               ("llama_layer", "llama_layer", {})):
             try:
-                models[name] = model_cases.CASES[name](device, **kw)
+                models[name] = model_cases.CASES[case](device, **kw)
             except Exception as e:   # a model case must not take the headline down with it
                 models[name] = {"error": f"{type(e).__name__}: {e}"}
             torch.cuda.empty_cache()

@@ -327,6 +327,56 @@ int aq_tfe_percentile_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_
                                const int32_t* d_stats_updated, double percentile, int bw, int symmetric,
                                int strict_symmetric, int unsigned_symmetric, double* d_out_encoding, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * aimet_torch v2 histogram statistics (_HistogramObserver) and SQNR range search (SqnrEncodingAnalyzer)
+ * ---------------------------------------------------------------------------------------------- */
+
+#define AQ_V2HIST_MAX_BINS 4096 /* the reference's default is 2048 */
+
+/* One histogram of the v2 observer in device memory: this header, then float histogram[bins], then
+ * float bin_edges[bins + 1] -- the fields of _Histogram (aimet_torch/v2/quantization/encoding_analyzer.py:57-62).
+ * Counts are float32 because the reference keeps them in a float32 tensor (torch.histc output). */
+typedef struct
+{
+    float min;           /* smallest finite value seen */
+    float max;           /* largest finite value seen */
+    int32_t initialized; /* 0 = no statistics yet */
+    int32_t error;       /* 1 = a batch held no finite value (the reference raises ValueError for it) */
+} aq_v2hist_head_t;
+
+#define AQ_V2HIST_BYTES(bins) (sizeof(aq_v2hist_head_t) + (size_t) (2 * (bins) + 1) * sizeof(float))
+
+/* Bytes of scratch for aq_v2hist_collect / aq_v2hist_merge (any content; 256-byte aligned). */
+int64_t aq_v2hist_scratch_bytes(void);
+
+/* _HistogramObserver.collect_stats for one histogram (encoding_analyzer.py:145-182): finite min / max of the batch,
+ * bin edges over that range, torch.histc counts (bin rule of the CPU operator: bin = min(bins - 1,
+ * floor(((x - lo) * bins) / (hi - lo))) in float32, elements outside [lo, hi] and NaN ignored), -inf / +inf and
+ * stragglers beyond the last edge folded into the end bins.  d_x: `n` elements of `dtype`, dense.  d_batch receives
+ * the batch's own _Histogram.  Three launches reading d_x twice; no host synchronisation. */
+int aq_v2hist_collect(const void* d_x, int dtype, int64_t n, int bins, aq_v2hist_head_t* d_batch, void* d_scratch,
+                      void* stream);
+
+/* _HistogramObserver.merge_stats for one histogram (encoding_analyzer.py:212-262).  state_has_stats = 0: the state
+ * adopts d_batch.  Otherwise the range grows to cover both, the old counts are re-binned with the reference's
+ * split-and-round rule (sequential float32 additions in the reference's order), and the batch is counted again at the
+ * widened range.  d_updates: bins floats of scratch. */
+int aq_v2hist_merge(const void* d_x, int dtype, int64_t n, int bins, aq_v2hist_head_t* d_state,
+                    const aq_v2hist_head_t* d_batch, int state_has_stats, void* d_scratch, float* d_updates,
+                    void* stream);
+
+/* Bytes of scratch for aq_v2hist_sqnr (zero-filled before first use, 256-byte aligned, left reusable). */
+int64_t aq_v2hist_sqnr_workspace_bytes(void);
+
+/* SqnrEncodingAnalyzer.compute_encodings_from_stats for one histogram (encoding_analyzer.py:577-725): candidate
+ * (delta, offset) pairs -- num_deltas deltas times, when asymmetric, the num_offsets offsets of d_offsets plus the
+ * observed offset, each clamped to the observed range; symmetric: d_offsets holds the single offset
+ * (-num_steps) // 2 --, the clipping / rounding noise of each over the bin mid-points with the clipped bins weighted
+ * by gamma, and the first candidate of least noise.  One warp per candidate.  d_out: {min, max} as float32. */
+int aq_v2hist_sqnr(const aq_v2hist_head_t* d_stats, int bins, double num_steps, int symmetric, int num_deltas,
+                   const float* d_offsets, int num_offsets, double gamma, float* d_out, void* d_workspace,
+                   int64_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,6 +17,12 @@ oracle/_ref exist; the fixtures are committed so that the tests need neither).
                      known-answer vector sets, its block-quantization cases, and the inputs / expected values of its
                      gradient-comparison tests as that file builds them (same seed, same helpers), with the expected
                      values computed on CPU by the reference's plain-autograd modules and by ``torch_builtins``.
+* v2_sqnr.npz      - aimet_torch v2 ``SqnrEncodingAnalyzer`` / ``_HistogramObserver`` (encoding_analyzer.py loaded by path,
+                     CPU): per-batch histograms, the merged histogram / bin edges / min / max after every update,
+                     dynamic and final encodings for several grids; includes the tensors of the reference's own
+                     histogram tests.
+* histc_rule.npz   - the installed ``torch.histc`` CPU operator on values on, just below and just above every bin
+                     boundary (the operator is third-party code: its bin rule is pinned by execution).
 * v1_ste.npz       - aimet_torch v1 straight-through gradient ``compute_dloss_by_dx`` (same file, CPU): per tensor
                      and per channel on axis 0 / 1, with inputs exactly on the encoding bounds.
 * libpymo.npz      - the reference DlQuantization CPU code (oracle/_ref): per-tensor QDQ / codes, TF and
@@ -395,6 +401,107 @@ def gen_reference_backend_tests(ref_root: str):
     np.savez_compressed(os.path.join(HERE, "v2_backend_reference_tests.npz"), **out)
 
 
+def sqnr_scenarios():
+    """(name, observer shape, num_bins, analyzer kwargs, list of batches)."""
+    g = torch.Generator().manual_seed(77)
+
+    def relu(n, seed):
+        gg = torch.Generator().manual_seed(seed)
+        a = torch.relu(torch.randn(n, generator=gg))
+        m = torch.rand(n, generator=gg) < 1e-3
+        return torch.where(m, a * 20, a)
+
+    sc = []
+    sc.append(("relu_512", (1,), 512, {}, [relu(20000, 1000 + b) for b in range(4)]))
+    sc.append(("relu_2048", (1,), 2048, {}, [relu(20000, 1000 + b) for b in range(3)]))
+    sc.append(("normal_growing", (), 512, {}, [torch.randn(10000, generator=g) * (1 + b) + 0.3 * b for b in range(4)]))
+    sc.append(("shrinking", (1,), 512, {}, [torch.randn(8000, generator=g) * s for s in (4.0, 1.0, 0.25)]))
+    sc.append(("negative", (1,), 512, {}, [-torch.rand(8000, generator=g) * 3 - 1, -torch.rand(8000, generator=g) * 5 - 0.5]))
+    sc.append(("with_inf_nan", (1,), 512, {}, [torch.cat([torch.randn(5000, generator=g), torch.tensor([float("inf"), -float("inf"), float("nan")])]),
+                                               torch.cat([torch.randn(5000, generator=g) * 2, torch.tensor([float("inf"), float("inf")])])]))
+    sc.append(("gamma1_uniform", (1,), 2048, {"gamma": 1}, [torch.arange(-100, 101) / 100]))
+    # the tensors of the reference's own histogram tests (test_encoding_analyzer.py:286-362), 3 bins
+    sc.append(("ref_resize", (), 3, {}, [torch.tensor([2.0, 3.5, 4.2, 5.0]), torch.tensor([5.3, 6.4, 7.0, 8.0]),
+                                          torch.tensor([-4.2, 0, 2.3, 4.5])]))
+    sc.append(("ref_no_resize", (), 3, {}, [torch.tensor([2.0, 3.5, 4.2, 5.0]), torch.tensor([2.0, 3.3, 4.8, 5]),
+                                             torch.tensor([3.1, 3.3, 3.7, 3.9])]))
+    sc.append(("ref_ambiguous", (), 3, {}, [torch.tensor([-4.2, 2.4, 7.0, 8.0]), torch.tensor([-6.7, -2.5, 7.2, 10.3])]))
+    sc.append(("constant_then_wider", (1,), 16, {}, [torch.full((100,), 2.0), torch.tensor([2.0, 2.0, 2.0])]))
+    sc.append(("per_channel", (4, 1), 64, {}, [torch.randn(4, 3000, generator=g) * torch.tensor([[0.5], [1.0], [2.0], [4.0]]),
+                                                torch.randn(4, 3000, generator=g) * torch.tensor([[1.0], [1.0], [3.0], [2.0]])]))
+    sc.append(("conv_weight_axis0", (6, 1, 1, 1), 128, {}, [torch.randn(6, 8, 3, 3, generator=g) * 0.2]))
+    return sc
+
+
+SQNR_GRIDS = ((255, False), (255, True), (15, False), (15, True), (65535, False), (256.0, False))
+
+
+def gen_sqnr(ref_root: str):
+    _, _, ea = load_reference_v2(ref_root)
+    out = {}
+    names = []
+    for name, shape, bins, kw, batches in sqnr_scenarios():
+        an = ea.SqnrEncodingAnalyzer(shape, bins, **kw)
+        names.append(name)
+        out[f"{name}/shape"] = np.array(shape, dtype=np.int64)
+        out[f"{name}/bins"] = np.array(bins)
+        out[f"{name}/gamma"] = np.array(float(kw.get("gamma", 3.0)))
+        out[f"{name}/num_batches"] = np.array(len(batches))
+        for b, x in enumerate(batches):
+            out[f"{name}/x{b}"] = x.numpy()
+            new = an.update_stats(x)
+            for h, st in enumerate(new):
+                out[f"{name}/b{b}/batch/{h}/hist"] = st.histogram.numpy()
+                out[f"{name}/b{b}/batch/{h}/edges"] = st.bin_edges.numpy()
+                out[f"{name}/b{b}/batch/{h}/minmax"] = np.array([st.min.item(), st.max.item()], np.float32)
+            for h, st in enumerate(an.observer.get_stats()):
+                out[f"{name}/b{b}/state/{h}/hist"] = st.histogram.numpy()
+                out[f"{name}/b{b}/state/{h}/edges"] = st.bin_edges.numpy()
+                out[f"{name}/b{b}/state/{h}/minmax"] = np.array([st.min.item(), st.max.item()], np.float32)
+            for gi, (steps, sym) in enumerate(SQNR_GRIDS):
+                mn, mx = an.compute_encodings_from_stats(new, steps, sym)
+                out[f"{name}/b{b}/dynamic/{gi}"] = np.stack([mn.reshape(-1).numpy(), mx.reshape(-1).numpy()])
+        for gi, (steps, sym) in enumerate(SQNR_GRIDS):
+            mn, mx = an.compute_encodings(steps, sym)
+            out[f"{name}/final/{gi}"] = np.stack([mn.reshape(-1).numpy(), mx.reshape(-1).numpy()])
+    out["names"] = np.array(names)
+    out["grids"] = np.array([[float(s), float(y)] for s, y in SQNR_GRIDS])
+    np.savez_compressed(os.path.join(HERE, "v2_sqnr.npz"), **out)
+
+
+def gen_histc_rule():
+    """torch.histc (CPU) on boundary values: for random ranges and bin counts, every value that the float32 expression
+    lo + k * (hi - lo) / bins produces, its two neighbours, the bounds themselves, and specials."""
+    rng = np.random.default_rng(5)
+    out = {}
+    cases = 0
+    for nb in (1, 3, 10, 64, 512, 2048):
+        for rep in range(6):
+            lo = np.float32(rng.standard_normal() * 10.0 ** rng.integers(-2, 3))
+            hi = np.float32(lo + abs(rng.standard_normal()) * 10.0 ** rng.integers(-2, 3) + 1e-3)
+            if rep == 0:
+                lo, hi = np.float32(0.0), np.float32(abs(hi))     # post-ReLU ranges start at zero
+            step = (hi - lo) / np.float32(nb)
+            k = rng.integers(0, nb + 1, 600).astype(np.float32)
+            e = (lo + k * step).astype(np.float32)
+            x = np.concatenate([e, np.nextafter(e, np.float32(np.inf)), np.nextafter(e, np.float32(-np.inf)),
+                                (rng.random(3000).astype(np.float32) * (hi - lo) * np.float32(1.2) + lo - np.float32(0.1) * (hi - lo)),
+                                np.array([np.nan, np.inf, -np.inf, lo, hi, np.nextafter(hi, np.float32(np.inf)),
+                                          np.nextafter(lo, np.float32(-np.inf)), 0.0, -0.0], np.float32)]).astype(np.float32)
+            want = torch.histc(torch.from_numpy(x), bins=nb, min=float(lo), max=float(hi)).numpy()
+            out[f"c{cases}/x"], out[f"c{cases}/range"], out[f"c{cases}/bins"] = x, np.array([lo, hi], np.float32), np.array(nb)
+            out[f"c{cases}/counts"] = want
+            cases += 1
+    # equal bounds: constant data, and data around the bound
+    for val in (2.0, 0.0, -3.5):
+        x = np.full(50, val, np.float32)
+        out[f"c{cases}/x"], out[f"c{cases}/range"], out[f"c{cases}/bins"] = x, np.array([val, val], np.float32), np.array(8)
+        out[f"c{cases}/counts"] = torch.histc(torch.from_numpy(x), bins=8, min=val, max=val).numpy()
+        cases += 1
+    out["count"] = np.array(cases)
+    np.savez_compressed(os.path.join(HERE, "histc_rule.npz"), **out)
+
+
 def _load_v1_grad(ref_root: str):
     at = os.path.join(ref_root, "TrainingExtensions", "torch", "src", "python", "aimet_torch")
     for name in ("aimet_torch", "aimet_torch.v1"):
@@ -486,10 +593,10 @@ if __name__ == "__main__":
     only = sys.argv[2:]   # optionally: names of the generators to run
     gens = {"v2": lambda: gen_v2(ref), "quantizer": lambda: gen_quantizer(ref),
             "range_learning": lambda: gen_range_learning(ref), "reference_backend_tests": lambda: gen_reference_backend_tests(ref),
-            "ste_v1": lambda: gen_ste_v1(ref), "libpymo": gen_libpymo}
+            "ste_v1": lambda: gen_ste_v1(ref), "sqnr": lambda: gen_sqnr(ref), "histc_rule": gen_histc_rule, "libpymo": gen_libpymo}
     for name, fn in gens.items():
         if not only or name in only:
             fn()
-    for f in ("v2_backend.npz", "v2_minmax.npz", "v2_quantizer.npz", "v1_range_learning.npz", "v1_ste.npz", "v2_backend_reference_tests.npz",
+    for f in ("v2_backend.npz", "v2_minmax.npz", "v2_quantizer.npz", "v1_range_learning.npz", "v1_ste.npz", "v2_sqnr.npz", "histc_rule.npz", "v2_backend_reference_tests.npz",
               "libpymo.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")

@@ -54,7 +54,7 @@ def test_resnet18_every_quantizer_matches_cpu_reference(cuda, oracle):
     m = _resnet("resnet18").to(cuda)
     g = torch.Generator().manual_seed(3)
     batches = [torch.randn(4, 3, 64, 64, generator=g).to(cuda) for _ in range(2)]
-    sim = QuantizationSimModel(m, batches[0])
+    sim = QuantizationSimModel(m, batches[0], quant_scheme="post_training_tf_enhanced_libpymo")
     seen = {name: [] for name in sim.activation_quantizers}
     hooks = [q.register_forward_pre_hook(lambda mod, args, n=name: seen[n].append(args[0].detach().float().cpu().numpy().reshape(-1)))
              for name, q in sim.activation_quantizers.items()]
@@ -108,7 +108,7 @@ def test_resnet50_full_size_every_quantizer_matches_cpu_reference(cuda, oracle):
     for b in range(2):
         g.manual_seed(2000 + b)
         batches.append(torch.randn(128, 3, 224, 224, device=cuda, generator=g))
-    sim = QuantizationSimModel(m, batches[0])
+    sim = QuantizationSimModel(m, batches[0], quant_scheme="post_training_tf_enhanced_libpymo")
     assert len(sim.layers) == 54 and len(sim.activation_quantizers) == 73
     refs = {name: OracleTfeAnalyzer(oracle) for name in sim.activation_quantizers}
     fed = {name: 0 for name in sim.activation_quantizers}
@@ -139,5 +139,45 @@ def test_resnet50_full_size_every_quantizer_matches_cpu_reference(cuda, oracle):
     x = batches[0].requires_grad_(True)
     y = sim.model(x)
     assert y.shape == (128, 1000) and torch.isfinite(y).all()
+    y.square().mean().backward()
+    assert x.grad is not None and torch.isfinite(x.grad).all()
+
+
+@pytest.mark.gpu
+def test_resnet18_v2_tf_enhanced_uses_sqnr_analyzers(cuda):
+    """quant_scheme="post_training_tf_enhanced" is the reference's v2 mapping: SqnrEncodingAnalyzer for parameters
+    (one histogram per output channel) and activations.  Every quantizer must end with what a stand-alone analyzer
+    (pinned bit for bit to the reference's class in test_v2_sqnr_gpu.py) computes from the tensors it saw."""
+    from aimet_b200.v2.encoding_analyzer import SqnrEncodingAnalyzer
+    from aimet_b200.v2.quantsim import QuantizationSimModel
+    m = _resnet("resnet18").to(cuda)
+    g = torch.Generator().manual_seed(3)
+    batches = [torch.randn(4, 3, 64, 64, generator=g).to(cuda) for _ in range(2)]
+    sim = QuantizationSimModel(m, batches[0], quant_scheme="post_training_tf_enhanced")
+    assert all(isinstance(q.encoding_analyzer, SqnrEncodingAnalyzer) for q in sim.quantizers())
+    refs = {name: SqnrEncodingAnalyzer(()) for name in sim.activation_quantizers}
+    def feed(name, t):
+        refs[name].update_stats(t.detach().clone())   # (a pre-hook's return value would replace the input)
+
+    hooks = [q.register_forward_pre_hook(lambda mod, args, n=name: feed(n, args[0]))
+             for name, q in sim.activation_quantizers.items()]
+    sim.compute_encodings(lambda model, data: [model(x) for x in data], batches)
+    for h in hooks:
+        h.remove()
+    for name, q in sim.activation_quantizers.items():
+        mn, mx = refs[name].compute_encodings(255, False)
+        assert q.is_initialized(), name
+        assert torch.equal(q.min.detach(), mn) and torch.equal(q.max.detach(), mx), name
+    for name, layer in list(sim.layers.items())[:6]:
+        w = layer.layer.weight.detach()
+        shape = (w.shape[0],) + (1,) * (w.dim() - 1)
+        ref = SqnrEncodingAnalyzer(shape)
+        ref.update_stats(w)
+        mn, mx = ref.compute_encodings(255, True)
+        wq = layer.param_quantizers["weight"]
+        assert torch.equal(wq.min.detach(), mn) and torch.equal(wq.max.detach(), mx), name
+    x = batches[0].clone().requires_grad_(True)
+    y = sim.model(x)
+    assert y.shape == (4, 1000) and torch.isfinite(y).all()
     y.square().mean().backward()
     assert x.grad is not None and torch.isfinite(x.grad).all()

@@ -1,0 +1,109 @@
+"""GPU parity of the v2 histogram observer and SQNR analyzer with the reference's own classes.
+
+tests/golden/v2_sqnr.npz was produced by the reference's ``SqnrEncodingAnalyzer`` / ``_HistogramObserver`` on CPU
+(tests/golden/gen_golden.py): per-batch histograms, the merged statistics after every update, dynamic and final
+encodings.  tests/golden/histc_rule.npz pins the bin rule of ``torch.histc`` (third-party code) on boundary values.
+Histograms, bin edges, min / max and encodings must be bit-identical.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from _data import assert_bits_equal
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+S = np.load(os.path.join(GOLD, "v2_sqnr.npz"))
+H = np.load(os.path.join(GOLD, "histc_rule.npz"))
+GRIDS = [(float(s), bool(y)) for s, y in S["grids"]]
+
+
+def steps_of(v):
+    return int(v) if float(v).is_integer() and v != 256.0 else v
+
+
+@pytest.mark.parametrize("case", range(int(H["count"])))
+def test_histc_rule(cuda, case):
+    """The counting pass against the installed torch.histc on boundary values (collect over a forced range)."""
+    from aimet_b200._lib import lib
+    x = H[f"c{case}/x"]
+    lo, hi = H[f"c{case}/range"]
+    nb = int(H[f"c{case}/bins"])
+    want = H[f"c{case}/counts"]
+    # Drive the merge path, whose counting range is exactly [state.min, state.max] when the batch lies inside it:
+    # keep only elements inside the range plus NaN (what histc looks at), so that the widened range stays [lo, hi].
+    keep = ((x >= lo) & (x <= hi)) | np.isnan(x)
+    xs = np.ascontiguousarray(x[keep])
+    xd = torch.from_numpy(xs).to(cuda)
+    words = (16 + (2 * nb + 1) * 4) // 4
+    state = torch.zeros(words, dtype=torch.int32, device=cuda)
+    state.view(torch.float32)[0] = float(lo)
+    state.view(torch.float32)[1] = float(hi)
+    state[2] = 1
+    batch = torch.zeros(words, dtype=torch.int32, device=cuda)
+    scratch = torch.empty(int(lib.aq_v2hist_scratch_bytes()), dtype=torch.uint8, device=cuda)
+    upd = torch.empty(nb, dtype=torch.float32, device=cuda)
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.aq_v2hist_merge(xd.data_ptr(), 0, xd.numel(), nb, state.data_ptr(), batch.data_ptr(), 1,
+                               scratch.data_ptr(), upd.data_ptr(), st) == 0
+    got = state.view(torch.float32)[4:4 + nb].cpu().numpy()
+    np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("name", [str(n) for n in S["names"]])
+def test_sqnr_analyzer_matches_reference(cuda, name):
+    from aimet_b200.v2.encoding_analyzer import SqnrEncodingAnalyzer
+    shape = tuple(int(v) for v in S[f"{name}/shape"])
+    bins = int(S[f"{name}/bins"])
+    an = SqnrEncodingAnalyzer(shape, bins, gamma=float(S[f"{name}/gamma"]))
+    nh = int(np.prod(shape)) if len(shape) else 1
+    for b in range(int(S[f"{name}/num_batches"])):
+        x = torch.from_numpy(S[f"{name}/x{b}"]).to(cuda)
+        new = an.update_stats(x)
+        state = an.observer.get_stats()
+        assert len(new) == nh and len(state) == nh
+        for h in range(nh):
+            for kind, st in (("batch", new[h]), ("state", state[h])):
+                key = f"{name}/b{b}/{kind}/{h}"
+                assert_bits_equal(st.histogram.cpu().numpy(), S[f"{key}/hist"], f"{key} histogram")
+                assert_bits_equal(st.bin_edges.cpu().numpy(), S[f"{key}/edges"], f"{key} bin edges")
+                assert_bits_equal(np.array([st.min.item(), st.max.item()], np.float32), S[f"{key}/minmax"], f"{key} min/max")
+        for gi, (steps, sym) in enumerate(GRIDS):
+            mn, mx = an.compute_encodings_from_stats(new, steps_of(steps), sym)
+            got = np.stack([mn.reshape(-1).cpu().numpy(), mx.reshape(-1).cpu().numpy()])
+            assert_bits_equal(got, S[f"{name}/b{b}/dynamic/{gi}"], f"{name} batch {b} dynamic grid {gi}")
+    for gi, (steps, sym) in enumerate(GRIDS):
+        mn, mx = an.compute_encodings(steps_of(steps), sym)
+        assert mn.shape == shape and mx.shape == shape
+        got = np.stack([mn.reshape(-1).cpu().numpy(), mx.reshape(-1).cpu().numpy()])
+        assert_bits_equal(got, S[f"{name}/final/{gi}"], f"{name} final grid {gi}")
+
+
+def test_sqnr_analyzer_protocol(cuda):
+    from aimet_b200.v2.encoding_analyzer import SqnrEncodingAnalyzer, StatisticsNotFoundError
+    with pytest.raises(ValueError):
+        SqnrEncodingAnalyzer((1,), 0)
+    an = SqnrEncodingAnalyzer((1,), 512)
+    with pytest.raises(StatisticsNotFoundError):
+        an.compute_encodings(255, False)
+    x = torch.randn(1000, device=cuda)
+    an.update_stats(x)
+    with pytest.raises(ValueError):
+        an.compute_encodings(0, False)
+    mn, mx = an.compute_encodings(255, False)
+    assert mn.shape == (1,) and mn.device.type == "cuda"
+    an.reset_stats()
+    with pytest.raises(StatisticsNotFoundError):
+        an.compute_encodings(255, False)
+    with pytest.raises(RuntimeError):
+        an.update_stats(torch.randn(10))          # CPU tensor: there is no CPU path
+    with pytest.raises(RuntimeError):
+        SqnrEncodingAnalyzer((3,), 64).update_stats(torch.randn(5, 4, device=cuda))   # shape not expandable
+    # 16-bit input: statistics in float32, encodings come back in the input dtype
+    h = SqnrEncodingAnalyzer((), 256)
+    h.update_stats(torch.randn(4000, device=cuda).to(torch.bfloat16))
+    mn, mx = h.compute_encodings(255, True)
+    assert mn.dtype == torch.bfloat16 and mn.shape == ()
