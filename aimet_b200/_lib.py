@@ -48,6 +48,8 @@ SIGNATURES = {
     "aq_minmax_encoding": (_i32, [_i32, _f64, _f64, _i32, _i32, _i32, C.POINTER(AqEncoding)]),
     "aq_qdq_per_tensor": (_i32, [_vp, _vp, _i64, _f64, _f64, _i32, _i32, _vp]),
     "aq_quantize_per_tensor": (_i32, [_vp, _vp, _i64, _f64, _f64, _i32, _i32, _i32, _vp]),
+    "aq_quantize_packed": (_i32, [_vp, _vp, _i64, _f64, _f64, _i32, _i32, _i32, _vp]),
+    "aq_dequantize_packed": (_i32, [_vp, _vp, _i64, _f64, _f64, _i32, _i32, _vp]),
     "aq_qdq_per_channel": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _vp, _f64, _i32, _vp]),
     "aq_qdq_broadcast": (_i32, [_vp, _vp, _i64, _i64, C.POINTER(_i64), C.POINTER(_i64), _vp, _vp, _vp, _vp, _vp]),
     "aq_ste_backward_v1": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp]),
@@ -55,6 +57,8 @@ SIGNATURES = {
     "aq_v2_dequantize": (_i32, [_vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _i32, _vp]),
     "aq_v2_qdq_backward": (_i32, [_vp, _vp, _vp, _i32, _i64, _vp]),
     "aq_v2_qdq_backward_params": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _f64, _f64, _vp]),
+    "aq_v2_qdq_backward_params_reduced": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _vp, _vp, _f64, _f64,
+                                                 _vp]),
     "aq_minmax_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "aq_minmax": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _i32, _i32, _vp, _i64, _vp]),
     "aq_minmax_static": (_i32, [_vp, _i32, _i64, _i64, _i64, _vp, _vp, _i32, _vp]),

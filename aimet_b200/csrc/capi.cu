@@ -152,6 +152,34 @@ int aq_quantize_per_tensor(const float* d_in, float* d_out, int64_t n, double en
                            (float) shift, (cudaStream_t) stream);
 }
 
+static inline bool packed_bw_ok(int bw)
+{
+    return bw == 1 || bw == 2 || bw == 4 || bw == 8 || bw == 16 || bw == 32;
+}
+
+int aq_quantize_packed(const float* d_in, void* d_out, int64_t n, double enc_min, double enc_max, int bw,
+                       int rounding_mode, int shift_to_signed, void* stream)
+{
+    if (n < 0 || (n > 0 && (!d_in || !d_out)) || !packed_bw_ok(bw) || ((uintptr_t) d_out % (bw > 16 ? 4 : (bw > 8 ? 2 : 1))))
+        return AQ_ERR_INVALID_ARG;
+    if (rounding_mode != AQ_ROUND_NEAREST)
+        return AQ_ERR_UNSUPPORTED;
+    aq_encoding_t e;
+    fill_encoding(bw, enc_min, enc_max, &e);
+    return packed_quantize(d_in, d_out, n, e.min, e.max, e.delta, e.offset, bw, shift_to_signed != 0,
+                           (cudaStream_t) stream);
+}
+
+int aq_dequantize_packed(const void* d_in, float* d_out, int64_t n, double enc_min, double enc_max, int bw,
+                         int shift_to_signed, void* stream)
+{
+    if (n < 0 || (n > 0 && (!d_in || !d_out)) || !packed_bw_ok(bw) || ((uintptr_t) d_in % (bw > 16 ? 4 : (bw > 8 ? 2 : 1))))
+        return AQ_ERR_INVALID_ARG;
+    aq_encoding_t e;
+    fill_encoding(bw, enc_min, enc_max, &e);
+    return packed_dequantize(d_in, d_out, n, e.delta, e.offset, bw, shift_to_signed != 0, (cudaStream_t) stream);
+}
+
 int aq_qdq_per_channel(const float* d_in, float* d_out, int64_t n, int64_t num_ch, int64_t inner,
                        const float* d_enc_min, const float* d_enc_max, double num_steps, int rounding_mode,
                        void* stream)
@@ -261,7 +289,22 @@ int aq_v2_qdq_backward_params(const void* d_x, const void* d_grad, const uint8_t
     a.x = d_x, a.grad = d_grad, a.mask = d_mask, a.dscale = d_dscale, a.doffset = d_doffset, a.n = n;
     a.scale = d_scale, a.offset = d_offset, a.qmin = (float) qmin, a.qmax = (float) qmax;
     a.geom.num_ch = num_ch, a.geom.inner = inner;
-    return v2_param_grad(a, dtype, (cudaStream_t) stream);
+    return v2_param_grad(a, dtype, 0, (cudaStream_t) stream);
+}
+
+int aq_v2_qdq_backward_params_reduced(const void* d_x, const void* d_grad, const uint8_t* d_mask, float* d_dscale,
+                                      float* d_doffset, int dtype, int64_t n, int64_t num_ch, int64_t inner,
+                                      const float* d_scale, const float* d_offset, double qmin, double qmax,
+                                      void* stream)
+{
+    if (bad_geom(n, num_ch, inner) || (n > 0 && (!d_x || !d_grad || !d_mask)) || (!d_dscale && !d_doffset) ||
+        !d_scale || !d_offset || qmin > qmax || dtype < AQ_F32 || dtype > AQ_BF16)
+        return AQ_ERR_INVALID_ARG;
+    V2GradArgs a;
+    a.x = d_x, a.grad = d_grad, a.mask = d_mask, a.dscale = d_dscale, a.doffset = d_doffset, a.n = n;
+    a.scale = d_scale, a.offset = d_offset, a.qmin = (float) qmin, a.qmax = (float) qmax;
+    a.geom.num_ch = num_ch, a.geom.inner = inner;
+    return v2_param_grad(a, dtype, 1, (cudaStream_t) stream);
 }
 
 int aq_v2_qdq_backward(const void* d_grad, const uint8_t* d_mask, void* d_dx, int dtype, int64_t n, void* stream)

@@ -826,6 +826,157 @@ int v2_launch(V2Args a, int dtype, int narrow_internal, cudaStream_t st)
 }
 
 // -------------------------------------------------------------------------------------------------
+// Integer codes in integer containers (libpymo "packed" form)
+// -------------------------------------------------------------------------------------------------
+// quantizeToFxpPackedCpu / dequantizeFromPackedFxpCpu (DlQuantization/src/trim_functions.cpp:220-605): unlike the
+// float-container path these evaluate clamp, divide, offset and round in DOUBLE from the double-precision encoding, and
+// store one code per container of max(bw, 8) bits (uint8/16/32, or int8/16/32 when shifted to signed by 2^(bw-1) - 1;
+// sub-byte widths keep one value per byte, the signed ones masked to their low bw bits).
+template <typename OUT>
+__device__ __forceinline__ OUT packed_store_cast(double v, double lo, double hi)
+{
+    const double c = (hi < v) ? hi : v;          // std::min(v, hi)
+    const double d = (c < lo) ? lo : c;          // std::max(., lo)
+    return (d == d) ? (OUT) d : (OUT) 0;
+}
+
+template <typename OUT>
+__global__ void __launch_bounds__(256) packed_quantize_kernel(const float* __restrict__ in, OUT* __restrict__ out,
+                                                              int64_t n, double e_min, double e_max, double delta,
+                                                              double offset, int bw, int to_signed)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const double shift = to_signed ? ldexp(1.0, bw - 1) - 1.0 : 0.0;
+    const double top   = ldexp(1.0, bw) - 1.0;
+    for (int64_t i = (int64_t) blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t) gridDim.x * 256)
+    {
+        const double x = (double) in[i];
+        double q       = (e_max < x) ? e_max : x;    // std::min(x, max)
+        q              = (q < e_min) ? e_min : q;    // std::max(., min)
+        q              = round(__dsub_rn(__ddiv_rn(q, delta), offset));
+        if (!to_signed)
+        {
+            if (bw < 8)
+            {
+                const uint8_t small = (q == q) ? (uint8_t) q : (uint8_t) 0;
+                out[i]              = (OUT) packed_store_cast<uint8_t>((double) small, 0.0, top);
+            }
+            else
+                out[i] = packed_store_cast<OUT>(q, 0.0, bw == 8 ? 255.0 : (bw == 16 ? 65535.0 : 4294967295.0));
+        }
+        else
+        {
+            q = __dsub_rn(q, shift);
+            if (bw < 8)
+            {
+                const int8_t small = (q == q) ? (int8_t) q : (int8_t) 0;
+                out[i]             = (OUT) (small & (int8_t) (int) top);
+            }
+            else
+                out[i] = packed_store_cast<OUT>(q, bw == 8 ? -128.0 : (bw == 16 ? -32768.0 : -2147483648.0),
+                                                bw == 8 ? 127.0 : (bw == 16 ? 32767.0 : 2147483647.0));
+        }
+    }
+}
+
+template <typename IN>
+__global__ void __launch_bounds__(256) packed_dequantize_kernel(const IN* __restrict__ in, float* __restrict__ out,
+                                                                int64_t n, double delta, double offset, int bw,
+                                                                int is_signed)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t) blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t) gridDim.x * 256)
+    {
+        double code = (double) in[i];
+        if (is_signed && bw < 8)
+        {
+            // one value per byte, sign-extended from its low bw bits
+            const int8_t b = (int8_t) in[i];
+            code           = (b & (int8_t) (1 << (bw - 1))) ? (double) (int8_t) (~((int8_t) ((1 << bw) - 1)) | b) : (double) b;
+        }
+        out[i] = (float) __dmul_rn(delta, __dadd_rn(code, offset));
+    }
+}
+
+static unsigned packed_grid(int64_t n)
+{
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > (int64_t) kNumSMs * 16)
+        blocks = (int64_t) kNumSMs * 16;
+    return (unsigned) (blocks < 1 ? 1 : blocks);
+}
+
+int packed_quantize(const float* in, void* out, int64_t n, double e_min, double e_max, double delta, double offset, int bw,
+                    int to_signed, cudaStream_t st)
+{
+    if (n == 0)
+        return AQ_OK;
+#define AQ_PQ(OUT)                                                                                                   \
+    launch_pdl(packed_quantize_kernel<OUT>, packed_grid(n), 256, 0, st, in, (OUT*) out, n, e_min, e_max, delta, offset, \
+               bw, to_signed)
+    if (bw <= 8)
+    {
+        if (to_signed)
+            AQ_PQ(int8_t);
+        else
+            AQ_PQ(uint8_t);
+    }
+    else if (bw == 16)
+    {
+        if (to_signed)
+            AQ_PQ(int16_t);
+        else
+            AQ_PQ(uint16_t);
+    }
+    else
+    {
+        if (to_signed)
+            AQ_PQ(int32_t);
+        else
+            AQ_PQ(uint32_t);
+    }
+#undef AQ_PQ
+    note_launch();
+    return check_launch();
+}
+
+int packed_dequantize(const void* in, float* out, int64_t n, double delta, double offset, int bw, int is_signed,
+                      cudaStream_t st)
+{
+    if (n == 0)
+        return AQ_OK;
+#define AQ_PD(IN)                                                                                                    \
+    launch_pdl(packed_dequantize_kernel<IN>, packed_grid(n), 256, 0, st, (const IN*) in, out, n, delta, offset, bw,    \
+               is_signed)
+    if (bw <= 8)
+    {
+        if (is_signed)
+            AQ_PD(int8_t);
+        else
+            AQ_PD(uint8_t);
+    }
+    else if (bw == 16)
+    {
+        if (is_signed)
+            AQ_PD(int16_t);
+        else
+            AQ_PD(uint16_t);
+    }
+    else
+    {
+        if (is_signed)
+            AQ_PD(int32_t);
+        else
+            AQ_PD(uint32_t);
+    }
+#undef AQ_PD
+    note_launch();
+    return check_launch();
+}
+
+// -------------------------------------------------------------------------------------------------
 // Backward kernels
 // -------------------------------------------------------------------------------------------------
 
@@ -936,15 +1087,22 @@ int v2_backward(const void* g, const uint8_t* mask, void* dx, int dtype, int64_t
     }
 }
 
-// v2 encoding gradients, element-wise and un-reduced exactly like the reference (autograd sums the broadcast
-// dimensions afterwards), torch_builtins.py:334-343:
+// v2 encoding gradients (torch_builtins.py:334-343):
 //   ds = g * (clamp(round(x/s), o + qmin, o + qmax) - (x/s) * mask)      do = g * ((1 - mask) * s)
-template <typename T, int VEC, bool PER_CH>
+// REDUCE = false: element-wise and un-reduced exactly like the reference returns them (its autograd sums over the
+// broadcast dimensions afterwards).  REDUCE = true: that sum is taken here -- per thread over its packets, per CTA
+// in shared memory (one slot per run of a channel inside the CTA's chunk), then one floating-point atomic per run into
+// the per-channel result -- so the two full-size fp32 tensors (8 bytes per element written, 8 read back) never exist.
+// The summation order differs from torch's, which is not specified either; the terms are identical.
+template <typename T, int VEC, bool PER_CH, bool REDUCE>
 __global__ void __launch_bounds__(kThreads) v2_param_grad_kernel(V2GradArgs a)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int CHUNK = chunk_elems<VEC>();
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
     __shared__ float s_sc[PER_CH ? kMaxRuns : 1], s_of[PER_CH ? kMaxRuns : 1];
+    __shared__ float s_ds[(PER_CH && REDUCE) ? kMaxRuns : kThreads / 32], s_do[(PER_CH && REDUCE) ? kMaxRuns : kThreads / 32];
     RunCtx rc {0, 0, 1, 0};
     float sc0 = 0.f, of0 = 0.f;
     Pack<T, VEC> xv[unroll_of<VEC>()], gv[unroll_of<VEC>()];
@@ -961,6 +1119,8 @@ __global__ void __launch_bounds__(kThreads) v2_param_grad_kernel(V2GradArgs a)
             const int64_t ch = run_channel(a.geom, rc, lr);
             s_sc[lr]         = a.scale[ch];
             s_of[lr]         = a.offset[ch];
+            if (REDUCE)
+                s_ds[lr] = 0.0f, s_do[lr] = 0.0f;
         }
         __syncthreads();
     }
@@ -969,19 +1129,22 @@ __global__ void __launch_bounds__(kThreads) v2_param_grad_kernel(V2GradArgs a)
         sc0 = __ldg(a.scale);
         of0 = __ldg(a.offset);
     }
+    float tot_s = 0.0f, tot_o = 0.0f;   // per-thread sums (per-tensor encodings)
 #pragma unroll
     for (int u = 0; u < unroll_of<VEC>(); ++u)
     {
         const uint32_t off = (uint32_t) (u * kThreads + threadIdx.x) * VEC;
         const int64_t idx  = base + off;
         float sc = sc0, of = of0;
+        uint32_t lr = 0;
         if (PER_CH)
         {
-            const uint32_t lr = run_of(a.geom, rc, off);
+            lr = run_of(a.geom, rc, off);
             sc = s_sc[lr], of = s_of[lr];
         }
         const float lo = __fadd_rn(of, a.qmin), hi = __fadd_rn(of, a.qmax);
         Pack<float, VEC> ds, dof;
+        float ps = 0.0f, po = 0.0f;
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
         {
@@ -991,58 +1154,135 @@ __global__ void __launch_bounds__(kThreads) v2_param_grad_kernel(V2GradArgs a)
             const float c = clamp_keep_nan(rintf(t), lo, hi);
             ds.v[e]       = __fmul_rn(g, __fsub_rn(c, __fmul_rn(t, m)));
             dof.v[e]      = __fmul_rn(g, __fmul_rn(1.0f - m, sc));
+            if (REDUCE && (full[u] || idx + e < a.n))
+                ps += ds.v[e], po += dof.v[e];
         }
-        if (a.dscale)
-            store_packet<float, VEC>(a.dscale, idx, a.n, ds, full[u]);
-        if (a.doffset)
-            store_packet<float, VEC>(a.doffset, idx, a.n, dof, full[u]);
+        if (REDUCE)
+        {
+            if (PER_CH)
+            {
+                if (idx < a.n)
+                {
+                    if (a.dscale)
+                        atomicAdd(&s_ds[lr], ps);
+                    if (a.doffset)
+                        atomicAdd(&s_do[lr], po);
+                }
+            }
+            else
+                tot_s += ps, tot_o += po;
+        }
+        else
+        {
+            if (a.dscale)
+                store_packet<float, VEC>(a.dscale, idx, a.n, ds, full[u]);
+            if (a.doffset)
+                store_packet<float, VEC>(a.doffset, idx, a.n, dof, full[u]);
+        }
+    }
+    if (!REDUCE)
+        return;
+    if (PER_CH)
+    {
+        __syncthreads();
+        for (int lr = threadIdx.x; lr < rc.nruns; lr += kThreads)
+        {
+            const int64_t ch = run_channel(a.geom, rc, lr);
+            if (a.dscale && s_ds[lr] != 0.0f)
+                atomicAdd(&a.dscale[ch], s_ds[lr]);
+            if (a.doffset && s_do[lr] != 0.0f)
+                atomicAdd(&a.doffset[ch], s_do[lr]);
+        }
+    }
+    else
+    {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+        {
+            tot_s += __shfl_xor_sync(0xffffffffu, tot_s, o);
+            tot_o += __shfl_xor_sync(0xffffffffu, tot_o, o);
+        }
+        if ((threadIdx.x & 31) == 0)
+            s_ds[threadIdx.x >> 5] = tot_s, s_do[threadIdx.x >> 5] = tot_o;
+        __syncthreads();
+        if (threadIdx.x == 0)
+        {
+            float bs = 0.0f, bo = 0.0f;
+            for (int w = 0; w < kThreads / 32; ++w)
+                bs += s_ds[w], bo += s_do[w];
+            if (a.dscale)
+                atomicAdd(a.dscale, bs);
+            if (a.doffset)
+                atomicAdd(a.doffset, bo);
+        }
     }
 }
 
 template <typename T>
-static int launch_param_grad(V2GradArgs a, cudaStream_t st)
+static int launch_param_grad(V2GradArgs a, bool reduce, cudaStream_t st)
 {
     const bool per_ch = a.geom.num_ch > 1;
     int vec           = pick_vec<T>(a.x, a.grad, nullptr, per_ch ? a.geom.inner : 0);
     if (vec > 4)
         vec = 4;   // fp32 outputs: 4 elements = 16 bytes
-    while (vec > 1 && (((uintptr_t) a.mask % vec) || ((uintptr_t) a.dscale % (4 * vec)) ||
-                       ((uintptr_t) a.doffset % (4 * vec))))
+    while (vec > 1 && (((uintptr_t) a.mask % vec) ||
+                       (!reduce && (((uintptr_t) a.dscale % (4 * vec)) || ((uintptr_t) a.doffset % (4 * vec))))))
         vec >>= 1;
-#define AQ_LAUNCH(V, PC)                                                                                             \
+    if (reduce)
+    {
+        // the sums start from zero (the outputs are small: one float per encoding)
+        cudaError_t e = cudaSuccess;
+        if (a.dscale)
+            e = cudaMemsetAsync(a.dscale, 0, sizeof(float) * (size_t) a.geom.num_ch, st);
+        if (e == cudaSuccess && a.doffset)
+            e = cudaMemsetAsync(a.doffset, 0, sizeof(float) * (size_t) a.geom.num_ch, st);
+        if (e != cudaSuccess)
+            return cuda_fail(e);
+    }
+#define AQ_LAUNCH(V, PC, RD)                                                                                         \
     {                                                                                                                \
         a.geom       = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>(), a.n);                                     \
         int64_t grid = (a.n + chunk_elems<V>() - 1) / chunk_elems<V>();                                              \
-        v2_param_grad_kernel<T, V, PC><<<(unsigned) grid, kThreads, 0, st>>>(a);                                     \
+        launch_pdl(v2_param_grad_kernel<T, V, PC, RD>, (unsigned) grid, kThreads, 0, st, a);                         \
     }
-    if (per_ch)
+#define AQ_PICK(RD)                                                                                                  \
+    if (per_ch)                                                                                                      \
+    {                                                                                                                \
+        if (vec == 4)                                                                                                \
+            AQ_LAUNCH(4, true, RD)                                                                                   \
+        else                                                                                                         \
+            AQ_LAUNCH(1, true, RD)                                                                                   \
+    }                                                                                                                \
+    else                                                                                                             \
+    {                                                                                                                \
+        if (vec == 4)                                                                                                \
+            AQ_LAUNCH(4, false, RD)                                                                                  \
+        else                                                                                                         \
+            AQ_LAUNCH(1, false, RD)                                                                                  \
+    }
+    if (reduce)
     {
-        if (vec == 4)
-            AQ_LAUNCH(4, true)
-        else
-            AQ_LAUNCH(1, true)
+        AQ_PICK(true)
     }
     else
     {
-        if (vec == 4)
-            AQ_LAUNCH(4, false)
-        else
-            AQ_LAUNCH(1, false)
+        AQ_PICK(false)
     }
+#undef AQ_PICK
 #undef AQ_LAUNCH
     note_launch();
     return check_launch();
 }
 
-int v2_param_grad(V2GradArgs a, int dtype, cudaStream_t st)
+int v2_param_grad(V2GradArgs a, int dtype, int reduce, cudaStream_t st)
 {
-    if (a.n == 0)
+    if (a.n == 0 && !reduce)
         return AQ_OK;
     switch (dtype)
     {
-    case AQ_F32: return launch_param_grad<float>(a, st);
-    case AQ_F16: return launch_param_grad<__half>(a, st);
-    case AQ_BF16: return launch_param_grad<__nv_bfloat16>(a, st);
+    case AQ_F32: return launch_param_grad<float>(a, reduce != 0, st);
+    case AQ_F16: return launch_param_grad<__half>(a, reduce != 0, st);
+    case AQ_BF16: return launch_param_grad<__nv_bfloat16>(a, reduce != 0, st);
     default: return AQ_ERR_INVALID_ARG;
     }
 }

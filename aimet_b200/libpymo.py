@@ -266,6 +266,21 @@ class TensorQuantizer:
         y = ops.qdq_per_tensor(self._to_dev(inputTensor), encodingMin, encodingMax, bitwidth, int(self.roundingMode))
         outputTensor.reshape(-1)[:] = y.reshape(-1).cpu().numpy()
 
+    def quantizeTensorPacked(self, inputTensor: np.ndarray, encodingMin: float, encodingMax: float, bw: int,
+                             roundMode: RoundingMode = RoundingMode.ROUND_NEAREST, useCuda: bool = True,
+                             useStrictSymmetric: bool = False) -> np.ndarray:
+        """Integer codes in uint8/16/32 containers (int8/16/32 when ``useStrictSymmetric`` shifts them to signed):
+        DlQuantization/src/TensorQuantizer.cpp:179-186.  The reference returns the bytes of that array."""
+        codes = ops.quantize_packed(self._to_dev(inputTensor), encodingMin, encodingMax, bw, useStrictSymmetric,
+                                    int(roundMode))
+        return codes.cpu().numpy()
+
+    def dequantize(self, codes: np.ndarray, encodingMin: float, encodingMax: float, bw: int,
+                   useStrictSymmetric: bool = False) -> np.ndarray:
+        """Inverse of ``quantizeTensorPacked`` (DlQuantization/src/TensorQuantizer.cpp:217-223)."""
+        t = torch.from_numpy(np.ascontiguousarray(codes)).to(self._device, non_blocking=True)
+        return ops.dequantize_packed(t, encodingMin, encodingMax, bw, useStrictSymmetric).cpu().numpy()
+
     def resetEncodingStats(self):
         self._q.resetEncodingStats()
         self.isEncodingValid = False

@@ -123,6 +123,35 @@ def quantize_per_tensor(x: torch.Tensor, enc_min: float, enc_max: float, bw: int
     return out
 
 
+_PACKED_DTYPES = {(8, False): torch.uint8, (8, True): torch.int8, (16, False): torch.uint16, (16, True): torch.int16,
+                  (32, False): torch.uint32, (32, True): torch.int32}
+
+
+def quantize_packed(x: torch.Tensor, enc_min: float, enc_max: float, bw: int, shift_to_signed: bool = False,
+                    rounding_mode: int = 0) -> torch.Tensor:
+    """Integer codes in uint8/16/32 (or int8/16/32) containers, one code per container of max(bw, 8) bits."""
+    x = _f32c(x, "input")
+    out = torch.empty(x.shape, dtype=_PACKED_DTYPES[(max(int(bw), 8), bool(shift_to_signed))], device=x.device)
+    with _on(x):
+        check(lib.aq_quantize_packed(x.data_ptr(), out.data_ptr(), x.numel(), float(enc_min), float(enc_max), int(bw),
+                                     int(rounding_mode), int(shift_to_signed), _stream(x)), "aq_quantize_packed")
+    return out
+
+
+def dequantize_packed(codes: torch.Tensor, enc_min: float, enc_max: float, bw: int,
+                      shift_to_signed: bool = False) -> torch.Tensor:
+    _cuda(codes, "codes")
+    if codes.dtype != _PACKED_DTYPES[(max(int(bw), 8), bool(shift_to_signed))]:
+        raise RuntimeError(f"aimet_b200: {bw}-bit {'signed' if shift_to_signed else 'unsigned'} codes cannot live in "
+                           f"{codes.dtype}")
+    codes = codes.contiguous()
+    out = torch.empty(codes.shape, dtype=torch.float32, device=codes.device)
+    with _on(codes):
+        check(lib.aq_dequantize_packed(codes.data_ptr(), out.data_ptr(), codes.numel(), float(enc_min), float(enc_max),
+                                       int(bw), int(shift_to_signed), _stream(codes)), "aq_dequantize_packed")
+    return out
+
+
 def qdq_per_channel(x: torch.Tensor, enc_min: torch.Tensor, enc_max: torch.Tensor, num_ch: int, inner: int,
                     num_steps: float, rounding_mode: int = 0) -> torch.Tensor:
     x = _f32c(x, "input").contiguous()
@@ -200,6 +229,22 @@ def v2_qdq_backward_params(x: torch.Tensor, grad: torch.Tensor, mask: torch.Tens
                                             doffset.data_ptr() if doffset is not None else None, _dt(x), x.numel(),
                                             int(num_ch), int(inner), scale.data_ptr(), offset.data_ptr(),
                                             float(qmin), float(qmax), _stream(x)), "aq_v2_qdq_backward_params")
+
+
+def v2_qdq_backward_params_reduced(x: torch.Tensor, grad: torch.Tensor, mask: torch.Tensor, want_scale: bool,
+                                   want_offset: bool, scale: torch.Tensor, offset: torch.Tensor, qmin: int, qmax: int,
+                                   num_ch: int, inner: int) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """Scale / offset gradients summed per encoding channel: float32 [num_ch] each (or None)."""
+    ds = torch.empty(num_ch, dtype=torch.float32, device=x.device) if want_scale else None
+    do = torch.empty(num_ch, dtype=torch.float32, device=x.device) if want_offset else None
+    with _on(x):
+        check(lib.aq_v2_qdq_backward_params_reduced(x.data_ptr(), grad.data_ptr(), mask.data_ptr(),
+                                                    ds.data_ptr() if ds is not None else None,
+                                                    do.data_ptr() if do is not None else None, _dt(x), x.numel(),
+                                                    int(num_ch), int(inner), scale.data_ptr(), offset.data_ptr(),
+                                                    float(qmin), float(qmax), _stream(x)),
+              "aq_v2_qdq_backward_params_reduced")
+    return ds, do
 
 
 def v2_qdq_backward(grad: torch.Tensor, mask: torch.Tensor, dx: torch.Tensor) -> None:

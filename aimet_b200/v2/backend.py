@@ -204,6 +204,15 @@ def _flat_encoding(e: torch.Tensor, g: _Geometry, narrow: Optional[torch.dtype])
     return e.reshape(-1).contiguous()
 
 
+def _encoding_from_flat(flat: torch.Tensor, g: _Geometry, enc_shape) -> torch.Tensor:
+    """Inverse of _flat_encoding: a float32 vector in channel order -> the encoding's own shape."""
+    view = list(g.enc_view)
+    if g.enc_perm != list(range(len(view))):
+        inv = [g.enc_perm.index(d) for d in range(len(view))]
+        flat = flat.reshape([view[d] for d in g.enc_perm]).permute(inv)
+    return flat.reshape(enc_shape)
+
+
 def _check_inputs(tensor: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor):
     if not tensor.is_cuda:
         raise RuntimeError("aimet_b200 backend: input must be a CUDA tensor (no CPU path exists)")
@@ -267,13 +276,13 @@ class _QuantDequantFn(torch.autograd.Function):
             ops.v2_qdq_backward(gw, mask, dxw)
             dx = g.from_work(dxw)
         if need_s or need_o:
-            dsw = torch.empty_like(gw, dtype=torch.float32) if need_s else None
-            dow = torch.empty_like(gw, dtype=torch.float32) if need_o else None
-            ops.v2_qdq_backward_params(ctx.x_keep, gw, mask, dsw, dow, sc, of, ctx.qmin, ctx.qmax, g.num_ch, g.inner)
-            if dsw is not None:
-                ds = _reduce_to_encoding(g.from_work(dsw), ctx.enc_shape, ctx.block_size)
-            if dow is not None:
-                do = _reduce_to_encoding(g.from_work(dow), ctx.enc_shape, ctx.block_size)
+            # summed per encoding channel inside the kernel: the un-reduced tensors of the reference never exist
+            dsf, dof = ops.v2_qdq_backward_params_reduced(ctx.x_keep, gw, mask, need_s, need_o, sc, of, ctx.qmin,
+                                                          ctx.qmax, g.num_ch, g.inner)
+            if dsf is not None:
+                ds = _encoding_from_flat(dsf, g, ctx.enc_shape)
+            if dof is not None:
+                do = _encoding_from_flat(dof, g, ctx.enc_shape)
                 if ctx.off_shape != ctx.enc_shape:
                     do = do.sum_to_size(ctx.off_shape)
         return dx, ds, do, None, None, None, None, None

@@ -142,6 +142,21 @@ int aq_qdq_broadcast(const float* d_in, float* d_out, int64_t n, int64_t ndims, 
                      const int64_t* h_enc_strides, const float* d_enc_min, const float* d_enc_max,
                      const float* d_enc_delta, const float* d_enc_offset, void* stream);
 
+/* Integer codes in integer containers.  Replaces TensorQuantizationSim<float>::quantizeTensorPacked ->
+ * quantizeToFxpPackedCpu (src/TensorQuantizationSim.cpp:128-139, src/trim_functions.cpp:220-385; CPU only, four host
+ * threads in the reference).  The grid is re-derived from (enc_min, enc_max, bw) as in aq_qdq_per_tensor, but clamp,
+ * divide, offset and round are evaluated in double.  bw in {1, 2, 4, 8, 16, 32}; one code per container of
+ * max(bw, 8) bits: uint8 / uint16 / uint32, or -- with shift_to_signed, which subtracts 2^(bw-1) - 1 -- int8 / int16 /
+ * int32 (sub-byte signed codes are masked to their low bw bits).  d_out: n containers, naturally aligned. */
+int aq_quantize_packed(const float* d_in, void* d_out, int64_t n, double enc_min, double enc_max, int bw,
+                       int rounding_mode, int shift_to_signed, void* stream);
+
+/* Inverse: replaces TensorQuantizationSim<float>::dequantizeTensor -> dequantizeFromPackedFxpCpu
+ * (src/TensorQuantizationSim.cpp:210-219, src/trim_functions.cpp:388-605): out = (float)(delta * (code + offset)) in
+ * double, codes read from the containers described above (signed sub-byte codes sign-extended). */
+int aq_dequantize_packed(const void* d_in, float* d_out, int64_t n, double enc_min, double enc_max, int bw,
+                         int shift_to_signed, void* stream);
+
 /* Straight-through backward of the v1 wrappers: dx = g * [enc_min <= x <= enc_max], per tensor
  * (num_ch = 1) or per channel.  Replaces compute_dloss_by_dx
  * (TrainingExtensions/torch/src/python/aimet_torch/v1/quantsim_straight_through_grad.py:91-118).
@@ -182,6 +197,16 @@ int aq_v2_dequantize(const void* d_x, void* d_y, int dtype, int64_t n, int64_t n
 int aq_v2_qdq_backward_params(const void* d_x, const void* d_grad, const uint8_t* d_mask, float* d_dscale,
                               float* d_doffset, int dtype, int64_t n, int64_t num_ch, int64_t inner,
                               const float* d_scale, const float* d_offset, double qmin, double qmax, void* stream);
+
+/* The same gradients already summed over everything an encoding is broadcast along: d_dscale / d_doffset receive
+ * num_ch floats each (either may be NULL), i.e. what autograd's reduction of the reference's un-reduced returns
+ * yields (torch_builtins.py:334-343 followed by sum_to_size).  The element-wise terms are the reference's; the order in
+ * which they are added is not (torch does not specify its own), so results agree to summation tolerance.  Reads
+ * 2 * sizeof(T) + 1 bytes per element and writes none, against 17 + 8 for the un-reduced form plus a reduction. */
+int aq_v2_qdq_backward_params_reduced(const void* d_x, const void* d_grad, const uint8_t* d_mask, float* d_dscale,
+                                      float* d_doffset, int dtype, int64_t n, int64_t num_ch, int64_t inner,
+                                      const float* d_scale, const float* d_offset, double qmin, double qmax,
+                                      void* stream);
 
 /* Replaces the tensor-gradient of QuantDequantFunc.backward (torch_builtins.py:329-344): dx = grad * mask.
  * d_mask holds one byte per element, 0 or 1 (what aq_v2_quantize writes, and how a bool tensor is stored). */

@@ -82,6 +82,8 @@ class Oracle:
         L.orc_tfe_candidates.argtypes = [_PD, _PD, C.c_int, C.c_int, C.c_int, C.c_int, _PF, _PI]
         L.orc_tfe_candidates.restype = C.c_int
         L.orc_tfe_compute.argtypes = [_PD, _PD, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
+        L.orc_quantize_packed.argtypes = [_PF, C.c_int64, _PD, C.c_int, C.c_int, C.c_void_p]
+        L.orc_dequantize_packed.argtypes = [C.c_void_p, C.c_int64, _PD, C.c_int, C.c_int, _PF]
         L.orc_percentile_compute.argtypes = [_PD, _PD, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
 
     # --- QDQ -------------------------------------------------------------------------------------
@@ -171,6 +173,27 @@ class Oracle:
         h = np.zeros(PDF_SIZE, np.uint32)
         self.lib.orc_hist512(_p(x, C.c_float), x.size, bucket_size, pdf_offset, _p(h, C.c_uint32))
         return h
+
+    @staticmethod
+    def packed_dtype(bw, signed):
+        return {(8, False): np.uint8, (8, True): np.int8, (16, False): np.uint16, (16, True): np.int16,
+                (32, False): np.uint32, (32, True): np.int32}[(max(int(bw), 8), bool(signed))]
+
+    def quantize_packed(self, x, mn, mx, bw, shift_to_signed=False):
+        x = _f32(x)
+        enc = np.ascontiguousarray(self.fill_encoding(bw, mn, mx), np.float64)
+        out = np.zeros(x.shape, self.packed_dtype(bw, shift_to_signed))
+        self.lib.orc_quantize_packed(_p(x, C.c_float), x.size, _p(enc, C.c_double), int(bw), int(shift_to_signed),
+                                     out.ctypes.data_as(C.c_void_p))
+        return out
+
+    def dequantize_packed(self, codes, mn, mx, bw, shift_to_signed=False):
+        codes = np.ascontiguousarray(codes)
+        enc = np.ascontiguousarray(self.fill_encoding(bw, mn, mx), np.float64)
+        out = np.zeros(codes.shape, np.float32)
+        self.lib.orc_dequantize_packed(codes.ctypes.data_as(C.c_void_p), codes.size, _p(enc, C.c_double), int(bw),
+                                       int(shift_to_signed), _p(out, C.c_float))
+        return out
 
     def percentile_compute(self, x_left, pdf, initialized, stats_updated, percentile, bw, symmetric=False,
                            strict=False, unsigned_sym=False):
@@ -264,6 +287,8 @@ class Reference:
             L.ref_pct_update.argtypes = [C.c_void_p, _PF, C.c_int64]
             L.ref_pct_set_percentile.argtypes = [C.c_void_p, C.c_float]
             L.ref_pct_compute.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
+            L.ref_quantize_packed.argtypes = [_PF, C.c_int64, C.c_void_p, C.c_double, C.c_double, C.c_int, C.c_int]
+            L.ref_dequantize_packed.argtypes = [C.c_void_p, C.c_int64, _PF, C.c_double, C.c_double, C.c_int, C.c_int]
             L.ref_partial_encoding.argtypes = [C.c_int, _PD, C.c_int, C.c_int, C.c_int]
             L.ref_partial_encoding.restype = C.c_int
 

@@ -602,3 +602,68 @@ void orc_percentile_compute(const double* x_left, const double* pdf, int initial
     out5[4] = bw;
 }
 
+/* ---------------------------------------------------------------------------------------------
+ * A7. Integer codes in integer containers.
+ * ------------------------------------------------------------------------------------------- */
+/* trim_functions.cpp:220-385 (quantizeToFxpPackedCpu, ROUND_NEAREST).  enc4 = {min, max, delta, offset} as
+ * orc_fill_encoding gives them.  out holds n containers of max(bw, 8) bits. */
+void orc_quantize_packed(const float* in, int64_t n, const double* enc4, int bw, int shift_to_signed, void* out)
+{
+    const double e_min = enc4[0], e_max = enc4[1], delta = enc4[2], offset = enc4[3];
+    for (int64_t i = 0; i < n; ++i)
+    {
+        double q = STD_MAX(STD_MIN((double) in[i], e_max), e_min);
+        q        = q / delta - offset;
+        q        = round(q);
+        if (!shift_to_signed)
+        {
+            if (bw < 8)
+            {
+                uint8_t small         = (uint8_t) q;
+                ((uint8_t*) out)[i] = (uint8_t) STD_MAX(STD_MIN((double) small, (double) (pow(2, bw) - 1)), 0.0);
+            }
+            else if (bw == 8)
+                ((uint8_t*) out)[i] = (uint8_t) STD_MAX(STD_MIN(q, 255.0), 0.0);
+            else if (bw == 16)
+                ((uint16_t*) out)[i] = (uint16_t) STD_MAX(STD_MIN(q, 65535.0), 0.0);
+            else
+                ((uint32_t*) out)[i] = (uint32_t) STD_MAX(STD_MIN(q, 4294967295.0), 0.0);
+        }
+        else
+        {
+            q -= pow(2, bw - 1) - 1;
+            if (bw < 8)
+            {
+                int8_t small       = (int8_t) q;
+                ((int8_t*) out)[i] = small & (int8_t) (pow(2, bw) - 1);
+            }
+            else if (bw == 8)
+                ((int8_t*) out)[i] = (int8_t) STD_MAX(STD_MIN(q, 127.0), -128.0);
+            else if (bw == 16)
+                ((int16_t*) out)[i] = (int16_t) STD_MAX(STD_MIN(q, 32767.0), -32768.0);
+            else
+                ((int32_t*) out)[i] = (int32_t) STD_MAX(STD_MIN(q, 2147483647.0), -2147483648.0);
+        }
+    }
+}
+
+/* trim_functions.cpp:388-605 (dequantizeFromPackedFxpCpu) */
+void orc_dequantize_packed(const void* in, int64_t n, const double* enc4, int bw, int is_signed, float* out)
+{
+    const double delta = enc4[2], offset = enc4[3];
+    for (int64_t i = 0; i < n; ++i)
+    {
+        double code;
+        if (!is_signed)
+            code = bw <= 8 ? (double) ((const uint8_t*) in)[i] : (bw == 16 ? (double) ((const uint16_t*) in)[i] : (double) ((const uint32_t*) in)[i]);
+        else if (bw < 8)
+        {
+            int8_t b = ((const int8_t*) in)[i];
+            code     = (b & (int8_t) pow(2, bw - 1)) ? (double) (int8_t) (~((int8_t) pow(2, bw) - 1) | b) : (double) b;
+        }
+        else
+            code = bw == 8 ? (double) ((const int8_t*) in)[i] : (bw == 16 ? (double) ((const int16_t*) in)[i] : (double) ((const int32_t*) in)[i]);
+        out[i] = (float) (delta * (code + offset));
+    }
+}
+

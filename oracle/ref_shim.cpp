@@ -200,6 +200,23 @@ void ref_pct_compute(void* h, int bw, int symmetric, int strict, int unsignedSym
     storeEncoding(e, out5);
 }
 
+// TensorQuantizationSim<float>::quantizeTensorPacked / dequantizeTensor (TensorQuantizationSim.cpp:128-139,210-219).
+// out must hold n containers of max(bw, 8) bits.
+void ref_quantize_packed(const float* in, int64_t n, void* out, double encMin, double encMax, int bw, int shiftToSigned)
+{
+    TensorQuantizationSim<float> sim;
+    std::vector<uint8_t> packed;
+    sim.quantizeTensorPacked(in, (size_t) n, packed, encMin, encMax, (uint8_t) bw, ROUND_NEAREST, false,
+                             shiftToSigned != 0);
+    std::memcpy(out, packed.data(), packed.size());
+}
+void ref_dequantize_packed(const void* in, int64_t n, float* out, double encMin, double encMax, int bw, int shiftToSigned)
+{
+    TensorQuantizationSim<float> sim;
+    sim.dequantizeTensor(static_cast<const uint8_t*>(in), (size_t) n, out, encMin, encMax, (uint8_t) bw,
+                         shiftToSigned != 0);
+}
+
 // computeMinMaxRangeFromDeltaOffset / computeDeltaAndOffsetFromMinMax (quantization_utils.cpp:158-228) the way
 // TensorQuantizer::computePartialEncoding picks between them (TensorQuantizer.cpp:327-343).  enc5 is in/out;
 // returns 1 when the reference throws.

@@ -301,3 +301,22 @@ def test_ref_partial_encoding(reference):
             compute_partial_encoding(bw, e, bool(sym), bool(uns), bool(strict))
             assert_bits_equal(np.array([e.min, e.max, e.delta, e.offset]), enc5[:4], f"{fields} {sym}{uns}{strict}")
 
+
+@pytest.mark.parametrize("bw", [1, 2, 4, 8, 16, 32])
+@pytest.mark.parametrize("signed", [False, True])
+def test_ref_packed_codes(oracle, reference, bw, signed):
+    """Integer containers: the restatement against quantizeTensorPacked / dequantizeTensor of the reference."""
+    import ctypes as C
+    x = np.concatenate([normal(5000, 3 + bw, 2.0, 0.3), np.array([0.0, -0.0, 1e-30, 4.0, -4.0, 3.99, -3.99, 100.0, -100.0], np.float32)])
+    for mn, mx in ((-3.1, 4.2), (0.0, 5.0), (-2.0, 2.0)):
+        dt = oracle.packed_dtype(bw, signed)
+        want = np.zeros(x.shape, dt)
+        reference.lib.ref_quantize_packed(x.ctypes.data_as(C.POINTER(C.c_float)), x.size, want.ctypes.data_as(C.c_void_p),
+                                          mn, mx, bw, int(signed))
+        got = oracle.quantize_packed(x, mn, mx, bw, signed)
+        np.testing.assert_array_equal(got, want, err_msg=f"codes bw={bw} signed={signed} [{mn},{mx}]")
+        back_want = np.zeros(x.shape, np.float32)
+        reference.lib.ref_dequantize_packed(want.ctypes.data_as(C.c_void_p), x.size,
+                                            back_want.ctypes.data_as(C.POINTER(C.c_float)), mn, mx, bw, int(signed))
+        assert_bits_equal(oracle.dequantize_packed(want, mn, mx, bw, signed), back_want, f"dequantize bw={bw}")
+
