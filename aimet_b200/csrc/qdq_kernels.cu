@@ -23,11 +23,26 @@ constexpr int kThreads = 256;
 #ifndef AQ_UNROLL8
 #define AQ_UNROLL8 2
 #endif
+#ifndef AQ_UNROLL4
+#define AQ_UNROLL4 4
+#endif
+#ifndef AQ_UNROLL8_PER_TENSOR
+#define AQ_UNROLL8_PER_TENSOR 1
+#endif
 // 16-byte packets in flight per thread, by packet width in elements (8 = 16-bit types)
 template <int VEC>
 __host__ __device__ constexpr int unroll_of()
 {
-    return VEC == 8 ? AQ_UNROLL8 : 4;
+    return VEC == 8 ? AQ_UNROLL8 : AQ_UNROLL4;
+}
+// v2 forward with one encoding for the whole tensor and 16-bit elements: one packet per thread and twice the CTAs
+// (measured on a [4096,11008] bf16 weight: 31.1 us against 34.1 us with two packets per thread; the blockwise form of
+// the same weight is the other way round, 40.9 us against 43.1 us, because its per-thread encoding fetch is shared
+// by both packets).
+template <int VEC, int PER_CH>
+__host__ __device__ constexpr int v2_unroll()
+{
+    return (VEC == 8 && PER_CH == 0) ? AQ_UNROLL8_PER_TENSOR : unroll_of<VEC>();
 }
 constexpr int kMaxRuns = 1026;   // chunk / inner + 2 with VEC | inner  (see make_geom)
 
@@ -555,14 +570,14 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
 {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int CHUNK = chunk_elems<VEC>();
+    constexpr int U     = v2_unroll<VEC, PER_CH>();
+    constexpr int CHUNK = kThreads * VEC * U;
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
     const int64_t hi    = a.n;
     const float qmin = a.qmin, qmax = a.qmax;
     __shared__ V2Slot s_slot[PER_CH == 1 ? kMaxRuns : 1];
     RunCtx rc {0, 0, 1, 0};
     V2Slot k0;
-    constexpr int U    = unroll_of<VEC>();
     constexpr bool ADJ = PER_CH == 2;
     if (!PER_CH)
         k0 = v2_load(a.scale, a.offset, 0, qmin, qmax);
@@ -694,8 +709,9 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
 template <typename T, int VEC, int PER_CH>
 static void launch_v2_variant(const V2Args& a, bool narrow, cudaStream_t st)
 {
-    const int64_t grid = (a.n + chunk_elems<VEC>() - 1) / chunk_elems<VEC>();
-    const unsigned g   = (unsigned) grid;
+    constexpr int64_t chunk = (int64_t) kThreads * VEC * v2_unroll<VEC, PER_CH>();
+    const int64_t grid      = (a.n + chunk - 1) / chunk;
+    const unsigned g        = (unsigned) grid;
     const bool codes = a.out_kind == AQ_V2_OUT_CODES, mask = a.mask != nullptr;
     const bool wide = (a.qmax - a.qmin) >= 2048.0f;
 #define AQ_K(MODE, NARROW, CODES, MASK, WIDE)                                                                        \
@@ -1000,21 +1016,36 @@ struct PairOf<__nv_bfloat16>
 };
 
 // v2: dx = grad * mask  (torch_builtins.py:342).  Mask bytes are 0 or 1 (as aq_v2_quantize writes them).
+// One packet per thread and 8 CTAs per SM: with four packets per thread the kernel needed 48 registers (5 CTAs per SM)
+// and a 25.7 MB gradient took 13.4 us; this form takes 10.1 us there and the same 89.6 us as before at 256 MB.
+#ifndef AQ_BWD_MINB
+#define AQ_BWD_MINB 8
+#endif
+#ifndef AQ_BWD_UNROLL
+#define AQ_BWD_UNROLL 1
+#endif
+template <int VEC>
+__host__ __device__ constexpr int bwd_unroll()
+{
+    return VEC == 8 ? AQ_UNROLL8 : AQ_BWD_UNROLL;
+}
 template <typename T, int VEC>
-__global__ void __launch_bounds__(kThreads) v2_bwd_kernel(const T* __restrict__ g, const uint8_t* __restrict__ mask,
-                                                          T* __restrict__ dx, int64_t n)
+__global__ void __launch_bounds__(kThreads, AQ_BWD_MINB) v2_bwd_kernel(const T* __restrict__ g,
+                                                                       const uint8_t* __restrict__ mask,
+                                                                       T* __restrict__ dx, int64_t n)
 {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int CHUNK = chunk_elems<VEC>();
+    constexpr int U     = bwd_unroll<VEC>();
+    constexpr int CHUNK = kThreads * VEC * U;
     const int64_t base  = (int64_t) blockIdx.x * CHUNK;
-    Pack<T, VEC> v[unroll_of<VEC>()];
-    Pack<uint8_t, VEC> m[unroll_of<VEC>()];
-    bool full[unroll_of<VEC>()];
-    load_chunk<T, VEC, unroll_of<VEC>()>(g, base, n, v, full);
-    load_chunk<uint8_t, VEC, unroll_of<VEC>()>(mask, base, n, m, full);
+    Pack<T, VEC> v[U];
+    Pack<uint8_t, VEC> m[U];
+    bool full[U];
+    load_chunk<T, VEC, U>(g, base, n, v, full);
+    load_chunk<uint8_t, VEC, U>(mask, base, n, m, full);
 #pragma unroll
-    for (int u = 0; u < unroll_of<VEC>(); ++u)
+    for (int u = 0; u < U; ++u)
     {
         const int64_t idx = base + (int64_t) (u * kThreads + threadIdx.x) * VEC;
         Pack<T, VEC> r;
@@ -1060,7 +1091,8 @@ static int launch_v2_bwd(const void* g, const uint8_t* mask, void* dx, int64_t n
         vec >>= 1;
 #define AQ_LAUNCH(V)                                                                                                 \
     {                                                                                                                \
-        int64_t grid = (n + chunk_elems<V>() - 1) / chunk_elems<V>();                                                \
+        const int64_t chunk = (int64_t) kThreads * V * bwd_unroll<V>();                                              \
+        int64_t grid        = (n + chunk - 1) / chunk;                                                               \
         launch_pdl(v2_bwd_kernel<T, V>, (unsigned) grid, kThreads, 0, st, (const T*) g, mask, (T*) dx, n);                    \
     }
     if (sizeof(T) == 2 && vec == 8)

@@ -566,7 +566,16 @@ def qdq_numbers(torch, lib, device, peak):
     mm = torch.empty(2, device=device)
     ws = torch.zeros(int(lib.aq_minmax_workspace_bytes(n1, 1, n1)), dtype=torch.uint8, device=device)
     rec("c1_minmax_4B", 4 * n1, timed([lambda i=i: lib.aq_minmax(P(xs[i]), 0, n1, 1, n1, P(mm[0:1]), P(mm[1:2]), 0, 0, P(ws), ws.numel(), stream) for i in range(nb)], 4))
-    del xs, ys, ms
+    # the same launches without the per-launch CPU cost (a ctypes call costs about as much as this kernel runs)
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(nb):
+            lib.aq_minmax(P(xs[i]), 0, n1, 1, n1, P(mm[0:1]), P(mm[1:2]), 0, 0, P(ws), ws.numel(), side.cuda_stream)
+    torch.cuda.current_stream().wait_stream(side)
+    rec("c1_minmax_4B_graph", 4 * n1, timed([graph.replay], 6) / nb)
+    del xs, ys, ms, graph
     # config 2: [512,256,3,3] fp32 per-output-channel 8-bit symmetric (launch-latency bound: 9.4 MB per launch);
     # timed launch by launch and, without the per-launch CPU cost, as one CUDA graph of all the launches
     n2, kb = 512 * 2304, 64
