@@ -498,6 +498,44 @@ int aq_v2hist_merge(const void* d_x, int dtype, int64_t n, int bins, aq_v2hist_h
                         (cudaStream_t) stream);
 }
 
+static inline bool bad_v2hist_rows(int rows, int64_t block_stride, int bins)
+{
+    return rows < 1 || block_stride < (int64_t) AQ_V2HIST_BYTES(bins) || (block_stride % 16) != 0;
+}
+
+int aq_v2hist_collect_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins,
+                           aq_v2hist_head_t* d_batches, int64_t block_stride, void* d_scratch, void* stream)
+{
+    if (bad_v2hist(d_x, dtype, n_per_row, bins, d_batches, d_scratch) || bad_v2hist_rows(rows, block_stride, bins))
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_collect_rows(d_x, dtype, n_per_row, rows, bins, d_batches, block_stride, d_scratch,
+                               (cudaStream_t) stream);
+}
+
+int aq_v2hist_merge_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, aq_v2hist_head_t* d_states,
+                         const aq_v2hist_head_t* d_batches, int64_t block_stride, int state_has_stats, void* d_scratch,
+                         float* d_updates, void* stream)
+{
+    if (bad_v2hist(d_x, dtype, n_per_row, bins, d_states, d_scratch) || !d_batches || !d_updates ||
+        bad_v2hist_rows(rows, block_stride, bins))
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_merge_rows(d_x, dtype, n_per_row, rows, bins, d_states, d_batches, block_stride, state_has_stats,
+                             d_scratch, d_updates, (cudaStream_t) stream);
+}
+
+int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,
+                        int symmetric, int num_deltas, const float* d_offsets, int num_offsets, double gamma,
+                        float* d_out, void* d_workspace, int64_t workspace_bytes, void* stream)
+{
+    if (!d_stats || bins < 1 || bins > AQ_V2HIST_MAX_BINS || !(num_steps > 0) || num_deltas < 2 || !d_offsets ||
+        num_offsets < 1 || !d_out || bad_v2hist_rows(rows, block_stride, bins))
+        return AQ_ERR_INVALID_ARG;
+    if (!d_workspace || ((uintptr_t) d_workspace % 256) != 0)
+        return AQ_ERR_WORKSPACE;
+    return v2hist_sqnr_rows(d_stats, block_stride, rows, bins, num_steps, symmetric, num_deltas, d_offsets, num_offsets,
+                            gamma, d_out, d_workspace, workspace_bytes, (cudaStream_t) stream);
+}
+
 int64_t aq_v2hist_sqnr_workspace_bytes(void)
 {
     return v2hist_sqnr_workspace_bytes();

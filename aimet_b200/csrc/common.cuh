@@ -37,11 +37,11 @@ __device__ __forceinline__ void pdl_wait()
 bool pdl_enabled();   // capi.cu: false when AQ_NO_PDL is set in the environment
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, unsigned block, size_t smem, cudaStream_t st,
                               Args... args)
 {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim            = dim3(grid, 1, 1);
+    cfg.gridDim            = grid;
     cfg.blockDim           = dim3(block, 1, 1);
     cfg.dynamicSmemBytes   = smem;
     cfg.stream             = st;

@@ -93,6 +93,14 @@ int64_t v2hist_scratch_bytes();
 int v2hist_collect(const void* x, int dtype, int64_t n, int nb, aq_v2hist_head_t* batch, void* scratch, cudaStream_t st);
 int v2hist_merge(const void* x, int dtype, int64_t n, int nb, aq_v2hist_head_t* state, const aq_v2hist_head_t* batch,
                  int state_has_stats, void* scratch, float* updates, cudaStream_t st);
+int v2hist_collect_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq_v2hist_head_t* batch,
+                        int64_t block_stride, void* scratch, cudaStream_t st);
+int v2hist_merge_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq_v2hist_head_t* state,
+                      const aq_v2hist_head_t* batch, int64_t block_stride, int state_has_stats, void* scratch,
+                      float* updates, cudaStream_t st);
+int v2hist_sqnr_rows(const aq_v2hist_head_t* stats, int64_t block_stride, int rows, int nb, double num_steps,
+                     int symmetric, int num_deltas, const float* offsets, int num_offsets, double gamma, float* out,
+                     void* ws, int64_t ws_bytes, cudaStream_t st);
 int64_t v2hist_sqnr_workspace_bytes();
 int v2hist_sqnr(const aq_v2hist_head_t* stats, int nb, double num_steps, int symmetric, int num_deltas,
                 const float* offsets, int num_offsets, double gamma, float* out, void* ws, int64_t ws_bytes,

@@ -19,6 +19,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include <type_traits>
 
 namespace aq
 {
@@ -39,6 +40,22 @@ struct V2HistScratch
     float plan[8];
 };
 
+// Several histograms per launch (per-channel observers): blockIdx.y is the histogram; these are the distances between
+// consecutive histograms' inputs, scratch areas, statistics blocks and re-binning buffers.  All zero for one histogram.
+struct V2HRows
+{
+    int64_t x_stride;     // elements
+    int64_t sc_stride;    // bytes
+    int64_t st_stride;    // bytes
+    int64_t upd_stride;   // floats
+};
+template <typename P>
+__device__ __forceinline__ P* v2h_row(P* base, int64_t stride_bytes)
+{
+    return reinterpret_cast<P*>(reinterpret_cast<char*>(const_cast<typename std::remove_const<P>::type*>(base)) +
+                                (int64_t) blockIdx.y * stride_bytes);
+}
+
 int64_t v2hist_scratch_bytes()
 {
     return (int64_t) ((sizeof(V2HistScratch) + 255) / 256 * 256);
@@ -56,10 +73,12 @@ __device__ __forceinline__ float* v2h_edges(aq_v2hist_head_t* s, int nb)
 // ---- pass 1: min / max over the finite elements -----------------------------------------------------------------
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kV2HistThreads) v2h_finite_minmax_kernel(const T* __restrict__ x, int64_t n,
-                                                                           float2* __restrict__ partials)
+                                                                           float2* __restrict__ partials, V2HRows rw)
 {
     pdl_launch_dependents();
     pdl_wait();
+    x += (int64_t) blockIdx.y * rw.x_stride;
+    partials = v2h_row(partials, rw.sc_stride);
     float mn = INFINITY, mx = -INFINITY;
     auto take = [&](float f) {
         if (fabsf(f) <= FLT_MAX)   // false for NaN and +-Inf
@@ -101,10 +120,13 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_finite_minmax_kernel(const
 // merge = 0: the batch alone (collect_stats): range = first and last bin edge of _create_bin_edges(min, max).
 // merge = 1: the widened range of merge_stats: [min(batch, state), max(batch, state)].
 __global__ void __launch_bounds__(kV2HistThreads) v2h_plan_kernel(V2HistScratch* __restrict__ sc, int nparts, int nb,
-                                                                  int merge, const aq_v2hist_head_t* __restrict__ state)
+                                                                  int merge, const aq_v2hist_head_t* __restrict__ state,
+                                                                  V2HRows rw)
 {
     pdl_launch_dependents();
     pdl_wait();
+    sc    = v2h_row(sc, rw.sc_stride);
+    state = state ? v2h_row(state, rw.st_stride) : nullptr;
     float mn = INFINITY, mx = -INFINITY;
     for (int i = threadIdx.x; i < nparts; i += kV2HistThreads)
     {
@@ -155,13 +177,15 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_plan_kernel(V2HistScratch*
 // ---- pass 2: counts with the torch.histc bin rule, plus the elements below lo and above hi ------------------------
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __restrict__ x, int64_t n,
-                                                                   V2HistScratch* __restrict__ sc, int nb)
+                                                                   V2HistScratch* __restrict__ sc, int nb, V2HRows rw)
 {
     pdl_launch_dependents();
     extern __shared__ uint32_t s_cnt[];   // nb + 2
     for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
         s_cnt[i] = 0;
     pdl_wait();
+    x += (int64_t) blockIdx.y * rw.x_stride;
+    sc = v2h_row(sc, rw.sc_stride);
     float lo = sc->plan[0], hi = sc->plan[1];
     const float cmp_lo = lo, cmp_hi = hi;
     if (lo == hi)
@@ -211,10 +235,12 @@ __device__ __forceinline__ void v2h_write_edges(float mn, float mx, int nb, floa
 
 // ---- collect_stats: the batch's own _Histogram ---------------------------------------------------------------------
 __global__ void __launch_bounds__(kV2HistThreads) v2h_finish_collect_kernel(const V2HistScratch* __restrict__ sc, int nb,
-                                                                            aq_v2hist_head_t* __restrict__ out)
+                                                                            aq_v2hist_head_t* __restrict__ out, V2HRows rw)
 {
     pdl_launch_dependents();
     pdl_wait();
+    sc  = v2h_row(sc, rw.sc_stride);
+    out = v2h_row(out, rw.st_stride);
     float* hist = v2h_hist(out);
     for (int i = threadIdx.x; i < nb; i += kV2HistThreads)
     {
@@ -256,10 +282,13 @@ __device__ __forceinline__ int v2h_bin_num(float width, float cur_min, float dat
 // once counts pass 2^24): one thread walks them in the same order; the rest is element-wise.
 __global__ void __launch_bounds__(kV2HistThreads) v2h_merge_kernel(const V2HistScratch* __restrict__ sc, int nb,
                                                                    aq_v2hist_head_t* __restrict__ state,
-                                                                   float* __restrict__ updates /* nb floats */)
+                                                                   float* __restrict__ updates /* nb floats */, V2HRows rw)
 {
     pdl_launch_dependents();
     pdl_wait();
+    sc      = v2h_row(sc, rw.sc_stride);
+    state   = v2h_row(state, rw.st_stride);
+    updates += (int64_t) blockIdx.y * rw.upd_stride;
     float* hist      = v2h_hist(state);
     const float umin = sc->plan[0], umax = sc->plan[1];
     const float cmin = state->min, cmax = state->max;
@@ -326,10 +355,12 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_merge_kernel(const V2HistS
 }
 
 __global__ void __launch_bounds__(kV2HistThreads) v2h_copy_kernel(const aq_v2hist_head_t* __restrict__ src, int nb,
-                                                                  aq_v2hist_head_t* __restrict__ dst)
+                                                                  aq_v2hist_head_t* __restrict__ dst, V2HRows rw)
 {
     pdl_launch_dependents();
     pdl_wait();
+    src = v2h_row(src, rw.st_stride);
+    dst = v2h_row(dst, rw.st_stride);
     const float* s = reinterpret_cast<const float*>(src + 1);
     float* d       = reinterpret_cast<float*>(dst + 1);
     for (int i = threadIdx.x; i < 2 * nb + 1; i += kV2HistThreads)
@@ -339,22 +370,26 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_copy_kernel(const aq_v2his
 }
 
 // ---- launchers ------------------------------------------------------------------------------------------------------
+// rows histograms of n elements each (row r starts at x + r * n), one grid row per histogram.
 template <typename T>
-static int v2h_passes(const T* x, int64_t n, int nb, int merge, const aq_v2hist_head_t* state, V2HistScratch* sc,
-                      cudaStream_t st)
+static int v2h_passes(const T* x, int64_t n, int rows, int nb, int merge, const aq_v2hist_head_t* state,
+                      V2HistScratch* sc, const V2HRows& rw, cudaStream_t st)
 {
-    const int vec      = pick_vec<T>(x, nullptr, nullptr, 0);
+    const int vec      = pick_vec<T>(x, nullptr, nullptr, rows > 1 ? n : 0);
     int64_t blocks     = (n + (int64_t) kV2HistThreads * vec * 4 - 1) / ((int64_t) kV2HistThreads * vec * 4);
-    const int64_t cap  = (int64_t) kNumSMs * 6;
+    int64_t cap        = (int64_t) kNumSMs * 6 / rows;   // about one resident wave over all rows
+    cap                = cap < 1 ? 1 : cap;
     blocks             = blocks > cap ? cap : (blocks < 1 ? 1 : blocks);
     const int nparts   = (int) (blocks < kV2HistMaxParts ? blocks : kV2HistMaxParts);
     const size_t smem  = (size_t) (nb + 2) * sizeof(uint32_t);
+    const unsigned ry  = (unsigned) rows;
 #define AQ_V2H(V)                                                                                                    \
-    launch_pdl(v2h_finite_minmax_kernel<T, V>, (unsigned) nparts, kV2HistThreads, 0, st, x, n, sc->partials);        \
+    launch_pdl(v2h_finite_minmax_kernel<T, V>, dim3((unsigned) nparts, ry), kV2HistThreads, 0, st, x, n,             \
+               sc->partials, rw);                                                                                    \
     note_launch();                                                                                                   \
-    launch_pdl(v2h_plan_kernel, 1, kV2HistThreads, 0, st, sc, nparts, nb, merge, state);                             \
+    launch_pdl(v2h_plan_kernel, dim3(1, ry), kV2HistThreads, 0, st, sc, nparts, nb, merge, state, rw);               \
     note_launch();                                                                                                   \
-    launch_pdl(v2h_count_kernel<T, V>, (unsigned) blocks, kV2HistThreads, smem, st, x, n, sc, nb);                   \
+    launch_pdl(v2h_count_kernel<T, V>, dim3((unsigned) blocks, ry), kV2HistThreads, smem, st, x, n, sc, nb, rw);     \
     note_launch();
     if (vec >= 4 && sizeof(T) == 4)
     {
@@ -372,46 +407,68 @@ static int v2h_passes(const T* x, int64_t n, int nb, int merge, const aq_v2hist_
     return check_launch();
 }
 
-static int v2h_passes_any(const void* x, int dtype, int64_t n, int nb, int merge, const aq_v2hist_head_t* state,
-                          V2HistScratch* sc, cudaStream_t st)
+static int v2h_passes_any(const void* x, int dtype, int64_t n, int rows, int nb, int merge,
+                          const aq_v2hist_head_t* state, V2HistScratch* sc, const V2HRows& rw, cudaStream_t st)
 {
     switch (dtype)
     {
-    case AQ_F32: return v2h_passes<float>((const float*) x, n, nb, merge, state, sc, st);
-    case AQ_F16: return v2h_passes<__half>((const __half*) x, n, nb, merge, state, sc, st);
-    case AQ_BF16: return v2h_passes<__nv_bfloat16>((const __nv_bfloat16*) x, n, nb, merge, state, sc, st);
+    case AQ_F32: return v2h_passes<float>((const float*) x, n, rows, nb, merge, state, sc, rw, st);
+    case AQ_F16: return v2h_passes<__half>((const __half*) x, n, rows, nb, merge, state, sc, rw, st);
+    case AQ_BF16: return v2h_passes<__nv_bfloat16>((const __nv_bfloat16*) x, n, rows, nb, merge, state, sc, rw, st);
     default: return AQ_ERR_INVALID_ARG;
     }
 }
 
-int v2hist_collect(const void* x, int dtype, int64_t n, int nb, aq_v2hist_head_t* batch, void* scratch, cudaStream_t st)
+int v2hist_collect_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq_v2hist_head_t* batch,
+                        int64_t block_stride, void* scratch, cudaStream_t st)
 {
+    if (rows < 1 || rows > 65535)
+        return AQ_ERR_TOO_LARGE;
     V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
-    int rc            = v2h_passes_any(x, dtype, n, nb, 0, nullptr, sc, st);
+    const V2HRows rw {rows > 1 ? n : 0, rows > 1 ? v2hist_scratch_bytes() : 0, rows > 1 ? block_stride : 0, 0};
+    int rc = v2h_passes_any(x, dtype, n, rows, nb, 0, nullptr, sc, rw, st);
     if (rc != AQ_OK)
         return rc;
-    launch_pdl(v2h_finish_collect_kernel, 1, kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb, batch);
+    launch_pdl(v2h_finish_collect_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb,
+               batch, rw);
     note_launch();
     return check_launch();
+}
+
+int v2hist_merge_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq_v2hist_head_t* state,
+                      const aq_v2hist_head_t* batch, int64_t block_stride, int state_has_stats, void* scratch,
+                      float* updates, cudaStream_t st)
+{
+    if (rows < 1 || rows > 65535)
+        return AQ_ERR_TOO_LARGE;
+    const V2HRows rw {rows > 1 ? n : 0, rows > 1 ? v2hist_scratch_bytes() : 0, rows > 1 ? block_stride : 0,
+                      rows > 1 ? (int64_t) nb : 0};
+    if (!state_has_stats)
+    {
+        // merge_stats on an empty observer adopts the batch's statistics as they are
+        launch_pdl(v2h_copy_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, batch, nb, state, rw);
+        note_launch();
+        return check_launch();
+    }
+    V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
+    int rc            = v2h_passes_any(x, dtype, n, rows, nb, 1, state, sc, rw, st);
+    if (rc != AQ_OK)
+        return rc;
+    launch_pdl(v2h_merge_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb, state,
+               updates, rw);
+    note_launch();
+    return check_launch();
+}
+
+int v2hist_collect(const void* x, int dtype, int64_t n, int nb, aq_v2hist_head_t* batch, void* scratch, cudaStream_t st)
+{
+    return v2hist_collect_rows(x, dtype, n, 1, nb, batch, 0, scratch, st);
 }
 
 int v2hist_merge(const void* x, int dtype, int64_t n, int nb, aq_v2hist_head_t* state, const aq_v2hist_head_t* batch,
                  int state_has_stats, void* scratch, float* updates, cudaStream_t st)
 {
-    if (!state_has_stats)
-    {
-        // merge_stats on an empty observer adopts the batch's statistics as they are
-        launch_pdl(v2h_copy_kernel, 1, kV2HistThreads, 0, st, batch, nb, state);
-        note_launch();
-        return check_launch();
-    }
-    V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
-    int rc            = v2h_passes_any(x, dtype, n, nb, 1, state, sc, st);
-    if (rc != AQ_OK)
-        return rc;
-    launch_pdl(v2h_merge_kernel, 1, kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb, state, updates);
-    note_launch();
-    return check_launch();
+    return v2hist_merge_rows(x, dtype, n, 1, nb, state, batch, 0, state_has_stats, scratch, updates, st);
 }
 
 // =================================================================================================
@@ -433,6 +490,8 @@ struct SqnrArgs
     float* noise;           // [candidates] workspace
     unsigned int* ticket;   // workspace, zero on entry, left zero
     float* out;             // {min, max}
+    int64_t st_stride;      // bytes between the statistics blocks of consecutive histograms (blockIdx.y)
+    int64_t ws_stride;      // bytes between their workspaces; results are 2 floats apart
 };
 
 __device__ __forceinline__ void sqnr_candidate(const SqnrArgs& a, float min_v, float max_v, int cand, float& delta,
@@ -471,6 +530,10 @@ __global__ void __launch_bounds__(kSqnrWarps * 32) v2h_sqnr_kernel(SqnrArgs a)
 {
     pdl_launch_dependents();
     pdl_wait();
+    a.stats  = v2h_row(a.stats, a.st_stride);
+    a.ticket = v2h_row(a.ticket, a.ws_stride);
+    a.noise  = v2h_row(a.noise, a.ws_stride);
+    a.out += 2 * (int64_t) blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_delta  = a.symmetric ? 1 : a.num_offsets + 1;
     const int candidates = a.num_deltas * per_delta;
@@ -569,9 +632,9 @@ int64_t v2hist_sqnr_workspace_bytes()
     return 256 + 4096 * (int64_t) sizeof(float);
 }
 
-int v2hist_sqnr(const aq_v2hist_head_t* stats, int nb, double num_steps, int symmetric, int num_deltas,
-                const float* offsets, int num_offsets, double gamma, float* out, void* ws, int64_t ws_bytes,
-                cudaStream_t st)
+int v2hist_sqnr_rows(const aq_v2hist_head_t* stats, int64_t block_stride, int rows, int nb, double num_steps,
+                     int symmetric, int num_deltas, const float* offsets, int num_offsets, double gamma, float* out,
+                     void* ws, int64_t ws_bytes, cudaStream_t st)
 {
     SqnrArgs a;
     a.stats = stats, a.nb = nb, a.num_steps = (float) num_steps;
@@ -581,13 +644,25 @@ int v2hist_sqnr(const aq_v2hist_head_t* stats, int nb, double num_steps, int sym
     a.ticket    = static_cast<unsigned int*>(ws);
     a.noise     = reinterpret_cast<float*>(static_cast<char*>(ws) + 256);
     a.out       = out;
+    a.st_stride = rows > 1 ? block_stride : 0;
+    a.ws_stride = rows > 1 ? v2hist_sqnr_workspace_bytes() : 0;
     const int candidates = num_deltas * (symmetric ? 1 : num_offsets + 1);
-    if (candidates < 1 || candidates > 4096 || ws_bytes < v2hist_sqnr_workspace_bytes())
+    if (rows < 1 || rows > 65535)
+        return AQ_ERR_TOO_LARGE;
+    if (candidates < 1 || candidates > 4096 || ws_bytes < (int64_t) rows * v2hist_sqnr_workspace_bytes())
         return candidates > 4096 ? AQ_ERR_TOO_LARGE : AQ_ERR_WORKSPACE;
     const int grid = (candidates + kSqnrWarps - 1) / kSqnrWarps;
-    launch_pdl(v2h_sqnr_kernel, (unsigned) grid, kSqnrWarps * 32, 0, st, a);
+    launch_pdl(v2h_sqnr_kernel, dim3((unsigned) grid, (unsigned) rows), kSqnrWarps * 32, 0, st, a);
     note_launch();
     return check_launch();
+}
+
+int v2hist_sqnr(const aq_v2hist_head_t* stats, int nb, double num_steps, int symmetric, int num_deltas,
+                const float* offsets, int num_offsets, double gamma, float* out, void* ws, int64_t ws_bytes,
+                cudaStream_t st)
+{
+    return v2hist_sqnr_rows(stats, 0, 1, nb, num_steps, symmetric, num_deltas, offsets, num_offsets, gamma, out, ws,
+                            ws_bytes, st);
 }
 
 }   // namespace aq

@@ -224,27 +224,64 @@ from .._lib import check, lib   # noqa: E402
 _DT = {torch.float32: _lib.AQ_F32, torch.float16: _lib.AQ_F16, torch.bfloat16: _lib.AQ_BF16}
 
 
-@dataclass
 class _Histogram:
-    """Host view of one histogram (reference: _Histogram, encoding_analyzer.py:57-62).  The tensors are views of the
-    device-resident statistics block; reading them synchronises like any device tensor."""
-    histogram: Optional[torch.Tensor] = None
-    bin_edges: Optional[torch.Tensor] = None
-    min: Optional[torch.Tensor] = None
-    max: Optional[torch.Tensor] = None
-    _block: Optional[torch.Tensor] = None   # the raw statistics block (header + histogram + edges)
+    """Host view of one histogram (reference: _Histogram, encoding_analyzer.py:57-62): ``histogram``, ``bin_edges``,
+    ``min``, ``max``.  When it describes device-resident statistics the four tensors are views of one row of the
+    statistics tensor, made on first access (a per-channel observer hands out thousands of these); reading their
+    values synchronises like any device tensor."""
+
+    def __init__(self, histogram=None, bin_edges=None, min=None, max=None):   # pylint: disable=redefined-builtin
+        self._fields = {"histogram": histogram, "bin_edges": bin_edges, "min": min, "max": max}
+        self._blocks = None    # [rows, words] int32 statistics tensor
+        self._row = 0
+        self._num_bins = 0
+        self._dtype = torch.float32
+        self._rows = None      # the batch these statistics were collected from, until it has been merged
 
     @staticmethod
-    def of_block(block: torch.Tensor, num_bins: int, dtype: torch.dtype) -> "_Histogram":
-        f = block.view(torch.float32)
-        hist = f[4:4 + num_bins]
-        edges = f[4 + num_bins:4 + 2 * num_bins + 1]
-        return _Histogram(hist, edges, f[0].to(dtype), f[1].to(dtype), block)
+    def of_block(blocks: torch.Tensor, row: int, num_bins: int, dtype: torch.dtype) -> "_Histogram":
+        h = _Histogram()
+        h._blocks, h._row, h._num_bins, h._dtype = blocks, row, num_bins, dtype
+        return h
+
+    @property
+    def _block(self) -> Optional[torch.Tensor]:
+        return None if self._blocks is None else self._blocks[self._row]
+
+    def _get(self, name):
+        if self._fields[name] is None and self._blocks is not None:
+            f, nb = self._blocks[self._row].view(torch.float32), self._num_bins
+            self._fields["histogram"] = f[4:4 + nb]
+            self._fields["bin_edges"] = f[4 + nb:4 + 2 * nb + 1]
+            self._fields["min"] = f[0].to(self._dtype)
+            self._fields["max"] = f[1].to(self._dtype)
+        return self._fields[name]
+
+    histogram = property(lambda self: self._get("histogram"))
+    bin_edges = property(lambda self: self._get("bin_edges"))
+    min = property(lambda self: self._get("min"))
+    max = property(lambda self: self._get("max"))
+
+    def __repr__(self):
+        return f"_Histogram(min={self.min}, max={self.max}, bins={self._num_bins})"
 
 
-def _new_block(num_bins: int, device) -> torch.Tensor:
-    words = (_lib.V2HIST_HEAD_BYTES + (2 * num_bins + 1) * 4 + 3) // 4
-    return torch.zeros(words, dtype=torch.int32, device=device)
+def _joint_blocks(stats) -> torch.Tensor:
+    """The statistics tensor whose rows the given histograms are, in order (a copy only if they are not)."""
+    blocks = stats[0]._blocks
+    if blocks is not None and blocks.shape[0] == len(stats) and all(h._blocks is blocks and h._row == i
+                                                                     for i, h in enumerate(stats)):
+        return blocks
+    return torch.stack([h._block for h in stats])
+
+
+def _block_words(num_bins: int) -> int:
+    """int32 words of one statistics block (header + histogram + edges), rounded up to 16 bytes."""
+    return ((_lib.V2HIST_HEAD_BYTES + (2 * num_bins + 1) * 4 + 15) // 16) * 4
+
+
+def _new_blocks(count: int, num_bins: int, device) -> torch.Tensor:
+    return torch.zeros((count, _block_words(num_bins)), dtype=torch.int32, device=device)
 
 
 class _HistogramObserver:
@@ -253,8 +290,9 @@ class _HistogramObserver:
     ``collect_stats`` gives the batch's own histograms (finite min / max, ``torch.histc`` counts over that range,
     infinities folded into the end bins); ``merge_stats`` widens the running histograms' range when needed, re-bins
     the old counts with the reference's split-and-round rule and counts the batch again at the widened range.  All of
-    it runs on the device, three launches per pass over the data, no host synchronisation.  With several histograms
-    (per-channel observers) the channels are processed one after the other, like the reference's Python loop.
+    it runs on the device, no host synchronisation.  With several histograms (per-channel observers) the reference
+    loops over the channels in Python; here all channels go through the same few launches (one grid row each), and
+    their statistics blocks are the rows of one tensor.
     """
 
     def __init__(self, shape: tuple, num_bins: int):
@@ -265,7 +303,9 @@ class _HistogramObserver:
         if self.num_bins > _lib.AQ_V2HIST_MAX_BINS:
             raise ValueError(f"aimet_b200: at most {_lib.AQ_V2HIST_MAX_BINS} histogram bins are supported")
         self.num_histograms = int(math.prod(self.shape))
-        self._state = None          # list of device blocks, one per histogram, once statistics exist
+        if self.num_histograms > 65535:
+            raise ValueError("aimet_b200: at most 65535 histograms per observer")
+        self._state = None          # [num_histograms, words] int32 device tensor once statistics exist
         self._dtype = torch.float32
         self._scratch = None
         self._updates = None
@@ -273,12 +313,14 @@ class _HistogramObserver:
     # ---- helpers ---------------------------------------------------------------------------------------------
     def _buffers(self, device):
         if self._scratch is None or self._scratch.device != device:
-            self._scratch = torch.empty(int(lib.aq_v2hist_scratch_bytes()), dtype=torch.uint8, device=device)
-            self._updates = torch.empty(self.num_bins, dtype=torch.float32, device=device)
+            self._scratch = torch.empty(self.num_histograms * int(lib.aq_v2hist_scratch_bytes()), dtype=torch.uint8,
+                                        device=device)
+            self._updates = torch.empty(self.num_histograms * self.num_bins, dtype=torch.float32, device=device)
         return self._scratch, self._updates
 
-    def _slices(self, input_tensor: torch.Tensor):
-        """The part of the input that belongs to each histogram, dense, in histogram order."""
+    def _rows(self, input_tensor: torch.Tensor) -> torch.Tensor:
+        """The input as a dense [num_histograms, elements per histogram] matrix, in histogram order (no copy when the
+        encoding axes already lead, e.g. a weight observed per output channel)."""
         x = input_tensor.detach()
         if not x.is_cuda:
             raise RuntimeError("aimet_b200: statistics are collected on the GPU only (no CPU path exists)")
@@ -288,28 +330,28 @@ class _HistogramObserver:
         if len(enc_shape) > x.dim() or any(s not in (1, t) for s, t in zip(enc_shape[::-1], tuple(x.shape)[::-1])):
             raise RuntimeError(f"Shape {self.shape} is incompatible with input of shape {tuple(x.shape)}")
         if self.num_histograms == 1:
-            return [x if x.is_contiguous() else x.contiguous()]
+            return x.reshape(1, -1).contiguous()
         padded = (1,) * (x.dim() - len(enc_shape)) + tuple(enc_shape)
         axes = [a for a, d in enumerate(padded) if d != 1]
         rest = [a for a in range(x.dim()) if a not in axes]
-        moved = x.permute(axes + rest).reshape(self.num_histograms, -1)
-        return [moved[i].contiguous() for i in range(self.num_histograms)]
+        return x.permute(axes + rest).reshape(self.num_histograms, -1).contiguous()
+
+    def _views(self, blocks: torch.Tensor, dtype: torch.dtype):
+        return [_Histogram.of_block(blocks, i, self.num_bins, dtype) for i in range(self.num_histograms)]
 
     # ---- observer interface ----------------------------------------------------------------------------------
     @torch.no_grad()
     def collect_stats(self, input_tensor: torch.Tensor):
-        parts = self._slices(input_tensor)
+        rows = self._rows(input_tensor)
         scratch, _ = self._buffers(input_tensor.device)
         stream = torch.cuda.current_stream(input_tensor.device).cuda_stream
-        out = []
+        blocks = _new_blocks(self.num_histograms, self.num_bins, rows.device)
         with ops._on(input_tensor):
-            for part in parts:
-                block = _new_block(self.num_bins, part.device)
-                check(lib.aq_v2hist_collect(part.data_ptr(), _DT[part.dtype], part.numel(), self.num_bins,
-                                            block.data_ptr(), scratch.data_ptr(), stream), "aq_v2hist_collect")
-                h = _Histogram.of_block(block, self.num_bins, input_tensor.dtype)
-                h._part = part
-                out.append(h)
+            check(lib.aq_v2hist_collect_rows(rows.data_ptr(), _DT[rows.dtype], rows.shape[1], self.num_histograms,
+                                             self.num_bins, blocks.data_ptr(), blocks.stride(0) * 4, scratch.data_ptr(),
+                                             stream), "aq_v2hist_collect_rows")
+        out = self._views(blocks, input_tensor.dtype)
+        out[0]._rows = rows   # kept for the merge that usually follows
         return out
 
     @torch.no_grad()
@@ -318,18 +360,18 @@ class _HistogramObserver:
         stream = torch.cuda.current_stream(input_tensor.device).cuda_stream
         first = self._state is None
         if first:
-            self._state = [_new_block(self.num_bins, input_tensor.device) for _ in range(self.num_histograms)]
+            self._state = _new_blocks(self.num_histograms, self.num_bins, input_tensor.device)
             self._dtype = input_tensor.dtype
-        parts = [getattr(h, "_part", None) for h in new_stats_list]
-        if any(p is None for p in parts):
-            parts = self._slices(input_tensor)
+        rows = new_stats_list[0]._rows
+        if rows is None:
+            rows = self._rows(input_tensor)
+        blocks = _joint_blocks(new_stats_list)
         with ops._on(input_tensor):
-            for block, new, part in zip(self._state, new_stats_list, parts):
-                check(lib.aq_v2hist_merge(part.data_ptr(), _DT[part.dtype], part.numel(), self.num_bins,
-                                          block.data_ptr(), new._block.data_ptr(), 0 if first else 1,
-                                          scratch.data_ptr(), updates.data_ptr(), stream), "aq_v2hist_merge")
-        for h in new_stats_list:
-            h._part = None   # the batch need not outlive the update
+            check(lib.aq_v2hist_merge_rows(rows.data_ptr(), _DT[rows.dtype], rows.shape[1], self.num_histograms,
+                                           self.num_bins, self._state.data_ptr(), blocks.data_ptr(),
+                                           blocks.stride(0) * 4, 0 if first else 1, scratch.data_ptr(),
+                                           updates.data_ptr(), stream), "aq_v2hist_merge_rows")
+        new_stats_list[0]._rows = None   # the batch need not outlive the update
 
     def reset_stats(self):
         self._state = None
@@ -337,7 +379,7 @@ class _HistogramObserver:
     def get_stats(self):
         if self._state is None:
             return [_Histogram() for _ in range(self.num_histograms)]
-        return [_Histogram.of_block(b, self.num_bins, self._dtype) for b in self._state]
+        return self._views(self._state, self._dtype)
 
     @property
     def stats(self):
@@ -388,22 +430,23 @@ class SqnrEncodingAnalyzer(EncodingAnalyzer):
     @torch.no_grad()
     def compute_encodings_from_stats(self, stats, num_steps: int, is_symmetric: bool) \
             -> Tuple[torch.Tensor, torch.Tensor]:
-        if stats[0].histogram is None:
+        if stats[0]._blocks is None:
             raise StatisticsNotFoundError('No statistics present to compute encodings.')
         if num_steps <= 0:
             raise ValueError('The number of quantization bins cannot be less than or equal to 0.')
-        device = stats[0]._block.device
+        device = stats[0]._blocks.device
         offsets = self._offset_grid(num_steps, bool(is_symmetric), device)
-        if self._ws is None or self._ws.device != device:
-            self._ws = torch.zeros(int(lib.aq_v2hist_sqnr_workspace_bytes()), dtype=torch.uint8, device=device)
         out = torch.empty((len(stats), 2), dtype=torch.float32, device=device)
         num_deltas = self.sym_delta_candidates if is_symmetric else self.asym_delta_candidates
         stream = torch.cuda.current_stream(device).cuda_stream
+        blocks = _joint_blocks(stats)
+        need = len(stats) * int(lib.aq_v2hist_sqnr_workspace_bytes())
+        if self._ws is None or self._ws.device != device or self._ws.numel() < need:
+            self._ws = torch.zeros(need, dtype=torch.uint8, device=device)
         with ops._on(out):
-            for i, st in enumerate(stats):
-                check(lib.aq_v2hist_sqnr(st._block.data_ptr(), self.observer.num_bins, float(num_steps),
-                                         int(bool(is_symmetric)), int(num_deltas), offsets.data_ptr(), offsets.numel(),
-                                         float(self.gamma), out[i].data_ptr(), self._ws.data_ptr(), self._ws.numel(),
-                                         stream), "aq_v2hist_sqnr")
-        dtype = stats[0].min.dtype
+            check(lib.aq_v2hist_sqnr_rows(blocks.data_ptr(), blocks.stride(0) * 4, len(stats), self.observer.num_bins,
+                                          float(num_steps), int(bool(is_symmetric)), int(num_deltas),
+                                          offsets.data_ptr(), offsets.numel(), float(self.gamma), out.data_ptr(),
+                                          self._ws.data_ptr(), self._ws.numel(), stream), "aq_v2hist_sqnr_rows")
+        dtype = stats[0]._dtype
         return out[:, 0].to(dtype).view(self.observer.shape), out[:, 1].to(dtype).view(self.observer.shape)

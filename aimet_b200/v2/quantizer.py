@@ -11,8 +11,8 @@ Host-side differences, on purpose:
 
 * scale and offset are cached between forward passes while ``min`` / ``max`` are unchanged and no gradient is
   being recorded (the reference recomputes them with five small tensor operations per call);
-* the outputs are plain tensors (the reference wraps them in tensor subclasses that carry the encoding; use
-  ``get_encoding()`` for it);
+* ``plain_outputs = True`` on a quantizer makes it return plain tensors instead of the tensor subclasses that carry
+  the encoding (:mod:`aimet_b200.v2.qtensor`);
 * ``scale = (max - min) / num_steps`` divides by a tensor, so that the CUDA result equals the reference's CPU
   result bit for bit (a CUDA tensor divided by a Python number is multiplied by its reciprocal instead).
 """
@@ -27,6 +27,7 @@ from torch import nn
 
 from . import backend
 from .encoding_analyzer import EncodingAnalyzer, MinMaxEncodingAnalyzer, StatisticsNotFoundError
+from .qtensor import DequantizedTensor, QuantizedTensor
 
 __all__ = ["AffineEncoding", "MinMaxQuantizer", "Quantize", "QuantizeDequantize"]
 
@@ -37,6 +38,23 @@ def derive_qmin_qmax(bitwidth: int, signed: bool) -> Tuple[int, int]:
     if signed:
         return -math.ceil(steps / 2), math.floor(steps / 2)
     return 0, steps
+
+
+def _grid_bitwidth(qmin: int, qmax: int, owner: str) -> int:
+    """Bit-width of a grid of the form [0, 2^B - 1] or [-2^(B-1), 2^(B-1) - 1]; undefined (RuntimeError) for any
+    other grid (affine/_utils.py:88-113)."""
+    if qmin + qmax == -1 or qmin == 0:
+        bits = math.log2(qmax - qmin + 1)
+        if bits == int(bits):
+            return int(bits)
+    raise RuntimeError(f"{owner}.bitwidth is undefined in the quantization grid [{qmin}, {qmax}].")
+
+
+def _grid_signed(qmin: int, qmax: int, owner: str) -> bool:
+    """Signedness under the same condition (affine/_utils.py:146-167)."""
+    if qmin + qmax == -1 or qmin == 0:
+        return qmin < 0 <= qmax
+    raise RuntimeError(f"{owner}.signed is undefined in the quantization grid [{qmin}, {qmax}].")
 
 
 class _RoundSte(torch.autograd.Function):
@@ -75,11 +93,11 @@ class AffineEncoding:
 
     @property
     def bitwidth(self) -> int:
-        return int(math.log2(self.num_steps + 1))
+        return _grid_bitwidth(self.qmin, self.qmax, "AffineEncoding")
 
     @property
     def signed(self) -> bool:
-        return self.qmin < 0
+        return _grid_signed(self.qmin, self.qmax, "AffineEncoding")
 
     @property
     def min(self) -> torch.Tensor:
@@ -91,17 +109,55 @@ class AffineEncoding:
 
     @property
     def dtype(self) -> torch.dtype:
-        return self.scale.dtype
+        """Smallest integer type that holds the grid (encoding.py:201-215)."""
+        if 0 <= self.qmin < self.qmax < 256:
+            return torch.uint8
+        if -128 <= self.qmin < self.qmax < 128:
+            return torch.int8
+        if -32768 <= self.qmin < self.qmax < 32768:
+            return torch.int16
+        return torch.int32
 
     def to(self, *args, **kwargs) -> "AffineEncoding":
-        return AffineEncoding(self.scale.to(*args, **kwargs), self.offset.to(*args, **kwargs), self.qmin, self.qmax,
-                              self.symmetry, self.block_size)
+        """Moves / casts scale and offset like ``Tensor.to``; only floating-point types (encoding.py:224-243)."""
+        device, dtype, _, _ = torch._C._nn._parse_to(*args, **kwargs)   # pylint: disable=protected-access
+        dtype = dtype or self.scale.dtype
+        device = device or self.scale.device
+        if dtype is self.scale.dtype and device == self.scale.device:
+            return self
+        if not dtype.is_floating_point:
+            raise RuntimeError(f"Cannot change encoding data dtype to {dtype}, "
+                               "only floating point data types are supported")
+        return AffineEncoding(self.scale.to(dtype=dtype, device=device), self.offset.to(dtype=dtype, device=device),
+                              self.qmin, self.qmax, self.symmetry, self.block_size)
+
+    def _clone(self) -> "AffineEncoding":
+        return AffineEncoding(self.scale.clone(), self.offset.clone(), self.qmin, self.qmax, self.symmetry,
+                              self.block_size)
+
+    def _detach(self) -> "AffineEncoding":
+        return AffineEncoding(self.scale.detach(), self.offset.detach(), self.qmin, self.qmax, self.symmetry,
+                              self.block_size)
 
     def quantize(self, x: torch.Tensor) -> torch.Tensor:
-        return backend.quantize(x, self.scale, self.offset, self.qmin, self.qmax, self.block_size)
+        x = x.as_subclass(torch.Tensor)
+        return backend.quantize(x, self.scale.to(x.dtype).as_subclass(torch.Tensor),
+                                self.offset.to(x.dtype).as_subclass(torch.Tensor), self.qmin, self.qmax,
+                                self.block_size)
 
     def dequantize(self, x: torch.Tensor) -> torch.Tensor:
-        return backend.dequantize(x, self.scale, self.offset, self.block_size)
+        x = x.as_subclass(torch.Tensor)
+        return backend.dequantize(x, self.scale.to(x.dtype).as_subclass(torch.Tensor),
+                                  self.offset.to(x.dtype).as_subclass(torch.Tensor), self.block_size)
+
+    def _to_legacy_format(self) -> List[dict]:
+        """One dict per channel / block, in flat order, as the exported encodings files hold them
+        (encoding.py:267-280): the offset is shifted by qmin, i.e. it is the code of the real value 0 relative to
+        an unsigned grid, and ``is_symmetric`` is the STRING "True" / "False"."""
+        rows = torch.stack([self.min.flatten().double(), self.max.flatten().double(), self.scale.flatten().double(),
+                            (self.offset.flatten() + self.qmin).double()]).cpu().tolist()
+        return [{"min": float(mn), "max": float(mx), "scale": float(sc), "offset": int(of), "bitwidth": self.bitwidth,
+                 "dtype": "int", "is_symmetric": str(self.symmetry)} for mn, mx, sc, of in zip(*rows)]
 
 
 def _encoding_shape_with_blocks(shape: Sequence[int], block_size: Optional[Sequence[int]]) -> Tuple[int, ...]:
@@ -165,6 +221,7 @@ class MinMaxQuantizer(nn.Module):
             raise RuntimeError(f"Encoding analyzer of shape {self.encoding_analyzer.observer.shape} "
                                f"is incompatible with quantizer of shape {self.shape}.")
         self._allow_overwrite = True
+        self.plain_outputs = False
         self._calibrating = False
         self._cache = None
         self.min = nn.Parameter(-torch.ones(self.shape))
@@ -184,7 +241,7 @@ class MinMaxQuantizer(nn.Module):
 
     @property
     def bitwidth(self) -> int:
-        return int(math.log2(self.qmax - self.qmin + 1))
+        return _grid_bitwidth(self.qmin, self.qmax, type(self).__qualname__)
 
     @bitwidth.setter
     def bitwidth(self, bitwidth: int):
@@ -193,7 +250,7 @@ class MinMaxQuantizer(nn.Module):
 
     @property
     def signed(self) -> bool:
-        return self.qmin < 0
+        return _grid_signed(self.qmin, self.qmax, type(self).__qualname__)
 
     def allow_overwrite(self, mode: bool):
         self._allow_overwrite = bool(mode)
@@ -273,6 +330,27 @@ class MinMaxQuantizer(nn.Module):
         return AffineEncoding(scale, offset, self.qmin, self.qmax, self._symmetric, self.block_size)
 
     @torch.no_grad()
+    def get_legacy_encodings(self) -> Optional[List[dict]]:
+        """The encodings as the list of dicts the exported files hold (affine/quantizer.py:222-232)."""
+        if not self.is_initialized():
+            return None
+        return self.get_encoding()._to_legacy_format()   # pylint: disable=protected-access
+
+    @torch.no_grad()
+    def set_legacy_encodings(self, encodings: List[dict]):
+        """Inverse of :meth:`get_legacy_encodings` (affine/quantizer.py:234-263): bit-width and symmetry come from
+        the first entry (symmetric means a signed grid, anything else an unsigned one), the range from every entry's
+        ``min`` / ``max``; scale and offset are re-derived from the range."""
+        flag = str(encodings[0]["is_symmetric"]).lower()
+        if flag not in ("true", "false"):
+            raise ValueError(f"is_symmetric must be 'True' or 'False', got {encodings[0]['is_symmetric']!r}")
+        symmetric = flag == "true"
+        self.qmin, self.qmax = derive_qmin_qmax(int(encodings[0]["bitwidth"]), signed=symmetric)
+        self.symmetric = symmetric
+        self.set_range(torch.tensor([e["min"] for e in encodings]).view(self.shape),
+                       torch.tensor([e["max"] for e in encodings]).view(self.shape))
+
+    @torch.no_grad()
     def set_range(self, min: torch.Tensor, max: torch.Tensor):   # pylint: disable=redefined-builtin
         self.min.copy_(min)
         self.max.copy_(max)
@@ -323,6 +401,16 @@ class MinMaxQuantizer(nn.Module):
             return True
         return False
 
+    def _wrap(self, out: torch.Tensor, cls, scale: torch.Tensor, offset: torch.Tensor) -> torch.Tensor:
+        """Outputs carry their encoding as the reference's do (affine/quantizer.py:549-563, 683-697) unless
+        ``plain_outputs`` is set: every later operation on such a tensor passes through a Python-level dispatch,
+        which a model wrapper that never looks at the encoding does not need to pay for."""
+        if self.plain_outputs:
+            return out
+        out = out.as_subclass(cls)
+        out.encoding = AffineEncoding(scale, offset, self.qmin, self.qmax, self._symmetric, self.block_size)
+        return out
+
     def _encoding_for(self, x: torch.Tensor, what: str) -> Tuple[torch.Tensor, torch.Tensor]:
         if self._calibrating:
             return self._dynamic_scale_offset(x)
@@ -338,8 +426,10 @@ class Quantize(MinMaxQuantizer):
     def forward(self, input: torch.Tensor) -> torch.Tensor:   # pylint: disable=redefined-builtin
         if self._observe_only(input):
             return input
+        input = input.as_subclass(torch.Tensor)
         scale, offset = self._encoding_for(input, "Quantize")
-        return backend.quantize(input, scale, offset, self.qmin, self.qmax, block_size=self.block_size)
+        out = backend.quantize(input, scale, offset, self.qmin, self.qmax, block_size=self.block_size)
+        return self._wrap(out, QuantizedTensor, scale, offset)
 
 
 class QuantizeDequantize(MinMaxQuantizer):
@@ -348,5 +438,7 @@ class QuantizeDequantize(MinMaxQuantizer):
     def forward(self, input: torch.Tensor) -> torch.Tensor:   # pylint: disable=redefined-builtin
         if self._observe_only(input):
             return input
+        input = input.as_subclass(torch.Tensor)
         scale, offset = self._encoding_for(input, "QuantizeDequantize")
-        return backend.quantize_dequantize(input, scale, offset, self.qmin, self.qmax, block_size=self.block_size)
+        out = backend.quantize_dequantize(input, scale, offset, self.qmin, self.qmax, block_size=self.block_size)
+        return self._wrap(out, DequantizedTensor, scale, offset)

@@ -123,13 +123,15 @@ class QuantizationSimModel:
         mods = dict(gm.named_modules())
         self.layers: Dict[str, QuantizedLayer] = {}
         self.activation_quantizers: Dict[str, QuantizeDequantize] = {}
+        self._activation_keys: Dict[str, tuple] = {}
         # ---- parameters ----
         for node in gm.graph.nodes:
             if node.op == "call_module" and isinstance(mods.get(node.target), _LAYERS):
                 layer = mods[node.target]
                 shape = (layer.weight.shape[0],) + (1,) * (layer.weight.dim() - 1) if per_channel_quantization else ()
-                wrapped = QuantizedLayer(layer, QuantizeDequantize(shape, self._param_bw, True,
-                                                                   self._new_analyzer(shape, for_param=True)))
+                wq = QuantizeDequantize(shape, self._param_bw, True, self._new_analyzer(shape, for_param=True))
+                wq.plain_outputs = True
+                wrapped = QuantizedLayer(layer, wq)
                 self._set_submodule(gm, node.target, wrapped)
                 self.layers[node.target] = wrapped
         mods = dict(gm.named_modules())
@@ -139,6 +141,10 @@ class QuantizationSimModel:
                 continue
             name = "act_q_" + node.name
             q = QuantizeDequantize((), self._act_bw, False, self._new_analyzer(()))
+            q.plain_outputs = True
+            # where the exported files list this quantizer: a layer's output, or the model input
+            self._activation_keys[name] = ((node.name, "input") if node.op == "placeholder" else
+                                           (node.target if node.op == "call_module" else node.name, "output"))
             gm.add_submodule(name, q)
             with gm.graph.inserting_after(node):
                 new = gm.graph.call_module(name, (node,))
@@ -196,3 +202,103 @@ class QuantizationSimModel:
                 stack.enter_context(q.compute_encodings())
             with torch.no_grad():
                 forward_pass_callback(self.model, forward_pass_callback_args)
+
+    # ---- encodings on disk -------------------------------------------------------------------------------------
+    def get_encodings_dict(self) -> dict:
+        """The calibrated encodings in the layout of the reference's ``<prefix>_torch.encodings`` file
+        (aimet_torch/v1/quantsim.py:884-938, 1028-1040): ``param_encodings`` maps ``<layer>.weight`` to one dict per
+        output channel, ``activation_encodings`` maps a layer name to ``{"input" | "output": {"0": dict}}``; every
+        dict is what ``get_legacy_encodings`` returns.  Quantizers that were never calibrated are left out."""
+        params, acts = {}, {}
+        for name, layer in self.layers.items():
+            wq = layer.param_quantizers["weight"]
+            enc = wq.get_legacy_encodings() if wq is not None else None
+            if enc is not None:
+                params[name + ".weight"] = enc
+        for name, q in self.activation_quantizers.items():
+            enc = q.get_legacy_encodings()
+            if enc is not None:
+                key, kind = self._activation_keys[name]
+                acts.setdefault(key, {}).setdefault(kind, {})["0"] = enc[0]
+        return {"version": "0.6.1", "activation_encodings": acts, "param_encodings": params, "excluded_layers": []}
+
+    def export_encodings(self, path: str, filename_prefix: str) -> str:
+        """Writes ``<path>/<filename_prefix>_torch.encodings`` (JSON) and returns its name."""
+        import json
+        import os
+        os.makedirs(path, exist_ok=True)
+        target = os.path.join(path, filename_prefix + "_torch.encodings")
+        with open(target, "w") as f:
+            json.dump(self.get_encodings_dict(), f, sort_keys=True, indent=4)
+        return target
+
+    def load_encodings(self, encodings, strict: bool = True, partial: bool = True,
+                       requires_grad: Optional[bool] = None, allow_overwrite: bool = True):
+        """Sets quantizers from an encodings dictionary or file (aimet_torch/v1/quantsim.py:1695-1756 with the
+        per-layer rules of aimet_torch/v2/nn/base.py:282-420).  ``strict``: unknown names raise; ``partial`` = False:
+        quantizers the dictionary does not mention are removed; ``requires_grad``: trainability of the loaded
+        ranges (None = unchanged); ``allow_overwrite`` = False freezes them against later calibration.  Quantizers
+        that were frozen by an earlier load are skipped."""
+        import json
+        import os
+        if isinstance(encodings, (str, os.PathLike)):
+            with open(encodings) as f:
+                encodings = json.load(f)
+        if "param_encodings" not in encodings:
+            params, acts = encodings, {}
+        else:
+            params, acts = encodings.get("param_encodings", {}), encodings.get("activation_encodings", {})
+        if not params and not acts:
+            raise RuntimeError("the encodings dictionary is empty")
+        by_key = {self._activation_keys[name]: name for name in self.activation_quantizers}
+        if strict:
+            known = {n + ".weight" for n in self.layers} | {key for key, _ in by_key}
+            missing = sorted((set(params) | set(acts)) - known)
+            if missing:
+                raise RuntimeError("Encoding dictionary contains modules/parameters that doesn't exist in the model: "
+                                   + ", ".join(missing))
+
+        def apply(q, enc):
+            q.set_legacy_encodings([enc] if isinstance(enc, dict) else list(enc))
+            if requires_grad is not None:
+                q.requires_grad_(requires_grad)
+            q.allow_overwrite(allow_overwrite)
+
+        for name, layer in self.layers.items():
+            wq = layer.param_quantizers["weight"]
+            if wq is not None and not wq._allow_overwrite:   # pylint: disable=protected-access
+                continue
+            enc = params.get(name + ".weight")
+            if not enc:
+                if not partial:
+                    layer.param_quantizers["weight"] = None
+                continue
+            if wq is None:
+                if strict:
+                    raise RuntimeError(f"Failed to import encoding of {name}.weight: no quantizer present.")
+                continue
+            apply(wq, enc)
+        for (key, kind), name in by_key.items():
+            q = self.activation_quantizers[name]
+            if not q._allow_overwrite:   # pylint: disable=protected-access
+                continue
+            enc = acts.get(key, {}).get(kind, {})
+            enc = enc.get("0", enc.get(0)) if isinstance(enc, dict) else None
+            if not enc:
+                if not partial:
+                    self._remove_activation_quantizer(name)
+                continue
+            apply(q, enc)
+
+    def _remove_activation_quantizer(self, name: str):
+        """Takes a quantizer out of the traced graph: its consumers read the tensor it used to wrap."""
+        for node in list(self.model.graph.nodes):
+            if node.op == "call_module" and node.target == name:
+                node.replace_all_uses_with(node.args[0])
+                self.model.graph.erase_node(node)
+        self.model.graph.lint()
+        self.model.recompile()
+        self.model.delete_submodule(name)
+        del self.activation_quantizers[name]
+        del self._activation_keys[name]
+

@@ -402,6 +402,21 @@ int aq_v2hist_sqnr(const aq_v2hist_head_t* d_stats, int bins, double num_steps, 
                    const float* d_offsets, int num_offsets, double gamma, float* d_out, void* d_workspace,
                    int64_t workspace_bytes, void* stream);
 
+/* The same three steps for `rows` histograms at once -- a per-channel observer, which the reference serves with a
+ * Python loop over channels (encoding_analyzer.py:158-182, 219-262, 586-600).  d_x: rows x n_per_row elements, row r
+ * dense at d_x + r * n_per_row (callers move the encoding axes to the front first).  Statistics blocks are
+ * block_stride bytes apart (>= AQ_V2HIST_BYTES(bins), a multiple of 16).  d_scratch: rows x
+ * aq_v2hist_scratch_bytes(); d_updates: rows x bins floats; d_workspace: rows x aq_v2hist_sqnr_workspace_bytes()
+ * (zero-filled before first use); d_out: rows x {min, max}.  rows <= 65535.  One set of launches whatever `rows` is. */
+int aq_v2hist_collect_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins,
+                           aq_v2hist_head_t* d_batches, int64_t block_stride, void* d_scratch, void* stream);
+int aq_v2hist_merge_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, aq_v2hist_head_t* d_states,
+                         const aq_v2hist_head_t* d_batches, int64_t block_stride, int state_has_stats, void* d_scratch,
+                         float* d_updates, void* stream);
+int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,
+                        int symmetric, int num_deltas, const float* d_offsets, int num_offsets, double gamma,
+                        float* d_out, void* d_workspace, int64_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -10,6 +10,10 @@ oracle/_ref exist; the fixtures are committed so that the tests need neither).
 * v2_quantizer.npz - aimet_torch v2 ``Quantize`` / ``QuantizeDequantize`` modules (affine/quantizer.py loaded by path,
                      CPU): outputs inside the calibration context (dynamic encodings), calibrated min / max /
                      scale / offset, outputs after calibration.
+* v2_wire_format.json - the legacy encoding dicts (``get_legacy_encodings``), their re-import
+                     (``set_legacy_encodings``), ``quantized_repr`` / ``dequantize`` of quantizer outputs and the class /
+                     encoding that results from operations on them, from the reference's own quantizer and tensor
+                     classes (CPU).
 * v1_range_learning.npz - aimet_torch v1 learned-grid functions ``calculate_forward_pass`` / ``calculate_gradients``
                      (v1/quantsim_straight_through_grad.py loaded by path, CPU): outputs, dx, min / max gradients.
 * v2_backend_reference_tests.npz - the data of the reference's OWN backend test file
@@ -242,6 +246,77 @@ def gen_quantizer(ref_root: str):
             out[f"{name}/out"] = q(probe).as_subclass(torch.Tensor).float().numpy()
         out[f"{name}/dtype"] = np.array(str(probe.dtype))
     np.savez_compressed(os.path.join(HERE, "v2_quantizer.npz"), **out)
+
+
+def wire_format_ops():
+    """(name, function) -- operations applied to a quantizer output; the fixture records what class and encoding the
+    reference's tensor subclasses give the result."""
+    return [
+        ("float16", lambda t: t.to(torch.float16)), ("double", lambda t: t.double()),
+        ("contiguous", lambda t: t.contiguous()),
+        ("view", lambda t: t.view(-1)), ("getitem", lambda t: t[0]), ("permute", lambda t: t.permute(1, 0)),
+        ("flatten_fn", lambda t: torch.flatten(t)), ("chunk", lambda t: t.chunk(2)[1]),
+        ("add", lambda t: t + 1.0), ("radd", lambda t: torch.ones(()) + t), ("mul_tensor", lambda t: t * t),
+        ("relu", lambda t: torch.relu(t)), ("add_", lambda t: t.clone().add_(1.0)),
+        ("clone", lambda t: t.clone()), ("detach", lambda t: t.detach()),
+    ]
+
+
+def gen_wire_format(ref_root: str):
+    """v2_wire_format.json: legacy encoding dicts, their re-import, and tensor-subclass behaviour, all produced by the
+    reference's own ``Quantize`` / ``QuantizeDequantize`` / ``QuantizedTensor`` classes (CPU)."""
+    import json
+    load_reference_v2(ref_root)
+    rq = load_reference_quantizer(ref_root)
+    out = {"quantizers": {}, "ops": {}}
+    for name, kind, args, kwargs, batches, probe in quantizer_cases():
+        if batches[0].dtype != torch.float32:
+            continue
+        cls = rq.QuantizeDequantize if kind == "qdq" else rq.Quantize
+        q = cls(*args, **kwargs)
+        with torch.no_grad():
+            with q.compute_encodings():
+                for x in batches:
+                    q(x)
+            enc = q.get_encoding()
+            y = q(probe)
+            try:
+                legacy = q.get_legacy_encodings()
+            except RuntimeError:
+                # a grid that is not a power of two has no bit-width, hence no legacy form
+                out["quantizers"][name] = {"legacy_error": "RuntimeError", "encoding_dtype": str(enc.dtype),
+                                           "quantized_repr": y.quantized_repr().flatten().tolist(),
+                                           "quantized_repr_dtype": str(y.quantized_repr().dtype)}
+                continue
+            rec = {"legacy": legacy, "encoding_dtype": str(enc.dtype), "granularity": enc.granularity,
+                   "bitwidth": enc.bitwidth, "signed": bool(enc.signed), "out_class": type(y).__name__,
+                   "quantized_repr": y.quantized_repr().flatten().tolist(),
+                   "quantized_repr_dtype": str(y.quantized_repr().dtype),
+                   "dequantized": y.dequantize().as_subclass(torch.Tensor).flatten().tolist(),
+                   "requantized": y.dequantize().quantize().as_subclass(torch.Tensor).flatten().tolist()}
+            # a fresh quantizer of the same shape takes the exported dicts back
+            q2 = cls(args[0], 8, False, **kwargs)   # grid and symmetry come from the dicts
+            q2.set_legacy_encodings(legacy)
+            rec["reimport"] = {"qmin": q2.qmin, "qmax": q2.qmax, "symmetric": bool(q2.symmetric),
+                               "min": q2.min.flatten().tolist(), "max": q2.max.flatten().tolist(),
+                               "scale": q2.get_scale().flatten().tolist(), "offset": q2.get_offset().flatten().tolist(),
+                               "legacy": q2.get_legacy_encodings()}
+        out["quantizers"][name] = rec
+    # propagation rules on a per-tensor and a per-channel output
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(4, 6, generator=g)
+    for tag, shape in (("pertensor", ()), ("perchannel", (4, 1))):
+        q = rq.QuantizeDequantize(shape, 8, False)
+        with torch.no_grad():
+            with q.compute_encodings():
+                q(x)
+            y = q(x)
+            for op, fn in wire_format_ops():
+                r = fn(y)
+                out["ops"][f"{tag}/{op}"] = {"class": type(r).__name__,
+                                             "has_encoding": bool(getattr(r, "encoding", None) is not None)}
+    with open(os.path.join(HERE, "v2_wire_format.json"), "w") as f:
+        json.dump(out, f, sort_keys=True)
 
 
 def range_learning_cases():
@@ -593,10 +668,10 @@ if __name__ == "__main__":
     only = sys.argv[2:]   # optionally: names of the generators to run
     gens = {"v2": lambda: gen_v2(ref), "quantizer": lambda: gen_quantizer(ref),
             "range_learning": lambda: gen_range_learning(ref), "reference_backend_tests": lambda: gen_reference_backend_tests(ref),
-            "ste_v1": lambda: gen_ste_v1(ref), "sqnr": lambda: gen_sqnr(ref), "histc_rule": gen_histc_rule, "libpymo": gen_libpymo}
+            "ste_v1": lambda: gen_ste_v1(ref), "wire_format": lambda: gen_wire_format(ref), "sqnr": lambda: gen_sqnr(ref), "histc_rule": gen_histc_rule, "libpymo": gen_libpymo}
     for name, fn in gens.items():
         if not only or name in only:
             fn()
     for f in ("v2_backend.npz", "v2_minmax.npz", "v2_quantizer.npz", "v1_range_learning.npz", "v1_ste.npz", "v2_sqnr.npz", "histc_rule.npz", "v2_backend_reference_tests.npz",
-              "libpymo.npz"):
+              "libpymo.npz", "v2_wire_format.json"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
