@@ -71,6 +71,8 @@ SIGNATURES = {
     "aq_tfe_pdf_replay": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp]),
     "aq_tfe_search_workspace_bytes": (_i64, []),
     "aq_tfe_search": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _vp]),
+    "aq_tfe_mse_workspace_bytes": (_i64, []),
+    "aq_tfe_mse_encoding": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _vp]),
     "aq_tfe_percentile_encoding": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _f64, _i32, _i32, _i32, _i32, _vp, _vp]),
     "aq_v2hist_scratch_bytes": (_i64, []),
     "aq_v2hist_collect": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp]),

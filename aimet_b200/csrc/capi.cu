@@ -469,6 +469,27 @@ int aq_tfe_percentile_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_
                           unsigned_sym, d_out_encoding, (cudaStream_t) stream);
 }
 
+int64_t aq_tfe_mse_workspace_bytes(void)
+{
+    return tfe_mse_workspace_bytes();
+}
+
+int aq_tfe_mse_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_hists, const int64_t* d_counts,
+                        int64_t num_batches, double* d_pdf, int32_t* d_iterations, int stats_updated,
+                        const int32_t* d_stats_updated, int bw, int symmetric, int strict, int unsigned_sym,
+                        double* d_out_encoding, void* d_workspace, int64_t workspace_bytes, void* stream)
+{
+    if (!d_state || !d_out_encoding || bw < 1 || bw > 32 || ((uintptr_t) d_stats_updated % 4))
+        return AQ_ERR_INVALID_ARG;
+    if (!d_workspace || ((uintptr_t) d_workspace % 256) != 0 || workspace_bytes < tfe_mse_workspace_bytes())
+        return AQ_ERR_WORKSPACE;
+    const int rc = aq_tfe_pdf_replay(d_hists, d_counts, num_batches, d_pdf, d_iterations, stream);
+    if (rc != AQ_OK)
+        return rc;
+    return tfe_mse(d_state, d_pdf, stats_updated, d_stats_updated, bw, symmetric, strict, unsigned_sym, d_out_encoding,
+                   d_workspace, (cudaStream_t) stream);
+}
+
 int64_t aq_v2hist_scratch_bytes(void)
 {
     return v2hist_scratch_bytes();

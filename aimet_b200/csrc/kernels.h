@@ -88,6 +88,9 @@ int tfe_search(const aq_tfe_state_t* st, const double* pdf, int stats_updated, c
 
 int tfe_percentile(const aq_tfe_state_t* st, const double* pdf, int stats_updated, const int32_t* stats_updated_dev,
                    float percentile, int bw, int symmetric, int strict, int unsigned_sym, double* out, cudaStream_t stream);
+int64_t tfe_mse_workspace_bytes();
+int tfe_mse(const aq_tfe_state_t* st, const double* pdf, int stats_updated, const int32_t* stats_updated_dev, int bw,
+            int symmetric, int strict, int unsigned_sym, double* out, void* ws, cudaStream_t stream);
 
 int64_t v2hist_scratch_bytes();
 int v2hist_collect(const void* x, int dtype, int64_t n, int nb, aq_v2hist_head_t* batch, void* scratch, cudaStream_t st);

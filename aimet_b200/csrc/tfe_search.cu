@@ -448,4 +448,196 @@ int tfe_percentile(const aq_tfe_state_t* st, const double* pdf, int stats_update
     return check_launch();
 }
 
+// ---- MSE analyzer on the same statistics -------------------------------------------------------------------------
+// MseEncodingAnalyzer<float>::computeEncoding (DlQuantization/src/MseEncodingAnalyzer.cpp:78-267): every pair of a
+// negative-or-zero and a positive-or-zero bucket edge inside the observed range is a (min, max) candidate -- up to
+// 66,564 of them, which the reference walks one after the other on the host; its cost is the PDF-weighted squared
+// fake-quantization error of the bucket centres, a sequential float sum over up to 513 centres whose order the result
+// depends on.  Here: one thread prepares the lists in the reference's float arithmetic, one thread per candidate
+// runs the reference's sum in order, one CTA takes the first candidate of least cost.
+constexpr int kMseMaxEdges = AQ_PDF_SIZE + 8;
+constexpr int kMseMaxCands = (AQ_PDF_SIZE / 2 + 2) * (AQ_PDF_SIZE / 2 + 2);   // (a + 1)(b + 1) with a + b <= 514
+constexpr int kMseThreads  = 128;
+
+struct MseWs
+{
+    int n_min, n_max, num_centers, done;
+    float fallback_min, fallback_max;
+    float pad[2];
+    float mins[kMseMaxEdges + 1], maxs[kMseMaxEdges + 1];
+    float centers[kMseMaxEdges], center_pdf[kMseMaxEdges];
+    float cost[kMseMaxCands];
+};
+
+int64_t tfe_mse_workspace_bytes()
+{
+    return (int64_t) ((sizeof(MseWs) + 255) / 256 * 256);
+}
+
+__global__ void tfe_mse_prepare_kernel(const aq_tfe_state_t* __restrict__ st, const double* __restrict__ pdf,
+                                       int stats_updated, const int32_t* __restrict__ stats_updated_dev, int bw,
+                                       int symmetric, int strict, MseWs* __restrict__ ws, double* __restrict__ out)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x != 0 || blockIdx.x != 0)
+        return;
+    ws->n_min = ws->n_max = ws->num_centers = 0;
+    ws->done  = 0;
+    float num_steps = (float) (ldexp(1.0, bw) - 1.0);
+    if (symmetric && strict)
+        num_steps = __fsub_rn(num_steps, 1.0f);
+    if (!st->initialized)
+    {
+        double e[5] = {0, 0, 0, 0, 0};
+        if (stats_updated_dev ? (*stats_updated_dev != 0) : (stats_updated != 0))
+        {
+            const double d = __ddiv_rn(2.0, (double) (int) num_steps);
+            const double o = floor(__ddiv_rn(-1.0, d));
+            e[0]           = __dmul_rn(o, d);
+            e[1]           = __dadd_rn(e[0], __dmul_rn((double) (int) num_steps, d));
+            e[2] = d, e[3] = o, e[4] = bw;
+        }
+        for (int i = 0; i < 5; ++i)
+            out[i] = e[i];
+        ws->done = 1;
+        return;
+    }
+    const double* __restrict__ xl = st->x_left;
+    const float bin_width = (float) __dsub_rn(xl[1], xl[0]);
+    const float hist_min  = (float) xl[0];
+    const float hist_max  = (float) __dadd_rn(xl[AQ_PDF_SIZE - 1], (double) bin_width);
+    // findOriginalRange<float> (src/math_functions.cpp:404-438)
+    float min_val = (float) xl[0], max_val = (float) xl[AQ_PDF_SIZE - 1];
+    for (int i = 0; i < AQ_PDF_SIZE; ++i)
+        if (pdf[i] > 0)
+        {
+            min_val = (float) xl[i];
+            break;
+        }
+    for (int i = AQ_PDF_SIZE - 1; i > 0; --i)
+        if (pdf[i] > 0)
+        {
+            max_val = (float) xl[i];
+            break;
+        }
+    min_val = smin(min_val, 0.0f);
+    max_val = smax(max_val, 0.0f);
+    max_val = smax(max_val, __fadd_rn(min_val, (float) 0.01));
+    max_val = __fadd_rn(max_val, bin_width);
+    ws->fallback_min = min_val, ws->fallback_max = max_val;
+    // bucket edges inside the observed range (a running float sum in the reference), split by sign as they come
+    int n_min = 0, n_max = 0, num_edges = 1;
+    if (min_val < 0)
+        ws->mins[n_min++] = min_val;
+    else if (min_val > 0)
+        ws->maxs[n_max++] = min_val;
+    float e = hist_min;
+    for (int it = 0; it < kMseMaxEdges - 1 && e <= hist_max; ++it, e = __fadd_rn(e, bin_width))
+    {
+        if (e >= min_val && e <= max_val)
+        {
+            ++num_edges;
+            if (e < 0)
+                ws->mins[n_min++] = e;
+            else if (e > 0)
+                ws->maxs[n_max++] = e;
+        }
+    }
+    ws->mins[n_min++] = 0.0f;
+    ws->maxs[n_max++] = 0.0f;
+    // bucket centres and the PDF value under each
+    const float pdf_start = (float) xl[0];
+    const int num_centers = num_edges - 1;
+    float c = 0.0f;
+    for (int i = 0; i < num_centers; ++i)
+    {
+        c       = i == 0 ? __fadd_rn(min_val, __fdiv_rn(bin_width, 2.0f)) : __fadd_rn(c, bin_width);
+        int idx = to_int_x86(floorf(__fdiv_rn(__fsub_rn(c, pdf_start), bin_width)));
+        idx     = min(max(0, idx), AQ_PDF_SIZE - 1);
+        ws->centers[i]    = c;
+        ws->center_pdf[i] = (float) pdf[idx];
+    }
+    ws->n_min = n_min, ws->n_max = n_max, ws->num_centers = num_centers;
+}
+
+__global__ void __launch_bounds__(kMseThreads) tfe_mse_cost_kernel(MseWs* __restrict__ ws, int bw, int symmetric,
+                                                                   int strict, int unsigned_sym)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n_max = ws->n_max;
+    const int cands = ws->n_min * n_max - 1;   // the last pair is {0, 0}
+    const int cand  = blockIdx.x * kMseThreads + threadIdx.x;
+    if (ws->done || cand >= cands)
+        return;
+    const float c_min = ws->mins[cand / n_max], c_max = ws->maxs[cand % n_max];
+    aq_encoding_t enc;
+    computed_encodings(bw, (double) c_min, (double) c_max, symmetric != 0, strict != 0, unsigned_sym != 0, &enc);
+    const int n = ws->num_centers;
+    float err   = 0.0f;
+    for (int i = 0; i < n; ++i)
+    {
+        const float v       = ws->centers[i];
+        const float clamped = smax(c_min, smin(v, c_max));
+        const int quantized = to_int_x86(round(__dsub_rn(__ddiv_rn((double) clamped, enc.delta), enc.offset)));
+        const float dequant = (float) __dmul_rn(enc.delta, __dadd_rn((double) quantized, enc.offset));
+        const double d      = (double) __fsub_rn(v, dequant);
+        err = (float) __dadd_rn((double) err, __dmul_rn((double) ws->center_pdf[i], __dmul_rn(d, d)));
+    }
+    ws->cost[cand] = err;
+}
+
+__global__ void __launch_bounds__(256) tfe_mse_select_kernel(MseWs* __restrict__ ws, int bw, int symmetric, int strict,
+                                                             int unsigned_sym, double* __restrict__ out)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    if (ws->done)
+        return;
+    const int n_max = ws->n_max;
+    const int cands = ws->n_min * n_max - 1;
+    // `if (mse < mseMin)` walking the candidates in order from FLT_MAX: the first candidate of least cost; NaN never wins
+    float best = FLT_MAX;
+    int best_i = INT_MAX;
+    for (int i = threadIdx.x; i < cands; i += 256)
+    {
+        const float v = ws->cost[i];
+        if (v < best)
+            best = v, best_i = i;
+    }
+    __shared__ float s_v[256];
+    __shared__ int s_i[256];
+    s_v[threadIdx.x] = best, s_i[threadIdx.x] = best_i;
+    __syncthreads();
+    if (threadIdx.x != 0)
+        return;
+    for (int t = 1; t < 256; ++t)
+        if (s_i[t] != INT_MAX && (s_v[t] < best || (s_v[t] == best && s_i[t] < best_i)))
+            best = s_v[t], best_i = s_i[t];
+    float a_min = ws->fallback_min, a_max = ws->fallback_max;
+    if (best_i != INT_MAX)
+        a_min = ws->mins[best_i / n_max], a_max = ws->maxs[best_i % n_max];
+    a_min = smin(a_min, 0.0f);
+    a_max = smax(a_max, 0.0f);
+    aq_encoding_t e;
+    computed_encodings(bw, (double) a_min, (double) a_max, symmetric != 0, strict != 0, unsigned_sym != 0, &e);
+    out[0] = e.min, out[1] = e.max, out[2] = e.delta, out[3] = e.offset, out[4] = (double) bw;
+}
+
+int tfe_mse(const aq_tfe_state_t* st, const double* pdf, int stats_updated, const int32_t* stats_updated_dev, int bw,
+            int symmetric, int strict, int unsigned_sym, double* out, void* ws, cudaStream_t stream)
+{
+    MseWs* w = static_cast<MseWs*>(ws);
+    launch_pdl(tfe_mse_prepare_kernel, 1, 32, 0, stream, st, pdf, stats_updated, stats_updated_dev, bw, symmetric, strict,
+               w, out);
+    note_launch();
+    launch_pdl(tfe_mse_cost_kernel, (unsigned) ((kMseMaxCands + kMseThreads - 1) / kMseThreads), kMseThreads, 0, stream, w,
+               bw, symmetric, strict, unsigned_sym);
+    note_launch();
+    launch_pdl(tfe_mse_select_kernel, 1, 256, 0, stream, w, bw, symmetric, strict, unsigned_sym, out);
+    note_launch();
+    return check_launch();
+}
+
 }   // namespace aq

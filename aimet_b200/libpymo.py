@@ -65,7 +65,8 @@ class TfEncoding:
 
 
 _SUPPORTED_SCHEMES = (QuantizationMode.QUANTIZATION_TF, QuantizationMode.QUANTIZATION_TF_ENHANCED,
-                      QuantizationMode.QUANTIZATION_RANGE_LEARNING, QuantizationMode.QUANTIZATION_PERCENTILE)
+                      QuantizationMode.QUANTIZATION_RANGE_LEARNING, QuantizationMode.QUANTIZATION_PERCENTILE,
+                      QuantizationMode.QUANTIZATION_MSE)
 
 
 def _require_gpu(t: torch.Tensor, use_cuda: bool, what: str):
@@ -109,9 +110,11 @@ class _TfEnhancedStats:
     """512-bucket PDF statistics on the device (TfEnhancedEncodingAnalyzer,
     DlQuantization/src/TfEnhancedEncodingAnalyzer.cpp:60-113)."""
 
-    def __init__(self, percentile_of=None):
+    def __init__(self, percentile_of=None, mse=False):
         self.dev: Optional[ops.TfeDeviceState] = None
         self.updated = False
+        #: True for the MSE analyzer (MseEncodingAnalyzer.cpp, same statistics)
+        self.mse = mse
         #: None for TF-Enhanced; for the percentile analyzer (PercentileEncodingAnalyzer.cpp, same statistics) a
         #: callable returning the percentile currently set on the owning quantizer
         self.percentile_of = percentile_of
@@ -130,7 +133,9 @@ class _TfEnhancedStats:
         st.add_batch(x)
 
     def compute(self, bw, symmetric, strict, unsigned_sym) -> TfEncoding:
-        if self.percentile_of is not None:
+        if self.mse:
+            e = self.dev.mse_encoding(self.updated, bw, symmetric, strict, unsigned_sym).tolist()
+        elif self.percentile_of is not None:
             e = self.dev.percentile_encoding(self.updated, self.percentile_of(), bw, symmetric, strict,
                                              unsigned_sym).tolist()
         else:
@@ -153,7 +158,7 @@ class AimetTensorQuantizer:
         self._scheme = QuantizationMode(quantizationScheme)
         if self._scheme not in _SUPPORTED_SCHEMES:
             raise RuntimeError(f"aimet_b200: quantization scheme {self._scheme.name} is outside the accelerated path "
-                               "(TF, TF-Enhanced and percentile are implemented)")
+                               "(TF, TF-Enhanced, percentile and MSE are implemented)")
         self._isEncodingValid = False
         self._stats = self._new_stats()
 
@@ -162,6 +167,8 @@ class AimetTensorQuantizer:
             return _TfEnhancedStats()
         if self._scheme == QuantizationMode.QUANTIZATION_PERCENTILE:
             return _TfEnhancedStats(percentile_of=self.getPercentileValue)
+        if self._scheme == QuantizationMode.QUANTIZATION_MSE:
+            return _TfEnhancedStats(mse=True)
         return _MinMaxStats()
 
     # -- statistics ----------------------------------------------------------------------------------

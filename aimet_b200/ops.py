@@ -529,6 +529,19 @@ class TfeDeviceState:
                   "aq_tfe_percentile_encoding")
         return self.encoding
 
+    def mse_encoding(self, stats_updated, bw: int, symmetric: bool, strict: bool, unsigned_sym: bool,
+                     num_batches: Optional[int] = None) -> torch.Tensor:
+        """Replay, then the MSE analyzer's candidate search on the same statistics (one call)."""
+        nb = self.num_batches if num_batches is None else num_batches
+        ws = workspace(self.state, int(lib.aq_tfe_mse_workspace_bytes()))
+        with _on(self.state):
+            check(lib.aq_tfe_mse_encoding(self._sp, self._hp, self._cp, nb, self.pdf.data_ptr(),
+                                          self.iterations.data_ptr(), int(bool(stats_updated)),
+                                          self.flags.data_ptr() if stats_updated is None else None, int(bw),
+                                          int(symmetric), int(strict), int(unsigned_sym), self.encoding.data_ptr(),
+                                          ws.data_ptr(), ws.numel(), _stream(self.state)), "aq_tfe_mse_encoding")
+        return self.encoding
+
     def x_left(self) -> torch.Tensor:
         return self.state[:_lib.AQ_PDF_SIZE * 8].view(torch.float64)
 

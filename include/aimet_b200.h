@@ -352,6 +352,21 @@ int aq_tfe_percentile_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_
                                const int32_t* d_stats_updated, double percentile, int bw, int symmetric,
                                int strict_symmetric, int unsigned_symmetric, double* d_out_encoding, void* stream);
 
+/* Bytes of scratch for aq_tfe_mse_encoding (any content; 256-byte aligned). */
+int64_t aq_tfe_mse_workspace_bytes(void);
+
+/* The MSE analyzer on the same per-batch rows: aq_tfe_pdf_replay, then MseEncodingAnalyzer<float>::computeEncoding
+ * (src/MseEncodingAnalyzer.cpp:78-267): every (negative-or-zero edge, positive-or-zero edge) pair of the buckets
+ * inside the observed range is a candidate range; its cost is the PDF-weighted squared fake-quantization error of the
+ * bucket centres (sequential float sum in the reference's order); the first candidate of least cost wins and goes
+ * through getComputedEncodings.  The reference evaluates its up to 66,564 candidates one by one on the host; here
+ * each gets a thread.  Statistics and d_stats_updated as for aq_tfe_compute_encoding. */
+int aq_tfe_mse_encoding(const aq_tfe_state_t* d_state, const uint32_t* d_hists, const int64_t* d_counts,
+                        int64_t num_batches, double* d_pdf, int32_t* d_iterations, int stats_updated,
+                        const int32_t* d_stats_updated, int bw, int symmetric, int strict_symmetric,
+                        int unsigned_symmetric, double* d_out_encoding, void* d_workspace, int64_t workspace_bytes,
+                        void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * aimet_torch v2 histogram statistics (_HistogramObserver) and SQNR range search (SqnrEncodingAnalyzer)
  * ---------------------------------------------------------------------------------------------- */

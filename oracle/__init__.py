@@ -84,6 +84,7 @@ class Oracle:
         L.orc_tfe_compute.argtypes = [_PD, _PD, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
         L.orc_quantize_packed.argtypes = [_PF, C.c_int64, _PD, C.c_int, C.c_int, C.c_void_p]
         L.orc_dequantize_packed.argtypes = [C.c_void_p, C.c_int64, _PD, C.c_int, C.c_int, _PF]
+        L.orc_mse_compute.argtypes = [_PD, _PD, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
         L.orc_percentile_compute.argtypes = [_PD, _PD, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
 
     # --- QDQ -------------------------------------------------------------------------------------
@@ -205,6 +206,15 @@ class Oracle:
                                         int(unsigned_sym), _p(out, C.c_double))
         return out
 
+    def mse_compute(self, x_left, pdf, initialized, stats_updated, bw, symmetric=False, strict=False,
+                    unsigned_sym=False):
+        out = np.zeros(5, np.float64)
+        x_left = np.ascontiguousarray(x_left, np.float64)
+        pdf = np.ascontiguousarray(pdf, np.float64)
+        self.lib.orc_mse_compute(_p(x_left, C.c_double), _p(pdf, C.c_double), int(initialized), int(stats_updated),
+                                 int(bw), int(symmetric), int(strict), int(unsigned_sym), _p(out, C.c_double))
+        return out
+
     def tfe_cost(self, x_left, pdf, bw, delta, offset):
         return self.lib.orc_tfe_cost(_p(x_left, C.c_double), _p(pdf, C.c_double), bw, delta, offset)
 
@@ -254,6 +264,12 @@ class OracleTfeAnalyzer:
                                          bw, symmetric, strict, unsigned_sym)
 
 
+    def compute_mse(self, bw, symmetric=False, strict=False, unsigned_sym=False):
+        """The MSE analyzer's encoding from the same statistics (MseEncodingAnalyzer.cpp:78-267)."""
+        return self.o.mse_compute(self.x_left, self.pdf, self.initialized.value, self.stats_updated, bw, symmetric,
+                                  strict, unsigned_sym)
+
+
 class Reference:
     """ctypes view of libaimet_ref.so (the reference's own CPU code). ``available()`` says whether it exists."""
 
@@ -287,6 +303,10 @@ class Reference:
             L.ref_pct_update.argtypes = [C.c_void_p, _PF, C.c_int64]
             L.ref_pct_set_percentile.argtypes = [C.c_void_p, C.c_float]
             L.ref_pct_compute.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
+            L.ref_mse_new.restype = C.c_void_p
+            L.ref_mse_free.argtypes = [C.c_void_p]
+            L.ref_mse_update.argtypes = [C.c_void_p, _PF, C.c_int64]
+            L.ref_mse_compute.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _PD]
             L.ref_quantize_packed.argtypes = [_PF, C.c_int64, C.c_void_p, C.c_double, C.c_double, C.c_int, C.c_int]
             L.ref_dequantize_packed.argtypes = [C.c_void_p, C.c_int64, _PF, C.c_double, C.c_double, C.c_int, C.c_int]
             L.ref_partial_encoding.argtypes = [C.c_int, _PD, C.c_int, C.c_int, C.c_int]
@@ -353,7 +373,7 @@ class Reference:
 
 
 class RefAnalyzer:
-    """Owns one reference analyzer object: kind 'tf' (MinMax), 'tfe' (TF-Enhanced) or 'pct' (percentile)."""
+    """Owns one reference analyzer object: kind 'tf' (MinMax), 'tfe' (TF-Enhanced), 'pct' (percentile) or 'mse'."""
 
     def __init__(self, ref: Reference, kind: str):
         self.ref, self.kind = ref, kind

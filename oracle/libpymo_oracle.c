@@ -603,6 +603,100 @@ void orc_percentile_compute(const double* x_left, const double* pdf, int initial
 }
 
 /* ---------------------------------------------------------------------------------------------
+ * A6b. MSE analyzer on the same 512-bucket PDF (DTYPE = float).
+ * ------------------------------------------------------------------------------------------- */
+/* MseEncodingAnalyzer.cpp:246-267 (_computeMSECost) */
+static float orc_mse_cost(int bw, const float* centers, const float* center_pdf, int num_centers, float c_min,
+                          float c_max, int symmetric, int strict, int unsigned_sym)
+{
+    double enc[5];
+    orc_computed_encodings(bw, c_min, c_max, symmetric, strict, unsigned_sym, enc);
+    const double delta = enc[2], offset = enc[3];
+    float err = 0;
+    for (int i = 0; i < num_centers; ++i)
+    {
+        float v        = centers[i];
+        float clamped  = STD_MAX(c_min, STD_MIN(v, c_max));
+        int quantized  = (int) round(clamped / delta - offset);
+        float dequant  = (float) (delta * (quantized + offset));
+        err            = (float) (err + center_pdf[i] * pow(v - dequant, 2));
+    }
+    return err;
+}
+
+/* MseEncodingAnalyzer.cpp:78-213 (computeEncoding, _minimizeMSE, _pickMinMaxCandidatesMSECalib) */
+void orc_mse_compute(const double* x_left, const double* pdf, int initialized, int stats_updated, int bw, int symmetric,
+                     int strict, int unsigned_sym, double* out5)
+{
+    for (int i = 0; i < 5; ++i)
+        out5[i] = 0;
+    float num_steps = (float) (pow(2, bw) - 1);
+    if (symmetric && strict)
+        num_steps -= 1;
+    if (!initialized)
+    {
+        if (stats_updated)
+        {
+            double e_min = -1, e_max = 1;
+            double delta  = (e_max - e_min) / (int) num_steps;
+            double offset = floor(e_min / delta);
+            e_min         = offset * delta;
+            e_max         = e_min + (int) num_steps * delta;
+            out5[0] = e_min, out5[1] = e_max, out5[2] = delta, out5[3] = offset, out5[4] = bw;
+        }
+        return;
+    }
+    const float bin_width = (float) (x_left[1] - x_left[0]);
+    float hist_min        = (float) x_left[0];
+    float hist_max        = (float) (x_left[ORC_PDF_SIZE - 1] + bin_width);
+    float min_val, max_val;
+    orc_original_range(x_left, pdf, &min_val, &max_val);
+    max_val = max_val + bin_width;
+    float edges[ORC_PDF_SIZE + 8];
+    int num_edges = 0;
+    edges[num_edges++] = min_val;
+    for (float i = hist_min; i <= hist_max; i += bin_width)
+        if (i >= min_val && i <= max_val && num_edges < ORC_PDF_SIZE + 8)
+            edges[num_edges++] = i;
+    float mins[ORC_PDF_SIZE + 9], maxs[ORC_PDF_SIZE + 9];
+    int n_min = 0, n_max = 0;
+    for (int k = 0; k < num_edges; ++k)
+    {
+        if (edges[k] < 0)
+            mins[n_min++] = edges[k];
+        else if (edges[k] > 0)
+            maxs[n_max++] = edges[k];
+    }
+    mins[n_min++] = 0, maxs[n_max++] = 0;
+    const float pdf_start = (float) x_left[0];
+    const float pdf_step  = (float) (x_left[1] - x_left[0]);
+    const int num_centers = num_edges - 1;
+    float centers[ORC_PDF_SIZE + 8], center_pdf[ORC_PDF_SIZE + 8];
+    for (int i = 0; i < num_centers; ++i)
+    {
+        centers[i] = i == 0 ? min_val + bin_width / 2 : centers[i - 1] + bin_width;
+        int idx    = (int) floorf((centers[i] - pdf_start) / pdf_step);
+        idx        = STD_MIN(STD_MAX(0, idx), ORC_PDF_SIZE - 1);
+        center_pdf[i] = (float) pdf[idx];
+    }
+    float mse_min = FLT_MAX;
+    float best_min = min_val, best_max = max_val;
+    for (int a = 0; a < n_min; ++a)
+        for (int b = 0; b < n_max; ++b)
+        {
+            if (a == n_min - 1 && b == n_max - 1)
+                break;   /* {0, 0} is not a candidate */
+            float mse = orc_mse_cost(bw, centers, center_pdf, num_centers, mins[a], maxs[b], symmetric, strict, unsigned_sym);
+            if (mse < mse_min)
+                mse_min = mse, best_min = mins[a], best_max = maxs[b];
+        }
+    best_min = STD_MIN(best_min, 0.0f);
+    best_max = STD_MAX(best_max, 0.0f);
+    orc_computed_encodings(bw, best_min, best_max, symmetric, strict, unsigned_sym, out5);
+    out5[4] = bw;
+}
+
+/* ---------------------------------------------------------------------------------------------
  * A7. Integer codes in integer containers.
  * ------------------------------------------------------------------------------------------- */
 /* trim_functions.cpp:220-385 (quantizeToFxpPackedCpu, ROUND_NEAREST).  enc4 = {min, max, delta, offset} as

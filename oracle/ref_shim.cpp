@@ -18,6 +18,7 @@
 #include "DlQuantization/Quantization.hpp"
 #include "TensorQuantizationSim.h"
 #include "TfEncodingAnalyzer.h"
+#include "MseEncodingAnalyzer.h"
 #include "PercentileEncodingAnalyzer.h"
 #include "TfEnhancedEncodingAnalyzer.h"
 #include "math_functions.hpp"
@@ -197,6 +198,26 @@ void ref_pct_compute(void* h, int bw, int symmetric, int strict, int unsignedSym
 {
     TfEncoding e = static_cast<PercentileEncodingAnalyzer<float>*>(h)->computeEncoding(
         (uint8_t) bw, symmetric != 0, strict != 0, unsignedSym != 0);
+    storeEncoding(e, out5);
+}
+
+// ---- MseEncodingAnalyzer<float> ----------------------------------------------------------------
+void* ref_mse_new()
+{
+    return new MseEncodingAnalyzer<float>();
+}
+void ref_mse_free(void* h)
+{
+    delete static_cast<MseEncodingAnalyzer<float>*>(h);
+}
+void ref_mse_update(void* h, const float* in, int64_t n)
+{
+    static_cast<MseEncodingAnalyzer<float>*>(h)->updateStats(in, (size_t) n, COMP_MODE_CPU);
+}
+void ref_mse_compute(void* h, int bw, int symmetric, int strict, int unsignedSym, double* out5)
+{
+    TfEncoding e = static_cast<MseEncodingAnalyzer<float>*>(h)->computeEncoding((uint8_t) bw, symmetric != 0,
+                                                                                strict != 0, unsignedSym != 0);
     storeEncoding(e, out5);
 }
 

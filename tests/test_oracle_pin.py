@@ -285,6 +285,26 @@ def test_ref_percentile(oracle, reference, kinds):
             assert_bits_equal(got[:4], want[:4], f"percentile {pct} bw={bw} sym={sym}{strict}{uns}")
 
 
+@pytest.mark.parametrize("kinds", [("relu",) * 4, ("normal",) * 3, ("zeros", "zeros", "relu"), ("neg", "neg"), ("zeros",),
+                                   ("pos",) * 2])
+def test_ref_mse(oracle, reference, kinds):
+    """The MSE restatement against the reference's MseEncodingAnalyzer on the same batches."""
+    from oracle import OracleTfeAnalyzer, RefAnalyzer
+    gens = {"relu": lambda s: relu_activations(7001, s), "normal": lambda s: normal(7001, s, 2.0, 1.0),
+            "neg": lambda s: normal(7001, s, 1.0, -6.0), "pos": lambda s: normal(7001, s, 0.5, 4.0),
+            "zeros": lambda s: np.zeros(500, np.float32)}
+    batches = [gens[k](41 + i) for i, k in enumerate(kinds)]
+    oa = OracleTfeAnalyzer(oracle)
+    ra = RefAnalyzer(reference, "mse")
+    for b in batches:
+        oa.update(b)
+        ra.update(b)
+    for bw, sym, strict, uns in ((8, 0, 0, 0), (8, 1, 0, 0), (4, 0, 0, 0), (4, 1, 1, 0), (16, 1, 0, 1), (2, 0, 0, 0)):
+        want = ra.compute(bw, sym, strict, uns)
+        got = oa.compute_mse(bw, sym, strict, uns)
+        assert_bits_equal(got[:4], want[:4], f"mse bw={bw} sym={sym}{strict}{uns}")
+
+
 def test_ref_partial_encoding(reference):
     """compute_partial_encoding (host arithmetic of the libpymo mirror) against the reference's two helper functions."""
     import ctypes as C

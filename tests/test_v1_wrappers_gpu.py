@@ -137,6 +137,26 @@ def test_percentile_scheme_matches_oracle(oracle, cuda, kinds, pct):
         assert_bits_equal(enc5(enc), oa.compute_percentile(pct, bw, sym, strict, uns), f"pct={pct} bw={bw} {sym}{strict}{uns}")
 
 
+@pytest.mark.parametrize("kinds", [("relu",) * 3, ("normal",) * 2, ("zeros", "relu"), ("zeros",), ("neg", "neg")])
+def test_mse_scheme_matches_oracle(oracle, cuda, kinds):
+    """MseEncodingAnalyzer on the device against the C restatement (which test_oracle_pin.py pins to the reference)."""
+    from oracle import OracleTfeAnalyzer
+    from aimet_b200 import libpymo
+    gens = {"relu": lambda s: relu_activations(50001, s), "zeros": lambda s: np.zeros(3000, np.float32),
+            "normal": lambda s: normal(40000, s, 2.0, 1.0), "neg": lambda s: normal(40000, s, 1.0, -6.0)}
+    batches = [gens[k](21 + i) for i, k in enumerate(kinds)]
+    q = libpymo.AimetTensorQuantizer(libpymo.QUANTIZATION_MSE)
+    oa = OracleTfeAnalyzer(oracle)
+    for b in batches:
+        q.updateStats(dev(b, cuda), True)
+        oa.update(b)
+    for bw, sym, strict, uns in ((8, False, False, False), (8, True, False, False), (4, False, False, False),
+                                 (4, True, True, False), (16, True, False, True), (2, False, False, False)):
+        enc, valid = q.getEncoding(bw, sym, strict, uns)
+        assert valid
+        assert_bits_equal(enc5(enc), oa.compute_mse(bw, sym, strict, uns), f"mse bw={bw} {sym}{strict}{uns}")
+
+
 def test_numpy_facing_mirrors(oracle, cuda):
     from oracle import OracleTfeAnalyzer
     from aimet_b200 import libpymo
