@@ -533,7 +533,11 @@ class TfeDeviceState:
                      num_batches: Optional[int] = None) -> torch.Tensor:
         """Replay, then the MSE analyzer's candidate search on the same statistics (one call)."""
         nb = self.num_batches if num_batches is None else num_batches
-        ws = workspace(self.state, int(lib.aq_tfe_mse_workspace_bytes()))
+        # scratch of its own: the shared per-stream workspace must stay zero where other kernels keep their tickets
+        ws = getattr(self, "_mse_ws", None)
+        if ws is None:
+            ws = self._mse_ws = torch.empty(int(lib.aq_tfe_mse_workspace_bytes()), dtype=torch.uint8,
+                                            device=self.state.device)
         with _on(self.state):
             check(lib.aq_tfe_mse_encoding(self._sp, self._hp, self._cp, nb, self.pdf.data_ptr(),
                                           self.iterations.data_ptr(), int(bool(stats_updated)),

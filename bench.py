@@ -775,6 +775,7 @@ def main():
                     help="whole-model calibration / fake-quant measurement instead of the calibration job")
     ap.add_argument("--batches", type=int, default=32, help="calibration batches for --model-case resnet50")
     ap.add_argument("--batch-size", type=int, default=128, help="batch size for --model-case resnet50")
+    ap.add_argument("--scheme", default=None, help="quant scheme for --model-case resnet50 (default: the case's own)")
     args = ap.parse_args()
     if args.model_case:
         import torch
@@ -784,6 +785,8 @@ def main():
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(dev)
         kw = {"batches": args.batches, "batch_size": args.batch_size} if args.model_case == "resnet50" else {}
+        if args.scheme and args.model_case == "resnet50":
+            kw["scheme"] = args.scheme
         print(json.dumps(model_cases.CASES[args.model_case](dev, **kw)), flush=True)
     elif args.kernel_case:
         run_kernel_case(args)
