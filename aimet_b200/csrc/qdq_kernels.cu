@@ -1194,12 +1194,38 @@ __global__ void __launch_bounds__(kThreads) v2_param_grad_kernel(V2GradArgs a)
         {
             if (PER_CH)
             {
-                if (idx < a.n)
+                // A warp's 32 packets are consecutive, so they nearly always lie in one run: the warp adds them up with
+                // shuffles and issues one shared atomic (thirty-two floating-point atomics on one shared address
+                // serialise: rows of 2304 elements ran at 0.06 of the copy bandwidth that way).
+                const bool active     = idx < a.n;
+                const unsigned livems = __ballot_sync(0xffffffffu, active);
+                if (livems)
                 {
-                    if (a.dscale)
-                        atomicAdd(&s_ds[lr], ps);
-                    if (a.doffset)
-                        atomicAdd(&s_do[lr], po);
+                    const int leader   = __ffs(livems) - 1;
+                    const uint32_t lrl = __shfl_sync(0xffffffffu, lr, leader);
+                    if (__all_sync(0xffffffffu, !active || lr == lrl))
+                    {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1)
+                        {
+                            ps += __shfl_xor_sync(0xffffffffu, ps, o);
+                            po += __shfl_xor_sync(0xffffffffu, po, o);
+                        }
+                        if ((threadIdx.x & 31) == leader)
+                        {
+                            if (a.dscale)
+                                atomicAdd(&s_ds[lrl], ps);
+                            if (a.doffset)
+                                atomicAdd(&s_do[lrl], po);
+                        }
+                    }
+                    else if (active)
+                    {
+                        if (a.dscale)
+                            atomicAdd(&s_ds[lr], ps);
+                        if (a.doffset)
+                            atomicAdd(&s_do[lr], po);
+                    }
                 }
             }
             else

@@ -24,6 +24,19 @@ from .backend import resolve_geometry
 _MINIMUM_SCALE = torch.finfo(torch.float32).eps
 
 
+_SCALARS = {}
+
+
+def device_scalar(value: float, dtype: torch.dtype, device) -> torch.Tensor:
+    """A 0-dim device tensor holding ``value``, made once per (value, dtype, device): creating one per call costs a
+    host-to-device copy each time, and the encoding arithmetic needs three or four of them per quantizer."""
+    key = (float(value), dtype, str(device))
+    t = _SCALARS.get(key)
+    if t is None:
+        t = _SCALARS[key] = torch.tensor(float(value), dtype=dtype, device=device)
+    return t
+
+
 class StatisticsNotFoundError(RuntimeError):
     """No statistics were collected before encodings were requested (aimet_torch/v2/utils.py)."""
 
@@ -128,7 +141,7 @@ class MinMaxEncodingAnalyzer(EncodingAnalyzer):
         # Divisors are 0-dim device tensors, not Python scalars: dividing a CUDA tensor by a host scalar is
         # evaluated as a multiplication by the reciprocal, which is not the IEEE quotient the CPU reference gets.
         def divisor(v):
-            return torch.tensor(float(v), dtype=torch.float32, device=stats.min.device)
+            return device_scalar(v, torch.float32, stats.min.device)
 
         min_with_zero = torch.clamp(stats.min, max=0)
         max_with_zero = torch.clamp(stats.max, min=0)

@@ -26,7 +26,7 @@ import torch
 from torch import nn
 
 from . import backend
-from .encoding_analyzer import EncodingAnalyzer, MinMaxEncodingAnalyzer, StatisticsNotFoundError
+from .encoding_analyzer import EncodingAnalyzer, MinMaxEncodingAnalyzer, StatisticsNotFoundError, device_scalar
 from .qtensor import DequantizedTensor, QuantizedTensor
 
 __all__ = ["AffineEncoding", "MinMaxQuantizer", "Quantize", "QuantizeDequantize"]
@@ -291,7 +291,7 @@ class MinMaxQuantizer(nn.Module):
         if not recording and self._cache is not None and all(a is b if isinstance(a, torch.Tensor) else a == b
                                                              for a, b in zip(self._cache[0], key)):
             return self._cache[1], self._cache[2]
-        steps = torch.tensor(float(self.qmax - self.qmin), dtype=dtype, device=self.min.device)
+        steps = device_scalar(self.qmax - self.qmin, dtype, self.min.device)
         scale = ((self.max.to(dtype) - self.min.to(dtype)) / steps).to(dtype)
         if self._symmetric:
             offset = torch.zeros_like(self.min, requires_grad=False, dtype=dtype)
@@ -389,7 +389,7 @@ class MinMaxQuantizer(nn.Module):
             dmin, dmax = dmin.view(self.min.shape), dmax.view(self.max.shape)
         dmin = dmin.to(dtype=self.min.dtype, device=self.min.device).expand_as(self.min)
         dmax = dmax.to(dtype=self.max.dtype, device=self.max.device).expand_as(self.max)
-        div = torch.tensor(float(steps), dtype=torch.float32, device=dmin.device)
+        div = device_scalar(steps, torch.float32, dmin.device)
         scale = (dmax.to(torch.float32) - dmin.to(torch.float32)) / div
         offset = torch.zeros_like(scale) if self._symmetric else torch.round(dmin.to(torch.float32) / scale) - self.qmin
         return scale, offset

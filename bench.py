@@ -612,7 +612,8 @@ def qdq_numbers(torch, lib, device, peak):
 # ---------------------------------------------------------------------------------------------------------------------
 KERNEL_CASES = ("tfe_hist", "tfe_hist_many", "tfe_offer_grid", "minmax_f32", "minmax_f32_rows", "minmax_bf16_block64", "v2_qdq_f32", "v2_qdq_f32_mask",
                 "v2_qdq_f32_per_channel", "v2_qdq_bf16", "v2_qdq_bf16_block64", "v2_bwd_f32", "v2_bwd_bf16",
-                "pymo_qdq_f32", "pymo_qdq_f32_per_channel", "ste_v1_f32", "tfe_replay", "tfe_search")
+                "pymo_qdq_f32", "pymo_qdq_f32_per_channel", "ste_v1_f32", "tfe_replay", "tfe_search",
+                "v2_param_grad_f32_per_channel", "pymo_broadcast_f32")
 
 
 def build_kernel_case(name, mb, torch, lib, device):
@@ -712,6 +713,28 @@ def build_kernel_case(name, mb, torch, lib, device):
         calls = [lambda i=i: lib.aq_v2_quantize(P(xs[i]), P(ys[i]), P(ms[i]) if ms else None, dt, n, num_ch, inner, P(s), P(o),
                                                 qmin, qmax, 0, 0, stream) for i in range(nbuf)]
         return calls, (2 * esz + (1 if ms else 0)) * n + (8 * num_ch if num_ch > 1 else 0), [s, o, ms, ys] + xs
+    if name == "v2_param_grad_f32_per_channel":
+        # scale / offset gradients summed per channel inside the kernel: rows of 2304 elements, 8-bit signed grid
+        num_ch, inner = n // 2304, 2304
+        s, o = torch.full((num_ch,), 0.03, device=device), torch.zeros(num_ch, device=device)
+        gs = [torch.randn(n, device=device) for _ in range(nbuf)]
+        ms = [(torch.rand(n, device=device) < 0.97).to(torch.uint8) for _ in range(nbuf)]
+        ds, do = torch.empty(num_ch, device=device), torch.empty(num_ch, device=device)
+        calls = [lambda i=i: lib.aq_v2_qdq_backward_params_reduced(P(xs[i]), P(gs[i]), P(ms[i]), P(ds), P(do), 0, n, num_ch,
+                                                                   inner, P(s), P(o), -128.0, 127.0, stream)
+                 for i in range(nbuf)]
+        return calls, 9 * n + 16 * num_ch, [s, o, gs, ms, ds, do] + xs
+    if name == "pymo_broadcast_f32":
+        # encodings interleaved with broadcast dimensions ([R, 1, 3] against a [R, 768, 3] tensor): the only shape that
+        # does not reduce to channel = (i / inner) % num_ch and therefore takes the general strided kernel
+        import ctypes as C
+        R = n // 2304
+        enc = [torch.full((R * 3,), v, device=device) for v in (-4.0, 4.0, 8.0 / 255.0, -128.0)]
+        in_strides = (C.c_int64 * 3)(2304, 3, 1)
+        enc_strides = (C.c_int64 * 3)(3, 0, 1)
+        calls = [lambda i=i: lib.aq_qdq_broadcast(P(xs[i]), P(ys[i]), n, 3, in_strides, enc_strides, P(enc[0]), P(enc[1]),
+                                                  P(enc[2]), P(enc[3]), stream) for i in range(nbuf)]
+        return calls, 8 * n + 16 * R * 3, [enc, in_strides, enc_strides, ys] + xs
     if name == "pymo_qdq_f32":
         calls = [lambda i=i: lib.aq_qdq_per_tensor(P(xs[i]), P(ys[i]), n, -4.4, 4.6, 8, 0, stream) for i in range(nbuf)]
         return calls, 8 * n, [ys] + xs
