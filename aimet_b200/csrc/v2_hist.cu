@@ -121,17 +121,27 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_finite_minmax_kernel(const
 // merge = 1: the widened range of merge_stats: [min(batch, state), max(batch, state)].
 __global__ void __launch_bounds__(kV2HistThreads) v2h_plan_kernel(V2HistScratch* __restrict__ sc, int nparts, int nb,
                                                                   int merge, const aq_v2hist_head_t* __restrict__ state,
-                                                                  V2HRows rw)
+                                                                  const aq_v2hist_head_t* __restrict__ batch, V2HRows rw)
 {
     pdl_launch_dependents();
     pdl_wait();
     sc    = v2h_row(sc, rw.sc_stride);
     state = state ? v2h_row(state, rw.st_stride) : nullptr;
+    batch = batch ? v2h_row(batch, rw.st_stride) : nullptr;
     float mn = INFINITY, mx = -INFINITY;
-    for (int i = threadIdx.x; i < nparts; i += kV2HistThreads)
+    if (batch)
     {
-        mn = fminf(mn, sc->partials[i].x);
-        mx = fmaxf(mx, sc->partials[i].y);
+        // the batch's own statistics already hold its finite min / max: no second pass over the data for them
+        if (!batch->error)
+            mn = batch->min, mx = batch->max;
+    }
+    else
+    {
+        for (int i = threadIdx.x; i < nparts; i += kV2HistThreads)
+        {
+            mn = fminf(mn, sc->partials[i].x);
+            mx = fmaxf(mx, sc->partials[i].y);
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
@@ -373,7 +383,7 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_copy_kernel(const aq_v2his
 // rows histograms of n elements each (row r starts at x + r * n), one grid row per histogram.
 template <typename T>
 static int v2h_passes(const T* x, int64_t n, int rows, int nb, int merge, const aq_v2hist_head_t* state,
-                      V2HistScratch* sc, const V2HRows& rw, cudaStream_t st)
+                      const aq_v2hist_head_t* batch, V2HistScratch* sc, const V2HRows& rw, cudaStream_t st)
 {
     const int vec      = pick_vec<T>(x, nullptr, nullptr, rows > 1 ? n : 0);
     int64_t blocks     = (n + (int64_t) kV2HistThreads * vec * 4 - 1) / ((int64_t) kV2HistThreads * vec * 4);
@@ -384,10 +394,13 @@ static int v2h_passes(const T* x, int64_t n, int rows, int nb, int merge, const 
     const size_t smem  = (size_t) (nb + 2) * sizeof(uint32_t);
     const unsigned ry  = (unsigned) rows;
 #define AQ_V2H(V)                                                                                                    \
-    launch_pdl(v2h_finite_minmax_kernel<T, V>, dim3((unsigned) nparts, ry), kV2HistThreads, 0, st, x, n,             \
-               sc->partials, rw);                                                                                    \
-    note_launch();                                                                                                   \
-    launch_pdl(v2h_plan_kernel, dim3(1, ry), kV2HistThreads, 0, st, sc, nparts, nb, merge, state, rw);               \
+    if (!batch)                                                                                                      \
+    {                                                                                                                \
+        launch_pdl(v2h_finite_minmax_kernel<T, V>, dim3((unsigned) nparts, ry), kV2HistThreads, 0, st, x, n,         \
+                   sc->partials, rw);                                                                                \
+        note_launch();                                                                                               \
+    }                                                                                                                \
+    launch_pdl(v2h_plan_kernel, dim3(1, ry), kV2HistThreads, 0, st, sc, nparts, nb, merge, state, batch, rw);        \
     note_launch();                                                                                                   \
     launch_pdl(v2h_count_kernel<T, V>, dim3((unsigned) blocks, ry), kV2HistThreads, smem, st, x, n, sc, nb, rw);     \
     note_launch();
@@ -408,13 +421,15 @@ static int v2h_passes(const T* x, int64_t n, int rows, int nb, int merge, const 
 }
 
 static int v2h_passes_any(const void* x, int dtype, int64_t n, int rows, int nb, int merge,
-                          const aq_v2hist_head_t* state, V2HistScratch* sc, const V2HRows& rw, cudaStream_t st)
+                          const aq_v2hist_head_t* state, const aq_v2hist_head_t* batch, V2HistScratch* sc,
+                          const V2HRows& rw, cudaStream_t st)
 {
     switch (dtype)
     {
-    case AQ_F32: return v2h_passes<float>((const float*) x, n, rows, nb, merge, state, sc, rw, st);
-    case AQ_F16: return v2h_passes<__half>((const __half*) x, n, rows, nb, merge, state, sc, rw, st);
-    case AQ_BF16: return v2h_passes<__nv_bfloat16>((const __nv_bfloat16*) x, n, rows, nb, merge, state, sc, rw, st);
+    case AQ_F32: return v2h_passes<float>((const float*) x, n, rows, nb, merge, state, batch, sc, rw, st);
+    case AQ_F16: return v2h_passes<__half>((const __half*) x, n, rows, nb, merge, state, batch, sc, rw, st);
+    case AQ_BF16:
+        return v2h_passes<__nv_bfloat16>((const __nv_bfloat16*) x, n, rows, nb, merge, state, batch, sc, rw, st);
     default: return AQ_ERR_INVALID_ARG;
     }
 }
@@ -426,7 +441,7 @@ int v2hist_collect_rows(const void* x, int dtype, int64_t n, int rows, int nb, a
         return AQ_ERR_TOO_LARGE;
     V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
     const V2HRows rw {rows > 1 ? n : 0, rows > 1 ? v2hist_scratch_bytes() : 0, rows > 1 ? block_stride : 0, 0};
-    int rc = v2h_passes_any(x, dtype, n, rows, nb, 0, nullptr, sc, rw, st);
+    int rc = v2h_passes_any(x, dtype, n, rows, nb, 0, nullptr, nullptr, sc, rw, st);
     if (rc != AQ_OK)
         return rc;
     launch_pdl(v2h_finish_collect_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb,
@@ -451,7 +466,7 @@ int v2hist_merge_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq_
         return check_launch();
     }
     V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
-    int rc            = v2h_passes_any(x, dtype, n, rows, nb, 1, state, sc, rw, st);
+    int rc            = v2h_passes_any(x, dtype, n, rows, nb, 1, state, batch, sc, rw, st);
     if (rc != AQ_OK)
         return rc;
     launch_pdl(v2h_merge_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb, state,

@@ -400,7 +400,8 @@ int aq_v2hist_collect(const void* d_x, int dtype, int64_t n, int bins, aq_v2hist
 /* _HistogramObserver.merge_stats for one histogram (encoding_analyzer.py:212-262).  state_has_stats = 0: the state
  * adopts d_batch.  Otherwise the range grows to cover both, the old counts are re-binned with the reference's
  * split-and-round rule (sequential float32 additions in the reference's order), and the batch is counted again at the
- * widened range.  d_updates: bins floats of scratch. */
+ * widened range (one pass over d_x: the batch's finite min / max come from d_batch).  d_updates: bins floats of
+ * scratch. */
 int aq_v2hist_merge(const void* d_x, int dtype, int64_t n, int bins, aq_v2hist_head_t* d_state,
                     const aq_v2hist_head_t* d_batch, int state_has_stats, void* d_scratch, float* d_updates,
                     void* stream);

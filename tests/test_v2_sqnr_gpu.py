@@ -47,6 +47,8 @@ def test_histc_rule(cuda, case):
     scratch = torch.empty(int(lib.aq_v2hist_scratch_bytes()), dtype=torch.uint8, device=cuda)
     upd = torch.empty(nb, dtype=torch.float32, device=cuda)
     st = torch.cuda.current_stream().cuda_stream
+    # the merge takes the batch's finite min / max from the batch's own statistics
+    assert lib.aq_v2hist_collect(xd.data_ptr(), 0, xd.numel(), nb, batch.data_ptr(), scratch.data_ptr(), st) == 0
     assert lib.aq_v2hist_merge(xd.data_ptr(), 0, xd.numel(), nb, state.data_ptr(), batch.data_ptr(), 1,
                                scratch.data_ptr(), upd.data_ptr(), st) == 0
     got = state.view(torch.float32)[4:4 + nb].cpu().numpy()
