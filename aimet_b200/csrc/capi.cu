@@ -152,6 +152,13 @@ int aq_quantize_per_tensor(const float* d_in, float* d_out, int64_t n, double en
                            (float) shift, (cudaStream_t) stream);
 }
 
+int aq_qdq_fp16(const float* d_in, float* d_out, int64_t n, void* stream)
+{
+    if (n < 0 || (n > 0 && (!d_in || !d_out)))
+        return AQ_ERR_INVALID_ARG;
+    return fp16_qdq(d_in, d_out, n, (cudaStream_t) stream);
+}
+
 static inline bool packed_bw_ok(int bw)
 {
     return bw == 1 || bw == 2 || bw == 4 || bw == 8 || bw == 16 || bw == 32;

@@ -843,6 +843,45 @@ int v2_launch(V2Args a, int dtype, int narrow_internal, cudaStream_t st)
 }
 
 // -------------------------------------------------------------------------------------------------
+// 16-bit float fake-quantization: out = float(half(in))  (quantizeDequantizeFp16Kernel, trim_functions.cu:135-148)
+// -------------------------------------------------------------------------------------------------
+template <int VEC>
+__global__ void __launch_bounds__(kThreads) fp16_qdq_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t n)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t idx = ((int64_t) blockIdx.x * kThreads + threadIdx.x) * VEC;
+    if (idx + VEC <= n)
+    {
+        const Pack<float, VEC> v = load_pack<float, VEC>(in + idx);
+        Pack<float, VEC> r;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+            r.v[e] = __half2float(__float2half_rn(v.v[e]));
+        store_pack<float, VEC>(out + idx, r);
+    }
+    else
+    {
+        for (int64_t i = idx; i < n; ++i)
+            out[i] = __half2float(__float2half_rn(in[i]));
+    }
+}
+
+int fp16_qdq(const float* in, float* out, int64_t n, cudaStream_t st)
+{
+    if (n == 0)
+        return AQ_OK;
+    const int vec = pick_vec<float>(in, out, nullptr, 0) >= 4 ? 4 : 1;
+    const int64_t grid = (n + (int64_t) kThreads * vec - 1) / ((int64_t) kThreads * vec);
+    if (vec == 4)
+        launch_pdl(fp16_qdq_kernel<4>, (unsigned) grid, kThreads, 0, st, in, out, n);
+    else
+        launch_pdl(fp16_qdq_kernel<1>, (unsigned) grid, kThreads, 0, st, in, out, n);
+    note_launch();
+    return check_launch();
+}
+
+// -------------------------------------------------------------------------------------------------
 // Integer codes in integer containers (libpymo "packed" form)
 // -------------------------------------------------------------------------------------------------
 // quantizeToFxpPackedCpu / dequantizeFromPackedFxpCpu (DlQuantization/src/trim_functions.cpp:220-605): unlike the

@@ -123,6 +123,15 @@ def quantize_per_tensor(x: torch.Tensor, enc_min: float, enc_max: float, bw: int
     return out
 
 
+def qdq_fp16(x: torch.Tensor) -> torch.Tensor:
+    """float32 -> float16 -> float32 in one pass (the 16-bit float fake-quantization of the v1 flow)."""
+    x = _f32c(x, "input")
+    out = torch.empty_like(x)
+    with _on(x):
+        check(lib.aq_qdq_fp16(x.data_ptr(), out.data_ptr(), x.numel(), _stream(x)), "aq_qdq_fp16")
+    return out
+
+
 _PACKED_DTYPES = {(8, False): torch.uint8, (8, True): torch.int8, (16, False): torch.uint16, (16, True): torch.int16,
                   (32, False): torch.uint32, (32, True): torch.int32}
 

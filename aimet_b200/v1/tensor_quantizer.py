@@ -324,6 +324,8 @@ class QuantizeDequantize(torch.autograd.Function):
             if tq.bitwidth != 16:
                 raise ValueError("aimet_b200: float data_type supports only the 16-bit cast on this path")
             ctx.save_for_backward(tensor)
+            if tensor.dtype == torch.float32 and tensor.is_cuda:
+                return ops.qdq_fp16(tensor)   # one pass instead of two casts
             return tensor.half().float()
         dtype = tensor.dtype
         x = tensor.to(torch.float32)

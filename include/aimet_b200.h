@@ -142,6 +142,11 @@ int aq_qdq_broadcast(const float* d_in, float* d_out, int64_t n, int64_t ndims, 
                      const int64_t* h_enc_strides, const float* d_enc_min, const float* d_enc_max,
                      const float* d_enc_delta, const float* d_enc_offset, void* stream);
 
+/* 16-bit float fake-quantization: out = (float) (half) in, round to nearest even.  Replaces
+ * quantizeDequantizeFp16Gpu (src/Fp16Quantization.cpp:46-50, kernel src/trim_functions.cu:135-148) and the
+ * tensor.half().float() pair of the v1 wrappers (aimet_torch/v1/tensor_quantizer.py:1104-1107). */
+int aq_qdq_fp16(const float* d_in, float* d_out, int64_t n, void* stream);
+
 /* Integer codes in integer containers.  Replaces TensorQuantizationSim<float>::quantizeTensorPacked ->
  * quantizeToFxpPackedCpu (src/TensorQuantizationSim.cpp:128-139, src/trim_functions.cpp:220-385; CPU only, four host
  * threads in the reference).  The grid is re-derived from (enc_min, enc_max, bw) as in aq_qdq_per_tensor, but clamp,

@@ -185,3 +185,17 @@ def test_numpy_facing_mirrors(oracle, cuda):
     p = libpymo.TfEncoding(delta=0.5, offset=-10.0, bw=8)
     tq.computePartialEncoding(8, p, False, False, False)
     assert (p.min, p.max) == (-5.0, 122.5)
+
+
+def test_fp16_fake_quant_is_the_double_cast(cuda):
+    """aq_qdq_fp16 against float(half(x)) computed by torch on the CPU: ties, subnormals of half, overflow to inf."""
+    from aimet_b200 import ops
+    edge = np.array([0.0, -0.0, 1.0, 65504.0, 65519.9, 65520.0, -65520.0, 1e-8, 5.96e-8, 2.98e-8, 2.9802322e-8, 6.1e-5,
+                     1.0009765625, 1.00048828125, 1.000732421875, np.inf, -np.inf, np.nan, 3.1415927], np.float32)
+    x = np.concatenate([normal(100_003, 9, 30.0, 0.0), normal(5000, 10, 1e-6, 0.0), edge])
+    want = torch.from_numpy(x).half().float().numpy()
+    got = ops.qdq_fp16(dev(x, cuda)).cpu().numpy()
+    assert_bits_equal(got, want, "fp16 fake-quant")
+    got1 = ops.qdq_fp16(dev(x, cuda)[1:]).cpu().numpy()   # unaligned view: scalar path
+    assert_bits_equal(got1, want[1:], "fp16 fake-quant, unaligned")
+
