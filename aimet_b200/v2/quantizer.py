@@ -29,7 +29,7 @@ from . import backend
 from .encoding_analyzer import EncodingAnalyzer, MinMaxEncodingAnalyzer, StatisticsNotFoundError, device_scalar
 from .qtensor import DequantizedTensor, QuantizedTensor
 
-__all__ = ["AffineEncoding", "MinMaxQuantizer", "Quantize", "QuantizeDequantize"]
+__all__ = ["AffineEncoding", "MinMaxQuantizer", "Quantize", "QuantizeDequantize", "GroupedBlockQuantizeDequantize"]
 
 
 def derive_qmin_qmax(bitwidth: int, signed: bool) -> Tuple[int, int]:
@@ -292,7 +292,7 @@ class MinMaxQuantizer(nn.Module):
                                                              for a, b in zip(self._cache[0], key)):
             return self._cache[1], self._cache[2]
         steps = device_scalar(self.qmax - self.qmin, dtype, self.min.device)
-        scale = ((self.max.to(dtype) - self.min.to(dtype)) / steps).to(dtype)
+        scale = self._transform_scale(((self.max.to(dtype) - self.min.to(dtype)) / steps).to(dtype))
         if self._symmetric:
             offset = torch.zeros_like(self.min, requires_grad=False, dtype=dtype)
         else:
@@ -300,6 +300,10 @@ class MinMaxQuantizer(nn.Module):
         if not recording:
             self._cache = (key, scale.detach(), offset.detach())
         return scale, offset
+
+    def _transform_scale(self, scale: torch.Tensor) -> torch.Tensor:
+        """Hook for quantizers whose effective scale is derived from the min/max scale (grouped blocks)."""
+        return scale
 
     def get_scale(self, dtype=None) -> Optional[torch.Tensor]:
         if not self.is_initialized():
@@ -390,7 +394,7 @@ class MinMaxQuantizer(nn.Module):
         dmin = dmin.to(dtype=self.min.dtype, device=self.min.device).expand_as(self.min)
         dmax = dmax.to(dtype=self.max.dtype, device=self.max.device).expand_as(self.max)
         div = device_scalar(steps, torch.float32, dmin.device)
-        scale = (dmax.to(torch.float32) - dmin.to(torch.float32)) / div
+        scale = self._transform_scale((dmax.to(torch.float32) - dmin.to(torch.float32)) / div)
         offset = torch.zeros_like(scale) if self._symmetric else torch.round(dmin.to(torch.float32) / scale) - self.qmin
         return scale, offset
 
@@ -442,3 +446,67 @@ class QuantizeDequantize(MinMaxQuantizer):
         scale, offset = self._encoding_for(input, "QuantizeDequantize")
         out = backend.quantize_dequantize(input, scale, offset, self.qmin, self.qmax, block_size=self.block_size)
         return self._wrap(out, DequantizedTensor, scale, offset)
+
+
+class GroupedBlockQuantizeDequantize(QuantizeDequantize):
+    """Blockwise quantize-dequantize whose per-block scales are themselves restricted to an integer multiple
+    (1 .. 2^(decompressed_bw - bitwidth)) of one scale per group of blocks -- "LPBQ"
+    (affine/quantizer.py:700-815: same constructor, ``get_scale`` override, ``get_expanded_scale_shape``,
+    ``get_per_channel_scale``, ``get_per_block_integer_scale``).  The element arithmetic is the blockwise kernel; the
+    scale adjustment is one small quantize-dequantize of the scale tensor."""
+
+    def __init__(self, shape, bitwidth: int, symmetric: bool, decompressed_bw: int,
+                 encoding_analyzer: Optional[EncodingAnalyzer] = None, block_size: Optional[Tuple[int, ...]] = None,
+                 block_grouping: Optional[Tuple[int, ...]] = None):
+        super().__init__(shape, bitwidth, symmetric, encoding_analyzer, block_size)
+        self.decompressed_bw = decompressed_bw
+        self.block_grouping = block_grouping if block_grouping is not None else tuple(1 for _ in self.shape)
+        if block_grouping is not None:
+            if len(block_grouping) != len(self.shape):
+                raise RuntimeError(f'Length of block grouping {block_grouping} must equal length of shape {shape}.')
+            for idx, block_group in enumerate(block_grouping):
+                if block_group != -1 and self.shape[idx] % block_group != 0:
+                    raise RuntimeError(f'Quantizer shape dimensions must divide evenly with corresponding block '
+                                       f'grouping values for shapes {shape} and block grouping {block_grouping}.')
+        if self.decompressed_bw < self.bitwidth:
+            raise RuntimeError(f'Decompressed bitwidth {decompressed_bw} cannot be smaller than self.bitwidth '
+                               f'{bitwidth}')
+        if not symmetric:
+            raise RuntimeError('GroupedBlockQuantizeDequantize only supports symmetric quantization.')
+
+    def get_expanded_scale_shape(self) -> Tuple[int, ...]:
+        """Every scale dimension split into (groups, blocks per group); -1 groups the whole dimension."""
+        expanded: List[int] = []
+        for idx, block_group in enumerate(self.block_grouping):
+            if block_group == -1:
+                expanded += [1, self.shape[idx]]
+            else:
+                expanded += [self.shape[idx] // block_group, block_group]
+        return tuple(expanded)
+
+    def _group_scale(self, scale: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        expanded = scale.view(self.get_expanded_scale_shape())
+        max_scale = torch.amax(expanded, list(range(1, len(scale.shape) * 2, 2)), keepdim=True)
+        # a power of two: dividing and multiplying by the reciprocal give the same bits
+        return expanded, max_scale / 2 ** (self.decompressed_bw - self.bitwidth)
+
+    def _transform_scale(self, scale: torch.Tensor) -> torch.Tensor:
+        expanded, per_channel_scale = self._group_scale(scale)
+        updated = backend.quantize_dequantize(expanded.contiguous(), per_channel_scale,
+                                              torch.zeros_like(per_channel_scale), 1,
+                                              2 ** (self.decompressed_bw - self.bitwidth))
+        return updated.as_subclass(torch.Tensor).view(scale.shape)
+
+    def _raw_scale(self, dtype=None) -> torch.Tensor:
+        dtype = dtype or torch.float32
+        steps = device_scalar(self.qmax - self.qmin, dtype, self.min.device)
+        return ((self.max.to(dtype) - self.min.to(dtype)) / steps).to(dtype)
+
+    def get_per_channel_scale(self, dtype=None) -> torch.Tensor:
+        return self._group_scale(self._raw_scale(dtype))[1]
+
+    def get_per_block_integer_scale(self) -> torch.Tensor:
+        per_channel_scale = self.get_per_channel_scale()
+        expanded = self.get_scale().view(self.get_expanded_scale_shape())
+        return torch.round(expanded / per_channel_scale).int().view(self.get_scale().shape)
+

@@ -224,6 +224,13 @@ def quantizer_cases():
         ("blk_w4_bf16", "qdq", ((12, 4), 4, True), {"block_size": (1, 8)}, [rnd(12, 32, s=0.02).to(torch.bfloat16)],
          rnd(12, 32, s=0.03).to(torch.bfloat16)),
         ("pt_a16", "qdq", ((), 16, False), {}, [rnd(2048, s=k) for k in (1.0, 4.0)], rnd(2048, s=5.0)),
+        # grouped blocks (LPBQ): 4-bit blocks of 8 decompressed to 8 bits, groups of 2 blocks / all blocks of a row
+        ("gbq_w4_g2", "gbq", ((12, 4), 4, True, 8), {"block_size": (-1, 8), "block_grouping": (1, 2)},
+         [rnd(12, 32, s=0.02)], rnd(12, 32, s=0.03)),
+        ("gbq_w4_all", "gbq", ((12, 4), 4, True, 8), {"block_size": (1, 8), "block_grouping": (1, -1)},
+         [rnd(12, 32, s=0.05)], rnd(12, 32, s=0.05)),
+        ("gbq_w4_rows", "gbq", ((12, 4), 4, True, 6), {"block_size": (1, 8), "block_grouping": (3, 4)},
+         [rnd(12, 32, s=0.02) * torch.linspace(0.2, 3.0, 12).view(12, 1)], rnd(12, 32, s=0.03)),
     ]
 
 
@@ -232,7 +239,7 @@ def gen_quantizer(ref_root: str):
     rq = load_reference_quantizer(ref_root)
     out = {}
     for name, kind, args, kwargs, batches, probe in quantizer_cases():
-        q = (rq.QuantizeDequantize if kind == "qdq" else rq.Quantize)(*args, **kwargs)
+        q = {"qdq": rq.QuantizeDequantize, "q": rq.Quantize, "gbq": rq.GroupedBlockQuantizeDequantize}[kind](*args, **kwargs)
         with torch.no_grad():
             with q.compute_encodings():
                 for b, x in enumerate(batches):
@@ -244,6 +251,9 @@ def gen_quantizer(ref_root: str):
             out[f"{name}/offset"] = q.get_offset().detach().numpy()
             out[f"{name}/probe"] = probe.float().numpy()
             out[f"{name}/out"] = q(probe).as_subclass(torch.Tensor).float().numpy()
+            if kind == "gbq":
+                out[f"{name}/per_channel_scale"] = q.get_per_channel_scale().numpy()
+                out[f"{name}/integer_scale"] = q.get_per_block_integer_scale().numpy()
         out[f"{name}/dtype"] = np.array(str(probe.dtype))
     np.savez_compressed(os.path.join(HERE, "v2_quantizer.npz"), **out)
 
@@ -270,7 +280,7 @@ def gen_wire_format(ref_root: str):
     rq = load_reference_quantizer(ref_root)
     out = {"quantizers": {}, "ops": {}}
     for name, kind, args, kwargs, batches, probe in quantizer_cases():
-        if batches[0].dtype != torch.float32:
+        if batches[0].dtype != torch.float32 or kind == "gbq":
             continue
         cls = rq.QuantizeDequantize if kind == "qdq" else rq.Quantize
         q = cls(*args, **kwargs)

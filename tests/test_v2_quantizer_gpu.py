@@ -23,10 +23,10 @@ def _cases():
 @pytest.mark.gpu
 @pytest.mark.parametrize("name,kind,args,kwargs", _cases(), ids=[c[0] for c in _cases()])
 def test_module_matches_reference_fixture(cuda, name, kind, args, kwargs):
-    from aimet_b200.v2.quantizer import Quantize, QuantizeDequantize
+    from aimet_b200.v2.quantizer import GroupedBlockQuantizeDequantize, Quantize, QuantizeDequantize
     g = np.load(os.path.join(GOLDEN, "v2_quantizer.npz"))
     dt = DT[str(g[f"{name}/dtype"])]
-    q = (QuantizeDequantize if kind == "qdq" else Quantize)(*args, **kwargs).to(cuda)
+    q = {"qdq": QuantizeDequantize, "q": Quantize, "gbq": GroupedBlockQuantizeDequantize}[kind](*args, **kwargs).to(cuda)
     assert not q.is_initialized() and q.get_scale() is None
     with pytest.raises(RuntimeError):
         q(torch.zeros(1, device=cuda))
@@ -45,6 +45,10 @@ def test_module_matches_reference_fixture(cuda, name, kind, args, kwargs):
         probe = torch.from_numpy(g[f"{name}/probe"]).to(cuda).to(dt)
         for _ in range(2):   # the second call takes the cached scale / offset
             assert_bits_equal(q(probe).float().cpu().numpy(), g[f"{name}/out"], "output")
+        if kind == "gbq":
+            # grouped blocks: one scale per group, an integer multiple of it per block
+            assert_bits_equal(q.get_per_channel_scale().cpu().numpy(), g[f"{name}/per_channel_scale"], "group scale")
+            np.testing.assert_array_equal(q.get_per_block_integer_scale().cpu().numpy(), g[f"{name}/integer_scale"])
     enc = q.get_encoding()
     assert enc.qmin == q.qmin and enc.qmax == q.qmax and enc.symmetry == q.symmetric
     np.testing.assert_array_equal(enc.min.detach().cpu().numpy(), q.get_min().detach().cpu().numpy())
@@ -125,3 +129,18 @@ def test_initialisation_tracking_and_state_dict():
     with e.compute_encodings():
         pass
     assert not e.is_initialized()
+
+
+def test_grouped_block_constructor_errors():
+    from aimet_b200.v2.quantizer import GroupedBlockQuantizeDequantize as G
+    with pytest.raises(RuntimeError, match="Length of block grouping"):
+        G((4, 8), 4, True, 8, None, (1, 16), (2,))
+    with pytest.raises(RuntimeError, match="divide evenly"):
+        G((4, 8), 4, True, 8, None, (1, 16), (1, 3))
+    with pytest.raises(RuntimeError, match="cannot be smaller"):
+        G((4, 8), 8, True, 4, None, (1, 16), (1, 2))
+    with pytest.raises(RuntimeError, match="only supports symmetric"):
+        G((4, 8), 4, False, 8, None, (1, 16), (1, 2))
+    assert G((4, 8), 4, True, 8, None, (1, 16), (1, -1)).get_expanded_scale_shape() == (4, 1, 1, 8)
+    assert G((4, 8), 4, True, 8, None, (1, 16)).block_grouping == (1, 1)
+
