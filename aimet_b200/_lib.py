@@ -48,6 +48,7 @@ SIGNATURES = {
     "aq_minmax_encoding": (_i32, [_i32, _f64, _f64, _i32, _i32, _i32, C.POINTER(AqEncoding)]),
     "aq_qdq_per_tensor": (_i32, [_vp, _vp, _i64, _f64, _f64, _i32, _i32, _vp]),
     "aq_quantize_per_tensor": (_i32, [_vp, _vp, _i64, _f64, _f64, _i32, _i32, _i32, _vp]),
+    "aq_v2_minmax_encoding": (_i32, [_vp, _vp, _i32, _i32, _i64, _f64, _i32, _f64, _vp, _vp]),
     "aq_qdq_fp16": (_i32, [_vp, _vp, _i64, _vp]),
     "aq_quantize_packed": (_i32, [_vp, _vp, _i64, _f64, _f64, _i32, _i32, _i32, _vp]),
     "aq_dequantize_packed": (_i32, [_vp, _vp, _i64, _f64, _f64, _i32, _i32, _vp]),

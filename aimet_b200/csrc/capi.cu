@@ -152,6 +152,16 @@ int aq_quantize_per_tensor(const float* d_in, float* d_out, int64_t n, double en
                            (float) shift, (cudaStream_t) stream);
 }
 
+int aq_v2_minmax_encoding(const float* d_batch_minmax, float* d_running_minmax, int running_valid, int stats_dtype,
+                          int64_t count, double num_steps, int symmetric, double qmin, float* d_out, void* stream)
+{
+    if (count < 0 || (!d_batch_minmax && !d_running_minmax) || !d_out || !(num_steps > 0) || stats_dtype < AQ_F32 ||
+        stats_dtype > AQ_BF16 || (!d_batch_minmax && !running_valid))
+        return AQ_ERR_INVALID_ARG;
+    return v2_minmax_encode(d_batch_minmax, d_running_minmax, running_valid, stats_dtype, count, num_steps, symmetric, qmin,
+                            d_out, (cudaStream_t) stream);
+}
+
 int aq_qdq_fp16(const float* d_in, float* d_out, int64_t n, void* stream)
 {
     if (n < 0 || (n > 0 && (!d_in || !d_out)))

@@ -10,6 +10,8 @@ int pymo_per_tensor(const float* in, float* out, int64_t n, float mn, float mx, 
 int pymo_per_channel(const float* in, float* out, int64_t n, int64_t num_ch, int64_t inner, const float* enc_min,
                      const float* enc_max, const float* enc_delta, const float* enc_offset, float num_steps,
                      int derive, cudaStream_t st);
+int v2_minmax_encode(const float* batch, float* running, int running_valid, int dtype, int64_t count, double num_steps,
+                     int symmetric, double qmin, float* out, cudaStream_t st);
 int fp16_qdq(const float* in, float* out, int64_t n, cudaStream_t st);
 int packed_quantize(const float* in, void* out, int64_t n, double e_min, double e_max, double delta, double offset, int bw,
                     int to_signed, cudaStream_t st);

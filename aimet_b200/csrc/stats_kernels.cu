@@ -1404,4 +1404,114 @@ int tfe_pdf_replay(const uint32_t* hists, const int64_t* counts, int64_t num_bat
     return check_launch();
 }
 
+// -------------------------------------------------------------------------------------------------
+// aimet_torch v2 min/max calibration, the part after the reduction: merge of the batch range into the running range,
+// MinMaxEncodingAnalyzer.compute_encodings_from_stats (aimet_torch/v2/quantization/encoding_analyzer.py:325-386) and the
+// quantizer's scale / offset (affine/quantizer.py:222-246) for `count` encodings in one launch.  The reference spends
+// about 25 small tensor operations per quantizer on this; every one of them is element-wise, so each encoding is one
+// thread here, evaluated in the reference's operation order and -- for 16-bit statistics -- with its roundings: the
+// statistics and the first quotient live in the statistics dtype, everything after the comparison with the minimum
+// scale is float32 (the adjustment term is a float32 tensor, which promotes the rest).
+// -------------------------------------------------------------------------------------------------
+template <int DT>
+__device__ __forceinline__ float round_to(float v)
+{
+    if (DT == AQ_F16)
+        return __half2float(__float2half_rn(v));
+    if (DT == AQ_BF16)
+        return __bfloat162float(__float2bfloat16_rn(v));
+    return v;
+}
+__device__ __forceinline__ float nan_min(float a, float b)   // torch.minimum: NaN wins
+{
+    return (a != a || b != b) ? NAN : fminf(a, b);
+}
+__device__ __forceinline__ float nan_max(float a, float b)
+{
+    return (a != a || b != b) ? NAN : fmaxf(a, b);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256) v2_minmax_encode_kernel(const float* __restrict__ batch /* [2, count] or null */,
+                                                               float* __restrict__ running /* [2, count] or null */,
+                                                               int running_valid, int64_t count, float num_steps,
+                                                               float steps_in_dt, float pos_steps, float neg_steps,
+                                                               int symmetric, float qmin, float type_max,
+                                                               float* __restrict__ out /* [4, count] */)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t i = (int64_t) blockIdx.x * 256 + threadIdx.x;
+    if (i >= count)
+        return;
+    float mn, mx;
+    if (batch)
+    {
+        mn = batch[i], mx = batch[count + i];
+        if (running)
+        {
+            // merge_stats: torch.minimum / torch.maximum with the running range (or adopt the batch)
+            const float rmn = running_valid ? nan_min(running[i], mn) : mn;
+            const float rmx = running_valid ? nan_max(running[count + i], mx) : mx;
+            running[i] = rmn, running[count + i] = rmx;
+        }
+    }
+    else
+        mn = running[i], mx = running[count + i];
+    const float eps  = 1.1920928955078125e-07f;   // torch.finfo(torch.float32).eps
+    const float min0 = (mn != mn) ? mn : fminf(mn, 0.0f);
+    const float max0 = (mx != mx) ? mx : fmaxf(mx, 0.0f);
+    const float diff = round_to<DT>(__fdiv_rn(round_to<DT>(__fsub_rn(max0, min0)), steps_in_dt));
+    const float adj  = (diff < eps) ? eps : 0.0f;
+    float umin, umax;
+    if (symmetric)
+    {
+        umax              = __fadd_rn(max0, __fmul_rn(pos_steps, adj));
+        umin              = __fsub_rn(min0, __fmul_rn(neg_steps, adj));
+        const float delta = nan_max(__fdiv_rn(umax, pos_steps), __fdiv_rn(-umin, neg_steps));
+        umin              = __fmul_rn(-neg_steps, delta);
+        umax              = __fmul_rn(pos_steps, delta);
+    }
+    else
+    {
+        umax = __fadd_rn(max0, __fmul_rn(num_steps, adj));
+        umin = min0;
+    }
+    // clamp to the statistics dtype's range (NaN stays NaN), then the cast to that dtype
+    const float emax = round_to<DT>((umax == umax) ? fminf(umax, type_max) : umax);
+    const float emin = round_to<DT>((umin == umin) ? fmaxf(umin, -type_max) : umin);
+    const float scale = __fdiv_rn(__fsub_rn(emax, emin), num_steps);
+    const float offset = symmetric ? 0.0f : __fsub_rn(rintf(__fdiv_rn(emin, scale)), qmin);
+    out[i] = emin, out[count + i] = emax, out[2 * count + i] = scale, out[3 * count + i] = offset;
+}
+
+int v2_minmax_encode(const float* batch, float* running, int running_valid, int dtype, int64_t count, double num_steps,
+                     int symmetric, double qmin, float* out, cudaStream_t st)
+{
+    if (count == 0)
+        return AQ_OK;
+    const float ns  = (float) num_steps;
+    const float pos = (float) floor(num_steps / 2.0), neg = (float) ceil(num_steps / 2.0);
+    // the divisor of the first quotient is a tensor of the statistics dtype in the reference's arithmetic
+    float ns_dt = ns, tmax = FLT_MAX;
+    if (dtype == AQ_F16)
+        ns_dt = __half2float(__float2half_rn(ns)), tmax = 65504.0f;
+    else if (dtype == AQ_BF16)
+        ns_dt = __bfloat162float(__float2bfloat16_rn(ns)), tmax = 3.3895313892515355e38f;
+    const unsigned grid = (unsigned) ((count + 255) / 256);
+#define AQ_ENC(DT)                                                                                                   \
+    launch_pdl(v2_minmax_encode_kernel<DT>, grid, 256, 0, st, batch, running, running_valid, count, ns, ns_dt, pos, neg, \
+               symmetric, (float) qmin, tmax, out)
+    switch (dtype)
+    {
+    case AQ_F32: AQ_ENC(AQ_F32); break;
+    case AQ_F16: AQ_ENC(AQ_F16); break;
+    case AQ_BF16: AQ_ENC(AQ_BF16); break;
+    default: return AQ_ERR_INVALID_ARG;
+    }
+#undef AQ_ENC
+    note_launch();
+    return check_launch();
+}
+
 }   // namespace aq

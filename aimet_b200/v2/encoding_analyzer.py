@@ -48,16 +48,22 @@ class _MinMaxRange:
 
 
 class _MinMaxObserver:
-    """Running min / max per encoding (reference: _MinMaxObserver, encoding_analyzer.py:92-128)."""
+    """Running min / max per encoding (reference: _MinMaxObserver, encoding_analyzer.py:92-128).
+
+    The running range lives in one float32 device tensor ``[2, count]`` (mins, then maxs, in the encoding's own
+    flattened order) whatever the dtype of the observed tensors -- float32 holds float16 / bfloat16 values exactly --
+    so that the fused calibration step (:meth:`MinMaxEncodingAnalyzer.fused_update`) can update it in place; the
+    ``_MinMaxRange`` the reference exposes is built from it on request, in the dtype of the observed tensors."""
 
     def __init__(self, shape):
         if isinstance(shape, int):
             shape = (shape,)
         self.shape = tuple(shape)
-        self.stats = _MinMaxRange()
+        self._running: Optional[torch.Tensor] = None
+        self._valid = False
+        self._dtype = torch.float32
 
-    @torch.no_grad()
-    def collect_stats(self, input_tensor: torch.Tensor) -> _MinMaxRange:
+    def _geometry(self, input_tensor: torch.Tensor):
         if not input_tensor.is_cuda:
             raise RuntimeError("aimet_b200: statistics are collected on the GPU only (no CPU path exists)")
         x = input_tensor.detach()
@@ -66,7 +72,12 @@ class _MinMaxObserver:
         enc_shape = self.shape
         if len(enc_shape) > x.dim() or any(s not in (1, t) for s, t in zip(enc_shape[::-1], tuple(x.shape)[::-1])):
             raise RuntimeError(f"Shape {self.shape} is incompatible with input of shape {tuple(x.shape)}")
-        g = resolve_geometry(x, enc_shape, None)
+        return x, resolve_geometry(x, enc_shape, None)
+
+    @torch.no_grad()
+    def collect_stats(self, input_tensor: torch.Tensor) -> _MinMaxRange:
+        x, g = self._geometry(input_tensor)
+        enc_shape = self.shape
         mm = ops.minmax(g.x_work, g.num_ch, g.inner, propagate_nan=True)   # [2, num_ch] float32, channel order
         # channel order -> the encoding's own layout
         view = [s for s in g.enc_view]
@@ -83,18 +94,29 @@ class _MinMaxObserver:
 
     @torch.no_grad()
     def merge_stats(self, stats: _MinMaxRange):
-        mn, mx = self.stats.min, self.stats.max
-        if stats.min is not None:
-            mn = stats.min.clone() if mn is None else torch.minimum(mn, stats.min)
-        if stats.max is not None:
-            mx = stats.max.clone() if mx is None else torch.maximum(mx, stats.max)
-        self.stats = _MinMaxRange(mn, mx)
+        if stats.min is None or stats.max is None:
+            return
+        new = torch.stack([stats.min.detach().float().reshape(-1), stats.max.detach().float().reshape(-1)])
+        if not self._valid or self._running is None or self._running.shape != new.shape \
+                or self._running.device != new.device:
+            self._running, self._dtype = new, stats.min.dtype
+        else:
+            self._running[0] = torch.minimum(self._running[0], new[0])
+            self._running[1] = torch.maximum(self._running[1], new[1])
+        self._valid = True
 
     def reset_stats(self):
-        self.stats = _MinMaxRange()
+        self._valid = False
 
     def get_stats(self) -> _MinMaxRange:
-        return self.stats
+        if not self._valid:
+            return _MinMaxRange()
+        return _MinMaxRange(self._running[0].view(self.shape).to(self._dtype),
+                            self._running[1].view(self.shape).to(self._dtype))
+
+    @property
+    def stats(self) -> _MinMaxRange:
+        return self.get_stats()
 
 
 class EncodingAnalyzer:
@@ -128,6 +150,48 @@ class MinMaxEncodingAnalyzer(EncodingAnalyzer):
 
     def __init__(self, shape: tuple):
         super().__init__(_MinMaxObserver(shape))
+
+    @torch.no_grad()
+    def fused_update(self, input_tensor: torch.Tensor, num_steps: int, is_symmetric: bool, qmin: int):
+        """One calibration step in two launches: the min/max reduction, then -- for all encodings at once -- the merge
+        into the running range, the encodings of THIS batch and the scale / offset to quantize it with (the
+        reference: update_stats + compute_encodings_from_stats + the quantizer's scale / offset arithmetic, about 25
+        small tensor operations).  Returns float32 ``(scale, offset)`` shaped like the observer, or None when the
+        encoding's layout is a permutation of the reduction's channel order (the general path handles that)."""
+        if num_steps <= 0:
+            raise ValueError('The number of quantization bins cannot be less than or equal to 0.')
+        obs = self.observer
+        x, g = obs._geometry(input_tensor)
+        if g.enc_perm != list(range(len(g.enc_view))):
+            return None
+        count = g.num_ch
+        mm = ops.minmax(g.x_work, count, g.inner, propagate_nan=True)
+        if obs._running is None or obs._running.shape != mm.shape or obs._running.device != mm.device:
+            obs._running, obs._valid = torch.empty_like(mm), False
+        out = torch.empty((4, count), dtype=torch.float32, device=mm.device)
+        with ops._on(mm):
+            check(lib.aq_v2_minmax_encoding(mm.data_ptr(), obs._running.data_ptr(), int(obs._valid), _DT[x.dtype], count,
+                                            float(num_steps), int(bool(is_symmetric)), float(qmin), out.data_ptr(),
+                                            ops._stream(mm)), "aq_v2_minmax_encoding")
+        if not obs._valid:
+            obs._dtype = x.dtype
+        obs._valid = True
+        return out[2].view(obs.shape), out[3].view(obs.shape)
+
+    @torch.no_grad()
+    def compute_encodings(self, num_steps: int, is_symmetric: bool):
+        obs = self.observer
+        if num_steps <= 0:
+            raise ValueError('The number of quantization bins cannot be less than or equal to 0.')
+        if not obs._valid:
+            raise StatisticsNotFoundError('No statistics present to compute encodings.')
+        count = obs._running.shape[1]
+        out = torch.empty((4, count), dtype=torch.float32, device=obs._running.device)
+        with ops._on(out):
+            check(lib.aq_v2_minmax_encoding(None, obs._running.data_ptr(), 1, _DT[obs._dtype], count, float(num_steps),
+                                            int(bool(is_symmetric)), 0.0, out.data_ptr(), ops._stream(out)),
+                  "aq_v2_minmax_encoding")
+        return out[0].view(obs.shape).to(obs._dtype), out[1].view(obs.shape).to(obs._dtype)
 
     @torch.no_grad()
     def compute_encodings_from_stats(self, stats: _MinMaxRange, num_steps: int, is_symmetric: bool) \

@@ -386,6 +386,13 @@ class MinMaxQuantizer(nn.Module):
                        enc_max.view(self.max.shape) if self.block_size is not None else enc_max)
 
     def _dynamic_scale_offset(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        fused = getattr(self.encoding_analyzer, "fused_update", None)
+        if (fused is not None and type(self)._transform_scale is MinMaxQuantizer._transform_scale
+                and math.prod(self.encoding_analyzer.observer.shape) == math.prod(self.shape)):
+            got = fused(_reshape_for_blocks(x, self.shape, self.block_size), self.qmax - self.qmin, self._symmetric,
+                        self.qmin)
+            if got is not None:
+                return got[0].view(self.min.shape), got[1].view(self.min.shape)
         stats = self.encoding_analyzer.update_stats(_reshape_for_blocks(x, self.shape, self.block_size))
         steps = self.qmax - self.qmin
         dmin, dmax = self.encoding_analyzer.compute_encodings_from_stats(stats, steps, self._symmetric)

@@ -142,6 +142,21 @@ int aq_qdq_broadcast(const float* d_in, float* d_out, int64_t n, int64_t ndims, 
                      const int64_t* h_enc_strides, const float* d_enc_min, const float* d_enc_max,
                      const float* d_enc_delta, const float* d_enc_offset, void* stream);
 
+/* Everything the v2 min/max calibration does after the reduction, for `count` encodings in one launch:
+ *   1. _MinMaxObserver.merge_stats (aimet_torch/v2/quantization/encoding_analyzer.py:112-128): d_running_minmax
+ *      ([2, count]: mins, then maxs) takes torch.minimum / torch.maximum with d_batch_minmax, or adopts it when
+ *      running_valid = 0 (skipped when d_running_minmax is NULL);
+ *   2. MinMaxEncodingAnalyzer.compute_encodings_from_stats (encoding_analyzer.py:340-386) on the batch range -- or on
+ *      the running range when d_batch_minmax is NULL -- in the reference's operation order and with the roundings of
+ *      statistics held in stats_dtype (AQ_F32 / AQ_F16 / AQ_BF16);
+ *   3. the quantizer's scale = (max - min) / num_steps and offset = round(min / scale) - qmin (0 when symmetric)
+ *      (aimet_torch/v2/quantization/affine/quantizer.py:222-246), in float32.
+ * Inputs hold float32 values that are exactly representable in stats_dtype (what aq_minmax yields on such a tensor).
+ * d_out: [4, count] = encoding min, encoding max, scale, offset.  The reference runs about 25 small tensor operations
+ * per quantizer for this. */
+int aq_v2_minmax_encoding(const float* d_batch_minmax, float* d_running_minmax, int running_valid, int stats_dtype,
+                          int64_t count, double num_steps, int symmetric, double qmin, float* d_out, void* stream);
+
 /* 16-bit float fake-quantization: out = (float) (half) in, round to nearest even.  Replaces
  * quantizeDequantizeFp16Gpu (src/Fp16Quantization.cpp:46-50, kernel src/trim_functions.cu:135-148) and the
  * tensor.half().float() pair of the v1 wrappers (aimet_torch/v1/tensor_quantizer.py:1104-1107). */
