@@ -894,18 +894,20 @@ __device__ __forceinline__ void hist_fix_packet(const float4* __restrict__ x4, u
     }
 }
 
-// Up to AQ_TFE_HIST_MANY batches per launch, each into its own row: the launch overhead (about 1.3 us of the 13 us a
-// 51 MB batch takes as a launch of its own) is paid once per launch instead of once per batch.  What stays per batch is
-// the stop at its end -- measured with cycle stamps at 51 MB per batch: 1.35 us until the CTA's slowest warp arrives,
-// 1.7 us to repair the ~30 queued packets (a dependent re-read), 1.0 us to fold (0.6 us with 128-bit shared loads) --
-// which the other CTA of the SM only partly covers.  Forms that avoid the stop were built and measured slower:
-// one CTA per SM with a dedicated fold warp and two counter sets (32 warps cannot keep the SM busy: 3.9 TB/s even
-// without any atomics), repair in place from the registers or through a queue of sample values (both make the compiler
-// spill inside the hot loop at 32 registers), and counters shared by the CTA with per-set tickets instead of a barrier
-// (same-address reductions cost nothing on this GPU, but the per-thread recount calls are slower than the joint
-// repair), and repairing straight in the batch's global row so that the re-read runs under the fold and one barrier
-// goes away (bit-identical, but the packet and flag kept across the fold cost the sweep its registers: 13.0 us per
-// batch against 11.6 us; as a function that is not inlined, 13.3 us).
+// Up to AQ_TFE_HIST_MANY batches per launch, each into its own row.  The launch overhead (about 1.3 us of the 13 us a
+// 51 MB batch takes as a launch of its own) is paid once per launch, and -- with the work split described at the kernel
+// -- so is most of the stop at the end of a sweep, measured with cycle stamps at 51 MB per batch: 1.35 us until the
+// CTA's slowest warp arrives, 1.7 us to repair the ~30 queued packets (a dependent re-read), 1.0 us to fold (0.6 us
+// with 128-bit shared loads), which the other CTA of the SM only partly covers.  16 batches per launch: 8.9 us per
+// batch (0.90 of the copy bandwidth) against 12.8 us (0.62) for one batch per launch.
+// Other forms that avoid the stop were built and measured slower: one CTA per SM with a dedicated fold warp and two
+// counter sets (32 warps cannot keep the SM busy: 3.9 TB/s even without any atomics), repair in place from the
+// registers or through a queue of sample values (both make the compiler spill inside the hot loop at 32 registers),
+// counters shared by the CTA with per-set tickets instead of a barrier (same-address reductions cost nothing on this
+// GPU, but the per-thread recount calls are slower than the joint repair), and repairing straight in the batch's
+// global row so that the re-read runs under the fold and one barrier goes away (bit-identical, but the packet and
+// flag kept across the fold cost the sweep its registers: 13.0 us per batch against 11.6 us; as a function that is
+// not inlined, 13.3 us).
 struct HistJob
 {
     const float* x[AQ_TFE_HIST_MANY];
@@ -915,6 +917,8 @@ struct HistJob
     uint32_t* hist;    // row of batch 0; batch b adds into hist + b * row_stride * 512
     int64_t* count;    // may be null; batch b sets count[b * row_stride]
     const int32_t* gate;   // may be null; *gate == 0 drops the batches (count 0, rows untouched)
+    int slices;            // S: CTAs that share one batch (interleaved, 1024 packets at a time)
+    int items;             // k: (batch, slice) pairs per CTA; m * S == k * gridDim.x
 };
 
 // A batch that does not start on a 16-byte boundary (a view into a larger buffer) has up to three leading elements
@@ -924,6 +928,12 @@ __device__ __forceinline__ int hist_lead(const float* x, int64_t n)
     return (int) min((int64_t) ((0u - (uint32_t) ((uintptr_t) x >> 2)) & 3u), n);
 }
 
+// Work split: a batch is swept by S CTAs that interleave 1024 packets at a time (so its bytes arrive as one sequential
+// stream), and a CTA takes k (batch, slice) pairs, m * S = k * gridDim.x with the smallest such k = m / gcd(m, gridDim.x):
+// 16 batches on 296 CTAs give S = 37 and k = 2, i.e. a CTA stops to repair and fold twice per launch.  When every CTA
+// took a slice of every batch (S = gridDim.x, k = m) it stopped 16 times, and those stops were a quarter of the
+// kernel's time.  Contiguous shares of the concatenated batches (one or two stops, but 296 distant streams) were
+// measured too: 11.2 us per 51 MB batch against 11.6 us -- the sweep itself is slower that way.
 __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(const __grid_constant__ HistJob job,
                                                                             const aq_tfe_state_t* __restrict__ st)
 {
@@ -940,20 +950,21 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
         if (threadIdx.x == 0)
             s_queued = 0;
     }
-    const uint32_t stride = gridDim.x * kLaneHistThreads;
-    const uint32_t p0     = blockIdx.x * kLaneHistThreads + threadIdx.x;
-    // Bringing a batch's first packets into L2 may start before the previous grid has finished even if that grid is
+    const uint32_t stride = (uint32_t) job.slices * kLaneHistThreads;
+    // Bringing a slice's first packets into L2 may start before the previous grid has finished even if that grid is
     // still writing them: L2 is the point of coherence, a line fetched early is simply updated by the later stores.
-    auto prefetch_head = [&](const float* x, int64_t n) {
-        const int lead    = hist_lead(x, n);
-        const float4* h4  = reinterpret_cast<const float4*>(x + lead);
-        const uint32_t np = (uint32_t) ((n - lead) / 4);
+    auto prefetch_head = [&](int item) {
+        const int b       = item / job.slices;
+        const uint32_t p0 = (uint32_t) (item - b * job.slices) * kLaneHistThreads + threadIdx.x;
+        const int lead    = hist_lead(job.x[b], job.n[b]);
+        const float4* h4  = reinterpret_cast<const float4*>(job.x[b] + lead);
+        const uint32_t np = (uint32_t) ((job.n[b] - lead) / 4);
 #pragma unroll
         for (int u = 0; u < kLaneUnroll; ++u)
             if (p0 + u * stride < np)
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(h4 + (p0 + u * stride)));
     };
-    prefetch_head(job.x[0], job.n[0]);
+    prefetch_head(blockIdx.x);
     pdl_wait();
     // bucket_size, pdf_offset and the initialized flag sit in one aligned 16-byte group: one load, one round trip
     const int4 tail = *reinterpret_cast<const int4*>(&st->bucket_size);
@@ -967,7 +978,6 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
     if (threadIdx.x == 0)
         s_bs = __int_as_float(tail.x), s_po = __int_as_float(tail.y);
     __syncthreads();
-
     const float margin = hist_margin(__int_as_float(tail.y));
     // A margin of a quarter bucket or more means the grid sits so far from zero that the reciprocal form is
     // useless: eps = 0 marks every packet unsure, the queue overflows and the CTA takes the exact sweep below.
@@ -997,15 +1007,20 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
         if (slot < (uint32_t) kFixQueue)                                                                             \
             s_queue[slot] = p;                                                                                       \
     }
-    for (int b = 0; b < job.m; ++b)
+    for (int it = 0; it < job.items; ++it)
     {
+        const int item                = (int) blockIdx.x + it * (int) gridDim.x;
+        const int b                   = item / job.slices;
+        const uint32_t first          = (uint32_t) (item - b * job.slices) * kLaneHistThreads;
         const float* __restrict__ x0  = job.x[b];
         const int lead                = hist_lead(x0, job.n[b]);
         const float4* __restrict__ x4 = reinterpret_cast<const float4*>(x0 + lead);
-        // Packet indices fit 32 bits (n <= 2^31 elements).  Every thread sweeps packets p, p + stride, ...;
-        // kLaneUnroll of them are in flight at once; the last, partial group is issued together as well.
-        const uint32_t npack = (uint32_t) ((job.n[b] - lead) / 4);
-        uint32_t p           = p0;
+        const uint32_t npack          = (uint32_t) ((job.n[b] - lead) / 4);
+        const bool more               = it + 1 < job.items;
+        // Packet indices within a batch fit 32 bits (n <= 2^31 elements).  Every thread sweeps packets p, p + stride,
+        // ... of its slice; kLaneUnroll of them are in flight at once; the last, partial group is issued together as
+        // well.
+        uint32_t p = first + threadIdx.x;
         if (npack >= (kLaneUnroll - 1) * stride)
         {
             const uint32_t last_full = npack - (kLaneUnroll - 1) * stride;   // p < last_full: a full group fits
@@ -1036,17 +1051,9 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
                     AQ_HIST_PACKET(v[u])
             AQ_HIST_QUEUE()
         }
-        // the next batch's first packets travel to L2 while this one is being repaired and folded
-        if (b + 1 < job.m)
-            prefetch_head(job.x[b + 1], job.n[b + 1]);
-        const int ragged = (int) (job.n[b] - lead - (int64_t) npack * 4);   // elements after the last whole packet
-        if (blockIdx.x == 0 && threadIdx.x < lead + ragged)
-        {
-            const int t = threadIdx.x;
-            int k;
-            if (bucket_of(t < lead ? x0[t] : x0[lead + (int64_t) npack * 4 + (t - lead)], s_bs, s_po, k))
-                lane_hist_inc(base, (uint32_t) k);
-        }
+        // the next slice's first packets travel to L2 while this one is being repaired and folded
+        if (more)
+            prefetch_head(item + (int) gridDim.x);
         __syncthreads();
         const uint32_t queued = s_queued;
         if (queued <= (uint32_t) kFixQueue)
@@ -1062,12 +1069,12 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
         else
         {
             // Queue overflow (adversarial data sitting on bucket boundaries): throw this CTA's counts away and redo
-            // its whole share with the exact formula.
+            // its slice with the exact formula.
             __syncthreads();
             for (int i = threadIdx.x; i < kLaneHistRows * 32; i += kLaneHistThreads)
                 s_lane_hist[i] = 0;
             __syncthreads();
-            for (uint32_t q = p0; q < npack; q += stride)
+            for (uint32_t q = first + threadIdx.x; q < npack; q += stride)
             {
                 const float4 w   = __ldg(x4 + q);
                 const float f[4] = {w.x, w.y, w.z, w.w};
@@ -1079,21 +1086,13 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
                         lane_hist_inc(base, (uint32_t) k);
                 }
             }
-            if (blockIdx.x == 0 && threadIdx.x < lead + ragged)
-            {
-                const int t = threadIdx.x;
-                int k;
-                if (bucket_of(t < lead ? x0[t] : x0[lead + (int64_t) npack * 4 + (t - lead)], s_bs, s_po, k))
-                    lane_hist_inc(base, (uint32_t) k);
-            }
         }
         __syncthreads();
-        // Fold the 32 lane copies of each bucket and add the sums to the global row.  Two threads per bucket, each
-        // sums 16 copies (and leaves them zero for the next batch); the column order is rotated by the bucket index so
-        // that the 32 lanes of a warp (16 buckets x 2 halves) touch 32 different banks at every step.  CTAs start at
-        // rotated buckets so that they do not all hit the same global counter at the same moment.
+        // Fold the 32 lane copies of each bucket and add the sums to the batch's global row.  Two threads per bucket,
+        // each sums 16 copies (and leaves them zero for the next segment); the column order is rotated by the bucket
+        // index so that the 32 lanes of a warp (16 buckets x 2 halves) touch 32 different banks at every step.  CTAs
+        // start at rotated buckets so that they do not all hit the same global counter at the same moment.
         {
-            const bool more = b + 1 < job.m;
             const int rot   = (blockIdx.x * 37) & (AQ_PDF_SIZE - 1);
             const int bk    = ((threadIdx.x >> 1) + rot) & (AQ_PDF_SIZE - 1);
             const int half  = threadIdx.x & 1;
@@ -1115,7 +1114,7 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
                 atomicAdd(&job.hist[b * job.row_stride * AQ_PDF_SIZE + bk], sum);
             if (more)
             {
-                // the trash row and the queue counter start the next batch at zero as well
+                // the trash row and the queue counter start the next segment at zero as well
                 if (threadIdx.x < 32)
                     s_lane_hist[(AQ_PDF_SIZE << 5) + threadIdx.x] = 0;
                 if (threadIdx.x == 32)
@@ -1123,11 +1122,26 @@ __global__ void __launch_bounds__(kLaneHistThreads, 2) tfe_hist_lane_kernel(cons
                 __syncthreads();
             }
         }
-    }   // batches
+    }   // (batch, slice) pairs
+    if (blockIdx.x == 0)
+    {
+        // Elements outside the aligned packets -- up to three before the first one of a batch (a view that does not
+        // start on a 16-byte boundary) and up to three after the last -- go straight to the batch's row.
+        for (int b = 0; b < job.m; ++b)
+        {
+            const float* x0  = job.x[b];
+            const int lead   = hist_lead(x0, job.n[b]);
+            const int64_t np = (job.n[b] - lead) / 4;
+            const int ragged = (int) (job.n[b] - lead - np * 4);
+            const int t      = threadIdx.x;
+            int k;
+            if (t < lead + ragged && bucket_of(t < lead ? x0[t] : x0[lead + np * 4 + (t - lead)], s_bs, s_po, k))
+                atomicAdd(&job.hist[b * job.row_stride * AQ_PDF_SIZE + k], 1u);
+        }
+    }
 #undef AQ_HIST_SAMPLE
 #undef AQ_HIST_PACKET
 #undef AQ_HIST_QUEUE
-#undef AQ_HIST_QUEUE_FULL
 }
 
 
@@ -1155,9 +1169,9 @@ static int hist_lane_attributes()
 int tfe_histogram_many(const float* const* xs, const int64_t* ns, int m, int64_t row_stride, const aq_tfe_state_t* st,
                        uint32_t* hist, int64_t* count, const int32_t* gate, cudaStream_t stream)
 {
-    int64_t n_max = 0;
+    int64_t n_total = 0;
     for (int b = 0; b < m; ++b)
-        n_max = ns[b] > n_max ? ns[b] : n_max;
+        n_total += ns[b];
     const int rc = hist_lane_attributes();
     if (rc != AQ_OK)
         return rc;
@@ -1169,12 +1183,21 @@ int tfe_histogram_many(const float* const* xs, const int64_t* ns, int m, int64_t
     }
     job.m = m, job.row_stride = row_stride, job.hist = hist, job.count = count, job.gate = gate;
     int64_t per_block = (int64_t) kLaneHistThreads * 4 * kLaneUnroll;
-    int64_t blocks    = (n_max + per_block - 1) / per_block;
+    int64_t blocks    = (n_total + per_block - 1) / per_block;
     int64_t cap       = (int64_t) kNumSMs * 2;   // two resident 1024-thread CTAs per SM (32 registers, 64 KiB each)
     if (blocks > cap)
         blocks = cap;
     if (blocks < 1)
         blocks = 1;
+    // smallest k with m * S == k * blocks
+    int g = m, r = (int) blocks;
+    while (r)
+    {
+        const int t = g % r;
+        g = r, r = t;
+    }
+    job.items  = m / g;
+    job.slices = (int) (blocks / g);
     launch_pdl(tfe_hist_lane_kernel, (unsigned) blocks, kLaneHistThreads, kLaneHistSmem, stream, job, st);
     note_launch();
     return check_launch();
