@@ -1189,7 +1189,27 @@ int tfe_histogram_many(const float* const* xs, const int64_t* ns, int m, int64_t
         blocks = cap;
     if (blocks < 1)
         blocks = 1;
-    // smallest k with m * S == k * blocks
+    // Two ways to split m batches over the CTAs: (a) cut the grid to a multiple of m, one slice per CTA and one stop
+    // per launch, with up to m - 1 CTAs idle; (b) the full grid with the smallest k such that m * S == k * blocks.
+    // The cheaper one by a simple model (a stop costs about 3 us, the sweep runs at about 6 TB/s): measured at 51 MB
+    // per batch, (a) wins for 3, 5, 7, 15 batches (15: 9.0 against 11.9 us per batch), (b) for 16 (8.96 against 9.12).
+    auto gcd = [](int a, int b) {
+        while (b)
+        {
+            const int t = a % b;
+            a = b, b = t;
+        }
+        return a;
+    };
+    if (blocks >= m)
+    {
+        const double sweep_us = (double) n_total * 4.0 / 6.0e6, stop_us = 3.0;
+        const int64_t cut     = (blocks / m) * m;
+        const double cost_cut  = sweep_us * (double) blocks / (double) cut + stop_us;
+        const double cost_full = sweep_us + stop_us * (m / gcd(m, (int) blocks));
+        if (cost_cut < cost_full)
+            blocks = cut;
+    }
     int g = m, r = (int) blocks;
     while (r)
     {
