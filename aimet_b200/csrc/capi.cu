@@ -248,6 +248,7 @@ int aq_qdq_broadcast(const float* d_in, float* d_out, int64_t n, int64_t ndims, 
     {
         a.in_strides[d]  = d < ndims ? h_in_strides[d] : 1;
         a.enc_strides[d] = d < ndims ? h_enc_strides[d] : 0;
+        a.in_m64[d]      = magic64(a.in_strides[d]);
     }
     a.mn = d_enc_min, a.mx = d_enc_max, a.dl = d_enc_delta, a.of = d_enc_offset;
     return pymo_broadcast(a, (cudaStream_t) stream);

@@ -25,6 +25,7 @@ struct BroadcastArgs
     int ndims;
     int64_t in_strides[8];
     int64_t enc_strides[8];
+    uint64_t in_m64[8];   // magic64(in_strides[d]) (0 for stride 1): exact 32-bit division by one multiply-high
     const float *mn, *mx, *dl, *of;
 };
 int pymo_broadcast(const BroadcastArgs& a, cudaStream_t st);

@@ -467,22 +467,69 @@ int pymo_per_channel(const float* in, float* out, int64_t n, int64_t num_ch, int
 // General broadcast QDQ (stride walk), libpymo semantics.  Rarely-used fallback for encodings that do not
 // reduce to (i / inner) % num_ch; one element per thread per step, exact division.
 // -------------------------------------------------------------------------------------------------
+// Encodings whose layout does not reduce to channel = (i / inner) % num_ch (broadcast dimensions between encoded
+// ones).  A thread takes VEC consecutive elements with one 16-byte load and store; the encoding index of each comes
+// from a per-dimension decomposition of its flat index -- for tensors below 2^32 elements with multiply-high by
+// precomputed magic numbers (a 64-bit division costs as many instructions as everything else here together).
+template <int VEC, bool SMALL>
 __global__ void __launch_bounds__(kThreads) pymo_broadcast_kernel(BroadcastArgs a)
 {
-    const int64_t stride = (int64_t) gridDim.x * kThreads;
-    for (int64_t i = (int64_t) blockIdx.x * kThreads + threadIdx.x; i < a.n; i += stride)
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t first = ((int64_t) blockIdx.x * kThreads + threadIdx.x) * VEC;
+    if (first >= a.n)
+        return;
+    const bool full = first + VEC <= a.n;
+    Pack<float, VEC> v, r;
+    if (full)
+        v = load_pack<float, VEC>(a.in + first);
+    else
     {
-        int64_t e = 0, rem = i;
-        for (int d = 0; d < a.ndims; ++d)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+            v.v[e] = first + e < a.n ? a.in[first + e] : 0.0f;
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+    {
+        int64_t enc = 0;
+        if (SMALL)
         {
-            const int64_t k = rem / a.in_strides[d];
-            rem -= k * a.in_strides[d];
-            e += a.enc_strides[d] * k;
+            uint32_t rem = (uint32_t) (first + e);
+#pragma unroll
+            for (int d = 0; d < 8; ++d)
+                if (d < a.ndims)
+                {
+                    const uint32_t k = div_m64(rem, a.in_m64[d]);
+                    rem -= k * (uint32_t) a.in_strides[d];
+                    enc += a.enc_strides[d] * (int64_t) k;
+                }
         }
-        const float dl = a.dl[e], of = a.of[e];
-        const float t  = fmaxf(fminf(a.in[i], a.mx[e]), a.mn[e]);
+        else
+        {
+            int64_t rem = first + e;
+            for (int d = 0; d < a.ndims; ++d)
+            {
+                const int64_t k = rem / a.in_strides[d];
+                rem -= k * a.in_strides[d];
+                enc += a.enc_strides[d] * k;
+            }
+        }
+        if (!full && first + e >= a.n)
+            enc = 0;
+        const float dl = __ldg(a.dl + enc), of = __ldg(a.of + enc);
+        const float t  = fmaxf(fminf(v.v[e], __ldg(a.mx + enc)), __ldg(a.mn + enc));
         const float q  = round_half_away(__fsub_rn(__fdiv_rn(t, dl), of));
-        a.out[i]       = __fmul_rn(dl, __fadd_rn(q, of));
+        r.v[e]         = __fmul_rn(dl, __fadd_rn(q, of));
+    }
+    if (full)
+        store_pack<float, VEC>(a.out + first, r);
+    else
+    {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+            if (first + e < a.n)
+                a.out[first + e] = r.v[e];
     }
 }
 
@@ -490,9 +537,15 @@ int pymo_broadcast(const BroadcastArgs& a, cudaStream_t st)
 {
     if (a.n == 0)
         return AQ_OK;
-    int64_t blocks = (a.n + kThreads - 1) / kThreads;
-    int64_t cap    = (int64_t) kNumSMs * 8 * 4;
-    pymo_broadcast_kernel<<<(unsigned) (blocks < cap ? blocks : cap), kThreads, 0, st>>>(a);
+    const bool small = (uint64_t) a.n <= 0xffffffffull;
+    const int vec    = pick_vec<float>(a.in, a.out, nullptr, 0) >= 4 ? 4 : 1;
+    const int64_t blocks = (a.n + (int64_t) kThreads * vec - 1) / ((int64_t) kThreads * vec);
+#define AQ_BC(V, S) launch_pdl(pymo_broadcast_kernel<V, S>, (unsigned) blocks, kThreads, 0, st, a)
+    if (vec == 4)
+        small ? AQ_BC(4, true) : AQ_BC(4, false);
+    else
+        small ? AQ_BC(1, true) : AQ_BC(1, false);
+#undef AQ_BC
     note_launch();
     return check_launch();
 }
