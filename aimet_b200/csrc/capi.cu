@@ -562,6 +562,17 @@ int aq_v2hist_merge_rows(const void* d_x, int dtype, int64_t n_per_row, int rows
                              d_scratch, d_updates, (cudaStream_t) stream);
 }
 
+int aq_v2hist_update_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, aq_v2hist_head_t* d_states,
+                          aq_v2hist_head_t* d_batches, int64_t block_stride, int state_has_stats, void* d_scratch,
+                          float* d_updates, void* stream)
+{
+    if (bad_v2hist(d_x, dtype, n_per_row, bins, d_states, d_scratch) || !d_batches || !d_updates ||
+        bad_v2hist_rows(rows, block_stride, bins))
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_update_rows(d_x, dtype, n_per_row, rows, bins, d_states, d_batches, block_stride, state_has_stats,
+                              d_scratch, d_updates, (cudaStream_t) stream);
+}
+
 int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,
                         int symmetric, int num_deltas, const float* d_offsets, int num_offsets, double gamma,
                         float* d_out, void* d_workspace, int64_t workspace_bytes, void* stream)

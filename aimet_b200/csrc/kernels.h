@@ -105,6 +105,9 @@ int v2hist_collect_rows(const void* x, int dtype, int64_t n, int rows, int nb, a
 int v2hist_merge_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq_v2hist_head_t* state,
                       const aq_v2hist_head_t* batch, int64_t block_stride, int state_has_stats, void* scratch,
                       float* updates, cudaStream_t st);
+int v2hist_update_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq_v2hist_head_t* state,
+                       aq_v2hist_head_t* batch, int64_t block_stride, int state_has_stats, void* scratch,
+                       float* updates, cudaStream_t st);
 int v2hist_sqnr_rows(const aq_v2hist_head_t* stats, int64_t block_stride, int rows, int nb, double num_steps,
                      int symmetric, int num_deltas, const float* offsets, int num_offsets, double gamma, float* out,
                      void* ws, int64_t ws_bytes, cudaStream_t st);

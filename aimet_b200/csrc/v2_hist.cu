@@ -30,14 +30,17 @@ constexpr float kEps32        = 1.1920928955078125e-07f;   // torch.finfo(torch.
 
 // Scratch of one collect / merge sequence (device memory, caller-owned):
 //   uint32 counts[AQ_V2HIST_MAX_BINS + 2]   bins, then "below lo", then "above hi"
+//   uint32 counts2[...]                     a second set for the fused collect + merge
 //   float2 partials[kV2HistMaxParts]        per-CTA finite (min, max)
 //   float  plan[8]                          lo, hi, batch_min, batch_max, any_finite, pad...
 struct V2HistScratch
 {
     uint32_t counts[AQ_V2HIST_MAX_BINS + 2];
     uint32_t pad[2];
+    uint32_t counts2[AQ_V2HIST_MAX_BINS + 2];   // the same batch counted over the widened range (fused update)
+    uint32_t pad2[2];
     float2 partials[kV2HistMaxParts];
-    float plan[8];
+    float plan[8];   // lo, hi, batch_min, batch_max, any_finite, widened lo, widened hi
 };
 
 // Several histograms per launch (per-channel observers): blockIdx.y is the histogram; these are the distances between
@@ -153,7 +156,11 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_plan_kernel(V2HistScratch*
     if ((threadIdx.x & 31) == 0)
         s_mn[threadIdx.x >> 5] = mn, s_mx[threadIdx.x >> 5] = mx;
     for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
+    {
         sc->counts[i] = 0;
+        if (merge == 2)
+            sc->counts2[i] = 0;
+    }
     __syncthreads();
     if (threadIdx.x != 0)
         return;
@@ -166,7 +173,7 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_plan_kernel(V2HistScratch*
         lo = 0.0f, hi = 1.0f;   // nothing finite: the caller is told through any_finite; counters stay meaningless
         mn = mx = 0.0f;
     }
-    else if (!merge)
+    else if (merge != 1)
     {
         float a = mn, b = mx;
         if (a == b)
@@ -182,16 +189,23 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_plan_kernel(V2HistScratch*
         hi = (state->max > mx) ? state->max : mx;
     }
     sc->plan[0] = lo, sc->plan[1] = hi, sc->plan[2] = mn, sc->plan[3] = mx, sc->plan[4] = any ? 1.0f : 0.0f;
+    if (merge == 2)
+    {
+        // fused collect + merge: the widened range as well (with nothing finite in the batch it is never used for bins)
+        sc->plan[5] = any ? ((state->min < mn) ? state->min : mn) : 0.0f;
+        sc->plan[6] = any ? ((state->max > mx) ? state->max : mx) : 1.0f;
+    }
 }
 
 // ---- pass 2: counts with the torch.histc bin rule, plus the elements below lo and above hi ------------------------
-template <typename T, int VEC>
+// DUAL: the batch is counted over its own range AND over the widened range of the merge in the same pass.
+template <typename T, int VEC, bool DUAL>
 __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __restrict__ x, int64_t n,
                                                                    V2HistScratch* __restrict__ sc, int nb, V2HRows rw)
 {
     pdl_launch_dependents();
-    extern __shared__ uint32_t s_cnt[];   // nb + 2
-    for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
+    extern __shared__ uint32_t s_cnt[];   // nb + 2 (twice with DUAL)
+    for (int i = threadIdx.x; i < (DUAL ? 2 : 1) * (nb + 2); i += kV2HistThreads)
         s_cnt[i] = 0;
     pdl_wait();
     x += (int64_t) blockIdx.y * rw.x_stride;
@@ -202,6 +216,16 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
         lo = __fsub_rn(lo, 1.0f), hi = __fadd_rn(hi, 1.0f);   // torch.histc's own rule for equal bounds
     const float width = __fsub_rn(hi, lo);
     const float nbf   = (float) nb;
+    float lo2 = 0.0f, hi2 = 0.0f, cmp_lo2 = 0.0f, cmp_hi2 = 0.0f, width2 = 1.0f;
+    if (DUAL)
+    {
+        lo2 = sc->plan[5], hi2 = sc->plan[6];
+        cmp_lo2 = lo2, cmp_hi2 = hi2;
+        if (lo2 == hi2)
+            lo2 = __fsub_rn(lo2, 1.0f), hi2 = __fadd_rn(hi2, 1.0f);
+        width2 = __fsub_rn(hi2, lo2);
+    }
+    uint32_t* s_cnt2 = s_cnt + (nb + 2);
     __syncthreads();
     auto take = [&](float f) {
         if (f >= lo && f <= hi)
@@ -214,6 +238,19 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
             atomicAdd(&s_cnt[nb], 1u);
         else if (f > cmp_hi)
             atomicAdd(&s_cnt[nb + 1], 1u);
+        if (DUAL)
+        {
+            if (f >= lo2 && f <= hi2)
+            {
+                int b = (int) floorf(__fdiv_rn(__fmul_rn(__fsub_rn(f, lo2), nbf), width2));
+                b     = b < nb - 1 ? b : nb - 1;
+                atomicAdd(&s_cnt2[b], 1u);
+            }
+            if (f < cmp_lo2)
+                atomicAdd(&s_cnt2[nb], 1u);
+            else if (f > cmp_hi2)
+                atomicAdd(&s_cnt2[nb + 1], 1u);
+        }
     };
     const int64_t npack  = n / VEC;
     const int64_t stride = (int64_t) gridDim.x * kV2HistThreads;
@@ -228,8 +265,12 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
         take(to_f32<T>(x[npack * VEC + threadIdx.x]));
     __syncthreads();
     for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
+    {
         if (s_cnt[i])
             atomicAdd(&sc->counts[i], s_cnt[i]);
+        if (DUAL && s_cnt2[i])
+            atomicAdd(&sc->counts2[i], s_cnt2[i]);
+    }
 }
 
 // _create_bin_edges(min, max): arange(0, bins + 1) * step + min with step = (max - min) / bins, after widening equal
@@ -292,7 +333,8 @@ __device__ __forceinline__ int v2h_bin_num(float width, float cur_min, float dat
 // once counts pass 2^24): one thread walks them in the same order; the rest is element-wise.
 __global__ void __launch_bounds__(kV2HistThreads) v2h_merge_kernel(const V2HistScratch* __restrict__ sc, int nb,
                                                                    aq_v2hist_head_t* __restrict__ state,
-                                                                   float* __restrict__ updates /* nb floats */, V2HRows rw)
+                                                                   float* __restrict__ updates /* nb floats */, V2HRows rw,
+                                                                   int dual)
 {
     pdl_launch_dependents();
     pdl_wait();
@@ -300,7 +342,16 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_merge_kernel(const V2HistS
     state   = v2h_row(state, rw.st_stride);
     updates += (int64_t) blockIdx.y * rw.upd_stride;
     float* hist      = v2h_hist(state);
-    const float umin = sc->plan[0], umax = sc->plan[1];
+    // after a fused pass the widened range and its counts sit in the second set
+    const uint32_t* __restrict__ counts = dual ? sc->counts2 : sc->counts;
+    const float umin = dual ? sc->plan[5] : sc->plan[0], umax = dual ? sc->plan[6] : sc->plan[1];
+    if (dual && sc->plan[4] == 0.0f)
+    {
+        // nothing finite in the batch: the reference raises; here the state is flagged and left as it is
+        if (threadIdx.x == 0)
+            state->error = 1;
+        return;
+    }
     const float cmin = state->min, cmax = state->max;
     const bool same  = (umin == cmin) && (umax == cmax);
     if (same)
@@ -347,11 +398,11 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_merge_kernel(const V2HistS
     __syncthreads();
     for (int i = threadIdx.x; i < nb; i += kV2HistThreads)
     {
-        float h = __fadd_rn((float) sc->counts[i], updates[i]);
+        float h = __fadd_rn((float) counts[i], updates[i]);
         if (i == 0)
-            h = __fadd_rn(h, (float) sc->counts[nb]);        // expanded[0]  += sum(x == -inf)
+            h = __fadd_rn(h, (float) counts[nb]);        // expanded[0]  += sum(x == -inf)
         if (i == nb - 1)
-            h = __fadd_rn(h, (float) sc->counts[nb + 1]);    // expanded[-1] += sum(x == +inf)
+            h = __fadd_rn(h, (float) counts[nb + 1]);    // expanded[-1] += sum(x == +inf)
         hist[i] = h;
     }
     v2h_write_edges(umin, umax, nb, v2h_edges(state, nb));
@@ -402,7 +453,12 @@ static int v2h_passes(const T* x, int64_t n, int rows, int nb, int merge, const 
     }                                                                                                                \
     launch_pdl(v2h_plan_kernel, dim3(1, ry), kV2HistThreads, 0, st, sc, nparts, nb, merge, state, batch, rw);        \
     note_launch();                                                                                                   \
-    launch_pdl(v2h_count_kernel<T, V>, dim3((unsigned) blocks, ry), kV2HistThreads, smem, st, x, n, sc, nb, rw);     \
+    if (merge == 2)                                                                                                  \
+        launch_pdl(v2h_count_kernel<T, V, true>, dim3((unsigned) blocks, ry), kV2HistThreads, 2 * smem, st, x, n, sc, \
+                   nb, rw);                                                                                          \
+    else                                                                                                             \
+        launch_pdl(v2h_count_kernel<T, V, false>, dim3((unsigned) blocks, ry), kV2HistThreads, smem, st, x, n, sc,   \
+                   nb, rw);                                                                                          \
     note_launch();
     if (vec >= 4 && sizeof(T) == 4)
     {
@@ -470,7 +526,37 @@ int v2hist_merge_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq_
     if (rc != AQ_OK)
         return rc;
     launch_pdl(v2h_merge_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb, state,
-               updates, rw);
+               updates, rw, 0);
+    note_launch();
+    return check_launch();
+}
+
+// collect_stats + merge_stats of one batch in two passes over the data instead of three: finite min / max, then ONE
+// counting pass that fills the batch's own histogram and the histogram over the widened range.
+int v2hist_update_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq_v2hist_head_t* state,
+                       aq_v2hist_head_t* batch, int64_t block_stride, int state_has_stats, void* scratch,
+                       float* updates, cudaStream_t st)
+{
+    if (!state_has_stats)
+    {
+        int rc = v2hist_collect_rows(x, dtype, n, rows, nb, batch, block_stride, scratch, st);
+        if (rc != AQ_OK)
+            return rc;
+        return v2hist_merge_rows(x, dtype, n, rows, nb, state, batch, block_stride, 0, scratch, updates, st);
+    }
+    if (rows < 1 || rows > 65535)
+        return AQ_ERR_TOO_LARGE;
+    V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
+    const V2HRows rw {rows > 1 ? n : 0, rows > 1 ? v2hist_scratch_bytes() : 0, rows > 1 ? block_stride : 0,
+                      rows > 1 ? (int64_t) nb : 0};
+    int rc = v2h_passes_any(x, dtype, n, rows, nb, 2, state, nullptr, sc, rw, st);
+    if (rc != AQ_OK)
+        return rc;
+    launch_pdl(v2h_finish_collect_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb,
+               batch, rw);
+    note_launch();
+    launch_pdl(v2h_merge_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb, state,
+               updates, rw, 1);
     note_launch();
     return check_launch();
 }

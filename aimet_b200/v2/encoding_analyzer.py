@@ -450,6 +450,24 @@ class _HistogramObserver:
                                            updates.data_ptr(), stream), "aq_v2hist_merge_rows")
         new_stats_list[0]._rows = None   # the batch need not outlive the update
 
+    @torch.no_grad()
+    def update_stats(self, input_tensor: torch.Tensor):
+        """collect_stats + merge_stats of one batch with a single counting pass (two passes over the data, not three)."""
+        rows = self._rows(input_tensor)
+        scratch, updates = self._buffers(input_tensor.device)
+        stream = torch.cuda.current_stream(input_tensor.device).cuda_stream
+        first = self._state is None
+        if first:
+            self._state = _new_blocks(self.num_histograms, self.num_bins, input_tensor.device)
+            self._dtype = input_tensor.dtype
+        blocks = _new_blocks(self.num_histograms, self.num_bins, rows.device)
+        with ops._on(input_tensor):
+            check(lib.aq_v2hist_update_rows(rows.data_ptr(), _DT[rows.dtype], rows.shape[1], self.num_histograms,
+                                            self.num_bins, self._state.data_ptr(), blocks.data_ptr(),
+                                            blocks.stride(0) * 4, 0 if first else 1, scratch.data_ptr(),
+                                            updates.data_ptr(), stream), "aq_v2hist_update_rows")
+        return self._views(blocks, input_tensor.dtype)
+
     def reset_stats(self):
         self._state = None
 
@@ -483,9 +501,7 @@ class SqnrEncodingAnalyzer(EncodingAnalyzer):
 
     @torch.no_grad()
     def update_stats(self, input_tensor: torch.Tensor):
-        new_stats = self.observer.collect_stats(input_tensor)
-        self.observer.merge_stats(new_stats, input_tensor)
-        return new_stats
+        return self.observer.update_stats(input_tensor)
 
     def compute_dynamic_encodings(self, input_tensor, num_steps, is_symmetric):
         return self.compute_encodings_from_stats(self.observer.collect_stats(input_tensor), num_steps, is_symmetric)

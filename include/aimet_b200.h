@@ -449,6 +449,12 @@ int aq_v2hist_collect_rows(const void* d_x, int dtype, int64_t n_per_row, int ro
 int aq_v2hist_merge_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, aq_v2hist_head_t* d_states,
                          const aq_v2hist_head_t* d_batches, int64_t block_stride, int state_has_stats, void* d_scratch,
                          float* d_updates, void* stream);
+/* aq_v2hist_collect_rows followed by aq_v2hist_merge_rows of the same batch (what update_stats does,
+ * encoding_analyzer.py:283-291), with one counting pass that fills both the batch's own histograms (d_batches) and
+ * the histograms over the widened range: two passes over d_x instead of three. */
+int aq_v2hist_update_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, aq_v2hist_head_t* d_states,
+                          aq_v2hist_head_t* d_batches, int64_t block_stride, int state_has_stats, void* d_scratch,
+                          float* d_updates, void* stream);
 int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,
                         int symmetric, int num_deltas, const float* d_offsets, int num_offsets, double gamma,
                         float* d_out, void* d_workspace, int64_t workspace_bytes, void* stream);
