@@ -83,6 +83,8 @@ SIGNATURES = {
     "aq_v2hist_merge_rows": (_i32, [_vp, _i32, _i64, _i32, _i32, _vp, _vp, _i64, _i32, _vp, _vp, _vp]),
     "aq_v2hist_update_rows": (_i32, [_vp, _i32, _i64, _i32, _i32, _vp, _vp, _i64, _i32, _vp, _vp, _vp]),
     "aq_v2hist_sqnr_rows": (_i32, [_vp, _i64, _i32, _i32, _f64, _i32, _i32, _vp, _i32, _f64, _vp, _vp, _i64, _vp]),
+    "aq_v2hist_sqnr_encode_rows": (_i32, [_vp, _i64, _i32, _i32, _f64, _i32, _i32, _vp, _i32, _f64, _i32, _f64, _vp, _vp,
+                                          _i64, _vp]),
     "aq_v2hist_sqnr_workspace_bytes": (_i64, []),
     "aq_v2hist_sqnr": (_i32, [_vp, _i32, _f64, _i32, _i32, _vp, _i32, _f64, _vp, _vp, _i64, _vp]),
     "aq_tfe_compute_encoding": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i64,

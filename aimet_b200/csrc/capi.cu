@@ -586,6 +586,21 @@ int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, i
                             gamma, d_out, d_workspace, workspace_bytes, (cudaStream_t) stream);
 }
 
+int aq_v2hist_sqnr_encode_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,
+                               int symmetric, int num_deltas, const float* d_offsets, int num_offsets, double gamma,
+                               int stats_dtype, double qmin, float* d_out, void* d_workspace, int64_t workspace_bytes,
+                               void* stream)
+{
+    if (!d_stats || bins < 1 || bins > AQ_V2HIST_MAX_BINS || !(num_steps > 0) || num_deltas < 2 || !d_offsets ||
+        num_offsets < 1 || !d_out || bad_v2hist_rows(rows, block_stride, bins) || stats_dtype < AQ_F32 ||
+        stats_dtype > AQ_BF16)
+        return AQ_ERR_INVALID_ARG;
+    if (!d_workspace || ((uintptr_t) d_workspace % 256) != 0)
+        return AQ_ERR_WORKSPACE;
+    return v2hist_sqnr_rows(d_stats, block_stride, rows, bins, num_steps, symmetric, num_deltas, d_offsets, num_offsets,
+                            gamma, d_out, d_workspace, workspace_bytes, (cudaStream_t) stream, 4, stats_dtype, qmin);
+}
+
 int64_t aq_v2hist_sqnr_workspace_bytes(void)
 {
     return v2hist_sqnr_workspace_bytes();

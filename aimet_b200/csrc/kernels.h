@@ -110,7 +110,8 @@ int v2hist_update_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq
                        float* updates, cudaStream_t st);
 int v2hist_sqnr_rows(const aq_v2hist_head_t* stats, int64_t block_stride, int rows, int nb, double num_steps,
                      int symmetric, int num_deltas, const float* offsets, int num_offsets, double gamma, float* out,
-                     void* ws, int64_t ws_bytes, cudaStream_t st);
+                     void* ws, int64_t ws_bytes, cudaStream_t st, int out_width = 2, int stats_dtype = 0,
+                     double qmin = 0.0);
 int64_t v2hist_sqnr_workspace_bytes();
 int v2hist_sqnr(const aq_v2hist_head_t* stats, int nb, double num_steps, int symmetric, int num_deltas,
                 const float* offsets, int num_offsets, double gamma, float* out, void* ws, int64_t ws_bytes,

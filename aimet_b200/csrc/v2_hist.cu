@@ -26,6 +26,7 @@ namespace aq
 
 constexpr int kV2HistThreads  = 256;
 constexpr int kV2HistMaxParts = 1024;
+constexpr int kV2HistUnroll   = 4;
 constexpr float kEps32        = 1.1920928955078125e-07f;   // torch.finfo(torch.float32).eps
 
 // Scratch of one collect / merge sequence (device memory, caller-owned):
@@ -92,12 +93,33 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_finite_minmax_kernel(const
     };
     const int64_t npack  = n / VEC;
     const int64_t stride = (int64_t) gridDim.x * kV2HistThreads;
-    for (int64_t p = (int64_t) blockIdx.x * kV2HistThreads + threadIdx.x; p < npack; p += stride)
+    int64_t p            = (int64_t) blockIdx.x * kV2HistThreads + threadIdx.x;
+    // kV2HistUnroll packets in flight per thread (one at a time left the pass latency-bound at a quarter of the
+    // memory bandwidth); the last, partial group is issued together as well
+    for (; p + (kV2HistUnroll - 1) * stride < npack; p += kV2HistUnroll * stride)
     {
-        const Pack<T, VEC> v = load_pack<T, VEC>(x + p * VEC);
+        Pack<T, VEC> v[kV2HistUnroll];
 #pragma unroll
-        for (int e = 0; e < VEC; ++e)
-            take(to_f32<T>(v.v[e]));
+        for (int u = 0; u < kV2HistUnroll; ++u)
+            v[u] = load_pack<T, VEC>(x + (p + u * stride) * VEC);
+#pragma unroll
+        for (int u = 0; u < kV2HistUnroll; ++u)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+                take(to_f32<T>(v[u].v[e]));
+    }
+    {
+        Pack<T, VEC> v[kV2HistUnroll - 1];
+#pragma unroll
+        for (int u = 0; u < kV2HistUnroll - 1; ++u)
+            if (p + u * stride < npack)
+                v[u] = load_pack<T, VEC>(x + (p + u * stride) * VEC);
+#pragma unroll
+        for (int u = 0; u < kV2HistUnroll - 1; ++u)
+            if (p + u * stride < npack)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e)
+                    take(to_f32<T>(v[u].v[e]));
     }
     if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * VEC))
         take(to_f32<T>(x[npack * VEC + threadIdx.x]));
@@ -227,42 +249,78 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
     }
     uint32_t* s_cnt2 = s_cnt + (nb + 2);
     __syncthreads();
-    auto take = [&](float f) {
+    // bin = min(nb - 1, floor(((f - lo) * nb) / width)) needs the correctly rounded quotient only when it lies next to an
+    // integer: the product with the rounded reciprocal differs from it by less than 2^-22 |q|, so the division is
+    // done again, exactly, only inside that band around an integer (about one element in a thousand).
+    const float rwidth = __frcp_rn(width), rwidth2 = __frcp_rn(width2);
+    auto bin_of = [&](float f, float lo_, float w_, float rw_) {
+        const float t  = __fmul_rn(__fsub_rn(f, lo_), nbf);
+        const float qf = __fmul_rn(t, rw_);
+        float fl       = floorf(qf);
+        const float d  = __fsub_rn(qf, fl), band = fmaf(qf, 2.384185791015625e-07f, 1e-30f);
+        if (!(d >= band && d <= 1.0f - band))   // also taken for NaN / Inf
+            fl = floorf(__fdiv_rn(t, w_));
+        const int b = (int) fl;
+        return b < nb - 1 ? b : nb - 1;
+    };
+    auto take_n = [&](float f, uint32_t k) {
         if (f >= lo && f <= hi)
-        {
-            int b = (int) floorf(__fdiv_rn(__fmul_rn(__fsub_rn(f, lo), nbf), width));
-            b     = b < nb - 1 ? b : nb - 1;
-            atomicAdd(&s_cnt[b], 1u);
-        }
+            atomicAdd(&s_cnt[bin_of(f, lo, width, rwidth)], k);
         if (f < cmp_lo)
-            atomicAdd(&s_cnt[nb], 1u);
+            atomicAdd(&s_cnt[nb], k);
         else if (f > cmp_hi)
-            atomicAdd(&s_cnt[nb + 1], 1u);
+            atomicAdd(&s_cnt[nb + 1], k);
         if (DUAL)
         {
             if (f >= lo2 && f <= hi2)
-            {
-                int b = (int) floorf(__fdiv_rn(__fmul_rn(__fsub_rn(f, lo2), nbf), width2));
-                b     = b < nb - 1 ? b : nb - 1;
-                atomicAdd(&s_cnt2[b], 1u);
-            }
+                atomicAdd(&s_cnt2[bin_of(f, lo2, width2, rwidth2)], k);
             if (f < cmp_lo2)
-                atomicAdd(&s_cnt2[nb], 1u);
+                atomicAdd(&s_cnt2[nb], k);
             else if (f > cmp_hi2)
-                atomicAdd(&s_cnt2[nb + 1], 1u);
+                atomicAdd(&s_cnt2[nb + 1], k);
         }
+    };
+    // Exact zeros (half of a post-ReLU activation) would all land on one counter: they are tallied in a register and
+    // added once per thread at the end.
+    uint32_t zeros = 0;
+    auto take = [&](float f) {
+        if (f == 0.0f)
+            ++zeros;
+        else
+            take_n(f, 1u);
     };
     const int64_t npack  = n / VEC;
     const int64_t stride = (int64_t) gridDim.x * kV2HistThreads;
-    for (int64_t p = (int64_t) blockIdx.x * kV2HistThreads + threadIdx.x; p < npack; p += stride)
+    int64_t p            = (int64_t) blockIdx.x * kV2HistThreads + threadIdx.x;
+    for (; p + (kV2HistUnroll - 1) * stride < npack; p += kV2HistUnroll * stride)
     {
-        const Pack<T, VEC> v = load_pack<T, VEC>(x + p * VEC);
+        Pack<T, VEC> v[kV2HistUnroll];
 #pragma unroll
-        for (int e = 0; e < VEC; ++e)
-            take(to_f32<T>(v.v[e]));
+        for (int u = 0; u < kV2HistUnroll; ++u)
+            v[u] = load_pack<T, VEC>(x + (p + u * stride) * VEC);
+#pragma unroll
+        for (int u = 0; u < kV2HistUnroll; ++u)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+                take(to_f32<T>(v[u].v[e]));
+    }
+    {
+        Pack<T, VEC> v[kV2HistUnroll - 1];
+#pragma unroll
+        for (int u = 0; u < kV2HistUnroll - 1; ++u)
+            if (p + u * stride < npack)
+                v[u] = load_pack<T, VEC>(x + (p + u * stride) * VEC);
+#pragma unroll
+        for (int u = 0; u < kV2HistUnroll - 1; ++u)
+            if (p + u * stride < npack)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e)
+                    take(to_f32<T>(v[u].v[e]));
     }
     if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * VEC))
         take(to_f32<T>(x[npack * VEC + threadIdx.x]));
+    if (zeros)
+        take_n(0.0f, zeros);
     __syncthreads();
     for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
     {
@@ -592,7 +650,10 @@ struct SqnrArgs
     unsigned int* ticket;   // workspace, zero on entry, left zero
     float* out;             // {min, max}
     int64_t st_stride;      // bytes between the statistics blocks of consecutive histograms (blockIdx.y)
-    int64_t ws_stride;      // bytes between their workspaces; results are 2 floats apart
+    int64_t ws_stride;      // bytes between their workspaces; results are out_width floats apart
+    int out_width;          // 2: {min, max};  4: {min, max, scale, offset} of a quantizer with lower code bound qmin,
+    int stats_dtype;        //    min / max first rounded to the statistics dtype as the reference's cast does
+    float qmin;
 };
 
 __device__ __forceinline__ void sqnr_candidate(const SqnrArgs& a, float min_v, float max_v, int cand, float& delta,
@@ -634,7 +695,7 @@ __global__ void __launch_bounds__(kSqnrWarps * 32) v2h_sqnr_kernel(SqnrArgs a)
     a.stats  = v2h_row(a.stats, a.st_stride);
     a.ticket = v2h_row(a.ticket, a.ws_stride);
     a.noise  = v2h_row(a.noise, a.ws_stride);
-    a.out += 2 * (int64_t) blockIdx.y;
+    a.out += a.out_width * (int64_t) blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_delta  = a.symmetric ? 1 : a.num_offsets + 1;
     const int candidates = a.num_deltas * per_delta;
@@ -721,10 +782,23 @@ __global__ void __launch_bounds__(kSqnrWarps * 32) v2h_sqnr_kernel(SqnrArgs a)
         float delta = 0.0f, offset = 0.0f;
         if (best_i != INT_MAX)
             sqnr_candidate(a, min_v, max_v, best_i, delta, offset);
-        const float mn = __fmul_rn(offset, delta);
-        a.out[0]       = mn;
-        a.out[1]       = __fadd_rn(mn, __fmul_rn(a.num_steps, delta));
-        *a.ticket      = 0;
+        float mn = __fmul_rn(offset, delta);
+        float mx = __fadd_rn(mn, __fmul_rn(a.num_steps, delta));
+        if (a.out_width == 4)
+        {
+            // what the quantizer derives from the returned range (affine/quantizer.py:222-246): the range in the
+            // statistics dtype, then float32 scale = (max - min) / num_steps and offset = round(min / scale) - qmin
+            if (a.stats_dtype == AQ_F16)
+                mn = __half2float(__float2half_rn(mn)), mx = __half2float(__float2half_rn(mx));
+            else if (a.stats_dtype == AQ_BF16)
+                mn = __bfloat162float(__float2bfloat16_rn(mn)), mx = __bfloat162float(__float2bfloat16_rn(mx));
+            const float scale = __fdiv_rn(__fsub_rn(mx, mn), a.num_steps);
+            a.out[2]          = scale;
+            a.out[3]          = a.symmetric ? 0.0f : __fsub_rn(rintf(__fdiv_rn(mn, scale)), a.qmin);
+        }
+        a.out[0]  = mn;
+        a.out[1]  = mx;
+        *a.ticket = 0;
     }
 }
 
@@ -735,9 +809,10 @@ int64_t v2hist_sqnr_workspace_bytes()
 
 int v2hist_sqnr_rows(const aq_v2hist_head_t* stats, int64_t block_stride, int rows, int nb, double num_steps,
                      int symmetric, int num_deltas, const float* offsets, int num_offsets, double gamma, float* out,
-                     void* ws, int64_t ws_bytes, cudaStream_t st)
+                     void* ws, int64_t ws_bytes, cudaStream_t st, int out_width, int stats_dtype, double qmin)
 {
     SqnrArgs a;
+    a.out_width = out_width, a.stats_dtype = stats_dtype, a.qmin = (float) qmin;
     a.stats = stats, a.nb = nb, a.num_steps = (float) num_steps;
     a.min_gap   = (float) ((double) kEps32 * num_steps);
     a.symmetric = symmetric, a.num_deltas = num_deltas, a.num_offsets = num_offsets, a.offsets = offsets;
@@ -763,7 +838,7 @@ int v2hist_sqnr(const aq_v2hist_head_t* stats, int nb, double num_steps, int sym
                 cudaStream_t st)
 {
     return v2hist_sqnr_rows(stats, 0, 1, nb, num_steps, symmetric, num_deltas, offsets, num_offsets, gamma, out, ws,
-                            ws_bytes, st);
+                            ws_bytes, st, 2, AQ_F32, 0.0);
 }
 
 }   // namespace aq

@@ -506,6 +506,34 @@ class SqnrEncodingAnalyzer(EncodingAnalyzer):
     def compute_dynamic_encodings(self, input_tensor, num_steps, is_symmetric):
         return self.compute_encodings_from_stats(self.observer.collect_stats(input_tensor), num_steps, is_symmetric)
 
+    @torch.no_grad()
+    def fused_update(self, input_tensor: torch.Tensor, num_steps: int, is_symmetric: bool, qmin: int):
+        """One calibration step: the statistics update (two passes over the data), then the search on THIS batch's
+        histograms with the scale / offset to quantize the batch with computed in the same launch.  Returns float32
+        ``(scale, offset)`` shaped like the observer."""
+        if num_steps <= 0:
+            raise ValueError('The number of quantization bins cannot be less than or equal to 0.')
+        obs = self.observer
+        stats = obs.update_stats(input_tensor)
+        blocks = stats[0]._blocks
+        device = blocks.device
+        rows = len(stats)
+        offsets = self._offset_grid(num_steps, bool(is_symmetric), device)
+        need = rows * int(lib.aq_v2hist_sqnr_workspace_bytes())
+        if self._ws is None or self._ws.device != device or self._ws.numel() < need:
+            self._ws = torch.zeros(need, dtype=torch.uint8, device=device)
+        out = torch.empty((rows, 4), dtype=torch.float32, device=device)
+        num_deltas = self.sym_delta_candidates if is_symmetric else self.asym_delta_candidates
+        with ops._on(out):
+            check(lib.aq_v2hist_sqnr_encode_rows(blocks.data_ptr(), blocks.stride(0) * 4, rows, obs.num_bins,
+                                                 float(num_steps), int(bool(is_symmetric)), int(num_deltas),
+                                                 offsets.data_ptr(), offsets.numel(), float(self.gamma),
+                                                 _DT[input_tensor.dtype], float(qmin), out.data_ptr(),
+                                                 self._ws.data_ptr(), self._ws.numel(),
+                                                 torch.cuda.current_stream(device).cuda_stream),
+                  "aq_v2hist_sqnr_encode_rows")
+        return out[:, 2].view(obs.shape), out[:, 3].view(obs.shape)
+
     def _offset_grid(self, num_steps, is_symmetric: bool, device) -> torch.Tensor:
         """The offsets the search walks: host arithmetic of a handful of values, exactly the reference's expressions
         (encoding_analyzer.py:629-632, :644), cached per (num_steps, symmetric, device)."""

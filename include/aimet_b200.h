@@ -459,6 +459,14 @@ int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, i
                         int symmetric, int num_deltas, const float* d_offsets, int num_offsets, double gamma,
                         float* d_out, void* d_workspace, int64_t workspace_bytes, void* stream);
 
+/* aq_v2hist_sqnr_rows plus what the quantizer derives from the chosen range while it calibrates (affine/quantizer.py:
+ * 222-246, 317-374): min / max cast to stats_dtype, then float32 scale = (max - min) / num_steps and offset =
+ * round(min / scale) - qmin (0 when symmetric).  d_out: rows x {min, max, scale, offset}. */
+int aq_v2hist_sqnr_encode_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,
+                               int symmetric, int num_deltas, const float* d_offsets, int num_offsets, double gamma,
+                               int stats_dtype, double qmin, float* d_out, void* d_workspace, int64_t workspace_bytes,
+                               void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -109,3 +109,31 @@ def test_sqnr_analyzer_protocol(cuda):
     h.update_stats(torch.randn(4000, device=cuda).to(torch.bfloat16))
     mn, mx = h.compute_encodings(255, True)
     assert mn.dtype == torch.bfloat16 and mn.shape == ()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,steps,sym", [((), 255, False), ((6, 1), 255, True), ((6, 1), 15, False)])
+def test_fused_calibration_step_matches_separate_calls(cuda, dtype, shape, steps, sym):
+    """fused_update (statistics update with one counting pass + search + scale / offset in the search launch) against
+    collect_stats / merge_stats / compute_encodings_from_stats followed by the quantizer's expressions."""
+    from aimet_b200.v2.encoding_analyzer import SqnrEncodingAnalyzer
+    torch.manual_seed(7)
+    qmin = -(steps + 1) // 2 if sym else 0
+    fused, plain = SqnrEncodingAnalyzer(shape), SqnrEncodingAnalyzer(shape)
+    for b in range(3):
+        x = (torch.randn(6, 4000, device=cuda) * (1.0 + b) + (0.0 if sym else 0.3)).to(dtype)
+        scale, offset = fused.fused_update(x, steps, sym, qmin)
+        stats = plain.observer.collect_stats(x)
+        plain.observer.merge_stats(stats, x)
+        dmin, dmax = plain.compute_encodings_from_stats(stats, steps, sym)
+        want_scale = (dmax.float() - dmin.float()) / torch.tensor(float(steps), device=cuda)
+        want_offset = torch.zeros_like(want_scale) if sym else torch.round(dmin.float() / want_scale) - qmin
+        np.testing.assert_array_equal(scale.cpu().numpy(), want_scale.cpu().numpy())
+        np.testing.assert_array_equal(offset.cpu().numpy(), want_offset.cpu().numpy())
+    for a, b in zip(fused.observer.get_stats(), plain.observer.get_stats()):
+        np.testing.assert_array_equal(a.histogram.cpu().numpy(), b.histogram.cpu().numpy())
+        np.testing.assert_array_equal(a.bin_edges.cpu().numpy(), b.bin_edges.cpu().numpy())
+    got, want = fused.compute_encodings(steps, sym), plain.compute_encodings(steps, sym)
+    np.testing.assert_array_equal(got[0].float().cpu().numpy(), want[0].float().cpu().numpy())
+    np.testing.assert_array_equal(got[1].float().cpu().numpy(), want[1].float().cpu().numpy())
+
