@@ -613,7 +613,8 @@ def qdq_numbers(torch, lib, device, peak):
 KERNEL_CASES = ("tfe_hist", "tfe_hist_many", "tfe_offer_grid", "minmax_f32", "minmax_f32_rows", "minmax_bf16_block64", "v2_qdq_f32", "v2_qdq_f32_mask",
                 "v2_qdq_f32_per_channel", "v2_qdq_bf16", "v2_qdq_bf16_block64", "v2_bwd_f32", "v2_bwd_bf16",
                 "pymo_qdq_f32", "pymo_qdq_f32_per_channel", "ste_v1_f32", "tfe_replay", "tfe_search",
-                "v2_param_grad_f32_per_channel", "pymo_broadcast_f32")
+                "v2_param_grad_f32_per_channel", "pymo_broadcast_f32", "v2hist_update_f32", "quantize_packed_f32",
+                "qdq_fp16_f32", "tfe_mse")
 
 
 def build_kernel_case(name, mb, torch, lib, device):
@@ -640,6 +641,17 @@ def build_kernel_case(name, mb, torch, lib, device):
             out.append((a * (0.02 if half else 1.0)).to(torch.bfloat16 if half else torch.float32))
         return out
 
+    if name == "tfe_mse":
+        # the MSE analyzer's candidate search on the statistics of 8 post-ReLU batches (replay included)
+        g = torch.Generator(device=device)
+        g.manual_seed(5)
+        x = torch.relu(torch.randn(1 << 22, device=device, generator=g))
+        st = ops.TfeDeviceState(device, capacity=8)
+        st.init_grid_from(ops.minmax(x).reshape(-1))
+        for r in range(8):
+            st.add_batch(x[r * 4096:r * 4096 + (1 << 19)], r)
+        calls = [lambda: (st.mse_encoding(True, 8, False, False, False), 0)[1]]
+        return calls, 8 * 2056 + 2 * 512 * 8, [st, x]
     if name in ("tfe_replay", "tfe_search"):
         # the tail of a calibration: running-mean replay over `mb` x 8 per-batch rows (2048 at the default), SQNR search
         rows = mb * 8
@@ -713,6 +725,22 @@ def build_kernel_case(name, mb, torch, lib, device):
         calls = [lambda i=i: lib.aq_v2_quantize(P(xs[i]), P(ys[i]), P(ms[i]) if ms else None, dt, n, num_ch, inner, P(s), P(o),
                                                 qmin, qmax, 0, 0, stream) for i in range(nbuf)]
         return calls, (2 * esz + (1 if ms else 0)) * n + (8 * num_ch if num_ch > 1 else 0), [s, o, ms, ys] + xs
+    if name == "v2hist_update_f32":
+        # one calibration step of the v2 histogram observer on a post-ReLU activation: finite min/max pass, then one
+        # counting pass for the batch's own range and the widened range (2048 bins), merge into the running histogram
+        from aimet_b200.v2.encoding_analyzer import SqnrEncodingAnalyzer
+        xr = data("relu_outliers")
+        an = SqnrEncodingAnalyzer(())
+        an.update_stats(xr[0])
+        calls = [lambda i=i: (an.update_stats(xr[i]), 0)[1] for i in range(nbuf)]
+        return calls, 8 * n, [an] + xr
+    if name == "quantize_packed_f32":
+        outs = [torch.empty(n, dtype=torch.uint8, device=device) for _ in range(nbuf)]
+        calls = [lambda i=i: lib.aq_quantize_packed(P(xs[i]), P(outs[i]), n, -4.4, 4.6, 8, 0, 0, stream) for i in range(nbuf)]
+        return calls, 5 * n, [outs] + xs
+    if name == "qdq_fp16_f32":
+        calls = [lambda i=i: lib.aq_qdq_fp16(P(xs[i]), P(ys[i]), n, stream) for i in range(nbuf)]
+        return calls, 8 * n, [ys] + xs
     if name == "v2_param_grad_f32_per_channel":
         # scale / offset gradients summed per channel inside the kernel: rows of 2304 elements, 8-bit signed grid
         num_ch, inner = n // 2304, 2304
