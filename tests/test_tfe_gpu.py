@@ -177,6 +177,31 @@ def test_histogram_many_equals_single(oracle, cuda, m, stride):
         np.testing.assert_array_equal(h0[i * stride], oracle.hist512(x.cpu().numpy(), bs, po))
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_histogram_many_mixed_sizes(oracle, cuda, seed):
+    """Launches of 1..16 batches whose sizes range from empty to millions of samples (so that every way of splitting
+    the batches over the CTAs is taken: fewer CTAs than batches, a grid cut to a multiple of the batch count, the full
+    grid with several (batch, slice) pairs per CTA), some starting off a 16-byte boundary, against the oracle row by row."""
+    from aimet_b200 import ops
+    rng = np.random.default_rng(900 + seed)
+    m = int(rng.integers(1, 17))
+    big = [int(rng.integers(200_000, 3_000_000)) for _ in range(m)] if seed % 2 else \
+          [int(rng.choice([0, 1, 3, 5, 17, 4096, 70_001, 900_000])) for _ in range(m)]
+    xs = []
+    for i, n in enumerate(big):
+        off = int(rng.integers(0, 4))
+        base = dev(relu_activations(n + off, 40 * seed + i) if i % 3 else normal(n + off, 40 * seed + i, 2.0, 0.5), cuda)
+        xs.append(base[off:])
+    st = ops.TfeDeviceState(cuda, m)
+    st.init_grid_from(torch.tensor([-1.5, 9.0], device=cuda))
+    st.add_batches(xs, 0, 1)
+    h, c = _rows(st)
+    np.testing.assert_array_equal(c[:m], [x.numel() for x in xs])
+    bs, po = oracle.pdf_geometry(st.x_left().cpu().numpy())
+    for i, x in enumerate(xs):
+        np.testing.assert_array_equal(h[i], oracle.hist512(x.cpu().numpy(), bs, po), err_msg=f"batch {i} of {m}, n={x.numel()}")
+
+
 def test_histogram_many_before_grid_counts_nothing(cuda):
     from aimet_b200 import ops
     st = ops.TfeDeviceState(cuda, 4)
