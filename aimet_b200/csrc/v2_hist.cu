@@ -263,10 +263,12 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
         const int b = (int) fl;
         return b < nb - 1 ? b : nb - 1;
     };
+    // An element inside [lo, hi] is never beyond the edges the end bins are judged by (the two pairs differ only when
+    // the bounds are equal, and then every finite element equals them), so the tests are exclusive.
     auto take_n = [&](float f, uint32_t k) {
         if (f >= lo && f <= hi)
             atomicAdd(&s_cnt[bin_of(f, lo, width, rwidth)], k);
-        if (f < cmp_lo)
+        else if (f < cmp_lo)
             atomicAdd(&s_cnt[nb], k);
         else if (f > cmp_hi)
             atomicAdd(&s_cnt[nb + 1], k);
@@ -274,7 +276,7 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
         {
             if (f >= lo2 && f <= hi2)
                 atomicAdd(&s_cnt2[bin_of(f, lo2, width2, rwidth2)], k);
-            if (f < cmp_lo2)
+            else if (f < cmp_lo2)
                 atomicAdd(&s_cnt2[nb], k);
             else if (f > cmp_hi2)
                 atomicAdd(&s_cnt2[nb + 1], k);
