@@ -608,7 +608,7 @@ def qdq_numbers(torch, lib, device, peak):
 
 
 # ---------------------------------------------------------------------------------------------------------------------
-# single-kernel cases (micro-benchmarks; also the small commands the ncu captures under profiles/ were taken with)
+# single-kernel cases (micro-benchmarks; small enough to capture under a profiler: one kernel, a few launches)
 # ---------------------------------------------------------------------------------------------------------------------
 KERNEL_CASES = ("tfe_hist", "tfe_hist_many", "tfe_offer_grid", "minmax_f32", "minmax_f32_rows", "minmax_bf16_block64", "v2_qdq_f32", "v2_qdq_f32_mask",
                 "v2_qdq_f32_per_channel", "v2_qdq_bf16", "v2_qdq_bf16_block64", "v2_bwd_f32", "v2_bwd_bf16",
