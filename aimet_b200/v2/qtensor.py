@@ -66,6 +66,18 @@ def _plain(value):
     return tree_map(lambda t: t.as_subclass(torch.Tensor) if isinstance(t, QuantizedTensorBase) else t, value)
 
 
+def _plain_unless_encoded(value):
+    """Results of operations that are not known to preserve the quantization: plain tensors -- except a result that
+    already carries an encoding of its own (a deep copy brings its copied attributes along)."""
+
+    def one(t):
+        if isinstance(t, QuantizedTensorBase) and getattr(t, "encoding", None) is None:
+            return t.as_subclass(torch.Tensor)
+        return t
+
+    return tree_map(one, value)
+
+
 class QuantizedTensorBase(torch.Tensor):
     """Common behaviour of the two classes below (tensor.py:62-358)."""
 
@@ -139,7 +151,7 @@ class QuantizedTensorBase(torch.Tensor):
         if out is first:
             out.encoding = None   # changed in place: whatever described the old values is stale
             return out
-        return _plain(out)
+        return _plain_unless_encoded(out)
 
 
 class QuantizedTensor(QuantizedTensorBase):

@@ -72,10 +72,30 @@ class _RoundSte(torch.autograd.Function):
 class AffineEncoding:
     """Scale / offset / integer grid of one quantizer (affine/encoding.py:54-280)."""
 
-    def __init__(self, scale: torch.Tensor, offset: torch.Tensor, qmin: int, qmax: int, symmetry: bool = False,
-                 block_size: Optional[Sequence[int]] = None):
+    def __init__(self, scale: torch.Tensor, offset: torch.Tensor, *args, **kwargs):
+        """``AffineEncoding(scale, offset, qmin, qmax, symmetry=False, block_size=None)`` or
+        ``AffineEncoding(scale, offset, bitwidth, signed=False, symmetry=False, block_size=None)``: the second form is
+        recognised by a boolean (or missing) fourth argument, as in the reference (encoding.py:60-110)."""
+        pos = list(args) + [None] * (4 - len(args))
+        first = kwargs.pop("qmin", kwargs.pop("bitwidth", pos[0]))
+        second = kwargs.pop("qmax", kwargs.pop("signed", pos[1]))
+        symmetry = kwargs.pop("symmetry", pos[2])
+        block_size = kwargs.pop("block_size", pos[3])
+        if kwargs:
+            raise TypeError(f"AffineEncoding.__init__ got unexpected keyword argument: {', '.join(kwargs.keys())}")
+        if second is None or isinstance(second, bool):
+            if first is None:
+                raise TypeError("AffineEncoding: expected (scale, offset, qmin, qmax, ...) or (scale, offset, bitwidth, "
+                                "signed, ...)")
+            qmin, qmax = derive_qmin_qmax(int(first), signed=bool(second))
+        else:
+            if first is None:
+                raise TypeError("AffineEncoding: qmin is missing")
+            qmin, qmax = first, second
+        if qmin >= qmax:
+            raise ValueError(f"qmax should be strictly larger than qmin. Got qmax={qmax}, qmin={qmin}")
         self.scale, self.offset, self.qmin, self.qmax = scale, offset, int(qmin), int(qmax)
-        self.symmetry, self.block_size = bool(symmetry), block_size
+        self.symmetry, self.block_size = bool(symmetry) if symmetry is not None else False, block_size
 
     mapping = "affine"
 

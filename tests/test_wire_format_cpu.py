@@ -66,3 +66,40 @@ def test_grid_properties_follow_reference_rules():
         AffineEncoding(s, o, -100, 27).bitwidth   # pylint: disable=expression-not-assigned
     with pytest.raises(RuntimeError, match="floating point"):
         AffineEncoding(s, o, 0, 255).to(torch.int8)
+
+
+@pytest.mark.parametrize("cls_name", ["QuantizedTensor", "DequantizedTensor"])
+def test_copies_keep_class_and_encoding(cls_name):
+    """Deep copies (copy.deepcopy, pickle) are tensors of the same class with a copy of the encoding; a shallow copy
+    shares storage and the encoding object (the reference's test_tensor.py:511-564)."""
+    import copy
+    import pickle
+    from aimet_b200.v2 import qtensor
+    from aimet_b200.v2.quantizer import AffineEncoding
+    cls = getattr(qtensor, cls_name)
+    for data in (torch.randn(5, 5), torch.nn.Parameter(torch.randn(5, 5))):
+        t = data.detach().clone().requires_grad_(data.requires_grad).as_subclass(cls)
+        t.encoding = AffineEncoding(torch.tensor(0.1), torch.tensor(-10.0), 8)   # (bitwidth[, signed]) form
+        assert (t.encoding.qmin, t.encoding.qmax) == (0, 255) and not t.encoding.signed
+        for deep in (copy.deepcopy, lambda v: pickle.loads(pickle.dumps(v))):
+            c = deep(t)
+            assert type(c) is cls and torch.equal(c, t) and c.data_ptr() != t.data_ptr()
+            assert c.requires_grad == t.requires_grad and c.dtype == t.dtype and c.stride() == t.stride()
+            assert c.encoding is not t.encoding and torch.equal(c.encoding.scale, t.encoding.scale)
+            assert c.encoding.bitwidth == t.encoding.bitwidth and c.encoding.signed == t.encoding.signed
+        c = copy.copy(t)
+        assert type(c) is cls and c.data_ptr() == t.data_ptr() and c.encoding is t.encoding
+
+
+def test_encoding_constructor_forms():
+    from aimet_b200.v2.quantizer import AffineEncoding
+    s, o = torch.tensor(0.5), torch.tensor(0.0)
+    assert (AffineEncoding(s, o, 4, True).qmin, AffineEncoding(s, o, 4, True).qmax) == (-8, 7)
+    assert (AffineEncoding(s, o, -100, 27).qmin, AffineEncoding(s, o, -100, 27).qmax) == (-100, 27)
+    e = AffineEncoding(s, o, bitwidth=8, signed=False, symmetry=True, block_size=(1, 4))
+    assert (e.qmin, e.qmax, e.symmetry, e.block_size) == (0, 255, True, (1, 4))
+    with pytest.raises(ValueError):
+        AffineEncoding(s, o, 5, 5)
+    with pytest.raises(TypeError):
+        AffineEncoding(s, o, 0, 255, nonsense=1)
+
