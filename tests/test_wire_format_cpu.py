@@ -78,7 +78,7 @@ def test_copies_keep_class_and_encoding(cls_name):
     from aimet_b200.v2.quantizer import AffineEncoding
     cls = getattr(qtensor, cls_name)
     for data in (torch.randn(5, 5), torch.nn.Parameter(torch.randn(5, 5))):
-        t = data.detach().clone().requires_grad_(data.requires_grad).as_subclass(cls)
+        t = data.detach().clone().as_subclass(cls)
         t.encoding = AffineEncoding(torch.tensor(0.1), torch.tensor(-10.0), 8)   # (bitwidth[, signed]) form
         assert (t.encoding.qmin, t.encoding.qmax) == (0, 255) and not t.encoding.signed
         for deep in (copy.deepcopy, lambda v: pickle.loads(pickle.dumps(v))):
