@@ -220,6 +220,66 @@ def gpu_numa_setup(local: int):
         return {"gpu_numa_node": None, "affinity": f"unchanged ({type(e).__name__})"}
 
 
+def _cpu_sets_by_node():
+    """CPU ids of every host NUMA node that sysfs lists (empty when it lists none)."""
+    sets = []
+    base = "/sys/devices/system/node"
+    try:
+        for name in sorted(os.listdir(base)):
+            if name.startswith("node") and name[4:].isdigit():
+                cpus = set()
+                for part in open(f"{base}/{name}/cpulist").read().strip().split(","):
+                    if part:
+                        lo, _, hi = part.partition("-")
+                        cpus.update(range(int(lo), int(hi or lo) + 1))
+                sets.append((name, cpus))
+    except OSError:
+        pass
+    return sets
+
+
+def pick_host_node_by_measurement(torch, device, info):
+    """When sysfs does not say which NUMA node a GPU hangs off (containers often hide it), find out by measurement:
+    pin this process to the CPUs of each host node in turn, allocate a pinned buffer there (pinned pages are placed on
+    the node of the allocating thread) and time host-to-device copies from it; stay on the fastest node, so that the
+    staging ring allocated afterwards is local to the GPU.  Before any timed region; changes only this process's CPU
+    affinity."""
+    if info.get("gpu_numa_node") not in (-1, None):
+        return info
+    try:
+        allowed = os.sched_getaffinity(0)
+        nodes = [(n, c & allowed) for n, c in _cpu_sets_by_node()]
+        nodes = [(n, c) for n, c in nodes if c]
+        if len(nodes) < 2:
+            return dict(info, affinity=f"unchanged ({len(nodes)} host NUMA node(s) visible)")
+        rates = {}
+        dst = torch.empty(64 << 20, dtype=torch.uint8, device=device)
+        for name, cpus in nodes:
+            os.sched_setaffinity(0, cpus)
+            src = torch.empty(64 << 20, dtype=torch.uint8).pin_memory()
+            src.fill_(1)
+            dst.copy_(src, non_blocking=True)
+            torch.cuda.synchronize(device)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(8):
+                dst.copy_(src, non_blocking=True)
+            b.record()
+            torch.cuda.synchronize(device)
+            rates[name] = 8 * src.numel() / (a.elapsed_time(b) * 1e-3) / 1e9
+            del src
+        best = max(rates, key=rates.get)
+        os.sched_setaffinity(0, dict(nodes)[best])
+        return dict(info, affinity=f"CPUs of {best}, chosen by measured H2D rate",
+                    probed_h2d_GBps={k: round(v, 1) for k, v in rates.items()})
+    except Exception as e:   # affinity calls not permitted, no sysfs ...: leave everything as it is
+        try:
+            os.sched_setaffinity(0, allowed)
+        except Exception:
+            pass
+        return dict(info, affinity=f"unchanged ({type(e).__name__})")
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -232,6 +292,7 @@ def run_b200(args):
     numa = gpu_numa_setup(local)
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    numa = pick_host_node_by_measurement(torch, device, numa)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
