@@ -18,6 +18,12 @@ result is bit-identical to the sequential reference run:
   bit.)  All ranks hold identical rows and run identical arithmetic, so every rank ends with the same encoding and
   nothing is broadcast.
 
+* SQNR on the aimet_torch v2 histograms (``SqnrCalibrator``): the observer's merge is sequential -- a batch is counted
+  over the range that it and all earlier batches cover, and old counts are re-binned with rounding when that range grows
+  (aimet_torch/v2/quantization/encoding_analyzer.py:212-262).  Two passes over each rank's batches and two all-reduces:
+  finite (min, max) per batch -> every batch's counting range (a scan in global batch order, on every rank) -> integer
+  counts per batch -> the merges replayed in global batch order on every rank.
+
 The arithmetic lives behind a small engine interface so that the exchange protocol can be tested on CPU ranks
 (gloo) with a stand-in engine; the product engine is ``CudaTfeEngine`` and runs everything on the device.
 """
@@ -240,3 +246,93 @@ class MinMaxCalibrator:
             dist.all_reduce(mn, op=dist.ReduceOp.MIN, group=self.group)
             dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=self.group)
         return TfEncoding._from_c(self._ops.minmax_encoding(bw, float(mn), float(mx), symmetric, strict, unsigned_sym))
+
+
+class SqnrCalibrator:
+    """SQNR calibration of one quantizer on the aimet_torch v2 histogram statistics, sharded by batch over the ranks of
+    ``group``; the statistics (and so the encodings) are those of one process feeding all batches in global order to
+    ``SqnrEncodingAnalyzer.update_stats``.
+
+    ``analyzer``: an ``aimet_b200.v2.encoding_analyzer.SqnrEncodingAnalyzer`` (any analyzer whose ``observer`` offers
+    ``batch_range`` / ``plan_batches`` / ``count_batch`` / ``replay_batches``).  ``calibrate(batches)`` takes this
+    rank's batches -- entry ``k`` is global batch ``k * world_size + rank``, ``None`` where the rank has none -- as a
+    sequence or as a callable that returns a fresh iterator (the batches are read twice).  Every rank passes the same
+    number of entries.
+    """
+
+    def __init__(self, analyzer, device, group=None):
+        self.analyzer = analyzer
+        self.device = torch.device(device)
+        self.group = group
+        self.distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.rank = dist.get_rank(group) if self.distributed else 0
+        self.world = dist.get_world_size(group) if self.distributed else 1
+        self._ranges = None
+        self._dtype = torch.float32
+        self._rounds = 0
+
+    def _exchange(self, table: torch.Tensor) -> None:
+        # every row is non-zero on exactly one rank: the integer sum hands every rank every row, bit for bit
+        if self.distributed:
+            dist.all_reduce(table, op=dist.ReduceOp.SUM, group=self.group)
+
+    @staticmethod
+    def _walker(batches):
+        return batches if callable(batches) else (lambda: iter(batches))
+
+    # The three local steps; calibrate() runs them with an exchange after the first two.
+    def local_ranges(self, batches) -> torch.Tensor:
+        """First pass: int32 ``[rounds * world, histograms, 4]`` with this rank's rows filled, the others zero."""
+        obs = self.analyzer.observer
+        records: List[torch.Tensor] = []
+        for x in self._walker(batches)():
+            rec = torch.zeros((obs.num_histograms, 4), dtype=torch.int32, device=self.device)
+            if x is not None:
+                obs.batch_range(x, rec)
+                self._dtype = x.dtype
+            records.append(rec)
+        self._rounds = len(records)
+        if not records:
+            raise ValueError("aimet_b200: no batches to calibrate with")
+        ranges = torch.zeros((self._rounds * self.world, obs.num_histograms, 4), dtype=torch.int32, device=self.device)
+        ranges[self.rank::self.world] = torch.stack(records)
+        return ranges
+
+    def local_counts(self, batches, ranges: torch.Tensor):
+        """Second pass, from every rank's range records: the plans of all batches and int32 ``[rounds * world,
+        histograms, bins + 2]`` counts with this rank's rows filled."""
+        obs = self.analyzer.observer
+        plans = obs.plan_batches(ranges)
+        counts = torch.zeros((ranges.shape[0], obs.num_histograms, obs.num_bins + 2), dtype=torch.int32,
+                             device=self.device)
+        seen = 0
+        for k, x in enumerate(self._walker(batches)()):
+            seen += 1
+            if x is not None:
+                g = k * self.world + self.rank
+                obs.count_batch(x, plans[g], counts[g])
+        if seen != self._rounds:
+            raise RuntimeError("aimet_b200: the batches changed between the two passes")
+        return plans, counts
+
+    def finish(self, ranges: torch.Tensor, plans: torch.Tensor, counts: torch.Tensor) -> None:
+        self.analyzer.observer.replay_batches(counts, plans, self._dtype)
+        self._ranges = ranges
+
+    def calibrate(self, batches) -> None:
+        ranges = self.local_ranges(batches)
+        self._exchange(ranges)
+        plans, counts = self.local_counts(batches, ranges)
+        self._exchange(counts)
+        self.finish(ranges, plans, counts)
+
+    def compute_encodings(self, num_steps: int, is_symmetric: bool):
+        """(min, max) like ``SqnrEncodingAnalyzer.compute_encodings``; identical on every rank."""
+        if self._ranges is None:
+            raise RuntimeError("aimet_b200: calibrate() has not run")
+        present, finite = self._ranges[..., 3] != 0, self._ranges[..., 2] != 0
+        if bool((present & ~finite).any()):
+            raise ValueError("Input tensor cannot contain only infinite or only NaN values")
+        if not bool((present & finite).any()):
+            raise ValueError("aimet_b200: no batch was offered on any rank")
+        return self.analyzer.compute_encodings(num_steps, is_symmetric)

@@ -573,6 +573,41 @@ int aq_v2hist_update_rows(const void* d_x, int dtype, int64_t n_per_row, int row
                               d_scratch, d_updates, (cudaStream_t) stream);
 }
 
+int aq_v2hist_range_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int32_t* d_range, void* d_scratch,
+                         void* stream)
+{
+    if (!d_x || !d_range || !d_scratch || n_per_row < 1 || rows < 1 ||
+        (dtype != AQ_F32 && dtype != AQ_F16 && dtype != AQ_BF16))
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_range_rows(d_x, dtype, n_per_row, rows, d_range, d_scratch, (cudaStream_t) stream);
+}
+
+int aq_v2hist_plan_batches(const int32_t* d_ranges, int n_batches, int rows, int bins, float* d_plans, void* stream)
+{
+    if (!d_ranges || !d_plans || n_batches < 1 || rows < 1 || bins < 1 || bins > AQ_V2HIST_MAX_BINS)
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_plan_batches(d_ranges, n_batches, rows, bins, d_plans, (cudaStream_t) stream);
+}
+
+int aq_v2hist_count_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, const float* d_plan,
+                         uint32_t* d_counts, void* d_scratch, void* stream)
+{
+    if (!d_x || !d_plan || !d_counts || !d_scratch || n_per_row < 1 || rows < 1 || bins < 1 ||
+        bins > AQ_V2HIST_MAX_BINS || (dtype != AQ_F32 && dtype != AQ_F16 && dtype != AQ_BF16))
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_count_rows(d_x, dtype, n_per_row, rows, bins, d_plan, d_counts, d_scratch, (cudaStream_t) stream);
+}
+
+int aq_v2hist_replay_batches(const uint32_t* d_counts, const float* d_plans, int n_batches, int rows, int bins,
+                             aq_v2hist_head_t* d_states, int64_t block_stride, float* d_updates, void* stream)
+{
+    if (!d_counts || !d_plans || !d_states || !d_updates || n_batches < 1 || bins < 1 || bins > AQ_V2HIST_MAX_BINS ||
+        bad_v2hist_rows(rows, block_stride, bins))
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_replay_batches(d_counts, d_plans, n_batches, rows, bins, d_states, block_stride, d_updates,
+                                 (cudaStream_t) stream);
+}
+
 int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,
                         int symmetric, int num_deltas, const float* d_offsets, int num_offsets, double gamma,
                         float* d_out, void* d_workspace, int64_t workspace_bytes, void* stream)

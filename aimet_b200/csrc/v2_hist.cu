@@ -345,6 +345,29 @@ __device__ __forceinline__ void v2h_write_edges(float mn, float mx, int nb, floa
 }
 
 // ---- collect_stats: the batch's own _Histogram ---------------------------------------------------------------------
+// One CTA; counts = bins, then "below the first edge", then "above the last edge".
+__device__ __forceinline__ void v2h_collect_step(const uint32_t* __restrict__ counts, float mn, float mx, bool any, int nb,
+                                                 aq_v2hist_head_t* __restrict__ out)
+{
+    float* hist = v2h_hist(out);
+    for (int i = threadIdx.x; i < nb; i += kV2HistThreads)
+    {
+        float h = (float) counts[i];
+        if (i == 0)
+            h = __fadd_rn(h, (float) counts[nb]);          // histogram[0]  += sum(x < bin_edges[0])
+        if (i == nb - 1)
+            h = __fadd_rn(h, (float) counts[nb + 1]);      // histogram[-1] += sum(x > bin_edges[-1])
+        hist[i] = h;
+    }
+    v2h_write_edges(mn, mx, nb, v2h_edges(out, nb));
+    if (threadIdx.x == 0)
+    {
+        out->min = mn, out->max = mx;
+        out->initialized = 1;
+        out->error       = any ? 0 : 1;
+    }
+}
+
 __global__ void __launch_bounds__(kV2HistThreads) v2h_finish_collect_kernel(const V2HistScratch* __restrict__ sc, int nb,
                                                                             aq_v2hist_head_t* __restrict__ out, V2HRows rw)
 {
@@ -352,23 +375,7 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_finish_collect_kernel(cons
     pdl_wait();
     sc  = v2h_row(sc, rw.sc_stride);
     out = v2h_row(out, rw.st_stride);
-    float* hist = v2h_hist(out);
-    for (int i = threadIdx.x; i < nb; i += kV2HistThreads)
-    {
-        float h = (float) sc->counts[i];
-        if (i == 0)
-            h = __fadd_rn(h, (float) sc->counts[nb]);          // histogram[0]  += sum(x < bin_edges[0])
-        if (i == nb - 1)
-            h = __fadd_rn(h, (float) sc->counts[nb + 1]);      // histogram[-1] += sum(x > bin_edges[-1])
-        hist[i] = h;
-    }
-    v2h_write_edges(sc->plan[2], sc->plan[3], nb, v2h_edges(out, nb));
-    if (threadIdx.x == 0)
-    {
-        out->min = sc->plan[2], out->max = sc->plan[3];
-        out->initialized = 1;
-        out->error       = sc->plan[4] != 0.0f ? 0 : 1;
-    }
+    v2h_collect_step(sc->counts, sc->plan[2], sc->plan[3], sc->plan[4] != 0.0f, nb, out);
 }
 
 // torch.minimum: NaN wins
@@ -391,27 +398,11 @@ __device__ __forceinline__ int v2h_bin_num(float width, float cur_min, float dat
 // ---- merge_stats: state <- state re-binned to the widened range + the batch counted at that range -----------------
 // The re-binning is two sequential scatter loops over the bins in the reference (float additions whose order matters
 // once counts pass 2^24): one thread walks them in the same order; the rest is element-wise.
-__global__ void __launch_bounds__(kV2HistThreads) v2h_merge_kernel(const V2HistScratch* __restrict__ sc, int nb,
-                                                                   aq_v2hist_head_t* __restrict__ state,
-                                                                   float* __restrict__ updates /* nb floats */, V2HRows rw,
-                                                                   int dual)
+// One CTA.  counts: the batch counted over [umin, umax] (bins, then -inf, then +inf elements).
+__device__ __forceinline__ void v2h_merge_step(const uint32_t* __restrict__ counts, float umin, float umax, bool any,
+                                               int nb, aq_v2hist_head_t* __restrict__ state, float* __restrict__ updates)
 {
-    pdl_launch_dependents();
-    pdl_wait();
-    sc      = v2h_row(sc, rw.sc_stride);
-    state   = v2h_row(state, rw.st_stride);
-    updates += (int64_t) blockIdx.y * rw.upd_stride;
     float* hist      = v2h_hist(state);
-    // after a fused pass the widened range and its counts sit in the second set
-    const uint32_t* __restrict__ counts = dual ? sc->counts2 : sc->counts;
-    const float umin = dual ? sc->plan[5] : sc->plan[0], umax = dual ? sc->plan[6] : sc->plan[1];
-    if (dual && sc->plan[4] == 0.0f)
-    {
-        // nothing finite in the batch: the reference raises; here the state is flagged and left as it is
-        if (threadIdx.x == 0)
-            state->error = 1;
-        return;
-    }
     const float cmin = state->min, cmax = state->max;
     const bool same  = (umin == cmin) && (umax == cmax);
     if (same)
@@ -470,9 +461,32 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_merge_kernel(const V2HistS
     if (threadIdx.x == 0)
     {
         state->min = umin, state->max = umax;
-        if (sc->plan[4] == 0.0f)
+        if (!any)
             state->error = 1;
     }
+}
+
+__global__ void __launch_bounds__(kV2HistThreads) v2h_merge_kernel(const V2HistScratch* __restrict__ sc, int nb,
+                                                                   aq_v2hist_head_t* __restrict__ state,
+                                                                   float* __restrict__ updates /* nb floats */, V2HRows rw,
+                                                                   int dual)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    sc      = v2h_row(sc, rw.sc_stride);
+    state   = v2h_row(state, rw.st_stride);
+    updates += (int64_t) blockIdx.y * rw.upd_stride;
+    // after a fused pass the widened range and its counts sit in the second set
+    const uint32_t* __restrict__ counts = dual ? sc->counts2 : sc->counts;
+    const float umin = dual ? sc->plan[5] : sc->plan[0], umax = dual ? sc->plan[6] : sc->plan[1];
+    if (dual && sc->plan[4] == 0.0f)
+    {
+        // nothing finite in the batch: the reference raises; here the state is flagged and left as it is
+        if (threadIdx.x == 0)
+            state->error = 1;
+        return;
+    }
+    v2h_merge_step(counts, umin, umax, sc->plan[4] != 0.0f, nb, state, updates);
 }
 
 __global__ void __launch_bounds__(kV2HistThreads) v2h_copy_kernel(const aq_v2hist_head_t* __restrict__ src, int nb,
@@ -546,6 +560,80 @@ static int v2h_passes_any(const void* x, int dtype, int64_t n, int rows, int nb,
     case AQ_F16: return v2h_passes<__half>((const __half*) x, n, rows, nb, merge, state, batch, sc, rw, st);
     case AQ_BF16:
         return v2h_passes<__nv_bfloat16>((const __nv_bfloat16*) x, n, rows, nb, merge, state, batch, sc, rw, st);
+    default: return AQ_ERR_INVALID_ARG;
+    }
+}
+
+// The two data passes on their own (sharded calibration runs them at different times).
+template <typename T>
+static void v2h_geometry(const T* x, int64_t n, int rows, int* vec, int64_t* blocks, int* nparts)
+{
+    *vec        = pick_vec<T>(x, nullptr, nullptr, rows > 1 ? n : 0);
+    int64_t b   = (n + (int64_t) kV2HistThreads * *vec * 4 - 1) / ((int64_t) kV2HistThreads * *vec * 4);
+    int64_t cap = (int64_t) kNumSMs * 6 / rows;
+    cap         = cap < 1 ? 1 : cap;
+    b           = b > cap ? cap : (b < 1 ? 1 : b);
+    *blocks     = b;
+    *nparts     = (int) (b < kV2HistMaxParts ? b : kV2HistMaxParts);
+}
+
+template <typename T>
+static int v2h_minmax_only(const T* x, int64_t n, int rows, V2HistScratch* sc, const V2HRows& rw, int* nparts,
+                           cudaStream_t st)
+{
+    int vec;
+    int64_t blocks;
+    v2h_geometry<T>(x, n, rows, &vec, &blocks, nparts);
+    const dim3 grid((unsigned) *nparts, (unsigned) rows);
+    if (vec >= 4 && sizeof(T) == 4)
+        launch_pdl(v2h_finite_minmax_kernel<T, 4>, grid, kV2HistThreads, 0, st, x, n, sc->partials, rw);
+    else if (vec >= 8)
+        launch_pdl(v2h_finite_minmax_kernel<T, (sizeof(T) == 2 ? 8 : 4)>, grid, kV2HistThreads, 0, st, x, n, sc->partials,
+                   rw);
+    else
+        launch_pdl(v2h_finite_minmax_kernel<T, 1>, grid, kV2HistThreads, 0, st, x, n, sc->partials, rw);
+    note_launch();
+    return check_launch();
+}
+
+template <typename T>
+static int v2h_count_only(const T* x, int64_t n, int rows, int nb, V2HistScratch* sc, const V2HRows& rw, cudaStream_t st)
+{
+    int vec, nparts;
+    int64_t blocks;
+    v2h_geometry<T>(x, n, rows, &vec, &blocks, &nparts);
+    const dim3 grid((unsigned) blocks, (unsigned) rows);
+    const size_t smem = (size_t) (nb + 2) * sizeof(uint32_t);
+    if (vec >= 4 && sizeof(T) == 4)
+        launch_pdl(v2h_count_kernel<T, 4, false>, grid, kV2HistThreads, smem, st, x, n, sc, nb, rw);
+    else if (vec >= 8)
+        launch_pdl(v2h_count_kernel<T, (sizeof(T) == 2 ? 8 : 4), false>, grid, kV2HistThreads, smem, st, x, n, sc, nb, rw);
+    else
+        launch_pdl(v2h_count_kernel<T, 1, false>, grid, kV2HistThreads, smem, st, x, n, sc, nb, rw);
+    note_launch();
+    return check_launch();
+}
+
+static int v2h_minmax_any(const void* x, int dtype, int64_t n, int rows, V2HistScratch* sc, const V2HRows& rw, int* nparts,
+                          cudaStream_t st)
+{
+    switch (dtype)
+    {
+    case AQ_F32: return v2h_minmax_only<float>((const float*) x, n, rows, sc, rw, nparts, st);
+    case AQ_F16: return v2h_minmax_only<__half>((const __half*) x, n, rows, sc, rw, nparts, st);
+    case AQ_BF16: return v2h_minmax_only<__nv_bfloat16>((const __nv_bfloat16*) x, n, rows, sc, rw, nparts, st);
+    default: return AQ_ERR_INVALID_ARG;
+    }
+}
+
+static int v2h_count_any(const void* x, int dtype, int64_t n, int rows, int nb, V2HistScratch* sc, const V2HRows& rw,
+                         cudaStream_t st)
+{
+    switch (dtype)
+    {
+    case AQ_F32: return v2h_count_only<float>((const float*) x, n, rows, nb, sc, rw, st);
+    case AQ_F16: return v2h_count_only<__half>((const __half*) x, n, rows, nb, sc, rw, st);
+    case AQ_BF16: return v2h_count_only<__nv_bfloat16>((const __nv_bfloat16*) x, n, rows, nb, sc, rw, st);
     default: return AQ_ERR_INVALID_ARG;
     }
 }
@@ -630,6 +718,228 @@ int v2hist_merge(const void* x, int dtype, int64_t n, int nb, aq_v2hist_head_t* 
                  int state_has_stats, void* scratch, float* updates, cudaStream_t st)
 {
     return v2hist_merge_rows(x, dtype, n, 1, nb, state, batch, 0, state_has_stats, scratch, updates, st);
+}
+
+// =================================================================================================
+// The same statistics with the batches of one calibration spread over several workers (one per GPU).
+//
+// merge_stats is sequential: batch b is counted over the range that batches 0..b cover together, and the old counts
+// are re-binned, with rounding, each time that range grows (encoding_analyzer.py:223-262).  To get the sequential
+// result bit for bit from workers that each hold a share of the batches:
+//   1. every worker takes the finite min / max of each of its batches (one pass)        -> aq_v2hist_range_rows
+//      and the workers exchange those few words;
+//   2. every worker derives, for every batch, the range it has to be counted over        -> aq_v2hist_plan_batches
+//      (a sequential scan in batch order with Python's min / max tie rules);
+//   3. every worker counts its own batches over their ranges (second pass)              -> aq_v2hist_count_rows
+//      and the workers exchange the integer counts (bins + 2 words per batch);
+//   4. every worker replays collect_stats / merge_stats in batch order from the counts  -> aq_v2hist_replay_batches
+//      -- the float additions and the re-binning happen in the reference's order.
+// A range record is 4 words: min and max (float bits), "has a finite value", "present".  A record of zeros is a batch
+// that does not exist (workers with fewer batches than others), so that records and counts can be exchanged by an
+// integer sum over buffers in which every worker fills only its own rows.
+// A plan is 8 floats: lo, hi (the range to count over), batch min, batch max, any_finite, first, present, pad.
+// =================================================================================================
+__global__ void __launch_bounds__(kV2HistThreads) v2h_range_kernel(const V2HistScratch* __restrict__ sc, int nparts,
+                                                                   int32_t* __restrict__ range, V2HRows rw)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    sc = v2h_row(sc, rw.sc_stride);
+    range += (int64_t) blockIdx.y * 4;
+    float mn = INFINITY, mx = -INFINITY;
+    for (int i = threadIdx.x; i < nparts; i += kV2HistThreads)
+    {
+        mn = fminf(mn, sc->partials[i].x);
+        mx = fmaxf(mx, sc->partials[i].y);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+    {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    __shared__ float s_mn[kV2HistThreads / 32], s_mx[kV2HistThreads / 32];
+    if ((threadIdx.x & 31) == 0)
+        s_mn[threadIdx.x >> 5] = mn, s_mx[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x != 0)
+        return;
+    for (int w = 1; w < kV2HistThreads / 32; ++w)
+        mn = fminf(mn, s_mn[w]), mx = fmaxf(mx, s_mx[w]);
+    const bool any = mn <= mx;
+    range[0] = __float_as_int(any ? mn : 0.0f);
+    range[1] = __float_as_int(any ? mx : 0.0f);
+    range[2] = any ? 1 : 0;
+    range[3] = 1;
+}
+
+// One thread per histogram walks the batches in order.
+__global__ void __launch_bounds__(kV2HistThreads) v2h_plan_batches_kernel(const int32_t* __restrict__ ranges, int n_batches,
+                                                                          int rows, int nb, float* __restrict__ plans)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x * kV2HistThreads + threadIdx.x;
+    if (r >= rows)
+        return;
+    bool have = false;
+    float smin = 0.0f, smax = 0.0f;
+    for (int b = 0; b < n_batches; ++b)
+    {
+        const int32_t* rg = ranges + ((int64_t) b * rows + r) * 4;
+        float* pl         = plans + ((int64_t) b * rows + r) * 8;
+        const bool present = rg[3] != 0, any = rg[2] != 0;
+        const float mn = __int_as_float(rg[0]), mx = __int_as_float(rg[1]);
+        float lo = 0.0f, hi = 1.0f;
+        bool first = false;
+        if (present && any)
+        {
+            if (!have)
+            {
+                // collect_stats: first and last edge of _create_bin_edges(min, max)
+                float a0 = mn, b0 = mx;
+                if (a0 == b0)
+                    a0 = __fsub_rn(a0, 0.5f), b0 = __fadd_rn(b0, 0.5f);
+                const float step = __fdiv_rn(__fsub_rn(b0, a0), (float) nb);
+                lo               = __fadd_rn(__fmul_rn(0.0f, step), a0);
+                hi               = __fadd_rn(__fmul_rn((float) nb, step), a0);
+                smin = mn, smax = mx;
+                have = first = true;
+            }
+            else
+            {
+                // Python min(new, cur) / max(new, cur): the second argument wins only when strictly smaller / larger
+                lo   = (smin < mn) ? smin : mn;
+                hi   = (smax > mx) ? smax : mx;
+                smin = lo, smax = hi;
+            }
+        }
+        pl[0] = lo, pl[1] = hi, pl[2] = mn, pl[3] = mx;
+        pl[4] = any ? 1.0f : 0.0f, pl[5] = first ? 1.0f : 0.0f, pl[6] = present ? 1.0f : 0.0f, pl[7] = 0.0f;
+    }
+}
+
+__global__ void __launch_bounds__(kV2HistThreads) v2h_load_plan_kernel(V2HistScratch* __restrict__ sc,
+                                                                       const float* __restrict__ plan, int nb, V2HRows rw)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    sc = v2h_row(sc, rw.sc_stride);
+    plan += (int64_t) blockIdx.y * 8;
+    for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
+        sc->counts[i] = 0;
+    if (threadIdx.x < 5)
+        sc->plan[threadIdx.x] = plan[threadIdx.x];
+}
+
+__global__ void __launch_bounds__(kV2HistThreads) v2h_export_counts_kernel(const V2HistScratch* __restrict__ sc, int nb,
+                                                                           uint32_t* __restrict__ counts, V2HRows rw)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    sc = v2h_row(sc, rw.sc_stride);
+    counts += (int64_t) blockIdx.y * (nb + 2);
+    for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
+        counts[i] = sc->counts[i];
+}
+
+// One CTA per histogram replays the batches in order.
+__global__ void __launch_bounds__(kV2HistThreads) v2h_replay_kernel(const uint32_t* __restrict__ counts,
+                                                                    const float* __restrict__ plans, int n_batches, int rows,
+                                                                    int nb, aq_v2hist_head_t* __restrict__ state,
+                                                                    float* __restrict__ updates, int64_t st_stride)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.y;
+    state       = v2h_row(state, st_stride);
+    updates += (int64_t) r * nb;
+    if (threadIdx.x == 0)
+        state->initialized = 0, state->error = 0;
+    __syncthreads();
+    for (int b = 0; b < n_batches; ++b)
+    {
+        const float* pl    = plans + ((int64_t) b * rows + r) * 8;
+        const uint32_t* cn = counts + ((int64_t) b * rows + r) * (nb + 2);
+        if (pl[6] == 0.0f)
+            continue;
+        if (pl[4] == 0.0f)
+        {
+            // a batch without a finite value: the reference raises ValueError when it meets it
+            if (threadIdx.x == 0)
+                state->error = 1;
+            continue;
+        }
+        if (pl[5] != 0.0f)
+        {
+            const int err = state->error;
+            __syncthreads();
+            v2h_collect_step(cn, pl[2], pl[3], true, nb, state);
+            __syncthreads();
+            if (threadIdx.x == 0 && err)
+                state->error = 1;
+        }
+        else
+            v2h_merge_step(cn, pl[0], pl[1], true, nb, state, updates);
+        __syncthreads();
+    }
+}
+
+int v2hist_range_rows(const void* x, int dtype, int64_t n, int rows, int32_t* range, void* scratch, cudaStream_t st)
+{
+    if (rows < 1 || rows > 65535)
+        return AQ_ERR_TOO_LARGE;
+    V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
+    const V2HRows rw {rows > 1 ? n : 0, rows > 1 ? v2hist_scratch_bytes() : 0, 0, 0};
+    int nparts = 0;
+    int rc     = v2h_minmax_any(x, dtype, n, rows, sc, rw, &nparts, st);
+    if (rc != AQ_OK)
+        return rc;
+    launch_pdl(v2h_range_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nparts, range,
+               rw);
+    note_launch();
+    return check_launch();
+}
+
+int v2hist_plan_batches(const int32_t* ranges, int n_batches, int rows, int nb, float* plans, cudaStream_t st)
+{
+    if (n_batches < 1 || rows < 1)
+        return AQ_ERR_INVALID_ARG;
+    launch_pdl(v2h_plan_batches_kernel, dim3((unsigned) ((rows + kV2HistThreads - 1) / kV2HistThreads)), kV2HistThreads, 0,
+               st, ranges, n_batches, rows, nb, plans);
+    note_launch();
+    return check_launch();
+}
+
+int v2hist_count_rows(const void* x, int dtype, int64_t n, int rows, int nb, const float* plan, uint32_t* counts,
+                      void* scratch, cudaStream_t st)
+{
+    if (rows < 1 || rows > 65535)
+        return AQ_ERR_TOO_LARGE;
+    V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
+    const V2HRows rw {rows > 1 ? n : 0, rows > 1 ? v2hist_scratch_bytes() : 0, 0, 0};
+    launch_pdl(v2h_load_plan_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, sc, plan, nb, rw);
+    note_launch();
+    int rc = v2h_count_any(x, dtype, n, rows, nb, sc, rw, st);
+    if (rc != AQ_OK)
+        return rc;
+    launch_pdl(v2h_export_counts_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb,
+               counts, rw);
+    note_launch();
+    return check_launch();
+}
+
+int v2hist_replay_batches(const uint32_t* counts, const float* plans, int n_batches, int rows, int nb,
+                          aq_v2hist_head_t* states, int64_t block_stride, float* updates, cudaStream_t st)
+{
+    if (rows < 1 || rows > 65535)
+        return AQ_ERR_TOO_LARGE;
+    if (n_batches < 1)
+        return AQ_ERR_INVALID_ARG;
+    launch_pdl(v2h_replay_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, counts, plans, n_batches, rows, nb,
+               states, updates, rows > 1 ? block_stride : (int64_t) 0);
+    note_launch();
+    return check_launch();
 }
 
 // =================================================================================================

@@ -468,6 +468,56 @@ class _HistogramObserver:
                                             updates.data_ptr(), stream), "aq_v2hist_update_rows")
         return self._views(blocks, input_tensor.dtype)
 
+    # ---- the same statistics from batches that are spread over several workers (aimet_b200.calibration) -------------
+    # merge_stats is sequential (the range a batch is counted over depends on every earlier batch), so the work is cut
+    # into: the batches' finite ranges -> [exchange] -> every batch's counting range -> counts -> [exchange] -> replay.
+    @torch.no_grad()
+    def batch_range(self, input_tensor: torch.Tensor, out: torch.Tensor) -> None:
+        """Writes the batch's range records (int32 ``[num_histograms, 4]``: min bits, max bits, any finite, 1)."""
+        rows = self._rows(input_tensor)
+        scratch, _ = self._buffers(input_tensor.device)
+        with ops._on(input_tensor):
+            check(lib.aq_v2hist_range_rows(rows.data_ptr(), _DT[rows.dtype], rows.shape[1], self.num_histograms,
+                                           out.data_ptr(), scratch.data_ptr(),
+                                           torch.cuda.current_stream(input_tensor.device).cuda_stream),
+                  "aq_v2hist_range_rows")
+
+    @torch.no_grad()
+    def plan_batches(self, ranges: torch.Tensor) -> torch.Tensor:
+        """``ranges``: int32 ``[n_batches, num_histograms, 4]`` in batch order -> float32 ``[n_batches, num_histograms,
+        8]``: the range every batch is counted over."""
+        plans = torch.empty(ranges.shape[:2] + (8,), dtype=torch.float32, device=ranges.device)
+        with ops._on(ranges):
+            check(lib.aq_v2hist_plan_batches(ranges.data_ptr(), ranges.shape[0], self.num_histograms, self.num_bins,
+                                             plans.data_ptr(), torch.cuda.current_stream(ranges.device).cuda_stream),
+                  "aq_v2hist_plan_batches")
+        return plans
+
+    @torch.no_grad()
+    def count_batch(self, input_tensor: torch.Tensor, plan: torch.Tensor, out: torch.Tensor) -> None:
+        """Counts the batch over ``plan`` (one batch's rows of ``plan_batches``) into ``out``, int32
+        ``[num_histograms, num_bins + 2]``."""
+        rows = self._rows(input_tensor)
+        scratch, _ = self._buffers(input_tensor.device)
+        with ops._on(input_tensor):
+            check(lib.aq_v2hist_count_rows(rows.data_ptr(), _DT[rows.dtype], rows.shape[1], self.num_histograms,
+                                           self.num_bins, plan.data_ptr(), out.data_ptr(), scratch.data_ptr(),
+                                           torch.cuda.current_stream(input_tensor.device).cuda_stream),
+                  "aq_v2hist_count_rows")
+
+    @torch.no_grad()
+    def replay_batches(self, counts: torch.Tensor, plans: torch.Tensor, dtype: torch.dtype = torch.float32) -> None:
+        """Replaces the statistics by those of feeding the counted batches one by one."""
+        device = counts.device
+        _, updates = self._buffers(device)
+        self._state = _new_blocks(self.num_histograms, self.num_bins, device)
+        self._dtype = dtype
+        with ops._on(counts):
+            check(lib.aq_v2hist_replay_batches(counts.data_ptr(), plans.data_ptr(), counts.shape[0], self.num_histograms,
+                                               self.num_bins, self._state.data_ptr(), self._state.stride(0) * 4,
+                                               updates.data_ptr(), torch.cuda.current_stream(device).cuda_stream),
+                  "aq_v2hist_replay_batches")
+
     def reset_stats(self):
         self._state = None
 

@@ -455,6 +455,26 @@ int aq_v2hist_merge_rows(const void* d_x, int dtype, int64_t n_per_row, int rows
 int aq_v2hist_update_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, aq_v2hist_head_t* d_states,
                           aq_v2hist_head_t* d_batches, int64_t block_stride, int state_has_stats, void* d_scratch,
                           float* d_updates, void* stream);
+/* The same statistics when the batches of one calibration are spread over several workers (one per GPU) and the result
+ * must be the sequential one, bit for bit.  merge_stats is sequential (encoding_analyzer.py:212-262): batch b is counted
+ * over the range that batches 0..b cover together and the old counts are re-binned, with rounding, each time the range
+ * grows.  So: (1) aq_v2hist_range_rows -- finite min / max of one batch (one pass), 4 words per histogram: min bits, max
+ * bits, "has a finite value", 1; the workers exchange the records of all batches (a record of zeros = no such batch, so
+ * an integer sum over buffers in which every worker fills only its own rows is a valid exchange); (2)
+ * aq_v2hist_plan_batches -- from all n_batches x rows records, in batch order, the range every batch is counted over
+ * (8 floats per batch and histogram: lo, hi, batch min, batch max, any_finite, first, present, 0); (3)
+ * aq_v2hist_count_rows -- one batch counted over its plan's range (second pass): bins + 2 integer words per histogram
+ * (bins, below / -inf, above / +inf); the workers exchange the counts the same way; (4) aq_v2hist_replay_batches --
+ * collect_stats of the first batch and merge_stats of every later one from the counts, in batch order, one launch.
+ * d_states receives what _HistogramObserver.stats holds after the same batches fed one by one; a batch without a finite
+ * value sets `error` (the reference raises ValueError for it).  d_updates: rows x bins floats of scratch. */
+int aq_v2hist_range_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int32_t* d_range, void* d_scratch,
+                         void* stream);
+int aq_v2hist_plan_batches(const int32_t* d_ranges, int n_batches, int rows, int bins, float* d_plans, void* stream);
+int aq_v2hist_count_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, const float* d_plan,
+                         uint32_t* d_counts, void* d_scratch, void* stream);
+int aq_v2hist_replay_batches(const uint32_t* d_counts, const float* d_plans, int n_batches, int rows, int bins,
+                             aq_v2hist_head_t* d_states, int64_t block_stride, float* d_updates, void* stream);
 int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,
                         int symmetric, int num_deltas, const float* d_offsets, int num_offsets, double gamma,
                         float* d_out, void* d_workspace, int64_t workspace_bytes, void* stream);

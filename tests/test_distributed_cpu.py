@@ -188,3 +188,79 @@ def test_single_process_protocol_matches_sequential():
                 cal.update(torch.from_numpy(b))
         e = cal.compute_encoding(8)
         assert [e.min, e.max, e.delta, e.offset, e.bw] == list(w), feed
+
+
+# ---- SQNR on the v2 histograms: two passes, two all-reduces --------------------------------------------------------
+class OracleHistogramObserver:
+    """Stand-in for the four sharded-calibration steps of _HistogramObserver on CPU tensors (one histogram), built on
+    the CPU oracle; ``state`` holds the replayed statistics."""
+
+    num_histograms = 1
+
+    def __init__(self, num_bins):
+        self.num_bins = num_bins
+        self.state = None
+
+    def batch_range(self, x, out):
+        from oracle import v2_hist_oracle as vh
+        out[0] = torch.from_numpy(vh.range_record(x.numpy()))
+
+    def plan_batches(self, ranges):
+        from oracle import v2_hist_oracle as vh
+        return torch.from_numpy(vh.plan_batches(ranges[:, 0].numpy(), self.num_bins)).unsqueeze(1).contiguous()
+
+    def count_batch(self, x, plan, out):
+        from oracle import v2_hist_oracle as vh
+        out[0] = torch.from_numpy(vh.count(x.numpy(), self.num_bins, plan[0].numpy()))
+
+    def replay_batches(self, counts, plans, dtype):
+        from oracle import v2_hist_oracle as vh
+        self.state = vh.replay(counts[:, 0].numpy(), plans[:, 0].numpy(), self.num_bins)
+
+
+class _OracleAnalyzer:
+    def __init__(self, num_bins):
+        self.observer = OracleHistogramObserver(num_bins)
+
+
+def make_v2_batches(scenario):
+    if scenario == "growing":
+        return [normal(4000 + 13 * b, 40 + b, 1.0 + 0.5 * b, 0.2 * b) for b in range(7)]
+    if scenario == "relu_inf":
+        out = [relu_activations(5000, 2000 + b) for b in range(5)]
+        out[2] = np.concatenate([out[2], np.array([np.inf, -np.inf, np.nan], np.float32)])
+        return out
+    if scenario == "shrinking":
+        return [normal(3000, 60 + b, s) for b, s in enumerate((4.0, 1.0, 0.25, 2.0))]
+    raise ValueError(scenario)
+
+
+def _v2_worker(rank, world, port, scenario, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from aimet_b200.calibration import SqnrCalibrator
+        batches = make_v2_batches(scenario)
+        rounds = (len(batches) + world - 1) // world
+        mine = [torch.from_numpy(batches[k * world + rank]) if k * world + rank < len(batches) else None
+                for k in range(rounds)]
+        cal = SqnrCalibrator(_OracleAnalyzer(128), "cpu")
+        cal.calibrate(mine)
+        st = cal.analyzer.observer.state
+        out[rank] = (st.hist.tobytes(), st.edges.tobytes(), float(st.min), float(st.max))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("scenario", ["growing", "relu_inf", "shrinking"])
+def test_sharded_v2_histograms_equal_sequential(world, scenario):
+    from oracle import v2_hist_oracle as vh
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_v2_worker, args=(world, _free_port(), scenario, out), nprocs=world, join=True)
+    want = vh.sequential(make_v2_batches(scenario), 128)[-1]
+    for rank in range(world):
+        hist, edges, mn, mx = out[rank]
+        assert hist == want.hist.tobytes() and edges == want.edges.tobytes(), (rank, scenario)
+        assert (mn, mx) == (float(want.min), float(want.max))

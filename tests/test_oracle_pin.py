@@ -340,3 +340,48 @@ def test_ref_packed_codes(oracle, reference, bw, signed):
                                             back_want.ctypes.data_as(C.POINTER(C.c_float)), mn, mx, bw, int(signed))
         assert_bits_equal(oracle.dequantize_packed(want, mn, mx, bw, signed), back_want, f"dequantize bw={bw}")
 
+
+
+# ---- v2 histogram observer: the sequential restatement and its cut into the steps of sharded calibration -----------
+SQNR_GOLD = np.load(os.path.join(GOLDEN, "v2_sqnr.npz"))
+
+
+def _sqnr_rows(name):
+    """Per histogram, the list of its batches (the encoding axes of these scenarios lead)."""
+    nh = max(1, int(np.prod(SQNR_GOLD[f"{name}/shape"])))
+    nbat = int(SQNR_GOLD[f"{name}/num_batches"])
+    return [[SQNR_GOLD[f"{name}/x{b}"].reshape(nh, -1)[h] for b in range(nbat)] for h in range(nh)]
+
+
+@pytest.mark.parametrize("name", [str(n) for n in SQNR_GOLD["names"]])
+def test_v2_histogram_oracle_matches_reference_class(name):
+    from oracle import v2_hist_oracle as vh
+    bins = int(SQNR_GOLD[f"{name}/bins"])
+    for h, batches in enumerate(_sqnr_rows(name)):
+        for b, st in enumerate(vh.sequential(batches, bins)):
+            own = vh.collect(batches[b], bins)
+            assert_bits_equal(own.hist, SQNR_GOLD[f"{name}/b{b}/batch/{h}/hist"], f"{name} batch {b} own hist")
+            assert_bits_equal(own.edges, SQNR_GOLD[f"{name}/b{b}/batch/{h}/edges"], f"{name} batch {b} own edges")
+            assert_bits_equal(st.hist, SQNR_GOLD[f"{name}/b{b}/state/{h}/hist"], f"{name} batch {b} hist")
+            assert_bits_equal(st.edges, SQNR_GOLD[f"{name}/b{b}/state/{h}/edges"], f"{name} batch {b} edges")
+            assert_bits_equal(np.array([st.min, st.max], np.float32), SQNR_GOLD[f"{name}/b{b}/state/{h}/minmax"],
+                              f"{name} batch {b} min/max")
+
+
+@pytest.mark.parametrize("name", [str(n) for n in SQNR_GOLD["names"]])
+def test_v2_histogram_oracle_steps_give_the_sequential_statistics(name):
+    """range records -> plans -> counts -> replay == feeding the batches one by one (also with absent batches)."""
+    from oracle import v2_hist_oracle as vh
+    bins = int(SQNR_GOLD[f"{name}/bins"])
+    for h, batches in enumerate(_sqnr_rows(name)):
+        padded = [batches[0], None] + list(batches[1:]) + [None]
+        ranges = np.stack([vh.range_record(x) if x is not None else np.zeros(4, np.int32) for x in padded])
+        plans = vh.plan_batches(ranges, bins)
+        counts = np.stack([vh.count(x, bins, plans[i]) if x is not None else np.zeros(bins + 2, np.int32)
+                           for i, x in enumerate(padded)])
+        st = vh.replay(counts, plans, bins)
+        last = len(batches) - 1
+        assert_bits_equal(st.hist, SQNR_GOLD[f"{name}/b{last}/state/{h}/hist"], f"{name} hist")
+        assert_bits_equal(st.edges, SQNR_GOLD[f"{name}/b{last}/state/{h}/edges"], f"{name} edges")
+        assert_bits_equal(np.array([st.min, st.max], np.float32), SQNR_GOLD[f"{name}/b{last}/state/{h}/minmax"],
+                          f"{name} min/max")
