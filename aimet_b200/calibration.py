@@ -284,6 +284,18 @@ class SqnrCalibrator:
     def local_ranges(self, batches) -> torch.Tensor:
         """First pass: int32 ``[rounds * world, histograms, 4]`` with this rank's rows filled, the others zero."""
         obs = self.analyzer.observer
+        if not callable(batches) and hasattr(batches, "__len__"):
+            # the number of rounds is known: the records go straight into their rows of the table
+            self._rounds = len(batches)
+            if self._rounds == 0:
+                raise ValueError("aimet_b200: no batches to calibrate with")
+            ranges = torch.zeros((self._rounds * self.world, obs.num_histograms, 4), dtype=torch.int32,
+                                 device=self.device)
+            for k, x in enumerate(batches):
+                if x is not None:
+                    obs.batch_range(x, ranges[k * self.world + self.rank])
+                    self._dtype = x.dtype
+            return ranges
         records: List[torch.Tensor] = []
         for x in self._walker(batches)():
             rec = torch.zeros((obs.num_histograms, 4), dtype=torch.int32, device=self.device)

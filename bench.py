@@ -372,6 +372,9 @@ def run_b200(args):
         parity = multi_gpu_parity(torch, dist, device, rank, world, batches,
                                   [("weak", weak["out"]), ("strong", strong["out"])] if strong else [("weak", weak["out"])])
 
+    # ---- the v2 flavour of the analyzer on the same batches, sharded the same way (secondary) --------------------------
+    v2 = None if args.skip_v2 else v2_sqnr_leg(torch, dist, device, rank, world, batches, barrier, max_over_ranks, e0, e1)
+
     # ---- roofline of the dominant kernel: back-to-back launches through the raw C ABI, CUDA events ---------------------
     roof = hist_roofline(torch, lib, ops, device, batches, e0, e1, sampler)
 
@@ -447,6 +450,8 @@ def run_b200(args):
         if parity is not None:
             line["parity_multi_gpu"] = parity["ok"]
             line["parity_multi_gpu_detail"] = parity
+        if v2 is not None:
+            line["v2_sqnr_sharded"] = v2
         if qdq is not None:
             line["qdq"] = qdq
         if models is not None:
@@ -494,6 +499,57 @@ def multi_gpu_parity(torch, dist, device, rank, world, batches, jobs):
     dist.broadcast(flag, 0)
     result["ok"] = bool(int(flag))
     return result
+
+
+def v2_sqnr_leg(torch, dist, device, rank, world, batches, barrier, max_over_ranks, e0, e1):
+    """The same batches through the aimet_torch v2 flavour of the analyzer (SqnrEncodingAnalyzer, 512 bins), sharded
+    like the headline job: per job two passes over the rank's resident batches, two integer all-reduces (N > 1), the
+    merges replayed in global batch order, the search, (min, max) read back.  Checked bit for bit against the
+    sequential observer fed all batches in global order by rank 0.  A secondary number, not the headline."""
+    from aimet_b200.calibration import SqnrCalibrator
+    from aimet_b200.v2.encoding_analyzer import SqnrEncodingAnalyzer
+    rounds, bins, jobs = 32, 512, 5
+    mine = batches[:rounds]
+
+    def job():
+        cal = SqnrCalibrator(SqnrEncodingAnalyzer((1,), bins), device)
+        cal.calibrate(mine)
+        mn, mx = cal.compute_encodings(255, False)
+        return cal, [float(mn), float(mx)]
+
+    for _ in range(3):
+        job()
+    barrier()
+    e0.record()
+    for _ in range(jobs):
+        cal, enc = job()
+    e1.record()
+    barrier()
+    secs = max_over_ranks(e0.elapsed_time(e1) * 1e-3)
+    # parity, outside the timed region
+    mine_enc = torch.tensor(enc, dtype=torch.float64, device=device)
+    ok = True
+    if world > 1:
+        everyone = torch.empty(world * 2, dtype=torch.float64, device=device)
+        dist.all_gather_into_tensor(everyone, mine_enc)
+        ok = bool((everyone.view(world, 2) == mine_enc).all())
+    if rank == 0:
+        seq = SqnrEncodingAnalyzer((1,), bins)
+        for g in range(rounds * world):
+            seq.update_stats(batches[g // world] if g % world == 0 else device_batch(g, device))
+        want, got = seq.observer.get_stats()[0], cal.analyzer.observer.get_stats()[0]
+        mn, mx = seq.compute_encodings(255, False)
+        ok = ok and bool(torch.equal(want.histogram.view(torch.int32), got.histogram.view(torch.int32))) \
+            and bool(torch.equal(want.bin_edges.view(torch.int32), got.bin_edges.view(torch.int32))) \
+            and [float(mn), float(mx)] == enc
+    if world > 1:
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+        dist.broadcast(flag, 0)
+        ok = bool(int(flag))
+    return {"value": world * jobs * rounds * SAMPLES_PER_BATCH / secs, "unit": "samples/s", "ms_per_job": secs / jobs * 1e3,
+            "batches_per_gpu": rounds, "bins": bins, "passes_over_data": 2, "encoding": enc,
+            "parity_with_sequential_observer": ok,
+            "algorithmic_GBps_per_gpu": jobs * rounds * 2 * BATCH_BYTES / secs / 1e9}
 
 
 def hist_roofline(torch, lib, ops, device, batches, e0, e1, sampler):
@@ -880,6 +936,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg")
     ap.add_argument("--skip-qdq", action="store_true", help="omit the secondary fake-quant kernel numbers")
+    ap.add_argument("--skip-v2", action="store_true", help="omit the sharded v2 SQNR calibration leg")
     ap.add_argument("--skip-models", action="store_true", help="omit the model-level cases (configurations 4 and 5)")
     ap.add_argument("--kernel-case", choices=KERNEL_CASES, help="time one kernel alone instead of the calibration job")
     ap.add_argument("--mb", type=int, default=256, help="input size in MB for --kernel-case")
