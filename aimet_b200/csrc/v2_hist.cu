@@ -27,6 +27,7 @@ namespace aq
 constexpr int kV2HistThreads  = 256;
 constexpr int kV2HistMaxParts = 1024;
 constexpr int kV2HistUnroll   = 4;
+constexpr int kV2HistQueue    = 1024;   // packets a CTA can put aside for the exact rule
 constexpr float kEps32        = 1.1920928955078125e-07f;   // torch.finfo(torch.float32).eps
 
 // Scratch of one collect / merge sequence (device memory, caller-owned):
@@ -221,14 +222,24 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_plan_kernel(V2HistScratch*
 
 // ---- pass 2: counts with the torch.histc bin rule, plus the elements below lo and above hi ------------------------
 // DUAL: the batch is counted over its own range AND over the widened range of the merge in the same pass.
+// The exact bin rule, out of line: it runs for about one element in a thousand.
+__device__ __noinline__ float v2h_exact_quotient_floor(float t, float w)
+{
+    return floorf(__fdiv_rn(t, w));
+}
+
 template <typename T, int VEC, bool DUAL>
 __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __restrict__ x, int64_t n,
                                                                    V2HistScratch* __restrict__ sc, int nb, V2HRows rw)
 {
     pdl_launch_dependents();
     extern __shared__ uint32_t s_cnt[];   // nb + 2 (twice with DUAL)
+    __shared__ long long s_queue[kV2HistQueue];   // packets put aside for the exact rule
+    __shared__ int s_queued;
     for (int i = threadIdx.x; i < (DUAL ? 2 : 1) * (nb + 2); i += kV2HistThreads)
         s_cnt[i] = 0;
+    if (threadIdx.x == 0)
+        s_queued = 0;   // (the barrier below comes before the first push)
     pdl_wait();
     x += (int64_t) blockIdx.y * rw.x_stride;
     sc = v2h_row(sc, rw.sc_stride);
@@ -250,37 +261,46 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
     uint32_t* s_cnt2 = s_cnt + (nb + 2);
     __syncthreads();
     // bin = min(nb - 1, floor(((f - lo) * nb) / width)) needs the correctly rounded quotient only when it lies next to an
-    // integer: the product with the rounded reciprocal differs from it by less than 2^-22 |q|, so the division is
-    // done again, exactly, only inside that band around an integer (about one element in a thousand).
+    // integer: the product with the rounded reciprocal differs from it by less than 2^-22 |q|.  The sweep bins with the
+    // reciprocal and tests a whole packet at once; a packet with an element inside that band around an integer (about
+    // one element in a thousand) is not counted but queued, and the CTA counts the queued packets with the exact rule
+    // after its sweep.  A queue that overflows (data sitting on the bin edges, e.g. values that are already quantized)
+    // makes the CTA drop what it has and count its whole share with the exact rule.
     const float rwidth = __frcp_rn(width), rwidth2 = __frcp_rn(width2);
-    auto bin_of = [&](float f, float lo_, float w_, float rw_) {
-        const float t  = __fmul_rn(__fsub_rn(f, lo_), nbf);
-        const float qf = __fmul_rn(t, rw_);
-        float fl       = floorf(qf);
-        const float d  = __fsub_rn(qf, fl), band = fmaf(qf, 2.384185791015625e-07f, 1e-30f);
-        if (!(d >= band && d <= 1.0f - band))   // also taken for NaN / Inf
-            fl = floorf(__fdiv_rn(t, w_));
-        const int b = (int) fl;
+    auto exact_bin = [&](float f, float lo_, float w_) {
+        const int b = (int) v2h_exact_quotient_floor(__fmul_rn(__fsub_rn(f, lo_), nbf), w_);
+        return b < nb - 1 ? b : nb - 1;
+    };
+    // Fast bin of one element, and in `slack` how far its quotient is from the nearest integer beyond the band (negative
+    // = unsure; NaN, from an infinite element, is ignored: such an element is never binned).  floor(qf) for 0 <= qf <
+    // 2^22 comes from two additions instead of the conversion unit: RN(qf - 0.5) + 1.5 * 2^23 rounds to floor(qf) +
+    // 1.5 * 2^23 unless qf is an integer (a tie), and integers lie inside the band.  A quotient of exactly 0 (an element
+    // equal to lo, e.g. the zeros of a post-ReLU batch) is bin 0 under either form and counts as sure.
+    constexpr float kMagic   = 12582912.0f;
+    constexpr int kMagicBits = 0x4B400000;
+    auto fast_bin = [&](float f, float lo_, float rw_, float& slack) {
+        const float qf = __fmul_rn(__fmul_rn(__fsub_rn(f, lo_), nbf), rw_);
+        const float u  = __fadd_rn(__fsub_rn(qf, 0.5f), kMagic);
+        const float d  = __fsub_rn(qf, __fsub_rn(u, kMagic));
+        const float m  = __fsub_rn(fminf(d, __fsub_rn(1.0f, d)), __fmul_rn(qf, 2.384185791015625e-07f));
+        slack          = fminf(slack, qf == 0.0f ? 1.0f : m);
+        const int b    = __float_as_int(u) - kMagicBits;
         return b < nb - 1 ? b : nb - 1;
     };
     // An element inside [lo, hi] is never beyond the edges the end bins are judged by (the two pairs differ only when
     // the bounds are equal, and then every finite element equals them), so the tests are exclusive.
+    auto put = [&](uint32_t* cnt, float f, int b, uint32_t k, float lo_, float hi_, float clo, float chi) {
+        if (f >= lo_ && f <= hi_)
+            atomicAdd(&cnt[b], k);
+        else if (f < clo)
+            atomicAdd(&cnt[nb], k);
+        else if (f > chi)
+            atomicAdd(&cnt[nb + 1], k);
+    };
     auto take_n = [&](float f, uint32_t k) {
-        if (f >= lo && f <= hi)
-            atomicAdd(&s_cnt[bin_of(f, lo, width, rwidth)], k);
-        else if (f < cmp_lo)
-            atomicAdd(&s_cnt[nb], k);
-        else if (f > cmp_hi)
-            atomicAdd(&s_cnt[nb + 1], k);
+        put(s_cnt, f, exact_bin(f, lo, width), k, lo, hi, cmp_lo, cmp_hi);
         if (DUAL)
-        {
-            if (f >= lo2 && f <= hi2)
-                atomicAdd(&s_cnt2[bin_of(f, lo2, width2, rwidth2)], k);
-            else if (f < cmp_lo2)
-                atomicAdd(&s_cnt2[nb], k);
-            else if (f > cmp_hi2)
-                atomicAdd(&s_cnt2[nb + 1], k);
-        }
+            put(s_cnt2, f, exact_bin(f, lo2, width2), k, lo2, hi2, cmp_lo2, cmp_hi2);
     };
     // Exact zeros (half of a post-ReLU activation) would all land on one counter: they are tallied in a register and
     // added once per thread at the end.
@@ -290,6 +310,38 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
             ++zeros;
         else
             take_n(f, 1u);
+    };
+    auto take_packet = [&](const Pack<T, VEC>& v, int64_t p) {
+        float f[VEC];
+        int b[VEC], b2[VEC];
+        float slack = 1.0f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+        {
+            f[e] = to_f32<T>(v.v[e]);
+            b[e] = fast_bin(f[e], lo, rwidth, slack);
+            if (DUAL)
+                b2[e] = fast_bin(f[e], lo2, rwidth2, slack);
+        }
+        if (!(slack >= 0.0f))
+        {
+            const int slot = atomicAdd(&s_queued, 1);
+            if ((unsigned) slot < (unsigned) kV2HistQueue)
+                s_queue[slot] = p;
+            return;
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+        {
+            if (f[e] == 0.0f)
+                ++zeros;
+            else
+            {
+                put(s_cnt, f[e], b[e], 1u, lo, hi, cmp_lo, cmp_hi);
+                if (DUAL)
+                    put(s_cnt2, f[e], b2[e], 1u, lo2, hi2, cmp_lo2, cmp_hi2);
+            }
+        }
     };
     const int64_t npack  = n / VEC;
     const int64_t stride = (int64_t) gridDim.x * kV2HistThreads;
@@ -302,9 +354,7 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
             v[u] = load_pack<T, VEC>(x + (p + u * stride) * VEC);
 #pragma unroll
         for (int u = 0; u < kV2HistUnroll; ++u)
-#pragma unroll
-            for (int e = 0; e < VEC; ++e)
-                take(to_f32<T>(v[u].v[e]));
+            take_packet(v[u], p + u * stride);
     }
     {
         Pack<T, VEC> v[kV2HistUnroll - 1];
@@ -315,12 +365,39 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
 #pragma unroll
         for (int u = 0; u < kV2HistUnroll - 1; ++u)
             if (p + u * stride < npack)
-#pragma unroll
-                for (int e = 0; e < VEC; ++e)
-                    take(to_f32<T>(v[u].v[e]));
+                take_packet(v[u], p + u * stride);
     }
     if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * VEC))
         take(to_f32<T>(x[npack * VEC + threadIdx.x]));
+    __syncthreads();
+    const int queued = s_queued;
+    if (queued <= kV2HistQueue)
+    {
+        for (int i = threadIdx.x; i < queued; i += kV2HistThreads)
+        {
+            const Pack<T, VEC> v = load_pack<T, VEC>(x + s_queue[i] * VEC);
+#pragma unroll 1
+            for (int e = 0; e < VEC; ++e)
+                take(to_f32<T>(v.v[e]));
+        }
+    }
+    else
+    {
+        // start over, exactly (block-uniform)
+        for (int i = threadIdx.x; i < (DUAL ? 2 : 1) * (nb + 2); i += kV2HistThreads)
+            s_cnt[i] = 0;
+        zeros = 0;
+        __syncthreads();
+        for (int64_t q = (int64_t) blockIdx.x * kV2HistThreads + threadIdx.x; q < npack; q += stride)
+        {
+            const Pack<T, VEC> v = load_pack<T, VEC>(x + q * VEC);
+#pragma unroll 1
+            for (int e = 0; e < VEC; ++e)
+                take(to_f32<T>(v.v[e]));
+        }
+        if (blockIdx.x == 0 && threadIdx.x < (int) (n - npack * VEC))
+            take(to_f32<T>(x[npack * VEC + threadIdx.x]));
+    }
     if (zeros)
         take_n(0.0f, zeros);
     __syncthreads();
@@ -505,6 +582,27 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_copy_kernel(const aq_v2his
 }
 
 // ---- launchers ------------------------------------------------------------------------------------------------------
+// Grid of the counting kernel: CTAs walk their share with a grid stride, so the grid is one resident wave over all rows
+// -- as many CTAs per SM as the instantiation's registers and this launch's shared memory allow.
+template <typename T, int V, bool DUAL>
+static int64_t v2h_count_grid(int64_t n, int rows, size_t smem)
+{
+    static int per_sm        = 0;
+    static size_t per_sm_for = 0;
+    if (per_sm == 0 || per_sm_for != smem)
+    {
+        int v = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, v2h_count_kernel<T, V, DUAL>, kV2HistThreads, smem) !=
+                cudaSuccess || v < 1)
+            v = 4;
+        per_sm = v, per_sm_for = smem;
+    }
+    int64_t blocks = (n + (int64_t) kV2HistThreads * V * 4 - 1) / ((int64_t) kV2HistThreads * V * 4);
+    int64_t cap    = (int64_t) kNumSMs * per_sm / rows;
+    cap            = cap < 1 ? 1 : cap;
+    return blocks > cap ? cap : (blocks < 1 ? 1 : blocks);
+}
+
 // rows histograms of n elements each (row r starts at x + r * n), one grid row per histogram.
 template <typename T>
 static int v2h_passes(const T* x, int64_t n, int rows, int nb, int merge, const aq_v2hist_head_t* state,
@@ -528,11 +626,11 @@ static int v2h_passes(const T* x, int64_t n, int rows, int nb, int merge, const 
     launch_pdl(v2h_plan_kernel, dim3(1, ry), kV2HistThreads, 0, st, sc, nparts, nb, merge, state, batch, rw);        \
     note_launch();                                                                                                   \
     if (merge == 2)                                                                                                  \
-        launch_pdl(v2h_count_kernel<T, V, true>, dim3((unsigned) blocks, ry), kV2HistThreads, 2 * smem, st, x, n, sc, \
-                   nb, rw);                                                                                          \
+        launch_pdl(v2h_count_kernel<T, V, true>, dim3((unsigned) v2h_count_grid<T, V, true>(n, rows, 2 * smem), ry), \
+                   kV2HistThreads, 2 * smem, st, x, n, sc, nb, rw);                                                  \
     else                                                                                                             \
-        launch_pdl(v2h_count_kernel<T, V, false>, dim3((unsigned) blocks, ry), kV2HistThreads, smem, st, x, n, sc,   \
-                   nb, rw);                                                                                          \
+        launch_pdl(v2h_count_kernel<T, V, false>, dim3((unsigned) v2h_count_grid<T, V, false>(n, rows, smem), ry),   \
+                   kV2HistThreads, smem, st, x, n, sc, nb, rw);                                                      \
     note_launch();
     if (vec >= 4 && sizeof(T) == 4)
     {
@@ -602,14 +700,18 @@ static int v2h_count_only(const T* x, int64_t n, int rows, int nb, V2HistScratch
     int vec, nparts;
     int64_t blocks;
     v2h_geometry<T>(x, n, rows, &vec, &blocks, &nparts);
-    const dim3 grid((unsigned) blocks, (unsigned) rows);
     const size_t smem = (size_t) (nb + 2) * sizeof(uint32_t);
+    const unsigned ry = (unsigned) rows;
+    constexpr int kWide = sizeof(T) == 2 ? 8 : 4;
     if (vec >= 4 && sizeof(T) == 4)
-        launch_pdl(v2h_count_kernel<T, 4, false>, grid, kV2HistThreads, smem, st, x, n, sc, nb, rw);
+        launch_pdl(v2h_count_kernel<T, 4, false>, dim3((unsigned) v2h_count_grid<T, 4, false>(n, rows, smem), ry),
+                   kV2HistThreads, smem, st, x, n, sc, nb, rw);
     else if (vec >= 8)
-        launch_pdl(v2h_count_kernel<T, (sizeof(T) == 2 ? 8 : 4), false>, grid, kV2HistThreads, smem, st, x, n, sc, nb, rw);
+        launch_pdl(v2h_count_kernel<T, kWide, false>, dim3((unsigned) v2h_count_grid<T, kWide, false>(n, rows, smem), ry),
+                   kV2HistThreads, smem, st, x, n, sc, nb, rw);
     else
-        launch_pdl(v2h_count_kernel<T, 1, false>, grid, kV2HistThreads, smem, st, x, n, sc, nb, rw);
+        launch_pdl(v2h_count_kernel<T, 1, false>, dim3((unsigned) v2h_count_grid<T, 1, false>(n, rows, smem), ry),
+                   kV2HistThreads, smem, st, x, n, sc, nb, rw);
     note_launch();
     return check_launch();
 }

@@ -137,3 +137,33 @@ def test_fused_calibration_step_matches_separate_calls(cuda, dtype, shape, steps
     np.testing.assert_array_equal(got[0].float().cpu().numpy(), want[0].float().cpu().numpy())
     np.testing.assert_array_equal(got[1].float().cpu().numpy(), want[1].float().cpu().numpy())
 
+
+
+@pytest.mark.parametrize("bins", [512, 2048])
+@pytest.mark.parametrize("edge_share", [1.0, 2e-3, 0.0])
+def test_counting_pass_with_values_on_bin_edges(cuda, bins, edge_share):
+    """Values that sit exactly on bin edges take the counting kernel's exact path: a few per CTA go through its queue,
+    many make it recount its share; either way the counts are those of torch.histc (on the CPU) over the same range."""
+    from aimet_b200.v2.encoding_analyzer import _HistogramObserver
+    g = torch.Generator().manual_seed(bins)
+    n = 3_000_000
+    x = torch.rand(n, generator=g) * bins
+    on_edge = torch.rand(n, generator=g) < edge_share
+    x = torch.where(on_edge, torch.floor(x), x)
+    x[0], x[1] = 0.0, float(bins)            # the range is [0, bins]: every integer is an edge
+    x[2], x[3], x[4] = float("inf"), float("-inf"), float("nan")
+    obs = _HistogramObserver((1,), bins)
+    got = obs.collect_stats(x.to(cuda))[0]
+    want = torch.histc(x, bins=bins, min=0.0, max=float(bins))
+    want[0] += 1       # -inf
+    want[-1] += 1      # +inf
+    assert got.min.item() == 0.0 and got.max.item() == float(bins)
+    assert_bits_equal(got.histogram.cpu().numpy(), want.numpy(), "histogram")
+    # the same batch merged into statistics with a wider range (the fused update counts it over both ranges at once)
+    obs.update_stats(torch.tensor([-1.0, float(bins) + 3.0], device=cuda))
+    obs.update_stats(x.to(cuda))
+    wide = torch.histc(x, bins=bins, min=-1.0, max=float(bins) + 3.0)
+    first = torch.histc(torch.tensor([-1.0, float(bins) + 3.0]), bins=bins, min=-1.0, max=float(bins) + 3.0)
+    wide[0] += 1
+    wide[-1] += 1
+    assert_bits_equal(obs.get_stats()[0].histogram.cpu().numpy(), (wide + first).numpy(), "merged histogram")
