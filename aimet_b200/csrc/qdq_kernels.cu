@@ -189,45 +189,6 @@ __device__ __forceinline__ float clamp_keep_nan(float r, float lo, float hi)
     return q;
 }
 
-// -------------------------------------------------------------------------------------------------
-// Two fp32 lanes per instruction (sm_100 add/sub/mul.f32x2, round-to-nearest, no flush): the 16-bit kernels carry
-// twice the elements per byte and are issue-bound with one lane per instruction.
-// -------------------------------------------------------------------------------------------------
-typedef unsigned long long f32x2_t;
-__device__ __forceinline__ f32x2_t pair(float lo, float hi)
-{
-    f32x2_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpair(f32x2_t v, float& lo, float& hi)
-{
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ f32x2_t mul2(f32x2_t a, f32x2_t b)
-{
-    f32x2_t r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f32x2_t add2(f32x2_t a, f32x2_t b)
-{
-    f32x2_t r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f32x2_t sub2(f32x2_t a, f32x2_t b)
-{
-    f32x2_t r;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ f32x2_t fma2(f32x2_t a, f32x2_t b, f32x2_t c)
-{
-    f32x2_t r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
 // max(a, |b|, |c|), NaN if any operand is NaN
 __device__ __forceinline__ float max3_abs_nan(float a, float b, float c)
 {

@@ -271,19 +271,22 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
         const int b = (int) v2h_exact_quotient_floor(__fmul_rn(__fsub_rn(f, lo_), nbf), w_);
         return b < nb - 1 ? b : nb - 1;
     };
-    // Fast bin of one element, and in `slack` how far its quotient is from the nearest integer beyond the band (negative
-    // = unsure; NaN, from an infinite element, is ignored: such an element is never binned).  floor(qf) for 0 <= qf <
-    // 2^22 comes from two additions instead of the conversion unit: RN(qf - 0.5) + 1.5 * 2^23 rounds to floor(qf) +
-    // 1.5 * 2^23 unless qf is an integer (a tie), and integers lie inside the band.  A quotient of exactly 0 (an element
-    // equal to lo, e.g. the zeros of a post-ReLU batch) is bin 0 under either form and counts as sure.
+    // Fast bin of one element; `worst` collects, over a packet, |frac(qf) - 0.5| + 2^-22 qf: above 0.5 means that some
+    // quotient is within its band of an integer (unsure).  floor(qf) for 0 <= qf < 2^22 comes from two additions
+    // instead of the conversion unit: with h = qf - 0.5 (exact), RN(h + 1.5 * 2^23) - 1.5 * 2^23 is the integer nearest
+    // to h, i.e. floor(qf) unless qf is an integer (a tie), and integers are unsure anyway; h minus that integer is
+    // frac(qf) - 0.5, exactly.  A quotient of exactly 0 (an element equal to lo, e.g. the zeros of a post-ReLU batch)
+    // gives 0.5 + 0, which counts as sure: it is bin 0 under either form.  The test itself may round as it likes (a
+    // fused multiply-add): the band has half an ulp of the quotient to spare.  NaN, from an infinite element, is
+    // ignored by the maximum: such an element is never binned.
     constexpr float kMagic   = 12582912.0f;
     constexpr int kMagicBits = 0x4B400000;
-    auto fast_bin = [&](float f, float lo_, float rw_, float& slack) {
+    auto fast_bin = [&](float f, float lo_, float rw_, float& worst) {
         const float qf = __fmul_rn(__fmul_rn(__fsub_rn(f, lo_), nbf), rw_);
-        const float u  = __fadd_rn(__fsub_rn(qf, 0.5f), kMagic);
-        const float d  = __fsub_rn(qf, __fsub_rn(u, kMagic));
-        const float m  = __fsub_rn(fminf(d, __fsub_rn(1.0f, d)), __fmul_rn(qf, 2.384185791015625e-07f));
-        slack          = fminf(slack, qf == 0.0f ? 1.0f : m);
+        const float h  = __fsub_rn(qf, 0.5f);
+        const float u  = __fadd_rn(h, kMagic);
+        const float e  = __fsub_rn(h, __fsub_rn(u, kMagic));
+        worst          = fmaxf(worst, __fmaf_rn(qf, 2.384185791015625e-07f, fabsf(e)));
         const int b    = __float_as_int(u) - kMagicBits;
         return b < nb - 1 ? b : nb - 1;
     };
@@ -311,19 +314,70 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
         else
             take_n(f, 1u);
     };
+    // The same for two elements at a time (two float32 lanes per instruction); every operation rounds as in fast_bin.
+    const f32x2_t k_nb = pair(nbf, nbf), k_half = pair(0.5f, 0.5f), k_magic = pair(kMagic, kMagic);
+    const f32x2_t k_band = pair(2.384185791015625e-07f, 2.384185791015625e-07f);
+    auto fast_bin2 = [&](float f0, float f1, float lo_, float rw_, float& worst, int& b0, int& b1) {
+        const f32x2_t qf = mul2(mul2(sub2(pair(f0, f1), pair(lo_, lo_)), k_nb), pair(rw_, rw_));
+        const f32x2_t h  = sub2(qf, k_half);
+        const f32x2_t u  = add2(h, k_magic);
+        const f32x2_t fl = sub2(u, k_magic);
+        // |e| + band = max(band + e, band - e) with e = h - fl
+        float p0, p1, n0, n1, u0, u1;
+        unpair(fma2(qf, k_band, sub2(h, fl)), p0, p1);
+        unpair(fma2(qf, k_band, sub2(fl, h)), n0, n1);
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(worst) : "f"(p0), "f"(p1));
+        asm("max.f32 %0, %0, %1, %2;" : "+f"(worst) : "f"(n0), "f"(n1));
+        unpair(u, u0, u1);
+        b0 = __float_as_int(u0) - kMagicBits;
+        b1 = __float_as_int(u1) - kMagicBits;
+        b0 = b0 < nb - 1 ? b0 : nb - 1;
+        b1 = b1 < nb - 1 ? b1 : nb - 1;
+    };
+    // counter += 1 under a predicate, without a branch
+    auto count_if = [&](uint32_t* counter, bool on) {
+        const unsigned a = (unsigned) __cvta_generic_to_shared(counter);
+        asm volatile("{ .reg .pred q; setp.ne.u32 q, %1, 0; @q red.shared.add.u32 [%0], 1; }" ::"r"(a), "r"((unsigned) on)
+                     : "memory");
+    };
     auto take_packet = [&](const Pack<T, VEC>& v, int64_t p) {
         float f[VEC];
         int b[VEC], b2[VEC];
-        float slack = 1.0f;
+        float worst = 0.0f;
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
-        {
             f[e] = to_f32<T>(v.v[e]);
-            b[e] = fast_bin(f[e], lo, rwidth, slack);
+        if (VEC == 1)
+        {
+            b[0] = fast_bin(f[0], lo, rwidth, worst);
             if (DUAL)
-                b2[e] = fast_bin(f[e], lo2, rwidth2, slack);
+                b2[0] = fast_bin(f[0], lo2, rwidth2, worst);
         }
-        if (!(slack >= 0.0f))
+        else
+        {
+#pragma unroll
+            for (int e = 0; e + 1 < VEC; e += 2)
+            {
+                fast_bin2(f[e], f[e + 1], lo, rwidth, worst, b[e], b[e + 1]);
+                if (DUAL)
+                    fast_bin2(f[e], f[e + 1], lo2, rwidth2, worst, b2[e], b2[e + 1]);
+            }
+        }
+        // the packet's smallest and largest element, NaN if it holds one: a packet that is not wholly inside the
+        // range(s) -- an infinity, a NaN, the one element beyond a rounded last edge -- is left to the exact pass too,
+        // so that the sweep needs no range test per element
+        float vmin = f[0], vmax = f[0];
+#pragma unroll
+        for (int e = 1; e < VEC; e += 2)
+        {
+            const float g = f[e + 1 < VEC ? e + 1 : e];
+            asm("min.NaN.f32 %0, %0, %1, %2;" : "+f"(vmin) : "f"(f[e]), "f"(g));
+            asm("max.NaN.f32 %0, %0, %1, %2;" : "+f"(vmax) : "f"(f[e]), "f"(g));
+        }
+        bool sure = worst <= 0.5f && vmin >= lo && vmax <= hi;
+        if (DUAL)
+            sure = sure && vmin >= lo2 && vmax <= hi2;
+        if (!sure)
         {
             const int slot = atomicAdd(&s_queued, 1);
             if ((unsigned) slot < (unsigned) kV2HistQueue)
@@ -333,13 +387,22 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
         {
-            if (f[e] == 0.0f)
-                ++zeros;
+            const bool nz = f[e] != 0.0f;
+            if (DUAL)
+            {
+                // two counters per element: skipping both for a zero is worth a branch
+                if (nz)
+                {
+                    atomicAdd(&s_cnt[b[e]], 1u);
+                    atomicAdd(&s_cnt2[b2[e]], 1u);
+                }
+                else
+                    ++zeros;
+            }
             else
             {
-                put(s_cnt, f[e], b[e], 1u, lo, hi, cmp_lo, cmp_hi);
-                if (DUAL)
-                    put(s_cnt2, f[e], b2[e], 1u, lo2, hi2, cmp_lo2, cmp_hi2);
+                zeros += nz ? 0u : 1u;
+                count_if(&s_cnt[b[e]], nz);
             }
         }
     };
