@@ -343,8 +343,37 @@ class _Histogram:
         return f"_Histogram(min={self.min}, max={self.max}, bins={self._num_bins})"
 
 
+class _HistogramRows:
+    """The list of ``_Histogram`` views of a statistics tensor, one per row, made when an entry is asked for (a
+    per-channel observer has thousands of rows and most callers hand the list straight back to the analyzer)."""
+
+    def __init__(self, blocks: torch.Tensor, count: int, num_bins: int, dtype: torch.dtype):
+        self.blocks, self.count, self.num_bins, self.dtype = blocks, count, num_bins, dtype
+        self._made = {}
+
+    def __len__(self):
+        return self.count
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return [self[j] for j in range(*i.indices(self.count))]
+        if i < 0:
+            i += self.count
+        if not 0 <= i < self.count:
+            raise IndexError(i)
+        h = self._made.get(i)
+        if h is None:
+            h = self._made[i] = _Histogram.of_block(self.blocks, i, self.num_bins, self.dtype)
+        return h
+
+    def __iter__(self):
+        return (self[i] for i in range(self.count))
+
+
 def _joint_blocks(stats) -> torch.Tensor:
     """The statistics tensor whose rows the given histograms are, in order (a copy only if they are not)."""
+    if isinstance(stats, _HistogramRows) and stats.blocks.shape[0] == stats.count:
+        return stats.blocks
     blocks = stats[0]._blocks
     if blocks is not None and blocks.shape[0] == len(stats) and all(h._blocks is blocks and h._row == i
                                                                      for i, h in enumerate(stats)):
@@ -414,7 +443,7 @@ class _HistogramObserver:
         return x.permute(axes + rest).reshape(self.num_histograms, -1).contiguous()
 
     def _views(self, blocks: torch.Tensor, dtype: torch.dtype):
-        return [_Histogram.of_block(blocks, i, self.num_bins, dtype) for i in range(self.num_histograms)]
+        return _HistogramRows(blocks, self.num_histograms, self.num_bins, dtype)
 
     # ---- observer interface ----------------------------------------------------------------------------------
     @torch.no_grad()
