@@ -1271,16 +1271,16 @@ __device__ __forceinline__ double div_by_rcp(double a, double b, double y)
     return __fma_rn(__fma_rn(-b, q, a), y, q);
 }
 
-constexpr int kReplayThreads = 128;   // buckets per CTA (4 CTAs cover the 512 buckets)
+constexpr int kReplayThreads = 64;    // buckets per CTA: 8 CTAs cover the 512 buckets (2,048 rows: 77 us; with 128: 85 us)
 constexpr int kReplayChunk   = 64;    // rows per shared-memory stage
 constexpr int kReplayGroup   = 16;    // rows folded between two checks of the speculation
 constexpr int kReplaySmem    = 2 * kReplayChunk * kReplayThreads * (int) sizeof(uint32_t);
 
 // Running mean of per-batch PDFs, batch order preserved (DlQuantization/src/math_functions.cpp:278-287):
 // pdf <- (pdf * k + hist / count) / (k + 1) for every batch with a non-zero count.  The chain over k is serial per
-// bucket and a CTA has one warp per scheduler, so the kernel is built to keep that warp's instruction stream short
+// bucket and a CTA's two warps sit on schedulers of their own, so the kernel is built to keep a warp's instruction stream short
 // and free of branches:
-//  * rows arrive through a two-stage cp.async ring (64 rows x this CTA's 128 buckets per stage);
+//  * rows arrive through a two-stage cp.async ring (64 rows x this CTA's 64 buckets per stage);
 //  * per stage the CTA prepares, per row, count, RN(1/count), k, k + 1 and RN(1/(k + 1)); both divisions then use
 //    div_by_rcp (bit-identical to IEEE division).  A dropped row (count 0, or past the end of the table) is encoded
 //    as (1, 0, 1, 1, 1): its probability evaluates to 0 and the mean step to (acc * 1 + 0) / 1 = acc, so the fold
@@ -1307,14 +1307,15 @@ __global__ void __launch_bounds__(kReplayThreads) tfe_pdf_replay_kernel(const ui
     const int i = blockIdx.x * kReplayThreads + t;
     auto issue  = [&](int stage, int64_t c0) {
         const int rows = (int) ((num_batches - c0 < CH) ? (num_batches - c0) : CH);
+        constexpr int LPR = kReplayThreads / 4;     // lanes that copy one row's slice, 16 bytes per lane
 #pragma unroll 4
-        for (int pass = 0; pass < CH / 4; ++pass)   // a warp copies one row's 512-byte slice, 16 bytes per lane
+        for (int pass = 0; pass < CH / 4; ++pass)   // four rows per pass
         {
-            const int r = pass * 4 + (t >> 5);
+            const int r = pass * 4 + t / LPR;
             if (r < rows)
             {
-                const unsigned dst  = (unsigned) __cvta_generic_to_shared(&buf[stage][r][(t & 31) * 4]);
-                const uint32_t* src = hists + (c0 + r) * AQ_PDF_SIZE + blockIdx.x * kReplayThreads + (t & 31) * 4;
+                const unsigned dst  = (unsigned) __cvta_generic_to_shared(&buf[stage][r][(t % LPR) * 4]);
+                const uint32_t* src = hists + (c0 + r) * AQ_PDF_SIZE + blockIdx.x * kReplayThreads + (t % LPR) * 4;
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
             }
         }
