@@ -599,13 +599,12 @@ int aq_v2hist_count_rows(const void* d_x, int dtype, int64_t n_per_row, int rows
 }
 
 int aq_v2hist_replay_batches(const uint32_t* d_counts, const float* d_plans, int n_batches, int rows, int bins,
-                             aq_v2hist_head_t* d_states, int64_t block_stride, float* d_updates, void* stream)
+                             aq_v2hist_head_t* d_states, int64_t block_stride, void* stream)
 {
-    if (!d_counts || !d_plans || !d_states || !d_updates || n_batches < 1 || bins < 1 || bins > AQ_V2HIST_MAX_BINS ||
+    if (!d_counts || !d_plans || !d_states || n_batches < 1 || bins < 1 || bins > AQ_V2HIST_MAX_BINS ||
         bad_v2hist_rows(rows, block_stride, bins))
         return AQ_ERR_INVALID_ARG;
-    return v2hist_replay_batches(d_counts, d_plans, n_batches, rows, bins, d_states, block_stride, d_updates,
-                                 (cudaStream_t) stream);
+    return v2hist_replay_batches(d_counts, d_plans, n_batches, rows, bins, d_states, block_stride, (cudaStream_t) stream);
 }
 
 int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,

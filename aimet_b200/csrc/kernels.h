@@ -113,7 +113,7 @@ int v2hist_plan_batches(const int32_t* ranges, int n_batches, int rows, int nb, 
 int v2hist_count_rows(const void* x, int dtype, int64_t n, int rows, int nb, const float* plan, uint32_t* counts,
                       void* scratch, cudaStream_t st);
 int v2hist_replay_batches(const uint32_t* counts, const float* plans, int n_batches, int rows, int nb,
-                          aq_v2hist_head_t* states, int64_t block_stride, float* updates, cudaStream_t st);
+                          aq_v2hist_head_t* states, int64_t block_stride, cudaStream_t st);
 int v2hist_sqnr_rows(const aq_v2hist_head_t* stats, int64_t block_stride, int rows, int nb, double num_steps,
                      int symmetric, int num_deltas, const float* offsets, int num_offsets, double gamma, float* out,
                      void* ws, int64_t ws_bytes, cudaStream_t st, int out_width = 2, int stats_dtype = 0,

@@ -538,6 +538,40 @@ __device__ __forceinline__ int v2h_bin_num(float width, float cur_min, float dat
 // ---- merge_stats: state <- state re-binned to the widened range + the batch counted at that range -----------------
 // The re-binning is two sequential scatter loops over the bins in the reference (float additions whose order matters
 // once counts pass 2^24): one thread walks them in the same order; the rest is element-wise.
+// The old counts moved into the bins of the widened range (merge_stats, encoding_analyzer.py:229-249): two sequential
+// scatter loops whose float additions happen in the reference's order.  One thread; `updates` starts at zero.
+__device__ __forceinline__ void v2h_rebin_serial(const float* __restrict__ hist, float* __restrict__ updates, float cmin,
+                                                 float cmax, float umin, float umax, int nb)
+{
+    const float dest_w = __fdiv_rn(__fsub_rn(umax, umin), (float) nb);
+    const float src_w  = __fdiv_rn(__fsub_rn(cmax, cmin), (float) nb);
+    for (int i = 0; i < nb; ++i)
+    {
+        const float src_start = __fadd_rn(cmin, __fmul_rn(src_w, (float) i));
+        const int dest        = v2h_bin_num(dest_w, umin, src_start, nb);
+        const float dest_end  = __fadd_rn(umin, __fmul_rn(dest_w, (float) (dest + 1)));
+        const float split     = rintf(__fmul_rn(__fdiv_rn(__fsub_rn(dest_end, src_start), src_w), hist[i]));
+        const float upd       = torch_minimum(split, hist[i]);
+        if (dest >= 0)
+            updates[dest] = __fadd_rn(updates[dest], upd);
+    }
+    for (int i = 0; i < nb; ++i)
+    {
+        // recomputed rather than stored: the same operations give the same values
+        const float src_start = __fadd_rn(cmin, __fmul_rn(src_w, (float) i));
+        const int dest        = v2h_bin_num(dest_w, umin, src_start, nb);
+        const float dest_end  = __fadd_rn(umin, __fmul_rn(dest_w, (float) (dest + 1)));
+        const float split     = rintf(__fmul_rn(__fdiv_rn(__fsub_rn(dest_end, src_start), src_w), hist[i]));
+        const float upd       = torch_minimum(split, hist[i]);
+        if (upd < hist[i])
+        {
+            const int other = v2h_bin_num(dest_w, umin, __fadd_rn(src_start, dest_w), nb);
+            if (other >= 0)
+                updates[other] = __fadd_rn(updates[other], __fsub_rn(hist[i], upd));
+        }
+    }
+}
+
 // One CTA.  counts: the batch counted over [umin, umax] (bins, then -inf, then +inf elements).
 __device__ __forceinline__ void v2h_merge_step(const uint32_t* __restrict__ counts, float umin, float umax, bool any,
                                                int nb, aq_v2hist_head_t* __restrict__ state, float* __restrict__ updates)
@@ -557,35 +591,7 @@ __device__ __forceinline__ void v2h_merge_step(const uint32_t* __restrict__ coun
     }
     __syncthreads();
     if (!same && threadIdx.x == 0)
-    {
-        const float dest_w = __fdiv_rn(__fsub_rn(umax, umin), (float) nb);
-        const float src_w  = __fdiv_rn(__fsub_rn(cmax, cmin), (float) nb);
-        for (int i = 0; i < nb; ++i)
-        {
-            const float src_start = __fadd_rn(cmin, __fmul_rn(src_w, (float) i));
-            const int dest        = v2h_bin_num(dest_w, umin, src_start, nb);
-            const float dest_end  = __fadd_rn(umin, __fmul_rn(dest_w, (float) (dest + 1)));
-            const float split     = rintf(__fmul_rn(__fdiv_rn(__fsub_rn(dest_end, src_start), src_w), hist[i]));
-            const float upd       = torch_minimum(split, hist[i]);
-            if (dest >= 0)
-                updates[dest] = __fadd_rn(updates[dest], upd);
-        }
-        for (int i = 0; i < nb; ++i)
-        {
-            // recomputed rather than stored: the same operations give the same values
-            const float src_start = __fadd_rn(cmin, __fmul_rn(src_w, (float) i));
-            const int dest        = v2h_bin_num(dest_w, umin, src_start, nb);
-            const float dest_end  = __fadd_rn(umin, __fmul_rn(dest_w, (float) (dest + 1)));
-            const float split     = rintf(__fmul_rn(__fdiv_rn(__fsub_rn(dest_end, src_start), src_w), hist[i]));
-            const float upd       = torch_minimum(split, hist[i]);
-            if (upd < hist[i])
-            {
-                const int other = v2h_bin_num(dest_w, umin, __fadd_rn(src_start, dest_w), nb);
-                if (other >= 0)
-                    updates[other] = __fadd_rn(updates[other], __fsub_rn(hist[i], upd));
-            }
-        }
-    }
+        v2h_rebin_serial(hist, updates, cmin, cmax, umin, umax, nb);
     __syncthreads();
     for (int i = threadIdx.x; i < nb; i += kV2HistThreads)
     {
@@ -1008,20 +1014,27 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_export_counts_kernel(const
         counts[i] = sc->counts[i];
 }
 
-// One CTA per histogram replays the batches in order.
+// One CTA per histogram replays the batches in order.  The running histogram lives in registers (bin i of thread t is
+// t + 256 j) and only a change of range goes through shared memory, where one thread re-bins the old counts in the
+// reference's order; a batch inside the current range costs one coalesced read of its counts and one addition per bin,
+// with no barrier.  Bin edges are written once, at the end (they follow from min / max alone).
+constexpr int kV2HistPerThread = (AQ_V2HIST_MAX_BINS + kV2HistThreads - 1) / kV2HistThreads;
 __global__ void __launch_bounds__(kV2HistThreads) v2h_replay_kernel(const uint32_t* __restrict__ counts,
                                                                     const float* __restrict__ plans, int n_batches, int rows,
                                                                     int nb, aq_v2hist_head_t* __restrict__ state,
-                                                                    float* __restrict__ updates, int64_t st_stride)
+                                                                    int64_t st_stride)
 {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float s_hist[AQ_V2HIST_MAX_BINS], s_upd[AQ_V2HIST_MAX_BINS];
     const int r = blockIdx.y;
     state       = v2h_row(state, st_stride);
-    updates += (int64_t) r * nb;
-    if (threadIdx.x == 0)
-        state->initialized = 0, state->error = 0;
-    __syncthreads();
+    float h[kV2HistPerThread];
+#pragma unroll
+    for (int j = 0; j < kV2HistPerThread; ++j)
+        h[j] = 0.0f;
+    float smin = 0.0f, smax = 0.0f;
+    int initialized = 0, error = 0;
     for (int b = 0; b < n_batches; ++b)
     {
         const float* pl    = plans + ((int64_t) b * rows + r) * 8;
@@ -1030,23 +1043,73 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_replay_kernel(const uint32
             continue;
         if (pl[4] == 0.0f)
         {
-            // a batch without a finite value: the reference raises ValueError when it meets it
-            if (threadIdx.x == 0)
-                state->error = 1;
+            error = 1;   // a batch without a finite value: the reference raises ValueError when it meets it
             continue;
         }
-        if (pl[5] != 0.0f)
+        const bool first = pl[5] != 0.0f;
+        const float umin = first ? pl[2] : pl[0], umax = first ? pl[3] : pl[1];
+        if (first)
         {
-            const int err = state->error;
-            __syncthreads();
-            v2h_collect_step(cn, pl[2], pl[3], true, nb, state);
-            __syncthreads();
-            if (threadIdx.x == 0 && err)
-                state->error = 1;
+#pragma unroll
+            for (int j = 0; j < kV2HistPerThread; ++j)
+                h[j] = 0.0f;
+            initialized = 1;
         }
-        else
-            v2h_merge_step(cn, pl[0], pl[1], true, nb, state, updates);
-        __syncthreads();
+        else if (!(umin == smin && umax == smax))
+        {
+            // block-uniform: the range grows
+#pragma unroll
+            for (int j = 0; j < kV2HistPerThread; ++j)
+            {
+                const int i = threadIdx.x + j * kV2HistThreads;
+                if (i < nb)
+                    s_hist[i] = h[j], s_upd[i] = 0.0f;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0)
+                v2h_rebin_serial(s_hist, s_upd, smin, smax, umin, umax, nb);
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < kV2HistPerThread; ++j)
+            {
+                const int i = threadIdx.x + j * kV2HistThreads;
+                if (i < nb)
+                    h[j] = s_upd[i];
+            }
+        }
+        // collect_stats: float(counts), then the elements beyond the edges; merge_stats: float(counts) + re-binned old
+        // counts, then the infinities -- the same three additions in the same order (the first batch adds to zero)
+        const float below = (float) cn[nb], above = (float) cn[nb + 1];
+#pragma unroll
+        for (int j = 0; j < kV2HistPerThread; ++j)
+        {
+            const int i = threadIdx.x + j * kV2HistThreads;
+            if (i < nb)
+            {
+                float v = first ? (float) cn[i] : __fadd_rn((float) cn[i], h[j]);
+                if (i == 0)
+                    v = __fadd_rn(v, below);
+                if (i == nb - 1)
+                    v = __fadd_rn(v, above);
+                h[j] = v;
+            }
+        }
+        smin = umin, smax = umax;
+    }
+    float* hist = v2h_hist(state);
+#pragma unroll
+    for (int j = 0; j < kV2HistPerThread; ++j)
+    {
+        const int i = threadIdx.x + j * kV2HistThreads;
+        if (i < nb)
+            hist[i] = h[j];
+    }
+    v2h_write_edges(smin, smax, nb, v2h_edges(state, nb));
+    if (threadIdx.x == 0)
+    {
+        state->min = smin, state->max = smax;
+        state->initialized = initialized;
+        state->error       = error;
     }
 }
 
@@ -1095,14 +1158,14 @@ int v2hist_count_rows(const void* x, int dtype, int64_t n, int rows, int nb, con
 }
 
 int v2hist_replay_batches(const uint32_t* counts, const float* plans, int n_batches, int rows, int nb,
-                          aq_v2hist_head_t* states, int64_t block_stride, float* updates, cudaStream_t st)
+                          aq_v2hist_head_t* states, int64_t block_stride, cudaStream_t st)
 {
     if (rows < 1 || rows > 65535)
         return AQ_ERR_TOO_LARGE;
     if (n_batches < 1)
         return AQ_ERR_INVALID_ARG;
     launch_pdl(v2h_replay_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, counts, plans, n_batches, rows, nb,
-               states, updates, rows > 1 ? block_stride : (int64_t) 0);
+               states, rows > 1 ? block_stride : (int64_t) 0);
     note_launch();
     return check_launch();
 }

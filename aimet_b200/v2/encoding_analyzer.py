@@ -538,13 +538,12 @@ class _HistogramObserver:
     def replay_batches(self, counts: torch.Tensor, plans: torch.Tensor, dtype: torch.dtype = torch.float32) -> None:
         """Replaces the statistics by those of feeding the counted batches one by one."""
         device = counts.device
-        _, updates = self._buffers(device)
         self._state = _new_blocks(self.num_histograms, self.num_bins, device)
         self._dtype = dtype
         with ops._on(counts):
             check(lib.aq_v2hist_replay_batches(counts.data_ptr(), plans.data_ptr(), counts.shape[0], self.num_histograms,
                                                self.num_bins, self._state.data_ptr(), self._state.stride(0) * 4,
-                                               updates.data_ptr(), torch.cuda.current_stream(device).cuda_stream),
+                                               torch.cuda.current_stream(device).cuda_stream),
                   "aq_v2hist_replay_batches")
 
     def reset_stats(self):

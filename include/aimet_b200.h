@@ -467,14 +467,14 @@ int aq_v2hist_update_rows(const void* d_x, int dtype, int64_t n_per_row, int row
  * (bins, below / -inf, above / +inf); the workers exchange the counts the same way; (4) aq_v2hist_replay_batches --
  * collect_stats of the first batch and merge_stats of every later one from the counts, in batch order, one launch.
  * d_states receives what _HistogramObserver.stats holds after the same batches fed one by one; a batch without a finite
- * value sets `error` (the reference raises ValueError for it).  d_updates: rows x bins floats of scratch. */
+ * value sets `error` (the reference raises ValueError for it). */
 int aq_v2hist_range_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int32_t* d_range, void* d_scratch,
                          void* stream);
 int aq_v2hist_plan_batches(const int32_t* d_ranges, int n_batches, int rows, int bins, float* d_plans, void* stream);
 int aq_v2hist_count_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, const float* d_plan,
                          uint32_t* d_counts, void* d_scratch, void* stream);
 int aq_v2hist_replay_batches(const uint32_t* d_counts, const float* d_plans, int n_batches, int rows, int bins,
-                             aq_v2hist_head_t* d_states, int64_t block_stride, float* d_updates, void* stream);
+                             aq_v2hist_head_t* d_states, int64_t block_stride, void* stream);
 int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,
                         int symmetric, int num_deltas, const float* d_offsets, int num_offsets, double gamma,
                         float* d_out, void* d_workspace, int64_t workspace_bytes, void* stream);
