@@ -84,7 +84,9 @@ SIGNATURES = {
     "aq_v2hist_update_rows": (_i32, [_vp, _i32, _i64, _i32, _i32, _vp, _vp, _i64, _i32, _vp, _vp, _vp]),
     "aq_v2hist_range_rows": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp]),
     "aq_v2hist_plan_batches": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp]),
-    "aq_v2hist_count_rows": (_i32, [_vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "aq_v2hist_count_rows": (_i32, [_vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp]),
+    "aq_v2hist_range_many": (_i32, [_vp, _i32, _i32, _i64, _i32, _vp, _i64, _vp, _vp]),
+    "aq_v2hist_count_many": (_i32, [_vp, _i32, _i32, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _vp]),
     "aq_v2hist_replay_batches": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _i64, _vp]),
     "aq_v2hist_sqnr_rows": (_i32, [_vp, _i64, _i32, _i32, _f64, _i32, _i32, _vp, _i32, _f64, _vp, _vp, _i64, _vp]),
     "aq_v2hist_sqnr_encode_rows": (_i32, [_vp, _i64, _i32, _i32, _f64, _i32, _i32, _vp, _i32, _f64, _i32, _f64, _vp, _vp,

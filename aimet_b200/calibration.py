@@ -291,6 +291,10 @@ class SqnrCalibrator:
                 raise ValueError("aimet_b200: no batches to calibrate with")
             ranges = torch.zeros((self._rounds * self.world, obs.num_histograms, 4), dtype=torch.int32,
                                  device=self.device)
+            many = getattr(obs, "batch_range_many", None)
+            if many is not None and many(batches, ranges, self.rank, self.world):
+                self._dtype = next((x.dtype for x in batches if x is not None), self._dtype)
+                return ranges
             for k, x in enumerate(batches):
                 if x is not None:
                     obs.batch_range(x, ranges[k * self.world + self.rank])
@@ -317,6 +321,10 @@ class SqnrCalibrator:
         plans = obs.plan_batches(ranges)
         counts = torch.zeros((ranges.shape[0], obs.num_histograms, obs.num_bins + 2), dtype=torch.int32,
                              device=self.device)
+        many = getattr(obs, "count_many", None)
+        if many is not None and not callable(batches) and hasattr(batches, "__len__") and \
+                len(batches) == self._rounds and many(batches, plans, counts, self.rank, self.world):
+            return plans, counts
         seen = 0
         for k, x in enumerate(self._walker(batches)()):
             seen += 1

@@ -590,12 +590,33 @@ int aq_v2hist_plan_batches(const int32_t* d_ranges, int n_batches, int rows, int
 }
 
 int aq_v2hist_count_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, const float* d_plan,
-                         uint32_t* d_counts, void* d_scratch, void* stream)
+                         uint32_t* d_counts, void* stream)
 {
-    if (!d_x || !d_plan || !d_counts || !d_scratch || n_per_row < 1 || rows < 1 || bins < 1 ||
+    if (!d_x || !d_plan || !d_counts || n_per_row < 1 || rows < 1 || bins < 1 ||
         bins > AQ_V2HIST_MAX_BINS || (dtype != AQ_F32 && dtype != AQ_F16 && dtype != AQ_BF16))
         return AQ_ERR_INVALID_ARG;
-    return v2hist_count_rows(d_x, dtype, n_per_row, rows, bins, d_plan, d_counts, d_scratch, (cudaStream_t) stream);
+    return v2hist_count_rows(d_x, dtype, n_per_row, rows, bins, d_plan, d_counts, (cudaStream_t) stream);
+}
+
+int aq_v2hist_range_many(const void* const* d_xs, int m, int dtype, int64_t n_per_row, int rows, int32_t* d_ranges,
+                         int64_t stride_words, void* d_scratch, void* stream)
+{
+    if (!d_xs || m < 1 || !d_ranges || !d_scratch || n_per_row < 1 || rows < 1 || stride_words < 4 * (int64_t) rows ||
+        (dtype != AQ_F32 && dtype != AQ_F16 && dtype != AQ_BF16))
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_range_many(d_xs, m, dtype, n_per_row, rows, d_ranges, stride_words, d_scratch, (cudaStream_t) stream);
+}
+
+int aq_v2hist_count_many(const void* const* d_xs, int m, int dtype, int64_t n_per_row, int rows, int bins,
+                         const float* d_plans, int64_t plan_stride, uint32_t* d_counts, int64_t count_stride,
+                         void* stream)
+{
+    if (!d_xs || m < 1 || !d_plans || !d_counts || n_per_row < 1 || rows < 1 || bins < 1 ||
+        bins > AQ_V2HIST_MAX_BINS || plan_stride < 8 * (int64_t) rows || count_stride < (int64_t) rows * (bins + 2) ||
+        (dtype != AQ_F32 && dtype != AQ_F16 && dtype != AQ_BF16))
+        return AQ_ERR_INVALID_ARG;
+    return v2hist_count_many(d_xs, m, dtype, n_per_row, rows, bins, d_plans, plan_stride, d_counts, count_stride,
+                             (cudaStream_t) stream);
 }
 
 int aq_v2hist_replay_batches(const uint32_t* d_counts, const float* d_plans, int n_batches, int rows, int bins,

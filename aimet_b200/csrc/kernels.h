@@ -111,7 +111,11 @@ int v2hist_update_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq
 int v2hist_range_rows(const void* x, int dtype, int64_t n, int rows, int32_t* range, void* scratch, cudaStream_t st);
 int v2hist_plan_batches(const int32_t* ranges, int n_batches, int rows, int nb, float* plans, cudaStream_t st);
 int v2hist_count_rows(const void* x, int dtype, int64_t n, int rows, int nb, const float* plan, uint32_t* counts,
+                      cudaStream_t st);
+int v2hist_range_many(const void* const* xs, int m, int dtype, int64_t n, int rows, int32_t* ranges, int64_t stride_words,
                       void* scratch, cudaStream_t st);
+int v2hist_count_many(const void* const* xs, int m, int dtype, int64_t n, int rows, int nb, const float* plans,
+                      int64_t plan_stride, uint32_t* counts, int64_t count_stride, cudaStream_t st);
 int v2hist_replay_batches(const uint32_t* counts, const float* plans, int n_batches, int rows, int nb,
                           aq_v2hist_head_t* states, int64_t block_stride, cudaStream_t st);
 int v2hist_sqnr_rows(const aq_v2hist_head_t* stats, int64_t block_stride, int rows, int nb, double num_steps,

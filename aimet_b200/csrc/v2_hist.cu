@@ -47,6 +47,14 @@ struct V2HistScratch
 
 // Several histograms per launch (per-channel observers): blockIdx.y is the histogram; these are the distances between
 // consecutive histograms' inputs, scratch areas, statistics blocks and re-binning buffers.  All zero for one histogram.
+// Where the counting kernel reads its range and adds its counts when that is not the scratch area: one batch's rows of
+// a plan table (8 floats per histogram) and of a counts table (bins + 2 words per histogram).  Null = scratch.
+struct V2HDirect
+{
+    const float* plan;
+    uint32_t* counts;
+};
+
 struct V2HRows
 {
     int64_t x_stride;     // elements
@@ -230,7 +238,8 @@ __device__ __noinline__ float v2h_exact_quotient_floor(float t, float w)
 
 template <typename T, int VEC, bool DUAL>
 __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __restrict__ x, int64_t n,
-                                                                   V2HistScratch* __restrict__ sc, int nb, V2HRows rw)
+                                                                   V2HistScratch* __restrict__ sc, int nb, V2HRows rw,
+                                                                   V2HDirect direct)
 {
     pdl_launch_dependents();
     extern __shared__ uint32_t s_cnt[];   // nb + 2 (twice with DUAL)
@@ -243,7 +252,10 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
     pdl_wait();
     x += (int64_t) blockIdx.y * rw.x_stride;
     sc = v2h_row(sc, rw.sc_stride);
-    float lo = sc->plan[0], hi = sc->plan[1];
+    // range and counters: the scratch area's, or (sharded calibration) a row of the caller's plan and counts tables
+    const float* __restrict__ plan = direct.plan ? direct.plan + (int64_t) blockIdx.y * 8 : sc->plan;
+    uint32_t* __restrict__ out     = direct.counts ? direct.counts + (int64_t) blockIdx.y * (nb + 2) : sc->counts;
+    float lo = plan[0], hi = plan[1];
     const float cmp_lo = lo, cmp_hi = hi;
     if (lo == hi)
         lo = __fsub_rn(lo, 1.0f), hi = __fadd_rn(hi, 1.0f);   // torch.histc's own rule for equal bounds
@@ -252,7 +264,7 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
     float lo2 = 0.0f, hi2 = 0.0f, cmp_lo2 = 0.0f, cmp_hi2 = 0.0f, width2 = 1.0f;
     if (DUAL)
     {
-        lo2 = sc->plan[5], hi2 = sc->plan[6];
+        lo2 = plan[5], hi2 = plan[6];
         cmp_lo2 = lo2, cmp_hi2 = hi2;
         if (lo2 == hi2)
             lo2 = __fsub_rn(lo2, 1.0f), hi2 = __fadd_rn(hi2, 1.0f);
@@ -467,7 +479,7 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_count_kernel(const T* __re
     for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
     {
         if (s_cnt[i])
-            atomicAdd(&sc->counts[i], s_cnt[i]);
+            atomicAdd(&out[i], s_cnt[i]);
         if (DUAL && s_cnt2[i])
             atomicAdd(&sc->counts2[i], s_cnt2[i]);
     }
@@ -696,10 +708,10 @@ static int v2h_passes(const T* x, int64_t n, int rows, int nb, int merge, const 
     note_launch();                                                                                                   \
     if (merge == 2)                                                                                                  \
         launch_pdl(v2h_count_kernel<T, V, true>, dim3((unsigned) v2h_count_grid<T, V, true>(n, rows, 2 * smem), ry), \
-                   kV2HistThreads, 2 * smem, st, x, n, sc, nb, rw);                                                  \
+                   kV2HistThreads, 2 * smem, st, x, n, sc, nb, rw, V2HDirect {nullptr, nullptr});                    \
     else                                                                                                             \
         launch_pdl(v2h_count_kernel<T, V, false>, dim3((unsigned) v2h_count_grid<T, V, false>(n, rows, smem), ry),   \
-                   kV2HistThreads, smem, st, x, n, sc, nb, rw);                                                      \
+                   kV2HistThreads, smem, st, x, n, sc, nb, rw, V2HDirect {nullptr, nullptr});                        \
     note_launch();
     if (vec >= 4 && sizeof(T) == 4)
     {
@@ -764,8 +776,9 @@ static int v2h_minmax_only(const T* x, int64_t n, int rows, V2HistScratch* sc, c
 }
 
 template <typename T>
-static int v2h_count_only(const T* x, int64_t n, int rows, int nb, V2HistScratch* sc, const V2HRows& rw, cudaStream_t st)
+static int v2h_count_only(const T* x, int64_t n, int rows, int nb, const V2HRows& rw, V2HDirect direct, cudaStream_t st)
 {
+    V2HistScratch* sc = nullptr;
     int vec, nparts;
     int64_t blocks;
     v2h_geometry<T>(x, n, rows, &vec, &blocks, &nparts);
@@ -774,13 +787,13 @@ static int v2h_count_only(const T* x, int64_t n, int rows, int nb, V2HistScratch
     constexpr int kWide = sizeof(T) == 2 ? 8 : 4;
     if (vec >= 4 && sizeof(T) == 4)
         launch_pdl(v2h_count_kernel<T, 4, false>, dim3((unsigned) v2h_count_grid<T, 4, false>(n, rows, smem), ry),
-                   kV2HistThreads, smem, st, x, n, sc, nb, rw);
+                   kV2HistThreads, smem, st, x, n, sc, nb, rw, direct);
     else if (vec >= 8)
         launch_pdl(v2h_count_kernel<T, kWide, false>, dim3((unsigned) v2h_count_grid<T, kWide, false>(n, rows, smem), ry),
-                   kV2HistThreads, smem, st, x, n, sc, nb, rw);
+                   kV2HistThreads, smem, st, x, n, sc, nb, rw, direct);
     else
         launch_pdl(v2h_count_kernel<T, 1, false>, dim3((unsigned) v2h_count_grid<T, 1, false>(n, rows, smem), ry),
-                   kV2HistThreads, smem, st, x, n, sc, nb, rw);
+                   kV2HistThreads, smem, st, x, n, sc, nb, rw, direct);
     note_launch();
     return check_launch();
 }
@@ -797,14 +810,14 @@ static int v2h_minmax_any(const void* x, int dtype, int64_t n, int rows, V2HistS
     }
 }
 
-static int v2h_count_any(const void* x, int dtype, int64_t n, int rows, int nb, V2HistScratch* sc, const V2HRows& rw,
+static int v2h_count_any(const void* x, int dtype, int64_t n, int rows, int nb, const V2HRows& rw, V2HDirect direct,
                          cudaStream_t st)
 {
     switch (dtype)
     {
-    case AQ_F32: return v2h_count_only<float>((const float*) x, n, rows, nb, sc, rw, st);
-    case AQ_F16: return v2h_count_only<__half>((const __half*) x, n, rows, nb, sc, rw, st);
-    case AQ_BF16: return v2h_count_only<__nv_bfloat16>((const __nv_bfloat16*) x, n, rows, nb, sc, rw, st);
+    case AQ_F32: return v2h_count_only<float>((const float*) x, n, rows, nb, rw, direct, st);
+    case AQ_F16: return v2h_count_only<__half>((const __half*) x, n, rows, nb, rw, direct, st);
+    case AQ_BF16: return v2h_count_only<__nv_bfloat16>((const __nv_bfloat16*) x, n, rows, nb, rw, direct, st);
     default: return AQ_ERR_INVALID_ARG;
     }
 }
@@ -990,30 +1003,6 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_plan_batches_kernel(const 
     }
 }
 
-__global__ void __launch_bounds__(kV2HistThreads) v2h_load_plan_kernel(V2HistScratch* __restrict__ sc,
-                                                                       const float* __restrict__ plan, int nb, V2HRows rw)
-{
-    pdl_launch_dependents();
-    pdl_wait();
-    sc = v2h_row(sc, rw.sc_stride);
-    plan += (int64_t) blockIdx.y * 8;
-    for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
-        sc->counts[i] = 0;
-    if (threadIdx.x < 5)
-        sc->plan[threadIdx.x] = plan[threadIdx.x];
-}
-
-__global__ void __launch_bounds__(kV2HistThreads) v2h_export_counts_kernel(const V2HistScratch* __restrict__ sc, int nb,
-                                                                           uint32_t* __restrict__ counts, V2HRows rw)
-{
-    pdl_launch_dependents();
-    pdl_wait();
-    sc = v2h_row(sc, rw.sc_stride);
-    counts += (int64_t) blockIdx.y * (nb + 2);
-    for (int i = threadIdx.x; i < nb + 2; i += kV2HistThreads)
-        counts[i] = sc->counts[i];
-}
-
 // One CTA per histogram replays the batches in order.  The running histogram lives in registers (bin i of thread t is
 // t + 256 j) and only a change of range goes through shared memory, where one thread re-bins the old counts in the
 // reference's order; a batch inside the current range costs one coalesced read of its counts and one addition per bin,
@@ -1140,21 +1129,43 @@ int v2hist_plan_batches(const int32_t* ranges, int n_batches, int rows, int nb, 
 }
 
 int v2hist_count_rows(const void* x, int dtype, int64_t n, int rows, int nb, const float* plan, uint32_t* counts,
-                      void* scratch, cudaStream_t st)
+                      cudaStream_t st)
 {
     if (rows < 1 || rows > 65535)
         return AQ_ERR_TOO_LARGE;
-    V2HistScratch* sc = static_cast<V2HistScratch*>(scratch);
-    const V2HRows rw {rows > 1 ? n : 0, rows > 1 ? v2hist_scratch_bytes() : 0, 0, 0};
-    launch_pdl(v2h_load_plan_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, sc, plan, nb, rw);
-    note_launch();
-    int rc = v2h_count_any(x, dtype, n, rows, nb, sc, rw, st);
-    if (rc != AQ_OK)
-        return rc;
-    launch_pdl(v2h_export_counts_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb,
-               counts, rw);
-    note_launch();
-    return check_launch();
+    const V2HRows rw {rows > 1 ? n : 0, 0, 0, 0};
+    return v2h_count_any(x, dtype, n, rows, nb, rw, V2HDirect {plan, counts}, st);
+}
+
+// The two passes for a list of equally shaped batches (one host call per pass: the launches of consecutive batches
+// queue back to back).  Batch i writes record / counts number i * stride of the tables it is given.
+int v2hist_range_many(const void* const* xs, int m, int dtype, int64_t n, int rows, int32_t* ranges, int64_t stride_words,
+                      void* scratch, cudaStream_t st)
+{
+    for (int i = 0; i < m; ++i)
+    {
+        if (!xs[i])
+            continue;
+        const int rc = v2hist_range_rows(xs[i], dtype, n, rows, ranges + (int64_t) i * stride_words, scratch, st);
+        if (rc != AQ_OK)
+            return rc;
+    }
+    return AQ_OK;
+}
+
+int v2hist_count_many(const void* const* xs, int m, int dtype, int64_t n, int rows, int nb, const float* plans,
+                      int64_t plan_stride, uint32_t* counts, int64_t count_stride, cudaStream_t st)
+{
+    for (int i = 0; i < m; ++i)
+    {
+        if (!xs[i])
+            continue;
+        const int rc = v2hist_count_rows(xs[i], dtype, n, rows, nb, plans + (int64_t) i * plan_stride,
+                                         counts + (int64_t) i * count_stride, st);
+        if (rc != AQ_OK)
+            return rc;
+    }
+    return AQ_OK;
 }
 
 int v2hist_replay_batches(const uint32_t* counts, const float* plans, int n_batches, int rows, int nb,

@@ -524,15 +524,64 @@ class _HistogramObserver:
 
     @torch.no_grad()
     def count_batch(self, input_tensor: torch.Tensor, plan: torch.Tensor, out: torch.Tensor) -> None:
-        """Counts the batch over ``plan`` (one batch's rows of ``plan_batches``) into ``out``, int32
-        ``[num_histograms, num_bins + 2]``."""
+        """Counts the batch over ``plan`` (one batch's rows of ``plan_batches``) and adds the counts to ``out``, int32
+        ``[num_histograms, num_bins + 2]`` (zero-filled by the caller)."""
         rows = self._rows(input_tensor)
-        scratch, _ = self._buffers(input_tensor.device)
         with ops._on(input_tensor):
             check(lib.aq_v2hist_count_rows(rows.data_ptr(), _DT[rows.dtype], rows.shape[1], self.num_histograms,
-                                           self.num_bins, plan.data_ptr(), out.data_ptr(), scratch.data_ptr(),
+                                           self.num_bins, plan.data_ptr(), out.data_ptr(),
                                            torch.cuda.current_stream(input_tensor.device).cuda_stream),
                   "aq_v2hist_count_rows")
+
+    def _uniform_rows(self, batches):
+        """For a list of batches (``None`` = absent): their row matrices, when all present ones have one shape and dtype
+        and need no copy to become row matrices -- otherwise ``None`` (the caller then goes batch by batch)."""
+        rows, like = [], None
+        for x in batches:
+            if x is None:
+                rows.append(None)
+                continue
+            if not x.is_cuda or x.dtype not in _DT:
+                return None
+            r = self._rows(x)
+            if r.data_ptr() != x.data_ptr() or (like is not None and (r.shape != like.shape or r.dtype != like.dtype)):
+                return None
+            like = r
+            rows.append(r)
+        return None if like is None else (rows, like)
+
+    @torch.no_grad()
+    def batch_range_many(self, batches, table: torch.Tensor, first: int, step: int) -> bool:
+        """``batch_range`` of ``batches[k]`` into ``table[first + k * step]`` for all k with one native call; False (and
+        nothing done) when the batches are not uniform enough for that."""
+        import ctypes
+        uniform = self._uniform_rows(batches)
+        if uniform is None:
+            return False
+        rows, like = uniform
+        ptrs = (ctypes.c_void_p * len(rows))(*[None if r is None else r.data_ptr() for r in rows])
+        scratch, _ = self._buffers(like.device)
+        with ops._on(like):
+            check(lib.aq_v2hist_range_many(ptrs, len(rows), _DT[like.dtype], like.shape[1], self.num_histograms,
+                                           table[first].data_ptr(), step * table.stride(0), scratch.data_ptr(),
+                                           torch.cuda.current_stream(like.device).cuda_stream), "aq_v2hist_range_many")
+        return True
+
+    @torch.no_grad()
+    def count_many(self, batches, plans: torch.Tensor, counts: torch.Tensor, first: int, step: int) -> bool:
+        """``count_batch`` of ``batches[k]`` with ``plans[first + k * step]`` into ``counts[first + k * step]``."""
+        import ctypes
+        uniform = self._uniform_rows(batches)
+        if uniform is None:
+            return False
+        rows, like = uniform
+        ptrs = (ctypes.c_void_p * len(rows))(*[None if r is None else r.data_ptr() for r in rows])
+        with ops._on(like):
+            check(lib.aq_v2hist_count_many(ptrs, len(rows), _DT[like.dtype], like.shape[1], self.num_histograms,
+                                           self.num_bins, plans[first].data_ptr(), step * plans.stride(0),
+                                           counts[first].data_ptr(), step * counts.stride(0),
+                                           torch.cuda.current_stream(like.device).cuda_stream), "aq_v2hist_count_many")
+        return True
 
     @torch.no_grad()
     def replay_batches(self, counts: torch.Tensor, plans: torch.Tensor, dtype: torch.dtype = torch.float32) -> None:

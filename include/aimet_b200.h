@@ -464,7 +464,8 @@ int aq_v2hist_update_rows(const void* d_x, int dtype, int64_t n_per_row, int row
  * aq_v2hist_plan_batches -- from all n_batches x rows records, in batch order, the range every batch is counted over
  * (8 floats per batch and histogram: lo, hi, batch min, batch max, any_finite, first, present, 0); (3)
  * aq_v2hist_count_rows -- one batch counted over its plan's range (second pass): bins + 2 integer words per histogram
- * (bins, below / -inf, above / +inf); the workers exchange the counts the same way; (4) aq_v2hist_replay_batches --
+ * (bins, below / -inf, above / +inf), ADDED to d_counts (one launch; the table starts zero-filled, which the exchange by
+ * integer sum needs anyway); the workers exchange the counts the same way; (4) aq_v2hist_replay_batches --
  * collect_stats of the first batch and merge_stats of every later one from the counts, in batch order, one launch.
  * d_states receives what _HistogramObserver.stats holds after the same batches fed one by one; a batch without a finite
  * value sets `error` (the reference raises ValueError for it). */
@@ -472,7 +473,17 @@ int aq_v2hist_range_rows(const void* d_x, int dtype, int64_t n_per_row, int rows
                          void* stream);
 int aq_v2hist_plan_batches(const int32_t* d_ranges, int n_batches, int rows, int bins, float* d_plans, void* stream);
 int aq_v2hist_count_rows(const void* d_x, int dtype, int64_t n_per_row, int rows, int bins, const float* d_plan,
-                         uint32_t* d_counts, void* d_scratch, void* stream);
+                         uint32_t* d_counts, void* stream);
+/* aq_v2hist_range_rows / aq_v2hist_count_rows for a list of m equally shaped batches in one call (d_xs: HOST array of m
+ * device pointers, NULL = no batch at that position): batch i writes the record / counts that start i * stride words
+ * into the table it is given and, for the counts, reads the plan i * plan_stride floats into d_plans -- with the
+ * strides of a worker's share of the global tables (world_size x the size of one batch's entry) a worker fills its
+ * rows of the exchange tables directly. */
+int aq_v2hist_range_many(const void* const* d_xs, int m, int dtype, int64_t n_per_row, int rows, int32_t* d_ranges,
+                         int64_t stride_words, void* d_scratch, void* stream);
+int aq_v2hist_count_many(const void* const* d_xs, int m, int dtype, int64_t n_per_row, int rows, int bins,
+                         const float* d_plans, int64_t plan_stride, uint32_t* d_counts, int64_t count_stride,
+                         void* stream);
 int aq_v2hist_replay_batches(const uint32_t* d_counts, const float* d_plans, int n_batches, int rows, int bins,
                              aq_v2hist_head_t* d_states, int64_t block_stride, void* stream);
 int aq_v2hist_sqnr_rows(const aq_v2hist_head_t* d_stats, int64_t block_stride, int rows, int bins, double num_steps,
