@@ -647,6 +647,31 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_merge_kernel(const V2HistS
     v2h_merge_step(counts, umin, umax, sc->plan[4] != 0.0f, nb, state, updates);
 }
 
+// The tail of a fused update in one launch: the batch's own statistics from the first set of counters, then the merge
+// from the second set (they write different blocks).
+__global__ void __launch_bounds__(kV2HistThreads) v2h_finish_update_kernel(const V2HistScratch* __restrict__ sc, int nb,
+                                                                           aq_v2hist_head_t* __restrict__ batch,
+                                                                           aq_v2hist_head_t* __restrict__ state,
+                                                                           float* __restrict__ updates, V2HRows rw)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    sc    = v2h_row(sc, rw.sc_stride);
+    batch = v2h_row(batch, rw.st_stride);
+    state = v2h_row(state, rw.st_stride);
+    updates += (int64_t) blockIdx.y * rw.upd_stride;
+    const bool any = sc->plan[4] != 0.0f;
+    v2h_collect_step(sc->counts, sc->plan[2], sc->plan[3], any, nb, batch);
+    if (!any)
+    {
+        // nothing finite in the batch: the reference raises; here the state is flagged and left as it is
+        if (threadIdx.x == 0)
+            state->error = 1;
+        return;
+    }
+    v2h_merge_step(sc->counts2, sc->plan[5], sc->plan[6], true, nb, state, updates);
+}
+
 __global__ void __launch_bounds__(kV2HistThreads) v2h_copy_kernel(const aq_v2hist_head_t* __restrict__ src, int nb,
                                                                   aq_v2hist_head_t* __restrict__ dst, V2HRows rw)
 {
@@ -884,11 +909,8 @@ int v2hist_update_rows(const void* x, int dtype, int64_t n, int rows, int nb, aq
     int rc = v2h_passes_any(x, dtype, n, rows, nb, 2, state, nullptr, sc, rw, st);
     if (rc != AQ_OK)
         return rc;
-    launch_pdl(v2h_finish_collect_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb,
-               batch, rw);
-    note_launch();
-    launch_pdl(v2h_merge_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb, state,
-               updates, rw, 1);
+    launch_pdl(v2h_finish_update_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, (const V2HistScratch*) sc, nb,
+               batch, state, updates, rw);
     note_launch();
     return check_launch();
 }

@@ -387,7 +387,8 @@ def _block_words(num_bins: int) -> int:
 
 
 def _new_blocks(count: int, num_bins: int, device) -> torch.Tensor:
-    return torch.zeros((count, _block_words(num_bins)), dtype=torch.int32, device=device)
+    """Statistics blocks for the kernels to fill (every field of a block is written by the launch that produces it)."""
+    return torch.empty((count, _block_words(num_bins)), dtype=torch.int32, device=device)
 
 
 class _HistogramObserver:
