@@ -979,49 +979,66 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_range_kernel(const V2HistS
     range[3] = 1;
 }
 
-// One thread per histogram walks the batches in order.
+// One CTA per histogram walks the batches in order: the records of a stretch of batches are staged in shared memory
+// by all threads, one thread scans them (the scan is a chain of a few compares per batch), all threads write the plans.
+constexpr int kV2HistPlanChunk = 512;
 __global__ void __launch_bounds__(kV2HistThreads) v2h_plan_batches_kernel(const int32_t* __restrict__ ranges, int n_batches,
                                                                           int rows, int nb, float* __restrict__ plans)
 {
     pdl_launch_dependents();
     pdl_wait();
-    const int r = blockIdx.x * kV2HistThreads + threadIdx.x;
-    if (r >= rows)
-        return;
-    bool have = false;
+    __shared__ int32_t s_rg[kV2HistPlanChunk * 4];
+    __shared__ float s_pl[kV2HistPlanChunk * 8];
+    const int r = blockIdx.y;
+    bool have = false;   // thread 0's scan state, carried from chunk to chunk
     float smin = 0.0f, smax = 0.0f;
-    for (int b = 0; b < n_batches; ++b)
+    for (int b0 = 0; b0 < n_batches; b0 += kV2HistPlanChunk)
     {
-        const int32_t* rg = ranges + ((int64_t) b * rows + r) * 4;
-        float* pl         = plans + ((int64_t) b * rows + r) * 8;
-        const bool present = rg[3] != 0, any = rg[2] != 0;
-        const float mn = __int_as_float(rg[0]), mx = __int_as_float(rg[1]);
-        float lo = 0.0f, hi = 1.0f;
-        bool first = false;
-        if (present && any)
+        const int m = n_batches - b0 < kV2HistPlanChunk ? n_batches - b0 : kV2HistPlanChunk;
+        for (int i = threadIdx.x; i < m * 4; i += kV2HistThreads)
+            s_rg[i] = ranges[((int64_t) (b0 + (i >> 2)) * rows + r) * 4 + (i & 3)];
+        __syncthreads();
+        if (threadIdx.x == 0)
         {
-            if (!have)
+            for (int k = 0; k < m; ++k)
             {
-                // collect_stats: first and last edge of _create_bin_edges(min, max)
-                float a0 = mn, b0 = mx;
-                if (a0 == b0)
-                    a0 = __fsub_rn(a0, 0.5f), b0 = __fadd_rn(b0, 0.5f);
-                const float step = __fdiv_rn(__fsub_rn(b0, a0), (float) nb);
-                lo               = __fadd_rn(__fmul_rn(0.0f, step), a0);
-                hi               = __fadd_rn(__fmul_rn((float) nb, step), a0);
-                smin = mn, smax = mx;
-                have = first = true;
-            }
-            else
-            {
-                // Python min(new, cur) / max(new, cur): the second argument wins only when strictly smaller / larger
-                lo   = (smin < mn) ? smin : mn;
-                hi   = (smax > mx) ? smax : mx;
-                smin = lo, smax = hi;
+                const int32_t* rg  = s_rg + k * 4;
+                float* pl          = s_pl + k * 8;
+                const bool present = rg[3] != 0, any = rg[2] != 0;
+                const float mn = __int_as_float(rg[0]), mx = __int_as_float(rg[1]);
+                float lo = 0.0f, hi = 1.0f;
+                bool first = false;
+                if (present && any)
+                {
+                    if (!have)
+                    {
+                        // collect_stats: first and last edge of _create_bin_edges(min, max)
+                        float a0 = mn, b1 = mx;
+                        if (a0 == b1)
+                            a0 = __fsub_rn(a0, 0.5f), b1 = __fadd_rn(b1, 0.5f);
+                        const float step = __fdiv_rn(__fsub_rn(b1, a0), (float) nb);
+                        lo               = __fadd_rn(__fmul_rn(0.0f, step), a0);
+                        hi               = __fadd_rn(__fmul_rn((float) nb, step), a0);
+                        smin = mn, smax = mx;
+                        have = first = true;
+                    }
+                    else
+                    {
+                        // Python min(new, cur) / max(new, cur): the second argument wins only when strictly smaller /
+                        // larger
+                        lo   = (smin < mn) ? smin : mn;
+                        hi   = (smax > mx) ? smax : mx;
+                        smin = lo, smax = hi;
+                    }
+                }
+                pl[0] = lo, pl[1] = hi, pl[2] = mn, pl[3] = mx;
+                pl[4] = any ? 1.0f : 0.0f, pl[5] = first ? 1.0f : 0.0f, pl[6] = present ? 1.0f : 0.0f, pl[7] = 0.0f;
             }
         }
-        pl[0] = lo, pl[1] = hi, pl[2] = mn, pl[3] = mx;
-        pl[4] = any ? 1.0f : 0.0f, pl[5] = first ? 1.0f : 0.0f, pl[6] = present ? 1.0f : 0.0f, pl[7] = 0.0f;
+        __syncthreads();
+        for (int i = threadIdx.x; i < m * 8; i += kV2HistThreads)
+            plans[((int64_t) (b0 + (i >> 3)) * rows + r) * 8 + (i & 7)] = s_pl[i];
+        __syncthreads();
     }
 }
 
@@ -1029,7 +1046,8 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_plan_batches_kernel(const 
 // t + 256 j) and only a change of range goes through shared memory, where one thread re-bins the old counts in the
 // reference's order; a batch inside the current range costs one coalesced read of its counts and one addition per bin,
 // with no barrier.  Bin edges are written once, at the end (they follow from min / max alone).
-constexpr int kV2HistPerThread = (AQ_V2HIST_MAX_BINS + kV2HistThreads - 1) / kV2HistThreads;
+constexpr int kV2HistPerThread   = (AQ_V2HIST_MAX_BINS + kV2HistThreads - 1) / kV2HistThreads;
+constexpr int kV2HistReplayChunk = 256;   // batches whose plans are staged in shared memory at a time
 __global__ void __launch_bounds__(kV2HistThreads) v2h_replay_kernel(const uint32_t* __restrict__ counts,
                                                                     const float* __restrict__ plans, int n_batches, int rows,
                                                                     int nb, aq_v2hist_head_t* __restrict__ state,
@@ -1038,18 +1056,48 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_replay_kernel(const uint32
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float s_hist[AQ_V2HIST_MAX_BINS], s_upd[AQ_V2HIST_MAX_BINS];
+    __shared__ float s_plan[kV2HistReplayChunk * 8];
     const int r = blockIdx.y;
     state       = v2h_row(state, st_stride);
     float h[kV2HistPerThread];
+    uint32_t nxt[kV2HistPerThread];   // the next batch's counts, fetched while this batch is folded in
+    uint32_t nxt_below = 0, nxt_above = 0;
 #pragma unroll
     for (int j = 0; j < kV2HistPerThread; ++j)
-        h[j] = 0.0f;
+        h[j] = 0.0f, nxt[j] = 0;
+    auto fetch = [&](int b) {
+        const uint32_t* cn = counts + ((int64_t) b * rows + r) * (nb + 2);
+#pragma unroll
+        for (int j = 0; j < kV2HistPerThread; ++j)
+        {
+            const int i = threadIdx.x + j * kV2HistThreads;
+            if (i < nb)
+                nxt[j] = cn[i];
+        }
+        nxt_below = cn[nb], nxt_above = cn[nb + 1];
+    };
     float smin = 0.0f, smax = 0.0f;
     int initialized = 0, error = 0;
+    fetch(0);
     for (int b = 0; b < n_batches; ++b)
     {
-        const float* pl    = plans + ((int64_t) b * rows + r) * 8;
-        const uint32_t* cn = counts + ((int64_t) b * rows + r) * (nb + 2);
+        if (b % kV2HistReplayChunk == 0)
+        {
+            // the plans of the next stretch of batches, staged by all threads
+            __syncthreads();
+            const int m = n_batches - b < kV2HistReplayChunk ? n_batches - b : kV2HistReplayChunk;
+            for (int i = threadIdx.x; i < m * 8; i += kV2HistThreads)
+                s_plan[i] = plans[((int64_t) (b + (i >> 3)) * rows + r) * 8 + (i & 7)];
+            __syncthreads();
+        }
+        const float* pl = s_plan + (b % kV2HistReplayChunk) * 8;
+        uint32_t cur[kV2HistPerThread];
+#pragma unroll
+        for (int j = 0; j < kV2HistPerThread; ++j)
+            cur[j] = nxt[j];
+        const float below = (float) nxt_below, above = (float) nxt_above;
+        if (b + 1 < n_batches)
+            fetch(b + 1);
         if (pl[6] == 0.0f)
             continue;
         if (pl[4] == 0.0f)
@@ -1060,12 +1108,7 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_replay_kernel(const uint32
         const bool first = pl[5] != 0.0f;
         const float umin = first ? pl[2] : pl[0], umax = first ? pl[3] : pl[1];
         if (first)
-        {
-#pragma unroll
-            for (int j = 0; j < kV2HistPerThread; ++j)
-                h[j] = 0.0f;
             initialized = 1;
-        }
         else if (!(umin == smin && umax == smax))
         {
             // block-uniform: the range grows
@@ -1089,15 +1132,14 @@ __global__ void __launch_bounds__(kV2HistThreads) v2h_replay_kernel(const uint32
             }
         }
         // collect_stats: float(counts), then the elements beyond the edges; merge_stats: float(counts) + re-binned old
-        // counts, then the infinities -- the same three additions in the same order (the first batch adds to zero)
-        const float below = (float) cn[nb], above = (float) cn[nb + 1];
+        // counts, then the infinities -- the same additions in the same order (the first batch has no old counts)
 #pragma unroll
         for (int j = 0; j < kV2HistPerThread; ++j)
         {
             const int i = threadIdx.x + j * kV2HistThreads;
             if (i < nb)
             {
-                float v = first ? (float) cn[i] : __fadd_rn((float) cn[i], h[j]);
+                float v = first ? (float) cur[j] : __fadd_rn((float) cur[j], h[j]);
                 if (i == 0)
                     v = __fadd_rn(v, below);
                 if (i == nb - 1)
@@ -1144,8 +1186,10 @@ int v2hist_plan_batches(const int32_t* ranges, int n_batches, int rows, int nb, 
 {
     if (n_batches < 1 || rows < 1)
         return AQ_ERR_INVALID_ARG;
-    launch_pdl(v2h_plan_batches_kernel, dim3((unsigned) ((rows + kV2HistThreads - 1) / kV2HistThreads)), kV2HistThreads, 0,
-               st, ranges, n_batches, rows, nb, plans);
+    if (rows > 65535)
+        return AQ_ERR_TOO_LARGE;
+    launch_pdl(v2h_plan_batches_kernel, dim3(1, (unsigned) rows), kV2HistThreads, 0, st, ranges, n_batches, rows, nb,
+               plans);
     note_launch();
     return check_launch();
 }
