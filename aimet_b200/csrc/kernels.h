@@ -41,6 +41,7 @@ struct V2Args
     double qmin_wide, qmax_wide;   // the same bounds for the float64 form (grids of 2^24 steps or more)
     int out_kind;
     int dequant_only;
+    int wide_ok;   // x and y are 32-byte aligned (set by the launcher): adjacent packets may move as one 32-byte access
     ChanGeom geom;
 };
 int v2_launch(V2Args a, int dtype, int narrow_internal, cudaStream_t st);

@@ -243,6 +243,30 @@ __device__ __forceinline__ void store_packet(T* __restrict__ y, int64_t idx, int
     }
 }
 
+// Two adjacent 16-byte packets of one thread as ONE 32-byte access (sm_100 ld / st.global.v8.b32): with the adjacent
+// layout a warp's 16-byte accesses cover every 32-byte sector only half, two instructions per sector; the wide form
+// touches whole sectors once.  The address must be 32-byte aligned.
+template <typename T, int VEC>
+__device__ __forceinline__ void load_pack_pair(const T* p, Pack<T, VEC>& a, Pack<T, VEC>& b)
+{
+    static_assert(sizeof(Pack<T, VEC>) == 16, "16-byte packets only");
+    uint32_t* ra = reinterpret_cast<uint32_t*>(&a);
+    uint32_t* rb = reinterpret_cast<uint32_t*>(&b);
+    asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(ra[0]), "=r"(ra[1]), "=r"(ra[2]), "=r"(ra[3]), "=r"(rb[0]), "=r"(rb[1]), "=r"(rb[2]), "=r"(rb[3])
+                 : "l"(p));
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_pack_pair(T* p, const Pack<T, VEC>& a, const Pack<T, VEC>& b)
+{
+    static_assert(sizeof(Pack<T, VEC>) == 16, "16-byte packets only");
+    const uint32_t* ra = reinterpret_cast<const uint32_t*>(&a);
+    const uint32_t* rb = reinterpret_cast<const uint32_t*>(&b);
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(ra[0]), "r"(ra[1]), "r"(ra[2]),
+                 "r"(ra[3]), "r"(rb[0]), "r"(rb[1]), "r"(rb[2]), "r"(rb[3])
+                 : "memory");
+}
+
 // =================================================================================================
 // libpymo semantics: quantizeValueCpu + dequantizeValueCpu (DlQuantization/src/trim_functions.cpp:140-171)
 //   t = fmax(fmin(x, max), min);  u = t / delta - offset;  q = roundf(u);  y = delta * (q + offset)
@@ -598,7 +622,23 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
     // per channel: the element loads go out first and the encodings are fetched while they are in flight
     Pack<T, VEC> v[U];
     bool full[U];
-    load_chunk<T, VEC, U, ADJ>(static_cast<const T*>(a.x), base, hi, v, full);
+    // adjacent layout, two 16-byte packets per thread, both inside the tensor, 32-byte aligned tensors: one 32-byte
+    // access each way (the mask, when there is one, keeps its narrower packets)
+    constexpr bool kPairable = ADJ && U == 2 && sizeof(Pack<T, VEC>) == 16;
+    bool paired              = false;
+    if constexpr (kPairable)
+    {
+        const int64_t first = base + (int64_t) packet_offset<VEC, U, true>(0);
+        paired              = a.wide_ok && first + 2 * VEC <= hi;
+        if (paired)
+        {
+            load_pack_pair<T, VEC>(static_cast<const T*>(a.x) + first, v[0], v[U - 1]);
+            full[0] = full[U - 1] = true;
+        }
+    }
+    if (!paired)
+        load_chunk<T, VEC, U, ADJ>(static_cast<const T*>(a.x), base, hi, v, full);
+    Pack<T, VEC> held;   // the first packet's result, kept until its neighbour is ready
     if (PER_CH == 1)
     {
         rc = make_run_ctx<VEC>(a.geom, base, hi);
@@ -708,7 +748,20 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
         }
         Pack<T, VEC> r;
         repack<T, VEC>(y, r);
-        store_packet<T, VEC>(static_cast<T*>(a.y), idx, hi, r, full[u]);
+        bool stored = false;
+        if constexpr (kPairable)
+        {
+            if (paired)
+            {
+                if (u == 0)
+                    held = r;
+                else
+                    store_pack_pair<T, VEC>(static_cast<T*>(a.y) + (idx - VEC), held, r);
+                stored = true;
+            }
+        }
+        if (!stored)
+            store_packet<T, VEC>(static_cast<T*>(a.y), idx, hi, r, full[u]);
         if (MASK)
         {
             Pack<uint8_t, VEC> mp;
@@ -761,7 +814,8 @@ static int launch_v2_vec(V2Args a, int vec, bool narrow, cudaStream_t st)
 {
     // more than 16 runs per tile, each a whole number of thread shares: per-thread encoding loads instead of
     // shared-memory staging (block 64 on a [4096,11008] bf16 weight: 40.9 us per thread, 50.2 us staged; forcing 6 or 8
-    // CTAs per SM on the per-thread form, which needs 47 registers, spills and ends at 42 us)
+    // CTAs per SM on the per-thread form spilled and ended at 42 us; moving a thread's two adjacent packets as one 32-byte
+    // access brought it to 36.6 us)
 #define AQ_LAUNCH(V)                                                                                                 \
     {                                                                                                                \
         a.geom = make_geom(a.geom.num_ch, a.geom.inner, chunk_elems<V>(), a.n);                                      \
@@ -785,6 +839,7 @@ template <typename T>
 static int launch_v2_t(V2Args a, bool narrow, cudaStream_t st)
 {
     const bool per_ch = a.geom.num_ch > 1;
+    a.wide_ok         = ((uintptr_t) a.x % 32 == 0 && (uintptr_t) a.y % 32 == 0) ? 1 : 0;
     // the mask is written with VEC-byte packets, so it constrains the width like the tensors do
     int vec = pick_vec<T>(a.x, a.y, nullptr, per_ch ? a.geom.inner : 0);
     while (vec > 1 && a.mask && ((uintptr_t) a.mask % vec))
