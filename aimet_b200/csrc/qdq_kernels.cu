@@ -27,7 +27,7 @@ constexpr int kThreads = 256;
 #define AQ_UNROLL4 4
 #endif
 #ifndef AQ_UNROLL8_PER_TENSOR
-#define AQ_UNROLL8_PER_TENSOR 1
+#define AQ_UNROLL8_PER_TENSOR 2
 #endif
 // 16-byte packets in flight per thread, by packet width in elements (8 = 16-bit types)
 template <int VEC>
@@ -35,10 +35,9 @@ __host__ __device__ constexpr int unroll_of()
 {
     return VEC == 8 ? AQ_UNROLL8 : AQ_UNROLL4;
 }
-// v2 forward with one encoding for the whole tensor and 16-bit elements: one packet per thread and twice the CTAs
-// (measured on a [4096,11008] bf16 weight: 31.1 us against 34.1 us with two packets per thread; the blockwise form of
-// the same weight is the other way round, 40.9 us against 43.1 us, because its per-thread encoding fetch is shared
-// by both packets).
+// v2 forward with one encoding for the whole tensor and 16-bit elements: two ADJACENT packets per thread, moved as one
+// 32-byte access each way (measured on a [4096,11008] bf16 weight: 29.0 us; one 16-byte packet per thread 31.3 us; two
+// interleaved 16-byte packets per thread 34.1 us).
 template <int VEC, int PER_CH>
 __host__ __device__ constexpr int v2_unroll()
 {
@@ -616,7 +615,8 @@ __global__ void __launch_bounds__(kThreads) v2_kernel(V2Args a)
     __shared__ V2Slot s_slot[PER_CH == 1 ? kMaxRuns : 1];
     RunCtx rc {0, 0, 1, 0};
     V2Slot k0;
-    constexpr bool ADJ = PER_CH == 2;
+    // adjacent packets: blockwise (one encoding per thread) and the 16-bit per-tensor form (for its 32-byte accesses)
+    constexpr bool ADJ = PER_CH == 2 || (PER_CH == 0 && VEC == 8 && U == 2);
     if (!PER_CH)
         k0 = v2_load(a.scale, a.offset, 0, qmin, qmax);
     // per channel: the element loads go out first and the encodings are fetched while they are in flight
