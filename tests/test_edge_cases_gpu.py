@@ -90,3 +90,35 @@ def test_one_element_per_channel_and_tiny_channels(cuda):
         got = b200.quantize_dequantize(torch.from_numpy(x).to(cuda), torch.from_numpy(scale).to(cuda),
                                        torch.from_numpy(offset).to(cuda), -8, 7)
         assert_bits_equal(got.cpu().numpy(), want, f"{shape} / {enc}")
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("shift", [0, 8, 16, 24])
+@pytest.mark.parametrize("rows", [1, 33, 1000])
+def test_16bit_forward_at_every_32_byte_phase(cuda, dtype, shift, rows):
+    """The 16-bit forward moves a thread's two adjacent packets as one 32-byte access when input and output are 32-byte
+    aligned and keeps 16-byte accesses otherwise; tensors that start 0, 16, 32 or 48 bytes past a 64-byte boundary, with
+    whole and ragged last tiles, per tensor and in blocks of 64, must give the same bits either way."""
+    import aimet_b200.v2.backend as b200
+    from oracle import v2_oracle as v2
+    tdt = getattr(torch, dtype)
+    cols = 192
+    n = rows * cols
+    base = v2.to_storage(normal(n + 32, seed=rows + shift, scale=0.05), dtype)
+    xn = base[shift:shift + n].reshape(rows, cols)
+    hold = torch.from_numpy(base).to(cuda).to(tdt)
+    xd = hold[shift:shift + n].view(rows, cols)
+    assert xd.data_ptr() % 64 == (2 * shift) % 64
+    # per tensor, 16-bit grid (the wide guard band) and 8-bit grid
+    for qmin, qmax, sc, of in ((0, 65535, 3.1e-6, -32768.0), (-128, 127, 1.7e-3, 3.0)):
+        want, _ = v2.quantize_dequantize(xn, np.array(np.float32(sc)), np.array(np.float32(of)), qmin, qmax, None, dtype)
+        got = b200.quantize_dequantize(xd, torch.tensor(sc, device=cuda), torch.tensor(of, device=cuda), qmin, qmax)
+        assert got.dtype == tdt
+        assert_bits_equal(got.float().cpu().numpy(), want, f"per tensor [{qmin}, {qmax}]")
+    # blocks of 64 along the last axis, 4-bit symmetric grid
+    scale = (np.abs(normal((rows, cols // 64), 7, 0.004)) + np.float32(0.002)).astype(np.float32)
+    offset = np.zeros_like(scale)
+    want, _ = v2.quantize_dequantize(xn, scale, offset, -8, 7, [1, 64], dtype)
+    got = b200.quantize_dequantize(xd, torch.from_numpy(scale).to(cuda), torch.from_numpy(offset).to(cuda), -8, 7,
+                                   block_size=[1, 64])
+    assert_bits_equal(got.float().cpu().numpy(), want, "blocks of 64")
