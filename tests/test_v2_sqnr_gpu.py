@@ -167,3 +167,30 @@ def test_counting_pass_with_values_on_bin_edges(cuda, bins, edge_share):
     wide[0] += 1
     wide[-1] += 1
     assert_bits_equal(obs.get_stats()[0].histogram.cpu().numpy(), (wide + first).numpy(), "merged histogram")
+
+
+@pytest.mark.parametrize("shape,enc", [((5, 77), (5, 1)), ((3, 1001), (3, 1)), ((1, 4099), (1,))])
+@pytest.mark.parametrize("shift", [0, 1, 3])
+def test_observer_on_odd_row_lengths_and_unaligned_starts(cuda, shape, enc, shift):
+    """Rows whose length is no multiple of the packet width, and tensors that start off a 16-byte boundary, take the
+    element-wise forms of the two passes; statistics must equal the CPU restatement of the reference observer (which
+    tests/test_oracle_pin.py pins to the reference class) after every update."""
+    from oracle import v2_hist_oracle as vh
+    from aimet_b200.v2.encoding_analyzer import _HistogramObserver
+    bins = 64
+    n = int(np.prod(shape))
+    rng = np.random.default_rng(shift + n)
+    obs = _HistogramObserver(enc, bins)
+    state = [None] * shape[0]
+    for b in range(3):
+        base = (rng.standard_normal(n + 4) * (1.0 + b)).astype(np.float32)
+        base[5] = 0.0
+        x = base[shift:shift + n].reshape(shape)
+        xd = torch.from_numpy(base).to(cuda)[shift:shift + n].view(shape)
+        obs.update_stats(xd)
+        got = obs.get_stats()
+        for r in range(shape[0]):
+            state[r] = vh.merge(state[r], x[r], bins)
+            assert_bits_equal(got[r].histogram.cpu().numpy(), state[r].hist, f"batch {b} row {r} histogram")
+            assert_bits_equal(got[r].bin_edges.cpu().numpy(), state[r].edges, f"batch {b} row {r} edges")
+            assert got[r].min.item() == float(state[r].min) and got[r].max.item() == float(state[r].max)
