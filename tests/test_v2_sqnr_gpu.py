@@ -194,3 +194,27 @@ def test_observer_on_odd_row_lengths_and_unaligned_starts(cuda, shape, enc, shif
             assert_bits_equal(got[r].histogram.cpu().numpy(), state[r].hist, f"batch {b} row {r} histogram")
             assert_bits_equal(got[r].bin_edges.cpu().numpy(), state[r].edges, f"batch {b} row {r} edges")
             assert got[r].min.item() == float(state[r].min) and got[r].max.item() == float(state[r].max)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("edge_share", [0.5, 1e-3, 0.0])
+def test_16bit_inputs_count_like_their_float32_values(cuda, dtype, edge_share):
+    """The reference upcasts the input before torch.histc, so a 16-bit batch must give the statistics of the same
+    values held in float32 (whose path the reference fixtures pin) -- through the 8-elements-per-packet forms of both
+    passes, with values on bin edges, infinities and a NaN."""
+    from aimet_b200.v2.encoding_analyzer import _HistogramObserver
+    g = torch.Generator().manual_seed(11)
+    bins, n = 128, 1_000_003
+    o16, o32 = _HistogramObserver((1,), bins), _HistogramObserver((1,), bins)
+    for b in range(3):
+        x = torch.rand(n, generator=g) * bins * (1 + b)
+        x = torch.where(torch.rand(n, generator=g) < edge_share, torch.floor(x), x)
+        x[0], x[1] = 0.0, float(bins * (1 + b))
+        x[7], x[9], x[11] = float("inf"), float("-inf"), float("nan")
+        x16 = x.to(dtype).to(cuda)
+        o16.update_stats(x16)
+        o32.update_stats(x16.float())
+        a, c = o16.get_stats()[0], o32.get_stats()[0]
+        assert_bits_equal(a.histogram.cpu().numpy(), c.histogram.cpu().numpy(), f"batch {b} histogram")
+        assert_bits_equal(a.bin_edges.cpu().numpy(), c.bin_edges.cpu().numpy(), f"batch {b} edges")
+        assert float(a.min) == float(c.min) and float(a.max) == float(c.max)
